@@ -1,0 +1,705 @@
+/*
+ * stark_oracle.c -- CPU restatement of the reference token-loop arithmetic.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA path is compared
+ * against (tests, the smoke check, and the `cpu_baseline` / `--impl reference`
+ * legs of the benchmark).  Nothing in the shipped library links, loads or calls
+ * it, and the shipped library has no CPU fallback.
+ *
+ * The reference (jshahbazi/stark) is Rust; it cannot be compiled where this
+ * repository is built, so each function below restates one reference routine
+ * and names it (paths are relative to the reference's repository root).  The
+ * restatement is pinned by the reference's own known answers:
+ *   - packed_code vectors            crates/stark-engine/src/backends/cpu/kernel/matmul/reference.rs:195-219
+ *   - exact packed tails             .../matmul/reference.rs:240-285
+ *   - GGUF block SHA-256 table       crates/stark-engine/src/engine/hybrid/weights.rs:3183-3221
+ *   - MLX plane layout closed forms  crates/stark-engine/src/engine/hybrid/weights.rs:4044-4083
+ *   - softmax / top-k / rms KATs     crates/stark-engine/src/engine/hybrid/math.rs:72-99
+ * Parts that depend on the platform libm (sinf/cosf/expf/powf in RoPE tables,
+ * SiLU and softmax) follow the reference's formulas and operation order, but a
+ * last-bit difference between libm implementations cannot be excluded there.
+ *
+ * Build with -ffp-contract=off: Rust never contracts a*b+c into an FMA.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define SO_OK 0
+#define SO_INVALID 1
+
+/* ------------------------------------------------------------------ scalars */
+
+/* half::bf16::to_f32 */
+static inline float bf16_to_f32(uint16_t h) {
+    uint32_t u = (uint32_t)h << 16;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+/* half::bf16::from_f32: round to nearest even, NaN kept quiet. */
+static inline uint16_t f32_to_bf16(float f) {
+    uint32_t u;
+    memcpy(&u, &f, 4);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x0040u);
+    uint32_t round_bit = 0x00008000u;
+    if ((u & round_bit) != 0 && (u & (3u * round_bit - 1u)) != 0) return (uint16_t)((u >> 16) + 1u);
+    return (uint16_t)(u >> 16);
+}
+
+static inline float bf16_round(float f) { return bf16_to_f32(f32_to_bf16(f)); }
+
+/* half::f16::to_f32 */
+static inline float f16_to_f32(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu;
+    uint32_t man = h & 0x3ffu;
+    uint32_t u;
+    if (exp == 0) {
+        if (man == 0) {
+            u = sign;
+        } else {
+            int e = -1;
+            do {
+                e++;
+                man <<= 1;
+            } while ((man & 0x400u) == 0);
+            u = sign | ((uint32_t)(127 - 15 - e) << 23) | ((man & 0x3ffu) << 13);
+        }
+    } else if (exp == 31) {
+        u = sign | 0x7f800000u | (man << 13);
+    } else {
+        u = sign | ((exp + 112u) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+uint16_t so_f32_to_bf16(float f) { return f32_to_bf16(f); }
+float so_bf16_to_f32(uint16_t h) { return bf16_to_f32(h); }
+float so_f16_to_f32(uint16_t h) { return f16_to_f32(h); }
+
+/* ------------------------------------------------------- integer unpacking */
+
+/* packed_code: crates/stark-engine/src/backends/cpu/kernel/matmul/reference.rs:91-104.
+ * Code `index` starts at bit index*bits, LSB first inside little-endian bytes. */
+uint8_t so_packed_code(const uint8_t *codes, size_t bits, size_t index) {
+    size_t bit = index * bits;
+    size_t offset = bit / 8;
+    size_t shift = bit % 8;
+    uint16_t value = codes[offset];
+    if (shift + bits > 8) value |= (uint16_t)codes[offset + 1] << 8;
+    return (uint8_t)((value >> shift) & ((1u << bits) - 1u));
+}
+
+void so_unpack_codes(const uint8_t *codes, size_t bits, size_t count, uint8_t *out) {
+    for (size_t i = 0; i < count; i++) out[i] = so_packed_code(codes, bits, i);
+}
+
+/* ------------------------------------------------------ MLX-affine matvec */
+
+/* Path A: MatmulCpuKernel quantized branch,
+ * crates/stark-engine/src/backends/cpu/kernel/matmul/kernel.rs:168-285.
+ *   acc(f32) += f32(a[m,k]) * (scale*f32(q) + bias), k ascending; output RNE to bf16.
+ * scale_layout 0: planes [N, G]  (MLX native, output_stride = G, group_stride = 1)
+ * scale_layout 1: planes [G, npad] (GroupOutput layout, crates/stark-engine/src/backends/common/kernel/matmul/mod.rs:120-156)
+ * correction 0: explicit bias plane; 1: symmetric (bias = -scale*2^(bits-1)).
+ * signed_codes: code ^= 1 << (bits-1) before widening (kernel.rs:233-235). */
+int so_affine_matvec_bf16(const uint8_t *codes, const uint16_t *scales, const uint16_t *biases, const uint16_t *a,
+                          uint16_t *d, uint32_t m, uint32_t n, uint32_t k, uint32_t bits, uint32_t group,
+                          uint32_t scale_layout, uint32_t npad, uint32_t correction, uint32_t signed_codes,
+                          int threads) {
+    if (!(bits == 4 || bits == 8) || group == 0 || k % group != 0) return SO_INVALID;
+    const size_t groups = k / group;
+    const size_t out_stride = scale_layout == 0 ? groups : 1;
+    const size_t grp_stride = scale_layout == 0 ? 1 : npad;
+    const float midpoint = (float)(1u << (bits - 1));
+    (void)threads;
+#pragma omp parallel for num_threads(threads > 0 ? threads : 1) schedule(static)
+    for (int64_t col = 0; col < (int64_t)n; col++) {
+        for (uint32_t row = 0; row < m; row++) {
+            float acc = 0.0f;
+            for (uint32_t inner = 0; inner < k; inner++) {
+                float a_value = bf16_to_f32(a[(size_t)row * k + inner]);
+                uint8_t code = so_packed_code(codes, bits, (size_t)col * k + inner);
+                if (signed_codes) code ^= (uint8_t)(1u << (bits - 1));
+                float q = (float)code;
+                size_t meta = (size_t)col * out_stride + (inner / group) * grp_stride;
+                float scale = bf16_to_f32(scales[meta]);
+                float bias_term = correction == 0 ? bf16_to_f32(biases[meta]) : -scale * midpoint;
+                float b_value = scale * q + bias_term;
+                acc += a_value * b_value;
+            }
+            d[(size_t)row * n + col] = f32_to_bf16(1.0f * acc);
+        }
+    }
+    return SO_OK;
+}
+
+/* Path B: Weights::affine_row + matrix_slice host branch,
+ * crates/stark-engine/src/engine/hybrid/weights.rs:1284-1309, 2534-2552.
+ * Decode a whole row to f32 (scale*q+bias), then sum(w*x) sequentially in f32.
+ * plane_kind: 0 = f32, 1 = f16, 30 = bf16 (weights.rs:1207). */
+static inline float plane_scalar(uint32_t kind, const void *base, size_t index) {
+    if (kind == 0) return ((const float *)base)[index];
+    if (kind == 1) return f16_to_f32(((const uint16_t *)base)[index]);
+    return bf16_to_f32(((const uint16_t *)base)[index]);
+}
+
+int so_affine_matvec_f32(const uint8_t *codes, const void *scales, const void *biases, uint32_t plane_kind,
+                         const float *x, float *y, uint32_t rows, uint32_t columns, uint32_t bits, uint32_t group,
+                         int threads) {
+    if (!(bits == 4 || bits == 8) || !(group == 32 || group == 64 || group == 128) || columns % group != 0)
+        return SO_INVALID;
+    for (uint32_t i = 0; i < columns; i++)
+        if (!isfinite(x[i])) return SO_INVALID;
+    const size_t group_count = columns / group;
+    const size_t packed_row = (size_t)columns * bits / 8;
+    (void)threads;
+#pragma omp parallel for num_threads(threads > 0 ? threads : 1) schedule(static)
+    for (int64_t row = 0; row < (int64_t)rows; row++) {
+        const uint8_t *row_codes = codes + (size_t)row * packed_row;
+        float total = 0.0f;
+        for (uint32_t column = 0; column < columns; column++) {
+            size_t index = (size_t)row * group_count + column / group;
+            float scale = plane_scalar(plane_kind, scales, index);
+            float bias = plane_scalar(plane_kind, biases, index);
+            uint8_t q = (uint8_t)((row_codes[(size_t)column * bits / 8] >> ((size_t)column * bits % 8)) &
+                                  (uint8_t)((1u << bits) - 1u));
+            float w = scale * (float)q + bias;
+            total += w * x[column];
+        }
+        y[row] = total;
+    }
+    return SO_OK;
+}
+
+/* Dequantize one affine row (for the plane-layout known answers). */
+int so_affine_row_f32(const uint8_t *codes, const void *scales, const void *biases, uint32_t plane_kind, float *out,
+                      uint32_t row, uint32_t columns, uint32_t bits, uint32_t group) {
+    if (!(bits == 4 || bits == 8) || columns % group != 0) return SO_INVALID;
+    const size_t group_count = columns / group;
+    const uint8_t *row_codes = codes + (size_t)row * columns * bits / 8;
+    for (uint32_t column = 0; column < columns; column++) {
+        size_t index = (size_t)row * group_count + column / group;
+        uint8_t q = (uint8_t)((row_codes[(size_t)column * bits / 8] >> ((size_t)column * bits % 8)) &
+                              (uint8_t)((1u << bits) - 1u));
+        out[column] = plane_scalar(plane_kind, scales, index) * (float)q + plane_scalar(plane_kind, biases, index);
+    }
+    return SO_OK;
+}
+
+/* ------------------------------------------------------------ GGUF blocks */
+
+/* block_layout: crates/stark-engine/src/engine/hybrid/weights.rs:2565-2584 (kinds 8 and 12 only). */
+int so_block_layout(uint32_t kind, uint32_t *elements, uint32_t *bytes) {
+    if (kind == 8) {
+        *elements = 32;
+        *bytes = 34;
+        return SO_OK;
+    }
+    if (kind == 12) {
+        *elements = 256;
+        *bytes = 144;
+        return SO_OK;
+    }
+    return SO_INVALID;
+}
+
+/* scale_min: weights.rs:2908-2920 */
+static inline void scale_min(const uint8_t *scales, int index, uint8_t *sc, uint8_t *mn) {
+    if (index < 4) {
+        *sc = scales[index] & 63;
+        *mn = scales[index + 4] & 63;
+    } else {
+        *sc = (uint8_t)((scales[index + 4] & 15) | ((scales[index - 4] >> 6) << 4));
+        *mn = (uint8_t)((scales[index + 4] >> 4) | ((scales[index] >> 6) << 4));
+    }
+}
+
+/* decode_block kinds 8 (Q8_0) and 12 (Q4_K): weights.rs:2936-2941, 2993-3017. */
+int so_decode_block(uint32_t kind, const uint8_t *bytes, float *output) {
+    if (kind == 8) {
+        float d = f16_to_f32((uint16_t)(bytes[0] | (bytes[1] << 8)));
+        for (int i = 0; i < 32; i++) output[i] = d * (float)(int8_t)bytes[2 + i];
+        return SO_OK;
+    }
+    if (kind == 12) {
+        float d = f16_to_f32((uint16_t)(bytes[0] | (bytes[1] << 8)));
+        float minimum = f16_to_f32((uint16_t)(bytes[2] | (bytes[3] << 8)));
+        const uint8_t *scales = bytes + 4;
+        for (int part = 0; part < 4; part++) {
+            for (int half = 0; half < 2; half++) {
+                uint8_t sc, mn;
+                scale_min(scales, part * 2 + half, &sc, &mn);
+                int at = part * 64 + half * 32;
+                for (int l = 0; l < 32; l++) {
+                    uint8_t ql = (bytes[16 + part * 32 + l] >> (half * 4)) & 15;
+                    output[at + l] = d * (float)sc * (float)ql - minimum * (float)mn;
+                }
+            }
+        }
+        return SO_OK;
+    }
+    return SO_INVALID;
+}
+
+/* Integer fields of a Q4_K block, for the bit-exact unpack test:
+ * codes[256], sub-block scales[8], mins[8]. */
+int so_q4k_unpack(const uint8_t *bytes, uint8_t *codes, uint8_t *scales6, uint8_t *mins6) {
+    for (int part = 0; part < 4; part++)
+        for (int half = 0; half < 2; half++) {
+            scale_min(bytes + 4, part * 2 + half, &scales6[part * 2 + half], &mins6[part * 2 + half]);
+            for (int l = 0; l < 32; l++)
+                codes[part * 64 + half * 32 + l] = (bytes[16 + part * 32 + l] >> (half * 4)) & 15;
+        }
+    return SO_OK;
+}
+
+/* decode_values + host matvec: weights.rs:2880-2895, 2534-2552.  GGUF rows are
+ * `columns/block` consecutive blocks; y[row] = sum(w*x) sequentially in f32. */
+int so_gguf_matvec_f32(uint32_t kind, const uint8_t *bytes, const float *x, float *y, uint32_t rows,
+                       uint32_t columns, int threads) {
+    uint32_t be, bb;
+    if (so_block_layout(kind, &be, &bb) != SO_OK || columns % be != 0) return SO_INVALID;
+    for (uint32_t i = 0; i < columns; i++)
+        if (!isfinite(x[i])) return SO_INVALID;
+    const size_t row_bytes = (size_t)(columns / be) * bb;
+    (void)threads;
+#pragma omp parallel for num_threads(threads > 0 ? threads : 1) schedule(static)
+    for (int64_t row = 0; row < (int64_t)rows; row++) {
+        float values[256];
+        float total = 0.0f;
+        const uint8_t *src = bytes + (size_t)row * row_bytes;
+        for (uint32_t b = 0; b < columns / be; b++) {
+            so_decode_block(kind, src + (size_t)b * bb, values);
+            for (uint32_t i = 0; i < be; i++) total += values[i] * x[b * be + i];
+        }
+        y[row] = total;
+    }
+    return SO_OK;
+}
+
+int so_gguf_decode_row(uint32_t kind, const uint8_t *bytes, float *out, uint32_t columns) {
+    uint32_t be, bb;
+    if (so_block_layout(kind, &be, &bb) != SO_OK || columns % be != 0) return SO_INVALID;
+    for (uint32_t b = 0; b < columns / be; b++) so_decode_block(kind, bytes + (size_t)b * bb, out + (size_t)b * be);
+    return SO_OK;
+}
+
+/* ------------------------------------------------------------- small ops */
+
+/* normalization (RMS, bf16 in/out, f32 scales, OnlyNormalization rounding):
+ * crates/stark-engine/src/backends/cpu/kernel/normalization/normalization.rs:13-191.
+ * residual_add != 0: val = bf16(input + shortcut), shortcut = val (ShortcutMode::Add);
+ * residual_add == 0 and shortcut != NULL: shortcut = input (ShortcutMode::Copy). */
+void so_rmsnorm_bf16(const uint16_t *input, const float *scales, uint16_t *output, uint16_t *shortcut,
+                     uint32_t batch, uint32_t count, float epsilon, int residual_add) {
+    for (uint32_t b = 0; b < batch; b++) {
+        const uint16_t *in = input + (size_t)b * count;
+        uint16_t *out = output + (size_t)b * count;
+        uint16_t *sc = shortcut ? shortcut + (size_t)b * count : NULL;
+        float sum_sq = 0.0f;
+        for (uint32_t i = 0; i < count; i++) {
+            uint16_t val = in[i];
+            if (sc) {
+                if (residual_add) val = f32_to_bf16(bf16_to_f32(val) + bf16_to_f32(sc[i]));
+                sc[i] = val;
+            }
+            float a = bf16_to_f32(val);
+            sum_sq = sum_sq + a * a;
+        }
+        float variance = sum_sq / (float)count - 0.0f * 0.0f;
+        float rms_inv = 1.0f / sqrtf(variance + epsilon);
+        for (uint32_t i = 0; i < count; i++) {
+            float v = (sc && residual_add) ? bf16_to_f32(sc[i]) : bf16_to_f32(in[i]);
+            float normalized = (v - 0.0f) * rms_inv;
+            float lo = bf16_round(normalized);
+            float s = bf16_round(scales[i] + 0.0f);
+            out[i] = f32_to_bf16(lo * s);
+        }
+    }
+}
+
+/* hybrid::math::rms_norm (f32 path): crates/stark-engine/src/engine/hybrid/math.rs:18-34 */
+int so_rmsnorm_f32(const float *x, const float *weight, float *out, uint32_t count, float eps) {
+    if (count == 0 || !(eps > 0.0f) || !isfinite(eps)) return SO_INVALID;
+    float sum = 0.0f;
+    for (uint32_t i = 0; i < count; i++) {
+        if (!isfinite(x[i]) || !isfinite(weight[i])) return SO_INVALID;
+        sum += x[i] * x[i];
+    }
+    float mean = sum / (float)count;
+    float scale = 1.0f / sqrtf(mean + eps);
+    for (uint32_t i = 0; i < count; i++) out[i] = x[i] * scale * weight[i];
+    return SO_OK;
+}
+
+/* qkv_norm (per-head RMS norm, in place, bf16, f32 scales):
+ * crates/stark-engine/src/backends/cpu/kernel/attention/qkv_norm.rs:8-111 */
+void so_head_norm_bf16(uint16_t *row, const float *scales, uint32_t head_offset, uint32_t head_count,
+                       uint32_t head_dim, float epsilon) {
+    for (uint32_t head = 0; head < head_count; head++) {
+        uint16_t *h = row + (size_t)(head_offset + head) * head_dim;
+        float total = 0.0f;
+        for (uint32_t i = 0; i < head_dim; i++) {
+            float v = bf16_to_f32(h[i]);
+            total = total + v * v;
+        }
+        float mean_square = total / (float)head_dim;
+        float rms = 1.0f / sqrtf(mean_square + epsilon);
+        for (uint32_t i = 0; i < head_dim; i++) {
+            float normalized = bf16_to_f32(h[i]) * rms;
+            h[i] = f32_to_bf16(bf16_round(normalized) * bf16_round(scales[i] + 0.0f));
+        }
+    }
+}
+
+/* RoPE coefficient for (position, pair): precalculate_cpu_tables, UnscaledRoPEConfig,
+ * crates/stark-engine/src/encodable_block/mixer/attention/rope.rs:346-440 */
+void so_rope_coeffs(uint32_t position, uint32_t head_dim, float base, float *cosines, float *sines) {
+    uint32_t half = head_dim / 2;
+    for (uint32_t pair = 0; pair < half; pair++) {
+        uint32_t channel = pair * 2;
+        float inv = 1.0f / powf(base, (float)channel / (float)head_dim);
+        float embedding = (float)position * inv;
+        float s = sinf(embedding) * 1.0f;
+        float c = cosf(embedding) * 1.0f;
+        sines[pair] = s;
+        sines[pair + half] = s;
+        cosines[pair] = c;
+        cosines[pair + half] = c;
+    }
+}
+
+/* apply_rope, half-split pairing, f32 math, bf16 store:
+ * crates/stark-engine/src/backends/cpu/kernel/attention/attention_prepare.rs:7-43 */
+void so_rope_head_bf16(const uint16_t *head, uint16_t *out, const float *cosines, const float *sines,
+                       uint32_t head_dim) {
+    uint32_t half = head_dim / 2;
+    for (uint32_t i = 0; i < head_dim; i++) {
+        uint32_t p = i < half ? i + half : i - half;
+        float input = bf16_to_f32(head[i]);
+        float paired = bf16_to_f32(head[p]);
+        float signed_paired = i < half ? -paired : paired;
+        out[i] = f32_to_bf16(input * cosines[i] + signed_paired * sines[i]);
+    }
+}
+
+/* attention_single_pass, causal, one query row per head (decode), GQA:
+ * crates/stark-engine/src/backends/cpu/kernel/attention/attention_single_pass.rs:11-133.
+ * keys/values: [sequence_length, kv_heads, head_dim] bf16; queries [heads, head_dim]; out [heads, head_dim]. */
+void so_attention_decode_bf16(const uint16_t *queries, const uint16_t *keys, const uint16_t *values, uint16_t *out,
+                              uint32_t heads, uint32_t kv_heads, uint32_t head_dim, uint32_t sequence_length,
+                              float scale, int threads) {
+    const uint32_t gqa = heads / kv_heads;
+    const size_t seq_stride = (size_t)kv_heads * head_dim;
+    (void)threads;
+#pragma omp parallel for num_threads(threads > 0 ? threads : 1) schedule(static)
+    for (int64_t head = 0; head < (int64_t)heads; head++) {
+        uint32_t kvh = (uint32_t)head / gqa;
+        float q[512], o[512];
+        for (uint32_t j = 0; j < head_dim; j++) {
+            q[j] = scale * bf16_to_f32(queries[(size_t)head * head_dim + j]);
+            o[j] = 0.0f;
+        }
+        float max_score = -INFINITY, sum_exp = 0.0f;
+        for (uint32_t i = 0; i < sequence_length; i++) {
+            const uint16_t *kr = keys + (size_t)i * seq_stride + (size_t)kvh * head_dim;
+            float score = 0.0f;
+            for (uint32_t j = 0; j < head_dim; j++) score += q[j] * bf16_to_f32(kr[j]);
+            float new_max = fmaxf(max_score, score);
+            float factor = expf(max_score - new_max);
+            float e = expf(score - new_max);
+            max_score = new_max;
+            sum_exp = sum_exp * factor + e;
+            const uint16_t *vr = values + (size_t)i * seq_stride + (size_t)kvh * head_dim;
+            for (uint32_t j = 0; j < head_dim; j++) o[j] = o[j] * factor + e * bf16_to_f32(vr[j]);
+        }
+        for (uint32_t j = 0; j < head_dim; j++) out[(size_t)head * head_dim + j] = f32_to_bf16(o[j] / sum_exp);
+    }
+}
+
+/* gated_act_mul on a fused [up; gate] row, SiLU alpha 1, bf16:
+ * crates/stark-engine/src/backends/cpu/kernel/gated_act_mul/gated_act_mul.rs:66-100,
+ * crates/stark-engine/src/backends/common/gpu_types/activation_type.rs:37-49 */
+void so_swiglu_bf16(const uint16_t *fused, uint16_t *out, uint32_t gated_dim) {
+    for (uint32_t g = 0; g < gated_dim; g++) {
+        float value = bf16_to_f32(fused[g]);
+        float gate = bf16_to_f32(fused[gated_dim + g]);
+        float activated = bf16_round(gate / (1.0f + expf(-1.0f * gate)));
+        out[g] = f32_to_bf16(bf16_round(value * activated));
+    }
+}
+
+/* input_embedding_lookup, quantized ScaleBias table, bf16 row:
+ * crates/stark-engine/src/backends/cpu/kernel/embedding/input_embedding_lookup.rs:59-105 */
+void so_embedding_row_bf16(const uint8_t *codes, const uint16_t *scales, const uint16_t *biases, uint32_t token,
+                           uint32_t vocab, uint32_t dim, uint32_t bits, uint32_t group, uint16_t *out) {
+    if (token >= vocab) {
+        memset(out, 0, (size_t)dim * 2);
+        return;
+    }
+    size_t groups = (dim + group - 1) / group;
+    for (uint32_t c = 0; c < dim; c++) {
+        size_t index = (size_t)token * groups + c / group;
+        float scale = bf16_to_f32(scales[index]);
+        float bias = bf16_to_f32(biases[index]);
+        float code = (float)so_packed_code(codes, bits, (size_t)token * dim + c);
+        float deq = scale * code + bias;
+        out[c] = f32_to_bf16(deq * 1.0f);
+    }
+}
+
+/* Greedy token: first index of the maximum; any non-finite logit => UINT32_MAX.
+ * crates/stark-engine/src/backends/cpu/kernel/sampling/unified_sampling.rs:36-45,108-116 */
+uint32_t so_argmax_bf16(const uint16_t *logits, uint32_t vocab) {
+    uint32_t best = UINT32_MAX;
+    float best_value = -INFINITY;
+    for (uint32_t i = 0; i < vocab; i++) {
+        float v = bf16_to_f32(logits[i]);
+        if (!isfinite(v)) return UINT32_MAX;
+        if (best == UINT32_MAX || v > best_value) {
+            best = i;
+            best_value = v;
+        }
+    }
+    return best;
+}
+
+uint32_t so_argmax_f32(const float *logits, uint32_t vocab) {
+    uint32_t best = UINT32_MAX;
+    float best_value = -INFINITY;
+    for (uint32_t i = 0; i < vocab; i++) {
+        if (!isfinite(logits[i])) return UINT32_MAX;
+        if (best == UINT32_MAX || logits[i] > best_value) {
+            best = i;
+            best_value = logits[i];
+        }
+    }
+    return best;
+}
+
+/* Full-vocabulary log-probabilities in f64:
+ * crates/stark-score/src/scoring.rs:299-336  log p_i = logit_i - (max + ln sum exp(logit - max)) */
+void so_log_softmax_f64(const float *logits, double *out, uint32_t vocab) {
+    double maximum = -INFINITY;
+    for (uint32_t i = 0; i < vocab; i++)
+        if ((double)logits[i] > maximum) maximum = (double)logits[i];
+    double sum = 0.0;
+    for (uint32_t i = 0; i < vocab; i++) sum += exp((double)logits[i] - maximum);
+    double lse = maximum + log(sum);
+    for (uint32_t i = 0; i < vocab; i++) out[i] = (double)logits[i] - lse;
+}
+
+/* hybrid::math::softmax: crates/stark-engine/src/engine/hybrid/math.rs:36-51 */
+int so_softmax_f32(const float *x, float *out, uint32_t count) {
+    if (count == 0) return SO_INVALID;
+    float maximum = -INFINITY;
+    for (uint32_t i = 0; i < count; i++) {
+        if (isnan(x[i]) || x[i] == INFINITY) return SO_INVALID;
+        maximum = fmaxf(maximum, x[i]);
+    }
+    if (!isfinite(maximum)) return SO_INVALID;
+    float sum = 0.0f;
+    for (uint32_t i = 0; i < count; i++) {
+        out[i] = expf(x[i] - maximum);
+        sum += out[i];
+    }
+    if (!isfinite(sum) || sum <= 0.0f) return SO_INVALID;
+    for (uint32_t i = 0; i < count; i++) out[i] /= sum;
+    return SO_OK;
+}
+
+/* hybrid::math::topk: stable by (value desc, index asc). math.rs:55-66 */
+int so_topk_f32(const float *x, uint32_t count, uint32_t k, uint32_t *indices) {
+    if (k == 0 || k > count) return SO_INVALID;
+    for (uint32_t i = 0; i < count; i++)
+        if (isnan(x[i])) return SO_INVALID;
+    uint8_t *taken = (uint8_t *)calloc(count, 1);
+    for (uint32_t r = 0; r < k; r++) {
+        uint32_t best = UINT32_MAX;
+        for (uint32_t i = 0; i < count; i++) {
+            if (taken[i]) continue;
+            if (best == UINT32_MAX || x[i] > x[best]) best = i;
+        }
+        taken[best] = 1;
+        indices[r] = best;
+    }
+    free(taken);
+    return SO_OK;
+}
+
+/* moe_route: softmax over all experts, iterative top-k (first maximum wins),
+ * renormalise over the selected, optional bf16 rounding of logits / weights.
+ * crates/stark-engine/src/backends/cpu/kernel/moe.rs:25-82 */
+int so_moe_route(const float *logits, uint32_t *ids, float *weights, uint32_t rows, uint32_t experts,
+                 uint32_t active, uint32_t round_weights, uint32_t round_logits) {
+    float *x = (float *)malloc(sizeof(float) * (experts ? experts : 1));
+    for (uint32_t row = 0; row < rows; row++) {
+        const float *source = logits + (size_t)row * experts;
+        uint32_t *rid = ids + (size_t)row * active;
+        float *rw = weights + (size_t)row * active;
+        int valid = experts >= 1 && experts <= 1024 && active >= 1 && active <= 32 && active <= experts;
+        for (uint32_t e = 0; e < experts; e++) {
+            x[e] = round_logits ? bf16_round(source[e]) : source[e];
+            if (!isfinite(x[e])) valid = 0;
+        }
+        float maximum = -INFINITY;
+        for (uint32_t e = 0; e < experts; e++) maximum = fmaxf(maximum, x[e]);
+        float denominator = 0.0f;
+        for (uint32_t e = 0; e < experts; e++) denominator += expf(x[e] - maximum);
+        float selected_sum = 0.0f;
+        for (uint32_t rank = 0; rank < active; rank++) {
+            float best = -INFINITY;
+            uint32_t selected = 0;
+            for (uint32_t e = 0; e < experts; e++) {
+                int used = 0;
+                for (uint32_t r = 0; r < rank; r++)
+                    if (rid[r] == e) used = 1;
+                if (!used && x[e] > best) {
+                    best = x[e];
+                    selected = e;
+                }
+            }
+            rid[rank] = valid ? selected : 0;
+            rw[rank] = expf(best - maximum) / denominator;
+            selected_sum += rw[rank];
+        }
+        for (uint32_t rank = 0; rank < active; rank++) {
+            rw[rank] /= selected_sum;
+            if (round_weights) rw[rank] = bf16_round(rw[rank]);
+            if (!valid) rw[rank] = NAN;
+        }
+    }
+    free(x);
+    return SO_OK;
+}
+
+/* ------------------------------------------------ dense decoder (bf16 graph) */
+
+typedef struct {
+    const uint8_t *codes;   /* [n, k*bits/8] MLX row-major packed codes */
+    const uint16_t *scales; /* [n, k/group] bf16 */
+    const uint16_t *biases; /* [n, k/group] bf16 */
+    uint32_t n, k, bits, group;
+} so_qmat;
+
+typedef struct {
+    const float *attn_norm; /* [hidden] f32 */
+    const float *mlp_norm;  /* [hidden] */
+    const float *q_norm;    /* [head_dim] */
+    const float *k_norm;    /* [head_dim] */
+    so_qmat qkv;            /* [(q_heads + 2 kv_heads) * head_dim, hidden], rows [q; k; v] */
+    so_qmat o;              /* [hidden, q_heads*head_dim] */
+    so_qmat upgate;         /* [2*inter, hidden], rows [up; gate] */
+    so_qmat down;           /* [hidden, inter] */
+} so_dense_layer;
+
+typedef struct {
+    uint32_t layers, hidden, q_heads, kv_heads, head_dim, inter, vocab;
+    float eps, rope_theta;
+    so_qmat embed;   /* [vocab, hidden] */
+    so_qmat lm_head; /* [vocab, hidden]; same planes as embed when tied */
+    const float *final_norm;
+    const so_dense_layer *layer;
+} so_dense_model;
+
+typedef struct {
+    uint16_t *keys;   /* [layers, capacity, kv_heads*head_dim] bf16 */
+    uint16_t *values; /* same */
+    uint32_t capacity;
+    uint32_t position; /* rows already in the cache */
+} so_dense_state;
+
+static void qmv(const so_qmat *w, const uint16_t *x, uint16_t *y, int threads) {
+    so_affine_matvec_bf16(w->codes, w->scales, w->biases, x, y, 1, w->n, w->k, w->bits, w->group, 0, 0, 0, 0,
+                          threads);
+}
+
+/* One decode row through the Qwen3 dense graph with the bf16 rounding points of
+ * the converted-model path:
+ *   wiring   crates/stark-engine/src/encodable_block/transformer_layer.rs:549-659
+ *            crates/stark-engine/src/encodable_block/mixer/attention/mode.rs:377-461
+ *            crates/stark-engine/src/encodable_block/mlp/dense.rs:99-115
+ *            crates/stark-engine/src/encodable_block/decoder.rs:494-555
+ * logits_out may be NULL (cache-only ingest of a prompt row); hidden_out (the
+ * final normalized row, [hidden] bf16) may be NULL. */
+int so_dense_step(const so_dense_model *m, so_dense_state *s, uint32_t token, uint16_t *logits_out,
+                  uint16_t *hidden_out, int threads) {
+    if (s->position >= s->capacity || token >= m->vocab) return SO_INVALID;
+    const uint32_t D = m->hidden, hd = m->head_dim, QH = m->q_heads, KH = m->kv_heads, I = m->inter;
+    const uint32_t qkv_n = (QH + 2 * KH) * hd;
+    const size_t kv_row = (size_t)KH * hd;
+    uint16_t *hidden = (uint16_t *)malloc(2 * (size_t)D);
+    uint16_t *shortcut = (uint16_t *)malloc(2 * (size_t)D);
+    uint16_t *normed = (uint16_t *)malloc(2 * (size_t)D);
+    uint16_t *qkv = (uint16_t *)malloc(2 * (size_t)qkv_n);
+    uint16_t *attn = (uint16_t *)malloc(2 * (size_t)QH * hd);
+    uint16_t *fused = (uint16_t *)malloc(2 * (size_t)2 * I);
+    uint16_t *act = (uint16_t *)malloc(2 * (size_t)I);
+    uint16_t *tmp = (uint16_t *)malloc(2 * (size_t)hd);
+    float *cosines = (float *)malloc(4 * (size_t)hd), *sines = (float *)malloc(4 * (size_t)hd);
+    const uint32_t pos = s->position;
+    so_rope_coeffs(pos, hd, m->rope_theta, cosines, sines);
+    const float scale = 1.0f / sqrtf((float)hd);
+
+    so_embedding_row_bf16(m->embed.codes, m->embed.scales, m->embed.biases, token, m->vocab, D, m->embed.bits,
+                          m->embed.group, hidden);
+    for (uint32_t l = 0; l < m->layers; l++) {
+        const so_dense_layer *L = &m->layer[l];
+        /* pre_mixer_norm: Copy on layer 0, Add afterwards (transformer_layer.rs:250-264) */
+        so_rmsnorm_bf16(hidden, L->attn_norm, normed, shortcut, 1, D, m->eps, l > 0);
+        qmv(&L->qkv, normed, qkv, threads);
+        so_head_norm_bf16(qkv, L->q_norm, 0, QH, hd, m->eps);
+        so_head_norm_bf16(qkv, L->k_norm, QH, KH, hd, m->eps);
+        uint16_t *kc = s->keys + ((size_t)l * s->capacity + pos) * kv_row;
+        uint16_t *vc = s->values + ((size_t)l * s->capacity + pos) * kv_row;
+        for (uint32_t h = 0; h < QH; h++) {
+            so_rope_head_bf16(qkv + (size_t)h * hd, tmp, cosines, sines, hd);
+            memcpy(qkv + (size_t)h * hd, tmp, 2 * (size_t)hd);
+        }
+        for (uint32_t h = 0; h < KH; h++)
+            so_rope_head_bf16(qkv + (size_t)(QH + h) * hd, kc + (size_t)h * hd, cosines, sines, hd);
+        memcpy(vc, qkv + (size_t)(QH + KH) * hd, 2 * kv_row);
+        so_attention_decode_bf16(qkv, s->keys + (size_t)l * s->capacity * kv_row,
+                                 s->values + (size_t)l * s->capacity * kv_row, attn, QH, KH, hd, pos + 1, scale,
+                                 threads);
+        qmv(&L->o, attn, hidden, threads);
+        so_rmsnorm_bf16(hidden, L->mlp_norm, normed, shortcut, 1, D, m->eps, 1);
+        qmv(&L->upgate, normed, fused, threads);
+        so_swiglu_bf16(fused, act, I);
+        qmv(&L->down, act, hidden, threads);
+    }
+    s->position = pos + 1;
+    if (logits_out || hidden_out) {
+        so_rmsnorm_bf16(hidden, m->final_norm, normed, shortcut, 1, D, m->eps, 1);
+        if (hidden_out) memcpy(hidden_out, normed, 2 * (size_t)D);
+        if (logits_out) qmv(&m->lm_head, normed, logits_out, threads);
+    }
+    free(hidden);
+    free(shortcut);
+    free(normed);
+    free(qkv);
+    free(attn);
+    free(fused);
+    free(act);
+    free(tmp);
+    free(cosines);
+    free(sines);
+    return SO_OK;
+}
+
+int so_max_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}

@@ -1,0 +1,239 @@
+// extern "C" surface of libstark_b200.so (declared in include/stark_b200.h).
+// No exception crosses the boundary and nothing is printed.
+#include <mutex>
+#include <new>
+
+#include "context.cuh"
+#include "qmv.cuh"
+
+namespace sb {
+
+static std::mutex g_ctx_mutex;
+static DeviceContext g_ctx[64];
+
+DeviceContext *device_context() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(g_ctx_mutex);
+    DeviceContext &c = g_ctx[dev];
+    if (c.device != dev) {
+        uint32_t *word = nullptr;
+        if (cudaMalloc(&word, 256) != cudaSuccess) return nullptr;
+        if (cudaMemset(word, 0, 256) != cudaSuccess) {
+            cudaFree(word);
+            return nullptr;
+        }
+        c.error_word = word;
+        c.device = dev;
+    }
+    return &c;
+}
+
+stark_b200_status ensure_buffer(void **buf, size_t *have, size_t want) {
+    if (*have >= want && *buf) return STARK_B200_OK;
+    if (*buf) cudaFree(*buf);
+    *buf = nullptr;
+    *have = 0;
+    size_t cap = want < 4096 ? 4096 : want;
+    SB_CUDA(cudaMalloc(buf, cap));
+    *have = cap;
+    return STARK_B200_OK;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+uint32_t stark_b200_abi_version(void) { return STARK_B200_ABI_VERSION; }
+
+const char *stark_b200_status_name(uint32_t status) {
+    switch (status) {
+        case STARK_B200_OK: return "ok";
+        case STARK_B200_INVALID_ARGUMENT: return "invalid_argument";
+        case STARK_B200_ABI_MISMATCH: return "abi_mismatch";
+        case STARK_B200_CONTEXT_LIMIT: return "context_limit";
+        case STARK_B200_CANCELLED: return "cancelled";
+        case STARK_B200_UNSUPPORTED: return "unsupported";
+        case STARK_B200_OUT_OF_MEMORY: return "out_of_memory";
+        case STARK_B200_IO_FAILURE: return "io_failure";
+        case STARK_B200_DEVICE_FAILURE: return "device_failure";
+        case STARK_B200_RELOAD_REQUIRED: return "reload_required";
+        case STARK_B200_BUSY: return "busy";
+        case STARK_B200_INVALID_STATE: return "invalid_state";
+        default: return "unknown";
+    }
+}
+
+stark_b200_status stark_b200_device_count(int32_t *out_count) {
+    if (!out_count) return STARK_B200_INVALID_ARGUMENT;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) {
+        *out_count = 0;
+        return STARK_B200_DEVICE_FAILURE;
+    }
+    *out_count = n;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_set_device(int32_t device) {
+    SB_CUDA(cudaSetDevice(device));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_device_malloc(void **out_ptr, size_t bytes) {
+    if (!out_ptr) return STARK_B200_INVALID_ARGUMENT;
+    *out_ptr = nullptr;
+    SB_CUDA(cudaMalloc(out_ptr, bytes ? bytes : 1));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_device_free(void *ptr) {
+    SB_CUDA(cudaFree(ptr));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_memcpy_h2d(void *dst, const void *src, size_t bytes, void *stream) {
+    SB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_memcpy_d2h(void *dst, const void *src, size_t bytes, void *stream) {
+    SB_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_stream_synchronize(void *stream) {
+    SB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_take_device_error(uint32_t *out_word) {
+    if (!out_word) return STARK_B200_INVALID_ARGUMENT;
+    DeviceContext *ctx = device_context();
+    if (!ctx) return STARK_B200_DEVICE_FAILURE;
+    SB_CUDA(cudaMemcpy(out_word, ctx->error_word, 4, cudaMemcpyDeviceToHost));
+    if (*out_word) SB_CUDA(cudaMemset(ctx->error_word, 0, 4));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_qmatrix_create_affine(const void *codes, const void *scales, const void *biases,
+                                                   const stark_b200_affine_desc *desc,
+                                                   stark_b200_qmatrix **out_matrix) {
+    if (!codes || !scales || !biases || !desc || !out_matrix) return STARK_B200_INVALID_ARGUMENT;
+    *out_matrix = nullptr;
+    if (desc->struct_size != sizeof(stark_b200_affine_desc) || desc->abi_version != STARK_B200_ABI_VERSION)
+        return STARK_B200_ABI_MISMATCH;
+    if (desc->rows == 0 || desc->columns == 0 || desc->group == 0 || desc->columns % desc->group != 0)
+        return STARK_B200_INVALID_ARGUMENT;
+    const size_t code_bytes = (size_t)desc->rows * desc->columns * desc->bits / 8u;
+    const size_t groups = desc->columns / desc->group;
+    const size_t plane_elems = desc->scale_layout == 0 ? (size_t)desc->rows * groups : groups * desc->plane_pitch;
+    const size_t plane_bytes = plane_elems * (desc->plane_kind == STARK_B200_PLANE_F32 ? 4u : 2u);
+    QMatrix *m = nullptr;
+    stark_b200_status st;
+    if (desc->location == STARK_B200_DEVICE) {
+        st = qmatrix_from_affine_device((const uint8_t *)codes, scales, biases, *desc, 0, &m);
+        if (st == STARK_B200_OK) st = cuda_status(cudaStreamSynchronize(0));
+    } else {
+        uint8_t *dc = nullptr, *ds = nullptr, *db = nullptr;
+        cudaError_t e = cudaMalloc(&dc, code_bytes);
+        if (e == cudaSuccess) e = cudaMalloc(&ds, plane_bytes);
+        if (e == cudaSuccess) e = cudaMalloc(&db, plane_bytes);
+        if (e == cudaSuccess) e = cudaMemcpy(dc, codes, code_bytes, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(ds, scales, plane_bytes, cudaMemcpyHostToDevice);
+        if (e == cudaSuccess) e = cudaMemcpy(db, biases, plane_bytes, cudaMemcpyHostToDevice);
+        st = cuda_status(e);
+        if (st == STARK_B200_OK) st = qmatrix_from_affine_device(dc, ds, db, *desc, 0, &m);
+        if (st == STARK_B200_OK) st = cuda_status(cudaStreamSynchronize(0));
+        cudaFree(dc);
+        cudaFree(ds);
+        cudaFree(db);
+    }
+    if (st != STARK_B200_OK) {
+        qmatrix_free(m);
+        return st;
+    }
+    *out_matrix = reinterpret_cast<stark_b200_qmatrix *>(m);
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_qmatrix_create_gguf(const void *blocks, uint32_t kind, uint32_t rows, uint32_t columns,
+                                                 uint32_t location, stark_b200_qmatrix **out_matrix) {
+    (void)blocks;
+    (void)kind;
+    (void)rows;
+    (void)columns;
+    (void)location;
+    if (out_matrix) *out_matrix = nullptr;
+    return STARK_B200_UNSUPPORTED;
+}
+
+stark_b200_status stark_b200_qmatrix_destroy(stark_b200_qmatrix **matrix) {
+    if (!matrix) return STARK_B200_INVALID_ARGUMENT;
+    qmatrix_free(reinterpret_cast<QMatrix *>(*matrix));
+    *matrix = nullptr;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_qmatrix_device_bytes(const stark_b200_qmatrix *matrix, uint64_t *out_bytes) {
+    if (!matrix || !out_bytes) return STARK_B200_INVALID_ARGUMENT;
+    *out_bytes = reinterpret_cast<const QMatrix *>(matrix)->bytes;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_qmatrix_unpack_codes(const stark_b200_qmatrix *matrix, uint8_t *dst_host,
+                                                  size_t count) {
+    const QMatrix *m = reinterpret_cast<const QMatrix *>(matrix);
+    if (!m || !dst_host || count != (size_t)m->rows * m->columns) return STARK_B200_INVALID_ARGUMENT;
+    uint8_t *d = nullptr;
+    SB_CUDA(cudaMalloc(&d, count));
+    stark_b200_status st = qmatrix_unpack_codes_device(m, d, 0);
+    if (st == STARK_B200_OK) st = cuda_status(cudaMemcpy(dst_host, d, count, cudaMemcpyDeviceToHost));
+    cudaFree(d);
+    return st;
+}
+
+stark_b200_status stark_b200_op_qmv(const stark_b200_qmatrix *matrix, const void *x, void *y, uint32_t m,
+                                    uint32_t io_type, uint32_t location, void *stream) {
+    const QMatrix *w = reinterpret_cast<const QMatrix *>(matrix);
+    if (!w || !x || !y || m == 0 || m > 8 || io_type > STARK_B200_F32) return STARK_B200_INVALID_ARGUMENT;
+    DeviceContext *ctx = device_context();
+    if (!ctx) return STARK_B200_DEVICE_FAILURE;
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t esz = io_type == STARK_B200_F32 ? 4u : 2u;
+    const size_t xin = (size_t)w->columns * esz, yout = (size_t)w->rows * esz;
+    const uint8_t *dx = (const uint8_t *)x;
+    uint8_t *dy = (uint8_t *)y;
+    if (location == STARK_B200_HOST) {
+        stark_b200_status st = ensure_buffer(&ctx->stage_in, &ctx->stage_in_bytes, xin * m);
+        if (st != STARK_B200_OK) return st;
+        st = ensure_buffer(&ctx->stage_out, &ctx->stage_out_bytes, yout * m);
+        if (st != STARK_B200_OK) return st;
+        SB_CUDA(cudaMemcpyAsync(ctx->stage_in, x, xin * m, cudaMemcpyHostToDevice, s));
+        dx = (const uint8_t *)ctx->stage_in;
+        dy = (uint8_t *)ctx->stage_out;
+    }
+    for (uint32_t row = 0; row < m; ++row) {
+        QmvArgs a{};
+        a.matrix = w;
+        a.x = dx + row * xin;
+        a.y = dy + row * yout;
+        a.m = 1;
+        a.io_type = io_type;
+        a.prologue = kProPlain;
+        a.epilogue = kEpiStore;
+        a.error_word = ctx->error_word;
+        a.pdl = false;
+        stark_b200_status st = qmv_launch(a, s);
+        if (st != STARK_B200_OK) return st;
+    }
+    if (location == STARK_B200_HOST) {
+        SB_CUDA(cudaMemcpyAsync(y, ctx->stage_out, yout * m, cudaMemcpyDeviceToHost, s));
+        SB_CUDA(cudaStreamSynchronize(s));
+    }
+    return STARK_B200_OK;
+}
+
+}  // extern "C"

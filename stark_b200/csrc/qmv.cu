@@ -1,0 +1,630 @@
+// Fused-dequant quantized matvec for sm_100a.
+//
+// y = W x for an MLX-affine 4-bit group-64 matrix, batch 1.  The kernel is HBM-bound
+// (0.5625 bytes per weight), so the design goal is one uninterrupted stream of weight bytes:
+//   * weights are re-tiled once at load time into 576-byte records (see qmv.cuh) so that each CTA
+//     owns one contiguous byte range;
+//   * a producer warp moves that range through a shared-memory ring with 1-D bulk copies
+//     (cp.async.bulk + mbarrier complete_tx), started BEFORE griddepcontrol.wait, so under
+//     programmatic dependent launch the ring is already full when the previous kernel's output
+//     (the input vector) becomes visible;
+//   * eight consumer warps turn nibbles into exact f16 integers with lop3 + one f16 FMA per pair
+//     and feed them to mma.sync.m16n8k16 (f16 x f16 -> f32).  The CUDA cores alone cannot keep up
+//     with B200's ~26 B/clk/SM of HBM bandwidth at 4 bit (2 weights per byte, one FMA + one
+//     conversion each); the tensor pipe does the multiply-accumulate so the ALU pipes only run the
+//     extraction.  Products q*x are exact and the accumulation is f32, as in the reference;
+//   * per group: acc += scale * sum(q x) and acc += bias * sum(x), which is algebraically the
+//     reference's sum x (scale q + bias)
+//     (crates/stark-engine/src/backends/cpu/kernel/matmul/kernel.rs:219-265);
+//   * the input vector is converted to f16 after an exact power-of-two rescale by its maximum, so
+//     the f16 range never clips it; bf16 inputs convert exactly.
+#include "qmv.cuh"
+
+#include <algorithm>
+#include <new>
+
+namespace sb {
+
+namespace {
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+
+struct QmvParams {
+    const uint8_t *w;
+    uint32_t rows;
+    uint32_t row_tiles;
+    uint32_t groups;           // K / 64
+    uint32_t stage_records;    // records per ring stage (divides groups)
+    uint32_t stages_per_tile;  // groups / stage_records
+    uint32_t stage_capacity;   // bytes reserved per ring slot
+    uint32_t num_stages;       // ring depth
+    uint32_t pair_halves;
+    uint32_t unit_tiles;  // 1, or 2 when an epilogue needs (up, gate) tile pairs
+    uint32_t io_type;
+    uint32_t prologue;
+    uint32_t epilogue;
+    const void *x;
+    void *y;
+    const float *norm_weight;
+    float eps;
+    const void *resid;
+    float *partial_max;
+    uint32_t *partial_index;
+    uint32_t *error_word;
+};
+
+// Exact 4-bit -> f16 integer conversion of one record word into an m16n8k16 A fragment.
+//   (w & 0x000f000f) | 0x64006400 is the f16 pair (1024 + q, 1024 + q'); subtracting 1024 is exact.
+//   (w & 0x00f000f0) | 0x64006400 is (1024 + 16 q, ...); x * 1/16 - 64 is exact in one FMA.
+__device__ inline void dequant_a4_word(uint32_t w, uint32_t (&a)[4]) {
+    const uint32_t magic = 0x64006400u;
+    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+    const __half2 k16th = __half2half2(__ushort_as_half(0x2c00));   // 1/16
+    const __half2 kneg64 = __half2half2(__ushort_as_half(0xd400));  // -64
+    uint32_t lo0 = lop3_and_or(w, 0x000f000fu, magic);
+    uint32_t hi0 = lop3_and_or(w, 0x00f000f0u, magic);
+    uint32_t w8 = w >> 8;
+    uint32_t lo1 = lop3_and_or(w8, 0x000f000fu, magic);
+    uint32_t hi1 = lop3_and_or(w8, 0x00f000f0u, magic);
+    __half2 r0 = __hsub2(*reinterpret_cast<__half2 *>(&lo0), k1024);
+    __half2 r1 = __hfma2(*reinterpret_cast<__half2 *>(&hi0), k16th, kneg64);
+    __half2 r2 = __hsub2(*reinterpret_cast<__half2 *>(&lo1), k1024);
+    __half2 r3 = __hfma2(*reinterpret_cast<__half2 *>(&hi1), k16th, kneg64);
+    a[0] = *reinterpret_cast<uint32_t *>(&r0);
+    a[1] = *reinterpret_cast<uint32_t *>(&r1);
+    a[2] = *reinterpret_cast<uint32_t *>(&r2);
+    a[3] = *reinterpret_cast<uint32_t *>(&r3);
+}
+
+struct SmemLayout {
+    uint32_t ring, xs, xlo, xsum, red, wred, bars, flags, total;
+};
+
+__host__ __device__ inline SmemLayout smem_layout(uint32_t num_stages, uint32_t stage_capacity, uint32_t columns,
+                                                  bool split) {
+    SmemLayout L;
+    uint32_t off = 0;
+    L.ring = off;
+    off += num_stages * stage_capacity;
+    L.xs = off;
+    off += columns * 2u;
+    L.xlo = off;
+    off += split ? columns * 2u : 0u;
+    L.xsum = off;
+    off += (columns / 64u) * 4u;
+    off = (off + 15u) & ~15u;
+    L.red = off;
+    off += 2u * kConsumerWarps * 16u * 4u;
+    L.wred = off;
+    off += 16u * 4u;
+    L.bars = off;
+    off += 2u * 8u * 8u;  // up to 8 stages: full[8], empty[8]
+    L.flags = off;
+    off += 16u;
+    L.total = off;
+    return L;
+}
+
+// SPLIT: the input is f32 and is carried as two f16 terms (hi + lo) so that ~22 mantissa bits
+// survive; bf16 inputs need one term.
+template <bool SPLIT>
+__global__ void __launch_bounds__(kThreads, 1) qmv_a4_kernel(const QmvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    const uint32_t columns = p.groups * 64u;
+    const SmemLayout L = smem_layout(p.num_stages, p.stage_capacity, columns, SPLIT);
+    uint8_t *ring = smem + L.ring;
+    __half *xs = reinterpret_cast<__half *>(smem + L.xs);
+    __half *xlo = reinterpret_cast<__half *>(smem + L.xlo);
+    float *xsum = reinterpret_cast<float *>(smem + L.xsum);
+    float *red = reinterpret_cast<float *>(smem + L.red);
+    float *wred = reinterpret_cast<float *>(smem + L.wred);
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bars);
+    uint64_t *empty = full + 8;
+    volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + L.flags);
+
+    const uint32_t tid = threadIdx.x;
+    const uint32_t warp = tid >> 5, lane = tid & 31u;
+
+    // This CTA's share: whole units (1 or 2 row tiles), contiguous in memory.
+    const uint32_t units = p.row_tiles / p.unit_tiles;
+    const uint32_t u0 = (uint32_t)(((uint64_t)blockIdx.x * units) / gridDim.x);
+    const uint32_t u1 = (uint32_t)(((uint64_t)(blockIdx.x + 1) * units) / gridDim.x);
+    const uint32_t t0 = u0 * p.unit_tiles, t1 = u1 * p.unit_tiles;
+    const uint32_t total_stages = (t1 - t0) * p.stages_per_tile;
+    const uint32_t stage_bytes = p.stage_records * kA4RecordBytes;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < p.num_stages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kConsumerWarps);
+        }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == kConsumerWarps) {
+        // ---------------- producer: stream this CTA's byte range through the ring ----------------
+        if (lane == 0) {
+            const uint8_t *src = p.w + (size_t)t0 * p.groups * kA4RecordBytes;
+            for (uint32_t s = 0; s < total_stages; ++s) {
+                const uint32_t slot = s % p.num_stages, use = s / p.num_stages;
+                if (use > 0 && !mbar_wait_bounded(&empty[slot], (use - 1u) & 1u, abort_flag)) {
+                    *abort_flag = 1;
+                    atomicOr(p.error_word, kErrMbarTimeout);
+                    break;
+                }
+                mbar_arrive_expect_tx(&full[slot], stage_bytes);
+                bulk_g2s(ring + (size_t)slot * p.stage_capacity, src + (size_t)s * stage_bytes, stage_bytes,
+                         &full[slot]);
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    pdl_wait();  // the input vector (and anything the epilogue overwrites) belongs to the previous kernel
+
+    // Prologue: build the f16 input vector, its power-of-two scale and the per-group sums.
+    const uint32_t chunks = columns / 8u;
+    float sumsq = 0.0f;
+    if (p.prologue == kProRmsNorm) {
+        const uint4 *h4 = reinterpret_cast<const uint4 *>(p.x);
+        for (uint32_t c = tid; c < chunks; c += kConsumerThreads) {
+            uint4 v = h4[c];
+            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float a = __uint_as_float(wv[i] << 16), b = __uint_as_float(wv[i] & 0xffff0000u);
+                sumsq += a * a;
+                sumsq += b * b;
+            }
+        }
+        sumsq = warp_sum(sumsq);
+        if (lane == 0) wred[warp] = sumsq;
+        named_bar_sync(1, kConsumerThreads);
+        sumsq = 0.0f;
+#pragma unroll
+        for (int i = 0; i < kConsumerWarps; ++i) sumsq += wred[i];
+        named_bar_sync(1, kConsumerThreads);
+    }
+    const float rms_inv = 1.0f / sqrtf(sumsq / (float)columns + p.eps);
+
+    // Pass 1: materialise x (f32 values kept in shared memory as raw f32 would not fit for large K,
+    // so bf16 inputs are parked as bf16 bits in `xs`, f32 inputs as bf16 hi in xs and are re-read).
+    float vmax = 0.0f;
+    for (uint32_t c = tid; c < chunks; c += kConsumerThreads) {
+        if (p.io_type == STARK_B200_F32 && p.prologue == kProPlain) {
+            const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
+            float4 a = x4[2 * c], b = x4[2 * c + 1];
+            vmax = fmaxf(vmax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
+            vmax = fmaxf(vmax, fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
+        } else {
+            uint4 v = reinterpret_cast<const uint4 *>(p.x)[c];
+            uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+            if (p.prologue == kProRmsNorm) {
+                const float4 *nw = reinterpret_cast<const float4 *>(p.norm_weight);
+                float4 n0 = nw[2 * c], n1 = nw[2 * c + 1];
+                const float ns[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float a = __uint_as_float(wv[i] << 16), b = __uint_as_float(wv[i] & 0xffff0000u);
+                    // normalization.rs:157-161: bf16(normalized) * bf16(scale), product rounded to bf16
+                    uint16_t ra = f32_to_bf16_bits(bf16_round(a * rms_inv) * bf16_round(ns[2 * i]));
+                    uint16_t rb = f32_to_bf16_bits(bf16_round(b * rms_inv) * bf16_round(ns[2 * i + 1]));
+                    wv[i] = (uint32_t)ra | ((uint32_t)rb << 16);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                vmax = fmaxf(vmax, fabsf(__uint_as_float(wv[i] << 16)));
+                vmax = fmaxf(vmax, fabsf(__uint_as_float(wv[i] & 0xffff0000u)));
+            }
+            reinterpret_cast<uint4 *>(xs)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+        }
+    }
+    vmax = warp_max(vmax);
+    if (lane == 0) wred[8 + warp] = vmax;
+    named_bar_sync(1, kConsumerThreads);
+    vmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kConsumerWarps; ++i) vmax = fmaxf(vmax, wred[8 + i]);
+    // Exact power-of-two scale: the largest element lands in [2^14, 2^15).
+    int expo = (int)((__float_as_uint(vmax) >> 23) & 0xffu) - 127;
+    int shift = 14 - expo;
+    shift = max(-100, min(100, shift));
+    if (!(vmax > 0.0f) || !isfinite(vmax)) shift = 0;
+    const float xscale = __uint_as_float((uint32_t)(shift + 127) << 23);
+    const float xunscale = __uint_as_float((uint32_t)(127 - shift) << 23);
+
+    // Pass 2: scaled f16 values in place, plus per-group sums of the unscaled input.
+    const uint32_t rounds = (chunks + kConsumerThreads - 1u) / kConsumerThreads;
+    for (uint32_t r = 0; r < rounds; ++r) {
+        const uint32_t c = tid + r * kConsumerThreads;
+        float s8 = 0.0f;
+        if (c < chunks) {
+            float f[8];
+            if (p.io_type == STARK_B200_F32 && p.prologue == kProPlain) {
+                const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
+                float4 a = x4[2 * c], b = x4[2 * c + 1];
+                f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
+            } else {
+                uint4 v = reinterpret_cast<const uint4 *>(xs)[c];
+                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    f[2 * i] = __uint_as_float(wv[i] << 16);
+                    f[2 * i + 1] = __uint_as_float(wv[i] & 0xffff0000u);
+                }
+            }
+            __half hh[8], hl[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                s8 += f[i];
+                float sv = f[i] * xscale;
+                hh[i] = __float2half_rn(sv);
+                if (SPLIT) hl[i] = __float2half_rn(sv - __half2float(hh[i]));
+            }
+            reinterpret_cast<uint4 *>(xs)[c] = *reinterpret_cast<uint4 *>(hh);
+            if (SPLIT) reinterpret_cast<uint4 *>(xlo)[c] = *reinterpret_cast<uint4 *>(hl);
+        }
+        s8 += __shfl_xor_sync(0xffffffffu, s8, 1);
+        s8 += __shfl_xor_sync(0xffffffffu, s8, 2);
+        s8 += __shfl_xor_sync(0xffffffffu, s8, 4);
+        if (c < chunks && (lane & 7u) == 0) xsum[c >> 3] = s8;
+    }
+    named_bar_sync(1, kConsumerThreads);
+
+    // Main loop.
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    uint32_t s = 0;
+    uint32_t buf = 0;
+    float held = 0.0f;  // kEpiSwiGlu: the `up` value of the even tile
+    float best = -INFINITY;
+    uint32_t best_index = 0xffffffffu;
+    for (uint32_t tile = t0; tile < t1; ++tile) {
+        float acc_s0 = 0.0f, acc_s1 = 0.0f, acc_b0 = 0.0f, acc_b1 = 0.0f;
+        for (uint32_t st = 0; st < p.stages_per_tile; ++st, ++s) {
+            const uint32_t slot = s % p.num_stages;
+            if (!mbar_wait_bounded(&full[slot], (s / p.num_stages) & 1u, abort_flag)) {
+                *abort_flag = 1;
+                atomicOr(p.error_word, kErrMbarTimeout);
+            }
+            const uint8_t *stage = ring + (size_t)slot * p.stage_capacity;
+            for (uint32_t r = warp; r < p.stage_records; r += kConsumerWarps) {
+                const uint32_t kg = st * p.stage_records + r;
+                const uint8_t *rec = stage + r * kA4RecordBytes;
+                const uint4 wq = *reinterpret_cast<const uint4 *>(rec + lane * 16u);
+                const uint32_t sw = *reinterpret_cast<const uint32_t *>(rec + 512u + 4u * g);
+                const uint32_t bw = *reinterpret_cast<const uint32_t *>(rec + 544u + 4u * g);
+                const uint4 *xp = reinterpret_cast<const uint4 *>(xs + kg * 64u + t * 16u);
+                const uint4 xa = xp[0], xb = xp[1];
+                const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w};
+                float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (SPLIT) {
+                    const uint4 *lp = reinterpret_cast<const uint4 *>(xlo + kg * 64u + t * 16u);
+                    const uint4 la = lp[0], lb = lp[1];
+                    const uint32_t lw[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t a[4];
+                        dequant_a4_word(ww[j], a);
+                        mma_m16n8k16_f16(c, a, xw[2 * j], xw[2 * j + 1]);
+                        mma_m16n8k16_f16(c, a, lw[2 * j], lw[2 * j + 1]);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t a[4];
+                        dequant_a4_word(ww[j], a);
+                        mma_m16n8k16_f16(c, a, xw[2 * j], xw[2 * j + 1]);
+                    }
+                }
+                const float xs_g = xsum[kg];
+                acc_s0 = fmaf(__uint_as_float(sw << 16), c[0], acc_s0);
+                acc_s1 = fmaf(__uint_as_float(sw & 0xffff0000u), c[2], acc_s1);
+                acc_b0 = fmaf(__uint_as_float(bw << 16), xs_g, acc_b0);
+                acc_b1 = fmaf(__uint_as_float(bw & 0xffff0000u), xs_g, acc_b1);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);
+        }
+        // Cross-warp reduction of the 16 rows of this tile.
+        if (t == 0) {
+            red[(buf * kConsumerWarps + warp) * 16u + g] = fmaf(acc_s0, xunscale, acc_b0);
+            red[(buf * kConsumerWarps + warp) * 16u + g + 8u] = fmaf(acc_s1, xunscale, acc_b1);
+        }
+        named_bar_sync(1, kConsumerThreads);
+        if (tid < 16) {
+            float v = 0.0f;
+#pragma unroll
+            for (int wv = 0; wv < kConsumerWarps; ++wv) v += red[(buf * kConsumerWarps + wv) * 16u + tid];
+            const uint32_t row = tile_row0(tile, p.pair_halves, p.rows) + tid;
+            const bool valid = row < p.rows;
+            if (p.epilogue == kEpiStore) {
+                if (valid) {
+                    if (p.io_type == STARK_B200_F32)
+                        reinterpret_cast<float *>(p.y)[row] = v;
+                    else
+                        reinterpret_cast<uint16_t *>(p.y)[row] = f32_to_bf16_bits(v);
+                }
+            } else if (p.epilogue == kEpiResidual) {
+                if (valid) {
+                    const float r = bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(p.resid)[row]);
+                    reinterpret_cast<uint16_t *>(p.y)[row] = f32_to_bf16_bits(bf16_round(v) + r);
+                }
+            } else if (p.epilogue == kEpiSwiGlu) {
+                if ((tile & 1u) == 0) {
+                    held = bf16_round(v);
+                } else {
+                    // gated_act_mul.rs:80-95: silu in f32 -> bf16, product of two bf16 -> bf16
+                    const float gate = bf16_round(v);
+                    const float activated = bf16_round(gate / (1.0f + expf(-1.0f * gate)));
+                    const uint32_t orow = (tile >> 1) * 16u + tid;
+                    if (orow < p.rows / 2u)
+                        reinterpret_cast<uint16_t *>(p.y)[orow] = f32_to_bf16_bits(held * activated);
+                }
+            } else {  // kEpiLogits
+                if (valid) {
+                    const uint16_t hb = f32_to_bf16_bits(v);
+                    reinterpret_cast<uint16_t *>(p.y)[row] = hb;
+                    const float lv = bf16_bits_to_f32(hb);
+                    // NaN must surface: treat any non-finite logit as the maximum so the host sees it.
+                    const float key = isfinite(lv) ? lv : INFINITY;
+                    if (key > best || (key == best && row < best_index)) {
+                        best = key;
+                        best_index = row;
+                    }
+                }
+            }
+        }
+        buf ^= 1u;
+    }
+    if (p.epilogue == kEpiLogits && warp == 0) {
+        // first index of the maximum over this CTA's rows
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) {
+            float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            uint32_t oi = __shfl_xor_sync(0xffffffffu, best_index, o);
+            if (ov > best || (ov == best && oi < best_index)) {
+                best = ov;
+                best_index = oi;
+            }
+        }
+        if (lane == 0) {
+            p.partial_max[blockIdx.x] = best;
+            p.partial_index[blockIdx.x] = best_index;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------ re-tiling
+
+__global__ void retile_a4_codes_kernel(const uint8_t *__restrict__ codes, uint8_t *__restrict__ out, uint32_t rows,
+                                       uint32_t columns, uint32_t row_tiles, uint32_t pair_halves) {
+    const uint32_t groups = columns / 64u;
+    const uint64_t total = (uint64_t)row_tiles * groups * 128u;  // words
+    const size_t row_bytes = columns / 2u;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t j = (uint32_t)(i & 3u), lane = (uint32_t)((i >> 2) & 31u);
+        const uint64_t recno = i >> 7;
+        const uint32_t kg = (uint32_t)(recno % groups), tile = (uint32_t)(recno / groups);
+        const uint32_t g = lane >> 2, t = lane & 3u;
+        const uint32_t row0 = tile_row0(tile, pair_halves, rows);
+        uint32_t word = 0;
+#pragma unroll
+        for (uint32_t pnib = 0; pnib < 8; ++pnib) {
+            const uint32_t e = pnib >> 2, r = (pnib >> 1) & 1u, h = pnib & 1u;
+            const uint32_t row = row0 + g + 8u * h;
+            const uint32_t col = 64u * kg + 16u * t + 4u * j + 2u * r + e;
+            uint32_t q = 0;
+            // packed_code for bits = 4: column 2j is the low nibble of byte j (reference.rs:91-104)
+            if (row < rows) q = (codes[(size_t)row * row_bytes + (col >> 1)] >> (4u * (col & 1u))) & 15u;
+            word |= q << (4u * pnib);
+        }
+        *reinterpret_cast<uint32_t *>(out + recno * kA4RecordBytes + lane * 16u + j * 4u) = word;
+    }
+}
+
+__global__ void retile_a4_planes_kernel(const uint16_t *__restrict__ scales, const uint16_t *__restrict__ biases,
+                                        uint8_t *__restrict__ out, uint32_t rows, uint32_t columns,
+                                        uint32_t row_tiles, uint32_t pair_halves, uint32_t scale_layout,
+                                        uint32_t plane_pitch) {
+    const uint32_t groups = columns / 64u;
+    const uint64_t total = (uint64_t)row_tiles * groups * 16u;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t idx = (uint32_t)(i & 15u);
+        const uint64_t recno = i >> 4;
+        const uint32_t kg = (uint32_t)(recno % groups), tile = (uint32_t)(recno / groups);
+        const uint32_t row = tile_row0(tile, pair_halves, rows) + (idx >> 1) + 8u * (idx & 1u);
+        uint16_t sv = 0, bv = 0;
+        if (row < rows) {
+            const size_t at = scale_layout == 0 ? (size_t)row * groups + kg : (size_t)kg * plane_pitch + row;
+            sv = scales[at];
+            bv = biases[at];
+        }
+        uint16_t *rec = reinterpret_cast<uint16_t *>(out + recno * kA4RecordBytes + 512u);
+        rec[idx] = sv;
+        rec[16u + idx] = bv;
+    }
+}
+
+// Integer codes back out of the records through dequant_a4_word (the matvec's own extraction).
+__global__ void unpack_a4_kernel(const uint8_t *__restrict__ data, uint8_t *__restrict__ dst, uint32_t rows,
+                                 uint32_t columns, uint32_t row_tiles, uint32_t pair_halves) {
+    const uint32_t groups = columns / 64u;
+    const uint64_t total = (uint64_t)row_tiles * groups * 128u;
+    for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < total;
+         i += (uint64_t)gridDim.x * blockDim.x) {
+        const uint32_t j = (uint32_t)(i & 3u), lane = (uint32_t)((i >> 2) & 31u);
+        const uint64_t recno = i >> 7;
+        const uint32_t kg = (uint32_t)(recno % groups), tile = (uint32_t)(recno / groups);
+        const uint32_t g = lane >> 2, t = lane & 3u;
+        const uint32_t row0 = tile_row0(tile, pair_halves, rows);
+        const uint32_t word = *reinterpret_cast<const uint32_t *>(data + recno * kA4RecordBytes + lane * 16u + j * 4u);
+        uint32_t a[4];
+        dequant_a4_word(word, a);
+        // a[0]: row g, k-pair r=0; a[1]: row g+8, r=0; a[2]: row g, r=1; a[3]: row g+8, r=1
+#pragma unroll
+        for (int reg = 0; reg < 4; ++reg) {
+            const uint32_t h = reg & 1u, r = (uint32_t)reg >> 1;
+            const __half2 v = *reinterpret_cast<const __half2 *>(&a[reg]);
+            const float lo = __low2float(v), hi = __high2float(v);
+            const uint32_t row = row0 + g + 8u * h;
+            const uint32_t col = 64u * kg + 16u * t + 4u * j + 2u * r;
+            if (row < rows) {
+                dst[(size_t)row * columns + col] = (uint8_t)(int)lo;
+                dst[(size_t)row * columns + col + 1u] = (uint8_t)(int)hi;
+            }
+        }
+    }
+}
+
+uint32_t pick_stage_records(uint32_t groups) {
+    for (uint32_t r = std::min(groups, kMaxStageRecords); r >= 1; --r)
+        if (groups % r == 0) return r;
+    return 1;
+}
+
+int sm_count_cached() {
+    static int cached[64] = {0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+}  // namespace
+
+stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
+    const QMatrix *m = a.matrix;
+    if (!m || !a.x || !a.y || a.m != 1) return STARK_B200_INVALID_ARGUMENT;
+    if (m->format != kFmtAffine4) return STARK_B200_UNSUPPORTED;
+    if (a.epilogue == kEpiSwiGlu && !m->pair_halves) return STARK_B200_INVALID_ARGUMENT;
+    if (a.io_type == STARK_B200_F32 && (a.prologue != kProPlain || a.epilogue != kEpiStore))
+        return STARK_B200_UNSUPPORTED;
+
+    QmvParams p{};
+    p.w = m->data;
+    p.rows = m->rows;
+    p.row_tiles = m->row_tiles;
+    p.groups = m->groups;
+    p.stage_records = pick_stage_records(m->groups);
+    p.stages_per_tile = m->groups / p.stage_records;
+    p.stage_capacity = (p.stage_records * kA4RecordBytes + 127u) & ~127u;
+    p.pair_halves = m->pair_halves;
+    p.unit_tiles = a.epilogue == kEpiSwiGlu ? 2u : 1u;
+    p.io_type = a.io_type;
+    p.prologue = a.prologue;
+    p.epilogue = a.epilogue;
+    p.x = a.x;
+    p.y = a.y;
+    p.norm_weight = a.norm_weight;
+    p.eps = a.eps;
+    p.resid = a.resid;
+    p.partial_max = a.partial_max;
+    p.partial_index = a.partial_index;
+    p.error_word = a.error_word;
+
+    const bool split = a.io_type == STARK_B200_F32;
+    // Ring depth: as deep as fits in ~100 KB so that two kernels of a dependent-launch chain are
+    // resident on an SM at once (the next one prefetches while this one drains).
+    const uint32_t budget = 100u * 1024u;
+    uint32_t stages = 8;
+    while (stages > 2 && smem_layout(stages, p.stage_capacity, m->columns, split).total > budget) --stages;
+    p.num_stages = stages;
+    const uint32_t smem = smem_layout(stages, p.stage_capacity, m->columns, split).total;
+    if (smem > 220u * 1024u) return STARK_B200_UNSUPPORTED;
+
+    const uint32_t units = p.row_tiles / p.unit_tiles;
+    const uint32_t grid = std::max(1u, std::min(units, (uint32_t)sm_count_cached()));
+    if (a.out_grid) *a.out_grid = grid;
+
+    auto kernel = split ? qmv_a4_kernel<true> : qmv_a4_kernel<false>;
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[split ? 1 : 0]) {
+        SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
+        attr_set[split ? 1 : 0] = true;
+    }
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = a.pdl ? 1 : 0;
+    SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+    return STARK_B200_OK;
+}
+
+stark_b200_status qmatrix_from_affine_device(const uint8_t *codes, const void *scales, const void *biases,
+                                             const stark_b200_affine_desc &d, cudaStream_t stream, QMatrix **out) {
+    if (d.bits != 4 || d.group != 64 || d.plane_kind != STARK_B200_PLANE_BF16) return STARK_B200_UNSUPPORTED;
+    if (d.rows == 0 || d.columns == 0 || d.columns % 64u != 0) return STARK_B200_INVALID_ARGUMENT;
+    if (d.pair_halves && (d.rows % 32u != 0)) return STARK_B200_INVALID_ARGUMENT;
+    if (d.scale_layout == 1 && d.plane_pitch < d.rows) return STARK_B200_INVALID_ARGUMENT;
+    QMatrix *m = new (std::nothrow) QMatrix();
+    if (!m) return STARK_B200_OUT_OF_MEMORY;
+    m->format = kFmtAffine4;
+    m->rows = d.rows;
+    m->columns = d.columns;
+    m->row_tiles = (d.rows + 15u) / 16u;
+    m->groups = d.columns / 64u;
+    m->pair_halves = d.pair_halves;
+    m->record_bytes = kA4RecordBytes;
+    m->bytes = (size_t)m->row_tiles * m->groups * kA4RecordBytes;
+    cudaGetDevice(&m->device);
+    cudaError_t e = cudaMalloc(&m->data, m->bytes);
+    if (e != cudaSuccess) {
+        delete m;
+        return cuda_status(e);
+    }
+    const uint64_t words = (uint64_t)m->row_tiles * m->groups * 128u;
+    const uint32_t blocks = (uint32_t)std::min<uint64_t>((words + 255u) / 256u, 148u * 16u);
+    retile_a4_codes_kernel<<<blocks, 256, 0, stream>>>(codes, m->data, m->rows, m->columns, m->row_tiles,
+                                                       m->pair_halves);
+    const uint64_t planes = (uint64_t)m->row_tiles * m->groups * 16u;
+    const uint32_t pblocks = (uint32_t)std::min<uint64_t>((planes + 255u) / 256u, 148u * 16u);
+    retile_a4_planes_kernel<<<pblocks, 256, 0, stream>>>(
+        reinterpret_cast<const uint16_t *>(scales), reinterpret_cast<const uint16_t *>(biases), m->data, m->rows,
+        m->columns, m->row_tiles, m->pair_halves, d.scale_layout, d.plane_pitch);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        cudaFree(m->data);
+        delete m;
+        return cuda_status(e);
+    }
+    *out = m;
+    return STARK_B200_OK;
+}
+
+stark_b200_status qmatrix_unpack_codes_device(const QMatrix *m, uint8_t *dst, cudaStream_t stream) {
+    if (m->format != kFmtAffine4) return STARK_B200_UNSUPPORTED;
+    const uint64_t words = (uint64_t)m->row_tiles * m->groups * 128u;
+    const uint32_t blocks = (uint32_t)std::min<uint64_t>((words + 255u) / 256u, 148u * 16u);
+    unpack_a4_kernel<<<blocks, 256, 0, stream>>>(m->data, dst, m->rows, m->columns, m->row_tiles, m->pair_halves);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+void qmatrix_free(QMatrix *m) {
+    if (!m) return;
+    if (m->data) cudaFree(m->data);
+    delete m;
+}
+
+}  // namespace sb

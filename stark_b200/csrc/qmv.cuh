@@ -1,0 +1,86 @@
+// Quantized matrix handle and the launch interface of the fused-dequant matvec kernels.
+#pragma once
+#include "common.cuh"
+
+namespace sb {
+
+// Storage formats of a re-tiled quantized matrix in device memory.
+enum QFormat : uint32_t {
+    kFmtAffine4 = 0,  // MLX affine, 4 bit, group 64, bf16 planes: 576-byte records
+    kFmtAffine8 = 1,  // MLX affine, 8 bit, group 64, bf16 planes: 1088-byte records
+    kFmtQ8_0 = 2,     // GGUF Q8_0: 16 rows x 64 columns per record, f16 block scales
+    kFmtQ4_K = 3,     // GGUF Q4_K: 16 rows x 256 columns per record
+};
+
+// One record covers 16 rows x 64 columns (one quantization group per row).
+//   bytes [0, 512): lane L (0..31) owns 16 bytes = 4 words; word j, nibble p (bits 4p..4p+3) holds
+//                   W[row0 + g + 8*(p&1)][64*kg + 16*t + 4*j + 2*((p>>1)&1) + (p>>2)],  g = L>>2, t = L&3.
+//                   That is exactly the A-fragment order of mma.m16n8k16 after the lop3 extraction
+//                   in dequant_a4_word(), so a lane needs one 128-bit load per record and no shuffles.
+//   bytes [512, 544): 16 bf16 scales, index 2*g + h <-> row row0 + g + 8*h
+//   bytes [544, 576): 16 bf16 biases, same order
+// Records are ordered [row tile][column group], so a CTA's share of the matrix is one contiguous
+// byte range that streams through bulk copies.  576 B per 1024 weights = 0.5625 B per weight, the
+// same as the MLX layout.
+constexpr uint32_t kA4RecordBytes = 576;
+constexpr uint32_t kA8RecordBytes = 1088;
+constexpr uint32_t kMaxStageRecords = 32;
+
+struct QMatrix {
+    QFormat format;
+    uint32_t rows;         // logical rows N
+    uint32_t columns;      // K
+    uint32_t row_tiles;    // ceil(N / 16) (even when pair_halves)
+    uint32_t groups;       // K / 64
+    uint32_t pair_halves;  // storage tile 2j = rows 16j.., tile 2j+1 = rows N/2 + 16j..
+    uint32_t record_bytes;
+    uint8_t *data;  // device
+    size_t bytes;
+    int device;
+};
+
+// First logical row of storage tile `tile`.
+__host__ __device__ inline uint32_t tile_row0(uint32_t tile, uint32_t pair_halves, uint32_t rows) {
+    if (!pair_halves) return tile * 16u;
+    return (tile >> 1) * 16u + ((tile & 1u) ? rows / 2u : 0u);
+}
+
+enum QmvPrologue : uint32_t {
+    kProPlain = 0,    // x is the input vector (bf16 or f32)
+    kProRmsNorm = 1,  // x = bf16(bf16(h * rms_inv) * bf16(norm_w)), h bf16
+};
+enum QmvEpilogue : uint32_t {
+    kEpiStore = 0,     // y[row] = value (bf16 or f32)
+    kEpiResidual = 1,  // y[row] = bf16(bf16(value) + resid[row])   (resid may alias y)
+    kEpiSwiGlu = 2,    // pair_halves matrix: y[r] = bf16(up[r] * bf16(silu(gate[r])))
+    kEpiLogits = 3,    // y[row] = bf16(value) and a per-CTA (max, first index) partial
+};
+
+struct QmvArgs {
+    const QMatrix *matrix;
+    const void *x;  // [m, K]
+    void *y;        // [m, N] (or [m, N/2] for kEpiSwiGlu)
+    uint32_t m;     // input rows, 1..8
+    uint32_t io_type;
+    QmvPrologue prologue;
+    QmvEpilogue epilogue;
+    const float *norm_weight;  // kProRmsNorm
+    float eps;
+    const void *resid;        // kEpiResidual
+    float *partial_max;       // kEpiLogits: [grid] per-CTA maxima
+    uint32_t *partial_index;  // kEpiLogits: [grid] per-CTA first index of the maximum
+    uint32_t *error_word;     // device word, OR-ed with kErr* bits
+    bool pdl;                 // launch with programmatic stream serialization
+    uint32_t *out_grid;       // optional: number of CTAs launched
+};
+
+stark_b200_status qmv_launch(const QmvArgs &args, cudaStream_t stream);
+
+// Re-tiling (device kernels; inputs already in device memory).
+stark_b200_status qmatrix_from_affine_device(const uint8_t *codes, const void *scales, const void *biases,
+                                             const stark_b200_affine_desc &desc, cudaStream_t stream,
+                                             QMatrix **out);
+stark_b200_status qmatrix_unpack_codes_device(const QMatrix *m, uint8_t *dst_device, cudaStream_t stream);
+void qmatrix_free(QMatrix *m);
+
+}  // namespace sb

@@ -1,0 +1,131 @@
+"""Host-side mirror of the reference's per-operator interface, over the C ABI.
+
+Names follow the reference: a quantized ``B`` operand with MLX-affine planes
+(``MatmulB::Quantized``, crates/stark-engine/src/backends/common/kernel/matmul/arguments.rs:7-24)
+becomes :class:`QMatrix`; ``MatmulKernel::encode`` / ``Weights::matvec`` become :meth:`QMatrix.matvec`.
+Arrays crossing this layer are numpy arrays of bit patterns (``uint16`` for bf16) or f32; device
+pointers are plain integers.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib
+from ._lib import BF16, DEVICE, F32, HOST, check
+
+
+def _ptr(a: np.ndarray) -> C.c_void_p:
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def device_count() -> int:
+    n = C.c_int32(0)
+    _lib.load().stark_b200_device_count(C.byref(n))
+    return n.value
+
+
+def take_device_error() -> int:
+    w = C.c_uint32(0)
+    check(_lib.load().stark_b200_take_device_error(C.byref(w)), "take_device_error")
+    return w.value
+
+
+class DeviceBuffer:
+    """A raw device allocation owned by the library's allocator."""
+
+    def __init__(self, nbytes: int):
+        self.nbytes = int(nbytes)
+        p = C.c_void_p()
+        check(_lib.load().stark_b200_device_malloc(C.byref(p), self.nbytes), "device_malloc")
+        self.ptr = p.value
+
+    def upload(self, a: np.ndarray, stream: int = 0) -> "DeviceBuffer":
+        a = np.ascontiguousarray(a)
+        assert a.nbytes <= self.nbytes
+        lib = _lib.load()
+        check(lib.stark_b200_memcpy_h2d(self.ptr, _ptr(a), a.nbytes, stream), "memcpy_h2d")
+        check(lib.stark_b200_stream_synchronize(stream), "stream_synchronize")
+        return self
+
+    def download(self, dtype, count: int, stream: int = 0) -> np.ndarray:
+        out = np.empty(count, dtype)
+        lib = _lib.load()
+        check(lib.stark_b200_memcpy_d2h(_ptr(out), self.ptr, out.nbytes, stream), "memcpy_d2h")
+        check(lib.stark_b200_stream_synchronize(stream), "stream_synchronize")
+        return out
+
+    def free(self):
+        if self.ptr:
+            _lib.load().stark_b200_device_free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class QMatrix:
+    """A quantized weight matrix resident (re-tiled) in device memory."""
+
+    def __init__(self, handle: int, rows: int, columns: int, pair_halves: bool = False):
+        self._h = C.c_void_p(handle)
+        self.rows, self.columns, self.pair_halves = rows, columns, pair_halves
+
+    @classmethod
+    def from_affine(cls, codes: np.ndarray, scales: np.ndarray, biases: np.ndarray, rows: int, columns: int,
+                    bits: int = 4, group: int = 64, plane_kind: int = _lib.PLANE_BF16, scale_layout: int = 0,
+                    plane_pitch: int = 0, pair_halves: bool = False) -> "QMatrix":
+        """codes: MLX ``uint32[rows, columns*bits/32]`` (or the same bytes as uint8); planes: bit patterns."""
+        codes = np.ascontiguousarray(codes)
+        scales = np.ascontiguousarray(scales)
+        biases = np.ascontiguousarray(biases)
+        if codes.nbytes != rows * columns * bits // 8:
+            raise ValueError("inconsistent affine planes")
+        d = _lib.AffineDesc(C.sizeof(_lib.AffineDesc), _lib.ABI_VERSION, rows, columns, bits, group, plane_kind,
+                            scale_layout, plane_pitch, HOST, int(pair_halves), 0)
+        h = C.c_void_p()
+        check(_lib.load().stark_b200_qmatrix_create_affine(_ptr(codes), _ptr(scales), _ptr(biases), C.byref(d),
+                                                           C.byref(h)), "qmatrix_create_affine")
+        return cls(h.value, rows, columns, pair_halves)
+
+    @property
+    def handle(self) -> int:
+        return self._h.value
+
+    def device_bytes(self) -> int:
+        n = C.c_uint64(0)
+        check(_lib.load().stark_b200_qmatrix_device_bytes(self._h, C.byref(n)), "qmatrix_device_bytes")
+        return n.value
+
+    def unpack_codes(self) -> np.ndarray:
+        out = np.empty(self.rows * self.columns, np.uint8)
+        check(_lib.load().stark_b200_qmatrix_unpack_codes(self._h, _ptr(out), out.size), "qmatrix_unpack_codes")
+        return out.reshape(self.rows, self.columns)
+
+    def matvec(self, x: np.ndarray, io_type: int = BF16) -> np.ndarray:
+        """y = W x through host buffers (copies in and out inside the call)."""
+        dt = np.float32 if io_type == F32 else np.uint16
+        x = np.ascontiguousarray(x, dtype=dt)
+        m = 1 if x.ndim == 1 else x.shape[0]
+        if x.size != m * self.columns:
+            raise ValueError("invalid matvec input shape or values")
+        y = np.empty((m, self.rows), dt)
+        check(_lib.load().stark_b200_op_qmv(self._h, _ptr(x), _ptr(y), m, io_type, HOST, None), "op_qmv")
+        return y[0] if x.ndim == 1 else y
+
+    def matvec_device(self, x_ptr: int, y_ptr: int, m: int = 1, io_type: int = BF16, stream: int = 0) -> None:
+        check(_lib.load().stark_b200_op_qmv(self._h, x_ptr, y_ptr, m, io_type, DEVICE, stream), "op_qmv")
+
+    def destroy(self):
+        if self._h and self._h.value:
+            _lib.load().stark_b200_qmatrix_destroy(C.byref(self._h))
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass

@@ -1,0 +1,87 @@
+"""Seeded synthetic weights and prompts in the reference's on-disk tensor layouts.
+
+No checkpoint or dataset is available offline, so every configuration is random-init by
+definition: codes uniform, bf16 scales uniform in a stated range, bias = -8 * scale (4 bit).  The
+arrays use the MLX layout the reference reads (``uint32[rows, columns/8]`` codes with 8 nibbles per
+word along K, planes ``[rows, columns/group]``;
+crates/stark-engine/src/engine/hybrid/weights.rs:1157-1228).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+# Shapes of the named configurations (Qwen3-shaped dense decoders).
+CONFIGS = {
+    "qwen3-0.6b": dict(layers=28, hidden=1024, q_heads=16, kv_heads=8, head_dim=128, inter=3072, vocab=151936,
+                       tied=True, eps=1e-6, rope_theta=1e6),
+    "qwen3-8b": dict(layers=36, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, inter=12288, vocab=151936,
+                     tied=False, eps=1e-6, rope_theta=1e6),
+    # small shapes for parity tests (same graph, minutes -> milliseconds on the CPU oracle)
+    "tiny": dict(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=128, inter=512, vocab=1024, tied=True,
+                 eps=1e-6, rope_theta=1e6),
+    "small": dict(layers=4, hidden=1024, q_heads=16, kv_heads=8, head_dim=128, inter=3072, vocab=8192, tied=False,
+                  eps=1e-6, rope_theta=1e6),
+}
+
+
+def f32_to_bf16(x: np.ndarray) -> np.ndarray:
+    u = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+
+
+def bf16_to_f32(h: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(h, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def affine4_matrix(rng: np.random.Generator, rows: int, columns: int, scale_lo: float = 0.005,
+                   scale_hi: float = 0.02, group: int = 64) -> dict:
+    """One 4-bit MLX-affine matrix: nibbles uniform 0..15, scale U[lo, hi] (bf16), bias = -8*scale."""
+    words = rows * columns // 8
+    codes = rng.integers(0, 1 << 32, size=words, dtype=np.uint32).reshape(rows, columns // 8)
+    scales_f = rng.uniform(scale_lo, scale_hi, size=(rows, columns // group)).astype(np.float32)
+    scales = f32_to_bf16(scales_f)
+    biases = f32_to_bf16(-8.0 * bf16_to_f32(scales))
+    return dict(codes=codes, scales=scales, biases=biases, n=rows, k=columns, bits=4, group=group)
+
+
+def bf16_normal(rng: np.random.Generator, count: int, sigma: float = 1.0) -> np.ndarray:
+    return f32_to_bf16((rng.standard_normal(count) * sigma).astype(np.float32))
+
+
+def matvec_case(seed: int = 0, rows: int = 4096, columns: int = 4096) -> dict:
+    """The single-matvec configuration: W 4096x4096, scales U[0.005, 0.02], x ~ N(0,1) in bf16."""
+    rng = np.random.default_rng(seed)
+    w = affine4_matrix(rng, rows, columns)
+    w["x"] = bf16_normal(rng, columns)
+    return w
+
+
+def dense_weights(cfg: dict, seed: int = 0) -> dict:
+    """Random-init weights for a Qwen3-shaped dense decoder.
+
+    Scale ranges are the single-matvec range times 17.3/sqrt(K), which keeps every linear layer's
+    output at the magnitude of its input (unit-variance rows) so that 28-36 layers stay in range.
+    """
+    rng = np.random.default_rng(seed)
+    D, hd, I, V = cfg["hidden"], cfg["head_dim"], cfg["inter"], cfg["vocab"]
+    qkv_n = (cfg["q_heads"] + 2 * cfg["kv_heads"]) * hd
+
+    def mat(n, k, gain=1.0):
+        c = gain * 17.3 / np.sqrt(k)
+        return affine4_matrix(rng, n, k, 0.005 * c, 0.02 * c)
+
+    def norm(n):
+        return (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+
+    layers = []
+    for _ in range(cfg["layers"]):
+        layers.append(dict(attn_norm=norm(D), mlp_norm=norm(D), q_norm=norm(hd), k_norm=norm(hd),
+                           qkv=mat(qkv_n, D), o=mat(D, cfg["q_heads"] * hd, 0.5), upgate=mat(2 * I, D),
+                           down=mat(D, I, 0.5)))
+    embed = mat(V, D)
+    lm_head = embed if cfg["tied"] else mat(V, D)
+    return dict(layers=layers, embed=embed, lm_head=lm_head, final_norm=norm(D))
+
+
+def prompt(cfg: dict, length: int, seed: int = 1) -> np.ndarray:
+    return np.random.default_rng(seed).integers(0, cfg["vocab"], size=length, dtype=np.uint32)
