@@ -73,6 +73,10 @@ enum {
 uint32_t stark_b200_abi_version(void);
 const char *stark_b200_status_name(uint32_t status);
 
+/* Name of the last CUDA runtime error this library saw on the calling thread ("cudaSuccess" if
+ * none); a diagnostic aid, the library itself never prints. */
+const char *stark_b200_last_cuda_error(void);
+
 /* Device plumbing for callers that do not bring their own allocator. */
 stark_b200_status stark_b200_device_count(int32_t *out_count);
 stark_b200_status stark_b200_set_device(int32_t device);
@@ -135,6 +139,169 @@ stark_b200_status stark_b200_qmatrix_unpack_codes(const stark_b200_qmatrix *matr
  * Weights::matvec (weights.rs:1311-1350, 2511-2553).  io_type selects bf16 or f32 vectors. */
 stark_b200_status stark_b200_op_qmv(const stark_b200_qmatrix *matrix, const void *x, void *y, uint32_t m,
                                     uint32_t io_type, uint32_t location, void *stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Small operators (bf16 bit patterns unless stated).  Each names the reference routine it stands
+ * in for; `location` applies to every pointer of the call.
+ */
+/* normalization (RMS, only-normalization rounding, optional fused residual add into `shortcut`):
+ * crates/stark-engine/src/backends/cpu/kernel/normalization/normalization.rs:13-191.
+ * shortcut may be NULL; residual_add != 0 requires it (ShortcutMode::Add), else it is a copy. */
+stark_b200_status stark_b200_op_rmsnorm(const void *input, const float *scales, void *output, void *shortcut,
+                                        uint32_t count, float epsilon, uint32_t residual_add, uint32_t location,
+                                        void *stream);
+/* gated_act_mul on a fused [up; gate] row, SiLU:
+ * crates/stark-engine/src/backends/cpu/kernel/gated_act_mul/gated_act_mul.rs:17-152. */
+stark_b200_status stark_b200_op_swiglu(const void *fused, void *out, uint32_t gated_dim, uint32_t location,
+                                       void *stream);
+/* Fused up/gate matvec + SwiGLU on a pair_halves matrix: out[r] = up[r] * silu(gate[r]), the
+ * composition of MatmulKernel::encode and GatedActMul (crates/stark-engine/src/encodable_block/mlp/dense.rs:99-115). */
+stark_b200_status stark_b200_op_qmv_swiglu(const stark_b200_qmatrix *matrix, const void *x, void *out,
+                                           uint32_t location, void *stream);
+/* Greedy token: first index of the maximum, UINT32_MAX if any logit is not finite
+ * (crates/stark-engine/src/backends/cpu/kernel/sampling/unified_sampling.rs:36-45,108-116). */
+stark_b200_status stark_b200_op_argmax(const void *logits_bf16, uint32_t vocab, uint32_t *out_index,
+                                       uint32_t location, void *stream);
+/* Full-vocabulary log-probabilities in f64: log p_i = logit_i - logsumexp
+ * (crates/stark-score/src/scoring.rs:299-336). */
+stark_b200_status stark_b200_op_log_softmax(const float *logits, double *out, uint32_t vocab, uint32_t location,
+                                            void *stream);
+/* moe_route: softmax over experts, iterative top-k (first maximum wins), renormalise
+ * (crates/stark-engine/src/backends/cpu/kernel/moe.rs:25-82). */
+stark_b200_status stark_b200_op_moe_route(const float *logits, uint32_t *ids, float *weights, uint32_t rows,
+                                          uint32_t experts, uint32_t active, uint32_t round_weights,
+                                          uint32_t round_logits, uint32_t location, void *stream);
+
+/* Decode attention for one new row over a KV cache of `position` earlier rows, with the
+ * per-head RMS norm of Q and K, RoPE and the cache append fused in.  Replaces QKVNorm +
+ * AttentionPrepare + AttentionSinglePass/TwoPass
+ * (crates/stark-engine/src/backends/cpu/kernel/attention/qkv_norm.rs:8-111,
+ *  attention_prepare.rs:187-316, attention_single_pass.rs:11-133).
+ * Host-memory call: keys/values are [capacity, kv_heads, 128] bf16 row-major (the reference's
+ * cache layout) holding `position` valid rows; row `position` is written on return.
+ * qkv is the packed [q; k; v] row; out is [q_heads, 128].  q_norm/k_norm may be NULL (no norm);
+ * rope_theta <= 0 disables RoPE. */
+typedef struct stark_b200_attention_desc {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    uint32_t q_heads;
+    uint32_t kv_heads;
+    uint32_t head_dim; /* 128 */
+    uint32_t position;
+    uint32_t capacity;
+    uint32_t splits; /* 0 = library default */
+    float epsilon;
+    float rope_theta;
+} stark_b200_attention_desc;
+stark_b200_status stark_b200_op_attention_decode(const void *qkv, void *keys, void *values, void *out,
+                                                 const float *q_norm, const float *k_norm,
+                                                 const stark_b200_attention_desc *desc);
+
+/* ------------------------------------------------------------------------------------------
+ * Model surface: the FFI image of hybrid::Model / LanguageModel for a Qwen3-shaped dense decoder
+ * (crates/stark-engine/src/engine/hybrid/mod.rs:347-1428,
+ *  crates/stark-engine/src/engine/language_model/mod.rs:72-127).
+ * A model is built empty from its shape, receives its tensors in the reference's layouts, and is
+ * then finalized; after that the calls mirror stark_glm_{reset,prefill,step,readout_f32,...}
+ * (stark_glm.h:128-147).  One host thread per handle.  A device fault fences the handle.
+ */
+typedef struct stark_b200_dense_config {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    uint32_t layers;
+    uint32_t hidden;
+    uint32_t q_heads;
+    uint32_t kv_heads;
+    uint32_t head_dim; /* 128 */
+    uint32_t inter;    /* SwiGLU intermediate width */
+    uint32_t vocab;
+    uint32_t tied;     /* 1: read-out shares the embedding table */
+    uint32_t context_tokens;
+    float eps;
+    float rope_theta;
+    uint32_t reserved;
+} stark_b200_dense_config;
+
+/* Which tensor a set call addresses.  Matrices: rows [q; k; v] for QKV and [up; gate] for UPGATE
+ * (crates/stark-engine/tools: tools/converter/stark_convert/adapters/dense.py:431-432). */
+#define STARK_B200_MAT_EMBED 0u
+#define STARK_B200_MAT_LM_HEAD 1u
+#define STARK_B200_MAT_QKV 2u
+#define STARK_B200_MAT_O 3u
+#define STARK_B200_MAT_UPGATE 4u
+#define STARK_B200_MAT_DOWN 5u
+#define STARK_B200_VEC_FINAL_NORM 0u
+#define STARK_B200_VEC_ATTN_NORM 1u
+#define STARK_B200_VEC_MLP_NORM 2u
+#define STARK_B200_VEC_Q_NORM 3u
+#define STARK_B200_VEC_K_NORM 4u
+
+typedef struct stark_b200_info {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    uint32_t vocab_size;
+    uint32_t prefill_chunk_tokens; /* 1024: the grid prefix reuse is aligned to */
+    uint64_t context_tokens;
+    uint64_t position;
+    uint64_t capabilities;
+    uint32_t fenced;
+    uint32_t launches_per_step;
+    uint64_t weight_bytes; /* device bytes of all quantized matrices */
+    uint64_t kv_bytes_per_token;
+    uint64_t launches_issued; /* kernels of this library launched on this handle so far */
+} stark_b200_info;
+
+#define STARK_B200_CAP_FULL_F32_READOUT UINT64_C(1)
+#define STARK_B200_CAP_SERIAL_DECODE UINT64_C(2)
+#define STARK_B200_CAP_PREFIX_REWIND UINT64_C(4)
+#define STARK_B200_CAP_DEVICE_GREEDY UINT64_C(8)
+
+stark_b200_status stark_b200_model_create(const stark_b200_dense_config *config, stark_b200_model **out_model);
+/* desc->pair_halves is set by the library for UPGATE; pass the matrix in the reference's layout. */
+stark_b200_status stark_b200_model_set_affine(stark_b200_model *model, uint32_t layer, uint32_t which,
+                                              const void *codes, const void *scales, const void *biases,
+                                              const stark_b200_affine_desc *desc);
+stark_b200_status stark_b200_model_set_vector(stark_b200_model *model, uint32_t layer, uint32_t which,
+                                              const float *data, uint32_t count);
+stark_b200_status stark_b200_model_finalize(stark_b200_model *model);
+stark_b200_status stark_b200_destroy(stark_b200_model **model);
+stark_b200_status stark_b200_reset(stark_b200_model *model);
+stark_b200_status stark_b200_drain(stark_b200_model *model);
+stark_b200_status stark_b200_cancel(stark_b200_model *model);
+/* Feeds token_ids; logits of the last row are available afterwards (asynchronous until a read-out
+ * or drain).  hybrid::Model::ingest_prefix + step (mod.rs:897-1018). */
+stark_b200_status stark_b200_prefill(stark_b200_model *model, const uint32_t *token_ids, size_t count);
+stark_b200_status stark_b200_step(stark_b200_model *model, uint32_t token_id);
+/* Full-vocabulary logits of the last row, f32 (stark_glm_readout_f32). */
+stark_b200_status stark_b200_readout_f32(stark_b200_model *model, float *dst, size_t count);
+/* The same logits as bf16 bit patterns, the precision they are computed in. */
+stark_b200_status stark_b200_readout_bf16(stark_b200_model *model, uint16_t *dst, size_t count);
+/* Full-vocabulary log-probabilities of the last row (f64 arithmetic, scoring.rs:299-336), as f32. */
+stark_b200_status stark_b200_readout_logprobs_f32(stark_b200_model *model, float *dst, size_t count);
+/* Greedy token of the last row (first index of the maximum). */
+stark_b200_status stark_b200_argmax(stark_b200_model *model, uint32_t *out_token);
+/* Greedy decode chained on the device: out_tokens[0] is the greedy token of the current logits,
+ * out_tokens[i] the one after feeding out_tokens[i-1]; steps + 1 entries.  The analogue of the
+ * reference's on-device token chaining (stream.rs:1041-1047). */
+stark_b200_status stark_b200_generate_greedy(stark_b200_model *model, uint32_t steps, uint32_t *out_tokens);
+/* Prefix reuse: drop rows at and after `position` (KVCacheState::rewind,
+ * crates/stark-engine/src/encodable_block/mixer/attention/state.rs:175-195). */
+stark_b200_status stark_b200_rewind(stark_b200_model *model, uint64_t position);
+stark_b200_status stark_b200_get_info(stark_b200_model *model, stark_b200_info *info);
+
+/* ------------------------------------------------------------------------------------------
+ * Recorded launch sequences.  The reference records a whole token into one command buffer
+ * (crates/stark-engine/src/engine/hybrid/decode_graph.rs; one completion per token,
+ * crates/stark-engine/src/engine/language_model/stream/stream.rs:1184); the analogue here is a
+ * CUDA graph captured from the per-operator calls issued on `stream` between begin and end.
+ * Only calls with device pointers may be recorded.  Call every operator once outside a
+ * recording first: first use may allocate library state.
+ */
+typedef struct stark_b200_graph stark_b200_graph;
+stark_b200_status stark_b200_graph_begin(void *stream);
+stark_b200_status stark_b200_graph_end(void *stream, stark_b200_graph **out_graph);
+stark_b200_status stark_b200_graph_launch(stark_b200_graph *graph, void *stream);
+stark_b200_status stark_b200_graph_destroy(stark_b200_graph **graph);
 
 #ifdef __cplusplus
 }

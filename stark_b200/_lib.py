@@ -34,6 +34,28 @@ class AffineDesc(C.Structure):
         "plane_pitch", "location", "pair_halves", "reserved")]
 
 
+class AttentionDesc(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("struct_size", "abi_version", "q_heads", "kv_heads", "head_dim",
+                                          "position", "capacity", "splits")] + [("epsilon", C.c_float),
+                                                                                 ("rope_theta", C.c_float)]
+
+
+class DenseConfig(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("struct_size", "abi_version", "layers", "hidden", "q_heads", "kv_heads",
+                                          "head_dim", "inter", "vocab", "tied", "context_tokens")] + [
+        ("eps", C.c_float), ("rope_theta", C.c_float), ("reserved", C.c_uint32)]
+
+
+class Info(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("abi_version", C.c_uint32), ("vocab_size", C.c_uint32),
+                ("prefill_chunk_tokens", C.c_uint32), ("context_tokens", C.c_uint64), ("position", C.c_uint64),
+                ("capabilities", C.c_uint64), ("fenced", C.c_uint32), ("launches_per_step", C.c_uint32),
+                ("weight_bytes", C.c_uint64), ("kv_bytes_per_token", C.c_uint64), ("launches_issued", C.c_uint64)]
+
+
+MAT_EMBED, MAT_LM_HEAD, MAT_QKV, MAT_O, MAT_UPGATE, MAT_DOWN = range(6)
+VEC_FINAL_NORM, VEC_ATTN_NORM, VEC_MLP_NORM, VEC_Q_NORM, VEC_K_NORM = range(5)
+
 _lib = None
 
 
@@ -51,6 +73,7 @@ def load() -> C.CDLL:
     sig = {
         "stark_b200_abi_version": (u32, []),
         "stark_b200_status_name": (C.c_char_p, [u32]),
+        "stark_b200_last_cuda_error": (C.c_char_p, []),
         "stark_b200_device_count": (u32, [C.POINTER(C.c_int32)]),
         "stark_b200_set_device": (u32, [C.c_int32]),
         "stark_b200_device_malloc": (u32, [C.POINTER(vp), sz]),
@@ -65,6 +88,34 @@ def load() -> C.CDLL:
         "stark_b200_qmatrix_device_bytes": (u32, [vp, C.POINTER(u64)]),
         "stark_b200_qmatrix_unpack_codes": (u32, [vp, vp, sz]),
         "stark_b200_op_qmv": (u32, [vp, vp, vp, u32, u32, u32, vp]),
+        "stark_b200_op_rmsnorm": (u32, [vp, vp, vp, vp, u32, C.c_float, u32, u32, vp]),
+        "stark_b200_op_swiglu": (u32, [vp, vp, u32, u32, vp]),
+        "stark_b200_op_qmv_swiglu": (u32, [vp, vp, vp, u32, vp]),
+        "stark_b200_op_argmax": (u32, [vp, u32, C.POINTER(u32), u32, vp]),
+        "stark_b200_op_log_softmax": (u32, [vp, vp, u32, u32, vp]),
+        "stark_b200_op_moe_route": (u32, [vp, vp, vp, u32, u32, u32, u32, u32, u32, vp]),
+        "stark_b200_op_attention_decode": (u32, [vp, vp, vp, vp, vp, vp, C.POINTER(AttentionDesc)]),
+        "stark_b200_model_create": (u32, [C.POINTER(DenseConfig), C.POINTER(vp)]),
+        "stark_b200_model_set_affine": (u32, [vp, u32, u32, vp, vp, vp, C.POINTER(AffineDesc)]),
+        "stark_b200_model_set_vector": (u32, [vp, u32, u32, vp, u32]),
+        "stark_b200_model_finalize": (u32, [vp]),
+        "stark_b200_destroy": (u32, [C.POINTER(vp)]),
+        "stark_b200_reset": (u32, [vp]),
+        "stark_b200_drain": (u32, [vp]),
+        "stark_b200_cancel": (u32, [vp]),
+        "stark_b200_prefill": (u32, [vp, vp, sz]),
+        "stark_b200_step": (u32, [vp, u32]),
+        "stark_b200_readout_f32": (u32, [vp, vp, sz]),
+        "stark_b200_readout_bf16": (u32, [vp, vp, sz]),
+        "stark_b200_readout_logprobs_f32": (u32, [vp, vp, sz]),
+        "stark_b200_argmax": (u32, [vp, C.POINTER(u32)]),
+        "stark_b200_generate_greedy": (u32, [vp, u32, vp]),
+        "stark_b200_rewind": (u32, [vp, u64]),
+        "stark_b200_get_info": (u32, [vp, C.POINTER(Info)]),
+        "stark_b200_graph_begin": (u32, [vp]),
+        "stark_b200_graph_end": (u32, [vp, C.POINTER(vp)]),
+        "stark_b200_graph_launch": (u32, [vp, vp]),
+        "stark_b200_graph_destroy": (u32, [C.POINTER(vp)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -78,4 +129,7 @@ def load() -> C.CDLL:
 
 def check(status: int, where: str) -> None:
     if status != 0:
-        raise StarkB200Error(status, where)
+        detail = ""
+        if status in (6, 8) and _lib is not None:
+            detail = " [" + _lib.stark_b200_last_cuda_error().decode() + "]"
+        raise StarkB200Error(status, where + detail)

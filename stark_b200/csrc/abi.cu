@@ -1,5 +1,6 @@
 // extern "C" surface of libstark_b200.so (declared in include/stark_b200.h).
 // No exception crosses the boundary and nothing is printed.
+#include <cstdlib>
 #include <mutex>
 #include <new>
 
@@ -44,6 +45,15 @@ stark_b200_status ensure_buffer(void **buf, size_t *have, size_t want) {
 
 using namespace sb;
 
+// Programmatic dependent launch between consecutive kernels of a stream (on unless STARK_B200_PDL=0).
+static bool pdl_enabled() {
+    static const bool on = [] {
+        const char *e = getenv("STARK_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 extern "C" {
 
 uint32_t stark_b200_abi_version(void) { return STARK_B200_ABI_VERSION; }
@@ -65,6 +75,8 @@ const char *stark_b200_status_name(uint32_t status) {
         default: return "unknown";
     }
 }
+
+const char *stark_b200_last_cuda_error(void) { return cudaGetErrorName(last_cuda_error()); }
 
 stark_b200_status stark_b200_device_count(int32_t *out_count) {
     if (!out_count) return STARK_B200_INVALID_ARGUMENT;
@@ -225,13 +237,62 @@ stark_b200_status stark_b200_op_qmv(const stark_b200_qmatrix *matrix, const void
         a.prologue = kProPlain;
         a.epilogue = kEpiStore;
         a.error_word = ctx->error_word;
-        a.pdl = false;
+        a.pdl = location == STARK_B200_DEVICE && pdl_enabled();
         stark_b200_status st = qmv_launch(a, s);
         if (st != STARK_B200_OK) return st;
     }
     if (location == STARK_B200_HOST) {
         SB_CUDA(cudaMemcpyAsync(y, ctx->stage_out, yout * m, cudaMemcpyDeviceToHost, s));
         SB_CUDA(cudaStreamSynchronize(s));
+    }
+    return STARK_B200_OK;
+}
+
+struct stark_b200_graph {
+    cudaGraph_t graph;
+    cudaGraphExec_t exec;
+};
+
+stark_b200_status stark_b200_graph_begin(void *stream) {
+    if (!device_context()) return STARK_B200_DEVICE_FAILURE;
+    SB_CUDA(cudaStreamBeginCapture((cudaStream_t)stream, cudaStreamCaptureModeThreadLocal));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_graph_end(void *stream, stark_b200_graph **out_graph) {
+    if (!out_graph) return STARK_B200_INVALID_ARGUMENT;
+    *out_graph = nullptr;
+    cudaGraph_t g = nullptr;
+    SB_CUDA(cudaStreamEndCapture((cudaStream_t)stream, &g));
+    cudaGraphExec_t exec = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&exec, g, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(g);
+        return cuda_status(e);
+    }
+    stark_b200_graph *out = new (std::nothrow) stark_b200_graph{g, exec};
+    if (!out) {
+        cudaGraphExecDestroy(exec);
+        cudaGraphDestroy(g);
+        return STARK_B200_OUT_OF_MEMORY;
+    }
+    *out_graph = out;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_graph_launch(stark_b200_graph *graph, void *stream) {
+    if (!graph) return STARK_B200_INVALID_ARGUMENT;
+    SB_CUDA(cudaGraphLaunch(graph->exec, (cudaStream_t)stream));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_graph_destroy(stark_b200_graph **graph) {
+    if (!graph) return STARK_B200_INVALID_ARGUMENT;
+    if (*graph) {
+        cudaGraphExecDestroy((*graph)->exec);
+        cudaGraphDestroy((*graph)->graph);
+        delete *graph;
+        *graph = nullptr;
     }
     return STARK_B200_OK;
 }

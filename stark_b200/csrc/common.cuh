@@ -128,8 +128,15 @@ __device__ inline uint4 ldg_nc_v4(const void *p) {
 }
 
 // ---- host-side status plumbing ---------------------------------------------------------------------
+// Last CUDA error seen by this library on the calling thread (for stark_b200_last_cuda_error).
+inline cudaError_t &last_cuda_error() {
+    static thread_local cudaError_t e = cudaSuccess;
+    return e;
+}
+
 inline stark_b200_status cuda_status(cudaError_t e) {
     if (e == cudaSuccess) return STARK_B200_OK;
+    last_cuda_error() = e;
     if (e == cudaErrorMemoryAllocation) return STARK_B200_OUT_OF_MEMORY;
     return STARK_B200_DEVICE_FAILURE;
 }

@@ -1,0 +1,494 @@
+// Dense Qwen3-shaped decode engine: one recorded launch sequence (CUDA graph with programmatic
+// dependent launch between its kernels) per token, replayed with the position and token read from
+// device memory.  Mirrors the reference's decode pass
+//   crates/stark-engine/src/engine/language_model/stream/stream.rs:787-1217 (one submission per token,
+//   on-device token chaining) and its layer wiring
+//   crates/stark-engine/src/encodable_block/transformer_layer.rs:549-659.
+//
+// Per layer the sequence is five kernels:
+//   qkv    = W_qkv  rmsnorm(h)                      matvec, norm fused in the prologue
+//   attn   = attention(rope(norm(q)), cache + k, v)  one kernel: QK-norm, RoPE, KV append, split-KV, merge
+//   h      = bf16(bf16(W_o attn) + h)                matvec, residual fused in the epilogue
+//   act    = silu(gate) * up,  [up; gate] = W rmsnorm(h)
+//   h      = bf16(bf16(W_down act) + h)
+// then logits = W_head rmsnorm(h) with the greedy read-out fused into the matvec epilogue.
+#include "model.cuh"
+
+#include <cmath>
+#include <cstring>
+#include <new>
+#include <vector>
+
+namespace sb {
+
+namespace {
+
+template <typename T>
+stark_b200_status dmalloc(T **p, size_t count) {
+    *p = nullptr;
+    SB_CUDA(cudaMalloc(p, count * sizeof(T) ? count * sizeof(T) : 1));
+    return STARK_B200_OK;
+}
+
+bool pdl_on() {
+    static const bool on = [] {
+        const char *e = getenv("STARK_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
+}  // namespace
+
+Model::~Model() {
+    if (step_graph) cudaGraphExecDestroy(step_graph);
+    if (ingest_graph) cudaGraphExecDestroy(ingest_graph);
+    for (auto &L : layers) {
+        qmatrix_free(L.qkv);
+        qmatrix_free(L.o);
+        qmatrix_free(L.upgate);
+        qmatrix_free(L.down);
+        cudaFree(L.attn_norm);
+        cudaFree(L.mlp_norm);
+        cudaFree(L.q_norm);
+        cudaFree(L.k_norm);
+        cudaFree(L.kv.keys);
+        cudaFree(L.kv.values);
+    }
+    if (lm_head != embed) qmatrix_free(lm_head);
+    qmatrix_free(embed);
+    cudaFree(final_norm);
+    cudaFree(block_table);
+    cudaFree(rope_cos);
+    cudaFree(rope_sin);
+    cudaFree(state);
+    cudaFree(pending);
+    cudaFree(h);
+    cudaFree(qkv);
+    cudaFree(attn);
+    cudaFree(act);
+    cudaFree(logits);
+    cudaFree(attn_scratch);
+    cudaFree(attn_counters);
+    cudaFree(partial_max);
+    cudaFree(partial_index);
+    if (host_state) cudaFreeHost(host_state);
+    if (host_logits) cudaFreeHost(host_logits);
+    if (stream) cudaStreamDestroy(stream);
+}
+
+stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
+    *out = nullptr;
+    if (c.layers == 0 || c.hidden == 0 || c.hidden % 512u != 0 || c.head_dim != kHeadDim || c.kv_heads == 0 ||
+        c.q_heads % c.kv_heads != 0 || c.q_heads / c.kv_heads > 8u || c.inter == 0 || c.inter % 512u != 0 ||
+        c.vocab == 0 || c.context_tokens == 0 || !(c.eps > 0.0f) || !(c.rope_theta > 0.0f))
+        return STARK_B200_INVALID_ARGUMENT;
+    Model *m = new (std::nothrow) Model();
+    if (!m) return STARK_B200_OUT_OF_MEMORY;
+    m->cfg = c;
+    cudaGetDevice(&m->device);
+    m->layers.resize(c.layers);
+    stark_b200_status st = STARK_B200_OK;
+    auto fail = [&](stark_b200_status s) {
+        delete m;
+        return s;
+    };
+    if (cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess) return fail(STARK_B200_DEVICE_FAILURE);
+
+    // KV pages: identity block table sized for the context (rounded up to whole pages).
+    m->num_blocks = (c.context_tokens + kPageTokens - 1u) / kPageTokens;
+    const size_t page_elems = (size_t)c.kv_heads * kPageTokens * kHeadDim;
+    for (auto &L : m->layers) {
+        if ((st = dmalloc(&L.kv.keys, m->num_blocks * page_elems)) != STARK_B200_OK) return fail(st);
+        if ((st = dmalloc(&L.kv.values, m->num_blocks * page_elems)) != STARK_B200_OK) return fail(st);
+    }
+    std::vector<int32_t> table(m->num_blocks);
+    for (uint32_t i = 0; i < m->num_blocks; ++i) table[i] = (int32_t)i;
+    if ((st = dmalloc(&m->block_table, m->num_blocks)) != STARK_B200_OK) return fail(st);
+    if (cudaMemcpy(m->block_table, table.data(), table.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess)
+        return fail(STARK_B200_DEVICE_FAILURE);
+
+    // RoPE tables on the host with the reference's formulas and operation order
+    // (crates/stark-engine/src/encodable_block/mixer/attention/rope.rs:346-440, UnscaledRoPEConfig).
+    {
+        const uint32_t positions = m->num_blocks * kPageTokens;
+        std::vector<float> cs((size_t)positions * kHeadDim), sn((size_t)positions * kHeadDim);
+        const uint32_t half = kHeadDim / 2u;
+        for (uint32_t pair = 0; pair < half; ++pair) {
+            const float inv = 1.0f / powf(c.rope_theta, (float)(pair * 2u) / (float)kHeadDim);
+            for (uint32_t pos = 0; pos < positions; ++pos) {
+                const float e = (float)pos * inv;
+                const float s = sinf(e) * 1.0f, co = cosf(e) * 1.0f;
+                sn[(size_t)pos * kHeadDim + pair] = s;
+                sn[(size_t)pos * kHeadDim + pair + half] = s;
+                cs[(size_t)pos * kHeadDim + pair] = co;
+                cs[(size_t)pos * kHeadDim + pair + half] = co;
+            }
+        }
+        if ((st = dmalloc(&m->rope_cos, cs.size())) != STARK_B200_OK) return fail(st);
+        if ((st = dmalloc(&m->rope_sin, sn.size())) != STARK_B200_OK) return fail(st);
+        if (cudaMemcpy(m->rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMemcpy(m->rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess)
+            return fail(STARK_B200_DEVICE_FAILURE);
+    }
+
+    const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
+    m->attn_splits = std::min<uint32_t>(kMaxAttnSplits, std::max<uint32_t>(1u, 296u / c.kv_heads));
+    if ((st = dmalloc(&m->state, 1)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->pending, (size_t)c.context_tokens + 1u)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->h, c.hidden)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->qkv, qkv_n)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->attn, c.q_heads * kHeadDim)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->act, c.inter)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->logits, c.vocab)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->attn_scratch, attention_scratch_floats(c.q_heads, c.kv_heads, m->attn_splits))) !=
+        STARK_B200_OK)
+        return fail(st);
+    if ((st = dmalloc(&m->attn_counters, c.kv_heads)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->partial_max, 1024)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->partial_index, 1024)) != STARK_B200_OK) return fail(st);
+    if (cudaMemset(m->attn_counters, 0, c.kv_heads * 4) != cudaSuccess ||
+        cudaMemset(m->state, 0, sizeof(StepState)) != cudaSuccess)
+        return fail(STARK_B200_DEVICE_FAILURE);
+    if (cudaMallocHost(&m->host_state, sizeof(StepState)) != cudaSuccess ||
+        cudaMallocHost(&m->host_logits, (size_t)c.vocab * 2u) != cudaSuccess)
+        return fail(STARK_B200_OUT_OF_MEMORY);
+    *out = m;
+    return STARK_B200_OK;
+}
+
+static stark_b200_status upload_f32(float **dst, const float *src, size_t n) {
+    if (*dst) cudaFree(*dst);
+    stark_b200_status st = dmalloc(dst, n);
+    if (st != STARK_B200_OK) return st;
+    SB_CUDA(cudaMemcpy(*dst, src, n * 4, cudaMemcpyHostToDevice));
+    return STARK_B200_OK;
+}
+
+stark_b200_status model_set_vector(Model *m, uint32_t layer, uint32_t which, const float *data, uint32_t count) {
+    if (m->finalized) return STARK_B200_INVALID_STATE;
+    const auto &c = m->cfg;
+    if (which == STARK_B200_VEC_FINAL_NORM) return count == c.hidden ? upload_f32(&m->final_norm, data, count) : STARK_B200_INVALID_ARGUMENT;
+    if (layer >= c.layers) return STARK_B200_INVALID_ARGUMENT;
+    auto &L = m->layers[layer];
+    switch (which) {
+        case STARK_B200_VEC_ATTN_NORM: return count == c.hidden ? upload_f32(&L.attn_norm, data, count) : STARK_B200_INVALID_ARGUMENT;
+        case STARK_B200_VEC_MLP_NORM: return count == c.hidden ? upload_f32(&L.mlp_norm, data, count) : STARK_B200_INVALID_ARGUMENT;
+        case STARK_B200_VEC_Q_NORM: return count == kHeadDim ? upload_f32(&L.q_norm, data, count) : STARK_B200_INVALID_ARGUMENT;
+        case STARK_B200_VEC_K_NORM: return count == kHeadDim ? upload_f32(&L.k_norm, data, count) : STARK_B200_INVALID_ARGUMENT;
+        default: return STARK_B200_INVALID_ARGUMENT;
+    }
+}
+
+stark_b200_status model_set_matrix(Model *m, uint32_t layer, uint32_t which, QMatrix *q) {
+    if (m->finalized) return STARK_B200_INVALID_STATE;
+    const auto &c = m->cfg;
+    const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
+    auto put = [&](QMatrix **slot, uint32_t rows, uint32_t cols, bool pair) -> stark_b200_status {
+        if (q->rows != rows || q->columns != cols || (q->pair_halves != 0) != pair) return STARK_B200_INVALID_ARGUMENT;
+        if (*slot && *slot != q) qmatrix_free(*slot);
+        *slot = q;
+        return STARK_B200_OK;
+    };
+    if (which == STARK_B200_MAT_EMBED) {
+        stark_b200_status st = put(&m->embed, c.vocab, c.hidden, false);
+        if (st == STARK_B200_OK && c.tied) m->lm_head = m->embed;
+        return st;
+    }
+    if (which == STARK_B200_MAT_LM_HEAD) {
+        if (c.tied) return STARK_B200_INVALID_ARGUMENT;
+        return put(&m->lm_head, c.vocab, c.hidden, false);
+    }
+    if (layer >= c.layers) return STARK_B200_INVALID_ARGUMENT;
+    auto &L = m->layers[layer];
+    switch (which) {
+        case STARK_B200_MAT_QKV: return put(&L.qkv, qkv_n, c.hidden, false);
+        case STARK_B200_MAT_O: return put(&L.o, c.hidden, c.q_heads * kHeadDim, false);
+        case STARK_B200_MAT_UPGATE: return put(&L.upgate, 2u * c.inter, c.hidden, true);
+        case STARK_B200_MAT_DOWN: return put(&L.down, c.hidden, c.inter, false);
+        default: return STARK_B200_INVALID_ARGUMENT;
+    }
+}
+
+// Issues the kernels of one token on m->stream.  full == false stops after the last layer
+// (cache-only ingest of a prompt row) and takes the next token from the pending list.
+static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
+    const auto &c = m->cfg;
+    DeviceContext *ctx = device_context();
+    if (!ctx) return STARK_B200_DEVICE_FAILURE;
+    const bool pdl = pdl_on();
+    cudaStream_t s = m->stream;
+    stark_b200_status st;
+    uint32_t n = 0;
+    if ((st = embedding_row_launch(m->embed, m->state, m->h, pdl, s)) != STARK_B200_OK) return st;
+    ++n;
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        auto &L = m->layers[l];
+        QmvArgs a{};
+        a.m = 1;
+        a.io_type = STARK_B200_BF16;
+        a.error_word = ctx->error_word;
+        a.pdl = pdl;
+        a.eps = c.eps;
+        // qkv = W_qkv rmsnorm(h)
+        a.matrix = L.qkv;
+        a.x = m->h;
+        a.y = m->qkv;
+        a.prologue = kProRmsNorm;
+        a.norm_weight = L.attn_norm;
+        a.epilogue = kEpiStore;
+        if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
+        // attention with fused QK-norm, RoPE and KV append
+        AttnArgs at{};
+        at.qkv = m->qkv;
+        at.out = m->attn;
+        at.kv = L.kv;
+        at.block_table = m->block_table;
+        at.q_norm = L.q_norm;
+        at.k_norm = L.k_norm;
+        at.rope_cos = m->rope_cos;
+        at.rope_sin = m->rope_sin;
+        at.state = m->state;
+        at.eps = c.eps;
+        at.scale = 1.0f / sqrtf((float)kHeadDim);
+        at.q_heads = c.q_heads;
+        at.kv_heads = c.kv_heads;
+        at.splits = m->attn_splits;
+        at.scratch = m->attn_scratch;
+        at.counters = m->attn_counters;
+        at.error_word = ctx->error_word;
+        at.pdl = pdl;
+        if ((st = attention_decode_launch(at, s)) != STARK_B200_OK) return st;
+        // h = bf16(bf16(W_o attn) + h)
+        a.matrix = L.o;
+        a.x = m->attn;
+        a.y = m->h;
+        a.resid = m->h;
+        a.prologue = kProPlain;
+        a.epilogue = kEpiResidual;
+        if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
+        // act = silu(gate) * up
+        a.matrix = L.upgate;
+        a.x = m->h;
+        a.y = m->act;
+        a.prologue = kProRmsNorm;
+        a.norm_weight = L.mlp_norm;
+        a.epilogue = kEpiSwiGlu;
+        if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
+        // h = bf16(bf16(W_down act) + h)
+        a.matrix = L.down;
+        a.x = m->act;
+        a.y = m->h;
+        a.resid = m->h;
+        a.prologue = kProPlain;
+        a.epilogue = kEpiResidual;
+        if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
+        n += 5;
+    }
+    if (full) {
+        QmvArgs a{};
+        a.m = 1;
+        a.io_type = STARK_B200_BF16;
+        a.error_word = ctx->error_word;
+        a.pdl = pdl;
+        a.eps = c.eps;
+        a.matrix = m->lm_head;
+        a.x = m->h;
+        a.y = m->logits;
+        a.prologue = kProRmsNorm;
+        a.norm_weight = m->final_norm;
+        a.epilogue = kEpiLogits;
+        a.partial_max = m->partial_max;
+        a.partial_index = m->partial_index;
+        uint32_t grid = 0;
+        a.out_grid = &grid;
+        if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
+        if ((st = argmax_finalize_launch(m->partial_max, m->partial_index, grid, m->state, true, pdl, s)) != STARK_B200_OK)
+            return st;
+        n += 2;
+    } else {
+        if ((st = ingest_advance_launch(m->state, m->pending, pdl, s)) != STARK_B200_OK) return st;
+        n += 1;
+    }
+    if (launches) *launches = n;
+    return STARK_B200_OK;
+}
+
+static stark_b200_status capture(Model *m, bool full, cudaGraphExec_t *exec, uint32_t *launches) {
+    SB_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+    stark_b200_status st = issue_token(m, full, launches);
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+    if (st != STARK_B200_OK) {
+        if (g) cudaGraphDestroy(g);
+        return st;
+    }
+    if (e != cudaSuccess) return cuda_status(e);
+    e = cudaGraphInstantiate(exec, g, 0);
+    cudaGraphDestroy(g);
+    return cuda_status(e);
+}
+
+stark_b200_status model_finalize(Model *m) {
+    if (m->finalized) return STARK_B200_INVALID_STATE;
+    if (!m->embed || !m->lm_head || !m->final_norm) return STARK_B200_INVALID_STATE;
+    for (auto &L : m->layers)
+        if (!L.qkv || !L.o || !L.upgate || !L.down || !L.attn_norm || !L.mlp_norm || !L.q_norm || !L.k_norm)
+            return STARK_B200_INVALID_STATE;
+    // One eager pass first (function attributes and lazily created library state must exist before
+    // a recording), on a scratch position; then record both sequences.
+    stark_b200_status st = model_reset(m);
+    if (st != STARK_B200_OK) return st;
+    if ((st = issue_token(m, true, nullptr)) != STARK_B200_OK) return st;
+    if ((st = issue_token(m, false, nullptr)) != STARK_B200_OK) return st;
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    if ((st = capture(m, true, &m->step_graph, &m->step_launches)) != STARK_B200_OK) return st;
+    if ((st = capture(m, false, &m->ingest_graph, &m->ingest_launches)) != STARK_B200_OK) return st;
+    m->finalized = true;
+    return model_reset(m);
+}
+
+stark_b200_status model_reset(Model *m) {
+    SB_CUDA(cudaMemsetAsync(m->state, 0, sizeof(StepState), m->stream));
+    SB_CUDA(cudaMemsetAsync(m->attn_counters, 0, m->cfg.kv_heads * 4, m->stream));
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    m->position = 0;
+    m->has_logits = false;
+    return STARK_B200_OK;
+}
+
+stark_b200_status model_rewind(Model *m, uint64_t position) {
+    if (position > m->position) return STARK_B200_INVALID_ARGUMENT;
+    const uint32_t pos = (uint32_t)position;
+    SB_CUDA(cudaMemcpyAsync(&m->state->position, &pos, 4, cudaMemcpyHostToDevice, m->stream));
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    m->position = position;
+    m->has_logits = false;
+    return STARK_B200_OK;
+}
+
+// Feeds `count` tokens; the last one runs the full sequence so that logits and the greedy token
+// are available afterwards (hybrid::Model: ingest all but the last, then step the last;
+// crates/stark-score/src/scoring.rs:453-489).
+stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count) {
+    if (!m->finalized || m->fenced) return STARK_B200_INVALID_STATE;
+    if (count == 0) return STARK_B200_INVALID_ARGUMENT;
+    if (m->position + count > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
+    for (size_t i = 0; i < count; ++i)
+        if (ids[i] >= m->cfg.vocab) return STARK_B200_INVALID_ARGUMENT;
+    // pending[0 .. count-2] = ids[1 ..]; the ingest-advance kernel pops one per row
+    if (count > 1) SB_CUDA(cudaMemcpyAsync(m->pending, ids + 1, (count - 1) * 4, cudaMemcpyHostToDevice, m->stream));
+    StepState hs{};
+    hs.position = (uint32_t)m->position;
+    hs.token = ids[0];
+    hs.next_token = 0;
+    hs.cursor = 0;
+    SB_CUDA(cudaMemcpyAsync(m->state, &hs, sizeof(hs), cudaMemcpyHostToDevice, m->stream));
+    for (size_t i = 0; i + 1 < count; ++i) {
+        if (m->cancel_requested) {
+            m->cancel_requested = false;
+            cudaStreamSynchronize(m->stream);
+            m->fenced = false;
+            model_reset(m);
+            return STARK_B200_CANCELLED;
+        }
+        SB_CUDA(cudaGraphLaunch(m->ingest_graph, m->stream));
+    }
+    SB_CUDA(cudaGraphLaunch(m->step_graph, m->stream));
+    m->position += count;
+    m->has_logits = true;
+    m->launches_issued += (count - 1) * m->ingest_launches + m->step_launches;
+    return STARK_B200_OK;
+}
+
+stark_b200_status model_step(Model *m, uint32_t token, bool chained) {
+    if (!m->finalized || m->fenced) return STARK_B200_INVALID_STATE;
+    if (m->position + 1 > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
+    if (!chained) {
+        if (token >= m->cfg.vocab) return STARK_B200_INVALID_ARGUMENT;
+        SB_CUDA(cudaMemcpyAsync(&m->state->token, &token, 4, cudaMemcpyHostToDevice, m->stream));
+    }
+    SB_CUDA(cudaGraphLaunch(m->step_graph, m->stream));
+    m->position += 1;
+    m->has_logits = true;
+    m->launches_issued += m->step_launches;
+    return STARK_B200_OK;
+}
+
+static stark_b200_status check_device_error(Model *m) {
+    DeviceContext *ctx = device_context();
+    if (!ctx) return STARK_B200_DEVICE_FAILURE;
+    uint32_t word = 0;
+    SB_CUDA(cudaMemcpyAsync(&word, ctx->error_word, 4, cudaMemcpyDeviceToHost, m->stream));
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    if (word) {
+        m->fenced = true;
+        return STARK_B200_DEVICE_FAILURE;
+    }
+    return STARK_B200_OK;
+}
+
+stark_b200_status model_drain(Model *m) {
+    cudaError_t e = cudaStreamSynchronize(m->stream);
+    if (e != cudaSuccess) {
+        m->fenced = true;
+        return cuda_status(e);
+    }
+    return check_device_error(m);
+}
+
+stark_b200_status model_next_token(Model *m, uint32_t *out) {
+    if (!m->has_logits) return STARK_B200_INVALID_STATE;
+    SB_CUDA(cudaMemcpyAsync(m->host_state, m->state, sizeof(StepState), cudaMemcpyDeviceToHost, m->stream));
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    *out = m->host_state->next_token;
+    return STARK_B200_OK;
+}
+
+stark_b200_status model_readout_bf16(Model *m, uint16_t *dst, size_t count) {
+    if (!m->has_logits) return STARK_B200_INVALID_STATE;
+    if (count != m->cfg.vocab) return STARK_B200_INVALID_ARGUMENT;
+    SB_CUDA(cudaMemcpyAsync(m->host_logits, m->logits, count * 2, cudaMemcpyDeviceToHost, m->stream));
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    memcpy(dst, m->host_logits, count * 2);
+    return STARK_B200_OK;
+}
+
+stark_b200_status model_readout_f32(Model *m, float *dst, size_t count) {
+    if (!m->has_logits) return STARK_B200_INVALID_STATE;
+    if (count != m->cfg.vocab) return STARK_B200_INVALID_ARGUMENT;
+    SB_CUDA(cudaMemcpyAsync(m->host_logits, m->logits, count * 2, cudaMemcpyDeviceToHost, m->stream));
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    for (size_t i = 0; i < count; ++i) dst[i] = bf16_bits_to_f32(m->host_logits[i]);
+    return STARK_B200_OK;
+}
+
+// Greedy decode of `steps` tokens chained on the device: the step sequence writes its own next
+// input.  Token ids come back through one small device-to-host copy per step, all asynchronous;
+// the host synchronises once at the end.
+stark_b200_status model_generate_greedy(Model *m, uint32_t steps, uint32_t *out_tokens) {
+    if (!m->finalized || m->fenced || !m->has_logits) return STARK_B200_INVALID_STATE;
+    if (m->position + steps > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
+    uint32_t *pinned = nullptr;
+    SB_CUDA(cudaMallocHost(&pinned, (size_t)(steps + 1u) * 4u));
+    cudaError_t e = cudaSuccess;
+    // out[0] is the token sampled from the logits already present (the prompt's last row).
+    e = cudaMemcpyAsync(&pinned[0], &m->state->next_token, 4, cudaMemcpyDeviceToHost, m->stream);
+    for (uint32_t i = 0; i < steps && e == cudaSuccess; ++i) {
+        e = cudaGraphLaunch(m->step_graph, m->stream);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(&pinned[i + 1], &m->state->next_token, 4, cudaMemcpyDeviceToHost, m->stream);
+    }
+    if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
+    if (e == cudaSuccess) memcpy(out_tokens, pinned, (size_t)(steps + 1u) * 4u);
+    cudaFreeHost(pinned);
+    if (e != cudaSuccess) {
+        m->fenced = true;
+        return cuda_status(e);
+    }
+    m->position += steps;
+    m->launches_issued += (uint64_t)steps * m->step_launches;
+    return check_device_error(m);
+}
+
+}  // namespace sb

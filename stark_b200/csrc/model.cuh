@@ -1,0 +1,60 @@
+// Dense decode engine state (see model.cu).
+#pragma once
+#include <vector>
+
+#include "context.cuh"
+#include "ops.cuh"
+#include "qmv.cuh"
+
+namespace sb {
+
+struct ModelLayer {
+    QMatrix *qkv = nullptr, *o = nullptr, *upgate = nullptr, *down = nullptr;
+    float *attn_norm = nullptr, *mlp_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    KvLayer kv{nullptr, nullptr};
+};
+
+struct Model {
+    stark_b200_dense_config cfg{};
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    QMatrix *embed = nullptr, *lm_head = nullptr;
+    std::vector<ModelLayer> layers;
+    float *final_norm = nullptr;
+    uint32_t num_blocks = 0;
+    int32_t *block_table = nullptr;
+    float *rope_cos = nullptr, *rope_sin = nullptr;
+    StepState *state = nullptr;
+    uint32_t *pending = nullptr;  // prompt tokens still to be ingested (device)
+    uint16_t *h = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr, *logits = nullptr;
+    float *attn_scratch = nullptr;
+    uint32_t *attn_counters = nullptr;
+    float *partial_max = nullptr;
+    uint32_t *partial_index = nullptr;
+    uint32_t attn_splits = 1;
+    cudaGraphExec_t step_graph = nullptr, ingest_graph = nullptr;
+    uint32_t step_launches = 0, ingest_launches = 0;
+    StepState *host_state = nullptr;    // pinned
+    uint16_t *host_logits = nullptr;    // pinned
+    uint64_t position = 0;              // host mirror of state->position
+    uint64_t launches_issued = 0;       // kernels of this library launched so far
+    bool finalized = false, fenced = false, has_logits = false;
+    volatile bool cancel_requested = false;
+    ~Model();
+};
+
+stark_b200_status model_create(const stark_b200_dense_config &cfg, Model **out);
+stark_b200_status model_set_matrix(Model *m, uint32_t layer, uint32_t which, QMatrix *q);  // takes ownership
+stark_b200_status model_set_vector(Model *m, uint32_t layer, uint32_t which, const float *data, uint32_t count);
+stark_b200_status model_finalize(Model *m);
+stark_b200_status model_reset(Model *m);
+stark_b200_status model_rewind(Model *m, uint64_t position);
+stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count);
+stark_b200_status model_step(Model *m, uint32_t token, bool chained);
+stark_b200_status model_drain(Model *m);
+stark_b200_status model_next_token(Model *m, uint32_t *out);
+stark_b200_status model_readout_bf16(Model *m, uint16_t *dst, size_t count);
+stark_b200_status model_readout_f32(Model *m, float *dst, size_t count);
+stark_b200_status model_generate_greedy(Model *m, uint32_t steps, uint32_t *out_tokens);
+
+}  // namespace sb

@@ -21,6 +21,7 @@
 #include "qmv.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 #include <new>
 
 namespace sb {
@@ -29,7 +30,10 @@ namespace {
 
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kProducerWarp = kConsumerWarps;
+constexpr int kEpilogueWarp = kConsumerWarps + 1;
+constexpr int kThreads = (kConsumerWarps + 2) * 32;
+constexpr int kRedSlots = 4;  // depth of the partial-sum hand-off ring between consumers and the epilogue warp
 
 struct QmvParams {
     const uint8_t *w;
@@ -55,31 +59,45 @@ struct QmvParams {
     uint32_t *error_word;
 };
 
-// Exact 4-bit -> f16 integer conversion of one record word into an m16n8k16 A fragment.
-//   (w & 0x000f000f) | 0x64006400 is the f16 pair (1024 + q, 1024 + q'); subtracting 1024 is exact.
-//   (w & 0x00f000f0) | 0x64006400 is (1024 + 16 q, ...); x * 1/16 - 64 is exact in one FMA.
+// 4-bit -> f16 conversion of one record word into an m16n8k16 A fragment.
+//   (w & 0x000f000f) | 0x64006400 is the f16 pair (1024 + q, 1024 + q');
+//   (w & 0x00f000f0) | 0x64006400 is (1024 + 16 q, ...).
+// FOLD == false: the offsets are removed here, exactly (x - 1024; x/16 - 64 in one FMA), so the
+//   tensor core sees the integers q.
+// FOLD == true: the patterns go to the tensor core as they are and the offsets are removed from
+//   the f32 group sums afterwards (row g: c - 1024 sum(x); row g+8: c/16 - 64 sum(x)).  That halves
+//   the instruction count of the extraction; the accumulation then carries 1024 x + q x, which
+//   costs about 7 bits of the f32 accumulator.
+template <bool FOLD>
 __device__ inline void dequant_a4_word(uint32_t w, uint32_t (&a)[4]) {
     const uint32_t magic = 0x64006400u;
-    const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-    const __half2 k16th = __half2half2(__ushort_as_half(0x2c00));   // 1/16
-    const __half2 kneg64 = __half2half2(__ushort_as_half(0xd400));  // -64
-    uint32_t lo0 = lop3_and_or(w, 0x000f000fu, magic);
-    uint32_t hi0 = lop3_and_or(w, 0x00f000f0u, magic);
-    uint32_t w8 = w >> 8;
-    uint32_t lo1 = lop3_and_or(w8, 0x000f000fu, magic);
-    uint32_t hi1 = lop3_and_or(w8, 0x00f000f0u, magic);
-    __half2 r0 = __hsub2(*reinterpret_cast<__half2 *>(&lo0), k1024);
-    __half2 r1 = __hfma2(*reinterpret_cast<__half2 *>(&hi0), k16th, kneg64);
-    __half2 r2 = __hsub2(*reinterpret_cast<__half2 *>(&lo1), k1024);
-    __half2 r3 = __hfma2(*reinterpret_cast<__half2 *>(&hi1), k16th, kneg64);
-    a[0] = *reinterpret_cast<uint32_t *>(&r0);
-    a[1] = *reinterpret_cast<uint32_t *>(&r1);
-    a[2] = *reinterpret_cast<uint32_t *>(&r2);
-    a[3] = *reinterpret_cast<uint32_t *>(&r3);
+    const uint32_t lo0 = lop3_and_or(w, 0x000f000fu, magic);
+    const uint32_t hi0 = lop3_and_or(w, 0x00f000f0u, magic);
+    const uint32_t w8 = w >> 8;
+    const uint32_t lo1 = lop3_and_or(w8, 0x000f000fu, magic);
+    const uint32_t hi1 = lop3_and_or(w8, 0x00f000f0u, magic);
+    if (FOLD) {
+        a[0] = lo0;
+        a[1] = hi0;
+        a[2] = lo1;
+        a[3] = hi1;
+    } else {
+        const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+        const __half2 k16th = __half2half2(__ushort_as_half(0x2c00));   // 1/16
+        const __half2 kneg64 = __half2half2(__ushort_as_half(0xd400));  // -64
+        __half2 r0 = __hsub2(*reinterpret_cast<const __half2 *>(&lo0), k1024);
+        __half2 r1 = __hfma2(*reinterpret_cast<const __half2 *>(&hi0), k16th, kneg64);
+        __half2 r2 = __hsub2(*reinterpret_cast<const __half2 *>(&lo1), k1024);
+        __half2 r3 = __hfma2(*reinterpret_cast<const __half2 *>(&hi1), k16th, kneg64);
+        a[0] = *reinterpret_cast<uint32_t *>(&r0);
+        a[1] = *reinterpret_cast<uint32_t *>(&r1);
+        a[2] = *reinterpret_cast<uint32_t *>(&r2);
+        a[3] = *reinterpret_cast<uint32_t *>(&r3);
+    }
 }
 
 struct SmemLayout {
-    uint32_t ring, xs, xlo, xsum, red, wred, bars, flags, total;
+    uint32_t ring, xs, xlo, xsum, xoff, red, wred, bars, flags, total;
 };
 
 __host__ __device__ inline SmemLayout smem_layout(uint32_t num_stages, uint32_t stage_capacity, uint32_t columns,
@@ -94,23 +112,33 @@ __host__ __device__ inline SmemLayout smem_layout(uint32_t num_stages, uint32_t 
     off += split ? columns * 2u : 0u;
     L.xsum = off;
     off += (columns / 64u) * 4u;
+    L.xoff = off;
+    off += (columns / 64u) * 4u;
     off = (off + 15u) & ~15u;
     L.red = off;
-    off += 2u * kConsumerWarps * 16u * 4u;
+    off += kRedSlots * kConsumerWarps * 16u * 4u;
     L.wred = off;
-    off += 16u * 4u;
+    off += 2u * kConsumerWarps * 4u;
     L.bars = off;
-    off += 2u * 8u * 8u;  // up to 8 stages: full[8], empty[8]
+    off += (8u + 8u + 2u * kRedSlots) * 8u;  // full[8], empty[8], red_full[4], red_empty[4]
     L.flags = off;
     off += 16u;
     L.total = off;
     return L;
 }
 
+// One thread reports a failed bounded wait; every later wait in the CTA then returns at once.
+__device__ inline void wait_failed(volatile uint32_t *abort_flag, uint32_t *error_word) {
+    *abort_flag = 1;
+    atomicOr(error_word, kErrMbarTimeout);
+}
+
 // SPLIT: the input is f32 and is carried as two f16 terms (hi + lo) so that ~22 mantissa bits
-// survive; bf16 inputs need one term.
-template <bool SPLIT>
-__global__ void __launch_bounds__(kThreads, 1) qmv_a4_kernel(const QmvParams p) {
+//        survive; bf16 inputs need one term.
+// RPW:   records per consumer warp per ring stage (stage = 8 * RPW records unless PRED).
+// PRED:  the stage holds fewer than 8 * RPW records (group counts that are not a multiple of 8).
+template <bool SPLIT, int RPW, bool PRED, bool FOLD>
+__global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t columns = p.groups * 64u;
     const SmemLayout L = smem_layout(p.num_stages, p.stage_capacity, columns, SPLIT);
@@ -118,10 +146,13 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_a4_kernel(const QmvParams p) 
     __half *xs = reinterpret_cast<__half *>(smem + L.xs);
     __half *xlo = reinterpret_cast<__half *>(smem + L.xlo);
     float *xsum = reinterpret_cast<float *>(smem + L.xsum);
+    float *xoff = reinterpret_cast<float *>(smem + L.xoff);
     float *red = reinterpret_cast<float *>(smem + L.red);
     float *wred = reinterpret_cast<float *>(smem + L.wred);
     uint64_t *full = reinterpret_cast<uint64_t *>(smem + L.bars);
     uint64_t *empty = full + 8;
+    uint64_t *red_full = empty + 8;
+    uint64_t *red_empty = red_full + kRedSlots;
     volatile uint32_t *abort_flag = reinterpret_cast<volatile uint32_t *>(smem + L.flags);
 
     const uint32_t tid = threadIdx.x;
@@ -132,13 +163,15 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_a4_kernel(const QmvParams p) 
     const uint32_t u0 = (uint32_t)(((uint64_t)blockIdx.x * units) / gridDim.x);
     const uint32_t u1 = (uint32_t)(((uint64_t)(blockIdx.x + 1) * units) / gridDim.x);
     const uint32_t t0 = u0 * p.unit_tiles, t1 = u1 * p.unit_tiles;
-    const uint32_t total_stages = (t1 - t0) * p.stages_per_tile;
-    const uint32_t stage_bytes = p.stage_records * kA4RecordBytes;
 
     if (tid == 0) {
         for (uint32_t s = 0; s < p.num_stages; ++s) {
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], kConsumerWarps);
+        }
+        for (uint32_t s = 0; s < kRedSlots; ++s) {
+            mbar_init(&red_full[s], kConsumerWarps);
+            mbar_init(&red_empty[s], 1);
         }
         *abort_flag = 0;
         mbar_fence_init();
@@ -146,39 +179,125 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_a4_kernel(const QmvParams p) 
     __syncthreads();
     pdl_launch_dependents();
 
-    if (warp == kConsumerWarps) {
+    if (warp == kProducerWarp) {
         // ---------------- producer: stream this CTA's byte range through the ring ----------------
+        // Weights do not depend on the previous kernel, so this starts before griddepcontrol.wait.
         if (lane == 0) {
+            const uint32_t total_stages = (t1 - t0) * p.stages_per_tile;
+            const uint32_t stage_bytes = p.stage_records * kA4RecordBytes;
             const uint8_t *src = p.w + (size_t)t0 * p.groups * kA4RecordBytes;
+            uint32_t slot = 0, phase = 1;  // a fresh barrier passes a wait on parity 1
             for (uint32_t s = 0; s < total_stages; ++s) {
-                const uint32_t slot = s % p.num_stages, use = s / p.num_stages;
-                if (use > 0 && !mbar_wait_bounded(&empty[slot], (use - 1u) & 1u, abort_flag)) {
-                    *abort_flag = 1;
-                    atomicOr(p.error_word, kErrMbarTimeout);
+                if (!mbar_wait_bounded(&empty[slot], phase, abort_flag)) {
+                    wait_failed(abort_flag, p.error_word);
                     break;
                 }
                 mbar_arrive_expect_tx(&full[slot], stage_bytes);
-                bulk_g2s(ring + (size_t)slot * p.stage_capacity, src + (size_t)s * stage_bytes, stage_bytes,
-                         &full[slot]);
+                bulk_g2s(ring + (size_t)slot * p.stage_capacity, src, stage_bytes, &full[slot]);
+                src += stage_bytes;
+                if (++slot == p.num_stages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        return;
+    }
+
+    pdl_wait();  // the input vector (and anything the epilogue overwrites) belongs to the previous kernel
+
+    if (warp == kEpilogueWarp) {
+        // ---------------- epilogue warp: cross-warp reduction and output of finished row tiles ----------
+        uint32_t rb = 0, rphase = 0;
+        float held = 0.0f;  // kEpiSwiGlu: the `up` value of the even tile
+        float best = -INFINITY;
+        uint32_t best_index = 0xffffffffu;
+        for (uint32_t tile = t0; tile < t1; ++tile) {
+            if (!mbar_wait_bounded(&red_full[rb], rphase, abort_flag)) wait_failed(abort_flag, p.error_word);
+            float v = 0.0f;
+            if (lane < 16) {
+#pragma unroll
+                for (int wv = 0; wv < kConsumerWarps; ++wv) v += red[(rb * kConsumerWarps + wv) * 16u + lane];
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&red_empty[rb]);
+            if (++rb == kRedSlots) {
+                rb = 0;
+                rphase ^= 1u;
+            }
+            if (lane < 16) {
+                const uint32_t row = tile_row0(tile, p.pair_halves, p.rows) + lane;
+                const bool valid = row < p.rows;
+                if (p.epilogue == kEpiStore) {
+                    if (valid) {
+                        if (p.io_type == STARK_B200_F32)
+                            reinterpret_cast<float *>(p.y)[row] = v;
+                        else
+                            reinterpret_cast<uint16_t *>(p.y)[row] = f32_to_bf16_bits(v);
+                    }
+                } else if (p.epilogue == kEpiResidual) {
+                    if (valid) {
+                        const float r = bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(p.resid)[row]);
+                        reinterpret_cast<uint16_t *>(p.y)[row] = f32_to_bf16_bits(bf16_round(v) + r);
+                    }
+                } else if (p.epilogue == kEpiSwiGlu) {
+                    if ((tile & 1u) == 0) {
+                        held = bf16_round(v);
+                    } else {
+                        // gated_act_mul.rs:80-95: silu in f32 -> bf16, product of two bf16 -> bf16
+                        const float gate = bf16_round(v);
+                        const float activated = bf16_round(gate / (1.0f + expf(-1.0f * gate)));
+                        const uint32_t orow = (tile >> 1) * 16u + lane;
+                        if (orow < p.rows / 2u)
+                            reinterpret_cast<uint16_t *>(p.y)[orow] = f32_to_bf16_bits(held * activated);
+                    }
+                } else {  // kEpiLogits
+                    if (valid) {
+                        const uint16_t hb = f32_to_bf16_bits(v);
+                        reinterpret_cast<uint16_t *>(p.y)[row] = hb;
+                        const float lv = bf16_bits_to_f32(hb);
+                        // a non-finite logit must surface: it sorts as the maximum so the host sees it
+                        const float key = isfinite(lv) ? lv : INFINITY;
+                        if (key > best || (key == best && row < best_index)) {
+                            best = key;
+                            best_index = row;
+                        }
+                    }
+                }
+            }
+        }
+        if (p.epilogue == kEpiLogits) {
+            // first index of the maximum over this CTA's rows (lanes >= 16 hold -inf)
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const uint32_t oi = __shfl_xor_sync(0xffffffffu, best_index, o);
+                if (ov > best || (ov == best && oi < best_index)) {
+                    best = ov;
+                    best_index = oi;
+                }
+            }
+            if (lane == 0) {
+                p.partial_max[blockIdx.x] = best;
+                p.partial_index[blockIdx.x] = best_index;
             }
         }
         return;
     }
 
     // ---------------- consumers ----------------
-    pdl_wait();  // the input vector (and anything the epilogue overwrites) belongs to the previous kernel
-
     // Prologue: build the f16 input vector, its power-of-two scale and the per-group sums.
     const uint32_t chunks = columns / 8u;
+    const bool f32_in = p.io_type == STARK_B200_F32 && p.prologue == kProPlain;
     float sumsq = 0.0f;
     if (p.prologue == kProRmsNorm) {
         const uint4 *h4 = reinterpret_cast<const uint4 *>(p.x);
         for (uint32_t c = tid; c < chunks; c += kConsumerThreads) {
-            uint4 v = h4[c];
+            const uint4 v = h4[c];
             const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                float a = __uint_as_float(wv[i] << 16), b = __uint_as_float(wv[i] & 0xffff0000u);
+                const float a = __uint_as_float(wv[i] << 16), b = __uint_as_float(wv[i] & 0xffff0000u);
                 sumsq += a * a;
                 sumsq += b * b;
             }
@@ -189,32 +308,30 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_a4_kernel(const QmvParams p) 
         sumsq = 0.0f;
 #pragma unroll
         for (int i = 0; i < kConsumerWarps; ++i) sumsq += wred[i];
-        named_bar_sync(1, kConsumerThreads);
     }
     const float rms_inv = 1.0f / sqrtf(sumsq / (float)columns + p.eps);
 
-    // Pass 1: materialise x (f32 values kept in shared memory as raw f32 would not fit for large K,
-    // so bf16 inputs are parked as bf16 bits in `xs`, f32 inputs as bf16 hi in xs and are re-read).
+    // Pass 1: the input row as bf16 bits parked in `xs` (f32 inputs are re-read in pass 2), and its maximum.
     float vmax = 0.0f;
     for (uint32_t c = tid; c < chunks; c += kConsumerThreads) {
-        if (p.io_type == STARK_B200_F32 && p.prologue == kProPlain) {
+        if (f32_in) {
             const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
-            float4 a = x4[2 * c], b = x4[2 * c + 1];
+            const float4 a = x4[2 * c], b = x4[2 * c + 1];
             vmax = fmaxf(vmax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
             vmax = fmaxf(vmax, fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
         } else {
-            uint4 v = reinterpret_cast<const uint4 *>(p.x)[c];
+            const uint4 v = reinterpret_cast<const uint4 *>(p.x)[c];
             uint32_t wv[4] = {v.x, v.y, v.z, v.w};
             if (p.prologue == kProRmsNorm) {
                 const float4 *nw = reinterpret_cast<const float4 *>(p.norm_weight);
-                float4 n0 = nw[2 * c], n1 = nw[2 * c + 1];
+                const float4 n0 = nw[2 * c], n1 = nw[2 * c + 1];
                 const float ns[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    float a = __uint_as_float(wv[i] << 16), b = __uint_as_float(wv[i] & 0xffff0000u);
+                    const float a = __uint_as_float(wv[i] << 16), b = __uint_as_float(wv[i] & 0xffff0000u);
                     // normalization.rs:157-161: bf16(normalized) * bf16(scale), product rounded to bf16
-                    uint16_t ra = f32_to_bf16_bits(bf16_round(a * rms_inv) * bf16_round(ns[2 * i]));
-                    uint16_t rb = f32_to_bf16_bits(bf16_round(b * rms_inv) * bf16_round(ns[2 * i + 1]));
+                    const uint16_t ra = f32_to_bf16_bits(bf16_round(a * rms_inv) * bf16_round(ns[2 * i]));
+                    const uint16_t rb = f32_to_bf16_bits(bf16_round(b * rms_inv) * bf16_round(ns[2 * i + 1]));
                     wv[i] = (uint32_t)ra | ((uint32_t)rb << 16);
                 }
             }
@@ -227,32 +344,32 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_a4_kernel(const QmvParams p) 
         }
     }
     vmax = warp_max(vmax);
-    if (lane == 0) wred[8 + warp] = vmax;
+    if (lane == 0) wred[kConsumerWarps + warp] = vmax;
     named_bar_sync(1, kConsumerThreads);
     vmax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < kConsumerWarps; ++i) vmax = fmaxf(vmax, wred[8 + i]);
+    for (int i = 0; i < kConsumerWarps; ++i) vmax = fmaxf(vmax, wred[kConsumerWarps + i]);
     // Exact power-of-two scale: the largest element lands in [2^14, 2^15).
-    int expo = (int)((__float_as_uint(vmax) >> 23) & 0xffu) - 127;
-    int shift = 14 - expo;
+    int shift = 14 - ((int)((__float_as_uint(vmax) >> 23) & 0xffu) - 127);
     shift = max(-100, min(100, shift));
     if (!(vmax > 0.0f) || !isfinite(vmax)) shift = 0;
     const float xscale = __uint_as_float((uint32_t)(shift + 127) << 23);
     const float xunscale = __uint_as_float((uint32_t)(127 - shift) << 23);
 
-    // Pass 2: scaled f16 values in place, plus per-group sums of the unscaled input.
+    // Pass 2: scaled f16 values in place, per-group sums of the input (for the bias term) and, for
+    // FOLD, -64 * the per-group sum of the f16 values the tensor core will see.
     const uint32_t rounds = (chunks + kConsumerThreads - 1u) / kConsumerThreads;
     for (uint32_t r = 0; r < rounds; ++r) {
         const uint32_t c = tid + r * kConsumerThreads;
-        float s8 = 0.0f;
+        float s8 = 0.0f, h8 = 0.0f;
         if (c < chunks) {
             float f[8];
-            if (p.io_type == STARK_B200_F32 && p.prologue == kProPlain) {
+            if (f32_in) {
                 const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
-                float4 a = x4[2 * c], b = x4[2 * c + 1];
+                const float4 a = x4[2 * c], b = x4[2 * c + 1];
                 f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
             } else {
-                uint4 v = reinterpret_cast<const uint4 *>(xs)[c];
+                const uint4 v = reinterpret_cast<const uint4 *>(xs)[c];
                 const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -264,140 +381,107 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_a4_kernel(const QmvParams p) 
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 s8 += f[i];
-                float sv = f[i] * xscale;
+                const float sv = f[i] * xscale;
                 hh[i] = __float2half_rn(sv);
-                if (SPLIT) hl[i] = __float2half_rn(sv - __half2float(hh[i]));
+                h8 += __half2float(hh[i]);
+                if (SPLIT) {
+                    hl[i] = __float2half_rn(sv - __half2float(hh[i]));
+                    h8 += __half2float(hl[i]);
+                }
             }
             reinterpret_cast<uint4 *>(xs)[c] = *reinterpret_cast<uint4 *>(hh);
             if (SPLIT) reinterpret_cast<uint4 *>(xlo)[c] = *reinterpret_cast<uint4 *>(hl);
         }
-        s8 += __shfl_xor_sync(0xffffffffu, s8, 1);
-        s8 += __shfl_xor_sync(0xffffffffu, s8, 2);
-        s8 += __shfl_xor_sync(0xffffffffu, s8, 4);
-        if (c < chunks && (lane & 7u) == 0) xsum[c >> 3] = s8;
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            s8 += __shfl_xor_sync(0xffffffffu, s8, o);
+            h8 += __shfl_xor_sync(0xffffffffu, h8, o);
+        }
+        if (c < chunks && (lane & 7u) == 0) {
+            xsum[c >> 3] = s8;
+            xoff[c >> 3] = -64.0f * h8;
+        }
     }
     named_bar_sync(1, kConsumerThreads);
 
-    // Main loop.
+    // Main loop: no block-wide barrier from here on.
     const uint32_t g = lane >> 2, t = lane & 3u;
-    uint32_t s = 0;
-    uint32_t buf = 0;
-    float held = 0.0f;  // kEpiSwiGlu: the `up` value of the even tile
-    float best = -INFINITY;
-    uint32_t best_index = 0xffffffffu;
+    const uint8_t *my_rec = ring + warp * kA4RecordBytes + lane * 16u;
+    const uint8_t *my_planes = ring + warp * kA4RecordBytes + 512u + 4u * g;
+    const __half *my_x = xs + warp * 64u + t * 16u;
+    const __half *my_xlo = xlo + warp * 64u + t * 16u;
+    uint32_t slot = 0, phase = 0;
+    uint32_t rb = 0, rphase = 1;
     for (uint32_t tile = t0; tile < t1; ++tile) {
         float acc_s0 = 0.0f, acc_s1 = 0.0f, acc_b0 = 0.0f, acc_b1 = 0.0f;
-        for (uint32_t st = 0; st < p.stages_per_tile; ++st, ++s) {
-            const uint32_t slot = s % p.num_stages;
-            if (!mbar_wait_bounded(&full[slot], (s / p.num_stages) & 1u, abort_flag)) {
-                *abort_flag = 1;
-                atomicOr(p.error_word, kErrMbarTimeout);
-            }
-            const uint8_t *stage = ring + (size_t)slot * p.stage_capacity;
-            for (uint32_t r = warp; r < p.stage_records; r += kConsumerWarps) {
-                const uint32_t kg = st * p.stage_records + r;
-                const uint8_t *rec = stage + r * kA4RecordBytes;
-                const uint4 wq = *reinterpret_cast<const uint4 *>(rec + lane * 16u);
-                const uint32_t sw = *reinterpret_cast<const uint32_t *>(rec + 512u + 4u * g);
-                const uint32_t bw = *reinterpret_cast<const uint32_t *>(rec + 544u + 4u * g);
-                const uint4 *xp = reinterpret_cast<const uint4 *>(xs + kg * 64u + t * 16u);
-                const uint4 xa = xp[0], xb = xp[1];
-                const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-                const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w};
-                float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-                if (SPLIT) {
-                    const uint4 *lp = reinterpret_cast<const uint4 *>(xlo + kg * 64u + t * 16u);
-                    const uint4 la = lp[0], lb = lp[1];
-                    const uint32_t lw[8] = {la.x, la.y, la.z, la.w, lb.x, lb.y, lb.z, lb.w};
+        uint32_t kg0 = 0;  // first group of the current stage
+        for (uint32_t st = 0; st < p.stages_per_tile; ++st) {
+            if (!mbar_wait_bounded(&full[slot], phase, abort_flag)) wait_failed(abort_flag, p.error_word);
+            const uint32_t soff = slot * p.stage_capacity;
+            // All of this warp's records of the stage are loaded first; the records are independent,
+            // so several tensor-pipe chains are in flight per warp.
+            uint4 wq[RPW];
+            uint32_t sw[RPW], bw[RPW];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t a[4];
-                        dequant_a4_word(ww[j], a);
-                        mma_m16n8k16_f16(c, a, xw[2 * j], xw[2 * j + 1]);
-                        mma_m16n8k16_f16(c, a, lw[2 * j], lw[2 * j + 1]);
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t a[4];
-                        dequant_a4_word(ww[j], a);
-                        mma_m16n8k16_f16(c, a, xw[2 * j], xw[2 * j + 1]);
-                    }
+            for (int i = 0; i < RPW; ++i) {
+                if (!PRED || warp + 8u * i < p.stage_records) {
+                    wq[i] = *reinterpret_cast<const uint4 *>(my_rec + soff + i * 8 * kA4RecordBytes);
+                    sw[i] = *reinterpret_cast<const uint32_t *>(my_planes + soff + i * 8 * kA4RecordBytes);
+                    bw[i] = *reinterpret_cast<const uint32_t *>(my_planes + soff + i * 8 * kA4RecordBytes + 32u);
                 }
-                const float xs_g = xsum[kg];
-                acc_s0 = fmaf(__uint_as_float(sw << 16), c[0], acc_s0);
-                acc_s1 = fmaf(__uint_as_float(sw & 0xffff0000u), c[2], acc_s1);
-                acc_b0 = fmaf(__uint_as_float(bw << 16), xs_g, acc_b0);
-                acc_b1 = fmaf(__uint_as_float(bw & 0xffff0000u), xs_g, acc_b1);
+            }
+#pragma unroll
+            for (int i = 0; i < RPW; ++i) {
+                if (!PRED || warp + 8u * i < p.stage_records) {
+                    const uint32_t kofs = (kg0 + 8u * i) * 64u;  // my_x already includes warp * 64
+                    const uint4 *xp = reinterpret_cast<const uint4 *>(my_x + kofs);
+                    const uint4 xa = xp[0], xb = xp[1];
+                    const uint32_t ww[4] = {wq[i].x, wq[i].y, wq[i].z, wq[i].w};
+                    const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t a[4];
+                        dequant_a4_word<FOLD>(ww[j], a);
+                        mma_m16n8k16_f16(c, a, xw[2 * j], xw[2 * j + 1]);
+                        if (SPLIT) {
+                            const uint2 lw = *reinterpret_cast<const uint2 *>(my_xlo + kofs + 4 * j);
+                            mma_m16n8k16_f16(c, a, lw.x, lw.y);
+                        }
+                    }
+                    const uint32_t kg = kg0 + warp + 8u * i;
+                    const float xs_g = xsum[kg];
+                    float d0 = c[0], d1 = c[2];
+                    if (FOLD) {
+                        const float xo = xoff[kg];      // -64 * sum of the f16 inputs of this group
+                        d0 = fmaf(16.0f, xo, d0);       // c - 1024 sum
+                        d1 = fmaf(d1, 0.0625f, xo);     // c / 16 - 64 sum
+                    }
+                    acc_s0 = fmaf(__uint_as_float(sw[i] << 16), d0, acc_s0);
+                    acc_s1 = fmaf(__uint_as_float(sw[i] & 0xffff0000u), d1, acc_s1);
+                    acc_b0 = fmaf(__uint_as_float(bw[i] << 16), xs_g, acc_b0);
+                    acc_b1 = fmaf(__uint_as_float(bw[i] & 0xffff0000u), xs_g, acc_b1);
+                }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[slot]);
+            kg0 += p.stage_records;
+            if (++slot == p.num_stages) {
+                slot = 0;
+                phase ^= 1u;
+            }
         }
-        // Cross-warp reduction of the 16 rows of this tile.
+        // Hand the 16 partial sums of this warp to the epilogue warp.
+        if (!mbar_wait_bounded(&red_empty[rb], rphase, abort_flag)) wait_failed(abort_flag, p.error_word);
         if (t == 0) {
-            red[(buf * kConsumerWarps + warp) * 16u + g] = fmaf(acc_s0, xunscale, acc_b0);
-            red[(buf * kConsumerWarps + warp) * 16u + g + 8u] = fmaf(acc_s1, xunscale, acc_b1);
+            red[(rb * kConsumerWarps + warp) * 16u + g] = fmaf(acc_s0, xunscale, acc_b0);
+            red[(rb * kConsumerWarps + warp) * 16u + g + 8u] = fmaf(acc_s1, xunscale, acc_b1);
         }
-        named_bar_sync(1, kConsumerThreads);
-        if (tid < 16) {
-            float v = 0.0f;
-#pragma unroll
-            for (int wv = 0; wv < kConsumerWarps; ++wv) v += red[(buf * kConsumerWarps + wv) * 16u + tid];
-            const uint32_t row = tile_row0(tile, p.pair_halves, p.rows) + tid;
-            const bool valid = row < p.rows;
-            if (p.epilogue == kEpiStore) {
-                if (valid) {
-                    if (p.io_type == STARK_B200_F32)
-                        reinterpret_cast<float *>(p.y)[row] = v;
-                    else
-                        reinterpret_cast<uint16_t *>(p.y)[row] = f32_to_bf16_bits(v);
-                }
-            } else if (p.epilogue == kEpiResidual) {
-                if (valid) {
-                    const float r = bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(p.resid)[row]);
-                    reinterpret_cast<uint16_t *>(p.y)[row] = f32_to_bf16_bits(bf16_round(v) + r);
-                }
-            } else if (p.epilogue == kEpiSwiGlu) {
-                if ((tile & 1u) == 0) {
-                    held = bf16_round(v);
-                } else {
-                    // gated_act_mul.rs:80-95: silu in f32 -> bf16, product of two bf16 -> bf16
-                    const float gate = bf16_round(v);
-                    const float activated = bf16_round(gate / (1.0f + expf(-1.0f * gate)));
-                    const uint32_t orow = (tile >> 1) * 16u + tid;
-                    if (orow < p.rows / 2u)
-                        reinterpret_cast<uint16_t *>(p.y)[orow] = f32_to_bf16_bits(held * activated);
-                }
-            } else {  // kEpiLogits
-                if (valid) {
-                    const uint16_t hb = f32_to_bf16_bits(v);
-                    reinterpret_cast<uint16_t *>(p.y)[row] = hb;
-                    const float lv = bf16_bits_to_f32(hb);
-                    // NaN must surface: treat any non-finite logit as the maximum so the host sees it.
-                    const float key = isfinite(lv) ? lv : INFINITY;
-                    if (key > best || (key == best && row < best_index)) {
-                        best = key;
-                        best_index = row;
-                    }
-                }
-            }
-        }
-        buf ^= 1u;
-    }
-    if (p.epilogue == kEpiLogits && warp == 0) {
-        // first index of the maximum over this CTA's rows
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) {
-            float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            uint32_t oi = __shfl_xor_sync(0xffffffffu, best_index, o);
-            if (ov > best || (ov == best && oi < best_index)) {
-                best = ov;
-                best_index = oi;
-            }
-        }
-        if (lane == 0) {
-            p.partial_max[blockIdx.x] = best;
-            p.partial_index[blockIdx.x] = best_index;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&red_full[rb]);
+        if (++rb == kRedSlots) {
+            rb = 0;
+            rphase ^= 1u;
         }
     }
 }
@@ -469,7 +553,7 @@ __global__ void unpack_a4_kernel(const uint8_t *__restrict__ data, uint8_t *__re
         const uint32_t row0 = tile_row0(tile, pair_halves, rows);
         const uint32_t word = *reinterpret_cast<const uint32_t *>(data + recno * kA4RecordBytes + lane * 16u + j * 4u);
         uint32_t a[4];
-        dequant_a4_word(word, a);
+        dequant_a4_word<false>(word, a);
         // a[0]: row g, k-pair r=0; a[1]: row g+8, r=0; a[2]: row g, r=1; a[3]: row g+8, r=1
 #pragma unroll
         for (int reg = 0; reg < 4; ++reg) {
@@ -486,10 +570,44 @@ __global__ void unpack_a4_kernel(const uint8_t *__restrict__ data, uint8_t *__re
     }
 }
 
-uint32_t pick_stage_records(uint32_t groups) {
+// Launch-shape knobs; the defaults are the measured best, the environment overrides exist for sweeps.
+struct Tuning {
+    uint32_t smem_budget_kb = 64;
+    uint32_t ctas_per_sm = 2;
+    bool fold = false;
+};
+const Tuning &tuning() {
+    static Tuning t = [] {
+        Tuning v;
+        if (const char *e = getenv("STARK_B200_QMV_SMEM_KB")) v.smem_budget_kb = std::max(32, std::min(200, atoi(e)));
+        if (const char *e = getenv("STARK_B200_QMV_CTAS")) v.ctas_per_sm = std::max(1, std::min(2, atoi(e)));
+        if (const char *e = getenv("STARK_B200_QMV_FOLD")) v.fold = atoi(e) != 0;
+        return v;
+    }();
+    return t;
+}
+
+// Records per ring stage: 8 * RPW when the group count allows it (no per-record predicates),
+// otherwise the largest divisor of the group count that fits.
+void pick_stage(uint32_t groups, uint32_t *records, uint32_t *rpw, bool *pred) {
+    for (uint32_t r : {32u, 16u, 8u}) {
+        if (groups % r == 0) {
+            *records = r;
+            *rpw = r / 8u;
+            *pred = false;
+            return;
+        }
+    }
+    uint32_t best = 1;
     for (uint32_t r = std::min(groups, kMaxStageRecords); r >= 1; --r)
-        if (groups % r == 0) return r;
-    return 1;
+        if (groups % r == 0) {
+            best = r;
+            break;
+        }
+    *records = best;
+    *rpw = (best + 7u) / 8u;
+    if (*rpw == 3) *rpw = 4;
+    *pred = true;
 }
 
 int sm_count_cached() {
@@ -520,7 +638,9 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     p.rows = m->rows;
     p.row_tiles = m->row_tiles;
     p.groups = m->groups;
-    p.stage_records = pick_stage_records(m->groups);
+    uint32_t rpw = 1;
+    bool pred = false;
+    pick_stage(m->groups, &p.stage_records, &rpw, &pred);
     p.stages_per_tile = m->groups / p.stage_records;
     p.stage_capacity = (p.stage_records * kA4RecordBytes + 127u) & ~127u;
     p.pair_halves = m->pair_halves;
@@ -538,9 +658,10 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     p.error_word = a.error_word;
 
     const bool split = a.io_type == STARK_B200_F32;
-    // Ring depth: as deep as fits in ~100 KB so that two kernels of a dependent-launch chain are
-    // resident on an SM at once (the next one prefetches while this one drains).
-    const uint32_t budget = 100u * 1024u;
+    const bool fold = tuning().fold;
+    // Ring depth: what fits the per-CTA budget.  Two CTAs share an SM, and under programmatic
+    // dependent launch CTAs of the next kernel join them and prefetch while this one drains.
+    const uint32_t budget = tuning().smem_budget_kb * 1024u;
     uint32_t stages = 8;
     while (stages > 2 && smem_layout(stages, p.stage_capacity, m->columns, split).total > budget) --stages;
     p.num_stages = stages;
@@ -548,14 +669,26 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     if (smem > 220u * 1024u) return STARK_B200_UNSUPPORTED;
 
     const uint32_t units = p.row_tiles / p.unit_tiles;
-    const uint32_t grid = std::max(1u, std::min(units, (uint32_t)sm_count_cached()));
+    const uint32_t grid = std::max(1u, std::min(units, (uint32_t)sm_count_cached() * tuning().ctas_per_sm));
     if (a.out_grid) *a.out_grid = grid;
 
-    auto kernel = split ? qmv_a4_kernel<true> : qmv_a4_kernel<false>;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[split ? 1 : 0]) {
+    using KernelFn = void (*)(const QmvParams);
+#define SB_QMV_ROW(SP, FO)                                                                               \
+    {                                                                                                    \
+        {qmv_a4_kernel<SP, 1, false, FO>, qmv_a4_kernel<SP, 2, false, FO>, qmv_a4_kernel<SP, 4, false, FO>}, { \
+            qmv_a4_kernel<SP, 1, true, FO>, qmv_a4_kernel<SP, 2, true, FO>, qmv_a4_kernel<SP, 4, true, FO>     \
+        }                                                                                                \
+    }
+    static const KernelFn table[2][2][2][3] = {{SB_QMV_ROW(false, false), SB_QMV_ROW(false, true)},
+                                               {SB_QMV_ROW(true, false), SB_QMV_ROW(true, true)}};
+#undef SB_QMV_ROW
+    const uint32_t ri = rpw == 1 ? 0u : (rpw == 2 ? 1u : 2u);
+    KernelFn kernel = table[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
+    static bool attr_set[2][2][2][3] = {};
+    bool &done = attr_set[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
+    if (!done) {
         SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        attr_set[split ? 1 : 0] = true;
+        done = true;
     }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);

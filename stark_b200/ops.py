@@ -129,3 +129,109 @@ class QMatrix:
             self.destroy()
         except Exception:
             pass
+
+
+class Graph:
+    """A recorded sequence of per-operator launches (device pointers only), replayed as one CUDA graph."""
+
+    def __init__(self, stream: int):
+        self.stream = stream
+        self._h = C.c_void_p()
+
+    def __enter__(self):
+        check(_lib.load().stark_b200_graph_begin(self.stream), "graph_begin")
+        return self
+
+    def __exit__(self, exc_type, exc, tb):
+        st = _lib.load().stark_b200_graph_end(self.stream, C.byref(self._h))
+        if exc_type is None:
+            check(st, "graph_end")
+        return False
+
+    def launch(self, stream: int | None = None):
+        check(_lib.load().stark_b200_graph_launch(self._h, self.stream if stream is None else stream),
+              "graph_launch")
+
+    def destroy(self):
+        if self._h and self._h.value:
+            _lib.load().stark_b200_graph_destroy(C.byref(self._h))
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+# ----------------------------------------------------------------------------- small operators (host buffers)
+
+def rmsnorm(x: np.ndarray, scales: np.ndarray, eps: float, shortcut: np.ndarray | None = None,
+            residual_add: bool = False):
+    """Returns (normed, shortcut_after) as bf16 bit patterns; mirrors Normalization::encode."""
+    x = np.ascontiguousarray(x, np.uint16)
+    scales = np.ascontiguousarray(scales, np.float32)
+    out = np.empty_like(x)
+    sc = None if shortcut is None else np.ascontiguousarray(shortcut, np.uint16).copy()
+    check(_lib.load().stark_b200_op_rmsnorm(_ptr(x), _ptr(scales), _ptr(out), None if sc is None else _ptr(sc),
+                                            x.size, eps, int(residual_add), HOST, None), "op_rmsnorm")
+    return out, sc
+
+
+def swiglu(fused: np.ndarray, gated_dim: int) -> np.ndarray:
+    fused = np.ascontiguousarray(fused, np.uint16)
+    out = np.empty(gated_dim, np.uint16)
+    check(_lib.load().stark_b200_op_swiglu(_ptr(fused), _ptr(out), gated_dim, HOST, None), "op_swiglu")
+    return out
+
+
+def qmv_swiglu(q: QMatrix, x: np.ndarray) -> np.ndarray:
+    x = np.ascontiguousarray(x, np.uint16)
+    out = np.empty(q.rows // 2, np.uint16)
+    check(_lib.load().stark_b200_op_qmv_swiglu(q._h, _ptr(x), _ptr(out), HOST, None), "op_qmv_swiglu")
+    return out
+
+
+def argmax(logits_bf16: np.ndarray) -> int:
+    logits = np.ascontiguousarray(logits_bf16, np.uint16)
+    out = C.c_uint32(0)
+    check(_lib.load().stark_b200_op_argmax(_ptr(logits), logits.size, C.byref(out), HOST, None), "op_argmax")
+    return out.value
+
+
+def log_softmax(logits: np.ndarray) -> np.ndarray:
+    logits = np.ascontiguousarray(logits, np.float32)
+    out = np.empty(logits.size, np.float64)
+    check(_lib.load().stark_b200_op_log_softmax(_ptr(logits), _ptr(out), logits.size, HOST, None),
+          "op_log_softmax")
+    return out
+
+
+def moe_route(logits: np.ndarray, experts: int, active: int, round_weights=False, round_logits=False):
+    logits = np.ascontiguousarray(logits, np.float32).reshape(-1, experts)
+    rows = logits.shape[0]
+    ids = np.zeros((rows, active), np.uint32)
+    weights = np.zeros((rows, active), np.float32)
+    check(_lib.load().stark_b200_op_moe_route(_ptr(logits), _ptr(ids), _ptr(weights), rows, experts, active,
+                                              int(round_weights), int(round_logits), HOST, None), "op_moe_route")
+    return ids, weights
+
+
+def attention_decode(qkv: np.ndarray, keys: np.ndarray, values: np.ndarray, q_heads: int, kv_heads: int,
+                     position: int, eps: float = 1e-6, rope_theta: float = 1e6, q_norm=None, k_norm=None,
+                     splits: int = 0) -> np.ndarray:
+    """One decode row of attention with fused QK-norm, RoPE and cache append.
+
+    keys/values: ``uint16[capacity, kv_heads, 128]`` with ``position`` valid rows; row ``position`` is
+    written in place.  Returns ``uint16[q_heads * 128]``.
+    """
+    qkv = np.ascontiguousarray(qkv, np.uint16)
+    assert keys.flags.c_contiguous and values.flags.c_contiguous and keys.dtype == np.uint16
+    capacity = keys.shape[0]
+    out = np.empty(q_heads * 128, np.uint16)
+    d = _lib.AttentionDesc(C.sizeof(_lib.AttentionDesc), _lib.ABI_VERSION, q_heads, kv_heads, 128, position,
+                           capacity, splits, eps, rope_theta)
+    qn = None if q_norm is None else _ptr(np.ascontiguousarray(q_norm, np.float32))
+    kn = None if k_norm is None else _ptr(np.ascontiguousarray(k_norm, np.float32))
+    check(_lib.load().stark_b200_op_attention_decode(_ptr(qkv), _ptr(keys), _ptr(values), _ptr(out), qn, kn,
+                                                     C.byref(d)), "op_attention_decode")
+    return out
