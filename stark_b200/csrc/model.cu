@@ -79,8 +79,8 @@ Model::~Model() {
 
 stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     *out = nullptr;
-    if (c.layers == 0 || c.hidden == 0 || c.hidden % 512u != 0 || c.head_dim != kHeadDim || c.kv_heads == 0 ||
-        c.q_heads % c.kv_heads != 0 || c.q_heads / c.kv_heads > 8u || c.inter == 0 || c.inter % 512u != 0 ||
+    if (c.layers == 0 || c.hidden == 0 || c.hidden % 64u != 0 || c.head_dim != kHeadDim || c.kv_heads == 0 ||
+        c.q_heads % c.kv_heads != 0 || c.q_heads / c.kv_heads > 8u || c.inter == 0 || c.inter % 64u != 0 ||
         c.vocab == 0 || c.context_tokens == 0 || !(c.eps > 0.0f) || !(c.rope_theta > 0.0f))
         return STARK_B200_INVALID_ARGUMENT;
     Model *m = new (std::nothrow) Model();
