@@ -1,0 +1,262 @@
+#!/usr/bin/env python
+"""Batch-1 decode benchmark of the token loop on synthetic random-init weights.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload qwen3-8b|qwen3-0.6b]
+    python bench.py --impl reference ...      # the reference's CPU path (oracle port), bounded sample
+
+A "step" is one greedy decode token at batch 1.  The default workload is the 4-bit Qwen3-8B-shaped
+dense decoder (36 layers, hidden 4096, 32 Q / 8 KV heads, intermediate 12288, vocab 151936) with a
+4096-token random prompt, the configuration the headline target is stated on.  Prints ONE JSON line.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+from stark_b200 import synthetic as S  # noqa: E402
+
+WORKLOADS = {
+    "qwen3-8b": dict(cfg="qwen3-8b", prompt=4096, context=4096 + 1024),
+    "qwen3-0.6b": dict(cfg="qwen3-0.6b", prompt=512, context=512 + 512),
+    "small": dict(cfg="small", prompt=96, context=512),
+}
+BYTES_PER_WEIGHT = 0.5625  # 4-bit codes + bf16 scale and bias per 64 columns
+
+
+def peaks() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def weight_count(cfg: dict) -> tuple[int, int]:
+    """(weights read by one decode step, of which read-out table)."""
+    D, hd, I, V = cfg["hidden"], cfg["head_dim"], cfg["inter"], cfg["vocab"]
+    per_layer = (cfg["q_heads"] + 2 * cfg["kv_heads"]) * hd * D + D * cfg["q_heads"] * hd + 2 * I * D + D * I
+    return cfg["layers"] * per_layer + V * D, V * D
+
+
+def step_bytes(cfg: dict, context_rows: float) -> float:
+    """Algorithmic bytes of one decode step: every quantized matrix once, the KV rows of the
+    context, one embedding row, and the activation vectors."""
+    n, _ = weight_count(cfg)
+    kv = cfg["layers"] * 2 * cfg["kv_heads"] * cfg["head_dim"] * 2 * context_rows
+    D, I = cfg["hidden"], cfg["inter"]
+    vectors = cfg["layers"] * 2 * (4 * D + (cfg["q_heads"] + 2 * cfg["kv_heads"]) * 128 + cfg["q_heads"] * 128 + I) \
+        + 2 * cfg["vocab"]
+    return n * BYTES_PER_WEIGHT + kv + cfg["hidden"] * BYTES_PER_WEIGHT + vectors
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm = [float(r[0]) for r in self.rows if len(r) >= 7 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[3 + i] == "Active" for r in self.rows)]
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def cpu_sample(cfg: dict, weights: dict, prompt: np.ndarray, prompt_rows: int, steps: int, threads: int) -> dict:
+    """Times the CPU oracle (a port of the reference's CPU kernels) on a bounded sample."""
+    from oracle import oracle as O
+    orc = O.DenseOracle(cfg, weights, capacity=prompt_rows + steps + 1, threads=threads)
+    for t in prompt[:prompt_rows - 1]:
+        orc.ingest(int(t))
+    logits = orc.step(int(prompt[prompt_rows - 1]))
+    tok = O.argmax_bf16(logits)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = O.argmax_bf16(orc.step(tok))
+    dt = time.perf_counter() - t0
+    return {"value": steps / dt, "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"{steps} greedy decode steps after a {prompt_rows}-token prompt, same weights"}
+
+
+def run_reference(args, wl, cfg) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    threads = O.max_threads()
+    weights = S.dense_weights(cfg, seed=args.seed)
+    prompt = S.prompt(cfg, wl["prompt"], seed=args.seed + 1)
+    # bounded sample: a short prompt, then `warmup` untimed and `steps` timed decode steps
+    steps = max(1, min(args.steps, 4 if cfg["layers"] >= 28 else 16))
+    warm = min(args.warmup, 1)
+    orc = O.DenseOracle(cfg, weights, capacity=8 + warm + steps + 1, threads=threads)
+    for t in prompt[:7]:
+        orc.ingest(int(t))
+    tok = O.argmax_bf16(orc.step(int(prompt[7])))
+    for _ in range(warm):
+        tok = O.argmax_bf16(orc.step(tok))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = O.argmax_bf16(orc.step(tok))
+    dt = time.perf_counter() - t0
+    value = steps / dt
+    sample = f"{steps} greedy decode steps after an 8-token prompt (CPU oracle port, OpenMP over rows)"
+    print(json.dumps({
+        "impl": "reference", "metric": "batch-1 decode tok/s", "value": value, "unit": "tok/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": 1e3 * dt / steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{wl['cfg']} 4-bit MLX-affine g64, batch 1, greedy decode"},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="qwen3-8b", choices=sorted(WORKLOADS))
+    ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    cfg = S.CONFIGS[wl["cfg"]]
+    if args.impl == "reference":
+        run_reference(args, wl, cfg)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    from stark_b200.engine import DenseModel
+    from stark_b200.ops import take_device_error
+
+    steps, warmup = args.steps, max(args.warmup, 3)
+    context = max(wl["context"], wl["prompt"] + warmup + 2 * steps + 8)
+    weights = S.dense_weights(cfg, seed=args.seed)
+    prompt = S.prompt(cfg, wl["prompt"], seed=args.seed + 1)
+    model = DenseModel.load(cfg, weights, context_tokens=context)
+    info = model.info()
+    stream = torch.cuda.ExternalStream(model.stream())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-timed decode: tokens chained on the device, inputs resident in HBM ------------
+    model.prefill(prompt)
+    model.drain()
+    model.generate_greedy(warmup)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        e0.record(stream)
+        model.generate_greedy(steps)
+        e1.record(stream)
+        barrier()
+    ms = e0.elapsed_time(e1)
+    assert take_device_error() == 0, "a kernel reported a timed-out wait"
+    mean_context = wl["prompt"] + warmup + steps / 2.0
+
+    # ---- end to end through the public API: host token in, host result out, every step --------
+    model.reset()
+    model.prefill(prompt)
+    tok = model.argmax()
+    for _ in range(warmup):
+        model.step_async(tok)
+        tok = model.argmax()
+    barrier()
+    e2e_steps = min(steps, 256)
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        model.step_async(tok)   # 4-byte host->device token copy
+        tok = model.argmax()    # 16-byte device->host read of the step result
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+
+    t = torch.tensor([ms, e2e_s], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_s = float(t[0]), float(t[1])
+    value = world * steps / (ms / 1e3)
+    e2e_value = world * e2e_steps / e2e_s
+
+    peak, peak_kind = peaks()
+    algo = step_bytes(cfg, mean_context)
+    achieved = algo / (ms / steps * 1e-3) / 1e9
+    line = {
+        "metric": "batch-1 decode tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{wl['cfg']} 4-bit MLX-affine g64, batch 1, {wl['prompt']}-token prompt, greedy decode",
+                   "parallelism": "tp1" if world == 1 else f"{world} independent replicas",
+                   "l2": "per-step inputs (weights %.2f GB + KV) exceed the 126 MB L2" % (info.weight_bytes / 1e9),
+                   "mean_context_rows": mean_context},
+        "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 16,
+                "steps": e2e_steps},
+        "gpu_launches": int(steps * info.launches_per_step),
+        "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "traffic": None, "peak_kind": peak_kind, "frac_of_8tbs": achieved / 8000.0,
+                     "algorithmic_bytes_per_step": algo,
+                     "note": "whole decode step (all kernels of the token) over the step's algorithmic bytes"},
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        from oracle import oracle as O
+        n = 2 if cfg["layers"] >= 28 else 8
+        line["cpu_baseline"] = cpu_sample(cfg, weights, prompt, 8, n, O.max_threads())
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

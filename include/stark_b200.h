@@ -288,6 +288,15 @@ stark_b200_status stark_b200_generate_greedy(stark_b200_model *model, uint32_t s
  * crates/stark-engine/src/encodable_block/mixer/attention/state.rs:175-195). */
 stark_b200_status stark_b200_rewind(stark_b200_model *model, uint64_t position);
 stark_b200_status stark_b200_get_info(stark_b200_model *model, stark_b200_info *info);
+/* Per-launch timeline of the token sequences issued since the last call: for each of the
+ * launches_per_step kernels, four device-clock values in ns {first CTA entered, wait on the previous
+ * kernel returned, last prologue done, last CTA left}.  Only available when the library was started
+ * with STARK_B200_TRACE=1 (UNSUPPORTED otherwise); the analogue of the reference's aggregate
+ * profiler (crates/stark-engine/src/engine/hybrid/profile.rs:1-89).  count = 4 * launches_per_step. */
+stark_b200_status stark_b200_read_trace(stark_b200_model *model, uint64_t *dst, size_t count);
+/* The CUDA stream (cudaStream_t) the model's work is issued on, for callers that time it with
+ * their own events. */
+stark_b200_status stark_b200_model_stream(stark_b200_model *model, void **out_stream);
 
 /* ------------------------------------------------------------------------------------------
  * Recorded launch sequences.  The reference records a whole token into one command buffer

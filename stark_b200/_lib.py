@@ -112,6 +112,8 @@ def load() -> C.CDLL:
         "stark_b200_generate_greedy": (u32, [vp, u32, vp]),
         "stark_b200_rewind": (u32, [vp, u64]),
         "stark_b200_get_info": (u32, [vp, C.POINTER(Info)]),
+        "stark_b200_model_stream": (u32, [vp, C.POINTER(vp)]),
+        "stark_b200_read_trace": (u32, [vp, vp, sz]),
         "stark_b200_graph_begin": (u32, [vp]),
         "stark_b200_graph_end": (u32, [vp, C.POINTER(vp)]),
         "stark_b200_graph_launch": (u32, [vp, vp]),

@@ -381,6 +381,17 @@ stark_b200_status stark_b200_rewind(stark_b200_model *model, uint64_t position) 
     return model_rewind(M(model), position);
 }
 
+stark_b200_status stark_b200_model_stream(stark_b200_model *model, void **out_stream) {
+    if (!model || !out_stream) return STARK_B200_INVALID_ARGUMENT;
+    *out_stream = (void *)M(model)->stream;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_read_trace(stark_b200_model *model, uint64_t *dst, size_t count) {
+    if (!model || !dst) return STARK_B200_INVALID_ARGUMENT;
+    return model_read_trace(M(model), reinterpret_cast<unsigned long long *>(dst), count);
+}
+
 stark_b200_status stark_b200_get_info(stark_b200_model *model, stark_b200_info *info) {
     if (!model || !info) return STARK_B200_INVALID_ARGUMENT;
     if (info->struct_size != sizeof(stark_b200_info) || info->abi_version != STARK_B200_ABI_VERSION)

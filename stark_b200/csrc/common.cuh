@@ -127,6 +127,24 @@ __device__ inline uint4 ldg_nc_v4(const void *p) {
     return v;
 }
 
+// ---- optional in-kernel timeline (off unless a trace buffer is passed) ---------------------------
+// One slot per launch of a recorded token sequence: when the first CTA entered, when its wait on
+// the previous kernel returned, when the last CTA finished its prologue, when the last CTA left.
+struct TraceSlot {
+    unsigned long long start, ready, compute, end;
+};
+__device__ inline unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ inline void trace_min(unsigned long long *field) {
+    if (field) atomicMin(field, global_ns());
+}
+__device__ inline void trace_max(unsigned long long *field) {
+    if (field) atomicMax(field, global_ns());
+}
+
 // ---- host-side status plumbing ---------------------------------------------------------------------
 // Last CUDA error seen by this library on the calling thread (for stark_b200_last_cuda_error).
 inline cudaError_t &last_cuda_error() {

@@ -63,6 +63,8 @@ Model::~Model() {
     cudaFree(rope_sin);
     cudaFree(state);
     cudaFree(pending);
+    cudaFree(generated);
+    cudaFree(trace);
     cudaFree(h);
     cudaFree(qkv);
     cudaFree(attn);
@@ -136,6 +138,7 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     m->attn_splits = std::min<uint32_t>(kMaxAttnSplits, std::max<uint32_t>(1u, 296u / c.kv_heads));
     if ((st = dmalloc(&m->state, 1)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->pending, (size_t)c.context_tokens + 1u)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->generated, (size_t)c.context_tokens + 1u)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->h, c.hidden)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->qkv, qkv_n)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->attn, c.q_heads * kHeadDim)) != STARK_B200_OK) return fail(st);
@@ -147,6 +150,12 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     if ((st = dmalloc(&m->attn_counters, c.kv_heads)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->partial_max, 1024)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->partial_index, 1024)) != STARK_B200_OK) return fail(st);
+    if (const char *e = getenv("STARK_B200_TRACE")) {
+        if (e[0] == '1') {
+            m->trace_slots = 1u + 5u * c.layers + 2u;
+            if ((st = dmalloc(&m->trace, m->trace_slots)) != STARK_B200_OK) return fail(st);
+        }
+    }
     if (cudaMemset(m->attn_counters, 0, c.kv_heads * 4) != cudaSuccess ||
         cudaMemset(m->state, 0, sizeof(StepState)) != cudaSuccess)
         return fail(STARK_B200_DEVICE_FAILURE);
@@ -222,6 +231,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
     uint32_t n = 0;
     if ((st = embedding_row_launch(m->embed, m->state, m->h, pdl, s)) != STARK_B200_OK) return st;
     ++n;
+    auto slot = [&](uint32_t index) -> TraceSlot * { return m->trace ? m->trace + index : nullptr; };
     for (uint32_t l = 0; l < c.layers; ++l) {
         auto &L = m->layers[l];
         QmvArgs a{};
@@ -237,6 +247,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.prologue = kProRmsNorm;
         a.norm_weight = L.attn_norm;
         a.epilogue = kEpiStore;
+        a.trace = slot(n);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
         // attention with fused QK-norm, RoPE and KV append
         AttnArgs at{};
@@ -258,6 +269,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         at.counters = m->attn_counters;
         at.error_word = ctx->error_word;
         at.pdl = pdl;
+        at.trace = slot(n + 1);
         if ((st = attention_decode_launch(at, s)) != STARK_B200_OK) return st;
         // h = bf16(bf16(W_o attn) + h)
         a.matrix = L.o;
@@ -266,6 +278,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.resid = m->h;
         a.prologue = kProPlain;
         a.epilogue = kEpiResidual;
+        a.trace = slot(n + 2);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
         // act = silu(gate) * up
         a.matrix = L.upgate;
@@ -274,6 +287,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.prologue = kProRmsNorm;
         a.norm_weight = L.mlp_norm;
         a.epilogue = kEpiSwiGlu;
+        a.trace = slot(n + 3);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
         // h = bf16(bf16(W_down act) + h)
         a.matrix = L.down;
@@ -282,6 +296,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.resid = m->h;
         a.prologue = kProPlain;
         a.epilogue = kEpiResidual;
+        a.trace = slot(n + 4);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
         n += 5;
     }
@@ -302,8 +317,9 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.partial_index = m->partial_index;
         uint32_t grid = 0;
         a.out_grid = &grid;
+        a.trace = slot(n);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
-        if ((st = argmax_finalize_launch(m->partial_max, m->partial_index, grid, m->state, true, pdl, s)) != STARK_B200_OK)
+        if ((st = argmax_finalize_launch(m->partial_max, m->partial_index, grid, m->state, m->generated, true, pdl, s)) != STARK_B200_OK)
             return st;
         n += 2;
     } else {
@@ -471,14 +487,16 @@ stark_b200_status model_generate_greedy(Model *m, uint32_t steps, uint32_t *out_
     if (m->position + steps > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
     uint32_t *pinned = nullptr;
     SB_CUDA(cudaMallocHost(&pinned, (size_t)(steps + 1u) * 4u));
-    cudaError_t e = cudaSuccess;
-    // out[0] is the token sampled from the logits already present (the prompt's last row).
-    e = cudaMemcpyAsync(&pinned[0], &m->state->next_token, 4, cudaMemcpyDeviceToHost, m->stream);
-    for (uint32_t i = 0; i < steps && e == cudaSuccess; ++i) {
-        e = cudaGraphLaunch(m->step_graph, m->stream);
-        if (e == cudaSuccess)
-            e = cudaMemcpyAsync(&pinned[i + 1], &m->state->next_token, 4, cudaMemcpyDeviceToHost, m->stream);
-    }
+    // out[0] is the token sampled from the logits already present (the prompt's last row); the
+    // rest are appended to the device-side list by each step and fetched in one copy at the end.
+    const uint32_t window[2] = {0u, steps};
+    cudaError_t e = cudaMemcpyAsync(&pinned[0], &m->state->next_token, 4, cudaMemcpyDeviceToHost, m->stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&m->state->gen_cursor, window, 8, cudaMemcpyHostToDevice, m->stream);
+    for (uint32_t i = 0; i < steps && e == cudaSuccess; ++i) e = cudaGraphLaunch(m->step_graph, m->stream);
+    if (e == cudaSuccess && steps)
+        e = cudaMemcpyAsync(&pinned[1], m->generated, (size_t)steps * 4u, cudaMemcpyDeviceToHost, m->stream);
+    const uint32_t closed[2] = {0u, 0u};
+    if (e == cudaSuccess) e = cudaMemcpyAsync(&m->state->gen_cursor, closed, 8, cudaMemcpyHostToDevice, m->stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(m->stream);
     if (e == cudaSuccess) memcpy(out_tokens, pinned, (size_t)(steps + 1u) * 4u);
     cudaFreeHost(pinned);
@@ -489,6 +507,17 @@ stark_b200_status model_generate_greedy(Model *m, uint32_t steps, uint32_t *out_
     m->position += steps;
     m->launches_issued += (uint64_t)steps * m->step_launches;
     return check_device_error(m);
+}
+
+// Copies out the timeline slots of the launches issued since the last call and re-arms them.
+stark_b200_status model_read_trace(Model *m, unsigned long long *dst, size_t count) {
+    if (!m->trace) return STARK_B200_UNSUPPORTED;
+    if (count != (size_t)m->trace_slots * 4u) return STARK_B200_INVALID_ARGUMENT;
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    SB_CUDA(cudaMemcpy(dst, m->trace, count * 8u, cudaMemcpyDeviceToHost));
+    std::vector<TraceSlot> init(m->trace_slots, TraceSlot{~0ull, ~0ull, 0ull, 0ull});
+    SB_CUDA(cudaMemcpy(m->trace, init.data(), count * 8u, cudaMemcpyHostToDevice));
+    return STARK_B200_OK;
 }
 
 }  // namespace sb

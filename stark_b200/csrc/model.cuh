@@ -25,7 +25,10 @@ struct Model {
     int32_t *block_table = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     StepState *state = nullptr;
-    uint32_t *pending = nullptr;  // prompt tokens still to be ingested (device)
+    uint32_t *pending = nullptr;    // prompt tokens still to be ingested (device)
+    uint32_t *generated = nullptr;  // greedy tokens of a device-chained run (device)
+    TraceSlot *trace = nullptr;     // optional per-launch timeline (STARK_B200_TRACE=1)
+    uint32_t trace_slots = 0;
     uint16_t *h = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr, *logits = nullptr;
     float *attn_scratch = nullptr;
     uint32_t *attn_counters = nullptr;
@@ -56,5 +59,6 @@ stark_b200_status model_next_token(Model *m, uint32_t *out);
 stark_b200_status model_readout_bf16(Model *m, uint16_t *dst, size_t count);
 stark_b200_status model_readout_f32(Model *m, float *dst, size_t count);
 stark_b200_status model_generate_greedy(Model *m, uint32_t steps, uint32_t *out_tokens);
+stark_b200_status model_read_trace(Model *m, unsigned long long *dst, size_t count);
 
 }  // namespace sb

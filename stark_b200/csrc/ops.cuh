@@ -17,6 +17,9 @@ struct StepState {
     uint32_t token;       // input token of this step
     uint32_t next_token;  // greedy read-out of this step (UINT32_MAX if a logit is not finite)
     uint32_t cursor;      // next entry of the pending prompt list (cache-only ingest)
+    uint32_t gen_cursor;  // next free slot of the generated-token list
+    uint32_t gen_capacity;
+    uint32_t reserved[2];
 };
 
 // Paged KV cache of one layer.  Page p of KV head h holds kPageTokens rows of kHeadDim bf16:
@@ -45,6 +48,7 @@ struct AttnArgs {
     float *scratch;           // [kv_heads * splits * gqa * (128 + 2)] partial (o, m, l)
     uint32_t *counters;       // [kv_heads] arrival counters, zero before the launch and after it
     uint32_t *error_word;
+    TraceSlot *trace;
     bool pdl;
 };
 stark_b200_status attention_decode_launch(const AttnArgs &a, cudaStream_t stream);
@@ -57,7 +61,8 @@ stark_b200_status embedding_row_launch(const QMatrix *table, const StepState *st
 // Final reduction of the per-CTA (max, first index) partials of the logits matvec; writes
 // state->next_token, optionally advances the step state (position += 1, token = next_token).
 stark_b200_status argmax_finalize_launch(const float *partial_max, const uint32_t *partial_index, uint32_t count,
-                                         StepState *state, bool advance, bool pdl, cudaStream_t stream);
+                                         StepState *state, uint32_t *generated, bool advance, bool pdl,
+                                         cudaStream_t stream);
 
 // End of a cache-only prompt row: position += 1, token = pending[cursor++].
 stark_b200_status ingest_advance_launch(StepState *state, const uint32_t *pending, bool pdl, cudaStream_t stream);

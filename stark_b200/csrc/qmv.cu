@@ -33,6 +33,7 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kProducerWarp = kConsumerWarps;
 constexpr int kEpilogueWarp = kConsumerWarps + 1;
 constexpr int kThreads = (kConsumerWarps + 2) * 32;
+constexpr int kMaxRounds = 6;  // input chunks (8 elements) a consumer thread keeps in registers: K <= 12288
 constexpr int kRedSlots = 4;  // depth of the partial-sum hand-off ring between consumers and the epilogue warp
 
 struct QmvParams {
@@ -57,6 +58,7 @@ struct QmvParams {
     float *partial_max;
     uint32_t *partial_index;
     uint32_t *error_word;
+    TraceSlot *trace;
 };
 
 // 4-bit -> f16 conversion of one record word into an m16n8k16 A fragment.
@@ -97,11 +99,11 @@ __device__ inline void dequant_a4_word(uint32_t w, uint32_t (&a)[4]) {
 }
 
 struct SmemLayout {
-    uint32_t ring, xs, xlo, xsum, xoff, red, wred, bars, flags, total;
+    uint32_t ring, xs, xlo, nws, xsum, xoff, red, wred, bars, flags, total;
 };
 
 __host__ __device__ inline SmemLayout smem_layout(uint32_t num_stages, uint32_t stage_capacity, uint32_t columns,
-                                                  bool split) {
+                                                  bool split, bool norm) {
     SmemLayout L;
     uint32_t off = 0;
     L.ring = off;
@@ -110,6 +112,8 @@ __host__ __device__ inline SmemLayout smem_layout(uint32_t num_stages, uint32_t 
     off += columns * 2u;
     L.xlo = off;
     off += split ? columns * 2u : 0u;
+    L.nws = off;
+    off += norm ? columns * 2u : 0u;
     L.xsum = off;
     off += (columns / 64u) * 4u;
     L.xoff = off;
@@ -141,10 +145,11 @@ template <bool SPLIT, int RPW, bool PRED, bool FOLD>
 __global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t columns = p.groups * 64u;
-    const SmemLayout L = smem_layout(p.num_stages, p.stage_capacity, columns, SPLIT);
+    const SmemLayout L = smem_layout(p.num_stages, p.stage_capacity, columns, SPLIT, p.prologue == kProRmsNorm);
     uint8_t *ring = smem + L.ring;
     __half *xs = reinterpret_cast<__half *>(smem + L.xs);
     __half *xlo = reinterpret_cast<__half *>(smem + L.xlo);
+    uint16_t *nws = reinterpret_cast<uint16_t *>(smem + L.nws);
     float *xsum = reinterpret_cast<float *>(smem + L.xsum);
     float *xoff = reinterpret_cast<float *>(smem + L.xoff);
     float *red = reinterpret_cast<float *>(smem + L.red);
@@ -178,6 +183,7 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) 
     }
     __syncthreads();
     pdl_launch_dependents();
+    if (tid == 0 && p.trace) trace_min(&p.trace->start);
 
     if (warp == kProducerWarp) {
         // ---------------- producer: stream this CTA's byte range through the ring ----------------
@@ -204,9 +210,8 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) 
         return;
     }
 
-    pdl_wait();  // the input vector (and anything the epilogue overwrites) belongs to the previous kernel
-
     if (warp == kEpilogueWarp) {
+        pdl_wait();  // everything the epilogue reads or overwrites belongs to the previous kernel
         // ---------------- epilogue warp: cross-warp reduction and output of finished row tiles ----------
         uint32_t rb = 0, rphase = 0;
         float held = 0.0f;  // kEpiSwiGlu: the `up` value of the even tile
@@ -266,6 +271,7 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) 
                 }
             }
         }
+        if (lane == 0 && p.trace) trace_max(&p.trace->end);
         if (p.epilogue == kEpiLogits) {
             // first index of the maximum over this CTA's rows (lanes >= 16 hold -inf)
 #pragma unroll
@@ -286,63 +292,86 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) 
     }
 
     // ---------------- consumers ----------------
-    // Prologue: build the f16 input vector, its power-of-two scale and the per-group sums.
+    // Before the wait: everything that does not depend on the previous kernel.  The norm weights
+    // are constants, so their bf16-rounded values (normalization.rs:157-161 rounds them before the
+    // product) are staged in shared memory while the previous kernel is still running.
     const uint32_t chunks = columns / 8u;
     const bool f32_in = p.io_type == STARK_B200_F32 && p.prologue == kProPlain;
-    float sumsq = 0.0f;
     if (p.prologue == kProRmsNorm) {
-        const uint4 *h4 = reinterpret_cast<const uint4 *>(p.x);
+        const float4 *nw = reinterpret_cast<const float4 *>(p.norm_weight);
         for (uint32_t c = tid; c < chunks; c += kConsumerThreads) {
-            const uint4 v = h4[c];
-            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float a = __uint_as_float(wv[i] << 16), b = __uint_as_float(wv[i] & 0xffff0000u);
-                sumsq += a * a;
-                sumsq += b * b;
-            }
+            const float4 n0 = nw[2 * c], n1 = nw[2 * c + 1];
+            uint4 o;
+            o.x = (uint32_t)f32_to_bf16_bits(n0.x) | ((uint32_t)f32_to_bf16_bits(n0.y) << 16);
+            o.y = (uint32_t)f32_to_bf16_bits(n0.z) | ((uint32_t)f32_to_bf16_bits(n0.w) << 16);
+            o.z = (uint32_t)f32_to_bf16_bits(n1.x) | ((uint32_t)f32_to_bf16_bits(n1.y) << 16);
+            o.w = (uint32_t)f32_to_bf16_bits(n1.z) | ((uint32_t)f32_to_bf16_bits(n1.w) << 16);
+            reinterpret_cast<uint4 *>(nws)[c] = o;
         }
+    }
+    pdl_wait();  // the input vector belongs to the previous kernel
+    if (tid == 0 && p.trace) trace_min(&p.trace->ready);
+
+    // One trip to global memory: this thread's chunks of the input row stay in registers for the
+    // whole prologue (up to kMaxRounds chunks of 8 elements; the launcher checks the width).
+    float f[kMaxRounds][8];
+#pragma unroll
+    for (int r = 0; r < kMaxRounds; ++r) {
+        const uint32_t c = tid + r * kConsumerThreads;
+        if (c < chunks) {
+            if (f32_in) {
+                const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
+                const float4 a = x4[2 * c], b = x4[2 * c + 1];
+                f[r][0] = a.x, f[r][1] = a.y, f[r][2] = a.z, f[r][3] = a.w;
+                f[r][4] = b.x, f[r][5] = b.y, f[r][6] = b.z, f[r][7] = b.w;
+            } else {
+                const uint4 v = reinterpret_cast<const uint4 *>(p.x)[c];
+                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    f[r][2 * i] = __uint_as_float(wv[i] << 16);
+                    f[r][2 * i + 1] = __uint_as_float(wv[i] & 0xffff0000u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[r][i] = 0.0f;
+        }
+    }
+    if (p.prologue == kProRmsNorm) {
+        float sumsq = 0.0f;
+#pragma unroll
+        for (int r = 0; r < kMaxRounds; ++r)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sumsq += f[r][i] * f[r][i];
         sumsq = warp_sum(sumsq);
         if (lane == 0) wred[warp] = sumsq;
-        named_bar_sync(1, kConsumerThreads);
+        named_bar_sync(1, kConsumerThreads);  // also orders the staging of the norm weights
         sumsq = 0.0f;
 #pragma unroll
         for (int i = 0; i < kConsumerWarps; ++i) sumsq += wred[i];
-    }
-    const float rms_inv = 1.0f / sqrtf(sumsq / (float)columns + p.eps);
-
-    // Pass 1: the input row as bf16 bits parked in `xs` (f32 inputs are re-read in pass 2), and its maximum.
-    float vmax = 0.0f;
-    for (uint32_t c = tid; c < chunks; c += kConsumerThreads) {
-        if (f32_in) {
-            const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
-            const float4 a = x4[2 * c], b = x4[2 * c + 1];
-            vmax = fmaxf(vmax, fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(a.z), fabsf(a.w))));
-            vmax = fmaxf(vmax, fmaxf(fmaxf(fabsf(b.x), fabsf(b.y)), fmaxf(fabsf(b.z), fabsf(b.w))));
-        } else {
-            const uint4 v = reinterpret_cast<const uint4 *>(p.x)[c];
-            uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-            if (p.prologue == kProRmsNorm) {
-                const float4 *nw = reinterpret_cast<const float4 *>(p.norm_weight);
-                const float4 n0 = nw[2 * c], n1 = nw[2 * c + 1];
-                const float ns[8] = {n0.x, n0.y, n0.z, n0.w, n1.x, n1.y, n1.z, n1.w};
+        const float rms_inv = 1.0f / sqrtf(sumsq / (float)columns + p.eps);
+#pragma unroll
+        for (int r = 0; r < kMaxRounds; ++r) {
+            const uint32_t c = tid + r * kConsumerThreads;
+            if (c < chunks) {
+                const uint4 nv = reinterpret_cast<const uint4 *>(nws)[c];
+                const uint32_t nwv[4] = {nv.x, nv.y, nv.z, nv.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const float a = __uint_as_float(wv[i] << 16), b = __uint_as_float(wv[i] & 0xffff0000u);
-                    // normalization.rs:157-161: bf16(normalized) * bf16(scale), product rounded to bf16
-                    const uint16_t ra = f32_to_bf16_bits(bf16_round(a * rms_inv) * bf16_round(ns[2 * i]));
-                    const uint16_t rb = f32_to_bf16_bits(bf16_round(b * rms_inv) * bf16_round(ns[2 * i + 1]));
-                    wv[i] = (uint32_t)ra | ((uint32_t)rb << 16);
+                    // bf16(normalized) * bf16(scale), product rounded to bf16
+                    f[r][2 * i] = bf16_round(bf16_round(f[r][2 * i] * rms_inv) * __uint_as_float(nwv[i] << 16));
+                    f[r][2 * i + 1] =
+                        bf16_round(bf16_round(f[r][2 * i + 1] * rms_inv) * __uint_as_float(nwv[i] & 0xffff0000u));
                 }
             }
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                vmax = fmaxf(vmax, fabsf(__uint_as_float(wv[i] << 16)));
-                vmax = fmaxf(vmax, fabsf(__uint_as_float(wv[i] & 0xffff0000u)));
-            }
-            reinterpret_cast<uint4 *>(xs)[c] = make_uint4(wv[0], wv[1], wv[2], wv[3]);
         }
     }
+    float vmax = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kMaxRounds; ++r)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) vmax = fmaxf(vmax, fabsf(f[r][i]));
     vmax = warp_max(vmax);
     if (lane == 0) wred[kConsumerWarps + warp] = vmax;
     named_bar_sync(1, kConsumerThreads);
@@ -356,39 +385,25 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) 
     const float xscale = __uint_as_float((uint32_t)(shift + 127) << 23);
     const float xunscale = __uint_as_float((uint32_t)(127 - shift) << 23);
 
-    // Pass 2: scaled f16 values in place, per-group sums of the input (for the bias term) and, for
-    // FOLD, -64 * the per-group sum of the f16 values the tensor core will see.
-    const uint32_t rounds = (chunks + kConsumerThreads - 1u) / kConsumerThreads;
-    for (uint32_t r = 0; r < rounds; ++r) {
+    // Scaled f16 values, per-group sums of the input (for the bias term) and, for FOLD, -64 * the
+    // per-group sum of the f16 values the tensor core will see.
+#pragma unroll
+    for (int r = 0; r < kMaxRounds; ++r) {
         const uint32_t c = tid + r * kConsumerThreads;
         float s8 = 0.0f, h8 = 0.0f;
+        __half hh[8], hl[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            s8 += f[r][i];
+            const float sv = f[r][i] * xscale;
+            hh[i] = __float2half_rn(sv);
+            h8 += __half2float(hh[i]);
+            if (SPLIT) {
+                hl[i] = __float2half_rn(sv - __half2float(hh[i]));
+                h8 += __half2float(hl[i]);
+            }
+        }
         if (c < chunks) {
-            float f[8];
-            if (f32_in) {
-                const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
-                const float4 a = x4[2 * c], b = x4[2 * c + 1];
-                f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
-            } else {
-                const uint4 v = reinterpret_cast<const uint4 *>(xs)[c];
-                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    f[2 * i] = __uint_as_float(wv[i] << 16);
-                    f[2 * i + 1] = __uint_as_float(wv[i] & 0xffff0000u);
-                }
-            }
-            __half hh[8], hl[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                s8 += f[i];
-                const float sv = f[i] * xscale;
-                hh[i] = __float2half_rn(sv);
-                h8 += __half2float(hh[i]);
-                if (SPLIT) {
-                    hl[i] = __float2half_rn(sv - __half2float(hh[i]));
-                    h8 += __half2float(hl[i]);
-                }
-            }
             reinterpret_cast<uint4 *>(xs)[c] = *reinterpret_cast<uint4 *>(hh);
             if (SPLIT) reinterpret_cast<uint4 *>(xlo)[c] = *reinterpret_cast<uint4 *>(hl);
         }
@@ -403,6 +418,7 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) 
         }
     }
     named_bar_sync(1, kConsumerThreads);
+    if (tid == 0 && p.trace) trace_max(&p.trace->compute);
 
     // Main loop: no block-wide barrier from here on.
     const uint32_t g = lane >> 2, t = lane & 3u;
@@ -632,6 +648,7 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     if (a.epilogue == kEpiSwiGlu && !m->pair_halves) return STARK_B200_INVALID_ARGUMENT;
     if (a.io_type == STARK_B200_F32 && (a.prologue != kProPlain || a.epilogue != kEpiStore))
         return STARK_B200_UNSUPPORTED;
+    if (m->columns > (uint32_t)kMaxRounds * kConsumerThreads * 8u) return STARK_B200_UNSUPPORTED;
 
     QmvParams p{};
     p.w = m->data;
@@ -656,6 +673,7 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     p.partial_max = a.partial_max;
     p.partial_index = a.partial_index;
     p.error_word = a.error_word;
+    p.trace = a.trace;
 
     const bool split = a.io_type == STARK_B200_F32;
     const bool fold = tuning().fold;
@@ -663,9 +681,10 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     // dependent launch CTAs of the next kernel join them and prefetch while this one drains.
     const uint32_t budget = tuning().smem_budget_kb * 1024u;
     uint32_t stages = 8;
-    while (stages > 2 && smem_layout(stages, p.stage_capacity, m->columns, split).total > budget) --stages;
+    const bool norm = a.prologue == kProRmsNorm;
+    while (stages > 2 && smem_layout(stages, p.stage_capacity, m->columns, split, norm).total > budget) --stages;
     p.num_stages = stages;
-    const uint32_t smem = smem_layout(stages, p.stage_capacity, m->columns, split).total;
+    const uint32_t smem = smem_layout(stages, p.stage_capacity, m->columns, split, norm).total;
     if (smem > 220u * 1024u) return STARK_B200_UNSUPPORTED;
 
     const uint32_t units = p.row_tiles / p.unit_tiles;

@@ -70,6 +70,7 @@ struct QmvArgs {
     float *partial_max;       // kEpiLogits: [grid] per-CTA maxima
     uint32_t *partial_index;  // kEpiLogits: [grid] per-CTA first index of the maximum
     uint32_t *error_word;     // device word, OR-ed with kErr* bits
+    TraceSlot *trace;         // optional timeline slot of this launch
     bool pdl;                 // launch with programmatic stream serialization
     uint32_t *out_grid;       // optional: number of CTAs launched
 };

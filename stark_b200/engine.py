@@ -131,6 +131,19 @@ class DenseModel:
         check(_lib.load().stark_b200_get_info(self._h, C.byref(i)), "get_info")
         return i
 
+    def read_trace(self) -> np.ndarray:
+        """Timeline of the launches since the last call, ``uint64[launches_per_step, 4]`` (ns)."""
+        n = self.info().launches_per_step
+        out = np.empty((n, 4), np.uint64)
+        check(_lib.load().stark_b200_read_trace(self._h, out.ctypes.data, out.size), "read_trace")
+        return out
+
+    def stream(self) -> int:
+        """The cudaStream_t the model issues its work on (an integer handle)."""
+        p = C.c_void_p()
+        check(_lib.load().stark_b200_model_stream(self._h, C.byref(p)), "model_stream")
+        return p.value or 0
+
     @property
     def position(self) -> int:
         return int(self.info().position)
