@@ -197,6 +197,30 @@ stark_b200_status stark_b200_op_attention_decode(const void *qkv, void *keys, vo
                                                  const float *q_norm, const float *k_norm,
                                                  const stark_b200_attention_desc *desc);
 
+/* The same decode attention for callers that must not allocate device memory: a worker that fixed
+ * its memory budget when it admitted the request, or a decode loop that cannot take the
+ * device-wide stall of cudaMalloc / cudaFree.  This entry point has no counterpart in the
+ * reference.  It calls no allocator: the split-KV partial results and arrival counters live in a
+ * 1 MiB array inside the library image (held by every GPU that loads the library until the
+ * process exits).
+ *   - All pointers are DEVICE pointers.  key_pages / value_pages use the library's page layout:
+ *     element ((page * kv_heads + head) * 64 + row_in_page) * 128 + dim, bf16; block_table[b] is
+ *     the page of positions 64 b .. 64 b + 63 and must cover position / 64.  rope_cos / rope_sin
+ *     are f32 tables [positions, 128] (both halves filled) or both NULL; q_norm / k_norm may be NULL.
+ *   - desc->position rows are read, row desc->position is appended.  desc->capacity and
+ *     desc->rope_theta are ignored.
+ *   - Limit: q_heads * splits * 520 bytes <= 1 MiB - 1 KiB and kv_heads <= 64 (splits defaults
+ *     to 8); beyond that the call returns STARK_B200_CONTEXT_LIMIT and launches nothing.
+ *   - The first call on each device resolves the address of the array (that device must be
+ *     current); make that first call before any stream capture begins.
+ *   - All calls on a device share the array.  Each call clears the counters it needs, but two calls
+ *     whose kernels overlap on the GPU (different streams) race on it: serialise them. */
+stark_b200_status stark_b200_op_attention_decode_static(const void *qkv, void *key_pages, void *value_pages,
+                                                        const int32_t *block_table, void *out,
+                                                        const float *q_norm, const float *k_norm,
+                                                        const float *rope_cos, const float *rope_sin,
+                                                        const stark_b200_attention_desc *desc, void *stream);
+
 /* ------------------------------------------------------------------------------------------
  * Model surface: the FFI image of hybrid::Model / LanguageModel for a Qwen3-shaped dense decoder
  * (crates/stark-engine/src/engine/hybrid/mod.rs:347-1428,

@@ -95,6 +95,8 @@ def load() -> C.CDLL:
         "stark_b200_op_log_softmax": (u32, [vp, vp, u32, u32, vp]),
         "stark_b200_op_moe_route": (u32, [vp, vp, vp, u32, u32, u32, u32, u32, u32, vp]),
         "stark_b200_op_attention_decode": (u32, [vp, vp, vp, vp, vp, vp, C.POINTER(AttentionDesc)]),
+        "stark_b200_op_attention_decode_static": (u32, [vp, vp, vp, vp, vp, vp, vp, vp, vp,
+                                                        C.POINTER(AttentionDesc), vp]),
         "stark_b200_model_create": (u32, [C.POINTER(DenseConfig), C.POINTER(vp)]),
         "stark_b200_model_set_affine": (u32, [vp, u32, u32, vp, vp, vp, C.POINTER(AffineDesc)]),
         "stark_b200_model_set_vector": (u32, [vp, u32, u32, vp, u32]),
