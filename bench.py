@@ -30,6 +30,8 @@ WORKLOADS = {
     "qwen3-8b": dict(cfg="qwen3-8b", prompt=4096, context=4096 + 1024),
     "qwen3-0.6b": dict(cfg="qwen3-0.6b", prompt=512, context=512 + 512),
     "small": dict(cfg="small", prompt=96, context=512),
+    # a single quantized matvec (BASELINE config 1 by default): micro-benchmark / profiling target
+    "matvec": dict(cfg=None, prompt=0, context=0),
 }
 BYTES_PER_WEIGHT = 0.5625  # 4-bit codes + bf16 scale and bias per 64 columns
 
@@ -115,6 +117,61 @@ def cpu_sample(cfg: dict, weights: dict, prompt: np.ndarray, prompt_rows: int, s
             "sample": f"{steps} greedy decode steps after a {prompt_rows}-token prompt, same weights"}
 
 
+def run_matvec(args) -> None:
+    """One y = W x per step over a pool of matrices larger than L2, recorded as a CUDA graph."""
+    import torch
+
+    from stark_b200.ops import Graph, QMatrix, take_device_error
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    rows, cols = args.rows, args.columns
+    w = S.matvec_case(seed=args.seed, rows=rows, columns=cols)
+    per = rows * cols * BYTES_PER_WEIGHT + 2 * (rows + cols)
+    pool_n = min(40, max(2, int(300e6 // per) + 1))
+    pool = [QMatrix.from_affine(w["codes"], w["scales"], w["biases"], rows, cols) for _ in range(pool_n)]
+    x = torch.from_numpy(w["x"].view(np.int16)).cuda()
+    y = torch.empty(rows, dtype=torch.int16, device="cuda")
+    stream = torch.cuda.Stream()
+    steps, warmup = args.steps, max(args.warmup, 3)
+    with torch.cuda.stream(stream):
+        st = stream.cuda_stream
+        pool[0].matvec_device(x.data_ptr(), y.data_ptr(), stream=st)
+        stream.synchronize()
+        with Graph(st) as graph:
+            for q in pool:
+                q.matvec_device(x.data_ptr(), y.data_ptr(), stream=st)
+        reps = max(1, (steps + pool_n - 1) // pool_n)
+        for _ in range(max(1, (warmup + pool_n - 1) // pool_n)):
+            graph.launch()
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(reps):
+            graph.launch()
+        e1.record(stream)
+        stream.synchronize()
+    n = reps * pool_n
+    us = e0.elapsed_time(e1) * 1e3 / n
+    assert take_device_error() == 0
+    peak, kind = peaks()
+    # end to end: host vectors in and out through the operator call, every step
+    t0 = time.perf_counter()
+    for i in range(min(n, 64)):
+        pool[i % pool_n].matvec(w["x"])
+    e2e = (time.perf_counter() - t0) / min(n, 64)
+    graph.destroy()
+    print(json.dumps({
+        "metric": "4-bit matvec GB/s", "value": per / us / 1e3, "unit": "GB/s", "n_gpus": 1, "steps": n,
+        "warmup": warmup, "ms_per_step": us / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"matvec {rows}x{cols} 4-bit MLX-affine g64, batch 1",
+                   "l2": f"pool of {pool_n} matrices ({pool_n * per / 1e6:.0f} MB) cycled, larger than L2"},
+        "e2e": {"value": per / e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 2 * cols, "d2h_bytes_per_step": 2 * rows},
+        "gpu_launches": n,
+        "roofline": {"bound": "hbm", "achieved": per / us / 1e3, "peak": peak, "unit": "GB/s",
+                     "frac": per / us / 1e3 / peak, "traffic": None, "peak_kind": kind},
+    }))
+
+
 def run_reference(args, wl, cfg) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -157,8 +214,13 @@ def main() -> None:
     ap.add_argument("--workload", default="qwen3-8b", choices=sorted(WORKLOADS))
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--rows", type=int, default=4096, help="matvec workload only")
+    ap.add_argument("--columns", type=int, default=4096, help="matvec workload only")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
+    if args.workload == "matvec":
+        run_matvec(args)
+        return
     cfg = S.CONFIGS[wl["cfg"]]
     if args.impl == "reference":
         run_reference(args, wl, cfg)

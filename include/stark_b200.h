@@ -273,6 +273,8 @@ typedef struct stark_b200_info {
     uint64_t weight_bytes; /* device bytes of all quantized matrices */
     uint64_t kv_bytes_per_token;
     uint64_t launches_issued; /* kernels of this library launched on this handle so far */
+    uint32_t trace_slots;     /* entries stark_b200_read_trace returns (0: tracing is off) */
+    uint32_t persistent;      /* 1: one persistent kernel per token, 0: one kernel per operator */
 } stark_b200_info;
 
 #define STARK_B200_CAP_FULL_F32_READOUT UINT64_C(1)
@@ -316,7 +318,8 @@ stark_b200_status stark_b200_get_info(stark_b200_model *model, stark_b200_info *
  * launches_per_step kernels, four device-clock values in ns {first CTA entered, wait on the previous
  * kernel returned, last prologue done, last CTA left}.  Only available when the library was started
  * with STARK_B200_TRACE=1 (UNSUPPORTED otherwise); the analogue of the reference's aggregate
- * profiler (crates/stark-engine/src/engine/hybrid/profile.rs:1-89).  count = 4 * launches_per_step. */
+ * profiler (crates/stark-engine/src/engine/hybrid/profile.rs:1-89).  count = 4 * Info.trace_slots
+ * (one slot per launch, or per operator of the persistent kernel). */
 stark_b200_status stark_b200_read_trace(stark_b200_model *model, uint64_t *dst, size_t count);
 /* The CUDA stream (cudaStream_t) the model's work is issued on, for callers that time it with
  * their own events. */

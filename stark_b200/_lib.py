@@ -50,7 +50,8 @@ class Info(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("abi_version", C.c_uint32), ("vocab_size", C.c_uint32),
                 ("prefill_chunk_tokens", C.c_uint32), ("context_tokens", C.c_uint64), ("position", C.c_uint64),
                 ("capabilities", C.c_uint64), ("fenced", C.c_uint32), ("launches_per_step", C.c_uint32),
-                ("weight_bytes", C.c_uint64), ("kv_bytes_per_token", C.c_uint64), ("launches_issued", C.c_uint64)]
+                ("weight_bytes", C.c_uint64), ("kv_bytes_per_token", C.c_uint64), ("launches_issued", C.c_uint64),
+                ("trace_slots", C.c_uint32), ("persistent", C.c_uint32)]
 
 
 MAT_EMBED, MAT_LM_HEAD, MAT_QKV, MAT_O, MAT_UPGATE, MAT_DOWN = range(6)

@@ -414,6 +414,8 @@ stark_b200_status stark_b200_get_info(stark_b200_model *model, stark_b200_info *
     info->weight_bytes = wb;
     info->kv_bytes_per_token = (uint64_t)m->cfg.layers * 2u * m->cfg.kv_heads * kHeadDim * 2u;
     info->launches_issued = m->launches_issued;
+    info->trace_slots = m->trace ? m->trace_slots : 0u;
+    info->persistent = m->use_mega ? 1u : 0u;
     return STARK_B200_OK;
 }
 

@@ -13,6 +13,7 @@
 //   h      = bf16(bf16(W_down act) + h)
 // then logits = W_head rmsnorm(h) with the greedy read-out fused into the matvec epilogue.
 #include "model.cuh"
+#include "mega.cuh"
 
 #include <cmath>
 #include <cstring>
@@ -65,6 +66,10 @@ Model::~Model() {
     cudaFree(pending);
     cudaFree(generated);
     cudaFree(trace);
+    cudaFree(mega_ops);
+    cudaFree(mega_ingest_ops);
+    cudaFree(mega_done);
+    cudaFree(mega_scratch);
     cudaFree(h);
     cudaFree(qkv);
     cudaFree(attn);
@@ -103,6 +108,9 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     for (auto &L : m->layers) {
         if ((st = dmalloc(&L.kv.keys, m->num_blocks * page_elems)) != STARK_B200_OK) return fail(st);
         if ((st = dmalloc(&L.kv.values, m->num_blocks * page_elems)) != STARK_B200_OK) return fail(st);
+        if (cudaMemset(L.kv.keys, 0, m->num_blocks * page_elems * 2) != cudaSuccess ||
+            cudaMemset(L.kv.values, 0, m->num_blocks * page_elems * 2) != cudaSuccess)
+            return fail(STARK_B200_DEVICE_FAILURE);
     }
     std::vector<int32_t> table(m->num_blocks);
     for (uint32_t i = 0; i < m->num_blocks; ++i) table[i] = (int32_t)i;
@@ -330,6 +338,149 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
     return STARK_B200_OK;
 }
 
+// Persistent-kernel path: builds the operator lists (full token / cache-only prompt row).
+static stark_b200_status build_mega(Model *m) {
+    const auto &c = m->cfg;
+    DeviceContext *ctx = device_context();
+    if (!ctx) return STARK_B200_DEVICE_FAILURE;
+    int sms = 0;
+    SB_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, m->device));
+    m->mega_grid = (uint32_t)sms;
+    m->mega_splits = std::max(1u, std::min<uint32_t>(kMaxAttnSplits, m->mega_grid / c.kv_heads));
+    std::vector<MegaOp> ops;
+    uint32_t max_columns = 0, stage_capacity = 0;
+    auto gemv = [&](const QMatrix *w, const uint16_t *x, uint16_t *y, uint32_t pro, const float *nw, uint32_t epi,
+                    const uint16_t *resid, uint32_t dep) {
+        MegaOp o{};
+        o.type = kOpGemv;
+        o.dep = dep;
+        o.participants = m->mega_grid;
+        o.w = w->data;
+        o.x = x;
+        o.y = y;
+        o.norm_weight = nw;
+        o.resid = resid;
+        o.rows = w->rows;
+        o.row_tiles = w->row_tiles;
+        o.groups = w->groups;
+        bool pred = false;
+        qmv_pick_stage(w->groups, &o.stage_records, &o.rpw, &pred);
+        // the persistent kernel has 16 consumer warps: records per warp and raggedness follow from that
+        o.rpw = (o.stage_records + 15u) / 16u;
+        o.pred = (o.stage_records % 16u != 0u) ? 1u : 0u;
+        o.stages_per_tile = w->groups / o.stage_records;
+        o.pair_halves = w->pair_halves;
+        o.unit_tiles = epi == kEpiSwiGlu ? 2u : 1u;
+        o.prologue = pro;
+        o.epilogue = epi;
+        max_columns = std::max(max_columns, w->columns);
+        stage_capacity = std::max(stage_capacity, (o.stage_records * kA4RecordBytes + 127u) & ~127u);
+        ops.push_back(o);
+        return (uint32_t)ops.size() - 1u;
+    };
+    MegaOp e{};
+    e.type = kOpEmbed;
+    e.dep = 0xffffffffu;
+    e.participants = 1;
+    ops.push_back(e);
+    uint32_t last = 0;
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        auto &L = m->layers[l];
+        const uint32_t q = gemv(L.qkv, m->h, m->qkv, kProRmsNorm, L.attn_norm, kEpiStore, nullptr, last);
+        MegaOp ap{};
+        ap.type = kOpAttnPartial;
+        ap.dep = q;
+        ap.participants = c.kv_heads * m->mega_splits;
+        ap.keys = L.kv.keys;
+        ap.values = L.kv.values;
+        ap.q_norm = L.q_norm;
+        ap.k_norm = L.k_norm;
+        ops.push_back(ap);
+        MegaOp am{};
+        am.type = kOpAttnMerge;
+        am.dep = (uint32_t)ops.size() - 1u;
+        am.participants = c.kv_heads;
+        ops.push_back(am);
+        const uint32_t o = gemv(L.o, m->attn, m->h, kProPlain, nullptr, kEpiResidual, m->h, (uint32_t)ops.size() - 1u);
+        const uint32_t u = gemv(L.upgate, m->h, m->act, kProRmsNorm, L.mlp_norm, kEpiSwiGlu, nullptr, o);
+        last = gemv(L.down, m->act, m->h, kProPlain, nullptr, kEpiResidual, m->h, u);
+    }
+    std::vector<MegaOp> ingest = ops;
+    const uint32_t head = gemv(m->lm_head, m->h, m->logits, kProRmsNorm, m->final_norm, kEpiLogits, nullptr, last);
+    MegaOp fin{};
+    fin.type = kOpFinalize;
+    fin.dep = head;
+    fin.participants = 1;
+    ops.push_back(fin);
+    MegaOp adv{};
+    adv.type = kOpIngestAdvance;
+    adv.dep = last;
+    adv.participants = 1;
+    ingest.push_back(adv);
+    if (c.kv_heads * m->mega_splits > m->mega_grid || c.kv_heads > m->mega_grid) return STARK_B200_UNSUPPORTED;
+
+    stark_b200_status st;
+    if ((st = dmalloc(&m->mega_ops, ops.size())) != STARK_B200_OK) return st;
+    if ((st = dmalloc(&m->mega_ingest_ops, ingest.size())) != STARK_B200_OK) return st;
+    if ((st = dmalloc(&m->mega_done, ops.size() + 1)) != STARK_B200_OK) return st;
+    if ((st = dmalloc(&m->mega_scratch, attention_scratch_floats(c.q_heads, c.kv_heads, m->mega_splits))) != STARK_B200_OK)
+        return st;
+    SB_CUDA(cudaMemcpy(m->mega_ops, ops.data(), ops.size() * sizeof(MegaOp), cudaMemcpyHostToDevice));
+    SB_CUDA(cudaMemcpy(m->mega_ingest_ops, ingest.data(), ingest.size() * sizeof(MegaOp), cudaMemcpyHostToDevice));
+    SB_CUDA(cudaMemset(m->mega_done, 0, (ops.size() + 1) * sizeof(unsigned long long)));
+    m->mega_num_ops = (uint32_t)ops.size();
+    m->mega_num_ingest_ops = (uint32_t)ingest.size();
+
+    MegaParams p{};
+    p.stage_capacity = stage_capacity;
+    p.max_columns = max_columns;
+    uint32_t stages = 8;
+    while (stages > 2 && mega_smem_bytes(stages, stage_capacity, max_columns) > 225u * 1024u) --stages;
+    p.num_stages = stages;
+    m->mega_smem = mega_smem_bytes(stages, stage_capacity, max_columns);
+    if (m->mega_smem > 227u * 1024u) return STARK_B200_UNSUPPORTED;
+    p.state = m->state;
+    p.done = m->mega_done;
+    p.embed = m->embed->data;
+    p.embed_rows = m->embed->rows;
+    p.embed_columns = m->embed->columns;
+    p.h = m->h;
+    p.qkv = m->qkv;
+    p.attn = m->attn;
+    p.block_table = m->block_table;
+    p.rope_cos = m->rope_cos;
+    p.rope_sin = m->rope_sin;
+    p.attn_scratch = m->mega_scratch;
+    p.eps = c.eps;
+    p.attn_scale = 1.0f / sqrtf((float)kHeadDim);
+    p.q_heads = c.q_heads;
+    p.kv_heads = c.kv_heads;
+    p.attn_splits = m->mega_splits;
+    p.partial_max = m->partial_max;
+    p.partial_index = m->partial_index;
+    p.generated = m->generated;
+    p.pending = m->pending;
+    p.error_word = ctx->error_word;
+    p.trace = m->trace;
+    m->mega_full = p;
+    m->mega_full.ops = m->mega_ops;
+    m->mega_full.num_ops = m->mega_num_ops;
+    m->mega_ingest = p;
+    m->mega_ingest.ops = m->mega_ingest_ops;
+    m->mega_ingest.num_ops = m->mega_num_ingest_ops;
+    return STARK_B200_OK;
+}
+
+// One token on the model's stream: the recorded launch sequence, or the persistent kernel.
+static stark_b200_status launch_token(Model *m, bool full) {
+    if (m->use_mega) {
+        SB_CUDA(cudaMemsetAsync(m->mega_done, 0, (m->mega_num_ops + 1u) * sizeof(unsigned long long), m->stream));
+        return mega_launch(full ? m->mega_full : m->mega_ingest, m->mega_grid, m->mega_smem, m->stream);
+    }
+    SB_CUDA(cudaGraphLaunch(full ? m->step_graph : m->ingest_graph, m->stream));
+    return STARK_B200_OK;
+}
+
 static stark_b200_status capture(Model *m, bool full, cudaGraphExec_t *exec, uint32_t *launches) {
     SB_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
     stark_b200_status st = issue_token(m, full, launches);
@@ -360,6 +511,18 @@ stark_b200_status model_finalize(Model *m) {
     SB_CUDA(cudaStreamSynchronize(m->stream));
     if ((st = capture(m, true, &m->step_graph, &m->step_launches)) != STARK_B200_OK) return st;
     if ((st = capture(m, false, &m->ingest_graph, &m->ingest_launches)) != STARK_B200_OK) return st;
+    if (const char *e = getenv("STARK_B200_MEGA")) m->use_mega = e[0] == '1';
+    if (m->use_mega) {
+        if (m->trace) {  // one slot per operator instead of one per launch
+            cudaFree(m->trace);
+            m->trace = nullptr;
+            m->trace_slots = 4u + 6u * m->cfg.layers;
+            if ((st = dmalloc(&m->trace, m->trace_slots)) != STARK_B200_OK) return st;
+        }
+        if ((st = build_mega(m)) != STARK_B200_OK) return st;
+        m->step_launches = 1;
+        m->ingest_launches = 1;
+    }
     m->finalized = true;
     return model_reset(m);
 }
@@ -367,6 +530,8 @@ stark_b200_status model_finalize(Model *m) {
 stark_b200_status model_reset(Model *m) {
     SB_CUDA(cudaMemsetAsync(m->state, 0, sizeof(StepState), m->stream));
     SB_CUDA(cudaMemsetAsync(m->attn_counters, 0, m->cfg.kv_heads * 4, m->stream));
+    if (m->mega_done)
+        SB_CUDA(cudaMemsetAsync(m->mega_done, 0, (m->mega_num_ops + 1u) * sizeof(unsigned long long), m->stream));
     SB_CUDA(cudaStreamSynchronize(m->stream));
     m->position = 0;
     m->has_logits = false;
@@ -408,9 +573,13 @@ stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count) {
             model_reset(m);
             return STARK_B200_CANCELLED;
         }
-        SB_CUDA(cudaGraphLaunch(m->ingest_graph, m->stream));
+        stark_b200_status ls = launch_token(m, false);
+        if (ls != STARK_B200_OK) return ls;
     }
-    SB_CUDA(cudaGraphLaunch(m->step_graph, m->stream));
+    {
+        stark_b200_status ls = launch_token(m, true);
+        if (ls != STARK_B200_OK) return ls;
+    }
     m->position += count;
     m->has_logits = true;
     m->launches_issued += (count - 1) * m->ingest_launches + m->step_launches;
@@ -424,7 +593,10 @@ stark_b200_status model_step(Model *m, uint32_t token, bool chained) {
         if (token >= m->cfg.vocab) return STARK_B200_INVALID_ARGUMENT;
         SB_CUDA(cudaMemcpyAsync(&m->state->token, &token, 4, cudaMemcpyHostToDevice, m->stream));
     }
-    SB_CUDA(cudaGraphLaunch(m->step_graph, m->stream));
+    {
+        stark_b200_status ls = launch_token(m, true);
+        if (ls != STARK_B200_OK) return ls;
+    }
     m->position += 1;
     m->has_logits = true;
     m->launches_issued += m->step_launches;
@@ -492,7 +664,9 @@ stark_b200_status model_generate_greedy(Model *m, uint32_t steps, uint32_t *out_
     const uint32_t window[2] = {0u, steps};
     cudaError_t e = cudaMemcpyAsync(&pinned[0], &m->state->next_token, 4, cudaMemcpyDeviceToHost, m->stream);
     if (e == cudaSuccess) e = cudaMemcpyAsync(&m->state->gen_cursor, window, 8, cudaMemcpyHostToDevice, m->stream);
-    for (uint32_t i = 0; i < steps && e == cudaSuccess; ++i) e = cudaGraphLaunch(m->step_graph, m->stream);
+    for (uint32_t i = 0; i < steps && e == cudaSuccess; ++i) {
+        if (launch_token(m, true) != STARK_B200_OK) e = last_cuda_error() != cudaSuccess ? last_cuda_error() : cudaErrorUnknown;
+    }
     if (e == cudaSuccess && steps)
         e = cudaMemcpyAsync(&pinned[1], m->generated, (size_t)steps * 4u, cudaMemcpyDeviceToHost, m->stream);
     const uint32_t closed[2] = {0u, 0u};

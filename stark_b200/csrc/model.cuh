@@ -3,6 +3,7 @@
 #include <vector>
 
 #include "context.cuh"
+#include "mega.cuh"
 #include "ops.cuh"
 #include "qmv.cuh"
 
@@ -36,6 +37,13 @@ struct Model {
     uint32_t *partial_index = nullptr;
     uint32_t attn_splits = 1;
     cudaGraphExec_t step_graph = nullptr, ingest_graph = nullptr;
+    // persistent-kernel path (STARK_B200_MEGA=1)
+    bool use_mega = false;
+    MegaOp *mega_ops = nullptr, *mega_ingest_ops = nullptr;
+    uint32_t mega_num_ops = 0, mega_num_ingest_ops = 0, mega_grid = 0, mega_smem = 0, mega_splits = 1;
+    unsigned long long *mega_done = nullptr;
+    float *mega_scratch = nullptr;
+    MegaParams mega_full{}, mega_ingest{};
     uint32_t step_launches = 0, ingest_launches = 0;
     StepState *host_state = nullptr;    // pinned
     uint16_t *host_logits = nullptr;    // pinned

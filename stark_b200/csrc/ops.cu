@@ -2,6 +2,7 @@
 // written for few launches and few dependent phases rather than for throughput; the only one that
 // moves real bytes is the decode attention, which streams the KV pages of one head per CTA row.
 #include "ops.cuh"
+#include "device_attention.cuh"
 
 #include <algorithm>
 
@@ -9,346 +10,35 @@ namespace sb {
 
 namespace {
 
-constexpr int kAttnThreads = 256;
-constexpr int kAttnWarps = kAttnThreads / 32;
-constexpr int kMaxGqa = 8;
-constexpr uint32_t kTileRowBytes = kHeadDim * 2u + 16u;  // 272: padded so that row-strided 16 B reads are conflict-free
-constexpr uint32_t kTileBytes = kPageTokens * kTileRowBytes;
-constexpr uint32_t kAttnSmemBytes = 4u * kTileBytes;  // K and V, double buffered
-
-struct AttnParams {
-    const uint16_t *qkv;
-    uint16_t *out;
-    uint16_t *keys;
-    uint16_t *values;
-    const int32_t *block_table;
-    const float *q_norm;
-    const float *k_norm;
-    const float *rope_cos;
-    const float *rope_sin;
-    const StepState *state;
-    float eps;
-    float scale;
-    uint32_t q_heads, kv_heads, gqa, splits;
-    float *scratch;
-    uint32_t *counters;
-    TraceSlot *trace;
-};
-
-__device__ inline void cp_async16(void *smem_dst, const void *gmem_src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
-}
-__device__ inline void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ inline void cp_async_wait() {
-    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
-
-// Per-head RMS norm + RoPE of 128-wide heads, two heads at a time (threads 0..127 and 128..255).
-//   qkv_norm.rs:44-108: f32 sum of squares, rms = 1/sqrt(mean + eps), bf16(normalized) * bf16(scale) -> bf16
-//   attention_prepare.rs:7-43: half-split pairing, x*cos + (+-pair)*sin with separately rounded products
-// `active` may differ between the two halves; every thread of the CTA must call it.
-__device__ inline float head_norm_rope(float v, bool active, bool has_norm, float norm_w, bool has_rope,
-                                       float cos_d, float sin_d, float eps, float *exch /* [256] */,
-                                       float *wsum /* [kAttnWarps] */) {
-    const int d = threadIdx.x & 127, half = threadIdx.x >> 7;
-    if (has_norm) {
-        const float sq = warp_sum(active ? v * v : 0.0f);
-        if ((threadIdx.x & 31) == 0) wsum[threadIdx.x >> 5] = sq;
-        __syncthreads();
-        const float total = wsum[half * 4] + wsum[half * 4 + 1] + wsum[half * 4 + 2] + wsum[half * 4 + 3];
-        const float rms = 1.0f / sqrtf(total / (float)kHeadDim + eps);
-        v = bf16_round(bf16_round(v * rms) * bf16_round(norm_w));
-        __syncthreads();
-    }
-    if (has_rope) {
-        exch[threadIdx.x] = v;
-        __syncthreads();
-        const float paired = exch[half * 128 + (d < 64 ? d + 64 : d - 64)];
-        const float signed_paired = d < 64 ? -paired : paired;
-        v = bf16_round(__fadd_rn(__fmul_rn(v, cos_d), __fmul_rn(signed_paired, sin_d)));
-        __syncthreads();
-    }
-    return v;
-}
-
-// One CTA = (split, KV head): streams its share of the head's KV pages through shared memory
-// (16 KB K tile + 16 KB V tile per page, cp.async double buffered), keeps an
-// online softmax for the G query heads that share the KV head, and publishes a partial
-// (o, max, sum); the last split of a head to finish merges the partials.
-__global__ void __launch_bounds__(kAttnThreads, 2) attention_decode_kernel(const AttnParams p) {
-    extern __shared__ __align__(128) uint8_t tiles[];  // [2][K, V][64][272]
-    __shared__ __align__(16) float q_s[kMaxGqa][kHeadDim];  // q after norm + RoPE (bf16 values), f32
-    __shared__ float p_s[kMaxGqa][kPageTokens];
-    __shared__ float exch[kAttnThreads];
-    __shared__ float wred[2][kMaxGqa][kAttnWarps];
-    __shared__ uint16_t knew[kHeadDim], vnew[kHeadDim];
+// One CTA = (split, KV head), four warps: the split's partial, then the last split of the head to
+// arrive merges all of them (see device_attention.cuh).
+__global__ void __launch_bounds__(kAttnThreads, 3) attention_decode_kernel(const AttnParams p) {
+    extern __shared__ __align__(128) uint8_t attn_smem[];
     __shared__ uint32_t is_last;
-
     pdl_launch_dependents();
-
-    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    const uint32_t split = blockIdx.x, h = blockIdx.y, G = p.gqa;
-    const uint32_t d128 = tid & 127u, half = tid >> 7;
+    const uint32_t tid = threadIdx.x;
+    const uint32_t split = blockIdx.x, h = blockIdx.y;
     if (tid == 0 && p.trace) trace_min(&p.trace->start);
-    // Constants first (they do not depend on the previous kernel).
-    const float qn_w = p.q_norm ? p.q_norm[d128] : 1.0f;
-    const float kn_w = p.k_norm ? p.k_norm[d128] : 1.0f;
-
     // Every kernel of the sequence launches its dependents at once, so several later kernels can be
     // resident and waiting here while the writer of `position` (the end of the previous token) is
     // still running: the position, and therefore the page range, is read only after the wait.
     pdl_wait();
     if (tid == 0 && p.trace) trace_min(&p.trace->ready);
-    // All loads that depend only on the previous kernel are issued together (one memory round trip):
-    // the position, this group's query rows and this head's new key / value row.
     const uint32_t pos = p.state->position;
-    float qv[kMaxGqa / 2];
-#pragma unroll
-    for (int i = 0; i < kMaxGqa / 2; ++i) {
-        const uint32_t g = 2u * i + half;
-        qv[i] = g < G ? bf16_bits_to_f32(p.qkv[(size_t)(h * G + g) * kHeadDim + d128]) : 0.0f;
-    }
-    const float k_in = bf16_bits_to_f32(p.qkv[(size_t)(p.q_heads + h) * kHeadDim + d128]);
-    const uint16_t v_in = p.qkv[(size_t)(p.q_heads + p.kv_heads + h) * kHeadDim + d128];
-
-    const uint32_t seq_len = pos + 1u;
-    const uint32_t nblocks = (seq_len + kPageTokens - 1u) / kPageTokens;
-    const uint32_t b0 = (uint32_t)(((uint64_t)split * nblocks) / p.splits);
-    const uint32_t b1 = (uint32_t)(((uint64_t)(split + 1u) * nblocks) / p.splits);
-    const uint32_t new_block = pos / kPageTokens;
-    const bool owner = new_block >= b0 && new_block < b1;
-    const uint32_t ntiles = b1 - b0;
-    // second round trip: RoPE coefficients of this position and the page numbers
-    const float cos_d = p.rope_cos ? p.rope_cos[(size_t)pos * kHeadDim + d128] : 1.0f;
-    const float sin_d = p.rope_sin ? p.rope_sin[(size_t)pos * kHeadDim + d128] : 0.0f;
-
-    auto issue_tile = [&](uint32_t t) {
-        const uint32_t buf = t & 1u;
-        const size_t page = ((size_t)p.block_table[b0 + t] * p.kv_heads + h) * kPageTokens * kHeadDim;
-        const uint8_t *ksrc = reinterpret_cast<const uint8_t *>(p.keys + page);
-        const uint8_t *vsrc = reinterpret_cast<const uint8_t *>(p.values + page);
-        uint8_t *kd = tiles + (size_t)(buf * 2u) * kTileBytes, *vd = kd + kTileBytes;
-        // 64 rows x 16 chunks of 16 B per tile; thread -> (row, chunk)
-#pragma unroll
-        for (uint32_t i = 0; i < 4; ++i) {
-            const uint32_t idx = tid + i * kAttnThreads, row = idx >> 4, ch = idx & 15u;
-            cp_async16(kd + row * kTileRowBytes + ch * 16u, ksrc + row * 256u + ch * 16u);
-            cp_async16(vd + row * kTileRowBytes + ch * 16u, vsrc + row * 256u + ch * 16u);
-        }
-        cp_async_commit();
-    };
-    if (ntiles > 0) issue_tile(0);
-
-    // Queries of this KV head's group, two heads per pass: norm + RoPE (values are bf16-exact).
-#pragma unroll
-    for (int i = 0; i < kMaxGqa / 2; ++i) {
-        if (2u * i < G) {
-            const uint32_t g = 2u * i + half;
-            const bool active = g < G;
-            const float v = head_norm_rope(qv[i], active, p.q_norm != nullptr, qn_w, p.rope_cos != nullptr, cos_d,
-                                           sin_d, p.eps, exch, wred[0][0]);
-            if (active) q_s[g][d128] = v;
-        }
-    }
-    // The split that owns the new position appends its key and value rows to the cache.
-    if (owner) {
-        const bool active = tid < 128;
-        const float kv = head_norm_rope(active ? k_in : 0.0f, active, p.k_norm != nullptr, kn_w,
-                                        p.rope_cos != nullptr, cos_d, sin_d, p.eps, exch, wred[0][0]);
-        if (active) {
-            const size_t row = ((size_t)p.block_table[new_block] * p.kv_heads + h) * kPageTokens + (pos % kPageTokens);
-            const uint16_t kb = f32_to_bf16_bits(kv);
-            p.keys[row * kHeadDim + tid] = kb;
-            p.values[row * kHeadDim + tid] = v_in;
-            knew[tid] = kb;
-            vnew[tid] = v_in;
-        }
-    }
-    __syncthreads();
-
-    if (tid == 0 && p.trace) trace_max(&p.trace->compute);
-    float m_run[kMaxGqa], l_run[kMaxGqa], o_acc[kMaxGqa][2];
-#pragma unroll
-    for (int g = 0; g < kMaxGqa; ++g) {
-        m_run[g] = -INFINITY;
-        l_run[g] = 0.0f;
-        o_acc[g][0] = o_acc[g][1] = 0.0f;
-    }
-    const uint32_t key = tid >> 2, jq = tid & 3u;  // score phase: 4 threads per key, interleaved 16 B chunks
-    const uint32_t dp = tid & 63u, kq = tid >> 6;  // PV phase: dim pair, key residue mod 4
-
-    for (uint32_t t = 0; t < ntiles; ++t) {
-        if (t + 1 < ntiles) {
-            issue_tile(t + 1);
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
-        const uint32_t buf = t & 1u;
-        uint8_t *kt = tiles + (size_t)(buf * 2u) * kTileBytes, *vt = kt + kTileBytes;
-        const uint32_t blk = b0 + t;
-        if (blk == new_block) {
-            // the copy may have raced the append above: patch the new row in shared memory
-            if (tid < 128) {
-                reinterpret_cast<uint16_t *>(kt + (pos % kPageTokens) * kTileRowBytes)[tid] = knew[tid];
-                reinterpret_cast<uint16_t *>(vt + (pos % kPageTokens) * kTileRowBytes)[tid] = vnew[tid];
-            }
-            __syncthreads();
-        }
-        const uint32_t valid = min(kPageTokens, seq_len - blk * kPageTokens);  // keys of this page in range
-
-        // ---- scores ----
-        float s[kMaxGqa];
-#pragma unroll
-        for (int g = 0; g < kMaxGqa; ++g) s[g] = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const uint32_t c = 4u * i + jq;
-            const uint4 kv = *reinterpret_cast<const uint4 *>(kt + key * kTileRowBytes + c * 16u);
-            const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
-            float kf[8];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                kf[2 * e] = __uint_as_float(w[e] << 16);
-                kf[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
-            }
-#pragma unroll
-            for (int g = 0; g < kMaxGqa; ++g) {
-                if (g < (int)G) {
-                    const float4 qa = *reinterpret_cast<const float4 *>(&q_s[g][c * 8u]);
-                    const float4 qb = *reinterpret_cast<const float4 *>(&q_s[g][c * 8u + 4u]);
-                    s[g] += qa.x * kf[0] + qa.y * kf[1] + qa.z * kf[2] + qa.w * kf[3] + qb.x * kf[4] +
-                            qb.y * kf[5] + qb.z * kf[6] + qb.w * kf[7];
-                }
-            }
-        }
-#pragma unroll
-        for (int g = 0; g < kMaxGqa; ++g) {
-            if (g < (int)G) {
-                s[g] += __shfl_xor_sync(0xffffffffu, s[g], 1);
-                s[g] += __shfl_xor_sync(0xffffffffu, s[g], 2);
-                s[g] = key < valid ? s[g] * p.scale : -INFINITY;
-                float wm = s[g];
-                wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, 4));
-                wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, 8));
-                wm = fmaxf(wm, __shfl_xor_sync(0xffffffffu, wm, 16));
-                if (lane == 0) wred[0][g][warp] = wm;
-            }
-        }
-        __syncthreads();
-        float factor[kMaxGqa];
-#pragma unroll
-        for (int g = 0; g < kMaxGqa; ++g) {
-            factor[g] = 1.0f;
-            if (g < (int)G) {
-                float cm = wred[0][g][0];
-#pragma unroll
-                for (int i = 1; i < kAttnWarps; ++i) cm = fmaxf(cm, wred[0][g][i]);
-                const float m_new = fmaxf(m_run[g], cm);
-                factor[g] = m_run[g] == -INFINITY ? 0.0f : expf(m_run[g] - m_new);
-                const float e = key < valid ? expf(s[g] - m_new) : 0.0f;
-                if (jq == 0) p_s[g][key] = e;
-                float ws = jq == 0 ? e : 0.0f;
-                ws = warp_sum(ws);
-                if (lane == 0) wred[1][g][warp] = ws;
-                m_run[g] = m_new;
-            }
-        }
-        __syncthreads();
-#pragma unroll
-        for (int g = 0; g < kMaxGqa; ++g) {
-            if (g < (int)G) {
-                float cs = 0.0f;
-#pragma unroll
-                for (int i = 0; i < kAttnWarps; ++i) cs += wred[1][g][i];
-                l_run[g] = l_run[g] * factor[g] + cs;
-                o_acc[g][0] *= factor[g];
-                o_acc[g][1] *= factor[g];
-            }
-        }
-        // ---- o += P V: thread = (dim pair, key residue) ----
-        for (uint32_t kk = kq; kk < valid; kk += 4) {
-            const uint32_t vv = *reinterpret_cast<const uint32_t *>(vt + kk * kTileRowBytes + 4u * dp);
-            const float v0 = __uint_as_float(vv << 16), v1 = __uint_as_float(vv & 0xffff0000u);
-#pragma unroll
-            for (int g = 0; g < kMaxGqa; ++g) {
-                if (g < (int)G) {
-                    const float pe = p_s[g][kk];
-                    o_acc[g][0] = fmaf(pe, v0, o_acc[g][0]);
-                    o_acc[g][1] = fmaf(pe, v1, o_acc[g][1]);
-                }
-            }
-        }
-        __syncthreads();  // the buffer of tile t is free for tile t + 2, p_s / wred for the next tile
-    }
-
-    // Combine the four key residues (reusing the tile memory), then publish this split's partial.
-    float *o_red = reinterpret_cast<float *>(tiles);  // [4][G][128]
-#pragma unroll
-    for (int g = 0; g < kMaxGqa; ++g) {
-        if (g < (int)G) {
-            o_red[(kq * G + g) * kHeadDim + 2u * dp] = o_acc[g][0];
-            o_red[(kq * G + g) * kHeadDim + 2u * dp + 1u] = o_acc[g][1];
-        }
-    }
-    __syncthreads();
-    const uint32_t stride = kHeadDim + 2u;
-    float *mine = p.scratch + ((size_t)(h * p.splits + split) * G) * stride;
-    for (uint32_t i = tid; i < G * kHeadDim; i += kAttnThreads) {
-        const uint32_t g = i >> 7, d = i & 127u;
-        mine[g * stride + d] = o_red[(0 * G + g) * kHeadDim + d] + o_red[(1 * G + g) * kHeadDim + d] +
-                               o_red[(2 * G + g) * kHeadDim + d] + o_red[(3 * G + g) * kHeadDim + d];
-    }
-    if (tid == 0) {
-#pragma unroll
-        for (int g = 0; g < kMaxGqa; ++g) {
-            if (g < (int)G) {
-                mine[g * stride + kHeadDim] = m_run[g];
-                mine[g * stride + kHeadDim + 1] = l_run[g];
-            }
-        }
-    }
-    __threadfence();
-    __syncthreads();
+    const AttnShared sm = carve_attn_shared(attn_smem);
+    attention_partial<0, kAttnThreads>(p, split, h, pos, sm, tid);
     if (tid == 0) {
         const uint32_t prev = atomicAdd(&p.counters[h], 1u);
         is_last = prev == p.splits - 1u;
     }
     __syncthreads();
-    if (!is_last) {
-        if (tid == 0 && p.trace) trace_max(&p.trace->end);
-        return;
+    if (is_last) {
+        __threadfence();
+        attention_merge<0, kAttnThreads>(p, h, reinterpret_cast<float *>(attn_smem), tid);
+        if (tid == 0) p.counters[h] = 0;
     }
-    __threadfence();
-    // Last split of this KV head to arrive merges all partials.  Weights first (one thread per
-    // (head, split)), then every thread sums its outputs with independent loads.
-    const float *base = p.scratch + ((size_t)h * p.splits * G) * stride;
-    float *wgt = reinterpret_cast<float *>(tiles);  // [G][splits] weights, then [G] 1/l
-    __syncthreads();
-    for (uint32_t g = warp; g < G; g += kAttnWarps) {
-        const float ms = lane < p.splits ? __ldcg(&base[(lane * G + g) * stride + kHeadDim]) : -INFINITY;
-        const float ls = lane < p.splits ? __ldcg(&base[(lane * G + g) * stride + kHeadDim + 1]) : 0.0f;
-        const float mmax = warp_max(ms);
-        const float w = ms == -INFINITY ? 0.0f : expf(ms - mmax);
-        const float lsum = warp_sum(w * ls);
-        if (lane < p.splits) wgt[g * kMaxAttnSplits + lane] = w;
-        if (lane == 0) wgt[kMaxGqa * kMaxAttnSplits + g] = 1.0f / lsum;
-    }
-    __syncthreads();
-    for (uint32_t i = tid; i < G * kHeadDim; i += kAttnThreads) {
-        const uint32_t g = i >> 7, d = i & 127u;
-        float osum = 0.0f;
-#pragma unroll 8
-        for (uint32_t sp = 0; sp < p.splits; ++sp)
-            osum = fmaf(wgt[g * kMaxAttnSplits + sp], __ldcg(&base[(sp * G + g) * stride + d]), osum);
-        p.out[(size_t)(h * G + g) * kHeadDim + d] = f32_to_bf16_bits(osum * wgt[kMaxGqa * kMaxAttnSplits + g]);
-    }
-    if (tid == 0) p.counters[h] = 0;
     if (tid == 0 && p.trace) trace_max(&p.trace->end);
 }
-
 
 // ---------------------------------------------------------------------------------------------------
 
@@ -652,10 +342,10 @@ stark_b200_status attention_decode_launch(const AttnArgs &a, cudaStream_t stream
     static bool attr_set = false;
     if (!attr_set) {
         SB_CUDA(cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)kAttnSmemBytes));
+                                     (int)kAttnSharedBytes));
         attr_set = true;
     }
-    return launch_pdl_smem(attention_decode_kernel, dim3(a.splits, a.kv_heads), dim3(kAttnThreads), kAttnSmemBytes,
+    return launch_pdl_smem(attention_decode_kernel, dim3(a.splits, a.kv_heads), dim3(kAttnThreads), kAttnSharedBytes,
                            a.pdl, stream, p);
 }
 

@@ -19,6 +19,7 @@
 //   * the input vector is converted to f16 after an exact power-of-two rescale by its maximum, so
 //     the f16 range never clips it; bf16 inputs convert exactly.
 #include "qmv.cuh"
+#include "device_math.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -60,43 +61,6 @@ struct QmvParams {
     uint32_t *error_word;
     TraceSlot *trace;
 };
-
-// 4-bit -> f16 conversion of one record word into an m16n8k16 A fragment.
-//   (w & 0x000f000f) | 0x64006400 is the f16 pair (1024 + q, 1024 + q');
-//   (w & 0x00f000f0) | 0x64006400 is (1024 + 16 q, ...).
-// FOLD == false: the offsets are removed here, exactly (x - 1024; x/16 - 64 in one FMA), so the
-//   tensor core sees the integers q.
-// FOLD == true: the patterns go to the tensor core as they are and the offsets are removed from
-//   the f32 group sums afterwards (row g: c - 1024 sum(x); row g+8: c/16 - 64 sum(x)).  That halves
-//   the instruction count of the extraction; the accumulation then carries 1024 x + q x, which
-//   costs about 7 bits of the f32 accumulator.
-template <bool FOLD>
-__device__ inline void dequant_a4_word(uint32_t w, uint32_t (&a)[4]) {
-    const uint32_t magic = 0x64006400u;
-    const uint32_t lo0 = lop3_and_or(w, 0x000f000fu, magic);
-    const uint32_t hi0 = lop3_and_or(w, 0x00f000f0u, magic);
-    const uint32_t w8 = w >> 8;
-    const uint32_t lo1 = lop3_and_or(w8, 0x000f000fu, magic);
-    const uint32_t hi1 = lop3_and_or(w8, 0x00f000f0u, magic);
-    if (FOLD) {
-        a[0] = lo0;
-        a[1] = hi0;
-        a[2] = lo1;
-        a[3] = hi1;
-    } else {
-        const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-        const __half2 k16th = __half2half2(__ushort_as_half(0x2c00));   // 1/16
-        const __half2 kneg64 = __half2half2(__ushort_as_half(0xd400));  // -64
-        __half2 r0 = __hsub2(*reinterpret_cast<const __half2 *>(&lo0), k1024);
-        __half2 r1 = __hfma2(*reinterpret_cast<const __half2 *>(&hi0), k16th, kneg64);
-        __half2 r2 = __hsub2(*reinterpret_cast<const __half2 *>(&lo1), k1024);
-        __half2 r3 = __hfma2(*reinterpret_cast<const __half2 *>(&hi1), k16th, kneg64);
-        a[0] = *reinterpret_cast<uint32_t *>(&r0);
-        a[1] = *reinterpret_cast<uint32_t *>(&r1);
-        a[2] = *reinterpret_cast<uint32_t *>(&r2);
-        a[3] = *reinterpret_cast<uint32_t *>(&r3);
-    }
-}
 
 struct SmemLayout {
     uint32_t ring, xs, xlo, nws, xsum, xoff, red, wred, bars, flags, total;
@@ -640,6 +604,10 @@ int sm_count_cached() {
 }
 
 }  // namespace
+
+void qmv_pick_stage(uint32_t groups, uint32_t *records, uint32_t *rpw, bool *pred) {
+    pick_stage(groups, records, rpw, pred);
+}
 
 stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     const QMatrix *m = a.matrix;

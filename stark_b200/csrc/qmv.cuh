@@ -76,6 +76,9 @@ struct QmvArgs {
 };
 
 stark_b200_status qmv_launch(const QmvArgs &args, cudaStream_t stream);
+// Ring-stage geometry for a matrix with `groups` column groups: records per stage, records per
+// consumer warp, and whether the stage is ragged (needs per-record predicates).
+void qmv_pick_stage(uint32_t groups, uint32_t *records, uint32_t *rpw, bool *pred);
 
 // Re-tiling (device kernels; inputs already in device memory).
 stark_b200_status qmatrix_from_affine_device(const uint8_t *codes, const void *scales, const void *biases,

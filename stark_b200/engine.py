@@ -133,7 +133,7 @@ class DenseModel:
 
     def read_trace(self) -> np.ndarray:
         """Timeline of the launches since the last call, ``uint64[launches_per_step, 4]`` (ns)."""
-        n = self.info().launches_per_step
+        n = self.info().trace_slots
         out = np.empty((n, 4), np.uint64)
         check(_lib.load().stark_b200_read_trace(self._h, out.ctypes.data, out.size), "read_trace")
         return out
