@@ -125,7 +125,17 @@ stark_b200_status stark_b200_qmatrix_create_affine(const void *codes, const void
 stark_b200_status stark_b200_qmatrix_create_gguf(const void *blocks, uint32_t kind, uint32_t rows,
                                                  uint32_t columns, uint32_t location,
                                                  stark_b200_qmatrix **out_matrix);
+/* A bank of `experts` GGUF matrices [experts, rows, columns] (ffn_{gate,up,down}_exps tensors,
+ * crates/stark-engine/src/engine/hybrid/glm.rs:954-1002), read by Weights::selected_matvec
+ * (weights.rs:1612-1689). */
+stark_b200_status stark_b200_qmatrix_create_gguf_bank(const void *blocks, uint32_t kind, uint32_t experts,
+                                                      uint32_t rows, uint32_t columns, uint32_t location,
+                                                      stark_b200_qmatrix **out_matrix);
 stark_b200_status stark_b200_qmatrix_destroy(stark_b200_qmatrix **matrix);
+/* One row dequantized to f32 through the kernels' own decode; must equal decode_values / affine_row
+ * (weights.rs:2880-3017, 1284-1309) bit for bit.  GGUF and 8-bit affine matrices only. */
+stark_b200_status stark_b200_qmatrix_dequantize_row(const stark_b200_qmatrix *matrix, uint32_t expert,
+                                                    uint32_t row, float *dst_host);
 /* Bytes the matrix occupies in device memory (codes + planes, after re-tiling). */
 stark_b200_status stark_b200_qmatrix_device_bytes(const stark_b200_qmatrix *matrix, uint64_t *out_bytes);
 /* Integer codes recovered from the re-tiled device copy through the same extraction the matvec
@@ -139,6 +149,24 @@ stark_b200_status stark_b200_qmatrix_unpack_codes(const stark_b200_qmatrix *matr
  * Weights::matvec (weights.rs:1311-1350, 2511-2553).  io_type selects bf16 or f32 vectors. */
 stark_b200_status stark_b200_op_qmv(const stark_b200_qmatrix *matrix, const void *x, void *y, uint32_t m,
                                     uint32_t io_type, uint32_t location, void *stream);
+
+/* y[i, rows] = W[expert_ids[i]] x_i for i < count: Weights::selected_matvec (weights.rs:1612-1689), the
+ * grouped expert matvec (one launch; the expert of each row is read on the device).  shared_input != 0:
+ * every row uses the same input x[columns]; otherwise x is [count, columns]. */
+stark_b200_status stark_b200_op_qmv_experts(const stark_b200_qmatrix *bank, const uint32_t *expert_ids,
+                                            uint32_t count, const void *x, uint32_t shared_input, void *y,
+                                            uint32_t io_type, uint32_t location, void *stream);
+/* Dense f32 matvec (the router projection of the host path). */
+stark_b200_status stark_b200_op_dense_matvec_f32(const float *w, const float *x, float *y, uint32_t rows,
+                                                 uint32_t columns, uint32_t location, void *stream);
+/* Routed-expert feed-forward of the hybrid host path (crates/stark-engine/src/engine/hybrid/qwen.rs:872-905,
+ * without the shared expert): top-k of `scores` (value descending, index ascending), softmax over the
+ * selected scores, out = sum_r p_r * down_r(silu(gate_r x) * (up_r x)), all f32.  ids_out / probs_out
+ * (host, `active` entries) may be NULL. */
+stark_b200_status stark_b200_op_moe_ffn(const stark_b200_qmatrix *gate_bank, const stark_b200_qmatrix *up_bank,
+                                        const stark_b200_qmatrix *down_bank, const float *scores, const float *x,
+                                        float *out, uint32_t active, uint32_t *ids_out, float *probs_out,
+                                        uint32_t location, void *stream);
 
 /* ------------------------------------------------------------------------------------------
  * Small operators (bf16 bit patterns unless stated).  Each names the reference routine it stands

@@ -358,3 +358,33 @@ class DenseOracle:
                                self.threads):
             raise ValueError("invalid token or context overflow")
         return (logits, hidden) if want_hidden else logits
+
+
+# ----------------------------------------------------------------------------- routed experts (f32 host path)
+
+def silu_f32(x: float) -> float:
+    lib().so_silu_f32.restype = C.c_float
+    return float(lib().so_silu_f32(C.c_float(x)))
+
+
+def dense_matvec_f32(w, x):
+    w = _c(w, np.float32)
+    x = _c(x, np.float32)
+    y = np.empty(w.shape[0], np.float32)
+    lib().so_dense_matvec_f32(_p(w), _p(x), _p(y), w.shape[0], w.shape[1])
+    return y
+
+
+def moe_ffn_f32(kind_gate_up, gate_bank, up_bank, kind_down, down_bank, scores, x, experts, active, hidden, inter,
+                threads=1):
+    """Returns (out, ids, probabilities) of the routed-expert feed-forward."""
+    gate_bank, up_bank, down_bank = _c(gate_bank, np.uint8), _c(up_bank, np.uint8), _c(down_bank, np.uint8)
+    scores, x = _c(scores, np.float32), _c(x, np.float32)
+    out = np.empty(hidden, np.float32)
+    ids = np.empty(active, np.uint32)
+    probs = np.empty(active, np.float32)
+    rc = lib().so_moe_ffn_f32(kind_gate_up, _p(gate_bank), _p(up_bank), kind_down, _p(down_bank), _p(scores), _p(x),
+                              _p(out), experts, active, hidden, inter, _p(ids), _p(probs), threads)
+    if rc:
+        raise ValueError("invalid expert geometry or inputs")
+    return out, ids, probs

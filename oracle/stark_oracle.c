@@ -703,3 +703,60 @@ int so_max_threads(void) {
     return 1;
 #endif
 }
+
+/* ------------------------------------------------------------ routed experts (f32 host path) */
+
+/* hybrid::math::sigmoid / silu: crates/stark-engine/src/engine/hybrid/math.rs:5-16 */
+static inline float sigmoid_f32(float x) {
+    if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
+    float e = expf(x);
+    return e / (1.0f + e);
+}
+float so_silu_f32(float x) { return x * sigmoid_f32(x); }
+
+/* Routed-expert feed-forward of the hybrid host path, without the shared expert:
+ * crates/stark-engine/src/engine/hybrid/qwen.rs:872-905 -- top-k of the router scores (value
+ * descending, index ascending), softmax over the SELECTED scores, per expert
+ * down(silu(gate x) * (up x)), mixture in selection order.  Banks are GGUF rows
+ * [experts, rows, columns] as selected_matvec reads them (weights.rs:1612-1689). */
+int so_moe_ffn_f32(uint32_t kind_gate_up, const uint8_t *gate_bank, const uint8_t *up_bank, uint32_t kind_down,
+                   const uint8_t *down_bank, const float *scores, const float *x, float *out, uint32_t experts,
+                   uint32_t active, uint32_t hidden, uint32_t inter, uint32_t *ids_out, float *probs_out,
+                   int threads) {
+    uint32_t be, bb, de, db;
+    if (so_block_layout(kind_gate_up, &be, &bb) != SO_OK || so_block_layout(kind_down, &de, &db) != SO_OK)
+        return SO_INVALID;
+    if (active == 0 || active > experts || active > 64 || hidden % be || inter % de) return SO_INVALID;
+    uint32_t ids[64];
+    float sel[64], prob[64];
+    if (so_topk_f32(scores, experts, active, ids) != SO_OK) return SO_INVALID;
+    for (uint32_t r = 0; r < active; r++) sel[r] = scores[ids[r]];
+    if (so_softmax_f32(sel, prob, active) != SO_OK) return SO_INVALID;
+    const size_t gu_bytes = (size_t)inter * (hidden / be) * bb;  /* one expert of a gate / up bank */
+    const size_t dn_bytes = (size_t)hidden * (inter / de) * db;
+    float *gate = (float *)malloc(sizeof(float) * inter), *up = (float *)malloc(sizeof(float) * inter);
+    float *eo = (float *)malloc(sizeof(float) * hidden);
+    for (uint32_t i = 0; i < hidden; i++) out[i] = 0.0f;
+    for (uint32_t r = 0; r < active; r++) {
+        so_gguf_matvec_f32(kind_gate_up, gate_bank + ids[r] * gu_bytes, x, gate, inter, hidden, threads);
+        so_gguf_matvec_f32(kind_gate_up, up_bank + ids[r] * gu_bytes, x, up, inter, hidden, threads);
+        for (uint32_t i = 0; i < inter; i++) gate[i] = so_silu_f32(gate[i]) * up[i];
+        so_gguf_matvec_f32(kind_down, down_bank + ids[r] * dn_bytes, gate, eo, hidden, inter, threads);
+        for (uint32_t i = 0; i < hidden; i++) out[i] += prob[r] * eo[i];
+        if (ids_out) ids_out[r] = ids[r];
+        if (probs_out) probs_out[r] = prob[r];
+    }
+    free(gate);
+    free(up);
+    free(eo);
+    return SO_OK;
+}
+
+/* Dense f32 matvec, sequential f32 sum (router "gate" projection on the host path). */
+void so_dense_matvec_f32(const float *w, const float *x, float *y, uint32_t rows, uint32_t columns) {
+    for (uint32_t r = 0; r < rows; r++) {
+        float total = 0.0f;
+        for (uint32_t c = 0; c < columns; c++) total += w[(size_t)r * columns + c] * x[c];
+        y[r] = total;
+    }
+}

@@ -85,6 +85,11 @@ def load() -> C.CDLL:
         "stark_b200_take_device_error": (u32, [C.POINTER(u32)]),
         "stark_b200_qmatrix_create_affine": (u32, [vp, vp, vp, C.POINTER(AffineDesc), C.POINTER(vp)]),
         "stark_b200_qmatrix_create_gguf": (u32, [vp, u32, u32, u32, u32, C.POINTER(vp)]),
+        "stark_b200_qmatrix_create_gguf_bank": (u32, [vp, u32, u32, u32, u32, u32, C.POINTER(vp)]),
+        "stark_b200_qmatrix_dequantize_row": (u32, [vp, u32, u32, vp]),
+        "stark_b200_op_qmv_experts": (u32, [vp, vp, u32, vp, u32, vp, u32, u32, vp]),
+        "stark_b200_op_dense_matvec_f32": (u32, [vp, vp, vp, u32, u32, u32, vp]),
+        "stark_b200_op_moe_ffn": (u32, [vp, vp, vp, vp, vp, vp, u32, vp, vp, u32, vp]),
         "stark_b200_qmatrix_destroy": (u32, [C.POINTER(vp)]),
         "stark_b200_qmatrix_device_bytes": (u32, [vp, C.POINTER(u64)]),
         "stark_b200_qmatrix_unpack_codes": (u32, [vp, vp, sz]),

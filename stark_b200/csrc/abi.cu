@@ -145,6 +145,31 @@ stark_b200_status stark_b200_qmatrix_create_affine(const void *codes, const void
     const size_t plane_bytes = plane_elems * (desc->plane_kind == STARK_B200_PLANE_F32 ? 4u : 2u);
     QMatrix *m = nullptr;
     stark_b200_status st;
+    if (desc->bits == 8) {
+        // 8-bit affine keeps the reference's byte layout: codes, then the scale plane, then the bias plane
+        if (desc->group != 64 || desc->plane_kind != STARK_B200_PLANE_BF16 || desc->scale_layout != 0 || desc->pair_halves)
+            return STARK_B200_UNSUPPORTED;
+        m = new (std::nothrow) QMatrix();
+        if (!m) return STARK_B200_OUT_OF_MEMORY;
+        m->format = kFmtAffine8;
+        m->rows = desc->rows;
+        m->columns = desc->columns;
+        m->groups = desc->columns / 64u;
+        m->experts = 1;
+        m->bytes = code_bytes + 2u * plane_bytes;
+        cudaGetDevice(&m->device);
+        const cudaMemcpyKind kind = desc->location == STARK_B200_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
+        cudaError_t e = cudaMalloc(&m->data, m->bytes);
+        if (e == cudaSuccess) e = cudaMemcpy(m->data, codes, code_bytes, kind);
+        if (e == cudaSuccess) e = cudaMemcpy(m->data + code_bytes, scales, plane_bytes, kind);
+        if (e == cudaSuccess) e = cudaMemcpy(m->data + code_bytes + plane_bytes, biases, plane_bytes, kind);
+        if (e != cudaSuccess) {
+            qmatrix_free(m);
+            return cuda_status(e);
+        }
+        *out_matrix = reinterpret_cast<stark_b200_qmatrix *>(m);
+        return STARK_B200_OK;
+    }
     if (desc->location == STARK_B200_DEVICE) {
         st = qmatrix_from_affine_device((const uint8_t *)codes, scales, biases, *desc, 0, &m);
         if (st == STARK_B200_OK) st = cuda_status(cudaStreamSynchronize(0));
@@ -171,17 +196,6 @@ stark_b200_status stark_b200_qmatrix_create_affine(const void *codes, const void
     return STARK_B200_OK;
 }
 
-stark_b200_status stark_b200_qmatrix_create_gguf(const void *blocks, uint32_t kind, uint32_t rows, uint32_t columns,
-                                                 uint32_t location, stark_b200_qmatrix **out_matrix) {
-    (void)blocks;
-    (void)kind;
-    (void)rows;
-    (void)columns;
-    (void)location;
-    if (out_matrix) *out_matrix = nullptr;
-    return STARK_B200_UNSUPPORTED;
-}
-
 stark_b200_status stark_b200_qmatrix_destroy(stark_b200_qmatrix **matrix) {
     if (!matrix) return STARK_B200_INVALID_ARGUMENT;
     qmatrix_free(reinterpret_cast<QMatrix *>(*matrix));
@@ -201,7 +215,14 @@ stark_b200_status stark_b200_qmatrix_unpack_codes(const stark_b200_qmatrix *matr
     if (!m || !dst_host || count != (size_t)m->rows * m->columns) return STARK_B200_INVALID_ARGUMENT;
     uint8_t *d = nullptr;
     SB_CUDA(cudaMalloc(&d, count));
-    stark_b200_status st = qmatrix_unpack_codes_device(m, d, 0);
+    stark_b200_status st = STARK_B200_OK;
+    if (qmv_rows_supports(m)) {
+        if (m->experts > 1) st = STARK_B200_UNSUPPORTED;
+        for (uint32_t row = 0; row < m->rows && st == STARK_B200_OK; ++row)
+            st = qmv_rows_dequantize(m, 0, row, nullptr, d + (size_t)row * m->columns, 0);
+    } else {
+        st = qmatrix_unpack_codes_device(m, d, 0);
+    }
     if (st == STARK_B200_OK) st = cuda_status(cudaMemcpy(dst_host, d, count, cudaMemcpyDeviceToHost));
     cudaFree(d);
     return st;
@@ -227,7 +248,11 @@ stark_b200_status stark_b200_op_qmv(const stark_b200_qmatrix *matrix, const void
         dx = (const uint8_t *)ctx->stage_in;
         dy = (uint8_t *)ctx->stage_out;
     }
-    for (uint32_t row = 0; row < m; ++row) {
+    if (qmv_rows_supports(w)) {
+        stark_b200_status st = qmv_rows_launch(w, dx, w->columns, dy, m, nullptr, io_type, s);
+        if (st != STARK_B200_OK) return st;
+    }
+    for (uint32_t row = 0; row < m && !qmv_rows_supports(w); ++row) {
         QmvArgs a{};
         a.matrix = w;
         a.x = dx + row * xin;

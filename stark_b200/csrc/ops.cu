@@ -283,6 +283,84 @@ __global__ void moe_route_kernel(const float *logits, uint32_t *ids, float *weig
     }
 }
 
+// math.rs:55-66 topk + math.rs:36-51 softmax over the selected; one warp, experts <= 1024, active <= 32.
+__global__ void moe_select_kernel(const float *scores, uint32_t experts, uint32_t active, uint32_t *ids,
+                                  float *probs) {
+    __shared__ uint32_t chosen[32];
+    __shared__ float chosen_v[32];
+    const uint32_t lane = threadIdx.x;
+    for (uint32_t r = 0; r < active; ++r) {
+        float best = -INFINITY;
+        uint32_t bi = 0xffffffffu;
+        for (uint32_t e = lane; e < experts; e += 32) {
+            bool used = false;
+            for (uint32_t k = 0; k < r; ++k) used |= chosen[k] == e;
+            const float v = scores[e];
+            if (!used && (bi == 0xffffffffu || v > best)) {
+                best = v;
+                bi = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0xffffffffu && (bi == 0xffffffffu || ov > best || (ov == best && oi < bi))) {
+                best = ov;
+                bi = oi;
+            }
+        }
+        if (lane == 0) {
+            chosen[r] = bi;
+            chosen_v[r] = best;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        float mx = -INFINITY;
+        for (uint32_t r = 0; r < active; ++r) mx = fmaxf(mx, chosen_v[r]);
+        float sum = 0.0f;
+        for (uint32_t r = 0; r < active; ++r) {
+            probs[r] = expf(chosen_v[r] - mx);
+            sum += probs[r];
+        }
+        for (uint32_t r = 0; r < active; ++r) {
+            probs[r] /= sum;
+            ids[r] = chosen[r];
+        }
+    }
+}
+
+__device__ inline float sigmoid_stable(float x) {
+    if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
+    const float e = expf(x);
+    return e / (1.0f + e);
+}
+
+__global__ void silu_mul_f32_kernel(float *gate, const float *up, uint32_t count) {
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < count; i += gridDim.x * blockDim.x)
+        gate[i] = __fmul_rn(__fmul_rn(gate[i], sigmoid_stable(gate[i])), up[i]);
+}
+
+__global__ void weighted_sum_kernel(const float *rows, const float *probs, float *out, uint32_t count,
+                                    uint32_t width) {
+    for (uint32_t h = blockIdx.x * blockDim.x + threadIdx.x; h < width; h += gridDim.x * blockDim.x) {
+        float acc = 0.0f;
+        for (uint32_t r = 0; r < count; ++r) acc = __fadd_rn(acc, __fmul_rn(probs[r], rows[(size_t)r * width + h]));
+        out[h] = acc;
+    }
+}
+
+__global__ void dense_matvec_f32_kernel(const float *w, const float *x, float *y, uint32_t rows, uint32_t columns) {
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    for (uint32_t r = blockIdx.x * (blockDim.x / 32u) + warp; r < rows; r += gridDim.x * (blockDim.x / 32u)) {
+        float acc = 0.0f;
+        for (uint32_t c = lane; c < columns; c += 32) acc = fmaf(w[(size_t)r * columns + c], x[c], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) y[r] = acc;
+    }
+}
+
 template <typename... Args>
 stark_b200_status launch_pdl_smem(void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, bool pdl,
                                   cudaStream_t stream, Args... args) {
@@ -401,6 +479,35 @@ stark_b200_status moe_route_launch(const float *logits, uint32_t *ids, float *we
                                    cudaStream_t stream) {
     moe_route_kernel<<<(rows + 63u) / 64u, 64, 0, stream>>>(logits, ids, weights, rows, experts, active,
                                                            round_weights ? 1u : 0u, round_logits ? 1u : 0u);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+stark_b200_status moe_select_launch(const float *scores, uint32_t experts, uint32_t active, uint32_t *ids,
+                                    float *probs, cudaStream_t stream) {
+    if (experts == 0 || experts > 1024 || active == 0 || active > 32 || active > experts) return STARK_B200_INVALID_ARGUMENT;
+    moe_select_kernel<<<1, 32, 0, stream>>>(scores, experts, active, ids, probs);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+stark_b200_status silu_mul_f32_launch(float *gate, const float *up, uint32_t count, cudaStream_t stream) {
+    silu_mul_f32_kernel<<<std::max(1u, std::min(148u, (count + 255u) / 256u)), 256, 0, stream>>>(gate, up, count);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+stark_b200_status weighted_sum_launch(const float *rows, const float *probs, float *out, uint32_t count,
+                                      uint32_t width, cudaStream_t stream) {
+    weighted_sum_kernel<<<std::max(1u, std::min(148u, (width + 255u) / 256u)), 256, 0, stream>>>(rows, probs, out, count,
+                                                                                              width);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+stark_b200_status dense_matvec_f32_launch(const float *w, const float *x, float *y, uint32_t rows, uint32_t columns,
+                                          cudaStream_t stream) {
+    dense_matvec_f32_kernel<<<std::max(1u, std::min(592u, (rows + 7u) / 8u)), 256, 0, stream>>>(w, x, y, rows, columns);
     SB_CUDA(cudaGetLastError());
     return STARK_B200_OK;
 }

@@ -80,4 +80,17 @@ stark_b200_status moe_route_launch(const float *logits, uint32_t *ids, float *we
                                    uint32_t experts, uint32_t active, bool round_weights, bool round_logits,
                                    cudaStream_t stream);
 
+// Routed-expert selection of the hybrid host path: top-k of the scores (value descending, index
+// ascending), softmax over the selected scores (hybrid/qwen.rs:872-874, math.rs:36-66).
+stark_b200_status moe_select_launch(const float *scores, uint32_t experts, uint32_t active, uint32_t *ids,
+                                    float *probs, cudaStream_t stream);
+// gate[i] = silu(gate[i]) * up[i], f32 (hybrid/qwen.rs:889-891, math.rs:5-16).
+stark_b200_status silu_mul_f32_launch(float *gate, const float *up, uint32_t count, cudaStream_t stream);
+// out[h] = sum_r probs[r] * rows[r, h], r ascending (hybrid/qwen.rs:894-899).
+stark_b200_status weighted_sum_launch(const float *rows, const float *probs, float *out, uint32_t count,
+                                      uint32_t width, cudaStream_t stream);
+// y = W x, dense f32, one warp per row.
+stark_b200_status dense_matvec_f32_launch(const float *w, const float *x, float *y, uint32_t rows, uint32_t columns,
+                                          cudaStream_t stream);
+
 }  // namespace sb

@@ -34,6 +34,7 @@ struct QMatrix {
     uint32_t groups;       // K / 64
     uint32_t pair_halves;  // storage tile 2j = rows 16j.., tile 2j+1 = rows N/2 + 16j..
     uint32_t record_bytes;
+    uint32_t experts;  // > 1: a bank of `experts` matrices of rows x columns (row-wise formats only)
     uint8_t *data;  // device
     size_t bytes;
     int device;
@@ -86,5 +87,15 @@ stark_b200_status qmatrix_from_affine_device(const uint8_t *codes, const void *s
                                              QMatrix **out);
 stark_b200_status qmatrix_unpack_codes_device(const QMatrix *m, uint8_t *dst_device, cudaStream_t stream);
 void qmatrix_free(QMatrix *m);
+
+// Row-wise kernels for the formats kept in the reference's byte layout (qmv_rows.cu).
+bool qmv_rows_supports(const QMatrix *m);
+// y[b, rows] = W[expert_ids[b]] x_b for b < batch (expert_ids == nullptr: the only matrix);
+// x_stride = elements between consecutive inputs, 0 if all launch rows share one input.
+stark_b200_status qmv_rows_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
+                                  const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream);
+// One row dequantized to f32 (and / or its integer codes, one byte each), device outputs.
+stark_b200_status qmv_rows_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,
+                                      uint8_t *codes_device, cudaStream_t stream);
 
 }  // namespace sb

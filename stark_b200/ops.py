@@ -235,3 +235,61 @@ def attention_decode(qkv: np.ndarray, keys: np.ndarray, values: np.ndarray, q_he
     check(_lib.load().stark_b200_op_attention_decode(_ptr(qkv), _ptr(keys), _ptr(values), _ptr(out), qn, kn,
                                                      C.byref(d)), "op_attention_decode")
     return out
+
+
+# ----------------------------------------------------------------------------- GGUF / 8-bit matrices, expert banks
+
+def _qmatrix_from_gguf(blocks: np.ndarray, kind: int, rows: int, columns: int, experts: int = 0) -> QMatrix:
+    blocks = np.ascontiguousarray(blocks, np.uint8)
+    h = C.c_void_p()
+    lib = _lib.load()
+    if experts:
+        check(lib.stark_b200_qmatrix_create_gguf_bank(_ptr(blocks), kind, experts, rows, columns, HOST, C.byref(h)),
+              "qmatrix_create_gguf_bank")
+    else:
+        check(lib.stark_b200_qmatrix_create_gguf(_ptr(blocks), kind, rows, columns, HOST, C.byref(h)),
+              "qmatrix_create_gguf")
+    q = QMatrix(h.value, rows, columns)
+    q.experts = experts or 1
+    return q
+
+
+QMatrix.from_gguf = staticmethod(_qmatrix_from_gguf)
+
+
+def dequantize_row(q: QMatrix, row: int, expert: int = 0) -> np.ndarray:
+    out = np.empty(q.columns, np.float32)
+    check(_lib.load().stark_b200_qmatrix_dequantize_row(q._h, expert, row, _ptr(out)), "qmatrix_dequantize_row")
+    return out
+
+
+def matvec_experts(bank: QMatrix, expert_ids, x: np.ndarray, shared_input: bool, io_type: int = F32) -> np.ndarray:
+    """``Weights::selected_matvec``: y[i] = W[expert_ids[i]] x_i (or x if shared)."""
+    ids = np.ascontiguousarray(expert_ids, np.uint32)
+    dt = np.float32 if io_type == F32 else np.uint16
+    x = np.ascontiguousarray(x, dt)
+    y = np.empty((ids.size, bank.rows), dt)
+    check(_lib.load().stark_b200_op_qmv_experts(bank._h, _ptr(ids), ids.size, _ptr(x), int(shared_input), _ptr(y),
+                                                io_type, HOST, None), "op_qmv_experts")
+    return y
+
+
+def dense_matvec_f32(w: np.ndarray, x: np.ndarray) -> np.ndarray:
+    w = np.ascontiguousarray(w, np.float32)
+    x = np.ascontiguousarray(x, np.float32)
+    y = np.empty(w.shape[0], np.float32)
+    check(_lib.load().stark_b200_op_dense_matvec_f32(_ptr(w), _ptr(x), _ptr(y), w.shape[0], w.shape[1], HOST, None),
+          "op_dense_matvec_f32")
+    return y
+
+
+def moe_ffn(gate: QMatrix, up: QMatrix, down: QMatrix, scores: np.ndarray, x: np.ndarray, active: int):
+    """Routed-expert feed-forward (hybrid host path).  Returns (out, ids, probabilities)."""
+    scores = np.ascontiguousarray(scores, np.float32)
+    x = np.ascontiguousarray(x, np.float32)
+    out = np.empty(down.rows, np.float32)
+    ids = np.empty(active, np.uint32)
+    probs = np.empty(active, np.float32)
+    check(_lib.load().stark_b200_op_moe_ffn(gate._h, up._h, down._h, _ptr(scores), _ptr(x), _ptr(out), active,
+                                            _ptr(ids), _ptr(probs), HOST, None), "op_moe_ffn")
+    return out, ids, probs

@@ -85,3 +85,36 @@ def dense_weights(cfg: dict, seed: int = 0) -> dict:
 
 def prompt(cfg: dict, length: int, seed: int = 1) -> np.ndarray:
     return np.random.default_rng(seed).integers(0, cfg["vocab"], size=length, dtype=np.uint32)
+
+
+# ----------------------------------------------------------------------------- GGUF blocks
+
+def q8_0_rows(rng: np.random.Generator, rows: int, columns: int, scale: float = 0.01) -> np.ndarray:
+    """Random Q8_0 rows: per 32 values an f16 scale d ~ U[0.5, 1.5] * scale and 32 int8 codes."""
+    blocks = rows * columns // 32
+    out = np.empty((blocks, 34), np.uint8)
+    d = (rng.uniform(0.5, 1.5, blocks) * scale).astype(np.float16)
+    out[:, 0:2] = d.view(np.uint8).reshape(blocks, 2)
+    out[:, 2:] = rng.integers(0, 256, size=(blocks, 32), dtype=np.uint8)
+    return out.reshape(rows, -1)
+
+
+def q4_k_rows(rng: np.random.Generator, rows: int, columns: int, scale: float = 0.01) -> np.ndarray:
+    """Random Q4_K rows: per 256 values f16 d and dmin, 12 bytes of packed 6-bit (scale, min) pairs, 128
+    bytes of nibbles.  d is sized so that d * sc * q stays O(scale)."""
+    blocks = rows * columns // 256
+    out = rng.integers(0, 256, size=(blocks, 144), dtype=np.uint8)
+    d = (rng.uniform(0.5, 1.5, blocks) * scale / 32.0).astype(np.float16)
+    dmin = (rng.uniform(0.5, 1.5, blocks) * scale / 8.0).astype(np.float16)
+    out[:, 0:2] = d.view(np.uint8).reshape(blocks, 2)
+    out[:, 2:4] = dmin.view(np.uint8).reshape(blocks, 2)
+    return out.reshape(rows, -1)
+
+
+def affine8_matrix(rng: np.random.Generator, rows: int, columns: int, scale_lo: float = 0.0005,
+                   scale_hi: float = 0.002, group: int = 64) -> dict:
+    """One 8-bit MLX-affine matrix: codes uniform 0..255, bias = -128 * scale."""
+    codes = rng.integers(0, 256, size=(rows, columns), dtype=np.uint8)
+    scales = f32_to_bf16(rng.uniform(scale_lo, scale_hi, size=(rows, columns // group)).astype(np.float32))
+    biases = f32_to_bf16(-128.0 * bf16_to_f32(scales))
+    return dict(codes=codes, scales=scales, biases=biases, n=rows, k=columns, bits=8, group=group)
