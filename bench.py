@@ -125,9 +125,20 @@ def run_matvec(args) -> None:
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
     rows, cols = args.rows, args.columns
     w = S.matvec_case(seed=args.seed, rows=rows, columns=cols)
-    per = rows * cols * BYTES_PER_WEIGHT + 2 * (rows + cols)
+    rng = np.random.default_rng(args.seed)
+    bytes_per_weight = {"affine4": 0.5625, "affine8": 1.0625, "q8_0": 34 / 32, "q4_k": 144 / 256}[args.format]
+    per = rows * cols * bytes_per_weight + 2 * (rows + cols)
     pool_n = min(40, max(2, int(300e6 // per) + 1))
-    pool = [QMatrix.from_affine(w["codes"], w["scales"], w["biases"], rows, cols) for _ in range(pool_n)]
+    if args.format == "affine4":
+        make = lambda: QMatrix.from_affine(w["codes"], w["scales"], w["biases"], rows, cols)
+    elif args.format == "affine8":
+        w8 = S.affine8_matrix(rng, rows, cols)
+        make = lambda: QMatrix.from_affine(w8["codes"], w8["scales"], w8["biases"], rows, cols, bits=8)
+    else:
+        kind = 8 if args.format == "q8_0" else 12
+        data = (S.q8_0_rows if kind == 8 else S.q4_k_rows)(rng, rows, cols)
+        make = lambda: QMatrix.from_gguf(data, kind, rows, cols)
+    pool = [make() for _ in range(pool_n)]
     x = torch.from_numpy(w["x"].view(np.int16)).cuda()
     y = torch.empty(rows, dtype=torch.int16, device="cuda")
     stream = torch.cuda.Stream()
@@ -160,10 +171,10 @@ def run_matvec(args) -> None:
     e2e = (time.perf_counter() - t0) / min(n, 64)
     graph.destroy()
     print(json.dumps({
-        "metric": "4-bit matvec GB/s", "value": per / us / 1e3, "unit": "GB/s", "n_gpus": 1, "steps": n,
+        "metric": f"{args.format} matvec GB/s", "value": per / us / 1e3, "unit": "GB/s", "n_gpus": 1, "steps": n,
         "warmup": warmup, "ms_per_step": us / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"matvec {rows}x{cols} 4-bit MLX-affine g64, batch 1",
+        "config": {"workload": f"matvec {rows}x{cols} {args.format}, batch 1",
                    "l2": f"pool of {pool_n} matrices ({pool_n * per / 1e6:.0f} MB) cycled, larger than L2"},
         "e2e": {"value": per / e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 2 * cols, "d2h_bytes_per_step": 2 * rows},
         "gpu_launches": n,
@@ -216,6 +227,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--rows", type=int, default=4096, help="matvec workload only")
     ap.add_argument("--columns", type=int, default=4096, help="matvec workload only")
+    ap.add_argument("--format", default="affine4", choices=["affine4", "affine8", "q8_0", "q4_k"],
+                    help="matvec workload only")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.workload == "matvec":
