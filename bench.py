@@ -225,6 +225,9 @@ def main() -> None:
     ap.add_argument("--workload", default="qwen3-8b", choices=sorted(WORKLOADS))
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
+                    help="N > 1: shard the one token stream over the GPUs (tensor parallel, strong scaling) or "
+                         "run N independent streams (weak scaling)")
     ap.add_argument("--rows", type=int, default=4096, help="matvec workload only")
     ap.add_argument("--columns", type=int, default=4096, help="matvec workload only")
     ap.add_argument("--format", default="affine4", choices=["affine4", "affine8", "q8_0", "q4_k"],
@@ -246,17 +249,26 @@ def main() -> None:
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
+    from stark_b200.engine import DenseModel, TensorParallel
+    from stark_b200.ops import take_device_error
+
+    tp = None
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        if args.parallel == "tp":
+            host_group = dist.new_group(backend="gloo")  # moves buffer handles and read-out shards, not tokens
 
-    from stark_b200.engine import DenseModel
-    from stark_b200.ops import take_device_error
+            def all_gather(blob: bytes):
+                out = [None] * world
+                dist.all_gather_object(out, blob, group=host_group)
+                return out
+            tp = TensorParallel(rank, world, all_gather)
 
     steps, warmup = args.steps, max(args.warmup, 3)
     context = max(wl["context"], wl["prompt"] + warmup + 2 * steps + 8)
     weights = S.dense_weights(cfg, seed=args.seed)
     prompt = S.prompt(cfg, wl["prompt"], seed=args.seed + 1)
-    model = DenseModel.load(cfg, weights, context_tokens=context)
+    model = DenseModel.load(cfg, weights, context_tokens=context, tp=tp)
     info = model.info()
     stream = torch.cuda.ExternalStream(model.stream())
 
@@ -300,18 +312,23 @@ def main() -> None:
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_s = float(t[0]), float(t[1])
-    value = world * steps / (ms / 1e3)
-    e2e_value = world * e2e_steps / e2e_s
+    streams = 1 if tp is not None else world  # tensor parallel: all GPUs work on the one token stream
+    value = streams * steps / (ms / 1e3)
+    e2e_value = streams * e2e_steps / e2e_s
 
     peak, peak_kind = peaks()
     algo = step_bytes(cfg, mean_context)
-    achieved = algo / (ms / steps * 1e-3) / 1e9
+    # per GPU: a rank of a tensor-parallel group streams 1/N of the step's bytes (plus the whole
+    # embedding row and vectors, which are negligible)
+    achieved = algo / (world if tp is not None else 1) / (ms / steps * 1e-3) / 1e9
     line = {
         "metric": "batch-1 decode tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps,
-        "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+        "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,
+        "scaling": "strong" if tp is not None else "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{wl['cfg']} 4-bit MLX-affine g64, batch 1, {wl['prompt']}-token prompt, greedy decode",
-                   "parallelism": "tp1" if world == 1 else f"{world} independent replicas",
+                   "parallelism": "tp1" if world == 1 else (f"tp{world}" if tp is not None
+                                                            else f"{world} independent replicas"),
                    "l2": "per-step inputs (weights %.2f GB + KV) exceed the 126 MB L2" % (info.weight_bytes / 1e9),
                    "mean_context_rows": mean_context},
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 16,
@@ -321,7 +338,8 @@ def main() -> None:
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": None, "peak_kind": peak_kind, "frac_of_8tbs": achieved / 8000.0,
                      "algorithmic_bytes_per_step": algo,
-                     "note": "whole decode step (all kernels of the token) over the step's algorithmic bytes"},
+                     "note": "whole decode step (all kernels of the token) over the step's algorithmic bytes"
+                             + (", per GPU" if world > 1 else "")},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import oracle as O
@@ -329,7 +347,9 @@ def main() -> None:
         line["cpu_baseline"] = cpu_sample(cfg, weights, prompt, 8, n, O.max_threads())
     if rank == 0:
         print(json.dumps(line))
+    model.close()
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
 
 

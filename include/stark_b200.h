@@ -317,6 +317,25 @@ stark_b200_status stark_b200_model_set_affine(stark_b200_model *model, uint32_t 
                                               const stark_b200_affine_desc *desc);
 stark_b200_status stark_b200_model_set_vector(stark_b200_model *model, uint32_t layer, uint32_t which,
                                               const float *data, uint32_t count);
+/* Tensor parallelism over several GPUs of one node, one process (or thread) and one handle per GPU.
+ * The reference runs on a single device, so these two calls replace nothing in it; they shard the same
+ * decode graph.  The config passed to model_create holds THIS RANK'S shapes: q_heads, kv_heads and
+ * inter divided by the rank count (whole heads; K shards of the o- and down-projections multiples of
+ * the quantization group), vocab = the rows of this rank's slice of the read-out matrix, tied = 0.
+ * The embedding table is passed whole (vocab_total rows) to every rank.
+ *   tp_init     allocates this rank's exchange buffers and returns their 64-byte inter-process handle;
+ *   tp_connect  takes the handles of all ranks in rank order (the caller moves them between processes)
+ *               and maps the peers' buffers.
+ * Afterwards model_finalize, prefill, step and generate_greedy are collective: every rank makes the
+ * same calls with the same tokens.  The o- and down-projections are followed by a one-shot all-reduce
+ * over NVLink peer memory fused with the bf16 rounding and the residual add; the greedy token is chosen
+ * across vocabulary shards on the device.  readout_f32 / readout_bf16 return this rank's slice
+ * (config.vocab entries, starting at vocab_offset); readout_logprobs_f32 is UNSUPPORTED.  A peer that
+ * does not arrive within 4 s sets the device error word: the next drain returns DEVICE_FAILURE and
+ * fences the handle.  cancel is not collective and must not be used between ranks' calls. */
+stark_b200_status stark_b200_model_tp_init(stark_b200_model *model, uint32_t rank, uint32_t ranks,
+                                           uint32_t vocab_offset, uint32_t vocab_total, uint8_t handle_out[64]);
+stark_b200_status stark_b200_model_tp_connect(stark_b200_model *model, const uint8_t *handles, size_t handle_bytes);
 stark_b200_status stark_b200_model_finalize(stark_b200_model *model);
 stark_b200_status stark_b200_destroy(stark_b200_model **model);
 stark_b200_status stark_b200_reset(stark_b200_model *model);

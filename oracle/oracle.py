@@ -110,7 +110,8 @@ def affine_matvec_bf16(codes, scales, biases, a, n, k, bits=4, group=64, m=1, sc
 
 def affine_matvec_f32(codes, scales, biases, plane_kind, x, rows, columns, bits=4, group=64, threads=1):
     """Path-B host matvec: f32 in/out, planes f32 (0) / f16 (1) / bf16 (30)."""
-    codes = _c(codes.view(np.uint8).reshape(-1), np.uint8)
+    codes = _c(np.ascontiguousarray(codes).view(np.uint8).reshape(-1), np.uint8)
+    scales, biases = np.ascontiguousarray(scales), np.ascontiguousarray(biases)
     x = _c(x, np.float32)
     y = np.empty(rows, np.float32)
     rc = lib().so_affine_matvec_f32(_p(codes), _p(scales), _p(biases), plane_kind, _p(x), _p(y), rows, columns,

@@ -295,6 +295,18 @@ stark_b200_status stark_b200_model_set_vector(stark_b200_model *model, uint32_t 
     return model_set_vector(M(model), layer, which, data, count);
 }
 
+stark_b200_status stark_b200_model_tp_init(stark_b200_model *model, uint32_t rank, uint32_t ranks,
+                                           uint32_t vocab_offset, uint32_t vocab_total, uint8_t handle_out[64]) {
+    if (!model || !handle_out) return STARK_B200_INVALID_ARGUMENT;
+    return model_tp_init(M(model), rank, ranks, vocab_offset, vocab_total, handle_out);
+}
+
+stark_b200_status stark_b200_model_tp_connect(stark_b200_model *model, const uint8_t *handles, size_t handle_bytes) {
+    if (!model || !handles) return STARK_B200_INVALID_ARGUMENT;
+    if (handle_bytes != (size_t)M(model)->tp.size * 64u) return STARK_B200_INVALID_ARGUMENT;
+    return model_tp_connect(M(model), handles);
+}
+
 stark_b200_status stark_b200_model_finalize(stark_b200_model *model) {
     if (!model) return STARK_B200_INVALID_ARGUMENT;
     return model_finalize(M(model));
@@ -351,6 +363,7 @@ stark_b200_status stark_b200_readout_logprobs_f32(stark_b200_model *model, float
     if (!model || !dst) return STARK_B200_INVALID_ARGUMENT;
     Model *m = M(model);
     if (!m->has_logits) return STARK_B200_INVALID_STATE;
+    if (m->tp.size > 1u) return STARK_B200_UNSUPPORTED;  // a shard's logits do not normalise alone
     if (count != m->cfg.vocab) return STARK_B200_INVALID_ARGUMENT;
     Staged st;
     float *df;

@@ -76,6 +76,13 @@ __device__ inline void mma_m16n8k16_bf16(float (&c)[4], uint32_t a0, uint32_t a1
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
+// Transposes an 8x8 matrix of 16-bit elements held one row-pair per lane (lane (g, t): row g, columns
+// 2t, 2t+1); afterwards the lane holds row g of the transpose.
+__device__ inline uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
 // f32 pair -> packed bf16 (hi) and the packed bf16 of the remainders (lo): hi + lo carries ~16 bits.
 __device__ inline void split_bf16x2(float x, float y, uint32_t &hi, uint32_t &lo) {
     const uint16_t xh = f32_to_bf16_bits(x), yh = f32_to_bf16_bits(y);
@@ -88,27 +95,43 @@ __device__ inline void split_bf16x2(float x, float y, uint32_t &hi, uint32_t &lo
 // so the half-split RoPE pairs (d, d+64) sit in the same lane and no shared memory is needed.
 //   qkv_norm.rs:44-108: f32 sum of squares, rms = 1/sqrt(mean + eps), bf16(normalized) * bf16(scale) -> bf16
 //   attention_prepare.rs:7-43: x*cos + (+-pair)*sin with separately rounded products, then bf16
-__device__ inline void warp_head_norm_rope(const uint16_t *head, const float *norm_w, const float *cosr,
-                                           const float *sinr, float eps, uint32_t lane, uint16_t *out /* smem [128] */) {
+// The constants of a lane (norm weights already rounded to bf16, cos / sin of the row's position) can be
+// fetched before the row itself exists.
+struct HeadConsts {
+    float nw[4], cs[4], sn[4];
+};
+__device__ inline HeadConsts load_head_consts(const float *norm_w, const float *cosr, const float *sinr,
+                                              uint32_t lane) {
+    HeadConsts c;
+    const uint32_t d[4] = {2u * lane, 2u * lane + 1u, 64u + 2u * lane, 65u + 2u * lane};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        c.nw[i] = norm_w ? bf16_round(norm_w[d[i]]) : 1.0f;
+        c.cs[i] = cosr ? cosr[d[i]] : 1.0f;
+        c.sn[i] = sinr ? sinr[d[i]] : 0.0f;
+    }
+    return c;
+}
+__device__ inline void warp_head_norm_rope(const uint16_t *head, const HeadConsts &c, bool has_norm, bool has_rope,
+                                           float eps, uint32_t lane, uint16_t *out /* smem [128] */) {
     // ld.cg: the row may have been written by another CTA of a kernel that is still running
     const uint32_t lo2 = __ldcg(reinterpret_cast<const uint32_t *>(head + 2u * lane));
     const uint32_t hi2 = __ldcg(reinterpret_cast<const uint32_t *>(head + 64u + 2u * lane));
     float v[4] = {__uint_as_float(lo2 << 16), __uint_as_float(lo2 & 0xffff0000u), __uint_as_float(hi2 << 16),
                   __uint_as_float(hi2 & 0xffff0000u)};
-    const uint32_t d[4] = {2u * lane, 2u * lane + 1u, 64u + 2u * lane, 65u + 2u * lane};
-    if (norm_w) {
+    if (has_norm) {
         const float total = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
         const float rms = 1.0f / sqrtf(total / (float)kHeadDim + eps);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = bf16_round(bf16_round(v[i] * rms) * bf16_round(norm_w[d[i]]));
+        for (int i = 0; i < 4; ++i) v[i] = bf16_round(bf16_round(v[i] * rms) * c.nw[i]);
     }
-    if (cosr) {
+    if (has_rope) {
         float r[4];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             // first half: x*cos - pair*sin ; second half: x*cos + pair*sin
-            r[i] = bf16_round(__fadd_rn(__fmul_rn(v[i], cosr[d[i]]), __fmul_rn(-v[i + 2], sinr[d[i]])));
-            r[i + 2] = bf16_round(__fadd_rn(__fmul_rn(v[i + 2], cosr[d[i + 2]]), __fmul_rn(v[i], sinr[d[i + 2]])));
+            r[i] = bf16_round(__fadd_rn(__fmul_rn(v[i], c.cs[i]), __fmul_rn(-v[i + 2], c.sn[i])));
+            r[i + 2] = bf16_round(__fadd_rn(__fmul_rn(v[i + 2], c.cs[i + 2]), __fmul_rn(v[i], c.sn[i + 2])));
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) v[i] = r[i];
@@ -116,6 +139,11 @@ __device__ inline void warp_head_norm_rope(const uint16_t *head, const float *no
     *reinterpret_cast<uint32_t *>(out + 2u * lane) = (uint32_t)f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
     *reinterpret_cast<uint32_t *>(out + 64u + 2u * lane) =
         (uint32_t)f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
+}
+__device__ inline void warp_head_norm_rope(const uint16_t *head, const float *norm_w, const float *cosr,
+                                           const float *sinr, float eps, uint32_t lane, uint16_t *out) {
+    const HeadConsts c = load_head_consts(norm_w, cosr, sinr, lane);
+    warp_head_norm_rope(head, c, norm_w != nullptr, cosr != nullptr, eps, lane, out);
 }
 
 

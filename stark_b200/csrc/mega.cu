@@ -501,7 +501,9 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_token_kernel(const Meg
                     a.scratch = p.attn_scratch;
                     a.counters = nullptr;
                     a.trace = nullptr;
-                    attention_partial<1, kCT>(a, unit % p.attn_splits, unit / p.attn_splits, pos, ash, tid);
+                    AttnPrefetch pf;
+                    attention_prefetch(a, unit % p.attn_splits, unit / p.attn_splits, pos, ash, tid, pf);
+                    attention_partial<1, kCT>(a, unit % p.attn_splits, unit / p.attn_splits, pos, ash, tid, pf);
                     if (tid == 0) atomicAdd(&p.done[i], 1ull);  // attention_partial ends with fence + barrier
                 }
                 break;

@@ -31,6 +31,10 @@ stark_b200_status dmalloc(T **p, size_t count) {
     return STARK_B200_OK;
 }
 
+// Size of the token id space: the embedding table's rows (under tensor parallelism cfg.vocab is the
+// read-out shard of this rank).
+uint32_t input_vocab(const Model *m) { return m->tp.size > 1u ? m->tp_vocab_total : m->cfg.vocab; }
+
 bool pdl_on() {
     static const bool on = [] {
         const char *e = getenv("STARK_B200_PDL");
@@ -79,6 +83,11 @@ Model::~Model() {
     cudaFree(attn_counters);
     cudaFree(partial_max);
     cudaFree(partial_index);
+    if (tp_connected)
+        for (uint32_t r = 0; r < tp.size; ++r)
+            if (r != tp.rank && tp.base[r]) cudaIpcCloseMemHandle(tp.base[r]);
+    cudaFree(tp_local);
+    cudaFree(tp_seq);
     if (host_state) cudaFreeHost(host_state);
     if (host_logits) cudaFreeHost(host_logits);
     if (stream) cudaStreamDestroy(stream);
@@ -144,6 +153,10 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
 
     const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
     m->attn_splits = std::min<uint32_t>(kMaxAttnSplits, std::max<uint32_t>(1u, 296u / c.kv_heads));
+    if (const char *e = getenv("STARK_B200_ATTN_SPLITS")) {  // tuning: CTAs per KV head
+        const int v = atoi(e);
+        if (v >= 1 && v <= (int)kMaxAttnSplits) m->attn_splits = (uint32_t)v;
+    }
     if ((st = dmalloc(&m->state, 1)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->pending, (size_t)c.context_tokens + 1u)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->generated, (size_t)c.context_tokens + 1u)) != STARK_B200_OK) return fail(st);
@@ -159,8 +172,8 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     if ((st = dmalloc(&m->partial_max, 1024)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->partial_index, 1024)) != STARK_B200_OK) return fail(st);
     if (const char *e = getenv("STARK_B200_TRACE")) {
-        if (e[0] == '1') {
-            m->trace_slots = 1u + 5u * c.layers + 2u;
+        if (e[0] == '1') {  // one slot per launch; 7 per layer covers the tensor-parallel sequence too
+            m->trace_slots = 1u + 7u * c.layers + 2u;
             if ((st = dmalloc(&m->trace, m->trace_slots)) != STARK_B200_OK) return fail(st);
         }
     }
@@ -208,7 +221,7 @@ stark_b200_status model_set_matrix(Model *m, uint32_t layer, uint32_t which, QMa
         return STARK_B200_OK;
     };
     if (which == STARK_B200_MAT_EMBED) {
-        stark_b200_status st = put(&m->embed, c.vocab, c.hidden, false);
+        stark_b200_status st = put(&m->embed, input_vocab(m), c.hidden, false);
         if (st == STARK_B200_OK && c.tied) m->lm_head = m->embed;
         return st;
     }
@@ -240,6 +253,17 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
     if ((st = embedding_row_launch(m->embed, m->state, m->h, pdl, s)) != STARK_B200_OK) return st;
     ++n;
     auto slot = [&](uint32_t index) -> TraceSlot * { return m->trace ? m->trace + index : nullptr; };
+    const bool tp = m->tp.size > 1u;
+    // K-split projection: this rank's f32 share goes to its exchange buffer, and the all-reduce
+    // kernel that follows rounds the sum to bf16 and adds the residual on every rank.
+    auto reduce_into_h = [&](QmvArgs &a, uint32_t buf) -> stark_b200_status {
+        a.y = tp_partial(m->tp_local, buf, c.hidden);
+        a.resid = nullptr;
+        a.epilogue = kEpiPartialF32;
+        stark_b200_status r = qmv_launch(a, s);
+        if (r != STARK_B200_OK) return r;
+        return tp_allreduce_residual_launch(m->tp, buf, m->tp_seq, m->h, ctx->error_word, slot(n++), pdl, s);
+    };
     for (uint32_t l = 0; l < c.layers; ++l) {
         auto &L = m->layers[l];
         QmvArgs a{};
@@ -255,7 +279,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.prologue = kProRmsNorm;
         a.norm_weight = L.attn_norm;
         a.epilogue = kEpiStore;
-        a.trace = slot(n);
+        a.trace = slot(n++);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
         // attention with fused QK-norm, RoPE and KV append
         AttnArgs at{};
@@ -277,7 +301,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         at.counters = m->attn_counters;
         at.error_word = ctx->error_word;
         at.pdl = pdl;
-        at.trace = slot(n + 1);
+        at.trace = slot(n++);
         if ((st = attention_decode_launch(at, s)) != STARK_B200_OK) return st;
         // h = bf16(bf16(W_o attn) + h)
         a.matrix = L.o;
@@ -286,8 +310,8 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.resid = m->h;
         a.prologue = kProPlain;
         a.epilogue = kEpiResidual;
-        a.trace = slot(n + 2);
-        if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
+        a.trace = slot(n++);
+        if ((st = tp ? reduce_into_h(a, 0u) : qmv_launch(a, s)) != STARK_B200_OK) return st;
         // act = silu(gate) * up
         a.matrix = L.upgate;
         a.x = m->h;
@@ -295,7 +319,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.prologue = kProRmsNorm;
         a.norm_weight = L.mlp_norm;
         a.epilogue = kEpiSwiGlu;
-        a.trace = slot(n + 3);
+        a.trace = slot(n++);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
         // h = bf16(bf16(W_down act) + h)
         a.matrix = L.down;
@@ -304,9 +328,8 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.resid = m->h;
         a.prologue = kProPlain;
         a.epilogue = kEpiResidual;
-        a.trace = slot(n + 4);
-        if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
-        n += 5;
+        a.trace = slot(n++);
+        if ((st = tp ? reduce_into_h(a, 1u) : qmv_launch(a, s)) != STARK_B200_OK) return st;
     }
     if (full) {
         QmvArgs a{};
@@ -325,11 +348,13 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.partial_index = m->partial_index;
         uint32_t grid = 0;
         a.out_grid = &grid;
-        a.trace = slot(n);
+        a.trace = slot(n++);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
-        if ((st = argmax_finalize_launch(m->partial_max, m->partial_index, grid, m->state, m->generated, true, pdl, s)) != STARK_B200_OK)
-            return st;
-        n += 2;
+        st = tp ? tp_argmax_finalize_launch(m->tp, m->tp_seq, m->partial_max, m->partial_index, grid,
+                                            m->tp_vocab_offset, m->state, m->generated, ctx->error_word, pdl, s)
+                : argmax_finalize_launch(m->partial_max, m->partial_index, grid, m->state, m->generated, true, pdl, s);
+        if (st != STARK_B200_OK) return st;
+        n += 1;
     } else {
         if ((st = ingest_advance_launch(m->state, m->pending, pdl, s)) != STARK_B200_OK) return st;
         n += 1;
@@ -496,9 +521,50 @@ static stark_b200_status capture(Model *m, bool full, cudaGraphExec_t *exec, uin
     return cuda_status(e);
 }
 
+stark_b200_status model_tp_init(Model *m, uint32_t rank, uint32_t size, uint32_t vocab_offset, uint32_t vocab_total,
+                                uint8_t *handle_out) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the interface");
+    if (m->finalized || m->tp_local) return STARK_B200_INVALID_STATE;
+    if (size < 2u || size > kMaxTpRanks || rank >= size || m->cfg.tied || m->cfg.hidden % 4u != 0 ||
+        (uint64_t)vocab_offset + m->cfg.vocab > vocab_total)
+        return STARK_B200_INVALID_ARGUMENT;
+    const size_t bytes = tp_region_bytes(m->cfg.hidden);
+    SB_CUDA(cudaMalloc(&m->tp_local, bytes));
+    SB_CUDA(cudaMemset(m->tp_local, 0, bytes));
+    stark_b200_status st = dmalloc(&m->tp_seq, kTpFlagSets);
+    if (st != STARK_B200_OK) return st;
+    SB_CUDA(cudaMemset(m->tp_seq, 0, kTpFlagSets * 4u));
+    SB_CUDA(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t handle;
+    SB_CUDA(cudaIpcGetMemHandle(&handle, m->tp_local));
+    memcpy(handle_out, &handle, 64);
+    m->tp.rank = rank;
+    m->tp.size = size;
+    m->tp.hidden = m->cfg.hidden;
+    m->tp.base[rank] = m->tp_local;
+    m->tp_vocab_offset = vocab_offset;
+    m->tp_vocab_total = vocab_total;
+    return STARK_B200_OK;
+}
+
+stark_b200_status model_tp_connect(Model *m, const uint8_t *handles) {
+    if (m->finalized || !m->tp_local || m->tp_connected) return STARK_B200_INVALID_STATE;
+    for (uint32_t r = 0; r < m->tp.size; ++r) {
+        if (r == m->tp.rank) continue;
+        cudaIpcMemHandle_t handle;
+        memcpy(&handle, handles + (size_t)r * 64u, 64);
+        void *p = nullptr;
+        SB_CUDA(cudaIpcOpenMemHandle(&p, handle, cudaIpcMemLazyEnablePeerAccess));
+        m->tp.base[r] = static_cast<uint8_t *>(p);
+    }
+    m->tp_connected = true;
+    return STARK_B200_OK;
+}
+
 stark_b200_status model_finalize(Model *m) {
     if (m->finalized) return STARK_B200_INVALID_STATE;
     if (!m->embed || !m->lm_head || !m->final_norm) return STARK_B200_INVALID_STATE;
+    if (m->tp.size > 1u && !m->tp_connected) return STARK_B200_INVALID_STATE;
     for (auto &L : m->layers)
         if (!L.qkv || !L.o || !L.upgate || !L.down || !L.attn_norm || !L.mlp_norm || !L.q_norm || !L.k_norm)
             return STARK_B200_INVALID_STATE;
@@ -511,7 +577,7 @@ stark_b200_status model_finalize(Model *m) {
     SB_CUDA(cudaStreamSynchronize(m->stream));
     if ((st = capture(m, true, &m->step_graph, &m->step_launches)) != STARK_B200_OK) return st;
     if ((st = capture(m, false, &m->ingest_graph, &m->ingest_launches)) != STARK_B200_OK) return st;
-    if (const char *e = getenv("STARK_B200_MEGA")) m->use_mega = e[0] == '1';
+    if (const char *e = getenv("STARK_B200_MEGA")) m->use_mega = e[0] == '1' && m->tp.size <= 1u;
     if (m->use_mega) {
         if (m->trace) {  // one slot per operator instead of one per launch
             cudaFree(m->trace);
@@ -556,7 +622,7 @@ stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count) {
     if (count == 0) return STARK_B200_INVALID_ARGUMENT;
     if (m->position + count > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
     for (size_t i = 0; i < count; ++i)
-        if (ids[i] >= m->cfg.vocab) return STARK_B200_INVALID_ARGUMENT;
+        if (ids[i] >= input_vocab(m)) return STARK_B200_INVALID_ARGUMENT;
     // pending[0 .. count-2] = ids[1 ..]; the ingest-advance kernel pops one per row
     if (count > 1) SB_CUDA(cudaMemcpyAsync(m->pending, ids + 1, (count - 1) * 4, cudaMemcpyHostToDevice, m->stream));
     StepState hs{};
@@ -590,7 +656,7 @@ stark_b200_status model_step(Model *m, uint32_t token, bool chained) {
     if (!m->finalized || m->fenced) return STARK_B200_INVALID_STATE;
     if (m->position + 1 > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
     if (!chained) {
-        if (token >= m->cfg.vocab) return STARK_B200_INVALID_ARGUMENT;
+        if (token >= input_vocab(m)) return STARK_B200_INVALID_ARGUMENT;
         SB_CUDA(cudaMemcpyAsync(&m->state->token, &token, 4, cudaMemcpyHostToDevice, m->stream));
     }
     {

@@ -6,6 +6,7 @@
 #include "mega.cuh"
 #include "ops.cuh"
 #include "qmv.cuh"
+#include "tp.cuh"
 
 namespace sb {
 
@@ -45,6 +46,13 @@ struct Model {
     float *mega_scratch = nullptr;
     MegaParams mega_full{}, mega_ingest{};
     uint32_t step_launches = 0, ingest_launches = 0;
+    // tensor-parallel exchange (tp.size == 0: single GPU).  cfg then holds this rank's shard shapes
+    // (heads, intermediate width, read-out rows); the embedding table is whole on every rank.
+    TpRegion tp{};
+    uint8_t *tp_local = nullptr;   // this rank's exchange region
+    uint32_t *tp_seq = nullptr;    // [kTpFlagSets] exchanges done per flag set
+    uint32_t tp_vocab_offset = 0, tp_vocab_total = 0;
+    bool tp_connected = false;
     StepState *host_state = nullptr;    // pinned
     uint16_t *host_logits = nullptr;    // pinned
     uint64_t position = 0;              // host mirror of state->position
@@ -57,6 +65,12 @@ struct Model {
 stark_b200_status model_create(const stark_b200_dense_config &cfg, Model **out);
 stark_b200_status model_set_matrix(Model *m, uint32_t layer, uint32_t which, QMatrix *q);  // takes ownership
 stark_b200_status model_set_vector(Model *m, uint32_t layer, uint32_t which, const float *data, uint32_t count);
+// Tensor parallelism, between create and finalize: init allocates this rank's exchange region and
+// returns its 64-byte inter-process handle; connect maps the regions of all ranks (handles in rank
+// order, this rank's own entry ignored).  After that finalize and every token are collective calls.
+stark_b200_status model_tp_init(Model *m, uint32_t rank, uint32_t size, uint32_t vocab_offset, uint32_t vocab_total,
+                                uint8_t *handle_out);
+stark_b200_status model_tp_connect(Model *m, const uint8_t *handles);
 stark_b200_status model_finalize(Model *m);
 stark_b200_status model_reset(Model *m);
 stark_b200_status model_rewind(Model *m, uint64_t position);

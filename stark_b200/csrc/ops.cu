@@ -12,21 +12,31 @@ namespace {
 
 // One CTA = (split, KV head), four warps: the split's partial, then the last split of the head to
 // arrive merges all of them (see device_attention.cuh).
-__global__ void __launch_bounds__(kAttnThreads, 3) attention_decode_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kAttnThreads, 5) attention_decode_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t attn_smem[];
     __shared__ uint32_t is_last;
     pdl_launch_dependents();
     const uint32_t tid = threadIdx.x;
     const uint32_t split = blockIdx.x, h = blockIdx.y;
     if (tid == 0 && p.trace) trace_min(&p.trace->start);
-    // Every kernel of the sequence launches its dependents at once, so several later kernels can be
-    // resident and waiting here while the writer of `position` (the end of the previous token) is
-    // still running: the position, and therefore the page range, is read only after the wait.
+    // Before the wait: the cache rows of earlier tokens and the constants of this position do not
+    // depend on the kernel before this one, so their fetch overlaps it.  Inside a recorded token the
+    // position is final here (its writer ran in the previous token's graph).  In an unrecorded sequence
+    // every kernel launches its dependents at once, so several later kernels can be resident and waiting
+    // while the writer of `position` is still running: the position is read again after the wait and
+    // the fetch repeated if it moved.
+    const AttnShared sm = carve_attn_shared(attn_smem);
+    AttnPrefetch pf;
+    attention_prefetch(p, split, h, __ldcg(&p.state->position), sm, tid, pf);
     pdl_wait();
     if (tid == 0 && p.trace) trace_min(&p.trace->ready);
-    const uint32_t pos = p.state->position;
-    const AttnShared sm = carve_attn_shared(attn_smem);
-    attention_partial<0, kAttnThreads>(p, split, h, pos, sm, tid);
+    const uint32_t pos = __ldcg(&p.state->position);
+    if (pos != pf.pos) {  // uniform across the CTA
+        cp_async_wait<0>();
+        __syncthreads();
+        attention_prefetch(p, split, h, pos, sm, tid, pf);
+    }
+    attention_partial<0, kAttnThreads>(p, split, h, pos, sm, tid, pf);
     if (tid == 0) {
         const uint32_t prev = atomicAdd(&p.counters[h], 1u);
         is_last = prev == p.splits - 1u;

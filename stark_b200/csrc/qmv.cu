@@ -101,12 +101,170 @@ __device__ inline void wait_failed(volatile uint32_t *abort_flag, uint32_t *erro
     atomicOr(error_word, kErrMbarTimeout);
 }
 
+// The consumers' prologue: waits for the previous kernel, brings the input row into shared memory as
+// exactly scaled f16 (plus the per-group sums the bias term needs) and returns the factor that undoes
+// the scale.  ROUNDS = chunks of 8 elements a thread keeps in registers (K <= ROUNDS * 2048): the
+// code is straight-line per round, and a short instance matters because every launch runs it cold.
+template <int ROUNDS, bool NORM, bool SPLIT>
+__device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, uint32_t columns, __half *xs, __half *xlo,
+                                            uint16_t *nws, float *xsum, float *xoff, float *wred, float &xunscale) {
+    const uint32_t warp = tid >> 5, lane = tid & 31u;
+    // Before the wait: everything that does not depend on the previous kernel.  The norm weights
+    // are constants, so their bf16-rounded values (normalization.rs:157-161 rounds them before the
+    // product) are staged in shared memory while the previous kernel is still running.
+    const uint32_t chunks = columns / 8u;
+    const bool f32_in = !NORM && p.io_type == STARK_B200_F32;
+    if (NORM) {
+        const float4 *nw = reinterpret_cast<const float4 *>(p.norm_weight);
+        for (uint32_t c = tid; c < chunks; c += kConsumerThreads) {
+            const float4 n0 = nw[2 * c], n1 = nw[2 * c + 1];
+            uint4 o;
+            o.x = (uint32_t)f32_to_bf16_bits(n0.x) | ((uint32_t)f32_to_bf16_bits(n0.y) << 16);
+            o.y = (uint32_t)f32_to_bf16_bits(n0.z) | ((uint32_t)f32_to_bf16_bits(n0.w) << 16);
+            o.z = (uint32_t)f32_to_bf16_bits(n1.x) | ((uint32_t)f32_to_bf16_bits(n1.y) << 16);
+            o.w = (uint32_t)f32_to_bf16_bits(n1.z) | ((uint32_t)f32_to_bf16_bits(n1.w) << 16);
+            reinterpret_cast<uint4 *>(nws)[c] = o;
+        }
+    }
+    pdl_wait();  // the input vector belongs to the previous kernel
+    if (tid == 0 && p.trace) trace_min(&p.trace->ready);
+
+    // One trip to global memory: this thread's chunks of the input row stay in registers for the
+    // whole prologue (up to ROUNDS chunks of 8 elements; the launcher checks the width).
+    float f[ROUNDS][8];
+#pragma unroll
+    for (int r = 0; r < ROUNDS; ++r) {
+        const uint32_t c = tid + r * kConsumerThreads;
+        if (c < chunks) {
+            if (f32_in) {
+                const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
+                const float4 a = x4[2 * c], b = x4[2 * c + 1];
+                f[r][0] = a.x, f[r][1] = a.y, f[r][2] = a.z, f[r][3] = a.w;
+                f[r][4] = b.x, f[r][5] = b.y, f[r][6] = b.z, f[r][7] = b.w;
+            } else {
+                const uint4 v = reinterpret_cast<const uint4 *>(p.x)[c];
+                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    f[r][2 * i] = __uint_as_float(wv[i] << 16);
+                    f[r][2 * i + 1] = __uint_as_float(wv[i] & 0xffff0000u);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) f[r][i] = 0.0f;
+        }
+    }
+    // One block-wide reduction gives both the sum of squares and the magnitude the scaled input can
+    // reach: max |h * w| * rms_inv bounds the normalized values up to their two bf16 roundings.  Each
+    // thread reads back only the norm weights it staged itself, so no barrier is needed before this.
+    float sumsq = 0.0f, vmax = 0.0f;
+    if (NORM) {
+#pragma unroll
+        for (int r = 0; r < ROUNDS; ++r) {
+            const uint32_t c = tid + r * kConsumerThreads;
+            if (c < chunks) {
+                const uint4 nv = reinterpret_cast<const uint4 *>(nws)[c];
+                const uint32_t nwv[4] = {nv.x, nv.y, nv.z, nv.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float a = f[r][2 * i], b = f[r][2 * i + 1];
+                    sumsq = fmaf(a, a, sumsq);
+                    sumsq = fmaf(b, b, sumsq);
+                    vmax = fmaxf(vmax, fabsf(a * __uint_as_float(nwv[i] << 16)));
+                    vmax = fmaxf(vmax, fabsf(b * __uint_as_float(nwv[i] & 0xffff0000u)));
+                }
+            }
+        }
+        sumsq = warp_sum(sumsq);
+    } else {
+#pragma unroll
+        for (int r = 0; r < ROUNDS; ++r)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) vmax = fmaxf(vmax, fabsf(f[r][i]));
+    }
+    vmax = warp_max(vmax);
+    if (lane == 0) {
+        wred[warp] = sumsq;
+        wred[kConsumerWarps + warp] = vmax;
+    }
+    named_bar_sync(1, kConsumerThreads);
+    sumsq = 0.0f;
+    vmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kConsumerWarps; ++i) {
+        sumsq += wred[i];
+        vmax = fmaxf(vmax, wred[kConsumerWarps + i]);
+    }
+    if (NORM) {
+        const float rms_inv = 1.0f / sqrtf(sumsq / (float)columns + p.eps);
+        vmax *= rms_inv * 1.015625f;
+#pragma unroll
+        for (int r = 0; r < ROUNDS; ++r) {
+            const uint32_t c = tid + r * kConsumerThreads;
+            if (c < chunks) {
+                const uint4 nv = reinterpret_cast<const uint4 *>(nws)[c];
+                const uint32_t nwv[4] = {nv.x, nv.y, nv.z, nv.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    // bf16(normalized) * bf16(scale), product rounded to bf16
+                    f[r][2 * i] = bf16_round(bf16_round(f[r][2 * i] * rms_inv) * __uint_as_float(nwv[i] << 16));
+                    f[r][2 * i + 1] =
+                        bf16_round(bf16_round(f[r][2 * i + 1] * rms_inv) * __uint_as_float(nwv[i] & 0xffff0000u));
+                }
+            }
+        }
+    }
+    // Exact power-of-two scale: the largest element lands in [2^14, 2^15).
+    int shift = 14 - ((int)((__float_as_uint(vmax) >> 23) & 0xffu) - 127);
+    shift = max(-100, min(100, shift));
+    if (!(vmax > 0.0f) || !isfinite(vmax)) shift = 0;
+    const float xscale = __uint_as_float((uint32_t)(shift + 127) << 23);
+    xunscale = __uint_as_float((uint32_t)(127 - shift) << 23);
+
+    // Scaled f16 values, per-group sums of the input (for the bias term) and, for FOLD, -64 * the
+    // per-group sum of the f16 values the tensor core will see.
+#pragma unroll
+    for (int r = 0; r < ROUNDS; ++r) {
+        const uint32_t c = tid + r * kConsumerThreads;
+        float s8 = 0.0f, h8 = 0.0f;
+        __half hh[8], hl[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            s8 += f[r][i];
+            const float sv = f[r][i] * xscale;
+            hh[i] = __float2half_rn(sv);
+            h8 += __half2float(hh[i]);
+            if (SPLIT) {
+                hl[i] = __float2half_rn(sv - __half2float(hh[i]));
+                h8 += __half2float(hl[i]);
+            }
+        }
+        if (c < chunks) {
+            reinterpret_cast<uint4 *>(xs)[c] = *reinterpret_cast<uint4 *>(hh);
+            if (SPLIT) reinterpret_cast<uint4 *>(xlo)[c] = *reinterpret_cast<uint4 *>(hl);
+        }
+#pragma unroll
+        for (int o = 1; o < 8; o <<= 1) {
+            s8 += __shfl_xor_sync(0xffffffffu, s8, o);
+            h8 += __shfl_xor_sync(0xffffffffu, h8, o);
+        }
+        if (c < chunks && (lane & 7u) == 0) {
+            xsum[c >> 3] = s8;
+            xoff[c >> 3] = -64.0f * h8;
+        }
+    }
+    named_bar_sync(1, kConsumerThreads);
+    if (tid == 0 && p.trace) trace_max(&p.trace->compute);
+
+}
+
 // SPLIT: the input is f32 and is carried as two f16 terms (hi + lo) so that ~22 mantissa bits
 //        survive; bf16 inputs need one term.
 // RPW:   records per consumer warp per ring stage (stage = 8 * RPW records unless PRED).
 // PRED:  the stage holds fewer than 8 * RPW records (group counts that are not a multiple of 8).
 template <bool SPLIT, int RPW, bool PRED, bool FOLD>
-__global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) {
+__global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t columns = p.groups * 64u;
     const SmemLayout L = smem_layout(p.num_stages, p.stage_capacity, columns, SPLIT, p.prologue == kProRmsNorm);
@@ -220,6 +378,8 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) 
                         if (orow < p.rows / 2u)
                             reinterpret_cast<uint16_t *>(p.y)[orow] = f32_to_bf16_bits(held * activated);
                     }
+                } else if (p.epilogue == kEpiPartialF32) {
+                    if (valid) reinterpret_cast<float *>(p.y)[row] = v;
                 } else {  // kEpiLogits
                     if (valid) {
                         const uint16_t hb = f32_to_bf16_bits(v);
@@ -256,133 +416,15 @@ __global__ void __launch_bounds__(kThreads, 2) qmv_a4_kernel(const QmvParams p) 
     }
 
     // ---------------- consumers ----------------
-    // Before the wait: everything that does not depend on the previous kernel.  The norm weights
-    // are constants, so their bf16-rounded values (normalization.rs:157-161 rounds them before the
-    // product) are staged in shared memory while the previous kernel is still running.
-    const uint32_t chunks = columns / 8u;
-    const bool f32_in = p.io_type == STARK_B200_F32 && p.prologue == kProPlain;
-    if (p.prologue == kProRmsNorm) {
-        const float4 *nw = reinterpret_cast<const float4 *>(p.norm_weight);
-        for (uint32_t c = tid; c < chunks; c += kConsumerThreads) {
-            const float4 n0 = nw[2 * c], n1 = nw[2 * c + 1];
-            uint4 o;
-            o.x = (uint32_t)f32_to_bf16_bits(n0.x) | ((uint32_t)f32_to_bf16_bits(n0.y) << 16);
-            o.y = (uint32_t)f32_to_bf16_bits(n0.z) | ((uint32_t)f32_to_bf16_bits(n0.w) << 16);
-            o.z = (uint32_t)f32_to_bf16_bits(n1.x) | ((uint32_t)f32_to_bf16_bits(n1.y) << 16);
-            o.w = (uint32_t)f32_to_bf16_bits(n1.z) | ((uint32_t)f32_to_bf16_bits(n1.w) << 16);
-            reinterpret_cast<uint4 *>(nws)[c] = o;
-        }
+    float xunscale;
+    const bool norm = p.prologue == kProRmsNorm;
+    if (columns <= 2u * kConsumerThreads * 8u) {
+        if (norm) stage_input<2, true, SPLIT>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        else stage_input<2, false, SPLIT>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+    } else {
+        if (norm) stage_input<kMaxRounds, true, SPLIT>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        else stage_input<kMaxRounds, false, SPLIT>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
     }
-    pdl_wait();  // the input vector belongs to the previous kernel
-    if (tid == 0 && p.trace) trace_min(&p.trace->ready);
-
-    // One trip to global memory: this thread's chunks of the input row stay in registers for the
-    // whole prologue (up to kMaxRounds chunks of 8 elements; the launcher checks the width).
-    float f[kMaxRounds][8];
-#pragma unroll
-    for (int r = 0; r < kMaxRounds; ++r) {
-        const uint32_t c = tid + r * kConsumerThreads;
-        if (c < chunks) {
-            if (f32_in) {
-                const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
-                const float4 a = x4[2 * c], b = x4[2 * c + 1];
-                f[r][0] = a.x, f[r][1] = a.y, f[r][2] = a.z, f[r][3] = a.w;
-                f[r][4] = b.x, f[r][5] = b.y, f[r][6] = b.z, f[r][7] = b.w;
-            } else {
-                const uint4 v = reinterpret_cast<const uint4 *>(p.x)[c];
-                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    f[r][2 * i] = __uint_as_float(wv[i] << 16);
-                    f[r][2 * i + 1] = __uint_as_float(wv[i] & 0xffff0000u);
-                }
-            }
-        } else {
-#pragma unroll
-            for (int i = 0; i < 8; ++i) f[r][i] = 0.0f;
-        }
-    }
-    if (p.prologue == kProRmsNorm) {
-        float sumsq = 0.0f;
-#pragma unroll
-        for (int r = 0; r < kMaxRounds; ++r)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) sumsq += f[r][i] * f[r][i];
-        sumsq = warp_sum(sumsq);
-        if (lane == 0) wred[warp] = sumsq;
-        named_bar_sync(1, kConsumerThreads);  // also orders the staging of the norm weights
-        sumsq = 0.0f;
-#pragma unroll
-        for (int i = 0; i < kConsumerWarps; ++i) sumsq += wred[i];
-        const float rms_inv = 1.0f / sqrtf(sumsq / (float)columns + p.eps);
-#pragma unroll
-        for (int r = 0; r < kMaxRounds; ++r) {
-            const uint32_t c = tid + r * kConsumerThreads;
-            if (c < chunks) {
-                const uint4 nv = reinterpret_cast<const uint4 *>(nws)[c];
-                const uint32_t nwv[4] = {nv.x, nv.y, nv.z, nv.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    // bf16(normalized) * bf16(scale), product rounded to bf16
-                    f[r][2 * i] = bf16_round(bf16_round(f[r][2 * i] * rms_inv) * __uint_as_float(nwv[i] << 16));
-                    f[r][2 * i + 1] =
-                        bf16_round(bf16_round(f[r][2 * i + 1] * rms_inv) * __uint_as_float(nwv[i] & 0xffff0000u));
-                }
-            }
-        }
-    }
-    float vmax = 0.0f;
-#pragma unroll
-    for (int r = 0; r < kMaxRounds; ++r)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) vmax = fmaxf(vmax, fabsf(f[r][i]));
-    vmax = warp_max(vmax);
-    if (lane == 0) wred[kConsumerWarps + warp] = vmax;
-    named_bar_sync(1, kConsumerThreads);
-    vmax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < kConsumerWarps; ++i) vmax = fmaxf(vmax, wred[kConsumerWarps + i]);
-    // Exact power-of-two scale: the largest element lands in [2^14, 2^15).
-    int shift = 14 - ((int)((__float_as_uint(vmax) >> 23) & 0xffu) - 127);
-    shift = max(-100, min(100, shift));
-    if (!(vmax > 0.0f) || !isfinite(vmax)) shift = 0;
-    const float xscale = __uint_as_float((uint32_t)(shift + 127) << 23);
-    const float xunscale = __uint_as_float((uint32_t)(127 - shift) << 23);
-
-    // Scaled f16 values, per-group sums of the input (for the bias term) and, for FOLD, -64 * the
-    // per-group sum of the f16 values the tensor core will see.
-#pragma unroll
-    for (int r = 0; r < kMaxRounds; ++r) {
-        const uint32_t c = tid + r * kConsumerThreads;
-        float s8 = 0.0f, h8 = 0.0f;
-        __half hh[8], hl[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            s8 += f[r][i];
-            const float sv = f[r][i] * xscale;
-            hh[i] = __float2half_rn(sv);
-            h8 += __half2float(hh[i]);
-            if (SPLIT) {
-                hl[i] = __float2half_rn(sv - __half2float(hh[i]));
-                h8 += __half2float(hl[i]);
-            }
-        }
-        if (c < chunks) {
-            reinterpret_cast<uint4 *>(xs)[c] = *reinterpret_cast<uint4 *>(hh);
-            if (SPLIT) reinterpret_cast<uint4 *>(xlo)[c] = *reinterpret_cast<uint4 *>(hl);
-        }
-#pragma unroll
-        for (int o = 1; o < 8; o <<= 1) {
-            s8 += __shfl_xor_sync(0xffffffffu, s8, o);
-            h8 += __shfl_xor_sync(0xffffffffu, h8, o);
-        }
-        if (c < chunks && (lane & 7u) == 0) {
-            xsum[c >> 3] = s8;
-            xoff[c >> 3] = -64.0f * h8;
-        }
-    }
-    named_bar_sync(1, kConsumerThreads);
-    if (tid == 0 && p.trace) trace_max(&p.trace->compute);
 
     // Main loop: no block-wide barrier from here on.
     const uint32_t g = lane >> 2, t = lane & 3u;

@@ -55,6 +55,7 @@ enum QmvEpilogue : uint32_t {
     kEpiResidual = 1,  // y[row] = bf16(bf16(value) + resid[row])   (resid may alias y)
     kEpiSwiGlu = 2,    // pair_halves matrix: y[r] = bf16(up[r] * bf16(silu(gate[r])))
     kEpiLogits = 3,    // y[row] = bf16(value) and a per-CTA (max, first index) partial
+    kEpiPartialF32 = 4,  // y[row] = value as f32, bf16 input: this rank's share of a K-split product
 };
 
 struct QmvArgs {

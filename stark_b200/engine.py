@@ -15,12 +15,80 @@ from . import _lib
 from ._lib import StarkB200Error, check
 
 
+def _rows(t: dict, lo: int, hi: int) -> dict:
+    """Rows [lo, hi) of a quantized matrix in the MLX layout (codes and planes are row-major)."""
+    return dict(t, codes=t["codes"][lo:hi], scales=t["scales"][lo:hi], biases=t["biases"][lo:hi], n=hi - lo)
+
+
+def _columns(t: dict, lo: int, hi: int) -> dict:
+    """Columns [lo, hi) of a quantized matrix; the cut must fall on quantization-group boundaries."""
+    g, per_word = t["group"], 32 // t["bits"]
+    if lo % g or hi % g:
+        raise ValueError("a column shard must consist of whole quantization groups")
+    return dict(t, codes=t["codes"][:, lo // per_word:hi // per_word], scales=t["scales"][:, lo // g:hi // g],
+                biases=t["biases"][:, lo // g:hi // g], k=hi - lo)
+
+
+def _stack(parts: list) -> dict:
+    return dict(parts[0], codes=np.concatenate([p["codes"] for p in parts]),
+                scales=np.concatenate([p["scales"] for p in parts]),
+                biases=np.concatenate([p["biases"] for p in parts]), n=sum(p["n"] for p in parts))
+
+
+def vocab_shard(vocab: int, rank: int, ranks: int) -> tuple[int, int]:
+    """Rows [lo, hi) of the read-out matrix owned by `rank`: equal runs of whole 16-row tiles, the
+    last rank taking what is left."""
+    per = -(-vocab // (16 * ranks)) * 16
+    lo = min(vocab, rank * per)
+    return lo, min(vocab, lo + per)
+
+
+def shard_dense(cfg: dict, weights: dict, rank: int, ranks: int) -> tuple[dict, dict, int]:
+    """This rank's share of a dense decoder under tensor parallelism.
+
+    qkv and up||gate are cut by output rows (whole heads, the KV cache follows the KV heads), the o- and
+    down-projections by input columns (whole quantization groups), the read-out by vocabulary rows; the
+    embedding table and all norm vectors stay whole.  Returns (local config, local weights, first
+    vocabulary row of the read-out shard).  The reference runs on one device; this is how the same
+    graph (crates/stark-engine/src/encodable_block/transformer_layer.rs:549-659) is spread over several.
+    """
+    hq, hkv, hd, inter = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["inter"]
+    if hq % ranks or hkv % ranks or inter % (16 * ranks) or (inter // ranks) % 64:
+        raise ValueError(f"{ranks} ranks do not divide heads {hq}/{hkv} or width {inter} into whole shards")
+    ql, kl, il = hq // ranks, hkv // ranks, inter // ranks
+    lo, hi = vocab_shard(cfg["vocab"], rank, ranks)
+    if hi <= lo:
+        raise ValueError("empty read-out shard")
+    local = dict(cfg, q_heads=ql, kv_heads=kl, inter=il, vocab=hi - lo, tied=False, vocab_total=cfg["vocab"])
+    k0, v0 = hq * hd, (hq + hkv) * hd
+    layers = []
+    for lw in weights["layers"]:
+        qkv = _stack([_rows(lw["qkv"], rank * ql * hd, (rank + 1) * ql * hd),
+                      _rows(lw["qkv"], k0 + rank * kl * hd, k0 + (rank + 1) * kl * hd),
+                      _rows(lw["qkv"], v0 + rank * kl * hd, v0 + (rank + 1) * kl * hd)])
+        upgate = _stack([_rows(lw["upgate"], rank * il, (rank + 1) * il),
+                         _rows(lw["upgate"], inter + rank * il, inter + (rank + 1) * il)])
+        layers.append(dict(lw, qkv=qkv, upgate=upgate, o=_columns(lw["o"], rank * ql * hd, (rank + 1) * ql * hd),
+                           down=_columns(lw["down"], rank * il, (rank + 1) * il)))
+    out = dict(weights, layers=layers, lm_head=_rows(weights["lm_head"], lo, hi))
+    return local, out, lo
+
+
+class TensorParallel:
+    """Rank layout of a tensor-parallel group plus the one host-side collective the engine needs:
+    ``all_gather(bytes) -> [bytes per rank]`` (for example ``torch.distributed.all_gather_object``)."""
+
+    def __init__(self, rank: int, ranks: int, all_gather):
+        self.rank, self.ranks, self.all_gather = int(rank), int(ranks), all_gather
+
+
 class DenseModel:
     PREFIX_CHUNK_TOKENS = 1024  # crates/stark-generate/src/prefix_cache.rs:14
 
     def __init__(self, cfg: dict, context_tokens: int):
         self.cfg = dict(cfg)
         self.context_tokens = int(context_tokens)
+        self.tp = None
         self._h = C.c_void_p()
         c = _lib.DenseConfig(C.sizeof(_lib.DenseConfig), _lib.ABI_VERSION, cfg["layers"], cfg["hidden"],
                              cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["inter"], cfg["vocab"],
@@ -44,9 +112,25 @@ class DenseModel:
               "model_set_vector")
 
     @classmethod
-    def load(cls, cfg: dict, weights: dict, context_tokens: int) -> "DenseModel":
-        """Build from in-memory tensors in the reference's MLX layout (see ``stark_b200.synthetic``)."""
+    def load(cls, cfg: dict, weights: dict, context_tokens: int, tp: "TensorParallel | None" = None) -> "DenseModel":
+        """Build from in-memory tensors in the reference's MLX layout (see ``stark_b200.synthetic``).
+
+        With ``tp`` the call is collective: every rank passes the WHOLE model's config and weights and
+        keeps its own shard (``shard_dense``); the ranks' exchange buffers are connected before the
+        launch sequences are recorded.
+        """
+        if tp is not None and tp.ranks > 1:
+            cfg, weights, vocab_offset = shard_dense(cfg, weights, tp.rank, tp.ranks)
+        else:
+            tp = None
         m = cls(cfg, context_tokens)
+        if tp is not None:
+            m.tp, m.vocab_offset, m.vocab_total = tp, vocab_offset, cfg["vocab_total"]
+            handle = (C.c_uint8 * 64)()
+            check(_lib.load().stark_b200_model_tp_init(m._h, tp.rank, tp.ranks, vocab_offset, cfg["vocab_total"],
+                                                       handle), "model_tp_init")
+            handles = b"".join(tp.all_gather(bytes(handle)))
+            check(_lib.load().stark_b200_model_tp_connect(m._h, handles, len(handles)), "model_tp_connect")
         m._set_matrix(0, _lib.MAT_EMBED, weights["embed"])
         if not cfg["tied"]:
             m._set_matrix(0, _lib.MAT_LM_HEAD, weights["lm_head"])
@@ -60,8 +144,17 @@ class DenseModel:
             m._set_vector(i, _lib.VEC_MLP_NORM, lw["mlp_norm"])
             m._set_vector(i, _lib.VEC_Q_NORM, lw["q_norm"])
             m._set_vector(i, _lib.VEC_K_NORM, lw["k_norm"])
+        if tp is not None:
+            tp.all_gather(b"")  # every rank has uploaded its shard: the recording pass below is collective
         check(_lib.load().stark_b200_model_finalize(m._h), "model_finalize")
         return m
+
+    def _gather_vocab(self, local: np.ndarray) -> np.ndarray:
+        """Whole-vocabulary vector from the ranks' read-out shards (identity on one GPU)."""
+        if self.tp is None:
+            return local
+        parts = self.tp.all_gather(local.tobytes())
+        return np.concatenate([np.frombuffer(p, local.dtype) for p in parts])
 
     # ------------------------------------------------------------------ token loop
     def reset(self):
@@ -76,6 +169,10 @@ class DenseModel:
 
     def prefill(self, token_ids) -> None:
         ids = np.ascontiguousarray(token_ids, np.uint32)
+        if self.tp is not None:
+            # Ranks wait for one another on the device with a time limit: line the hosts up where a
+            # request starts, so that host-side skew (tokenising, scoring) is not charged to that limit.
+            self.tp.all_gather(b"")
         self._guard(_lib.load().stark_b200_prefill(self._h, ids.ctypes.data, ids.size), "prefill")
 
     def ingest_prefix(self, token_ids) -> None:
@@ -92,14 +189,17 @@ class DenseModel:
     def logits(self) -> np.ndarray:
         out = np.empty(self.cfg["vocab"], np.float32)
         self._guard(_lib.load().stark_b200_readout_f32(self._h, out.ctypes.data, out.size), "readout_f32")
-        return out
+        return self._gather_vocab(out)
 
     def logits_bf16(self) -> np.ndarray:
         out = np.empty(self.cfg["vocab"], np.uint16)
         self._guard(_lib.load().stark_b200_readout_bf16(self._h, out.ctypes.data, out.size), "readout_bf16")
-        return out
+        return self._gather_vocab(out)
 
     def log_probabilities(self) -> np.ndarray:
+        if self.tp is not None:  # normalise over the gathered vocabulary with the same f64 kernel
+            from . import ops
+            return ops.log_softmax(self.logits()).astype(np.float32)
         out = np.empty(self.cfg["vocab"], np.float32)
         self._guard(_lib.load().stark_b200_readout_logprobs_f32(self._h, out.ctypes.data, out.size),
                     "readout_logprobs_f32")
@@ -148,13 +248,20 @@ class DenseModel:
     def position(self) -> int:
         return int(self.info().position)
 
-    def close(self):
+    def close(self, collective: bool = True):
+        if self._h and self._h.value and self.tp is not None and collective:
+            # peers read this rank's exchange buffers: nobody unmaps before everybody is idle
+            try:
+                _lib.load().stark_b200_drain(self._h)
+                self.tp.all_gather(b"")
+            except Exception:
+                pass
         if self._h and self._h.value:
             _lib.load().stark_b200_destroy(C.byref(self._h))
 
     def __del__(self):
         try:
-            self.close()
+            self.close(collective=False)
         except Exception:
             pass
 

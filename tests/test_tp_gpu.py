@@ -1,0 +1,114 @@
+"""Tensor-parallel decode on two GPUs against the CPU oracle and against the single-GPU engine.
+
+The test launches one process per GPU (this file is also the rank program); it is skipped on a box
+with fewer than two GPUs.  Ranks rendezvous over gloo on 127.0.0.1: the host side only moves the
+64-byte buffer handles and read-out shards, the per-token exchange happens on the device.
+"""
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _gpu_count() -> int:
+    import ctypes as C
+    from stark_b200 import _lib
+    n = C.c_int32(0)
+    return n.value if _lib.load().stark_b200_device_count(C.byref(n)) == 0 else 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("config", ["tiny", "small"])
+def test_two_ranks_match_oracle_and_single_gpu(config):
+    if _gpu_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), str(Path(__file__).resolve()), config]
+    res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "TP-OK" in res.stdout
+
+
+def _rank_main(config: str) -> None:
+    sys.path.insert(0, str(ROOT))
+    import ctypes as C
+    import torch.distributed as dist
+    from oracle import oracle as O
+    from stark_b200 import _lib, synthetic as S
+    from stark_b200.engine import DenseModel, TensorParallel
+    from stark_b200.ops import take_device_error
+    from tests.test_model_gpu import assert_logits_accepted
+
+    rank, ranks = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    dist.init_process_group("gloo", rank=rank, world_size=ranks)
+    _lib.check(_lib.load().stark_b200_set_device(int(os.environ.get("LOCAL_RANK", rank))), "set_device")
+
+    def all_gather(blob: bytes):
+        out = [None] * ranks
+        dist.all_gather_object(out, blob)
+        return out
+
+    cfg = S.CONFIGS[config]
+    w = S.dense_weights(cfg, seed=0)
+    context = 256
+    model = DenseModel.load(cfg, w, context, tp=TensorParallel(rank, ranks, all_gather))
+    info = model.info()
+    assert info.launches_per_step == 1 + 7 * cfg["layers"] + 2  # two exchange kernels per layer
+
+    prompt = S.prompt(cfg, 70, seed=5)  # crosses a KV page boundary
+    model.prefill(prompt)
+    logits = model.logits_bf16()        # gathered from the ranks' vocabulary shards
+    assert logits.size == cfg["vocab"]
+    first = model.argmax()
+    assert first == O.argmax_bf16(logits)  # the cross-shard pick is the first index of the global maximum
+    steps = 24
+    tokens = model.generate_greedy(steps)
+    model.drain()
+    assert take_device_error() == 0
+    assert int(tokens[0]) == first
+    everyone = all_gather(tokens.tobytes())
+    assert all(t == everyone[0] for t in everyone)  # all ranks chose the same tokens
+
+    if rank == 0:
+        oracle = O.DenseOracle(cfg, w, capacity=context)
+        for t in prompt[:-1]:
+            oracle.ingest(int(t))
+        assert_logits_accepted(oracle.step(int(prompt[-1])), logits)
+        agree, tok = 0, int(tokens[0])
+        for i in range(steps):  # teacher-forced on the engine's tokens
+            agree += int(O.argmax_bf16(oracle.step(tok)) == int(tokens[i + 1]))
+            tok = int(tokens[i + 1])
+        assert agree / steps >= 0.95, agree
+        # the same model on one GPU: logits within the acceptance, and the same first token
+        single = DenseModel.load(cfg, w, context)
+        single.prefill(prompt)
+        assert_logits_accepted(single.logits_bf16(), logits)
+        single.close()
+    # host-fed steps follow the same path as the device-chained ones (prefill lines the ranks up
+    # again after rank 0's checks)
+    model.reset()
+    model.prefill(prompt)
+    tok, fed = model.argmax(), []
+    for _ in range(4):
+        fed.append(tok)
+        model.step_async(tok)
+        tok = model.argmax()
+    assert fed == tokens[:4].tolist()
+    model.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("TP-OK", config, flush=True)
+
+
+if __name__ == "__main__":
+    _rank_main(sys.argv[1])

@@ -1,0 +1,116 @@
+"""Host side of the tensor-parallel path on CPU: two gloo ranks shard the same model, and the oracle's
+matvecs over the shards must reassemble the unsharded results (row splits exactly, column splits up to
+f32 summation order, the vocabulary split to the same first index of the maximum)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from stark_b200 import synthetic as S
+from stark_b200.engine import TensorParallel, shard_dense, vocab_shard
+
+
+def test_vocab_shards_tile_the_vocabulary():
+    for vocab, ranks in [(151936, 8), (151936, 2), (1024, 2), (1000, 4), (48, 4)]:
+        spans = [vocab_shard(vocab, r, ranks) for r in range(ranks)]
+        assert spans[0][0] == 0 and spans[-1][1] == vocab
+        for (a, b), (c, d) in zip(spans, spans[1:]):
+            assert b == c and a % 16 == 0 and c % 16 == 0
+
+
+def test_indivisible_shapes_are_refused():
+    cfg = S.CONFIGS["tiny"]
+    w = S.dense_weights(cfg, seed=0)
+    with pytest.raises(ValueError):
+        shard_dense(cfg, w, 0, 4)  # 2 KV heads over 4 ranks
+    with pytest.raises(ValueError):
+        shard_dense(dict(cfg, inter=320), w, 0, 2)  # 160 columns: not whole 64-wide groups
+
+
+def _mv(t, x):
+    return O.affine_matvec_f32(t["codes"], t["scales"], t["biases"], 30, x, t["n"], t["k"])
+
+
+def _worker(rank: int, ranks: int, port: int, failures):
+    import torch.distributed as dist
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=ranks)
+
+        def all_gather(blob: bytes):
+            out = [None] * ranks
+            dist.all_gather_object(out, blob)
+            return out
+
+        tp = TensorParallel(rank, ranks, all_gather)
+        cfg = S.CONFIGS["tiny"]
+        w = S.dense_weights(cfg, seed=0)  # every rank draws the same whole model
+        local, lw, vocab_offset = shard_dense(cfg, w, rank, ranks)
+        rng = np.random.default_rng(7)
+        hd, hq, hkv, inter = cfg["head_dim"], cfg["q_heads"], cfg["kv_heads"], cfg["inter"]
+        L, F = lw["layers"][0], w["layers"][0]
+        x = rng.standard_normal(cfg["hidden"]).astype(np.float32)
+
+        # row splits: each rank's outputs are a subset of the unsharded outputs, bit for bit
+        full = _mv(F["qkv"], x)
+        mine = _mv(L["qkv"], x)
+        ql, kl = local["q_heads"] * hd, local["kv_heads"] * hd
+        want = np.concatenate([full[rank * ql:(rank + 1) * ql], full[hq * hd + rank * kl:hq * hd + (rank + 1) * kl],
+                               full[(hq + hkv) * hd + rank * kl:(hq + hkv) * hd + (rank + 1) * kl]])
+        assert np.array_equal(mine.view(np.uint32), want.view(np.uint32))
+        full = _mv(F["upgate"], x)
+        mine = _mv(L["upgate"], x)
+        il = local["inter"]
+        want = np.concatenate([full[rank * il:(rank + 1) * il], full[inter + rank * il:inter + (rank + 1) * il]])
+        assert np.array_equal(mine.view(np.uint32), want.view(np.uint32))
+
+        # column splits: the ranks' partial products sum to the unsharded product
+        for name, width, lo in (("o", hq * hd, rank * ql), ("down", inter, rank * il)):
+            a = rng.standard_normal(width).astype(np.float32)
+            part = _mv(L[name], a[lo:lo + L[name]["k"]])
+            parts = [np.frombuffer(b, np.float32) for b in tp.all_gather(part.tobytes())]
+            total = np.sum(parts, axis=0, dtype=np.float32)
+            full = _mv(F[name], a)
+            np.testing.assert_allclose(total, full, rtol=0, atol=2e-5 * np.abs(full).max() + 1e-6)
+
+        # vocabulary split: (max, first index) per shard reduces to the unsharded greedy token
+        h = rng.standard_normal(cfg["hidden"]).astype(np.float32)
+        full = O.f32_to_bf16(_mv(w["lm_head"], h))
+        full[[5, 900]] = O.f32_to_bf16(np.float32([abs(O.bf16_to_f32(full)).max() * 2 + 1]))[0]  # a tie across shards
+        lo, hi = vocab_shard(cfg["vocab"], rank, ranks)
+        assert lo == vocab_offset and local["vocab"] == hi - lo and local["vocab_total"] == cfg["vocab"]
+        shard = full[lo:hi]
+        cand = (float(O.bf16_to_f32(shard).max()), lo + O.argmax_bf16(shard))
+        cands = [tuple(np.frombuffer(b, np.float64)) for b in tp.all_gather(np.array(cand, np.float64).tobytes())]
+        best = max(cands, key=lambda c: (c[0], -c[1]))
+        assert int(best[1]) == O.argmax_bf16(full) == 5
+        dist.barrier()
+        dist.destroy_process_group()
+    except BaseException as e:  # surfaced by the parent
+        failures.put(f"rank {rank}: {type(e).__name__}: {e}")
+        raise
+
+
+def test_two_gloo_ranks_reassemble_the_unsharded_results():
+    import torch.multiprocessing as mp
+    O.lib()  # build the oracle once, before the ranks race for it
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    failures = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, failures)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+    msgs = []
+    while not failures.empty():
+        msgs.append(failures.get())
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            msgs.append("a rank did not finish")
+    assert not msgs and all(p.exitcode == 0 for p in procs), msgs
