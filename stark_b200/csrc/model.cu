@@ -75,6 +75,7 @@ Model::~Model() {
     cudaFree(mega_done);
     cudaFree(mega_scratch);
     cudaFree(h);
+    cudaFree(h_alt);
     cudaFree(qkv);
     cudaFree(attn);
     cudaFree(act);
@@ -152,7 +153,10 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     }
 
     const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
-    m->attn_splits = std::min<uint32_t>(kMaxAttnSplits, std::max<uint32_t>(1u, 296u / c.kv_heads));
+    // CTAs per KV head: at most ~1.3 attention CTAs per SM in total.  One of them fits beside the two
+    // resident CTAs of the matvec before it and fetches its cache tiles while that matvec runs; more
+    // splits than that start cold.
+    m->attn_splits = std::min<uint32_t>(kMaxAttnSplits, std::max<uint32_t>(1u, 192u / c.kv_heads));
     if (const char *e = getenv("STARK_B200_ATTN_SPLITS")) {  // tuning: CTAs per KV head
         const int v = atoi(e);
         if (v >= 1 && v <= (int)kMaxAttnSplits) m->attn_splits = (uint32_t)v;
@@ -161,6 +165,7 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     if ((st = dmalloc(&m->pending, (size_t)c.context_tokens + 1u)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->generated, (size_t)c.context_tokens + 1u)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->h, c.hidden)) != STARK_B200_OK) return fail(st);
+    if ((st = dmalloc(&m->h_alt, c.hidden)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->qkv, qkv_n)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->attn, c.q_heads * kHeadDim)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->act, c.inter)) != STARK_B200_OK) return fail(st);
@@ -172,8 +177,8 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     if ((st = dmalloc(&m->partial_max, 1024)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->partial_index, 1024)) != STARK_B200_OK) return fail(st);
     if (const char *e = getenv("STARK_B200_TRACE")) {
-        if (e[0] == '1') {  // one slot per launch; 7 per layer covers the tensor-parallel sequence too
-            m->trace_slots = 1u + 7u * c.layers + 2u;
+        if (e[0] == '1') {  // one slot per launch
+            m->trace_slots = 1u + 5u * c.layers + 2u;
             if ((st = dmalloc(&m->trace, m->trace_slots)) != STARK_B200_OK) return fail(st);
         }
     }
@@ -254,15 +259,24 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
     ++n;
     auto slot = [&](uint32_t index) -> TraceSlot * { return m->trace ? m->trace + index : nullptr; };
     const bool tp = m->tp.size > 1u;
-    // K-split projection: this rank's f32 share goes to its exchange buffer, and the all-reduce
-    // kernel that follows rounds the sum to bf16 and adds the residual on every rank.
-    auto reduce_into_h = [&](QmvArgs &a, uint32_t buf) -> stark_b200_status {
-        a.y = tp_partial(m->tp_local, buf, c.hidden);
+    // Tensor parallel: a K-split projection pushes its share to every rank and the next matvec sums
+    // the shares, adds the residual and stores the new residual stream into the other of two buffers
+    // (its own blocks still read the old one).  2 exchanges per layer; exchange 2l+1 (after `down`) is
+    // consumed by the next layer's qkv, the last one by the read-out matvec or the ingest close.
+    const uint32_t per_token = 2u * c.layers;
+    uint32_t *tokens = m->tp_seq;
+    uint16_t *hcur = m->h, *hnext = m->h_alt;
+    QmvExchange hooks{};
+    auto consume = [&](QmvArgs &a, uint32_t index) {
+        hooks = tp_consumer_hooks(m->tp, index, per_token, tokens, hnext);
+        a.exchange = &hooks;
+        std::swap(hcur, hnext);  // after this matvec the residual stream lives in the other buffer
+    };
+    auto produce = [&](QmvArgs &a, uint32_t index) {
+        hooks = tp_producer_hooks(m->tp, index, per_token, tokens);
+        a.exchange = &hooks;
+        a.epilogue = kEpiPush;
         a.resid = nullptr;
-        a.epilogue = kEpiPartialF32;
-        stark_b200_status r = qmv_launch(a, s);
-        if (r != STARK_B200_OK) return r;
-        return tp_allreduce_residual_launch(m->tp, buf, m->tp_seq, m->h, ctx->error_word, slot(n++), pdl, s);
     };
     for (uint32_t l = 0; l < c.layers; ++l) {
         auto &L = m->layers[l];
@@ -274,13 +288,15 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.eps = c.eps;
         // qkv = W_qkv rmsnorm(h)
         a.matrix = L.qkv;
-        a.x = m->h;
+        a.x = hcur;
         a.y = m->qkv;
         a.prologue = kProRmsNorm;
         a.norm_weight = L.attn_norm;
         a.epilogue = kEpiStore;
         a.trace = slot(n++);
+        if (tp && l > 0) consume(a, 2u * l - 1u);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
+        a.exchange = nullptr;
         // attention with fused QK-norm, RoPE and KV append
         AttnArgs at{};
         at.qkv = m->qkv;
@@ -306,30 +322,35 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         // h = bf16(bf16(W_o attn) + h)
         a.matrix = L.o;
         a.x = m->attn;
-        a.y = m->h;
-        a.resid = m->h;
+        a.y = hcur;
+        a.resid = hcur;
         a.prologue = kProPlain;
         a.epilogue = kEpiResidual;
         a.trace = slot(n++);
-        if ((st = tp ? reduce_into_h(a, 0u) : qmv_launch(a, s)) != STARK_B200_OK) return st;
+        if (tp) produce(a, 2u * l);
+        if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
+        a.exchange = nullptr;
         // act = silu(gate) * up
         a.matrix = L.upgate;
-        a.x = m->h;
+        a.x = hcur;
         a.y = m->act;
         a.prologue = kProRmsNorm;
         a.norm_weight = L.mlp_norm;
         a.epilogue = kEpiSwiGlu;
         a.trace = slot(n++);
+        if (tp) consume(a, 2u * l);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
+        a.exchange = nullptr;
         // h = bf16(bf16(W_down act) + h)
         a.matrix = L.down;
         a.x = m->act;
-        a.y = m->h;
-        a.resid = m->h;
+        a.y = hcur;
+        a.resid = hcur;
         a.prologue = kProPlain;
         a.epilogue = kEpiResidual;
         a.trace = slot(n++);
-        if ((st = tp ? reduce_into_h(a, 1u) : qmv_launch(a, s)) != STARK_B200_OK) return st;
+        if (tp) produce(a, 2u * l + 1u);
+        if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
     }
     if (full) {
         QmvArgs a{};
@@ -339,7 +360,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.pdl = pdl;
         a.eps = c.eps;
         a.matrix = m->lm_head;
-        a.x = m->h;
+        a.x = hcur;
         a.y = m->logits;
         a.prologue = kProRmsNorm;
         a.norm_weight = m->final_norm;
@@ -349,14 +370,18 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         uint32_t grid = 0;
         a.out_grid = &grid;
         a.trace = slot(n++);
+        if (tp) consume(a, per_token - 1u);
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
-        st = tp ? tp_argmax_finalize_launch(m->tp, m->tp_seq, m->partial_max, m->partial_index, grid,
+        st = tp ? tp_argmax_finalize_launch(m->tp, tokens, m->partial_max, m->partial_index, grid,
                                             m->tp_vocab_offset, m->state, m->generated, ctx->error_word, pdl, s)
                 : argmax_finalize_launch(m->partial_max, m->partial_index, grid, m->state, m->generated, true, pdl, s);
         if (st != STARK_B200_OK) return st;
         n += 1;
     } else {
-        if ((st = ingest_advance_launch(m->state, m->pending, pdl, s)) != STARK_B200_OK) return st;
+        st = tp ? tp_ingest_advance_launch(m->tp, per_token - 1u, per_token, tokens, m->state, m->pending,
+                                           ctx->error_word, pdl, s)
+                : ingest_advance_launch(m->state, m->pending, pdl, s);
+        if (st != STARK_B200_OK) return st;
         n += 1;
     }
     if (launches) *launches = n;
@@ -531,9 +556,9 @@ stark_b200_status model_tp_init(Model *m, uint32_t rank, uint32_t size, uint32_t
     const size_t bytes = tp_region_bytes(m->cfg.hidden);
     SB_CUDA(cudaMalloc(&m->tp_local, bytes));
     SB_CUDA(cudaMemset(m->tp_local, 0, bytes));
-    stark_b200_status st = dmalloc(&m->tp_seq, kTpFlagSets);
+    stark_b200_status st = dmalloc(&m->tp_seq, 4);
     if (st != STARK_B200_OK) return st;
-    SB_CUDA(cudaMemset(m->tp_seq, 0, kTpFlagSets * 4u));
+    SB_CUDA(cudaMemset(m->tp_seq, 0, 16u));
     SB_CUDA(cudaDeviceSynchronize());
     cudaIpcMemHandle_t handle;
     SB_CUDA(cudaIpcGetMemHandle(&handle, m->tp_local));

@@ -31,6 +31,7 @@ struct Model {
     uint32_t *generated = nullptr;  // greedy tokens of a device-chained run (device)
     TraceSlot *trace = nullptr;     // optional per-launch timeline (STARK_B200_TRACE=1)
     uint32_t trace_slots = 0;
+    uint16_t *h_alt = nullptr;      // second residual-stream buffer (tensor parallel only)
     uint16_t *h = nullptr, *qkv = nullptr, *attn = nullptr, *act = nullptr, *logits = nullptr;
     float *attn_scratch = nullptr;
     uint32_t *attn_counters = nullptr;
@@ -50,7 +51,7 @@ struct Model {
     // (heads, intermediate width, read-out rows); the embedding table is whole on every rank.
     TpRegion tp{};
     uint8_t *tp_local = nullptr;   // this rank's exchange region
-    uint32_t *tp_seq = nullptr;    // [kTpFlagSets] exchanges done per flag set
+    uint32_t *tp_seq = nullptr;    // [0] tokens finished: the base of the exchange tickets
     uint32_t tp_vocab_offset = 0, tp_vocab_total = 0;
     bool tp_connected = false;
     StepState *host_state = nullptr;    // pinned

@@ -60,6 +60,7 @@ struct QmvParams {
     uint32_t *partial_index;
     uint32_t *error_word;
     TraceSlot *trace;
+    QmvExchange ex;
 };
 
 struct SmemLayout {
@@ -105,7 +106,7 @@ __device__ inline void wait_failed(volatile uint32_t *abort_flag, uint32_t *erro
 // exactly scaled f16 (plus the per-group sums the bias term needs) and returns the factor that undoes
 // the scale.  ROUNDS = chunks of 8 elements a thread keeps in registers (K <= ROUNDS * 2048): the
 // code is straight-line per round, and a short instance matters because every launch runs it cold.
-template <int ROUNDS, bool NORM, bool SPLIT>
+template <int ROUNDS, bool NORM, bool SPLIT, bool TPX>
 __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, uint32_t columns, __half *xs, __half *xlo,
                                             uint16_t *nws, float *xsum, float *xoff, float *wred, float &xunscale) {
     const uint32_t warp = tid >> 5, lane = tid & 31u;
@@ -153,6 +154,68 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
         } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) f[r][i] = 0.0f;
+        }
+    }
+    if (NORM && TPX && p.ex.recv) {
+        // Tensor-parallel consumer: h' = bf16(bf16(sum of the ranks' shares, rank order) + h) replaces
+        // the row just loaded.  A share is there when its packet carries this exchange's ticket.  The
+        // packets of two ranks are fetched per trip to memory.
+        const uint32_t ticket = __ldcg(p.ex.tokens) * p.ex.ticket_mul + p.ex.ticket_add;
+        const unsigned long long t0 = global_ns();
+#pragma unroll
+        for (int r = 0; r < ROUNDS; ++r) {
+            const uint32_t c = tid + r * kConsumerThreads;
+            if (c < chunks) {
+                float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+                for (uint32_t k = 0; k < p.ex.ranks; k += 2u) {
+                    const bool two = k + 1u < p.ex.ranks;
+                    const unsigned long long *s0 = p.ex.recv + (size_t)k * columns + 8u * c;
+                    const unsigned long long *s1 = two ? s0 + columns : s0;
+                    unsigned long long q0[8], q1[8];
+                    uint32_t spins = 0;
+                    for (;;) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];"
+                                         : "=l"(q0[2 * i]), "=l"(q0[2 * i + 1])
+                                         : "l"(s0 + 2 * i)
+                                         : "memory");
+                            asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];"
+                                         : "=l"(q1[2 * i]), "=l"(q1[2 * i + 1])
+                                         : "l"(s1 + 2 * i)
+                                         : "memory");
+                        }
+                        bool all = true;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            all = all && (uint32_t)(q0[i] >> 32) == ticket && (uint32_t)(q1[i] >> 32) == ticket;
+                        if (all) break;
+                        if (++spins > 8u) {
+                            __nanosleep(64);
+                            if (global_ns() - t0 > 4000000000ull) {  // a rank is missing: give up after 4 s
+                                atomicOr(p.error_word, kErrPeerTimeout);
+                                break;
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        acc[i] += __uint_as_float((uint32_t)q0[i]);
+                        if (two) acc[i] += __uint_as_float((uint32_t)q1[i]);
+                    }
+                }
+                uint32_t packed[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint16_t lo = f32_to_bf16_bits(bf16_round(acc[2 * i]) + f[r][2 * i]);
+                    const uint16_t hi = f32_to_bf16_bits(bf16_round(acc[2 * i + 1]) + f[r][2 * i + 1]);
+                    f[r][2 * i] = bf16_bits_to_f32(lo);
+                    f[r][2 * i + 1] = bf16_bits_to_f32(hi);
+                    packed[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+                }
+                if (blockIdx.x == 0)
+                    reinterpret_cast<uint4 *>(p.ex.h_out)[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
         }
     }
     // One block-wide reduction gives both the sum of squares and the magnitude the scaled input can
@@ -263,7 +326,9 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
 //        survive; bf16 inputs need one term.
 // RPW:   records per consumer warp per ring stage (stage = 8 * RPW records unless PRED).
 // PRED:  the stage holds fewer than 8 * RPW records (group counts that are not a multiple of 8).
-template <bool SPLIT, int RPW, bool PRED, bool FOLD>
+// TPX:   the kernel takes part in a tensor-parallel exchange (QmvExchange); kept out of the single-GPU
+//        instances so that their code and register allocation stay as they are.
+template <bool SPLIT, int RPW, bool PRED, bool FOLD, bool TPX = false>
 __global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t columns = p.groups * 64u;
@@ -337,6 +402,8 @@ __global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
         // ---------------- epilogue warp: cross-warp reduction and output of finished row tiles ----------
         uint32_t rb = 0, rphase = 0;
         float held = 0.0f;  // kEpiSwiGlu: the `up` value of the even tile
+        const uint32_t push_ticket =
+            TPX && p.epilogue == kEpiPush ? __ldcg(p.ex.tokens) * p.ex.ticket_mul + p.ex.ticket_add : 0u;
         float best = -INFINITY;
         uint32_t best_index = 0xffffffffu;
         for (uint32_t tile = t0; tile < t1; ++tile) {
@@ -380,6 +447,13 @@ __global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
                     }
                 } else if (p.epilogue == kEpiPartialF32) {
                     if (valid) reinterpret_cast<float *>(p.y)[row] = v;
+                } else if (TPX && p.epilogue == kEpiPush) {
+                    if (valid) {
+                        const unsigned long long packet = ((unsigned long long)push_ticket << 32) | __float_as_uint(v);
+                        for (uint32_t r = 0; r < p.ex.ranks; ++r)
+                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p.ex.push[r] + row), "l"(packet)
+                                         : "memory");
+                    }
                 } else {  // kEpiLogits
                     if (valid) {
                         const uint16_t hb = f32_to_bf16_bits(v);
@@ -419,11 +493,11 @@ __global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
     float xunscale;
     const bool norm = p.prologue == kProRmsNorm;
     if (columns <= 2u * kConsumerThreads * 8u) {
-        if (norm) stage_input<2, true, SPLIT>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
-        else stage_input<2, false, SPLIT>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        if (norm) stage_input<2, true, SPLIT, TPX>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        else stage_input<2, false, SPLIT, false>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
     } else {
-        if (norm) stage_input<kMaxRounds, true, SPLIT>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
-        else stage_input<kMaxRounds, false, SPLIT>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        if (norm) stage_input<kMaxRounds, true, SPLIT, TPX>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        else stage_input<kMaxRounds, false, SPLIT, false>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
     }
 
     // Main loop: no block-wide barrier from here on.
@@ -684,6 +758,9 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     p.partial_index = a.partial_index;
     p.error_word = a.error_word;
     p.trace = a.trace;
+    if (a.exchange) p.ex = *a.exchange;
+    if ((a.epilogue == kEpiPush) != (p.ex.ranks != 0 && p.ex.push[0] != nullptr)) return STARK_B200_INVALID_ARGUMENT;
+    if (p.ex.recv && a.prologue != kProRmsNorm) return STARK_B200_INVALID_ARGUMENT;
 
     const bool split = a.io_type == STARK_B200_F32;
     const bool fold = tuning().fold;
@@ -712,9 +789,16 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
                                                {SB_QMV_ROW(true, false), SB_QMV_ROW(true, true)}};
 #undef SB_QMV_ROW
     const uint32_t ri = rpw == 1 ? 0u : (rpw == 2 ? 1u : 2u);
-    KernelFn kernel = table[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
-    static bool attr_set[2][2][2][3] = {};
-    bool &done = attr_set[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
+    static const KernelFn tpx_table[2][3] = {
+        {qmv_a4_kernel<false, 1, false, false, true>, qmv_a4_kernel<false, 2, false, false, true>,
+         qmv_a4_kernel<false, 4, false, false, true>},
+        {qmv_a4_kernel<false, 1, true, false, true>, qmv_a4_kernel<false, 2, true, false, true>,
+         qmv_a4_kernel<false, 4, true, false, true>}};
+    const bool tpx = p.ex.ranks != 0;
+    if (tpx && split) return STARK_B200_UNSUPPORTED;
+    KernelFn kernel = tpx ? tpx_table[pred ? 1 : 0][ri] : table[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
+    static bool attr_set[2][2][2][3] = {}, tpx_attr_set[2][3] = {};
+    bool &done = tpx ? tpx_attr_set[pred ? 1 : 0][ri] : attr_set[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
     if (!done) {
         SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
         done = true;

@@ -56,6 +56,28 @@ enum QmvEpilogue : uint32_t {
     kEpiSwiGlu = 2,    // pair_halves matrix: y[r] = bf16(up[r] * bf16(silu(gate[r])))
     kEpiLogits = 3,    // y[row] = bf16(value) and a per-CTA (max, first index) partial
     kEpiPartialF32 = 4,  // y[row] = value as f32, bf16 input: this rank's share of a K-split product
+    kEpiPush = 5,        // the f32 share goes to every rank's receive buffer as {value, ticket} packets
+};
+
+// Tensor-parallel exchange hooks of a matvec (see tp.cuh).  A K-split projection pushes its f32 share
+// into every rank's receive buffer over peer mappings (kEpiPush) as 8-byte packets {value, ticket},
+// each written with one 64-bit store: a packet is valid exactly when its ticket is the exchange's, so
+// the producer needs no fence, no flag and no arrival counter, and the data is usable the moment it
+// lands.  The matvec that consumes the sum (kProRmsNorm with `recv` set) polls the packets of all ranks
+// while it loads its input, forms
+//   h' = bf16(bf16(sum over ranks, in rank order) + h)
+// in its prologue -- the rounding of the projection output and the residual add of the reference
+// graph -- normalizes h' as usual, and block 0 stores h' for the next residual.  Tickets are
+// tokens * ticket_mul + ticket_add with `tokens` a device word that advances once per token, so every
+// exchange of a run has its own non-zero value and nothing is ever reset.
+constexpr uint32_t kMaxExchangeRanks = 8;
+struct QmvExchange {
+    uint32_t ranks;
+    unsigned long long *push[kMaxExchangeRanks];  // kEpiPush: on rank r, this rank's row of packets
+    const unsigned long long *recv;               // consumer: local [kMaxExchangeRanks][columns] packets
+    uint16_t *h_out;                              // consumer: [columns] bf16, written by block 0
+    const uint32_t *tokens;
+    uint32_t ticket_mul, ticket_add;
 };
 
 struct QmvArgs {
@@ -75,6 +97,7 @@ struct QmvArgs {
     TraceSlot *trace;         // optional timeline slot of this launch
     bool pdl;                 // launch with programmatic stream serialization
     uint32_t *out_grid;       // optional: number of CTAs launched
+    const QmvExchange *exchange;  // optional tensor-parallel hooks
 };
 
 stark_b200_status qmv_launch(const QmvArgs &args, cudaStream_t stream);

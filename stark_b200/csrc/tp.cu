@@ -1,6 +1,5 @@
-// Tensor-parallel exchange kernels (see tp.cuh): flag-synchronised one-shot all-reduce fused with the
-// bf16 rounding and residual add that follow the o- and down-projections, and the gather that picks
-// the greedy token across vocabulary shards.  Peers' memory is reached with plain system-scope loads
+// Tensor-parallel end-of-token kernels (see tp.cuh; the all-reduce itself lives in the matvecs): the
+// gather that picks the greedy token across vocabulary shards, and the close of a cache-only prompt row.  Peers' memory is reached with plain system-scope loads
 // and stores; every wait on a peer is bounded in time and reports through the device error word.
 #include "tp.cuh"
 
@@ -18,14 +17,6 @@ __device__ inline uint32_t ld_acquire_sys(const uint32_t *p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-__device__ inline float4 ld_sys_f32x4(const float *p) {
-    float4 v;
-    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                 : "l"(p)
-                 : "memory");
-    return v;
-}
 __device__ inline uint2 ld_sys_u32x2(const uint32_t *p) {
     uint2 v;
     asm volatile("ld.relaxed.sys.global.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
@@ -35,15 +26,12 @@ __device__ inline void st_sys_u32x2(uint32_t *p, uint2 v) {
     asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
 }
 
-// Thread r < size tells rank r that this rank's data for exchange `ticket` is in place, then waits
-// until rank r has said the same.  Returns false (and records the error) when the wait ran out.
-__device__ inline bool exchange_flags(const TpRegion &g, uint32_t set, uint32_t ticket, uint32_t *error_word) {
+// Bounded wait of thread r < size for rank r's flag of flag set `set`.  Returns false (and records the
+// error) when a wait ran out.  All threads of the block must call it.
+__device__ inline bool wait_flags(const TpRegion &g, uint32_t set, uint32_t ticket, uint32_t *error_word) {
     bool ok = true;
     if (threadIdx.x < g.size) {
-        const uint32_t r = threadIdx.x;
-        __threadfence_system();
-        st_release_sys(tp_flags(g.base[r], set) + g.rank, ticket);
-        const uint32_t *mine = tp_flags(g.base[g.rank], set) + r;
+        const uint32_t *mine = tp_flags(g.base[g.rank], set) + threadIdx.x;
         const unsigned long long t0 = global_ns();
         uint32_t spins = 0;
         while (ld_acquire_sys(mine) != ticket) {
@@ -60,43 +48,44 @@ __device__ inline bool exchange_flags(const TpRegion &g, uint32_t set, uint32_t 
     return __syncthreads_and(ok ? 1 : 0) != 0;
 }
 
-__global__ void __launch_bounds__(1024) tp_allreduce_residual_kernel(TpRegion g, uint32_t buf, uint32_t *seq,
-                                                                     uint16_t *h, uint32_t *error_word,
-                                                                     TraceSlot *trace) {
+__global__ void __launch_bounds__(256) tp_ingest_advance_kernel(TpRegion g, uint32_t buf, uint32_t ticket_mul,
+                                                                uint32_t ticket_add, uint32_t *tokens,
+                                                                StepState *state, const uint32_t *pending,
+                                                                uint32_t *error_word) {
     pdl_launch_dependents();
-    if (threadIdx.x == 0 && trace) trace_min(&trace->start);
-    pdl_wait();  // this rank's partial (the matvec before this kernel) and h are final
-    if (threadIdx.x == 0 && trace) trace_min(&trace->ready);
-    const uint32_t ticket = seq[buf] + 1u;
-    const bool ok = exchange_flags(g, buf, ticket, error_word);
-    if (threadIdx.x == 0 && trace) trace_max(&trace->compute);  // every peer's share is in place
-    if (ok) {
-        for (uint32_t i = threadIdx.x * 4u; i < g.hidden; i += blockDim.x * 4u) {
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t r = 0; r < g.size; ++r) {  // rank order: every rank computes the same bits
-                const float4 v = ld_sys_f32x4(tp_partial(g.base[r], buf, g.hidden) + i);
-                acc.x += v.x;
-                acc.y += v.y;
-                acc.z += v.z;
-                acc.w += v.w;
+    pdl_wait();
+    const uint32_t ticket = *tokens * ticket_mul + ticket_add;
+    const unsigned long long t0 = global_ns();
+    bool ok = true;
+    for (uint32_t r = 0; r < g.size && ok; ++r) {
+        const unsigned long long *row = tp_recv(g.base[g.rank], buf, r, g.hidden);
+        for (uint32_t i = threadIdx.x; i < g.hidden && ok; i += blockDim.x) {
+            uint32_t spins = 0;
+            for (;;) {
+                unsigned long long q;
+                asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(q) : "l"(row + i) : "memory");
+                if ((uint32_t)(q >> 32) == ticket) break;
+                if (++spins > 8u) {
+                    __nanosleep(100);
+                    if (global_ns() - t0 > kPeerWaitNs) {
+                        atomicOr(error_word, kErrPeerTimeout);
+                        ok = false;
+                        break;
+                    }
+                }
             }
-            const uint2 old = *reinterpret_cast<const uint2 *>(h + i);
-            const float r0 = bf16_bits_to_f32((uint16_t)(old.x & 0xffffu)), r1 = bf16_bits_to_f32((uint16_t)(old.x >> 16));
-            const float r2 = bf16_bits_to_f32((uint16_t)(old.y & 0xffffu)), r3 = bf16_bits_to_f32((uint16_t)(old.y >> 16));
-            uint2 o;
-            o.x = (uint32_t)f32_to_bf16_bits(bf16_round(acc.x) + r0) | ((uint32_t)f32_to_bf16_bits(bf16_round(acc.y) + r1) << 16);
-            o.y = (uint32_t)f32_to_bf16_bits(bf16_round(acc.z) + r2) | ((uint32_t)f32_to_bf16_bits(bf16_round(acc.w) + r3) << 16);
-            *reinterpret_cast<uint2 *>(h + i) = o;
         }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        seq[buf] = ticket;
-        if (trace) trace_max(&trace->end);
+        state->position += 1u;
+        state->token = pending[state->cursor];
+        state->cursor += 1u;
+        *tokens += 1u;
     }
 }
 
-__global__ void __launch_bounds__(256) tp_argmax_finalize_kernel(TpRegion g, uint32_t *seq, const float *partial_max,
+__global__ void __launch_bounds__(256) tp_argmax_finalize_kernel(TpRegion g, uint32_t *tokens, const float *partial_max,
                                                                  const uint32_t *partial_index, uint32_t count,
                                                                  uint32_t vocab_offset, StepState *state,
                                                                  uint32_t *generated, uint32_t *error_word) {
@@ -128,8 +117,8 @@ __global__ void __launch_bounds__(256) tp_argmax_finalize_kernel(TpRegion g, uin
         is[threadIdx.x >> 5] = bi;
     }
     __syncthreads();
-    const uint32_t set = kTpFlagSets - 1u;
-    const uint32_t ticket = seq[set] + 1u;
+    const uint32_t set = 0u;
+    const uint32_t ticket = *tokens + 1u;
     if (threadIdx.x == 0) {
         for (uint32_t w = 1; w < blockDim.x / 32u; ++w)
             if (vs[w] > best || (vs[w] == best && is[w] < bi)) {
@@ -140,9 +129,12 @@ __global__ void __launch_bounds__(256) tp_argmax_finalize_kernel(TpRegion g, uin
         is[0] = bi == 0xffffffffu ? bi : bi + vocab_offset;
     }
     __syncthreads();
-    if (threadIdx.x < g.size)  // this rank's candidate into every rank's slot table
+    if (threadIdx.x < g.size) {  // this rank's candidate into every rank's slot table, then its flag there
         st_sys_u32x2(tp_gather(g.base[threadIdx.x]) + 2u * g.rank, make_uint2(__float_as_uint(vs[0]), is[0]));
-    const bool ok = exchange_flags(g, set, ticket, error_word);
+        __threadfence_system();
+        st_release_sys(tp_flags(g.base[threadIdx.x], set) + g.rank, ticket);
+    }
+    const bool ok = wait_flags(g, set, ticket, error_word);
     if (threadIdx.x == 0) {
         float top = -INFINITY;
         uint32_t ti = 0xffffffffu;
@@ -162,7 +154,7 @@ __global__ void __launch_bounds__(256) tp_argmax_finalize_kernel(TpRegion g, uin
         if (generated && state->gen_cursor < state->gen_capacity) generated[state->gen_cursor++] = tok;
         state->position += 1u;
         state->token = tok;
-        seq[set] = ticket;
+        *tokens = ticket;
     }
 }
 
@@ -183,20 +175,42 @@ stark_b200_status launch_one(void (*kernel)(Args...), uint32_t threads, bool pdl
 
 }  // namespace
 
-stark_b200_status tp_allreduce_residual_launch(const TpRegion &region, uint32_t buf, uint32_t *seq, uint16_t *h,
-                                               uint32_t *error_word, TraceSlot *trace, bool pdl, cudaStream_t stream) {
-    if (region.size < 2 || region.size > kMaxTpRanks || region.rank >= region.size || buf > 1u ||
-        region.hidden % 4u != 0)
-        return STARK_B200_INVALID_ARGUMENT;
-    return launch_one(tp_allreduce_residual_kernel, 1024u, pdl, stream, region, buf, seq, h, error_word, trace);
+QmvExchange tp_producer_hooks(const TpRegion &g, uint32_t index, uint32_t per_token, const uint32_t *tokens) {
+    QmvExchange x{};
+    x.ranks = g.size;
+    for (uint32_t r = 0; r < g.size; ++r) x.push[r] = tp_recv(g.base[r], index & 1u, g.rank, g.hidden);
+    x.tokens = tokens;
+    x.ticket_mul = per_token;
+    x.ticket_add = index + 1u;
+    return x;
 }
 
-stark_b200_status tp_argmax_finalize_launch(const TpRegion &region, uint32_t *seq, const float *partial_max,
+QmvExchange tp_consumer_hooks(const TpRegion &g, uint32_t index, uint32_t per_token, const uint32_t *tokens,
+                              uint16_t *h_out) {
+    QmvExchange x{};
+    x.ranks = g.size;
+    x.recv = tp_recv(g.base[g.rank], index & 1u, 0u, g.hidden);
+    x.h_out = h_out;
+    x.tokens = tokens;
+    x.ticket_mul = per_token;
+    x.ticket_add = index + 1u;
+    return x;
+}
+
+stark_b200_status tp_ingest_advance_launch(const TpRegion &g, uint32_t last_index, uint32_t per_token,
+                                           uint32_t *tokens, StepState *state, const uint32_t *pending,
+                                           uint32_t *error_word, bool pdl, cudaStream_t stream) {
+    if (g.size < 2 || g.size > kMaxTpRanks || g.rank >= g.size) return STARK_B200_INVALID_ARGUMENT;
+    return launch_one(tp_ingest_advance_kernel, 256u, pdl, stream, g, last_index & 1u, per_token, last_index + 1u,
+                      tokens, state, pending, error_word);
+}
+
+stark_b200_status tp_argmax_finalize_launch(const TpRegion &region, uint32_t *tokens, const float *partial_max,
                                             const uint32_t *partial_index, uint32_t count, uint32_t vocab_offset,
                                             StepState *state, uint32_t *generated, uint32_t *error_word, bool pdl,
                                             cudaStream_t stream) {
     if (region.size < 2 || region.size > kMaxTpRanks || region.rank >= region.size) return STARK_B200_INVALID_ARGUMENT;
-    return launch_one(tp_argmax_finalize_kernel, 256u, pdl, stream, region, seq, partial_max, partial_index, count,
+    return launch_one(tp_argmax_finalize_kernel, 256u, pdl, stream, region, tokens, partial_max, partial_index, count,
                       vocab_offset, state, generated, error_word);
 }
 
