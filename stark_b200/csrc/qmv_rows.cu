@@ -10,6 +10,7 @@
 // bit-identical to the CPU decode.
 #include <algorithm>
 
+#include "device_math.cuh"
 #include "qmv.cuh"
 
 namespace sb {
@@ -119,10 +120,11 @@ __device__ inline float row_dot(const RowParams &p, const uint8_t *row, const ui
     return warp_sum(acc);
 }
 
-// grid = (row blocks, batch).  Launch row `blockIdx.y` multiplies matrix `expert_ids[blockIdx.y]` of the
-// bank (or the only matrix) with its input row.
+// Fallback for widths whose rows do not start on 16-byte boundaries (one lane per 32-value block straight
+// from global memory; slow).  grid = (row blocks, batch).  Launch row `blockIdx.y` multiplies matrix
+// `expert_ids[blockIdx.y]` of the bank (or the only matrix) with its input row.
 template <uint32_t FORMAT>
-__global__ void __launch_bounds__(kRowThreads) qmv_rows_kernel(const RowParams p) {
+__global__ void __launch_bounds__(kRowThreads) qmv_rows_generic_kernel(const RowParams p) {
     extern __shared__ __align__(16) float xs[];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t b = blockIdx.y;
@@ -153,6 +155,168 @@ __global__ void __launch_bounds__(kRowThreads) qmv_rows_kernel(const RowParams p
                 reinterpret_cast<uint16_t *>(p.y)[(size_t)b * p.rows + row] = f32_to_bf16_bits(v);
         }
     }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Streaming kernel.  A warp owns whole rows; a row is cut into chunks of 1024 values (Q8_0: 1088 bytes,
+// Q4_K: 576, affine 8-bit: 1024) that travel global -> shared memory as 16-byte cp.async copies, four
+// chunks deep per warp, so the DRAM side sees long contiguous reads regardless of the block layout.
+// Each lane then decodes one 32-value block of the chunk from shared memory.  Codes become f32 without
+// an integer conversion (byte | 0x4B000000 is 2^23 + byte), the block's scale is applied once to the
+// block's sum of code * x, and the offset terms (Q4_K minimum, affine bias) use sums of x over 32
+// values prepared once per CTA.  The input vector sits in shared memory as f32, stored so that the 32
+// lanes' 128-bit reads of their own blocks hit distinct banks (float4 index XOR block index).
+constexpr uint32_t kChunkValues = 1024;
+constexpr int kRowStages = 4;
+
+template <uint32_t FORMAT>
+__host__ __device__ constexpr uint32_t chunk_bytes() {
+    return FORMAT == kFmtQ8_0 ? 1088u : (FORMAT == kFmtQ4_K ? 576u : 1024u);
+}
+
+__device__ inline float byte_to_f32(uint32_t word, uint32_t selector) {
+    // selector 0x7540 + j: byte j of `word` under the exponent of 2^23
+    return __uint_as_float(__byte_perm(word, 0x4B000000u, selector)) - 8388608.0f;
+}
+__device__ inline float dot4_bytes(uint32_t w, const float4 &x, float acc) {
+    acc = fmaf(byte_to_f32(w, 0x7540u), x.x, acc);
+    acc = fmaf(byte_to_f32(w, 0x7541u), x.y, acc);
+    acc = fmaf(byte_to_f32(w, 0x7542u), x.z, acc);
+    acc = fmaf(byte_to_f32(w, 0x7543u), x.w, acc);
+    return acc;
+}
+
+template <uint32_t FORMAT>
+__global__ void __launch_bounds__(kRowThreads) qmv_rows_kernel(const RowParams p) {
+    extern __shared__ __align__(16) uint8_t rows_smem[];
+    constexpr uint32_t CB = chunk_bytes<FORMAT>();
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t b = blockIdx.y;
+    const uint32_t padded = (p.columns + kChunkValues - 1u) / kChunkValues * kChunkValues;
+    float4 *xs4 = reinterpret_cast<float4 *>(rows_smem);
+    float *xsum = reinterpret_cast<float *>(rows_smem + (size_t)padded * 4u);
+    uint8_t *stage = rows_smem + (size_t)padded * 4u + (size_t)(padded / 32u) * 4u + (size_t)warp * kRowStages * CB;
+
+    // input vector: f32, float4 (block, i4) of every chunk stored at block * 8 + (i4 ^ (block & 7))
+    for (uint32_t q = tid; q < padded / 4u; q += kRowThreads) {
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (q * 4u < p.columns) {
+            if (p.io_type == STARK_B200_F32) {
+                v = reinterpret_cast<const float4 *>(reinterpret_cast<const float *>(p.x) + (size_t)b * p.x_stride)[q];
+            } else {
+                const uint2 h = reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(p.x) + (size_t)b * p.x_stride)[q];
+                v = make_float4(__uint_as_float(h.x << 16), __uint_as_float(h.x & 0xffff0000u),
+                                __uint_as_float(h.y << 16), __uint_as_float(h.y & 0xffff0000u));
+            }
+        }
+        const uint32_t block = q >> 3, i4 = q & 7u;
+        xs4[block * 8u + (i4 ^ (block & 7u))] = v;
+        float s4 = (v.x + v.y) + (v.z + v.w);
+        s4 += __shfl_xor_sync(0xffffffffu, s4, 1);
+        s4 += __shfl_xor_sync(0xffffffffu, s4, 2);
+        s4 += __shfl_xor_sync(0xffffffffu, s4, 4);
+        if (i4 == 0) xsum[block] = s4;
+    }
+    __syncthreads();
+
+    uint32_t expert = 0;
+    if (p.expert_ids) {
+        expert = p.expert_ids[b];
+        if (expert >= p.experts) expert = 0;  // moe_gather_rows: an invalid id falls back to expert 0 (moe.rs:84-101)
+    }
+    const uint8_t *base = p.data + (size_t)expert * p.expert_bytes;
+    const uint16_t *sbase = p.scales ? p.scales + (size_t)expert * p.expert_plane_elems : nullptr;
+    const uint16_t *bbase = p.biases ? p.biases + (size_t)expert * p.expert_plane_elems : nullptr;
+    const uint32_t groups = p.columns / 64u;
+    const uint32_t cpr = padded / kChunkValues;  // chunks per row
+    const uint32_t gw = blockIdx.x * kRowWarps + warp, nw = gridDim.x * kRowWarps;
+    const uint32_t my_rows = gw < p.rows ? (p.rows - gw + nw - 1u) / nw : 0u;
+    const uint32_t items = my_rows * cpr;
+
+    auto issue = [&](uint32_t item) {
+        if (item < items) {
+            const uint32_t row = gw + (item / cpr) * nw, c = item % cpr;
+            const uint32_t bytes = min((uint32_t)CB, (uint32_t)(p.row_bytes - (size_t)c * CB));
+            const uint8_t *src = base + (size_t)row * p.row_bytes + (size_t)c * CB;
+            uint8_t *dst = stage + (item % kRowStages) * CB;
+            for (uint32_t off = lane * 16u; off < bytes; off += 512u) cp_async16(dst + off, src + off);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int i = 0; i < kRowStages - 1; ++i) issue(i);
+
+    float acc = 0.0f;
+    for (uint32_t item = 0; item < items; ++item) {
+        issue(item + kRowStages - 1);
+        cp_async_wait<kRowStages - 1>();
+        __syncwarp();
+        const uint32_t row = gw + (item / cpr) * nw, c = item % cpr;
+        const uint8_t *chunk = stage + (item % kRowStages) * CB;
+        const uint32_t block = c * 32u + lane;          // this lane's 32-value block of the row
+        if (block * 32u < p.columns) {
+            const float4 *xb = xs4 + (size_t)block * 8u;
+            const uint32_t sw = lane & 7u;               // block & 7 == lane & 7
+            if (FORMAT == kFmtQ8_0) {
+                const uint8_t *blk = chunk + 34u * lane;
+                const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk));
+                float t = 0.0f;
+#pragma unroll
+                for (uint32_t i4 = 0; i4 < 8; ++i4) {
+                    const uint32_t lo = *reinterpret_cast<const uint16_t *>(blk + 2u + 4u * i4);
+                    const uint32_t hi = *reinterpret_cast<const uint16_t *>(blk + 4u + 4u * i4);
+                    const uint32_t w = (lo | (hi << 16)) ^ 0x80808080u;  // int8 + 128
+                    t = dot4_bytes(w, xb[i4 ^ sw], t);
+                }
+                // sum (q + 128) x - 128 sum x
+                acc = fmaf(d, fmaf(-128.0f, xsum[block], t), acc);
+            } else if (FORMAT == kFmtQ4_K) {
+                const uint8_t *blk = chunk + 144u * (lane >> 3);
+                const uint32_t j = lane & 7u;
+                const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk);
+                const float d = f16_bits_to_f32((uint16_t)(dd & 0xffffu)), dmin = f16_bits_to_f32((uint16_t)(dd >> 16));
+                uint32_t sc, mn;
+                q4k_scale_min(blk + 4, (int)j, sc, mn);
+                const uint4 *q = reinterpret_cast<const uint4 *>(blk + 16u + (j >> 1) * 32u);
+                const uint4 qa = q[0], qb = q[1];
+                const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                const uint32_t shift = (j & 1u) * 4u;
+                float t = 0.0f;
+#pragma unroll
+                for (uint32_t i4 = 0; i4 < 8; ++i4) t = dot4_bytes((words[i4] >> shift) & 0x0f0f0f0fu, xb[i4 ^ sw], t);
+                acc = fmaf(d * (float)sc, t, acc);
+                acc = fmaf(-(dmin * (float)mn), xsum[block], acc);
+            } else {  // kFmtAffine8
+                const uint4 *q = reinterpret_cast<const uint4 *>(chunk + 32u * lane);
+                const uint4 qa = q[0], qb = q[1];
+                const uint32_t words[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+                const float scale = bf16_bits_to_f32(sbase[(size_t)row * groups + (block >> 1)]);
+                const float bias = bf16_bits_to_f32(bbase[(size_t)row * groups + (block >> 1)]);
+                float t = 0.0f;
+#pragma unroll
+                for (uint32_t i4 = 0; i4 < 8; ++i4) t = dot4_bytes(words[i4], xb[i4 ^ sw], t);
+                acc = fmaf(scale, t, acc);
+                acc = fmaf(bias, xsum[block], acc);
+            }
+        }
+        __syncwarp();  // the stage may be refilled by the next iteration's copy
+        if (c + 1u == cpr) {
+            const float v = warp_sum(acc);
+            acc = 0.0f;
+            if (lane == 0) {
+                if (p.io_type == STARK_B200_F32)
+                    reinterpret_cast<float *>(p.y)[(size_t)b * p.rows + row] = v;
+                else
+                    reinterpret_cast<uint16_t *>(p.y)[(size_t)b * p.rows + row] = f32_to_bf16_bits(v);
+            }
+        }
+    }
+}
+
+template <uint32_t FORMAT>
+size_t rows_smem_bytes(uint32_t columns) {
+    const uint32_t padded = (columns + kChunkValues - 1u) / kChunkValues * kChunkValues;
+    return (size_t)padded * 4u + (size_t)(padded / 32u) * 4u + (size_t)kRowWarps * kRowStages * chunk_bytes<FORMAT>();
 }
 
 // Dequantizes one row to f32 (bit-exact image of decode_values / affine_row), one thread per element.
@@ -212,11 +376,33 @@ RowParams row_params(const QMatrix *m) {
     return p;
 }
 
-template <typename... Args>
-void dispatch_rows(QFormat f, dim3 grid, size_t smem, cudaStream_t s, const RowParams &p) {
-    if (f == kFmtQ4_K) qmv_rows_kernel<kFmtQ4_K><<<grid, kRowThreads, smem, s>>>(p);
-    else if (f == kFmtQ8_0) qmv_rows_kernel<kFmtQ8_0><<<grid, kRowThreads, smem, s>>>(p);
-    else qmv_rows_kernel<kFmtAffine8><<<grid, kRowThreads, smem, s>>>(p);
+template <uint32_t FORMAT>
+stark_b200_status launch_rows(const QMatrix *m, const RowParams &p, uint32_t batch, cudaStream_t s) {
+    // the streaming kernel copies 16 bytes at a time: every row must start on a 16-byte boundary
+    if (p.row_bytes % 16u == 0) {
+        const size_t smem = rows_smem_bytes<FORMAT>(m->columns);
+        static bool attr_set = false;
+        if (!attr_set) {
+            SB_CUDA(cudaFuncSetAttribute(qmv_rows_kernel<FORMAT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+            attr_set = true;
+        }
+        const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (200u * 1024u) / smem));
+        const uint32_t row_blocks =
+            std::max(1u, std::min((m->rows + kRowWarps - 1u) / kRowWarps, (148u * per_sm + batch - 1u) / batch));
+        qmv_rows_kernel<FORMAT><<<dim3(row_blocks, batch), kRowThreads, smem, s>>>(p);
+    } else {
+        const size_t smem = (size_t)m->columns * 4u;
+        static bool attr_set = false;
+        if (!attr_set) {
+            SB_CUDA(cudaFuncSetAttribute(qmv_rows_generic_kernel<FORMAT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+            attr_set = true;
+        }
+        const uint32_t row_blocks =
+            std::max(1u, std::min((m->rows + kRowWarps - 1u) / kRowWarps, 148u * 4u / std::max(1u, batch) + 1u));
+        qmv_rows_generic_kernel<FORMAT><<<dim3(row_blocks, batch), kRowThreads, smem, s>>>(p);
+    }
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
 }
 
 }  // namespace
@@ -235,18 +421,9 @@ stark_b200_status qmv_rows_launch(const QMatrix *m, const void *x, size_t x_stri
     p.y = y;
     p.io_type = io_type;
     p.expert_ids = expert_ids;
-    const size_t smem = (size_t)m->columns * 4u;
-    static bool attr_set = false;
-    if (!attr_set) {
-        SB_CUDA(cudaFuncSetAttribute(qmv_rows_kernel<kFmtQ4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        SB_CUDA(cudaFuncSetAttribute(qmv_rows_kernel<kFmtQ8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        SB_CUDA(cudaFuncSetAttribute(qmv_rows_kernel<kFmtAffine8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        attr_set = true;
-    }
-    const uint32_t row_blocks = std::max(1u, std::min((m->rows + kRowWarps - 1u) / kRowWarps, 148u * 4u / std::max(1u, batch) + 1u));
-    dispatch_rows(m->format, dim3(row_blocks, batch), smem, stream, p);
-    SB_CUDA(cudaGetLastError());
-    return STARK_B200_OK;
+    if (m->format == kFmtQ4_K) return launch_rows<kFmtQ4_K>(m, p, batch, stream);
+    if (m->format == kFmtQ8_0) return launch_rows<kFmtQ8_0>(m, p, batch, stream);
+    return launch_rows<kFmtAffine8>(m, p, batch, stream);
 }
 
 stark_b200_status qmv_rows_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,
