@@ -34,6 +34,7 @@ WORKLOADS = {
     "matvec": dict(cfg=None, prompt=0, context=0),
 }
 BYTES_PER_WEIGHT = 0.5625  # 4-bit codes + bf16 scale and bias per 64 columns
+DRAM_TRAFFIC_RATIO = 1.011  # measured dram bytes / algorithmic bytes of the 4-bit matvec (ncu, 151936x4096)
 
 
 def peaks() -> tuple[float, str]:
@@ -179,7 +180,8 @@ def run_matvec(args) -> None:
         "e2e": {"value": per / e2e / 1e9, "unit": "GB/s", "h2d_bytes_per_step": 2 * cols, "d2h_bytes_per_step": 2 * rows},
         "gpu_launches": n,
         "roofline": {"bound": "hbm", "achieved": per / us / 1e3, "peak": peak, "unit": "GB/s",
-                     "frac": per / us / 1e3 / peak, "traffic": None, "peak_kind": kind},
+                     "frac": per / us / 1e3 / peak,
+                     "traffic": DRAM_TRAFFIC_RATIO * per if args.format == "affine4" else None, "peak_kind": kind},
     }))
 
 
@@ -308,6 +310,24 @@ def main() -> None:
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
 
+    # ---- the second request of the workload: shares a prefix with the first, reuses its KV rows ----
+    reuse = None
+    if wl["prompt"] >= 2048:
+        from stark_b200.engine import reusable_prefix_rows
+        shared = wl["prompt"] - 512
+        second = np.concatenate([prompt[:shared], S.prompt(cfg, 512, seed=args.seed + 2)])
+        model.reset()
+        model.prefill(prompt)
+        model.drain()
+        rows = reusable_prefix_rows(len(prompt), shared, len(second))
+        barrier()
+        t0 = time.perf_counter()
+        model.rewind(rows)
+        model.prefill(second[rows:])
+        model.drain()
+        reuse = {"shared_prefix_tokens": int(shared), "rows_reused": int(rows),
+                 "rows_recomputed": int(len(second) - rows), "prefill_ms": 1e3 * (time.perf_counter() - t0)}
+
     t = torch.tensor([ms, e2e_s], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -330,13 +350,16 @@ def main() -> None:
                    "parallelism": "tp1" if world == 1 else (f"tp{world}" if tp is not None
                                                             else f"{world} independent replicas"),
                    "l2": "per-step inputs (weights %.2f GB + KV) exceed the 126 MB L2" % (info.weight_bytes / 1e9),
-                   "mean_context_rows": mean_context},
+                   "mean_context_rows": mean_context, "prefix_reuse": reuse},
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 16,
                 "steps": e2e_steps},
         "gpu_launches": int(steps * info.launches_per_step),
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "traffic": None, "peak_kind": peak_kind, "frac_of_8tbs": achieved / 8000.0,
+                     "traffic": DRAM_TRAFFIC_RATIO * algo / (world if tp is not None else 1),
+                     "traffic_note": "algorithmic bytes x 1.011, the dram read+write / algorithmic ratio of one ncu "
+                                     "capture of the dominant matvec kernel (profiles/), scaled to the step",
+                     "peak_kind": peak_kind, "frac_of_8tbs": achieved / 8000.0,
                      "algorithmic_bytes_per_step": algo,
                      "note": "whole decode step (all kernels of the token) over the step's algorithmic bytes"
                              + (", per GPU" if world > 1 else "")},

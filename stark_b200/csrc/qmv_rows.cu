@@ -167,7 +167,6 @@ __global__ void __launch_bounds__(kRowThreads) qmv_rows_generic_kernel(const Row
 // values prepared once per CTA.  The input vector sits in shared memory as f32, stored so that the 32
 // lanes' 128-bit reads of their own blocks hit distinct banks (float4 index XOR block index).
 constexpr uint32_t kChunkValues = 1024;
-constexpr int kRowStages = 4;
 
 template <uint32_t FORMAT>
 __host__ __device__ constexpr uint32_t chunk_bytes() {
@@ -186,10 +185,14 @@ __device__ inline float dot4_bytes(uint32_t w, const float4 &x, float acc) {
     return acc;
 }
 
-template <uint32_t FORMAT>
+// NB = 32-value blocks a lane decodes per item (an item is NB * 1024 values of one row): the larger the
+// item, the less the per-item bookkeeping weighs; STAGES = items in flight per warp.
+template <uint32_t FORMAT, uint32_t NB, uint32_t STAGES>
 __global__ void __launch_bounds__(kRowThreads) qmv_rows_kernel(const RowParams p) {
     extern __shared__ __align__(16) uint8_t rows_smem[];
-    constexpr uint32_t CB = chunk_bytes<FORMAT>();
+    constexpr uint32_t CB1 = chunk_bytes<FORMAT>();
+    constexpr uint32_t CB = CB1 * NB;
+    constexpr uint32_t kRowStages = STAGES;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t b = blockIdx.y;
     const uint32_t padded = (p.columns + kChunkValues - 1u) / kChunkValues * kChunkValues;
@@ -228,32 +231,41 @@ __global__ void __launch_bounds__(kRowThreads) qmv_rows_kernel(const RowParams p
     const uint16_t *sbase = p.scales ? p.scales + (size_t)expert * p.expert_plane_elems : nullptr;
     const uint16_t *bbase = p.biases ? p.biases + (size_t)expert * p.expert_plane_elems : nullptr;
     const uint32_t groups = p.columns / 64u;
-    const uint32_t cpr = padded / kChunkValues;  // chunks per row
+    const uint32_t cpr = (p.columns + kChunkValues * NB - 1u) / (kChunkValues * NB);  // items per row
     const uint32_t gw = blockIdx.x * kRowWarps + warp, nw = gridDim.x * kRowWarps;
     const uint32_t my_rows = gw < p.rows ? (p.rows - gw + nw - 1u) / nw : 0u;
     const uint32_t items = my_rows * cpr;
 
-    auto issue = [&](uint32_t item) {
-        if (item < items) {
-            const uint32_t row = gw + (item / cpr) * nw, c = item % cpr;
-            const uint32_t bytes = min((uint32_t)CB, (uint32_t)(p.row_bytes - (size_t)c * CB));
-            const uint8_t *src = base + (size_t)row * p.row_bytes + (size_t)c * CB;
-            uint8_t *dst = stage + (item % kRowStages) * CB;
+    // (row, chunk) of the next item to copy and of the next item to compute advance as counters: no
+    // division in the loop
+    uint32_t in_row = gw, in_c = 0, in_item = 0;
+    auto issue = [&]() {
+        if (in_item < items) {
+            const uint32_t bytes = min((uint32_t)CB, (uint32_t)(p.row_bytes - (size_t)in_c * CB));
+            const uint8_t *src = base + (size_t)in_row * p.row_bytes + (size_t)in_c * CB;
+            uint8_t *dst = stage + (in_item & (kRowStages - 1)) * CB;
             for (uint32_t off = lane * 16u; off < bytes; off += 512u) cp_async16(dst + off, src + off);
+            ++in_item;
+            if (++in_c == cpr) {
+                in_c = 0;
+                in_row += nw;
+            }
         }
         cp_async_commit();
     };
 #pragma unroll
-    for (int i = 0; i < kRowStages - 1; ++i) issue(i);
+    for (int i = 0; i < kRowStages - 1; ++i) issue();
 
     float acc = 0.0f;
+    uint32_t row = gw, c = 0;
     for (uint32_t item = 0; item < items; ++item) {
-        issue(item + kRowStages - 1);
+        issue();
         cp_async_wait<kRowStages - 1>();
         __syncwarp();
-        const uint32_t row = gw + (item / cpr) * nw, c = item % cpr;
-        const uint8_t *chunk = stage + (item % kRowStages) * CB;
-        const uint32_t block = c * 32u + lane;          // this lane's 32-value block of the row
+#pragma unroll
+        for (uint32_t nb = 0; nb < NB; ++nb) {
+        const uint8_t *chunk = stage + (item & (kRowStages - 1)) * CB + nb * CB1;
+        const uint32_t block = (c * NB + nb) * 32u + lane;  // one of this lane's 32-value blocks of the row
         if (block * 32u < p.columns) {
             const float4 *xb = xs4 + (size_t)block * 8u;
             const uint32_t sw = lane & 7u;               // block & 7 == lane & 7
@@ -299,8 +311,10 @@ __global__ void __launch_bounds__(kRowThreads) qmv_rows_kernel(const RowParams p
                 acc = fmaf(bias, xsum[block], acc);
             }
         }
+        }
         __syncwarp();  // the stage may be refilled by the next iteration's copy
-        if (c + 1u == cpr) {
+        if (++c == cpr) {
+            c = 0;
             const float v = warp_sum(acc);
             acc = 0.0f;
             if (lane == 0) {
@@ -309,14 +323,15 @@ __global__ void __launch_bounds__(kRowThreads) qmv_rows_kernel(const RowParams p
                 else
                     reinterpret_cast<uint16_t *>(p.y)[(size_t)b * p.rows + row] = f32_to_bf16_bits(v);
             }
+            row += nw;
         }
     }
 }
 
 template <uint32_t FORMAT>
-size_t rows_smem_bytes(uint32_t columns) {
+size_t rows_smem_bytes(uint32_t columns, uint32_t nb, uint32_t stages) {
     const uint32_t padded = (columns + kChunkValues - 1u) / kChunkValues * kChunkValues;
-    return (size_t)padded * 4u + (size_t)(padded / 32u) * 4u + (size_t)kRowWarps * kRowStages * chunk_bytes<FORMAT>();
+    return (size_t)padded * 4u + (size_t)(padded / 32u) * 4u + (size_t)kRowWarps * stages * nb * chunk_bytes<FORMAT>();
 }
 
 // Dequantizes one row to f32 (bit-exact image of decode_values / affine_row), one thread per element.
@@ -380,16 +395,22 @@ template <uint32_t FORMAT>
 stark_b200_status launch_rows(const QMatrix *m, const RowParams &p, uint32_t batch, cudaStream_t s) {
     // the streaming kernel copies 16 bytes at a time: every row must start on a 16-byte boundary
     if (p.row_bytes % 16u == 0) {
-        const size_t smem = rows_smem_bytes<FORMAT>(m->columns);
-        static bool attr_set = false;
-        if (!attr_set) {
-            SB_CUDA(cudaFuncSetAttribute(qmv_rows_kernel<FORMAT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-            attr_set = true;
+        // whole rows per item where they are long enough: 4096 values x 2 in flight, else 2048 x 4, else 1024 x 4
+        const uint32_t nb = m->columns >= 4096u ? 4u : (m->columns >= 2048u ? 2u : 1u);
+        const uint32_t stages = nb == 4u ? 2u : 4u;
+        const size_t smem = rows_smem_bytes<FORMAT>(m->columns, nb, stages);
+        auto kernel = nb == 4u ? qmv_rows_kernel<FORMAT, 4, 2> : (nb == 2u ? qmv_rows_kernel<FORMAT, 2, 4> : qmv_rows_kernel<FORMAT, 1, 4>);
+        static bool attr_set[3] = {false, false, false};
+        bool &done = attr_set[nb == 4u ? 2 : (nb == 2u ? 1 : 0)];
+        if (!done) {
+            SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+            done = true;
         }
-        const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (200u * 1024u) / smem));
+        if (smem > 160u * 1024u) return STARK_B200_UNSUPPORTED;
+        const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (220u * 1024u) / smem));
         const uint32_t row_blocks =
             std::max(1u, std::min((m->rows + kRowWarps - 1u) / kRowWarps, (148u * per_sm + batch - 1u) / batch));
-        qmv_rows_kernel<FORMAT><<<dim3(row_blocks, batch), kRowThreads, smem, s>>>(p);
+        kernel<<<dim3(row_blocks, batch), kRowThreads, smem, s>>>(p);
     } else {
         const size_t smem = (size_t)m->columns * 4u;
         static bool attr_set = false;
