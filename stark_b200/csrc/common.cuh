@@ -40,6 +40,13 @@ __host__ __device__ inline uint16_t f32_to_bf16_bits(float f) {
 }
 
 __device__ inline float bf16_round(float f) { return bf16_bits_to_f32(f32_to_bf16_bits(f)); }
+// Two roundings in one instruction: bits 0-15 = bf16(lo), bits 16-31 = bf16(hi), round to nearest even.
+// Differs from f32_to_bf16_bits only in the payload of a NaN (the hardware returns the canonical one).
+__device__ inline uint32_t f32x2_to_bf16x2(float lo, float hi) {
+    uint32_t d;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+    return d;
+}
 
 // ---- warp / block reductions ---------------------------------------------------------------------
 __device__ inline float warp_sum(float v) {

@@ -106,7 +106,7 @@ __device__ inline void wait_failed(volatile uint32_t *abort_flag, uint32_t *erro
 // exactly scaled f16 (plus the per-group sums the bias term needs) and returns the factor that undoes
 // the scale.  ROUNDS = chunks of 8 elements a thread keeps in registers (K <= ROUNDS * 2048): the
 // code is straight-line per round, and a short instance matters because every launch runs it cold.
-template <int ROUNDS, bool NORM, bool SPLIT, bool TPX>
+template <int ROUNDS, bool NORM, bool SPLIT, bool TPX, bool FOLD>
 __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, uint32_t columns, __half *xs, __half *xlo,
                                             uint16_t *nws, float *xsum, float *xoff, float *wred, float &xunscale) {
     const uint32_t warp = tid >> 5, lane = tid & 31u;
@@ -207,11 +207,11 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
                 uint32_t packed[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const uint16_t lo = f32_to_bf16_bits(bf16_round(acc[2 * i]) + f[r][2 * i]);
-                    const uint16_t hi = f32_to_bf16_bits(bf16_round(acc[2 * i + 1]) + f[r][2 * i + 1]);
-                    f[r][2 * i] = bf16_bits_to_f32(lo);
-                    f[r][2 * i + 1] = bf16_bits_to_f32(hi);
-                    packed[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+                    const uint32_t s2 = f32x2_to_bf16x2(acc[2 * i], acc[2 * i + 1]);  // the projection's bf16 output
+                    packed[i] = f32x2_to_bf16x2(__uint_as_float(s2 << 16) + f[r][2 * i],
+                                                __uint_as_float(s2 & 0xffff0000u) + f[r][2 * i + 1]);
+                    f[r][2 * i] = __uint_as_float(packed[i] << 16);
+                    f[r][2 * i + 1] = __uint_as_float(packed[i] & 0xffff0000u);
                 }
                 if (blockIdx.x == 0)
                     reinterpret_cast<uint4 *>(p.ex.h_out)[c] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -270,10 +270,14 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
                 const uint32_t nwv[4] = {nv.x, nv.y, nv.z, nv.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    // bf16(normalized) * bf16(scale), product rounded to bf16
-                    f[r][2 * i] = bf16_round(bf16_round(f[r][2 * i] * rms_inv) * __uint_as_float(nwv[i] << 16));
-                    f[r][2 * i + 1] =
-                        bf16_round(bf16_round(f[r][2 * i + 1] * rms_inv) * __uint_as_float(nwv[i] & 0xffff0000u));
+                    // bf16(normalized) * bf16(scale), product rounded to bf16; the pair is rounded by one
+                    // packed conversion (every CTA normalizes the whole row, so instruction count matters)
+                    const uint32_t n2 = f32x2_to_bf16x2(f[r][2 * i] * rms_inv, f[r][2 * i + 1] * rms_inv);
+                    const uint32_t p2 = f32x2_to_bf16x2(__uint_as_float(n2 << 16) * __uint_as_float(nwv[i] << 16),
+                                                        __uint_as_float(n2 & 0xffff0000u) *
+                                                            __uint_as_float(nwv[i] & 0xffff0000u));
+                    f[r][2 * i] = __uint_as_float(p2 << 16);
+                    f[r][2 * i + 1] = __uint_as_float(p2 & 0xffff0000u);
                 }
             }
         }
@@ -286,35 +290,47 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
     xunscale = __uint_as_float((uint32_t)(127 - shift) << 23);
 
     // Scaled f16 values, per-group sums of the input (for the bias term) and, for FOLD, -64 * the
-    // per-group sum of the f16 values the tensor core will see.
+    // per-group sum of the f16 values the tensor core will see.  Pairs are converted by one packed
+    // instruction.
 #pragma unroll
     for (int r = 0; r < ROUNDS; ++r) {
         const uint32_t c = tid + r * kConsumerThreads;
         float s8 = 0.0f, h8 = 0.0f;
-        __half hh[8], hl[8];
+        uint32_t hh[4], hl[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            s8 += f[r][i];
-            const float sv = f[r][i] * xscale;
-            hh[i] = __float2half_rn(sv);
-            h8 += __half2float(hh[i]);
-            if (SPLIT) {
-                hl[i] = __float2half_rn(sv - __half2float(hh[i]));
-                h8 += __half2float(hl[i]);
+        for (int i = 0; i < 4; ++i) {
+            const float a = f[r][2 * i], b = f[r][2 * i + 1];
+            s8 += a;
+            s8 += b;
+            const float sa = a * xscale, sb2 = b * xscale;
+            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(hh[i]) : "f"(sb2), "f"(sa));
+            if (SPLIT || FOLD) {
+                const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&hh[i]));
+                h8 += back.x;
+                if (SPLIT) {
+                    const float la = sa - back.x, lb = sb2 - back.y;
+                    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(hl[i]) : "f"(lb), "f"(la));
+                    const float2 lo = __half22float2(*reinterpret_cast<const __half2 *>(&hl[i]));
+                    h8 += lo.x;
+                    h8 += back.y;
+                    h8 += lo.y;
+                } else {
+                    h8 += back.y;
+                }
             }
         }
         if (c < chunks) {
-            reinterpret_cast<uint4 *>(xs)[c] = *reinterpret_cast<uint4 *>(hh);
-            if (SPLIT) reinterpret_cast<uint4 *>(xlo)[c] = *reinterpret_cast<uint4 *>(hl);
+            reinterpret_cast<uint4 *>(xs)[c] = make_uint4(hh[0], hh[1], hh[2], hh[3]);
+            if (SPLIT) reinterpret_cast<uint4 *>(xlo)[c] = make_uint4(hl[0], hl[1], hl[2], hl[3]);
         }
 #pragma unroll
         for (int o = 1; o < 8; o <<= 1) {
             s8 += __shfl_xor_sync(0xffffffffu, s8, o);
-            h8 += __shfl_xor_sync(0xffffffffu, h8, o);
+            if (FOLD) h8 += __shfl_xor_sync(0xffffffffu, h8, o);
         }
         if (c < chunks && (lane & 7u) == 0) {
             xsum[c >> 3] = s8;
-            xoff[c >> 3] = -64.0f * h8;
+            if (FOLD) xoff[c >> 3] = -64.0f * h8;
         }
     }
     named_bar_sync(1, kConsumerThreads);
@@ -493,11 +509,11 @@ __global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
     float xunscale;
     const bool norm = p.prologue == kProRmsNorm;
     if (columns <= 2u * kConsumerThreads * 8u) {
-        if (norm) stage_input<2, true, SPLIT, TPX>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
-        else stage_input<2, false, SPLIT, false>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        if (norm) stage_input<2, true, SPLIT, TPX, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        else stage_input<2, false, SPLIT, false, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
     } else {
-        if (norm) stage_input<kMaxRounds, true, SPLIT, TPX>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
-        else stage_input<kMaxRounds, false, SPLIT, false>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        if (norm) stage_input<kMaxRounds, true, SPLIT, TPX, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        else stage_input<kMaxRounds, false, SPLIT, false, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
     }
 
     // Main loop: no block-wide barrier from here on.
