@@ -1,0 +1,49 @@
+"""Regenerates `oracle_outputs.npz`: outputs of the CPU oracle on seeded inputs, committed so that the GPU
+parity tests can also be checked against values that were produced once and never move.
+
+    python tests/golden/make_golden.py
+
+Inputs come from `stark_b200.synthetic` (seeded), outputs from `oracle/` only.  The arrays:
+  matvec_y        bf16 bits, the 4-bit affine matvec of `matvec_case(seed=3, rows=512, columns=1024)`
+  tiny_logits     bf16 bits, last-row logits of the `tiny` decoder (weights seed 0) after `prompt(tiny, 70, seed=5)`
+  tiny_greedy     the oracle's own greedy continuation of that prompt, 8 tokens
+  q8_0_row / q4_k_row   f32, row 1 of `q8_0_rows` / `q4_k_rows` (default_rng(11), 4 x 512) decoded
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+
+from oracle import oracle as O  # noqa: E402
+from stark_b200 import synthetic as S  # noqa: E402
+
+
+def build() -> dict:
+    out = {}
+    w = S.matvec_case(seed=3, rows=512, columns=1024)
+    out["matvec_y"] = O.affine_matvec_bf16(w["codes"], w["scales"], w["biases"], w["x"], 512, 1024)[0]
+    cfg = S.CONFIGS["tiny"]
+    weights = S.dense_weights(cfg, seed=0)
+    prompt = S.prompt(cfg, 70, seed=5)
+    orc = O.DenseOracle(cfg, weights, capacity=128)
+    for t in prompt[:-1]:
+        orc.ingest(int(t))
+    logits = orc.step(int(prompt[-1]))
+    out["tiny_logits"] = np.asarray(logits, np.uint16)
+    toks, tok = [], O.argmax_bf16(logits)
+    for _ in range(8):
+        toks.append(tok)
+        tok = O.argmax_bf16(orc.step(tok))
+    out["tiny_greedy"] = np.asarray(toks, np.uint32)
+    rng = np.random.default_rng(11)
+    out["q8_0_row"] = O.gguf_decode_row(O.Q8_0, S.q8_0_rows(rng, 4, 512)[1], 512)
+    out["q4_k_row"] = O.gguf_decode_row(O.Q4_K, S.q4_k_rows(rng, 4, 512)[1], 512)
+    return out
+
+
+if __name__ == "__main__":
+    np.savez_compressed(Path(__file__).with_name("oracle_outputs.npz"), **build())
+    print("wrote", Path(__file__).with_name("oracle_outputs.npz"))
