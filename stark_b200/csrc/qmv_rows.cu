@@ -272,12 +272,18 @@ __global__ void __launch_bounds__(kRowThreads) qmv_rows_kernel(const RowParams p
             if (FORMAT == kFmtQ8_0) {
                 const uint8_t *blk = chunk + 34u * lane;
                 const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t *>(blk));
+                // The 32 codes start 2 bytes into the 34-byte block, i.e. on a 4-byte boundary for odd
+                // lanes and 2 bytes past one for even lanes: read aligned words and funnel-shift.
+                const uint32_t qoff = 34u * lane + 2u, sh = (qoff & 2u) * 8u;
+                const uint32_t *wp = reinterpret_cast<const uint32_t *>(chunk + (qoff & ~3u));
+                uint32_t wv[9];
+#pragma unroll
+                for (uint32_t k = 0; k < 8; ++k) wv[k] = wp[k];
+                wv[8] = sh ? wp[8] : 0u;  // only even lanes need the ninth word (it exists: it is the next block)
                 float t = 0.0f;
 #pragma unroll
                 for (uint32_t i4 = 0; i4 < 8; ++i4) {
-                    const uint32_t lo = *reinterpret_cast<const uint16_t *>(blk + 2u + 4u * i4);
-                    const uint32_t hi = *reinterpret_cast<const uint16_t *>(blk + 4u + 4u * i4);
-                    const uint32_t w = (lo | (hi << 16)) ^ 0x80808080u;  // int8 + 128
+                    const uint32_t w = __funnelshift_r(wv[i4], wv[i4 + 1], sh) ^ 0x80808080u;  // int8 + 128
                     t = dot4_bytes(w, xb[i4 ^ sw], t);
                 }
                 // sum (q + 128) x - 128 sum x
