@@ -52,6 +52,10 @@ def shard_dense(cfg: dict, weights: dict, rank: int, ranks: int) -> tuple[dict, 
     vocabulary row of the read-out shard).  The reference runs on one device; this is how the same
     graph (crates/stark-engine/src/encodable_block/transformer_layer.rs:549-659) is spread over several.
     """
+    from .artifact import row_major_planes
+    weights = dict(weights, embed=row_major_planes(weights["embed"]), lm_head=row_major_planes(weights["lm_head"]),
+                   layers=[dict(lw, **{k: row_major_planes(lw[k]) for k in ("qkv", "o", "upgate", "down")})
+                           for lw in weights["layers"]])
     hq, hkv, hd, inter = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["inter"]
     if hq % ranks or hkv % ranks or inter % (16 * ranks) or (inter // ranks) % 64:
         raise ValueError(f"{ranks} ranks do not divide heads {hq}/{hkv} or width {inter} into whole shards")
@@ -99,7 +103,8 @@ class DenseModel:
     def _set_matrix(self, layer: int, which: int, t: dict):
         lib = _lib.load()
         d = _lib.AffineDesc(C.sizeof(_lib.AffineDesc), _lib.ABI_VERSION, t["n"], t["k"], t["bits"], t["group"],
-                            _lib.PLANE_BF16, 0, 0, _lib.HOST, 0, 0)
+                            _lib.PLANE_BF16, int(t.get("scale_layout", 0)), int(t.get("plane_pitch", 0)), _lib.HOST,
+                            0, 0)
         codes = np.ascontiguousarray(t["codes"])
         scales = np.ascontiguousarray(t["scales"], np.uint16)
         biases = np.ascontiguousarray(t["biases"], np.uint16)
@@ -148,6 +153,15 @@ class DenseModel:
             tp.all_gather(b"")  # every rank has uploaded its shard: the recording pass below is collective
         check(_lib.load().stark_b200_model_finalize(m._h), "model_finalize")
         return m
+
+    @classmethod
+    def from_artifact(cls, directory, context_tokens: int, tp: "TensorParallel | None" = None) -> "DenseModel":
+        """Load a converted-model directory (``config.json`` + ``model.safetensors`` in the reference's
+        layout, see ``stark_b200.artifact``); the analogue of ``Engine::new`` -> ``load_language_model``
+        (crates/stark-engine/src/engine/language_model/mod.rs:72-127)."""
+        from .artifact import read_artifact
+        cfg, weights = read_artifact(directory)
+        return cls.load(cfg, weights, context_tokens, tp=tp)
 
     def _gather_vocab(self, local: np.ndarray) -> np.ndarray:
         """Whole-vocabulary vector from the ranks' read-out shards (identity on one GPU)."""

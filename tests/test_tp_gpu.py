@@ -1,7 +1,7 @@
-"""Tensor-parallel decode on two GPUs against the CPU oracle and against the single-GPU engine.
+"""Tensor-parallel decode on 2, 4 and 8 GPUs against the CPU oracle and against the single-GPU engine.
 
-The test launches one process per GPU (this file is also the rank program); it is skipped on a box
-with fewer than two GPUs.  Ranks rendezvous over gloo on 127.0.0.1: the host side only moves the
+The test launches one process per GPU (this file is also the rank program); a case is skipped on a box
+with fewer GPUs than it needs.  Ranks rendezvous over gloo on 127.0.0.1: the host side only moves the
 64-byte buffer handles and read-out shards, the per-token exchange happens on the device.
 """
 import os
@@ -24,14 +24,14 @@ def _gpu_count() -> int:
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("config", ["tiny", "small"])
-def test_two_ranks_match_oracle_and_single_gpu(config):
-    if _gpu_count() < 2:
-        pytest.skip("needs two GPUs")
+@pytest.mark.parametrize("config,ranks", [("tiny", 2), ("small", 2), ("small", 4), ("small", 8)])
+def test_ranks_match_oracle_and_single_gpu(config, ranks):
+    if _gpu_count() < ranks:
+        pytest.skip(f"needs {ranks} GPUs")
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
         port = s.getsockname()[1]
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
            "127.0.0.1", "--master-port", str(port), str(Path(__file__).resolve()), config]
     res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=900)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
