@@ -353,6 +353,35 @@ stark_b200_status stark_b200_readout_bf16(stark_b200_model *model, uint16_t *dst
 stark_b200_status stark_b200_readout_logprobs_f32(stark_b200_model *model, float *dst, size_t count);
 /* Greedy token of the last row (first index of the maximum). */
 stark_b200_status stark_b200_argmax(stark_b200_model *model, uint32_t *out_token);
+/* Sampling parameters of the reference's unified sampler
+ * (crates/stark-engine/src/backends/cpu/kernel/sampling/unified_sampling.rs:15-117; bounds as in
+ * SamplingMethod::validate, crates/stark-generate/src/generation.rs:67-111).  flags: 1 stochastic
+ * (Gumbel-max with Philox4x32-10 noise keyed by `seed`; derive the seed per position on the host as the
+ * reference does, sampling/prng.rs:12-22), 2 temperature, 4 top_k, 8 top_p, 16 min_p.  flags = 0 is the
+ * greedy pick.  top-k / top-p / min-p cut ONE prefix of the descending order (ties: lower index first),
+ * exactly as the reference; the token is UINT32_MAX if any logit is not finite. */
+typedef struct stark_b200_sampling {
+    uint32_t struct_size;
+    uint32_t flags;
+    uint64_t seed;
+    float temperature;
+    uint32_t top_k;
+    float top_p;
+    float min_p;
+} stark_b200_sampling;
+#define STARK_B200_SAMPLE_STOCHASTIC 1u
+#define STARK_B200_SAMPLE_TEMPERATURE 2u
+#define STARK_B200_SAMPLE_TOP_K 4u
+#define STARK_B200_SAMPLE_TOP_P 8u
+#define STARK_B200_SAMPLE_MIN_P 16u
+/* One row of `vocab` logits (io_type BF16 or F32; host or device) -> one token (host). */
+stark_b200_status stark_b200_op_sample(const void *logits, uint32_t vocab, uint32_t io_type,
+                                       const stark_b200_sampling *params, uint32_t *out_token, uint32_t location,
+                                       void *stream);
+/* Samples from the logits of the model's last row (Sampling::encode on the last row,
+ * encodable_block/sampling/mod.rs:119-249); feed the token back with stark_b200_step.  UNSUPPORTED on a
+ * tensor-parallel handle (the logits are sharded). */
+stark_b200_status stark_b200_sample(stark_b200_model *model, const stark_b200_sampling *params, uint32_t *out_token);
 /* Greedy decode chained on the device: out_tokens[0] is the greedy token of the current logits,
  * out_tokens[i] the one after feeding out_tokens[i-1]; steps + 1 entries.  The analogue of the
  * reference's on-device token chaining (stream.rs:1041-1047). */

@@ -253,6 +253,48 @@ def argmax_f32(logits) -> int:
     return int(lib().so_argmax_f32(_p(logits), logits.size))
 
 
+def philox4x32_10(ctr, key) -> np.ndarray:
+    """gumbel.rs:16-46: ten rounds, key bumped by the Weyl constants between rounds."""
+    ctr, key, out = _c(ctr, np.uint32), _c(key, np.uint32), np.zeros(4, np.uint32)
+    lib().so_philox4x32_10(_p(ctr), _p(key), _p(out))
+    return out
+
+
+def unit_interval(word: int) -> float:
+    f = lib().so_unit_interval
+    f.restype, f.argtypes = C.c_float, [C.c_uint32]
+    return float(f(word))
+
+
+def gumbel_float(key: int, offset: int, word: int) -> float:
+    f = lib().so_gumbel_float
+    f.restype, f.argtypes = C.c_float, [C.c_uint64, C.c_uint32, C.c_uint32]
+    return float(f(key, offset, word))
+
+
+def revidx(index: int, vocab: int) -> tuple[int, int]:
+    off, word = C.c_uint32(0), C.c_uint32(0)
+    lib().so_revidx(C.c_uint32(index), C.c_uint32(vocab), C.byref(off), C.byref(word))
+    return off.value, word.value
+
+
+def prng_derive(seed: int, index: int) -> int:
+    f = lib().so_prng_derive
+    f.restype, f.argtypes = C.c_uint64, [C.c_uint64, C.c_uint64]
+    return int(f(seed, index))
+
+
+def unified_sampling(logits, seed=None, temperature=None, top_k=None, top_p=None, min_p=None) -> int:
+    """unified_sampling.rs:15-117 on one row of f32 logits; ``seed`` None = greedy."""
+    logits = _c(logits, np.float32)
+    flags = (1 if seed is not None else 0) | (2 if temperature is not None else 0) | (4 if top_k is not None else 0) \
+        | (8 if top_p is not None else 0) | (16 if min_p is not None else 0)
+    f = lib().so_unified_sampling_f32
+    f.restype = C.c_uint32
+    f.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint64, C.c_float, C.c_uint32, C.c_float, C.c_float]
+    return int(f(_p(logits), logits.size, flags, seed or 0, temperature or 1.0, top_k or 0, top_p or 1.0, min_p or 0.0))
+
+
 def log_softmax_f64(logits) -> np.ndarray:
     logits = _c(logits, np.float32)
     out = np.empty(logits.size, np.float64)

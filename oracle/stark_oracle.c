@@ -760,3 +760,142 @@ void so_dense_matvec_f32(const float *w, const float *x, float *y, uint32_t rows
         y[r] = total;
     }
 }
+
+/* ------------------------------------------------------------------------------------------------
+ * Stochastic sampling of the converted-model path.
+ *   Philox4x32-10 counter-based generator, Gumbel noise, index -> (counter offset, word) mapping:
+ *     crates/stark-engine/src/encodable_block/sampling/gumbel.rs:1-85
+ *   per-position seed derivation (the 64-bit finalizer of MurmurHash3):
+ *     crates/stark-engine/src/encodable_block/sampling/prng.rs:12-22
+ *   the sampler itself (finite check, temperature with overflow centring, top-k / top-p / min-p as one
+ *   prefix of the descending order, Gumbel-max, first index of the maximum):
+ *     crates/stark-engine/src/backends/cpu/kernel/sampling/unified_sampling.rs:15-117
+ */
+static void philox_round(uint32_t c[4], const uint32_t k[2]) {
+    const uint64_t p0 = (uint64_t)0xD2511F53u * c[0], p1 = (uint64_t)0xCD9E8D57u * c[2];
+    const uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k[0], n1 = (uint32_t)p1;
+    const uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k[1], n3 = (uint32_t)p0;
+    c[0] = n0, c[1] = n1, c[2] = n2, c[3] = n3;
+}
+
+void so_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]) {
+    uint32_t c[4] = {ctr[0], ctr[1], ctr[2], ctr[3]}, k[2] = {key[0], key[1]};
+    philox_round(c, k);
+    for (int i = 0; i < 9; ++i) {
+        k[0] += 0x9E3779B9u;
+        k[1] += 0xBB67AE85u;
+        philox_round(c, k);
+    }
+    memcpy(out, c, sizeof c);
+}
+
+float so_unit_interval(uint32_t word) {
+    uint32_t v = word >> 8;
+    if (v < 1u) v = 1u;
+    return (float)v * (1.0f / 16777216.0f);
+}
+
+float so_gumbel_float(uint64_t key, uint32_t offset, uint32_t word) {
+    const uint32_t ctr[4] = {offset, 0u, 0u, 0u}, k[2] = {(uint32_t)key, (uint32_t)(key >> 32)};
+    uint32_t out[4];
+    so_philox4x32_10(ctr, k, out);
+    return -logf(-logf(so_unit_interval(out[word])));
+}
+
+void so_revidx(uint32_t logit_idx, uint32_t vocab, uint32_t *offset, uint32_t *word) {
+    const uint32_t thread_idx = logit_idx % 1024u;
+    const uint32_t thread_offset = ((vocab + 4095u) / 4096u) * thread_idx;
+    const uint32_t block_idx = logit_idx / 1024u;
+    *offset = thread_offset + block_idx / 4u;
+    *word = block_idx % 4u;
+}
+
+uint64_t so_prng_derive(uint64_t seed, uint64_t index) {
+    uint64_t h = seed + index;
+    h ^= h >> 33;
+    h *= 0xff51afd7ed558ccdULL;
+    h ^= h >> 33;
+    h *= 0xc4ceb9fe1a85ec53ULL;
+    h ^= h >> 33;
+    return h;
+}
+
+typedef struct {
+    float v;
+    uint32_t i;
+} so_ranked;
+static int so_ranked_cmp(const void *pa, const void *pb) {
+    const so_ranked *a = (const so_ranked *)pa, *b = (const so_ranked *)pb;
+    if (a->v > b->v) return -1;
+    if (a->v < b->v) return 1;
+    return a->i < b->i ? -1 : (a->i > b->i ? 1 : 0);
+}
+
+/* flags: 1 stochastic, 2 temperature, 4 top_k, 8 top_p, 16 min_p.  Returns the token, UINT32_MAX if a
+ * logit is not finite (or nothing finite is left). */
+uint32_t so_unified_sampling_f32(const float *in, uint32_t vocab, uint32_t flags, uint64_t seed, float temperature,
+                                 uint32_t top_k, float top_p, float min_p) {
+    float *l = (float *)malloc((size_t)vocab * sizeof(float));
+    uint32_t result = 0xffffffffu;
+    for (uint32_t i = 0; i < vocab; ++i) {
+        l[i] = in[i];
+        if (!isfinite(l[i])) {
+            free(l);
+            return result;
+        }
+    }
+    if (flags & 2u) {
+        const float recip = 1.0f / temperature;
+        int center = 0;
+        for (uint32_t i = 0; i < vocab; ++i)
+            if (isfinite(l[i]) && !isfinite(l[i] * recip)) center = 1;
+        float shift = 0.0f;
+        if (center) {
+            shift = -INFINITY;
+            for (uint32_t i = 0; i < vocab; ++i) shift = fmaxf(shift, l[i]);
+        }
+        for (uint32_t i = 0; i < vocab; ++i) {
+            if (center) l[i] -= shift;
+            l[i] *= recip;
+        }
+    }
+    if (flags & (4u | 8u | 16u)) {
+        so_ranked *s = (so_ranked *)malloc((size_t)vocab * sizeof(so_ranked));
+        for (uint32_t i = 0; i < vocab; ++i) s[i].v = l[i], s[i].i = i;
+        qsort(s, vocab, sizeof(so_ranked), so_ranked_cmp);
+        const float top = s[0].v;
+        float norm = 0.0f;
+        for (uint32_t i = 0; i < vocab; ++i) norm += expf(s[i].v - top);
+        for (uint32_t i = 0; i < vocab; ++i) l[i] = -INFINITY;
+        float mass = 0.0f;
+        for (uint32_t n = 0; n < vocab; ++n) {
+            if (((flags & 4u) && n >= top_k) || ((flags & 8u) && mass >= top_p) ||
+                ((flags & 16u) && s[n].v < top + logf(min_p)))
+                break;
+            l[s[n].i] = s[n].v;
+            mass += expf(s[n].v - top) / norm;
+        }
+        free(s);
+    }
+    if (flags & 1u) {
+        for (uint32_t i = 0; i < vocab; ++i) {
+            uint32_t off, word;
+            so_revidx(i, vocab, &off, &word);
+            l[i] += so_gumbel_float(seed, off, word);
+        }
+    }
+    float best = -INFINITY;
+    int have = 0;
+    for (uint32_t i = 0; i < vocab; ++i) {  /* max_by with ties to the lower index; NaN compares equal */
+        if (!have || l[i] > best) {
+            if (!have || l[i] > best) {
+                best = l[i];
+                result = i;
+                have = 1;
+            }
+        }
+    }
+    if (!have || !isfinite(best)) result = 0xffffffffu;
+    free(l);
+    return result;
+}

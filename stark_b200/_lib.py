@@ -57,6 +57,19 @@ class Info(C.Structure):
 MAT_EMBED, MAT_LM_HEAD, MAT_QKV, MAT_O, MAT_UPGATE, MAT_DOWN = range(6)
 VEC_FINAL_NORM, VEC_ATTN_NORM, VEC_MLP_NORM, VEC_Q_NORM, VEC_K_NORM = range(5)
 
+class Sampling(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("flags", C.c_uint32), ("seed", C.c_uint64),
+                ("temperature", C.c_float), ("top_k", C.c_uint32), ("top_p", C.c_float), ("min_p", C.c_float)]
+
+
+def sampling(seed=None, temperature=None, top_k=None, top_p=None, min_p=None) -> Sampling:
+    """``seed`` None = no noise (greedy over whatever the filters keep)."""
+    flags = (1 if seed is not None else 0) | (2 if temperature is not None else 0) | (4 if top_k is not None else 0) \
+        | (8 if top_p is not None else 0) | (16 if min_p is not None else 0)
+    return Sampling(C.sizeof(Sampling), flags, seed or 0, temperature if temperature is not None else 1.0,
+                    top_k or 0, top_p if top_p is not None else 1.0, min_p if min_p is not None else 0.0)
+
+
 _lib = None
 
 
@@ -119,6 +132,8 @@ def load() -> C.CDLL:
         "stark_b200_readout_bf16": (u32, [vp, vp, sz]),
         "stark_b200_readout_logprobs_f32": (u32, [vp, vp, sz]),
         "stark_b200_argmax": (u32, [vp, C.POINTER(u32)]),
+        "stark_b200_sample": (u32, [vp, C.POINTER(Sampling), C.POINTER(u32)]),
+        "stark_b200_op_sample": (u32, [vp, u32, u32, C.POINTER(Sampling), C.POINTER(u32), u32, vp]),
         "stark_b200_generate_greedy": (u32, [vp, u32, vp]),
         "stark_b200_rewind": (u32, [vp, u64]),
         "stark_b200_get_info": (u32, [vp, C.POINTER(Info)]),

@@ -379,6 +379,46 @@ stark_b200_status stark_b200_readout_logprobs_f32(stark_b200_model *model, float
     return STARK_B200_OK;
 }
 
+stark_b200_status stark_b200_sample(stark_b200_model *model, const stark_b200_sampling *params, uint32_t *out_token) {
+    if (!model || !params || !out_token) return STARK_B200_INVALID_ARGUMENT;
+    if (params->struct_size != sizeof(stark_b200_sampling)) return STARK_B200_ABI_MISMATCH;
+    Model *m = M(model);
+    if (!m->has_logits) return STARK_B200_INVALID_STATE;
+    if (m->tp.size > 1u) return STARK_B200_UNSUPPORTED;
+    SB_TRY(sampling_validate(*params, m->cfg.vocab));
+    if (!m->sample_scratch) SB_CUDA(cudaMalloc(&m->sample_scratch, sampling_scratch_bytes(m->cfg.vocab) + 16u));
+    // the token lands behind the working arrays
+    uint32_t *out = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(m->sample_scratch) +
+                                                 sampling_scratch_bytes(m->cfg.vocab));
+    SB_TRY(sampling_launch(m->logits, STARK_B200_BF16, m->cfg.vocab, *params, m->sample_scratch, out, m->stream));
+    SB_CUDA(cudaMemcpyAsync(out_token, out, 4, cudaMemcpyDeviceToHost, m->stream));
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_op_sample(const void *logits, uint32_t vocab, uint32_t io_type,
+                                       const stark_b200_sampling *params, uint32_t *out_token, uint32_t location,
+                                       void *stream) {
+    if (!logits || !params || !out_token || io_type > STARK_B200_F32) return STARK_B200_INVALID_ARGUMENT;
+    if (params->struct_size != sizeof(stark_b200_sampling)) return STARK_B200_ABI_MISMATCH;
+    SB_TRY(sampling_validate(*params, vocab));
+    cudaStream_t s = (cudaStream_t)stream;
+    Staged st;
+    const uint8_t *din = static_cast<const uint8_t *>(logits);
+    if (location == STARK_B200_HOST) {
+        uint8_t *copy;
+        SB_TRY(st.in(static_cast<const uint8_t *>(logits), (size_t)vocab * (io_type == STARK_B200_F32 ? 4u : 2u), &copy));
+        din = copy;
+    }
+    uint8_t *scratch;
+    SB_TRY(st.in((const uint8_t *)nullptr, sampling_scratch_bytes(vocab) + 16u, &scratch));
+    uint32_t *out = reinterpret_cast<uint32_t *>(scratch + sampling_scratch_bytes(vocab));
+    SB_TRY(sampling_launch(din, io_type, vocab, *params, scratch, out, s));
+    SB_CUDA(cudaMemcpyAsync(out_token, out, 4, cudaMemcpyDeviceToHost, s));
+    SB_CUDA(cudaStreamSynchronize(s));
+    return STARK_B200_OK;
+}
+
 stark_b200_status stark_b200_argmax(stark_b200_model *model, uint32_t *out_token) {
     if (!model || !out_token) return STARK_B200_INVALID_ARGUMENT;
     return model_next_token(M(model), out_token);

@@ -88,6 +88,7 @@ Model::~Model() {
         for (uint32_t r = 0; r < tp.size; ++r)
             if (r != tp.rank && tp.base[r]) cudaIpcCloseMemHandle(tp.base[r]);
     cudaFree(tp_local);
+    cudaFree(sample_scratch);
     cudaFree(tp_seq);
     if (host_state) cudaFreeHost(host_state);
     if (host_logits) cudaFreeHost(host_logits);

@@ -54,6 +54,7 @@ struct Model {
     uint32_t *tp_seq = nullptr;    // [0] tokens finished: the base of the exchange tickets
     uint32_t tp_vocab_offset = 0, tp_vocab_total = 0;
     bool tp_connected = false;
+    void *sample_scratch = nullptr;     // device working memory of the sampler (allocated at first use)
     StepState *host_state = nullptr;    // pinned
     uint16_t *host_logits = nullptr;    // pinned
     uint64_t position = 0;              // host mirror of state->position

@@ -80,6 +80,13 @@ stark_b200_status moe_route_launch(const float *logits, uint32_t *ids, float *we
                                    uint32_t experts, uint32_t active, bool round_weights, bool round_logits,
                                    cudaStream_t stream);
 
+// Stochastic sampling over one row of logits (sampling.cu); `scratch` = sampling_scratch_bytes(vocab)
+// bytes of device memory, `out_device` one u32.
+size_t sampling_scratch_bytes(uint32_t vocab);
+stark_b200_status sampling_validate(const stark_b200_sampling &s, uint32_t vocab);
+stark_b200_status sampling_launch(const void *logits, uint32_t io_type, uint32_t vocab, const stark_b200_sampling &s,
+                                  void *scratch, uint32_t *out_device, cudaStream_t stream);
+
 // Routed-expert selection of the hybrid host path: top-k of the scores (value descending, index
 // ascending), softmax over the selected scores (hybrid/qwen.rs:872-874, math.rs:36-66).
 stark_b200_status moe_select_launch(const float *scores, uint32_t experts, uint32_t active, uint32_t *ids,

@@ -224,6 +224,14 @@ class DenseModel:
         self._guard(_lib.load().stark_b200_argmax(self._h, C.byref(t)), "argmax")
         return t.value
 
+    def sample(self, seed=None, temperature=None, top_k=None, top_p=None, min_p=None) -> int:
+        """One token from the last row's logits through the device sampler (the reference's unified
+        sampler; ``seed`` is the per-position seed, see ``position_seed``)."""
+        params = _lib.sampling(seed, temperature, top_k, top_p, min_p)
+        t = C.c_uint32(0)
+        self._guard(_lib.load().stark_b200_sample(self._h, C.byref(params), C.byref(t)), "sample")
+        return t.value
+
     def generate_greedy(self, steps: int) -> np.ndarray:
         out = np.empty(steps + 1, np.uint32)
         self._guard(_lib.load().stark_b200_generate_greedy(self._h, steps, out.ctypes.data), "generate_greedy")
@@ -278,6 +286,19 @@ class DenseModel:
             self.close(collective=False)
         except Exception:
             pass
+
+
+def position_seed(seed: int, position: int) -> int:
+    """Per-position sampling seed, ``PRng::derive`` (crates/stark-engine/src/encodable_block/sampling/prng.rs:12-22):
+    the 64-bit MurmurHash3 finalizer of ``seed + position``."""
+    mask = (1 << 64) - 1
+    h = (seed + position) & mask
+    h ^= h >> 33
+    h = (h * 0xFF51AFD7ED558CCD) & mask
+    h ^= h >> 33
+    h = (h * 0xC4CEB9FE1A85EC53) & mask
+    h ^= h >> 33
+    return h
 
 
 def reusable_prefix_rows(previous_prompt_len: int, common_prefix: int, new_prompt_len: int,

@@ -206,6 +206,17 @@ def log_softmax(logits: np.ndarray) -> np.ndarray:
     return out
 
 
+def sample(logits: np.ndarray, seed=None, temperature=None, top_k=None, top_p=None, min_p=None) -> int:
+    """One token from one row of logits (f32, or bf16 bit patterns as uint16) through the device sampler."""
+    logits = np.ascontiguousarray(logits)
+    io = _lib.F32 if logits.dtype == np.float32 else _lib.BF16
+    params = _lib.sampling(seed, temperature, top_k, top_p, min_p)
+    tok = C.c_uint32(0)
+    check(_lib.load().stark_b200_op_sample(_ptr(logits), logits.size, io, C.byref(params), C.byref(tok), HOST, None),
+          "op_sample")
+    return tok.value
+
+
 def moe_route(logits: np.ndarray, experts: int, active: int, round_weights=False, round_logits=False):
     logits = np.ascontiguousarray(logits, np.float32).reshape(-1, experts)
     rows = logits.shape[0]
