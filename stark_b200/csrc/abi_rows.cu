@@ -47,20 +47,34 @@ stark_b200_status make_gguf(const void *blocks, uint32_t kind, uint32_t experts,
     if (rows == 0 || columns == 0 || experts == 0 || columns % block != 0) return STARK_B200_INVALID_ARGUMENT;
     QMatrix *m = new (std::nothrow) QMatrix();
     if (!m) return STARK_B200_OUT_OF_MEMORY;
-    m->format = kind == STARK_B200_GGUF_Q8_0 ? kFmtQ8_0 : kFmtQ4_K;
+    static const bool q4k_rows = [] {
+        const char *e = getenv("STARK_B200_Q4K_ROWS");
+        return e && e[0] == '1';
+    }();
+    const bool tiled = kind == STARK_B200_GGUF_Q4_K && !q4k_rows;
+    m->format = kind == STARK_B200_GGUF_Q8_0 ? kFmtQ8_0 : (tiled ? kFmtQ4_K : kFmtQ4_KRaw);
     m->rows = rows;
     m->columns = columns;
-    m->row_tiles = 0;
+    m->row_tiles = tiled ? (rows + 15u) / 16u : 0;
     m->groups = columns / 64u;
     m->pair_halves = 0;
     m->record_bytes = 0;
     m->experts = experts;
-    m->bytes = gguf_row_bytes(kind, columns) * rows * experts;
+    const size_t source_bytes = gguf_row_bytes(kind, columns) * rows * experts;
+    m->bytes = tiled ? q4kt_bytes(experts, rows, columns) : source_bytes;
     cudaGetDevice(&m->device);
+    const cudaMemcpyKind dir = location == STARK_B200_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
     cudaError_t e = cudaMalloc(&m->data, m->bytes);
-    if (e == cudaSuccess)
-        e = cudaMemcpy(m->data, blocks, m->bytes,
-                       location == STARK_B200_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice);
+    if (e == cudaSuccess && !tiled) e = cudaMemcpy(m->data, blocks, m->bytes, dir);
+    if (e == cudaSuccess && tiled) {
+        // Q4_K is re-tiled into tensor-core fragment order: stage the source bytes, re-tile, drop the copy
+        uint8_t *staging = nullptr;
+        e = cudaMalloc(&staging, source_bytes);
+        if (e == cudaSuccess) e = cudaMemcpy(staging, blocks, source_bytes, dir);
+        if (e == cudaSuccess && q4kt_retile(staging, m, nullptr) != STARK_B200_OK) e = cudaErrorUnknown;
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        cudaFree(staging);
+    }
     if (e != cudaSuccess) {
         qmatrix_free(m);
         return cuda_status(e);

@@ -9,7 +9,8 @@ enum QFormat : uint32_t {
     kFmtAffine4 = 0,  // MLX affine, 4 bit, group 64, bf16 planes: 576-byte records
     kFmtAffine8 = 1,  // MLX affine, 8 bit, group 64, bf16 planes: 1088-byte records
     kFmtQ8_0 = 2,     // GGUF Q8_0: 16 rows x 64 columns per record, f16 block scales
-    kFmtQ4_K = 3,     // GGUF Q4_K: 16 rows x 256 columns per record
+    kFmtQ4_K = 3,     // GGUF Q4_K re-tiled: 16 rows x 256 columns per 2304-byte super-record (qmv_q4k.cu)
+    kFmtQ4_KRaw = 4,  // GGUF Q4_K in the source byte layout (row-wise kernel; STARK_B200_Q4K_ROWS=1)
 };
 
 // One record covers 16 rows x 64 columns (one quantization group per row).
@@ -111,6 +112,14 @@ stark_b200_status qmatrix_from_affine_device(const uint8_t *codes, const void *s
                                              QMatrix **out);
 stark_b200_status qmatrix_unpack_codes_device(const QMatrix *m, uint8_t *dst_device, cudaStream_t stream);
 void qmatrix_free(QMatrix *m);
+
+// Tensor-core Q4_K (qmv_q4k.cu): re-tile a device copy of the source blocks into m->data, multiply, decode.
+size_t q4kt_bytes(uint32_t experts, uint32_t rows, uint32_t columns);
+stark_b200_status q4kt_retile(const uint8_t *blocks_device, QMatrix *m, cudaStream_t stream);
+stark_b200_status q4kt_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
+                              const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream);
+stark_b200_status q4kt_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,
+                                  uint8_t *codes_device, cudaStream_t stream);
 
 // Row-wise kernels for the formats kept in the reference's byte layout (qmv_rows.cu).
 bool qmv_rows_supports(const QMatrix *m);

@@ -81,7 +81,7 @@ template <uint32_t FORMAT>
 __device__ inline float row_dot(const RowParams &p, const uint8_t *row, const uint16_t *srow, const uint16_t *brow,
                                 const float *xs, uint32_t lane) {
     float acc = 0.0f;
-    if (FORMAT == kFmtQ4_K) {
+    if (FORMAT == kFmtQ4_KRaw) {
         const uint32_t subs = p.columns / 32u;
         for (uint32_t si = lane; si < subs; si += 32) {
             const Q4kSub s = q4k_load_sub(row + (size_t)(si >> 3) * 144u, si & 7u);
@@ -170,7 +170,7 @@ constexpr uint32_t kChunkValues = 1024;
 
 template <uint32_t FORMAT>
 __host__ __device__ constexpr uint32_t chunk_bytes() {
-    return FORMAT == kFmtQ8_0 ? 1088u : (FORMAT == kFmtQ4_K ? 576u : 1024u);
+    return FORMAT == kFmtQ8_0 ? 1088u : (FORMAT == kFmtQ4_KRaw ? 576u : 1024u);
 }
 
 __device__ inline float byte_to_f32(uint32_t word, uint32_t selector) {
@@ -288,7 +288,7 @@ __global__ void __launch_bounds__(kRowThreads) qmv_rows_kernel(const RowParams p
                 }
                 // sum (q + 128) x - 128 sum x
                 acc = fmaf(d, fmaf(-128.0f, xsum[block], t), acc);
-            } else if (FORMAT == kFmtQ4_K) {
+            } else if (FORMAT == kFmtQ4_KRaw) {
                 const uint8_t *blk = chunk + 144u * (lane >> 3);
                 const uint32_t j = lane & 7u;
                 const uint32_t dd = *reinterpret_cast<const uint32_t *>(blk);
@@ -348,7 +348,7 @@ __global__ void dequant_row_kernel(const RowParams p, uint32_t row, float *out, 
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < p.columns; i += gridDim.x * blockDim.x) {
         float v;
         uint32_t code;
-        if (FORMAT == kFmtQ4_K) {
+        if (FORMAT == kFmtQ4_KRaw) {
             const Q4kSub s = q4k_load_sub(r + (size_t)(i >> 8) * 144u, (i >> 5) & 7u);
             code = q4k_code(s, i & 31u);
             v = q4k_value(s, code);
@@ -370,7 +370,7 @@ __global__ void dequant_row_kernel(const RowParams p, uint32_t row, float *out, 
 
 size_t format_row_bytes(QFormat f, uint32_t columns) {
     switch (f) {
-        case kFmtQ4_K: return (size_t)(columns / 256u) * 144u;
+        case kFmtQ4_KRaw: return (size_t)(columns / 256u) * 144u;
         case kFmtQ8_0: return (size_t)(columns / 32u) * 34u;
         case kFmtAffine8: return columns;
         default: return 0;
@@ -435,12 +435,14 @@ stark_b200_status launch_rows(const QMatrix *m, const RowParams &p, uint32_t bat
 }  // namespace
 
 bool qmv_rows_supports(const QMatrix *m) {
-    return m && (m->format == kFmtQ4_K || m->format == kFmtQ8_0 || m->format == kFmtAffine8);
+    return m && (m->format == kFmtQ4_K || m->format == kFmtQ4_KRaw || m->format == kFmtQ8_0 ||
+                 m->format == kFmtAffine8);
 }
 
 stark_b200_status qmv_rows_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
                                   const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream) {
     if (!qmv_rows_supports(m) || !x || !y || batch == 0) return STARK_B200_INVALID_ARGUMENT;
+    if (m->format == kFmtQ4_K) return q4kt_launch(m, x, x_stride, y, batch, expert_ids, io_type, stream);
     if (m->columns > 12288u) return STARK_B200_UNSUPPORTED;
     RowParams p = row_params(m);
     p.x = x;
@@ -448,7 +450,7 @@ stark_b200_status qmv_rows_launch(const QMatrix *m, const void *x, size_t x_stri
     p.y = y;
     p.io_type = io_type;
     p.expert_ids = expert_ids;
-    if (m->format == kFmtQ4_K) return launch_rows<kFmtQ4_K>(m, p, batch, stream);
+    if (m->format == kFmtQ4_KRaw) return launch_rows<kFmtQ4_KRaw>(m, p, batch, stream);
     if (m->format == kFmtQ8_0) return launch_rows<kFmtQ8_0>(m, p, batch, stream);
     return launch_rows<kFmtAffine8>(m, p, batch, stream);
 }
@@ -456,6 +458,7 @@ stark_b200_status qmv_rows_launch(const QMatrix *m, const void *x, size_t x_stri
 stark_b200_status qmv_rows_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,
                                       uint8_t *codes_device, cudaStream_t stream) {
     if (!qmv_rows_supports(m) || row >= m->rows || expert >= (m->experts ? m->experts : 1u)) return STARK_B200_INVALID_ARGUMENT;
+    if (m->format == kFmtQ4_K) return q4kt_dequantize(m, expert, row, out_device, codes_device, stream);
     RowParams p = row_params(m);
     p.data += (size_t)expert * p.expert_bytes;
     if (p.scales) {
@@ -463,7 +466,7 @@ stark_b200_status qmv_rows_dequantize(const QMatrix *m, uint32_t expert, uint32_
         p.biases += (size_t)expert * p.expert_plane_elems;
     }
     const uint32_t blocks = std::max(1u, std::min(64u, (m->columns + 255u) / 256u));
-    if (m->format == kFmtQ4_K) dequant_row_kernel<kFmtQ4_K><<<blocks, 256, 0, stream>>>(p, row, out_device, codes_device);
+    if (m->format == kFmtQ4_KRaw) dequant_row_kernel<kFmtQ4_KRaw><<<blocks, 256, 0, stream>>>(p, row, out_device, codes_device);
     else if (m->format == kFmtQ8_0) dequant_row_kernel<kFmtQ8_0><<<blocks, 256, 0, stream>>>(p, row, out_device, codes_device);
     else dequant_row_kernel<kFmtAffine8><<<blocks, 256, 0, stream>>>(p, row, out_device, codes_device);
     SB_CUDA(cudaGetLastError());
