@@ -18,6 +18,7 @@
 // decode (crates/stark-engine/src/engine/hybrid/weights.rs:2993-3017, 2908-2920); the dot product
 // regroups it as d*sc * sum(q x) - dmin*m * sum(x), inside the reference's 2e-5 * sum|w x| bound.
 #include <algorithm>
+#include <cmath>
 
 #include "device_math.cuh"
 #include "qmv.cuh"
@@ -27,7 +28,6 @@ namespace sb {
 namespace {
 
 constexpr uint32_t kSuperBytes = 2304;
-constexpr int kQ4Threads = 256, kQ4Warps = 8, kQ4Stages = 4;
 
 __device__ inline float f16_bits_f32(uint32_t h) { return __half2float(__ushort_as_half((uint16_t)h)); }
 
@@ -39,6 +39,18 @@ __device__ inline void q4k_pair(const uint4 &hdr, uint32_t j, uint32_t &sc, uint
     const bool upper = j >= 4u;
     sc = upper ? ((hi & 15u) | ((lo >> 6) << 4)) : (lo & 63u);
     mn = upper ? ((hi >> 4) | ((mid >> 6) << 4)) : (mid & 63u);
+}
+
+// d*sc and dmin*m of sub-blocks t and t + 4 of one row: both take their bytes from the same lane of the
+// three scale words, so the extraction is shared.
+__device__ inline void q4k_scales_pair(const uint4 &hdr, uint32_t t, float (&dsc)[2], float (&dm)[2]) {
+    const uint32_t s = 8u * t;
+    const uint32_t lo = (hdr.y >> s) & 255u, mid = (hdr.z >> s) & 255u, hi = (hdr.w >> s) & 255u;
+    const float d = f16_bits_f32(hdr.x & 0xffffu), dmin = f16_bits_f32(hdr.x >> 16);
+    dsc[0] = d * (float)(lo & 63u);
+    dm[0] = dmin * (float)(mid & 63u);
+    dsc[1] = d * (float)((hi & 15u) | ((lo >> 6) << 4));
+    dm[1] = dmin * (float)((hi >> 4) | ((mid >> 6) << 4));
 }
 
 struct Q4ktParams {
@@ -53,15 +65,23 @@ struct Q4ktParams {
     uint32_t io_type;
 };
 
-__global__ void __launch_bounds__(kQ4Threads) qmv_q4kt_kernel(const Q4ktParams p) {
+// WARPS x STAGES super-records of shared memory per CTA: how many warps hide the decode latency against how
+// many copies each keeps in flight.
+// KS warps (a team) share a row tile, each taking every KS-th super-block, and add their partial rows
+// through shared memory: small matrices have too few row tiles to fill the GPU with one warp per tile.
+template <int kQ4Warps, int kQ4Stages, int KS>
+__global__ void __launch_bounds__(kQ4Warps * 32) qmv_q4kt_kernel(const Q4ktParams p) {
+    constexpr int kQ4Threads = kQ4Warps * 32;
+    constexpr int kTeams = kQ4Warps / KS;
+    __shared__ float team_rows[kQ4Warps][16];
     extern __shared__ __align__(16) uint8_t q4_smem[];
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5, b = blockIdx.y;
     const uint32_t g = lane >> 2, t = lane & 3u, K = p.columns;
     __half *xhi = reinterpret_cast<__half *>(q4_smem);
-    __half *xlo = xhi + K;
-    float *xsum = reinterpret_cast<float *>(xlo + K);  // per 32 columns, of the unscaled input
-    float *red = xsum + K / 32u;                       // [8] block maxima
-    uint8_t *stage = reinterpret_cast<uint8_t *>(red + 8) + (size_t)warp * kQ4Stages * kSuperBytes;
+    __half *xlo = xhi + K + 32;  // 64 bytes on: the head and remainder reads of a warp hit different banks
+    float *xsum = reinterpret_cast<float *>(xlo + K + 32);  // per 32 columns, of the unscaled input
+    float *red = xsum + K / 32u;                       // [kQ4Warps] block maxima
+    uint8_t *stage = reinterpret_cast<uint8_t *>(red + kQ4Warps) + (size_t)warp * kQ4Stages * kSuperBytes;
 
     // ---- input row: exact power-of-two scale into f16 range, head + remainder, per-32 sums ----
     float vmax = 0.0f;
@@ -101,19 +121,20 @@ __global__ void __launch_bounds__(kQ4Threads) qmv_q4kt_kernel(const Q4ktParams p
         if (expert >= p.experts) expert = 0;  // moe_gather_rows: an invalid id falls back to expert 0 (moe.rs:84-101)
     }
     const uint8_t *base = p.data + (size_t)expert * p.expert_bytes;
-    const uint32_t gw = blockIdx.x * kQ4Warps + warp, nw = gridDim.x * kQ4Warps;
+    const uint32_t team = warp / KS, member = warp % KS;
+    const uint32_t gw = blockIdx.x * kTeams + team, nw = gridDim.x * kTeams;  // teams, not warps
     const uint32_t my_tiles = gw < p.row_tiles ? (p.row_tiles - gw + nw - 1u) / nw : 0u;
-    const uint32_t items = my_tiles * p.supers;
+    const uint32_t items = my_tiles * (p.supers / KS);  // the launcher makes KS divide the super-block count
 
-    uint32_t in_tile = gw, in_sb = 0, in_item = 0;
+    uint32_t in_tile = gw, in_sb = member, in_item = 0;
     auto issue = [&]() {
         if (in_item < items) {
             const uint8_t *src = base + ((size_t)in_tile * p.supers + in_sb) * kSuperBytes;
-            uint8_t *dst = stage + (in_item & (kQ4Stages - 1)) * kSuperBytes;
+            uint8_t *dst = stage + (in_item % kQ4Stages) * kSuperBytes;
             for (uint32_t off = lane * 16u; off < kSuperBytes; off += 512u) cp_async16(dst + off, src + off);
             ++in_item;
-            if (++in_sb == p.supers) {
-                in_sb = 0;
+            if ((in_sb += KS) >= p.supers) {
+                in_sb = member;
                 in_tile += nw;
             }
         }
@@ -124,28 +145,20 @@ __global__ void __launch_bounds__(kQ4Threads) qmv_q4kt_kernel(const Q4ktParams p
 
     const __half *xsel = (g & 1u) ? xlo : xhi;  // B column n = g: even columns the head, odd the remainder
     float acc_s0 = 0.0f, acc_s1 = 0.0f, acc_m0 = 0.0f, acc_m1 = 0.0f;
-    uint32_t tile = gw, sb = 0;
+    uint32_t tile = gw, sb = member;
     for (uint32_t item = 0; item < items; ++item) {
         issue();
         cp_async_wait<kQ4Stages - 1>();
         __syncwarp();
-        const uint8_t *rec = stage + (item & (kQ4Stages - 1)) * kSuperBytes;
+        const uint8_t *rec = stage + (item % kQ4Stages) * kSuperBytes;
         // this lane scales sub-blocks t and t + 4 of rows g and g + 8
         const uint4 h0 = *reinterpret_cast<const uint4 *>(rec + 2048u + 16u * g);
         const uint4 h1 = *reinterpret_cast<const uint4 *>(rec + 2048u + 16u * (g + 8u));
         float dsc0[2], dm0[2], dsc1[2], dm1[2];
-#pragma unroll
-        for (uint32_t u = 0; u < 2; ++u) {
-            uint32_t sc, mn;
-            q4k_pair(h0, t + 4u * u, sc, mn);
-            dsc0[u] = f16_bits_f32(h0.x & 0xffffu) * (float)sc;
-            dm0[u] = f16_bits_f32(h0.x >> 16) * (float)mn;
-            q4k_pair(h1, t + 4u * u, sc, mn);
-            dsc1[u] = f16_bits_f32(h1.x & 0xffffu) * (float)sc;
-            dm1[u] = f16_bits_f32(h1.x >> 16) * (float)mn;
-        }
+        q4k_scales_pair(h0, t, dsc0, dm0);
+        q4k_scales_pair(h1, t, dsc1, dm1);
         const __half *xk = xsel + (size_t)sb * 256u + 8u * t;
-        const float *xs32 = xsum + sb * 8u;
+        float s0[2] = {0.0f, 0.0f}, s1[2] = {0.0f, 0.0f};  // sum(q x) of this lane's two sub-blocks, rows g and g + 8
 #pragma unroll
         for (uint32_t jb = 0; jb < 8; ++jb) {
             const uint2 w = *reinterpret_cast<const uint2 *>(rec + jb * 256u + lane * 8u);
@@ -156,25 +169,42 @@ __global__ void __launch_bounds__(kQ4Threads) qmv_q4kt_kernel(const Q4ktParams p
             mma_m16n8k16_f16(c, a, xv.x, xv.y);
             dequant_a4_word<false>(w.y, a);
             mma_m16n8k16_f16(c, a, xv.z, xv.w);
-            if ((jb & 3u) == t) {
-                const uint32_t u = jb >> 2;
-                const float xs = xs32[jb];
-                acc_s0 = fmaf(dsc0[u], c[0] + c[1], acc_s0);
-                acc_s1 = fmaf(dsc1[u], c[2] + c[3], acc_s1);
-                acc_m0 = fmaf(dm0[u], xs, acc_m0);
-                acc_m1 = fmaf(dm1[u], xs, acc_m1);
-            }
+            const bool mine = (jb & 3u) == t;
+            s0[jb >> 2] = mine ? c[0] + c[1] : s0[jb >> 2];
+            s1[jb >> 2] = mine ? c[2] + c[3] : s1[jb >> 2];
         }
+        const float xa = xsum[sb * 8u + t], xb = xsum[sb * 8u + t + 4u];
+        acc_s0 = fmaf(dsc0[0], s0[0], fmaf(dsc0[1], s0[1], acc_s0));
+        acc_s1 = fmaf(dsc1[0], s1[0], fmaf(dsc1[1], s1[1], acc_s1));
+        acc_m0 = fmaf(dm0[0], xa, fmaf(dm0[1], xb, acc_m0));
+        acc_m1 = fmaf(dm1[0], xa, fmaf(dm1[1], xb, acc_m1));
         __syncwarp();  // the stage may be refilled by the next iteration's copy
-        if (++sb == p.supers) {
-            sb = 0;
+        if ((sb += KS) >= p.supers) {
+            sb = member;
             float v0 = fmaf(acc_s0, xunscale, -acc_m0), v1 = fmaf(acc_s1, xunscale, -acc_m1);
             v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
             v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
             v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
             v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
             acc_s0 = acc_s1 = acc_m0 = acc_m1 = 0.0f;
-            if (t == 0) {
+            if (KS > 1) {
+                // the team's members finish a tile together (same item count): add their rows in member order
+                if (t == 0) {
+                    team_rows[warp][g] = v0;
+                    team_rows[warp][g + 8u] = v1;
+                }
+                named_bar_sync(1 + (int)team, KS * 32);
+                if (member == 0) {
+                    v0 = 0.0f, v1 = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < KS; ++r) {
+                        v0 += team_rows[team * KS + r][g];
+                        v1 += team_rows[team * KS + r][g + 8u];
+                    }
+                }
+                named_bar_sync(1 + (int)team, KS * 32);  // the rows may be overwritten by the next tile
+            }
+            if (t == 0 && member == 0) {
                 const uint32_t r0 = tile * 16u + g, r1 = r0 + 8u;
                 if (p.io_type == STARK_B200_F32) {
                     float *y = reinterpret_cast<float *>(p.y) + (size_t)b * p.rows;
@@ -278,18 +308,43 @@ stark_b200_status q4kt_launch(const QMatrix *m, const void *x, size_t x_stride, 
     p.x_stride = x_stride;
     p.y = y;
     p.io_type = io_type;
-    const size_t smem = (size_t)m->columns * 4u + (size_t)(m->columns / 32u) * 4u + 32u +
-                        (size_t)kQ4Warps * kQ4Stages * kSuperBytes;
-    static bool attr_set = false;
-    if (!attr_set) {
-        SB_CUDA(cudaFuncSetAttribute(qmv_q4kt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        attr_set = true;
+    // 12 warps x 3 copies in flight each; teams of 1, 2 or 4 warps per row tile so that a GPU's worth of warps
+    // (~24 per SM) has work even when the matrix has few row tiles.  STARK_B200_Q4K_TEAM overrides.
+    const uint32_t supers = m->columns / 256u;
+    // team size: the one that wastes the least of the last wave of warps (a team costs one barrier pair per tile)
+    uint32_t ks = 1;
+    double best = 0.0;
+    for (uint32_t cand = 1; cand <= 4u; cand *= 2u) {
+        if (supers % cand != 0) break;
+        const double slots = 148.0 * 2.0 * 12.0, units = (double)m->row_tiles * cand * batch;
+        const double waves = std::ceil(units / slots);
+        const double score = units / (waves * slots) * (cand == 1 ? 1.0 : (cand == 2 ? 0.98 : 0.96));
+        if (score > best) {
+            best = score;
+            ks = cand;
+        }
+    }
+    static const int forced = [] {
+        const char *e = getenv("STARK_B200_Q4K_TEAM");
+        return e ? atoi(e) : 0;
+    }();
+    if ((forced == 1 || forced == 2 || forced == 4) && supers % (uint32_t)forced == 0) ks = (uint32_t)forced;
+    constexpr uint32_t warps = 12, stages = 3;
+    const size_t smem = (size_t)m->columns * 4u + 128u + (size_t)(m->columns / 32u) * 4u + 4u * warps +
+                        (size_t)warps * stages * kSuperBytes;
+    auto kernel = ks == 4u ? qmv_q4kt_kernel<12, 3, 4> : (ks == 2u ? qmv_q4kt_kernel<12, 3, 2> : qmv_q4kt_kernel<12, 3, 1>);
+    static bool attr_set[3] = {false, false, false};
+    bool &done = attr_set[ks == 4u ? 2 : (ks == 2u ? 1 : 0)];
+    if (!done) {
+        SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+        done = true;
     }
     if (smem > 160u * 1024u) return STARK_B200_UNSUPPORTED;
     const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(3, (220u * 1024u) / smem));
-    const uint32_t blocks = std::max(1u, std::min((m->row_tiles + kQ4Warps - 1u) / kQ4Warps,
-                                                  (148u * per_sm + batch - 1u) / batch));
-    qmv_q4kt_kernel<<<dim3(blocks, batch), kQ4Threads, smem, stream>>>(p);
+    const uint32_t teams = warps / ks;
+    const uint32_t blocks =
+        std::max(1u, std::min((m->row_tiles + teams - 1u) / teams, (148u * per_sm + batch - 1u) / batch));
+    kernel<<<dim3(blocks, batch), warps * 32u, smem, stream>>>(p);
     SB_CUDA(cudaGetLastError());
     return STARK_B200_OK;
 }
