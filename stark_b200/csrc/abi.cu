@@ -151,18 +151,37 @@ stark_b200_status stark_b200_qmatrix_create_affine(const void *codes, const void
             return STARK_B200_UNSUPPORTED;
         m = new (std::nothrow) QMatrix();
         if (!m) return STARK_B200_OUT_OF_MEMORY;
-        m->format = kFmtAffine8;
+        static const bool b8_rows = [] {  // the tensor-core 8-bit layout is opt-in: STARK_B200_B8_TILED=1
+            const char *e = getenv("STARK_B200_B8_TILED");
+            return !(e && e[0] == '1');
+        }();
+        const bool tiled = !b8_rows && desc->columns % 256u == 0;  // tensor-core layout (qmv_b8.cu)
+        m->format = tiled ? kFmtAffine8T : kFmtAffine8;
         m->rows = desc->rows;
         m->columns = desc->columns;
+        m->row_tiles = tiled ? (desc->rows + 15u) / 16u : 0;
         m->groups = desc->columns / 64u;
         m->experts = 1;
-        m->bytes = code_bytes + 2u * plane_bytes;
+        m->bytes = tiled ? b8t_bytes(1, desc->rows, desc->columns) : code_bytes + 2u * plane_bytes;
         cudaGetDevice(&m->device);
         const cudaMemcpyKind kind = desc->location == STARK_B200_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
         cudaError_t e = cudaMalloc(&m->data, m->bytes);
-        if (e == cudaSuccess) e = cudaMemcpy(m->data, codes, code_bytes, kind);
-        if (e == cudaSuccess) e = cudaMemcpy(m->data + code_bytes, scales, plane_bytes, kind);
-        if (e == cudaSuccess) e = cudaMemcpy(m->data + code_bytes + plane_bytes, biases, plane_bytes, kind);
+        uint8_t *staging = nullptr;
+        uint8_t *dst = m->data;
+        if (e == cudaSuccess && tiled) {
+            e = cudaMalloc(&staging, code_bytes + 2u * plane_bytes);
+            dst = staging;
+        }
+        if (e == cudaSuccess) e = cudaMemcpy(dst, codes, code_bytes, kind);
+        if (e == cudaSuccess) e = cudaMemcpy(dst + code_bytes, scales, plane_bytes, kind);
+        if (e == cudaSuccess) e = cudaMemcpy(dst + code_bytes + plane_bytes, biases, plane_bytes, kind);
+        if (e == cudaSuccess && tiled) {
+            if (b8t_retile(staging, reinterpret_cast<const uint16_t *>(staging + code_bytes),
+                           reinterpret_cast<const uint16_t *>(staging + code_bytes + plane_bytes), m, nullptr) != STARK_B200_OK)
+                e = cudaErrorUnknown;
+            if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        }
+        cudaFree(staging);
         if (e != cudaSuccess) {
             qmatrix_free(m);
             return cuda_status(e);

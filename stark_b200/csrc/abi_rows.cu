@@ -51,8 +51,13 @@ stark_b200_status make_gguf(const void *blocks, uint32_t kind, uint32_t experts,
         const char *e = getenv("STARK_B200_Q4K_ROWS");
         return e && e[0] == '1';
     }();
-    const bool tiled = kind == STARK_B200_GGUF_Q4_K && !q4k_rows;
-    m->format = kind == STARK_B200_GGUF_Q8_0 ? kFmtQ8_0 : (tiled ? kFmtQ4_K : kFmtQ4_KRaw);
+    static const bool b8_rows = [] {  // the tensor-core 8-bit layout is opt-in: STARK_B200_B8_TILED=1
+        const char *e = getenv("STARK_B200_B8_TILED");
+        return !(e && e[0] == '1');
+    }();
+    // the tensor-core layouts cut rows into 256-column super-records; other widths keep the source layout
+    const bool tiled = kind == STARK_B200_GGUF_Q4_K ? !q4k_rows : (!b8_rows && columns % 256u == 0);
+    m->format = kind == STARK_B200_GGUF_Q8_0 ? (tiled ? kFmtQ8_0T : kFmtQ8_0) : (tiled ? kFmtQ4_K : kFmtQ4_KRaw);
     m->rows = rows;
     m->columns = columns;
     m->row_tiles = tiled ? (rows + 15u) / 16u : 0;
@@ -61,17 +66,22 @@ stark_b200_status make_gguf(const void *blocks, uint32_t kind, uint32_t experts,
     m->record_bytes = 0;
     m->experts = experts;
     const size_t source_bytes = gguf_row_bytes(kind, columns) * rows * experts;
-    m->bytes = tiled ? q4kt_bytes(experts, rows, columns) : source_bytes;
+    m->bytes = !tiled ? source_bytes
+                      : (kind == STARK_B200_GGUF_Q4_K ? q4kt_bytes(experts, rows, columns) : b8t_bytes(experts, rows, columns));
     cudaGetDevice(&m->device);
     const cudaMemcpyKind dir = location == STARK_B200_DEVICE ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice;
     cudaError_t e = cudaMalloc(&m->data, m->bytes);
     if (e == cudaSuccess && !tiled) e = cudaMemcpy(m->data, blocks, m->bytes, dir);
     if (e == cudaSuccess && tiled) {
-        // Q4_K is re-tiled into tensor-core fragment order: stage the source bytes, re-tile, drop the copy
+        // re-tiled into tensor-core fragment order: stage the source bytes, re-tile, drop the copy
         uint8_t *staging = nullptr;
         e = cudaMalloc(&staging, source_bytes);
         if (e == cudaSuccess) e = cudaMemcpy(staging, blocks, source_bytes, dir);
-        if (e == cudaSuccess && q4kt_retile(staging, m, nullptr) != STARK_B200_OK) e = cudaErrorUnknown;
+        if (e == cudaSuccess) {
+            const stark_b200_status rs = kind == STARK_B200_GGUF_Q4_K ? q4kt_retile(staging, m, nullptr)
+                                                                      : b8t_retile(staging, nullptr, nullptr, m, nullptr);
+            if (rs != STARK_B200_OK) e = cudaErrorUnknown;
+        }
         if (e == cudaSuccess) e = cudaDeviceSynchronize();
         cudaFree(staging);
     }

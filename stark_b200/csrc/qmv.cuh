@@ -11,6 +11,8 @@ enum QFormat : uint32_t {
     kFmtQ8_0 = 2,     // GGUF Q8_0: 16 rows x 64 columns per record, f16 block scales
     kFmtQ4_K = 3,     // GGUF Q4_K re-tiled: 16 rows x 256 columns per 2304-byte super-record (qmv_q4k.cu)
     kFmtQ4_KRaw = 4,  // GGUF Q4_K in the source byte layout (row-wise kernel; STARK_B200_Q4K_ROWS=1)
+    kFmtQ8_0T = 5,    // GGUF Q8_0 re-tiled: 16 rows x 256 columns per 4352-byte super-record (qmv_b8.cu)
+    kFmtAffine8T = 6, // MLX affine 8-bit re-tiled the same way
 };
 
 // One record covers 16 rows x 64 columns (one quantization group per row).
@@ -120,6 +122,15 @@ stark_b200_status q4kt_launch(const QMatrix *m, const void *x, size_t x_stride, 
                               const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream);
 stark_b200_status q4kt_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,
                                   uint8_t *codes_device, cudaStream_t stream);
+
+// Tensor-core 8-bit formats (qmv_b8.cu): Q8_0 and MLX affine 8-bit, re-tiled from device copies of the source.
+size_t b8t_bytes(uint32_t experts, uint32_t rows, uint32_t columns);
+stark_b200_status b8t_retile(const uint8_t *codes, const uint16_t *scales, const uint16_t *biases, QMatrix *m,
+                             cudaStream_t stream);
+stark_b200_status b8t_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
+                             const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream);
+stark_b200_status b8t_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,
+                                 uint8_t *codes_device, cudaStream_t stream);
 
 // Row-wise kernels for the formats kept in the reference's byte layout (qmv_rows.cu).
 bool qmv_rows_supports(const QMatrix *m);

@@ -436,13 +436,15 @@ stark_b200_status launch_rows(const QMatrix *m, const RowParams &p, uint32_t bat
 
 bool qmv_rows_supports(const QMatrix *m) {
     return m && (m->format == kFmtQ4_K || m->format == kFmtQ4_KRaw || m->format == kFmtQ8_0 ||
-                 m->format == kFmtAffine8);
+                 m->format == kFmtAffine8 || m->format == kFmtQ8_0T || m->format == kFmtAffine8T);
 }
 
 stark_b200_status qmv_rows_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
                                   const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream) {
     if (!qmv_rows_supports(m) || !x || !y || batch == 0) return STARK_B200_INVALID_ARGUMENT;
     if (m->format == kFmtQ4_K) return q4kt_launch(m, x, x_stride, y, batch, expert_ids, io_type, stream);
+    if (m->format == kFmtQ8_0T || m->format == kFmtAffine8T)
+        return b8t_launch(m, x, x_stride, y, batch, expert_ids, io_type, stream);
     if (m->columns > 12288u) return STARK_B200_UNSUPPORTED;
     RowParams p = row_params(m);
     p.x = x;
@@ -459,6 +461,8 @@ stark_b200_status qmv_rows_dequantize(const QMatrix *m, uint32_t expert, uint32_
                                       uint8_t *codes_device, cudaStream_t stream) {
     if (!qmv_rows_supports(m) || row >= m->rows || expert >= (m->experts ? m->experts : 1u)) return STARK_B200_INVALID_ARGUMENT;
     if (m->format == kFmtQ4_K) return q4kt_dequantize(m, expert, row, out_device, codes_device, stream);
+    if (m->format == kFmtQ8_0T || m->format == kFmtAffine8T)
+        return b8t_dequantize(m, expert, row, out_device, codes_device, stream);
     RowParams p = row_params(m);
     p.data += (size_t)expert * p.expert_bytes;
     if (p.scales) {
