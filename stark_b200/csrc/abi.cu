@@ -151,9 +151,9 @@ stark_b200_status stark_b200_qmatrix_create_affine(const void *codes, const void
             return STARK_B200_UNSUPPORTED;
         m = new (std::nothrow) QMatrix();
         if (!m) return STARK_B200_OUT_OF_MEMORY;
-        static const bool b8_rows = [] {  // the tensor-core 8-bit layout is opt-in: STARK_B200_B8_TILED=1
-            const char *e = getenv("STARK_B200_B8_TILED");
-            return !(e && e[0] == '1');
+        static const bool b8_rows = [] {  // STARK_B200_B8_ROWS=1 keeps the source layout and the row-wise kernel
+            const char *e = getenv("STARK_B200_B8_ROWS");
+            return e && e[0] == '1';
         }();
         const bool tiled = !b8_rows && desc->columns % 256u == 0;  // tensor-core layout (qmv_b8.cu)
         m->format = tiled ? kFmtAffine8T : kFmtAffine8;

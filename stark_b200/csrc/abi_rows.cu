@@ -51,9 +51,9 @@ stark_b200_status make_gguf(const void *blocks, uint32_t kind, uint32_t experts,
         const char *e = getenv("STARK_B200_Q4K_ROWS");
         return e && e[0] == '1';
     }();
-    static const bool b8_rows = [] {  // the tensor-core 8-bit layout is opt-in: STARK_B200_B8_TILED=1
-        const char *e = getenv("STARK_B200_B8_TILED");
-        return !(e && e[0] == '1');
+    static const bool b8_rows = [] {  // STARK_B200_B8_ROWS=1 keeps the source layout and the row-wise kernel
+        const char *e = getenv("STARK_B200_B8_ROWS");
+        return e && e[0] == '1';
     }();
     // the tensor-core layouts cut rows into 256-column super-records; other widths keep the source layout
     const bool tiled = kind == STARK_B200_GGUF_Q4_K ? !q4k_rows : (!b8_rows && columns % 256u == 0);
