@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/stark_b200.h"
 
 namespace sb {
@@ -171,5 +173,22 @@ inline stark_b200_status cuda_status(cudaError_t e) {
         cudaError_t _e = (expr);                              \
         if (_e != cudaSuccess) return ::sb::cuda_status(_e);  \
     } while (0)
+
+
+// cudaFuncSetAttribute applies to the current device only: a kernel that needs more than 48 KB of dynamic
+// shared memory is opted in once per device (one process may drive several GPUs from several threads).
+struct SmemOptIn {
+    std::atomic<uint64_t> devices{0};
+};
+template <typename Kernel>
+inline stark_b200_status ensure_dynamic_smem(Kernel kernel, int bytes, SmemOptIn &once) {
+    int dev = 0;
+    SB_CUDA(cudaGetDevice(&dev));
+    const uint64_t bit = 1ull << (dev & 63);
+    if (once.devices.load(std::memory_order_acquire) & bit) return STARK_B200_OK;
+    SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    once.devices.fetch_or(bit, std::memory_order_release);
+    return STARK_B200_OK;
+}
 
 }  // namespace sb

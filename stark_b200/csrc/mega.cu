@@ -573,11 +573,8 @@ uint32_t mega_smem_bytes(uint32_t num_stages, uint32_t stage_capacity, uint32_t 
 }
 
 stark_b200_status mega_launch(const MegaParams &p, uint32_t grid, uint32_t smem_bytes, cudaStream_t stream) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        SB_CUDA(cudaFuncSetAttribute(decode_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-        attr_set = true;
-    }
+    static SmemOptIn once;
+    if (stark_b200_status s = ensure_dynamic_smem(decode_token_kernel, 227 * 1024, once)) return s;
     if (p.max_columns > (uint32_t)kMaxRounds * kCT * 8u) return STARK_B200_UNSUPPORTED;
     decode_token_kernel<<<grid, kMegaThreads, smem_bytes, stream>>>(p);
     SB_CUDA(cudaGetLastError());

@@ -427,12 +427,8 @@ stark_b200_status attention_decode_launch(const AttnArgs &a, cudaStream_t stream
     p.scratch = a.scratch;
     p.counters = a.counters;
     p.trace = a.trace;
-    static bool attr_set = false;
-    if (!attr_set) {
-        SB_CUDA(cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     (int)kAttnSharedBytes));
-        attr_set = true;
-    }
+    static SmemOptIn once;
+    if (stark_b200_status s = ensure_dynamic_smem(attention_decode_kernel, (int)kAttnSharedBytes, once)) return s;
     return launch_pdl_smem(attention_decode_kernel, dim3(a.splits, a.kv_heads), dim3(kAttnThreads), kAttnSharedBytes,
                            a.pdl, stream, p);
 }

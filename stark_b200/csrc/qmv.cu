@@ -813,12 +813,9 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     const bool tpx = p.ex.ranks != 0;
     if (tpx && split) return STARK_B200_UNSUPPORTED;
     KernelFn kernel = tpx ? tpx_table[pred ? 1 : 0][ri] : table[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
-    static bool attr_set[2][2][2][3] = {}, tpx_attr_set[2][3] = {};
-    bool &done = tpx ? tpx_attr_set[pred ? 1 : 0][ri] : attr_set[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
-    if (!done) {
-        SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        done = true;
-    }
+    static SmemOptIn once[2][2][2][3], tpx_once[2][3];
+    SmemOptIn &opted = tpx ? tpx_once[pred ? 1 : 0][ri] : once[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
+    if (stark_b200_status s = ensure_dynamic_smem(kernel, 220 * 1024, opted)) return s;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kThreads);

@@ -320,12 +320,8 @@ stark_b200_status launch_b8(const QMatrix *m, const B8Params &p, uint32_t batch,
                         (size_t)warps * stages * kB8SuperBytes;
     auto kernel = ks == 4u ? qmv_b8t_kernel<AFFINE, 12, 3, 4>
                            : (ks == 2u ? qmv_b8t_kernel<AFFINE, 12, 3, 2> : qmv_b8t_kernel<AFFINE, 12, 3, 1>);
-    static bool attr_set[3] = {false, false, false};
-    bool &done = attr_set[ks == 4u ? 2 : (ks == 2u ? 1 : 0)];
-    if (!done) {
-        SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
-        done = true;
-    }
+    static SmemOptIn once[3];
+    if (stark_b200_status s = ensure_dynamic_smem(kernel, 220 * 1024, once[ks == 4u ? 2 : (ks == 2u ? 1 : 0)])) return s;
     if (smem > 220u * 1024u) return STARK_B200_UNSUPPORTED;
     const uint32_t teams = warps / ks;
     const uint32_t blocks = std::max(1u, std::min((m->row_tiles + teams - 1u) / teams, (148u + batch - 1u) / batch));

@@ -333,12 +333,8 @@ stark_b200_status q4kt_launch(const QMatrix *m, const void *x, size_t x_stride, 
     const size_t smem = (size_t)m->columns * 4u + 128u + (size_t)(m->columns / 32u) * 4u + 4u * warps +
                         (size_t)warps * stages * kSuperBytes;
     auto kernel = ks == 4u ? qmv_q4kt_kernel<12, 3, 4> : (ks == 2u ? qmv_q4kt_kernel<12, 3, 2> : qmv_q4kt_kernel<12, 3, 1>);
-    static bool attr_set[3] = {false, false, false};
-    bool &done = attr_set[ks == 4u ? 2 : (ks == 2u ? 1 : 0)];
-    if (!done) {
-        SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-        done = true;
-    }
+    static SmemOptIn once[3];
+    if (stark_b200_status s = ensure_dynamic_smem(kernel, 160 * 1024, once[ks == 4u ? 2 : (ks == 2u ? 1 : 0)])) return s;
     if (smem > 160u * 1024u) return STARK_B200_UNSUPPORTED;
     const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(3, (220u * 1024u) / smem));
     const uint32_t teams = warps / ks;

@@ -406,12 +406,8 @@ stark_b200_status launch_rows(const QMatrix *m, const RowParams &p, uint32_t bat
         const uint32_t stages = nb == 4u ? 2u : 4u;
         const size_t smem = rows_smem_bytes<FORMAT>(m->columns, nb, stages);
         auto kernel = nb == 4u ? qmv_rows_kernel<FORMAT, 4, 2> : (nb == 2u ? qmv_rows_kernel<FORMAT, 2, 4> : qmv_rows_kernel<FORMAT, 1, 4>);
-        static bool attr_set[3] = {false, false, false};
-        bool &done = attr_set[nb == 4u ? 2 : (nb == 2u ? 1 : 0)];
-        if (!done) {
-            SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-            done = true;
-        }
+        static SmemOptIn once[3];
+        if (stark_b200_status s = ensure_dynamic_smem(kernel, 160 * 1024, once[nb == 4u ? 2 : (nb == 2u ? 1 : 0)])) return s;
         if (smem > 160u * 1024u) return STARK_B200_UNSUPPORTED;
         const uint32_t per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (220u * 1024u) / smem));
         const uint32_t row_blocks =
@@ -419,11 +415,8 @@ stark_b200_status launch_rows(const QMatrix *m, const RowParams &p, uint32_t bat
         kernel<<<dim3(row_blocks, batch), kRowThreads, smem, s>>>(p);
     } else {
         const size_t smem = (size_t)m->columns * 4u;
-        static bool attr_set = false;
-        if (!attr_set) {
-            SB_CUDA(cudaFuncSetAttribute(qmv_rows_generic_kernel<FORMAT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-            attr_set = true;
-        }
+        static SmemOptIn once;
+        if (stark_b200_status s = ensure_dynamic_smem(qmv_rows_generic_kernel<FORMAT>, 64 * 1024, once)) return s;
         const uint32_t row_blocks =
             std::max(1u, std::min((m->rows + kRowWarps - 1u) / kRowWarps, 148u * 4u / std::max(1u, batch) + 1u));
         qmv_rows_generic_kernel<FORMAT><<<dim3(row_blocks, batch), kRowThreads, smem, s>>>(p);
