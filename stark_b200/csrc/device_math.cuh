@@ -85,10 +85,8 @@ __device__ inline uint32_t movmatrix_trans(uint32_t a) {
 }
 // f32 pair -> packed bf16 (hi) and the packed bf16 of the remainders (lo): hi + lo carries ~16 bits.
 __device__ inline void split_bf16x2(float x, float y, uint32_t &hi, uint32_t &lo) {
-    const uint16_t xh = f32_to_bf16_bits(x), yh = f32_to_bf16_bits(y);
-    hi = (uint32_t)xh | ((uint32_t)yh << 16);
-    const uint16_t xl = f32_to_bf16_bits(x - bf16_bits_to_f32(xh)), yl = f32_to_bf16_bits(y - bf16_bits_to_f32(yh));
-    lo = (uint32_t)xl | ((uint32_t)yl << 16);
+    hi = f32x2_to_bf16x2(x, y);
+    lo = f32x2_to_bf16x2(x - __uint_as_float(hi << 16), y - __uint_as_float(hi & 0xffff0000u));
 }
 
 // Per-head RMS norm + RoPE of one 128-wide head by ONE warp; lane l holds dims {2l, 2l+1, 64+2l, 65+2l},
@@ -119,26 +117,33 @@ __device__ inline void warp_head_norm_rope(const uint16_t *head, const HeadConst
     const uint32_t hi2 = __ldcg(reinterpret_cast<const uint32_t *>(head + 64u + 2u * lane));
     float v[4] = {__uint_as_float(lo2 << 16), __uint_as_float(lo2 & 0xffff0000u), __uint_as_float(hi2 << 16),
                   __uint_as_float(hi2 & 0xffff0000u)};
+    // The roundings go through the packed hardware conversion (round to nearest even, like the reference's
+    // bf16 type; only the payload of a NaN differs): this code sits on the critical path of every layer.
     if (has_norm) {
         const float total = warp_sum(v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3]);
         const float rms = 1.0f / sqrtf(total / (float)kHeadDim + eps);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = bf16_round(bf16_round(v[i] * rms) * c.nw[i]);
-    }
-    if (has_rope) {
-        float r[4];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            // first half: x*cos - pair*sin ; second half: x*cos + pair*sin
-            r[i] = bf16_round(__fadd_rn(__fmul_rn(v[i], c.cs[i]), __fmul_rn(-v[i + 2], c.sn[i])));
-            r[i + 2] = bf16_round(__fadd_rn(__fmul_rn(v[i + 2], c.cs[i + 2]), __fmul_rn(v[i], c.sn[i + 2])));
+        for (int i = 0; i < 4; i += 2) {
+            const uint32_t n2 = f32x2_to_bf16x2(v[i] * rms, v[i + 1] * rms);
+            const uint32_t p2 = f32x2_to_bf16x2(__uint_as_float(n2 << 16) * c.nw[i],
+                                                __uint_as_float(n2 & 0xffff0000u) * c.nw[i + 1]);
+            v[i] = __uint_as_float(p2 << 16);
+            v[i + 1] = __uint_as_float(p2 & 0xffff0000u);
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = r[i];
     }
-    *reinterpret_cast<uint32_t *>(out + 2u * lane) = (uint32_t)f32_to_bf16_bits(v[0]) | ((uint32_t)f32_to_bf16_bits(v[1]) << 16);
-    *reinterpret_cast<uint32_t *>(out + 64u + 2u * lane) =
-        (uint32_t)f32_to_bf16_bits(v[2]) | ((uint32_t)f32_to_bf16_bits(v[3]) << 16);
+    uint32_t lo_pair, hi_pair;
+    if (has_rope) {
+        // first half: x*cos - pair*sin ; second half: x*cos + pair*sin (products rounded separately)
+        lo_pair = f32x2_to_bf16x2(__fadd_rn(__fmul_rn(v[0], c.cs[0]), __fmul_rn(-v[2], c.sn[0])),
+                                  __fadd_rn(__fmul_rn(v[1], c.cs[1]), __fmul_rn(-v[3], c.sn[1])));
+        hi_pair = f32x2_to_bf16x2(__fadd_rn(__fmul_rn(v[2], c.cs[2]), __fmul_rn(v[0], c.sn[2])),
+                                  __fadd_rn(__fmul_rn(v[3], c.cs[3]), __fmul_rn(v[1], c.sn[3])));
+    } else {
+        lo_pair = f32x2_to_bf16x2(v[0], v[1]);
+        hi_pair = f32x2_to_bf16x2(v[2], v[3]);
+    }
+    *reinterpret_cast<uint32_t *>(out + 2u * lane) = lo_pair;
+    *reinterpret_cast<uint32_t *>(out + 64u + 2u * lane) = hi_pair;
 }
 __device__ inline void warp_head_norm_rope(const uint16_t *head, const float *norm_w, const float *cosr,
                                            const float *sinr, float eps, uint32_t lane, uint16_t *out) {
