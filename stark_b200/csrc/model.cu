@@ -179,7 +179,7 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     if ((st = dmalloc(&m->partial_index, 1024)) != STARK_B200_OK) return fail(st);
     if (const char *e = getenv("STARK_B200_TRACE")) {
         if (e[0] == '1') {  // one slot per launch
-            m->trace_slots = 1u + 5u * c.layers + 2u;
+            m->trace_slots = 1u + 7u * c.layers + 3u;  // up to 7 launches per layer with tensor-parallel reductions
             if ((st = dmalloc(&m->trace, m->trace_slots)) != STARK_B200_OK) return fail(st);
         }
     }
@@ -268,10 +268,24 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
     uint32_t *tokens = m->tp_seq;
     uint16_t *hcur = m->h, *hnext = m->h_alt;
     QmvExchange hooks{};
+    // Two ways to close an exchange.  Default: the consuming matvec sums the packets in its prologue -- no
+    // extra launch, but every one of its CTAs reads every packet.  STARK_B200_TP_REDUCE=1: a small kernel
+    // sums them once, in place, polling the peers while this rank's projection still runs.
+    static const bool fused = [] {
+        const char *e = getenv("STARK_B200_TP_REDUCE");
+        return !(e && e[0] == '1');
+    }();
+    stark_b200_status consume_status = STARK_B200_OK;
     auto consume = [&](QmvArgs &a, uint32_t index) {
-        hooks = tp_consumer_hooks(m->tp, index, per_token, tokens, hnext);
-        a.exchange = &hooks;
-        std::swap(hcur, hnext);  // after this matvec the residual stream lives in the other buffer
+        if (fused) {
+            hooks = tp_consumer_hooks(m->tp, index, per_token, tokens, hnext);
+            a.exchange = &hooks;
+            std::swap(hcur, hnext);  // after this matvec the residual stream lives in the other buffer
+        } else {
+            TraceSlot *own = a.trace;  // the reduction takes the slot, the matvec the next one
+            consume_status = tp_reduce_residual_launch(m->tp, index, per_token, tokens, hcur, ctx->error_word, own, pdl, s);
+            a.trace = slot(n++);
+        }
     };
     auto produce = [&](QmvArgs &a, uint32_t index) {
         hooks = tp_producer_hooks(m->tp, index, per_token, tokens);
@@ -296,6 +310,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.epilogue = kEpiStore;
         a.trace = slot(n++);
         if (tp && l > 0) consume(a, 2u * l - 1u);
+        if (consume_status != STARK_B200_OK) return consume_status;
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
         a.exchange = nullptr;
         // attention with fused QK-norm, RoPE and KV append
@@ -340,6 +355,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.epilogue = kEpiSwiGlu;
         a.trace = slot(n++);
         if (tp) consume(a, 2u * l);
+        if (consume_status != STARK_B200_OK) return consume_status;
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
         a.exchange = nullptr;
         // h = bf16(bf16(W_down act) + h)
@@ -372,6 +388,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.out_grid = &grid;
         a.trace = slot(n++);
         if (tp) consume(a, per_token - 1u);
+        if (consume_status != STARK_B200_OK) return consume_status;
         if ((st = qmv_launch(a, s)) != STARK_B200_OK) return st;
         st = tp ? tp_argmax_finalize_launch(m->tp, tokens, m->partial_max, m->partial_index, grid,
                                             m->tp_vocab_offset, m->state, m->generated, ctx->error_word, pdl, s)

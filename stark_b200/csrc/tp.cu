@@ -85,6 +85,72 @@ __global__ void __launch_bounds__(256) tp_ingest_advance_kernel(TpRegion g, uint
     }
 }
 
+// Sums the ranks' packets of one exchange ONCE and folds the result into the residual stream:
+//   h[i] = bf16(bf16(sum over ranks in rank order) + h[i]).
+// A handful of small CTAs: they fit beside the matvec that is still producing this rank's share, so the
+// peers' packets are polled while it runs; only this rank's own packets and h wait for it.
+constexpr int kReduceCtas = 8, kReduceThreads = 256;
+__global__ void __launch_bounds__(kReduceThreads) tp_reduce_residual_kernel(TpRegion g, uint32_t buf, uint32_t ticket_mul,
+                                                                            uint32_t ticket_add, const uint32_t *tokens,
+                                                                            uint16_t *h, uint32_t *error_word,
+                                                                            TraceSlot *trace) {
+    pdl_launch_dependents();
+    if (threadIdx.x == 0 && trace) trace_min(&trace->start);
+    const uint32_t ticket = __ldcg(tokens) * ticket_mul + ticket_add;  // advanced only at the end of a token
+    const unsigned long long t0 = global_ns();
+    bool waited = false;
+    for (uint32_t i = (blockIdx.x * kReduceThreads + threadIdx.x) * 2u; i < g.hidden;
+         i += kReduceCtas * kReduceThreads * 2u) {
+        float v[kMaxTpRanks][2];
+        bool ok = true;
+        for (uint32_t step = 0; step < 2; ++step) {  // 0: the peers, before the wait; 1: this rank, after it
+            if (step == 1 && !waited) {
+                pdl_wait();
+                waited = true;
+                if (threadIdx.x == 0 && trace) trace_min(&trace->ready);
+            }
+#pragma unroll
+            for (uint32_t r = 0; r < kMaxTpRanks; ++r) {  // unrolled: the per-rank values stay in registers
+                if (r >= g.size || (r == g.rank) != (step == 1)) continue;
+                const unsigned long long *src = tp_recv(g.base[g.rank], buf, r, g.hidden) + i;
+                unsigned long long q0, q1;
+                uint32_t spins = 0;
+                for (;;) {
+                    asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(q0), "=l"(q1) : "l"(src) : "memory");
+                    if ((uint32_t)(q0 >> 32) == ticket && (uint32_t)(q1 >> 32) == ticket) break;
+                    if (++spins > 8u) {
+                        __nanosleep(64);
+                        if (global_ns() - t0 > kPeerWaitNs) {
+                            atomicOr(error_word, kErrPeerTimeout);
+                            ok = false;
+                            break;
+                        }
+                    }
+                }
+                v[r][0] = __uint_as_float((uint32_t)q0);
+                v[r][1] = __uint_as_float((uint32_t)q1);
+            }
+        }
+        if (ok) {
+            float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+            for (uint32_t r = 0; r < kMaxTpRanks; ++r) {  // rank order: every rank computes the same bits
+                if (r < g.size) {
+                    a0 += v[r][0];
+                    a1 += v[r][1];
+                }
+            }
+            const uint32_t old = *reinterpret_cast<const uint32_t *>(h + i);
+            const uint32_t s2 = f32x2_to_bf16x2(a0, a1);  // the projection's bf16 output
+            *reinterpret_cast<uint32_t *>(h + i) =
+                f32x2_to_bf16x2(__uint_as_float(s2 << 16) + __uint_as_float(old << 16),
+                                __uint_as_float(s2 & 0xffff0000u) + __uint_as_float(old & 0xffff0000u));
+        }
+    }
+    if (!waited) pdl_wait();  // a thread without elements still takes part in the kernel ordering
+    if (threadIdx.x == 0 && trace) trace_max(&trace->end);
+}
+
 __global__ void __launch_bounds__(256) tp_argmax_finalize_kernel(TpRegion g, uint32_t *tokens, const float *partial_max,
                                                                  const uint32_t *partial_index, uint32_t count,
                                                                  uint32_t vocab_offset, StepState *state,
@@ -195,6 +261,24 @@ QmvExchange tp_consumer_hooks(const TpRegion &g, uint32_t index, uint32_t per_to
     x.ticket_mul = per_token;
     x.ticket_add = index + 1u;
     return x;
+}
+
+stark_b200_status tp_reduce_residual_launch(const TpRegion &g, uint32_t index, uint32_t per_token,
+                                            const uint32_t *tokens, uint16_t *h, uint32_t *error_word, TraceSlot *trace,
+                                            bool pdl, cudaStream_t stream) {
+    if (g.size < 2 || g.size > kMaxTpRanks || g.rank >= g.size || g.hidden % 2u != 0) return STARK_B200_INVALID_ARGUMENT;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(kReduceCtas);
+    cfg.blockDim = dim3(kReduceThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    SB_CUDA(cudaLaunchKernelEx(&cfg, tp_reduce_residual_kernel, g, index & 1u, per_token, index + 1u, tokens, h,
+                               error_word, trace));
+    return STARK_B200_OK;
 }
 
 stark_b200_status tp_ingest_advance_launch(const TpRegion &g, uint32_t last_index, uint32_t per_token,

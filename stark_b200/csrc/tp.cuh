@@ -44,6 +44,12 @@ QmvExchange tp_producer_hooks(const TpRegion &g, uint32_t index, uint32_t per_to
 QmvExchange tp_consumer_hooks(const TpRegion &g, uint32_t index, uint32_t per_token, const uint32_t *tokens,
                               uint16_t *h_out);
 
+// The exchange as a kernel of its own between the producing and the consuming matvec (the alternative to
+// the consumer hooks): h[i] = bf16(bf16(sum over ranks) + h[i]), in place, packets summed once.
+stark_b200_status tp_reduce_residual_launch(const TpRegion &g, uint32_t index, uint32_t per_token,
+                                            const uint32_t *tokens, uint16_t *h, uint32_t *error_word, TraceSlot *trace,
+                                            bool pdl, cudaStream_t stream);
+
 // End of a cache-only prompt row: waits until every rank's packets of the row's last exchange are in
 // (nobody may start the next row's pushes into a buffer a slower rank still reads), then position += 1,
 // token = pending[cursor++], tokens += 1.
