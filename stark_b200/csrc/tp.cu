@@ -87,8 +87,9 @@ __global__ void __launch_bounds__(256) tp_ingest_advance_kernel(TpRegion g, uint
 
 // Sums the ranks' packets of one exchange ONCE and folds the result into the residual stream:
 //   h[i] = bf16(bf16(sum over ranks in rank order) + h[i]).
-// A handful of small CTAs: they fit beside the matvec that is still producing this rank's share, so the
-// peers' packets are polled while it runs; only this rank's own packets and h wait for it.
+// A handful of small CTAs.  Everything happens after the wait on the previous kernel: the ticket depends
+// on the token counter, whose writer (the end of the previous token) may still be running while the first
+// kernels of this token are already resident, and a poll for a stale ticket would never be answered.
 constexpr int kReduceCtas = 8, kReduceThreads = 256;
 __global__ void __launch_bounds__(kReduceThreads) tp_reduce_residual_kernel(TpRegion g, uint32_t buf, uint32_t ticket_mul,
                                                                             uint32_t ticket_add, const uint32_t *tokens,
@@ -96,50 +97,34 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_residual_kernel(TpRe
                                                                             TraceSlot *trace) {
     pdl_launch_dependents();
     if (threadIdx.x == 0 && trace) trace_min(&trace->start);
-    const uint32_t ticket = __ldcg(tokens) * ticket_mul + ticket_add;  // advanced only at the end of a token
+    pdl_wait();
+    if (threadIdx.x == 0 && trace) trace_min(&trace->ready);
+    const uint32_t ticket = __ldcg(tokens) * ticket_mul + ticket_add;
     const unsigned long long t0 = global_ns();
-    bool waited = false;
     for (uint32_t i = (blockIdx.x * kReduceThreads + threadIdx.x) * 2u; i < g.hidden;
          i += kReduceCtas * kReduceThreads * 2u) {
-        float v[kMaxTpRanks][2];
+        float a0 = 0.0f, a1 = 0.0f;
         bool ok = true;
-        for (uint32_t step = 0; step < 2; ++step) {  // 0: the peers, before the wait; 1: this rank, after it
-            if (step == 1 && !waited) {
-                pdl_wait();
-                waited = true;
-                if (threadIdx.x == 0 && trace) trace_min(&trace->ready);
-            }
-#pragma unroll
-            for (uint32_t r = 0; r < kMaxTpRanks; ++r) {  // unrolled: the per-rank values stay in registers
-                if (r >= g.size || (r == g.rank) != (step == 1)) continue;
-                const unsigned long long *src = tp_recv(g.base[g.rank], buf, r, g.hidden) + i;
-                unsigned long long q0, q1;
-                uint32_t spins = 0;
-                for (;;) {
-                    asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(q0), "=l"(q1) : "l"(src) : "memory");
-                    if ((uint32_t)(q0 >> 32) == ticket && (uint32_t)(q1 >> 32) == ticket) break;
-                    if (++spins > 8u) {
-                        __nanosleep(64);
-                        if (global_ns() - t0 > kPeerWaitNs) {
-                            atomicOr(error_word, kErrPeerTimeout);
-                            ok = false;
-                            break;
-                        }
+        for (uint32_t r = 0; r < g.size && ok; ++r) {  // rank order: every rank computes the same bits
+            const unsigned long long *src = tp_recv(g.base[g.rank], buf, r, g.hidden) + i;
+            unsigned long long q0, q1;
+            uint32_t spins = 0;
+            for (;;) {
+                asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(q0), "=l"(q1) : "l"(src) : "memory");
+                if ((uint32_t)(q0 >> 32) == ticket && (uint32_t)(q1 >> 32) == ticket) break;
+                if (++spins > 8u) {
+                    __nanosleep(64);
+                    if (global_ns() - t0 > kPeerWaitNs) {
+                        atomicOr(error_word, kErrPeerTimeout);
+                        ok = false;
+                        break;
                     }
                 }
-                v[r][0] = __uint_as_float((uint32_t)q0);
-                v[r][1] = __uint_as_float((uint32_t)q1);
             }
+            a0 += __uint_as_float((uint32_t)q0);
+            a1 += __uint_as_float((uint32_t)q1);
         }
         if (ok) {
-            float a0 = 0.0f, a1 = 0.0f;
-#pragma unroll
-            for (uint32_t r = 0; r < kMaxTpRanks; ++r) {  // rank order: every rank computes the same bits
-                if (r < g.size) {
-                    a0 += v[r][0];
-                    a1 += v[r][1];
-                }
-            }
             const uint32_t old = *reinterpret_cast<const uint32_t *>(h + i);
             const uint32_t s2 = f32x2_to_bf16x2(a0, a1);  // the projection's bf16 output
             *reinterpret_cast<uint32_t *>(h + i) =
@@ -147,7 +132,6 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_residual_kernel(TpRe
                                 __uint_as_float(s2 & 0xffff0000u) + __uint_as_float(old & 0xffff0000u));
         }
     }
-    if (!waited) pdl_wait();  // a thread without elements still takes part in the kernel ordering
     if (threadIdx.x == 0 && trace) trace_max(&trace->end);
 }
 
