@@ -2,13 +2,13 @@
 // through CUDA IPC, plain loads and stores over NVLink (no multimem, no library collective).
 //
 // At batch 1 the messages are one [hidden] f32 vector per rank (16 KB), so the exchange is bound by
-// latency, not bandwidth.  The all-reduce after a K-split projection is therefore fused into the two
-// matvecs around it (QmvExchange in qmv.cuh): the projection's epilogue pushes its share into every
-// rank's receive buffer as self-validating {value, ticket} packets, and the next matvec's prologue
-// polls the packets and sums the shares in rank order (so all ranks compute identical bits) while it
-// forms its input.  What is left
-// for kernels of their own is the end of a token: the greedy pick across vocabulary shards, or, for a
-// cache-only prompt row, closing the last exchange.
+// latency, not bandwidth.  The all-reduce after a K-split projection is therefore taken apart
+// (QmvExchange in qmv.cuh): the projection's epilogue pushes its share into every rank's receive buffer
+// as self-validating {value, ticket} packets, and a small kernel between the two matvecs polls the
+// packets, sums the shares in rank order (so all ranks compute identical bits) and folds the bf16-rounded
+// sum into the residual stream.  (The consuming matvec can also do that in its own prologue; see the
+// consumer hooks.)  What else needs kernels of its own is the end of a token: the greedy pick across
+// vocabulary shards, or, for a cache-only prompt row, closing the last exchange.
 #pragma once
 #include "common.cuh"
 #include "ops.cuh"
