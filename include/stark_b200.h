@@ -374,6 +374,14 @@ typedef struct stark_b200_sampling {
 #define STARK_B200_SAMPLE_TOP_K 4u
 #define STARK_B200_SAMPLE_TOP_P 8u
 #define STARK_B200_SAMPLE_MIN_P 16u
+/* With STARK_B200_SAMPLE_ORDERED_F64 (requires STOCHASTIC) the draw follows the generation worker's host
+ * sampler instead (crates/stark-generate/src/hybrid.rs:1103-1212): candidates in descending total order
+ * (signed zeros distinct, lower id first), probabilities exp(f64((l - max) / temperature)) summed
+ * sequentially in f64, the min-p / top-p prefix on those sums, and ONE SplitMix64 draw scaled by the kept
+ * mass.  `seed` is the SplitMix64 state before the draw; the caller advances its copy by
+ * STARK_B200_SPLITMIX64_STEP per sampled token, as `uniform` does.  Temperature defaults to 1. */
+#define STARK_B200_SAMPLE_ORDERED_F64 32u
+#define STARK_B200_SPLITMIX64_STEP 0x9e3779b97f4a7c15ull
 /* One row of `vocab` logits (io_type BF16 or F32; host or device) -> one token (host). */
 stark_b200_status stark_b200_op_sample(const void *logits, uint32_t vocab, uint32_t io_type,
                                        const stark_b200_sampling *params, uint32_t *out_token, uint32_t location,

@@ -295,6 +295,36 @@ def unified_sampling(logits, seed=None, temperature=None, top_k=None, top_p=None
     return int(f(_p(logits), logits.size, flags, seed or 0, temperature or 1.0, top_k or 0, top_p or 1.0, min_p or 0.0))
 
 
+SPLITMIX64_STEP = 0x9E3779B97F4A7C15
+
+
+def splitmix64_uniform(state: int) -> tuple[float, int]:
+    """`uniform` (crates/stark-generate/src/hybrid.rs:1103-1111): (value in [0, 1), advanced state)."""
+    st = C.c_uint64(state & (2**64 - 1))
+    f = lib().so_splitmix64_uniform
+    f.restype, f.argtypes = C.c_double, [C.POINTER(C.c_uint64)]
+    return float(f(C.byref(st))), int(st.value)
+
+
+def descending_sample_key(value: float) -> int:
+    f = lib().so_descending_sample_key
+    f.restype, f.argtypes = C.c_uint32, [C.c_float]
+    return int(f(value))
+
+
+def host_sampling(logits, rng: int, temperature: float = 1.0, top_k=None, top_p=None, min_p=None) -> tuple[int, int]:
+    """The generation worker's stochastic host sampler (hybrid.rs:1122-1212): (token, advanced rng state);
+    token 0xffffffff for an empty or non-finite row."""
+    logits = _c(logits, np.float32)
+    flags = (4 if top_k is not None else 0) | (8 if top_p is not None else 0) | (16 if min_p is not None else 0)
+    st = C.c_uint64(rng & (2**64 - 1))
+    f = lib().so_host_sampling_f64
+    f.restype = C.c_uint32
+    f.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint64), C.c_float, C.c_uint32, C.c_float, C.c_float]
+    tok = int(f(_p(logits), logits.size, flags, C.byref(st), temperature, top_k or 0, top_p or 1.0, min_p or 0.0))
+    return tok, int(st.value)
+
+
 def log_softmax_f64(logits) -> np.ndarray:
     logits = _c(logits, np.float32)
     out = np.empty(logits.size, np.float64)

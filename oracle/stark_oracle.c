@@ -831,6 +831,80 @@ static int so_ranked_cmp(const void *pa, const void *pb) {
     return a->i < b->i ? -1 : (a->i > b->i ? 1 : 0);
 }
 
+/* ---- the generation worker's host sampler (crates/stark-generate/src/hybrid.rs) ---- */
+
+/* `uniform` (hybrid.rs:1103-1111): one SplitMix64 step, the top 53 bits as a double in [0, 1). */
+double so_splitmix64_uniform(uint64_t *state) {
+    *state += 0x9e3779b97f4a7c15ull;
+    uint64_t z = *state;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    return (double)((z ^ (z >> 31)) >> 11) * (1.0 / 9007199254740992.0);
+}
+
+/* `descending_sample_key` (hybrid.rs:1324-1328): ascending integer order of the key = descending
+ * `total_cmp` order of the value (signed zeros stay distinct). */
+uint32_t so_descending_sample_key(float value) {
+    uint32_t bits;
+    memcpy(&bits, &value, 4);
+    const uint32_t mask = ((bits & 0x80000000u) ? 0xffffffffu : 0u) | 0x80000000u;
+    return ~(bits ^ mask);
+}
+
+static int so_u64_cmp(const void *pa, const void *pb) {
+    const uint64_t a = *(const uint64_t *)pa, b = *(const uint64_t *)pb;
+    return a < b ? -1 : (a > b ? 1 : 0);
+}
+
+/* `sample_with_mapper` over `sampling_distribution` (hybrid.rs:1122-1212) for Sampling::Stochastic:
+ * all logits finite, candidates = the first k of the descending (total order, then lower id) sequence
+ * (`sampling_indices`, :1265-1288, every branch of which yields that prefix), probabilities
+ * exp(f64((l - max) / temperature)) with the subtraction and the division in f32 (:138-165), their
+ * sequential f64 total, the min-p / top-p prefix (:1192-1204), then one SplitMix64 draw scaled by the kept
+ * mass and a sequential scan (:1134-1142).  flags: 4 top_k, 8 top_p, 16 min_p.  Returns the token,
+ * UINT32_MAX for an empty or non-finite row or k = 0; *rng advances by one step only when a token is drawn. */
+uint32_t so_host_sampling_f64(const float *logits, uint32_t vocab, uint32_t flags, uint64_t *rng, float temperature,
+                              uint32_t top_k, float top_p, float min_p) {
+    if (vocab == 0) return 0xffffffffu;
+    for (uint32_t i = 0; i < vocab; ++i)
+        if (!isfinite(logits[i])) return 0xffffffffu;
+    uint32_t k = vocab;
+    if ((flags & 4u) && top_k < k) k = top_k;
+    if (k == 0) return 0xffffffffu;
+    uint64_t *order = (uint64_t *)malloc((size_t)vocab * sizeof(uint64_t));
+    for (uint32_t i = 0; i < vocab; ++i) order[i] = ((uint64_t)so_descending_sample_key(logits[i]) << 32) | i;
+    qsort(order, vocab, sizeof(uint64_t), so_u64_cmp);
+    double *p = (double *)malloc((size_t)k * sizeof(double));
+    const float max = logits[(uint32_t)order[0]];
+    double total = 0.0;
+    for (uint32_t n = 0; n < k; ++n) {
+        const float arg = (logits[(uint32_t)order[n]] - max) / temperature;
+        p[n] = exp((double)arg);
+        total += p[n];
+    }
+    uint32_t kept = 0;
+    double cumulative = 0.0;
+    for (uint32_t n = 0; n < k; ++n) {
+        if (kept > 0 && (((flags & 16u) && p[n] < (double)min_p) || ((flags & 8u) && cumulative / total >= (double)top_p)))
+            break;
+        cumulative += p[n];
+        kept += 1;
+    }
+    const double target = so_splitmix64_uniform(rng) * cumulative;
+    uint32_t token = (uint32_t)order[kept - 1];
+    double mass = 0.0;
+    for (uint32_t n = 0; n < kept; ++n) {
+        mass += p[n];
+        if (target < mass) {
+            token = (uint32_t)order[n];
+            break;
+        }
+    }
+    free(p);
+    free(order);
+    return token;
+}
+
 /* flags: 1 stochastic, 2 temperature, 4 top_k, 8 top_p, 16 min_p.  Returns the token, UINT32_MAX if a
  * logit is not finite (or nothing finite is left). */
 uint32_t so_unified_sampling_f32(const float *in, uint32_t vocab, uint32_t flags, uint64_t seed, float temperature,

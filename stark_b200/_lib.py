@@ -62,10 +62,15 @@ class Sampling(C.Structure):
                 ("temperature", C.c_float), ("top_k", C.c_uint32), ("top_p", C.c_float), ("min_p", C.c_float)]
 
 
-def sampling(seed=None, temperature=None, top_k=None, top_p=None, min_p=None) -> Sampling:
-    """``seed`` None = no noise (greedy over whatever the filters keep)."""
+SPLITMIX64_STEP = 0x9E3779B97F4A7C15
+
+
+def sampling(seed=None, temperature=None, top_k=None, top_p=None, min_p=None, ordered=False) -> Sampling:
+    """``seed`` None = no noise (greedy over whatever the filters keep).  ``ordered`` selects the generation
+    worker's host-sampler semantics (sorted f64 probabilities, one SplitMix64 draw; ``seed`` is the
+    generator state before the draw)."""
     flags = (1 if seed is not None else 0) | (2 if temperature is not None else 0) | (4 if top_k is not None else 0) \
-        | (8 if top_p is not None else 0) | (16 if min_p is not None else 0)
+        | (8 if top_p is not None else 0) | (16 if min_p is not None else 0) | (32 if ordered else 0)
     return Sampling(C.sizeof(Sampling), flags, seed or 0, temperature if temperature is not None else 1.0,
                     top_k or 0, top_p if top_p is not None else 1.0, min_p if min_p is not None else 0.0)
 

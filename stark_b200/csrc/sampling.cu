@@ -81,6 +81,74 @@ __device__ inline T block_reduce(T v, F f, T *scratch /* [32] */) {
     return r;
 }
 
+// Stable LSD radix sort of (key, id) pairs by key, ascending, 8-bit digits, by one CTA of kSampleThreads.
+// The sorted pairs end in buffer 0.  counts: [256][kSampleWarps] shared words, uscratch: [32] shared words.
+__device__ inline void sort_pairs(uint32_t *const (&keys)[2], uint32_t *const (&idx)[2], uint32_t V, uint32_t *counts,
+                                  uint32_t *uscratch) {
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    // each warp owns a contiguous span, read 32 elements at a time: stable within the span by lane order
+    const uint32_t span = (V + kSampleWarps - 1u) / kSampleWarps;
+    const uint32_t lo = min(V, warp * span), hi = min(V, lo + span);
+    for (uint32_t pass = 0; pass < 4; ++pass) {
+        const uint32_t *kin = keys[pass & 1u], *iin = idx[pass & 1u];
+        uint32_t *kout = keys[(pass & 1u) ^ 1u], *iout = idx[(pass & 1u) ^ 1u];
+        const uint32_t shift = pass * 8u;
+        for (uint32_t i = tid; i < 256u * kSampleWarps; i += kSampleThreads) counts[i] = 0;
+        __syncthreads();
+        for (uint32_t base = lo; base < hi; base += 32u) {
+            const uint32_t i = base + lane;
+            const bool live = i < hi;
+            const uint32_t digit = live ? (kin[i] >> shift) & 255u : 256u + lane;  // idle lanes match nobody
+            const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+            if (live && (peers & ((1u << lane) - 1u)) == 0) counts[digit * kSampleWarps + warp] += __popc(peers);
+            __syncwarp();
+        }
+        __syncthreads();
+        // exclusive scan over (digit major, warp minor): 8192 entries, 8 per thread
+        uint32_t local[8], sum = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            local[j] = counts[tid * 8u + j];
+            sum += local[j];
+        }
+        uint32_t incl = sum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= (uint32_t)o) incl += n;
+        }
+        if (lane == 31u) uscratch[warp] = incl;
+        __syncthreads();
+        uint32_t before = 0;
+        for (uint32_t w = 0; w < warp; ++w) before += uscratch[w];
+        uint32_t run = before + incl - sum;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            counts[tid * 8u + j] = run;
+            run += local[j];
+        }
+        __syncthreads();
+        for (uint32_t base = lo; base < hi; base += 32u) {
+            const uint32_t i = base + lane;
+            const bool live = i < hi;
+            const uint32_t key = live ? kin[i] : 0u, id = live ? iin[i] : 0u;
+            const uint32_t digit = live ? (key >> shift) & 255u : 256u + lane;
+            const uint32_t peers = __match_any_sync(0xffffffffu, digit);
+            const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
+            uint32_t start = 0;
+            if (live) start = counts[digit * kSampleWarps + warp];
+            __syncwarp();
+            if (live) {
+                kout[start + rank] = key;
+                iout[start + rank] = id;
+                if (rank == 0) counts[digit * kSampleWarps + warp] = start + __popc(peers);
+            }
+            __syncwarp();
+        }
+        __syncthreads();
+    }
+}
+
 __global__ void __launch_bounds__(kSampleThreads) unified_sampling_kernel(const SampleParams p) {
     extern __shared__ uint32_t counts[];  // [256][kSampleWarps] radix counters
     __shared__ float fscratch[32];
@@ -128,67 +196,7 @@ __global__ void __launch_bounds__(kSampleThreads) unified_sampling_kernel(const 
             p.idx[0][i] = i;
         }
         __syncthreads();
-        // each warp owns a contiguous span, read 32 elements at a time: stable within the span by lane order
-        const uint32_t span = (V + kSampleWarps - 1u) / kSampleWarps;
-        const uint32_t lo = min(V, warp * span), hi = min(V, lo + span);
-        for (uint32_t pass = 0; pass < 4; ++pass) {
-            const uint32_t *kin = p.keys[pass & 1u], *iin = p.idx[pass & 1u];
-            uint32_t *kout = p.keys[(pass & 1u) ^ 1u], *iout = p.idx[(pass & 1u) ^ 1u];
-            const uint32_t shift = pass * 8u;
-            for (uint32_t i = tid; i < 256u * kSampleWarps; i += kSampleThreads) counts[i] = 0;
-            __syncthreads();
-            for (uint32_t base = lo; base < hi; base += 32u) {
-                const uint32_t i = base + lane;
-                const bool live = i < hi;
-                const uint32_t digit = live ? (kin[i] >> shift) & 255u : 256u + lane;  // idle lanes match nobody
-                const uint32_t peers = __match_any_sync(0xffffffffu, digit);
-                if (live && (peers & ((1u << lane) - 1u)) == 0) counts[digit * kSampleWarps + warp] += __popc(peers);
-                __syncwarp();
-            }
-            __syncthreads();
-            // exclusive scan over (digit major, warp minor): 8192 entries, 8 per thread
-            uint32_t local[8], sum = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                local[j] = counts[tid * 8u + j];
-                sum += local[j];
-            }
-            uint32_t incl = sum;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const uint32_t n = __shfl_up_sync(0xffffffffu, incl, o);
-                if (lane >= (uint32_t)o) incl += n;
-            }
-            if (lane == 31u) uscratch[warp] = incl;
-            __syncthreads();
-            uint32_t before = 0;
-            for (uint32_t w = 0; w < warp; ++w) before += uscratch[w];
-            uint32_t run = before + incl - sum;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                counts[tid * 8u + j] = run;
-                run += local[j];
-            }
-            __syncthreads();
-            for (uint32_t base = lo; base < hi; base += 32u) {
-                const uint32_t i = base + lane;
-                const bool live = i < hi;
-                const uint32_t key = live ? kin[i] : 0u, id = live ? iin[i] : 0u;
-                const uint32_t digit = live ? (key >> shift) & 255u : 256u + lane;
-                const uint32_t peers = __match_any_sync(0xffffffffu, digit);
-                const uint32_t rank = __popc(peers & ((1u << lane) - 1u));
-                uint32_t start = 0;
-                if (live) start = counts[digit * kSampleWarps + warp];
-                __syncwarp();
-                if (live) {
-                    kout[start + rank] = key;
-                    iout[start + rank] = id;
-                    if (rank == 0) counts[digit * kSampleWarps + warp] = start + __popc(peers);
-                }
-                __syncwarp();
-            }
-            __syncthreads();
-        }
+        sort_pairs(p.keys, p.idx, V, counts, uscratch);
         // four passes: the sorted pairs are back in buffer 0
         const uint32_t *skey = p.keys[0], *sidx = p.idx[0];
         const float top = key_value(skey[0]);
@@ -255,6 +263,114 @@ __global__ void __launch_bounds__(kSampleThreads) unified_sampling_kernel(const 
     }
 }
 
+// The generation worker's host sampler (crates/stark-generate/src/hybrid.rs:1122-1212) on the device:
+// candidates = the first k of the descending total order (lower id first among equal bit patterns,
+// :1265-1372), probabilities exp(f64((l - max) / temperature)) with the subtraction and division in f32
+// (:138-165), the sequential f64 total, the min-p / top-p prefix (:1192-1204), one SplitMix64 draw scaled
+// by the kept mass and a sequential scan (:1103-1111, :1134-1142).
+//
+// The partial sums S_n of the probabilities in candidate order serve the total, the prefix walk and the
+// scan alike, and they are what fixes the result bit for bit, so one thread forms them in order.  Two
+// things keep that short: once adding a term leaves S unchanged no later (smaller) term can change it, so
+// every walk stops adding there; and the quotient S / total is only formed when S is within 1e-14 of the
+// threshold, where the comparison could go either way.
+__global__ void __launch_bounds__(kSampleThreads) ordered_sampling_kernel(const SampleParams p) {
+    extern __shared__ uint32_t counts[];
+    __shared__ uint32_t uscratch[32];
+    __shared__ uint32_t first_below;
+    const uint32_t tid = threadIdx.x, V = p.vocab;
+    int bad = 0;
+    for (uint32_t i = tid; i < V; i += kSampleThreads) {
+        const float v = p.io_type == STARK_B200_F32 ? reinterpret_cast<const float *>(p.logits)[i]
+                                                     : bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(p.logits)[i]);
+        bad |= !isfinite(v);
+        p.keys[0][i] = descending_key(v);  // signed zeros stay distinct, as under total_cmp
+        p.idx[0][i] = i;
+    }
+    if (tid == 0) first_below = 0xffffffffu;
+    if (__syncthreads_or(bad)) {
+        if (tid == 0) *p.out = 0xffffffffu;
+        return;
+    }
+    sort_pairs(p.keys, p.idx, V, counts, uscratch);
+    const uint32_t *skey = p.keys[0], *sidx = p.idx[0];
+    double *terms = reinterpret_cast<double *>(p.idx[1]);  // idx[1] and the f32 term array: 8 bytes per entry
+    const uint32_t k = (p.flags & 4u) ? min(p.top_k, V) : V;
+    const float top = key_value(skey[0]);
+    const float temperature = (p.flags & 2u) ? p.temperature : 1.0f;
+    const double min_p = (double)p.min_p;
+    uint32_t below = 0xffffffffu;
+    for (uint32_t i = tid; i < k; i += kSampleThreads) {
+        const double t = exp((double)__fdiv_rn(__fsub_rn(key_value(skey[i]), top), temperature));
+        terms[i] = t;
+        if ((p.flags & 16u) && i > 0 && t < min_p) below = min(below, i);
+    }
+    if (below != 0xffffffffu) atomicMin(&first_below, below);
+    __syncthreads();
+    if (tid != 0) return;
+    const uint32_t limit = min(k, first_below);  // the min-p cut: the first candidate after the top one below it
+    // total; `live` = number of leading terms that still move the partial sums
+    double total = 0.0;
+    uint32_t live = k;
+    for (uint32_t base = 0; base < k && live == k; base += 8u) {
+        double t[8];
+#pragma unroll
+        for (uint32_t j = 0; j < 8u; ++j) t[j] = base + j < k ? terms[base + j] : 0.0;
+#pragma unroll
+        for (uint32_t j = 0; j < 8u; ++j) {
+            if (base + j >= k) break;
+            if (base + j > 0 && total + 2.0 * t[j] == total) {
+                live = base + j;
+                break;
+            }
+            total += t[j];
+        }
+    }
+    // prefix: stop before candidate n > 0 once S_n / total >= top_p
+    double cumulative = 0.0;
+    uint32_t kept = 0;
+    if (p.flags & 8u) {
+        const double top_p = (double)p.top_p, edge = top_p * total;
+        const double lo = edge * (1.0 - 1e-14), hi = edge * (1.0 + 1e-14);
+        for (; kept < limit; ++kept) {
+            if (kept > 0 && cumulative >= lo && (cumulative > hi || cumulative / total >= top_p)) break;
+            if (kept >= live) {  // S no longer changes: neither does the comparison
+                kept = limit;
+                break;
+            }
+            cumulative += terms[kept];
+        }
+    } else {
+        const uint32_t n = min(limit, live);
+        for (uint32_t base = 0; base < n; base += 8u) {
+            double t[8];
+#pragma unroll
+            for (uint32_t j = 0; j < 8u; ++j) t[j] = base + j < n ? terms[base + j] : 0.0;
+#pragma unroll
+            for (uint32_t j = 0; j < 8u; ++j)
+                if (base + j < n) cumulative += t[j];
+        }
+        kept = limit;
+    }
+    // draw
+    unsigned long long z = p.seed + 0x9e3779b97f4a7c15ull;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    const double u = (double)((z ^ (z >> 31)) >> 11) * (1.0 / 9007199254740992.0);
+    const double target = u * cumulative;
+    uint32_t chosen = kept - 1u;
+    double mass = 0.0;
+    const uint32_t scan = min(kept, live);
+    for (uint32_t n = 0; n < scan; ++n) {
+        mass += terms[n];
+        if (target < mass) {
+            chosen = n;
+            break;
+        }
+    }
+    *p.out = sidx[chosen];
+}
+
 }  // namespace
 
 size_t sampling_scratch_bytes(uint32_t vocab) { return (size_t)vocab * 4u * 6u; }
@@ -262,7 +378,8 @@ size_t sampling_scratch_bytes(uint32_t vocab) { return (size_t)vocab * 4u * 6u; 
 // SamplingMethod::validate (generation.rs:67-111): finite temperature in (0, 100] with a finite
 // reciprocal, 1 <= top_k <= vocab, 0 < top_p <= 1, 0 <= min_p <= 1.
 stark_b200_status sampling_validate(const stark_b200_sampling &s, uint32_t vocab) {
-    if (vocab == 0 || (s.flags & ~31u)) return STARK_B200_INVALID_ARGUMENT;
+    if (vocab == 0 || (s.flags & ~63u)) return STARK_B200_INVALID_ARGUMENT;
+    if ((s.flags & 32u) && !(s.flags & 1u)) return STARK_B200_INVALID_ARGUMENT;  // the ordered sampler only draws
     if (s.flags & 2u) {
         if (!std::isfinite(s.temperature) || !(s.temperature > 0.0f) || s.temperature > 100.0f ||
             !std::isfinite(1.0f / s.temperature))
@@ -298,7 +415,10 @@ stark_b200_status sampling_launch(const void *logits, uint32_t io_type, uint32_t
     p.terms = reinterpret_cast<float *>(base + 5u * (size_t)vocab);
     p.out = out_device;
     const size_t smem = 256u * kSampleWarps * sizeof(uint32_t);
-    unified_sampling_kernel<<<1, kSampleThreads, smem, stream>>>(p);
+    if (s.flags & 32u)
+        ordered_sampling_kernel<<<1, kSampleThreads, smem, stream>>>(p);
+    else
+        unified_sampling_kernel<<<1, kSampleThreads, smem, stream>>>(p);
     SB_CUDA(cudaGetLastError());
     return STARK_B200_OK;
 }

@@ -224,10 +224,12 @@ class DenseModel:
         self._guard(_lib.load().stark_b200_argmax(self._h, C.byref(t)), "argmax")
         return t.value
 
-    def sample(self, seed=None, temperature=None, top_k=None, top_p=None, min_p=None) -> int:
+    def sample(self, seed=None, temperature=None, top_k=None, top_p=None, min_p=None, ordered: bool = False) -> int:
         """One token from the last row's logits through the device sampler (the reference's unified
-        sampler; ``seed`` is the per-position seed, see ``position_seed``)."""
-        params = _lib.sampling(seed, temperature, top_k, top_p, min_p)
+        sampler; ``seed`` is the per-position seed, see ``position_seed``).  ``ordered`` selects the
+        generation worker's host-sampler semantics instead (crates/stark-generate/src/hybrid.rs:1122-1212);
+        ``seed`` is then the SplitMix64 state before the draw."""
+        params = _lib.sampling(seed, temperature, top_k, top_p, min_p, ordered)
         t = C.c_uint32(0)
         self._guard(_lib.load().stark_b200_sample(self._h, C.byref(params), C.byref(t)), "sample")
         return t.value

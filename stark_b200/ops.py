@@ -206,11 +206,14 @@ def log_softmax(logits: np.ndarray) -> np.ndarray:
     return out
 
 
-def sample(logits: np.ndarray, seed=None, temperature=None, top_k=None, top_p=None, min_p=None) -> int:
-    """One token from one row of logits (f32, or bf16 bit patterns as uint16) through the device sampler."""
+def sample(logits: np.ndarray, seed=None, temperature=None, top_k=None, top_p=None, min_p=None,
+           ordered: bool = False) -> int:
+    """One token from one row of logits (f32, or bf16 bit patterns as uint16) through the device sampler.
+    ``ordered``: the generation worker's host-sampler semantics; ``seed`` is then the SplitMix64 state
+    before the draw (advance it by ``_lib.SPLITMIX64_STEP`` per sampled token)."""
     logits = np.ascontiguousarray(logits)
     io = _lib.F32 if logits.dtype == np.float32 else _lib.BF16
-    params = _lib.sampling(seed, temperature, top_k, top_p, min_p)
+    params = _lib.sampling(seed, temperature, top_k, top_p, min_p, ordered)
     tok = C.c_uint32(0)
     check(_lib.load().stark_b200_op_sample(_ptr(logits), logits.size, io, C.byref(params), C.byref(tok), HOST, None),
           "op_sample")
