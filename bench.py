@@ -30,6 +30,9 @@ WORKLOADS = {
     "qwen3-8b": dict(cfg="qwen3-8b", prompt=4096, context=4096 + 1024),
     "qwen3-0.6b": dict(cfg="qwen3-0.6b", prompt=512, context=512 + 512),
     "small": dict(cfg="small", prompt=96, context=512),
+    # routed-expert decoders (f32 host-path conventions, GGUF Q8_0 attention + Q4_K experts)
+    "qwen3-30b-a3b": dict(cfg="qwen3-30b-a3b", prompt=2048, context=2048 + 512, moe=True),
+    "moe-small": dict(cfg="moe-small", prompt=64, context=256, moe=True),
     # a single quantized matvec (BASELINE config 1 by default): micro-benchmark / profiling target
     "matvec": dict(cfg=None, prompt=0, context=0),
 }
@@ -185,6 +188,107 @@ def run_matvec(args) -> None:
     }))
 
 
+def moe_weights_cycled(cfg: dict, seed: int, distinct: int = 4) -> dict:
+    """Weights of a routed-expert decoder with `distinct` independently drawn layers repeated in turn: the
+    full shape has 16 GB of expert banks, and drawing every layer separately would take minutes of host time
+    without changing what a step reads (each layer still gets its own device copy)."""
+    rng = np.random.default_rng(seed)
+    g = dict(token_table=S.q8_0_rows(rng, cfg["vocab"], cfg["hidden"], scale=3e-4),
+             output=S.q8_0_rows(rng, cfg["vocab"], cfg["hidden"], scale=3e-4),
+             final_norm=(1.0 + 0.1 * rng.standard_normal(cfg["hidden"])).astype(np.float32))
+    drawn = [S.moe_layer_weights(cfg, rng) for _ in range(min(distinct, cfg["layers"]))]
+    g["layers"] = [drawn[i % len(drawn)] for i in range(cfg["layers"])]
+    return g
+
+
+def moe_step_bytes(model, cfg: dict, context_rows: float) -> float:
+    """Algorithmic bytes of one decode token: the weights it reads plus the f32 key/value rows."""
+    kv = cfg["layers"] * 2 * cfg["kv_heads"] * cfg["head_dim"] * 4 * context_rows
+    return model.weight_bytes_per_token() + kv
+
+
+def moe_cpu_sample(cfg: dict, weights: dict, prompt: np.ndarray, prompt_rows: int, steps: int, threads: int) -> dict:
+    from oracle import oracle as O
+    orc = O.MoEDecoder(cfg, weights, prompt_rows + steps + 1, threads=threads)
+    orc.ingest(prompt[:prompt_rows - 1])
+    tok = int(orc.step(int(prompt[prompt_rows - 1])).argmax())
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = int(orc.step(tok).argmax())
+    dt = time.perf_counter() - t0
+    return {"value": steps / dt, "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": f"{steps} greedy decode steps after a {prompt_rows}-token prompt, same weights"}
+
+
+def run_moe(args, wl) -> None:
+    """Greedy decode of a routed-expert decoder on one GPU (the path has no multi-GPU form yet)."""
+    import torch
+
+    from stark_b200.engine import MoEModel
+    cfg = S.MOE_CONFIGS[wl["cfg"]]
+    steps, warmup = args.steps, max(args.warmup, 3)
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    weights = moe_weights_cycled(cfg, args.seed)
+    prompt = S.prompt(cfg, wl["prompt"], seed=args.seed + 1)
+    threads = os.cpu_count() or 1
+    if args.impl == "reference":
+        sample_steps = max(1, min(args.steps, 4))
+        rows = min(wl["prompt"], 16)
+        for _ in range(max(args.warmup, 0) and 1):
+            moe_cpu_sample(cfg, weights, prompt, rows, 1, threads)
+        base = moe_cpu_sample(cfg, weights, prompt, rows, sample_steps, threads)
+        print(json.dumps({
+            "impl": "reference", "metric": "decode tokens/s", "value": base["value"], "unit": "tok/s",
+            "n_gpus": args.gpus, "steps": sample_steps, "warmup": args.warmup, "ms_per_step": 1e3 / base["value"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{wl['cfg']} routed-expert decoder, GGUF Q8_0 attention + Q4_K experts, batch 1"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    torch.cuda.set_device(0)
+    model = MoEModel.load(cfg, weights, wl["context"])
+    model.ingest(prompt[:-1])
+    first = int(model.step(int(prompt[-1])).argmax())
+    picks = model.generate_greedy(first, warmup)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    stream = torch.cuda.ExternalStream(model.stream)  # events go on the stream the decoder launches on
+    with ClockSampler(0) as clocks:
+        torch.cuda.synchronize()
+        e0.record(stream)
+        out = model.generate_greedy(int(picks[-1]), steps)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        # end to end: the token goes in from the host, the full logits come back, the host picks
+        tok = int(out[-1])
+        t0 = time.perf_counter()
+        e2e_steps = min(steps, 64)
+        for _ in range(e2e_steps):
+            tok = int(model.step(tok).argmax())
+        e2e = (time.perf_counter() - t0) / e2e_steps
+    ms = e0.elapsed_time(e1) / steps
+    rows = wl["prompt"] + warmup + steps / 2
+    per = moe_step_bytes(model, cfg, rows)
+    peak, kind = peaks()
+    line = {
+        "metric": "decode tokens/s", "value": 1e3 / ms, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": f"{wl['cfg']} routed-expert decoder, GGUF Q8_0 attention + Q4_K experts, batch 1, "
+                               f"{wl['prompt']}-token prompt, greedy decode",
+                   "l2": f"{per / 1e6:.0f} MB read per step, larger than L2" if per > 126e6 else
+                         f"{per / 1e6:.0f} MB read per step (fits in L2: a test shape, not a bench line)"},
+        "e2e": {"value": 1.0 / e2e, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4 * cfg["vocab"]},
+        "gpu_launches": steps * model.launches_per_token, "clocks": clocks.summary(),
+        "roofline": {"bound": "hbm", "achieved": per / ms / 1e6, "peak": peak, "unit": "GB/s",
+                     "frac": per / ms / 1e6 / peak, "traffic": None, "peak_kind": kind},
+    }
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = moe_cpu_sample(cfg, weights, prompt, min(wl["prompt"], 16), 2, threads)
+    model.close()
+    print(json.dumps(line))
+
+
 def run_reference(args, wl, cfg) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -236,6 +340,9 @@ def main() -> None:
                     help="matvec workload only")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
+    if wl.get("moe"):
+        run_moe(args, wl)
+        return
     if args.workload == "matvec":
         run_matvec(args)
         return

@@ -423,6 +423,67 @@ stark_b200_status stark_b200_graph_end(void *stream, stark_b200_graph **out_grap
 stark_b200_status stark_b200_graph_launch(stark_b200_graph *graph, void *stream);
 stark_b200_status stark_b200_graph_destroy(stark_b200_graph **graph);
 
+/* ---- Routed-expert (MoE) decoder on the hybrid host path's conventions ----------------------------------
+ * f32 activations and logits, GGUF blocks decoded as decode_block, f32 key/value cache; the engine surface
+ * is hybrid::Model's (crates/stark-engine/src/engine/hybrid/mod.rs:347,863,897,990: load, reset, ingest,
+ * step -> logits).  The step composes the reference's host operators: rms_norm (engine/hybrid/math.rs:18-34),
+ * projections + per-head norm + rope + causal attention (engine/hybrid/ripple.rs:653-741), router -> top-k ->
+ * softmax over the selected -> expert mixture without a shared expert (engine/hybrid/qwen.rs:872-899),
+ * pre-norm residuals and the output projection (ripple.rs:474-482).  head_dim must be 128, hidden a multiple
+ * of 256, expert_intermediate a multiple of 256, experts <= 1024, active_experts <= 32. */
+typedef struct stark_b200_moe_model stark_b200_moe_model;
+typedef struct stark_b200_moe_config {
+    uint32_t struct_size;
+    uint32_t vocab, hidden, layers, q_heads, kv_heads, head_dim;
+    uint32_t experts, active_experts, expert_intermediate;
+    uint32_t context_tokens;
+    float rms_eps, rope_theta;
+} stark_b200_moe_config;
+/* Matrices are borrowed qmatrix handles (they must outlive the model): QKV = Q8_0 rows [q; k; v]
+ * ((q_heads + 2 kv_heads) * head_dim x hidden), O = Q8_0 hidden x q_heads*head_dim, GATE / UP = Q4_K banks
+ * [experts, expert_intermediate, hidden], DOWN = Q4_K bank [experts, hidden, expert_intermediate], OUTPUT =
+ * Q8_0 vocab x hidden (layer ignored). */
+#define STARK_B200_MOE_MAT_QKV 0u
+#define STARK_B200_MOE_MAT_O 1u
+#define STARK_B200_MOE_MAT_GATE 2u
+#define STARK_B200_MOE_MAT_UP 3u
+#define STARK_B200_MOE_MAT_DOWN 4u
+#define STARK_B200_MOE_MAT_OUTPUT 5u
+/* Host tensors, copied: f32 vectors ATTN_NORM / FFN_NORM [hidden], Q_NORM / K_NORM [head_dim], FINAL_NORM
+ * [hidden] (layer ignored), ROUTER f32 [experts, hidden]; TOKEN_TABLE = the Q8_0 blocks of the token
+ * embedding [vocab, hidden] in the file's byte layout (layer ignored).  `bytes` must match exactly. */
+#define STARK_B200_MOE_TENSOR_ATTN_NORM 0u
+#define STARK_B200_MOE_TENSOR_FFN_NORM 1u
+#define STARK_B200_MOE_TENSOR_Q_NORM 2u
+#define STARK_B200_MOE_TENSOR_K_NORM 3u
+#define STARK_B200_MOE_TENSOR_FINAL_NORM 4u
+#define STARK_B200_MOE_TENSOR_ROUTER 5u
+#define STARK_B200_MOE_TENSOR_TOKEN_TABLE 6u
+stark_b200_status stark_b200_moe_model_create(const stark_b200_moe_config *config, stark_b200_moe_model **out_model);
+stark_b200_status stark_b200_moe_model_set_matrix(stark_b200_moe_model *model, uint32_t kind, uint32_t layer,
+                                                  const stark_b200_qmatrix *matrix);
+stark_b200_status stark_b200_moe_model_set_tensor(stark_b200_moe_model *model, uint32_t kind, uint32_t layer,
+                                                  const void *host_data, size_t bytes);
+stark_b200_status stark_b200_moe_model_reset(stark_b200_moe_model *model);
+/* Appends `count` prompt tokens to the cache without computing logits (Model::ingest). */
+stark_b200_status stark_b200_moe_model_ingest(stark_b200_moe_model *model, const uint32_t *tokens, uint32_t count);
+/* Consumes one token and returns the full-vocabulary f32 logits for the next (Model::step: finite, else the
+ * model is reset and DEVICE_FAILURE returned).  logits_host may be NULL. */
+stark_b200_status stark_b200_moe_model_step(stark_b200_moe_model *model, uint32_t token, float *logits_host,
+                                            size_t count);
+/* Greedy decode chained on the device: consumes `first`, then each step's own pick; out_tokens[i] is the pick
+ * after i + 1 steps (first index of the maximum logit). */
+stark_b200_status stark_b200_moe_model_generate_greedy(stark_b200_moe_model *model, uint32_t first, uint32_t steps,
+                                                       uint32_t *out_tokens);
+/* Expert ids the last token selected, [layers][active_experts], selection order. */
+stark_b200_status stark_b200_moe_model_last_experts(stark_b200_moe_model *model, uint32_t *ids_host, size_t count);
+stark_b200_status stark_b200_moe_model_position(const stark_b200_moe_model *model, uint32_t *out_position);
+/* Kernel launches of one token step with logits (the graph's node count). */
+stark_b200_status stark_b200_moe_model_launches_per_token(const stark_b200_moe_model *model, uint32_t *out_launches);
+/* The CUDA stream (cudaStream_t) the model's work is issued on, for events around it. */
+stark_b200_status stark_b200_moe_model_stream(const stark_b200_moe_model *model, void **out_stream);
+stark_b200_status stark_b200_moe_model_destroy(stark_b200_moe_model **model);
+
 #ifdef __cplusplus
 }
 #endif

@@ -461,3 +461,71 @@ def moe_ffn_f32(kind_gate_up, gate_bank, up_bank, kind_down, down_bank, scores, 
     if rc:
         raise ValueError("invalid expert geometry or inputs")
     return out, ids, probs
+
+
+class _SoMoeModel(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("vocab", "hidden", "layers", "q_heads", "kv_heads", "head_dim", "experts",
+                                          "active", "inter", "context")] + [
+        ("eps", C.c_float), ("theta", C.c_float), ("embed", C.c_void_p), ("output", C.c_void_p),
+        ("final_norm", C.c_void_p)] + [(n, C.POINTER(C.c_void_p)) for n in (
+            "attn_norm", "ffn_norm", "q_norm", "k_norm", "wq", "wk", "wv", "wo", "router", "gate", "up", "down")]
+
+
+class MoEDecoder:
+    """The routed-expert decoder step of the hybrid host path (`so_moe_step`), over weights in the layout
+    of ``stark_b200.synthetic.moe_weights`` ([q; k; v] rows fused in one Q8_0 array)."""
+
+    def __init__(self, cfg: dict, weights: dict, context_tokens: int, threads: int = 0):
+        self.cfg, self.context, self.threads = dict(cfg), int(context_tokens), threads or max_threads()
+        self._keep = []
+        L = cfg["layers"]
+        qd, kd = cfg["q_heads"] * cfg["head_dim"], cfg["kv_heads"] * cfg["head_dim"]
+
+        def hold(a, dtype):
+            a = np.ascontiguousarray(a, dtype)
+            self._keep.append(a)
+            return a.ctypes.data
+
+        def per_layer(fn):
+            arr = (C.c_void_p * L)(*[fn(w) for w in weights["layers"]])
+            self._keep.append(arr)
+            return C.cast(arr, C.POINTER(C.c_void_p))
+
+        m = _SoMoeModel(cfg["vocab"], cfg["hidden"], L, cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"],
+                        cfg["experts"], cfg["active"], cfg["inter"], self.context, cfg["eps"], cfg["rope_theta"])
+        m.embed, m.output = hold(weights["token_table"], np.uint8), hold(weights["output"], np.uint8)
+        m.final_norm = hold(weights["final_norm"], np.float32)
+        rows = lambda w, lo, hi: np.asarray(w["qkv"], np.uint8).reshape(qd + 2 * kd, -1)[lo:hi]
+        m.wq = per_layer(lambda w: hold(rows(w, 0, qd), np.uint8))
+        m.wk = per_layer(lambda w: hold(rows(w, qd, qd + kd), np.uint8))
+        m.wv = per_layer(lambda w: hold(rows(w, qd + kd, qd + 2 * kd), np.uint8))
+        m.wo = per_layer(lambda w: hold(w["o"], np.uint8))
+        for name in ("attn_norm", "ffn_norm", "q_norm", "k_norm", "router"):
+            setattr(m, name, per_layer(lambda w, n=name: hold(w[n], np.float32)))
+        for name in ("gate", "up", "down"):
+            setattr(m, name, per_layer(lambda w, n=name: hold(w[n], np.uint8)))
+        self._m = m
+        kv = L * self.context * kd
+        self.keys, self.values = np.zeros(kv, np.float32), np.zeros(kv, np.float32)
+        self.position = 0
+        self.last_experts = np.zeros((L, cfg["active"]), np.uint32)
+
+    def reset(self):
+        self.position = 0
+
+    def step(self, token: int, want_logits: bool = True):
+        logits = np.empty(self.cfg["vocab"], np.float32) if want_logits else None
+        f = lib().so_moe_step
+        f.restype = C.c_int
+        f.argtypes = [C.POINTER(_SoMoeModel), C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p,
+                      C.c_int]
+        rc = f(C.byref(self._m), _p(self.keys), _p(self.values), self.position, int(token),
+               _p(logits) if want_logits else None, _p(self.last_experts), self.threads)
+        if rc != 0:
+            raise ValueError("moe step")
+        self.position += 1
+        return logits
+
+    def ingest(self, tokens):
+        for t in tokens:
+            self.step(int(t), want_logits=False)

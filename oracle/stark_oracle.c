@@ -761,6 +761,109 @@ void so_dense_matvec_f32(const float *w, const float *x, float *y, uint32_t rows
     }
 }
 
+/* ------------------------------------------------------------ routed-expert decoder (f32 host path) */
+
+/* `rope` of the hybrid host graphs (crates/stark-engine/src/engine/hybrid/ripple.rs:653-666, the same
+ * in flint.rs:412-425): angle = position * theta^(-(2i)/d) in f32, half-split pairing (i, i + d/2). */
+void so_rope_f32(float *head, uint32_t dim, uint32_t position, float theta) {
+    const uint32_t half = dim / 2;
+    for (uint32_t i = 0; i < half; i++) {
+        const float angle = (float)position * powf(theta, -((float)(2 * i)) / (float)dim);
+        const float sn = sinf(angle), cs = cosf(angle);
+        const float a = head[i], b = head[i + half];
+        head[i] = a * cs - b * sn;
+        head[i + half] = a * sn + b * cs;
+    }
+}
+
+/* One token of a routed-expert decoder on the hybrid host path's conventions (f32 activations, GGUF
+ * blocks decoded as decode_block, sequential f32 sums).  The reference ships no model of exactly this
+ * shape; the step is composed of its operators:
+ *   rms_norm                                math.rs:18-34
+ *   q/k/v projections, per-head norm, rope, causal attention over the f32 cache, o projection
+ *                                           ripple.rs:668-741 (no blend, no gate, no window)
+ *   router scores -> top-k -> softmax over the selected -> expert mixture
+ *                                           qwen.rs:872-899 (no shared expert), math.rs:36-66
+ *   x += update (pre-norm residual), final norm, output projection
+ *                                           ripple.rs:474-482 (without the post norms)
+ * Attention matrices, the token table and the output matrix are Q8_0, expert banks Q4_K. */
+typedef struct {
+    uint32_t vocab, hidden, layers, q_heads, kv_heads, head_dim, experts, active, inter, context;
+    float eps, theta;
+    const uint8_t *embed, *output;               /* Q8_0 [vocab, hidden] */
+    const float *final_norm;                     /* [hidden] */
+    const float *const *attn_norm, *const *ffn_norm, *const *q_norm, *const *k_norm;
+    const uint8_t *const *wq, *const *wk, *const *wv, *const *wo; /* Q8_0 */
+    const float *const *router;                  /* f32 [experts, hidden] */
+    const uint8_t *const *gate, *const *up, *const *down; /* Q4_K banks [experts, rows, columns] */
+} so_moe_model;
+
+/* keys / values: [layers][context][kv_heads * head_dim] f32, filled up to `position`.  logits may be
+ * NULL (a prompt token that only fills the cache).  ids_out (may be NULL): [layers][active]. */
+int so_moe_step(const so_moe_model *m, float *keys, float *values, uint32_t position, uint32_t token,
+                float *logits, uint32_t *ids_out, int threads) {
+    const uint32_t H = m->hidden, D = m->head_dim, QH = m->q_heads, KV = m->kv_heads;
+    if (token >= m->vocab || position >= m->context || H % 256u || QH % KV) return SO_INVALID;
+    const uint32_t kind_q8 = 8, kind_q4k = 12; /* ggml type ids */
+    const size_t kv_row = (size_t)KV * D;
+    float *x = (float *)malloc(sizeof(float) * H), *n = (float *)malloc(sizeof(float) * H);
+    float *q = (float *)malloc(sizeof(float) * QH * D), *att = (float *)malloc(sizeof(float) * QH * D);
+    float *upd = (float *)malloc(sizeof(float) * H), *scores = (float *)malloc(sizeof(float) * m->experts);
+    float *sc = (float *)malloc(sizeof(float) * (position + 1)), *pr = (float *)malloc(sizeof(float) * (position + 1));
+    float *tmp = (float *)malloc(sizeof(float) * D);
+    int rc = so_gguf_decode_row(kind_q8, m->embed + (size_t)token * (H / 32u) * 34u, x, H);
+    for (uint32_t l = 0; l < m->layers && rc == SO_OK; l++) {
+        float *kc = keys + ((size_t)l * m->context + position) * kv_row;
+        float *vc = values + ((size_t)l * m->context + position) * kv_row;
+        rc |= so_rmsnorm_f32(x, m->attn_norm[l], n, H, m->eps);
+        rc |= so_gguf_matvec_f32(kind_q8, m->wq[l], n, q, QH * D, H, threads);
+        rc |= so_gguf_matvec_f32(kind_q8, m->wk[l], n, kc, KV * D, H, threads);
+        rc |= so_gguf_matvec_f32(kind_q8, m->wv[l], n, vc, KV * D, H, threads);
+        if (rc != SO_OK) break;
+        for (uint32_t h = 0; h < QH; h++) {
+            rc |= so_rmsnorm_f32(q + h * D, m->q_norm[l], tmp, D, m->eps);
+            memcpy(q + h * D, tmp, sizeof(float) * D);
+            so_rope_f32(q + h * D, D, position, m->theta);
+        }
+        for (uint32_t h = 0; h < KV; h++) {
+            rc |= so_rmsnorm_f32(kc + h * D, m->k_norm[l], tmp, D, m->eps);
+            memcpy(kc + h * D, tmp, sizeof(float) * D);
+            so_rope_f32(kc + h * D, D, position, m->theta);
+        }
+        const float scale = 1.0f / sqrtf((float)D);
+        for (uint32_t h = 0; h < QH; h++) {
+            const uint32_t begin = h / (QH / KV) * D;
+            const float *qh = q + h * D;
+            float *out = att + h * D;
+            for (uint32_t t = 0; t <= position; t++) {
+                const float *k = keys + ((size_t)l * m->context + t) * kv_row + begin;
+                float dot = 0.0f;
+                for (uint32_t i = 0; i < D; i++) dot += qh[i] * k[i];
+                sc[t] = dot * scale;
+            }
+            rc |= so_softmax_f32(sc, pr, position + 1);
+            for (uint32_t i = 0; i < D; i++) out[i] = 0.0f;
+            for (uint32_t t = 0; t <= position; t++) {
+                const float *v = values + ((size_t)l * m->context + t) * kv_row + begin;
+                for (uint32_t i = 0; i < D; i++) out[i] += pr[t] * v[i];
+            }
+        }
+        rc |= so_gguf_matvec_f32(kind_q8, m->wo[l], att, upd, H, QH * D, threads);
+        for (uint32_t i = 0; i < H; i++) x[i] += upd[i];
+        rc |= so_rmsnorm_f32(x, m->ffn_norm[l], n, H, m->eps);
+        so_dense_matvec_f32(m->router[l], n, scores, m->experts, H);
+        rc |= so_moe_ffn_f32(kind_q4k, m->gate[l], m->up[l], kind_q4k, m->down[l], scores, n, upd, m->experts, m->active,
+                             H, m->inter, ids_out ? ids_out + (size_t)l * m->active : NULL, NULL, threads);
+        for (uint32_t i = 0; i < H; i++) x[i] += upd[i];
+    }
+    if (rc == SO_OK && logits) {
+        rc |= so_rmsnorm_f32(x, m->final_norm, n, H, m->eps);
+        rc |= so_gguf_matvec_f32(kind_q8, m->output, n, logits, m->vocab, H, threads);
+    }
+    free(x), free(n), free(q), free(att), free(upd), free(scores), free(sc), free(pr), free(tmp);
+    return rc == SO_OK ? SO_OK : SO_INVALID;
+}
+
 /* ------------------------------------------------------------------------------------------------
  * Stochastic sampling of the converted-model path.
  *   Philox4x32-10 counter-based generator, Gumbel noise, index -> (counter offset, word) mapping:

@@ -46,6 +46,16 @@ class DenseConfig(C.Structure):
         ("eps", C.c_float), ("rope_theta", C.c_float), ("reserved", C.c_uint32)]
 
 
+class MoeConfig(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("struct_size", "vocab", "hidden", "layers", "q_heads", "kv_heads", "head_dim",
+                                          "experts", "active_experts", "expert_intermediate", "context_tokens")] + [
+        ("rms_eps", C.c_float), ("rope_theta", C.c_float)]
+
+
+MOE_MAT_QKV, MOE_MAT_O, MOE_MAT_GATE, MOE_MAT_UP, MOE_MAT_DOWN, MOE_MAT_OUTPUT = range(6)
+(MOE_ATTN_NORM, MOE_FFN_NORM, MOE_Q_NORM, MOE_K_NORM, MOE_FINAL_NORM, MOE_ROUTER, MOE_TOKEN_TABLE) = range(7)
+
+
 class Info(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("abi_version", C.c_uint32), ("vocab_size", C.c_uint32),
                 ("prefill_chunk_tokens", C.c_uint32), ("context_tokens", C.c_uint64), ("position", C.c_uint64),
@@ -144,6 +154,18 @@ def load() -> C.CDLL:
         "stark_b200_get_info": (u32, [vp, C.POINTER(Info)]),
         "stark_b200_model_stream": (u32, [vp, C.POINTER(vp)]),
         "stark_b200_read_trace": (u32, [vp, vp, sz]),
+        "stark_b200_moe_model_create": (u32, [C.POINTER(MoeConfig), C.POINTER(vp)]),
+        "stark_b200_moe_model_set_matrix": (u32, [vp, u32, u32, vp]),
+        "stark_b200_moe_model_set_tensor": (u32, [vp, u32, u32, vp, sz]),
+        "stark_b200_moe_model_reset": (u32, [vp]),
+        "stark_b200_moe_model_ingest": (u32, [vp, vp, u32]),
+        "stark_b200_moe_model_step": (u32, [vp, u32, vp, sz]),
+        "stark_b200_moe_model_generate_greedy": (u32, [vp, u32, u32, vp]),
+        "stark_b200_moe_model_last_experts": (u32, [vp, vp, sz]),
+        "stark_b200_moe_model_position": (u32, [vp, C.POINTER(u32)]),
+        "stark_b200_moe_model_launches_per_token": (u32, [vp, C.POINTER(u32)]),
+        "stark_b200_moe_model_stream": (u32, [vp, C.POINTER(vp)]),
+        "stark_b200_moe_model_destroy": (u32, [C.POINTER(vp)]),
         "stark_b200_graph_begin": (u32, [vp]),
         "stark_b200_graph_end": (u32, [vp, C.POINTER(vp)]),
         "stark_b200_graph_launch": (u32, [vp, vp]),

@@ -1,0 +1,663 @@
+// A routed-expert (MoE) decoder on the conventions of the reference's hybrid host path: f32 activations
+// and logits, GGUF blocks decoded exactly as decode_block, an f32 key/value cache.  The reference ships no
+// model of exactly this shape; the token step composes its operators:
+//   rms_norm                                          crates/stark-engine/src/engine/hybrid/math.rs:18-34
+//   q/k/v projection, per-head norm, rope, causal attention, o projection
+//                                                     engine/hybrid/ripple.rs:653-741
+//   router -> top-k -> softmax over the selected -> expert mixture (no shared expert)
+//                                                     engine/hybrid/qwen.rs:872-899, math.rs:36-66
+//   pre-norm residuals, final norm, output projection engine/hybrid/ripple.rs:474-482
+// Projections and expert banks go through the quantized matvec kernels (Q8_0 / Q4_K, tensor-core MAC);
+// the kernels here are the f32 glue between them.  One token = one CUDA graph; token and position live on
+// the device, so greedy decode chains without the host.
+#include <cmath>
+#include <vector>
+
+#include "context.cuh"
+#include "ops.cuh"
+#include "qmv.cuh"
+
+#define SB_TRY(expr)                        \
+    do {                                    \
+        stark_b200_status _s = (expr);      \
+        if (_s != STARK_B200_OK) return _s; \
+    } while (0)
+
+namespace sb {
+
+namespace {
+
+struct MoeState {
+    uint32_t token;     // the token this step consumes (written by the host, or taken from `next`)
+    uint32_t chain;     // 1: consume `next` (the greedy pick of the previous step)
+    uint32_t next;      // first index of the maximum of the last logits
+    uint32_t position;  // rows in the cache
+    uint32_t error;     // sticky: 1 token out of range, 2 non-finite logits, 4 context exhausted
+};
+
+constexpr uint32_t kAttnSplits = 8, kAttnWarps = 8;
+
+template <int THREADS>
+__device__ inline float block_sum(float v, float *scratch /* [32] */) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31u) == 0) scratch[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.0f;
+    for (int w = 0; w < THREADS / 32; ++w) r += scratch[w];
+    return r;
+}
+
+// Token row of a Q8_0 table in the source layout (34-byte blocks of 32): d * q, as decode_block
+// (engine/hybrid/weights.rs:2936-2941).
+__global__ void __launch_bounds__(256) moe_embed_kernel(MoeState *st, const uint8_t *blocks, float *x, uint32_t hidden,
+                                                        uint32_t vocab, uint32_t context) {
+    uint32_t token = st->chain ? st->next : st->token;
+    __syncthreads();
+    if (token >= vocab || st->position >= context) {
+        if (threadIdx.x == 0) st->error |= token >= vocab ? 1u : 4u;
+        token = 0;
+    }
+    if (threadIdx.x == 0) st->token = token;
+    const uint8_t *row = blocks + (size_t)token * (hidden / 32u) * 34u;
+    for (uint32_t i = threadIdx.x; i < hidden; i += 256u) {
+        const uint8_t *b = row + (i >> 5) * 34u;
+        const float d = __half2float(__ushort_as_half((unsigned short)(b[0] | (b[1] << 8))));
+        x[i] = d * (float)(int8_t)b[2u + (i & 31u)];
+    }
+}
+
+// out = x * (1 / sqrt(mean(x^2) + eps)) * w   (math.rs:18-34)
+__global__ void __launch_bounds__(1024) moe_rmsnorm_kernel(const float *x, const float *w, float *out, uint32_t n,
+                                                           float eps) {
+    __shared__ float scratch[32];
+    float s = 0.0f;
+    for (uint32_t i = threadIdx.x; i < n; i += 1024u) s += x[i] * x[i];
+    const float mean = block_sum<1024>(s, scratch) / (float)n;
+    const float scale = 1.0f / sqrtf(mean + eps);
+    for (uint32_t i = threadIdx.x; i < n; i += 1024u) out[i] = x[i] * scale * w[i];
+}
+
+// One CTA of `dim` threads per head of the fused [q; k; v] projection: q and k heads get the per-head norm
+// and rope (ripple.rs:696-703, 653-666); k and v heads land in the cache row of this position.
+__global__ void moe_heads_kernel(const MoeState *st, float *qkv, const float *q_norm, const float *k_norm, float *keys,
+                                 float *values, uint32_t q_heads, uint32_t kv_heads, uint32_t dim, float eps,
+                                 float theta, uint32_t context) {
+    __shared__ float scratch[32];
+    __shared__ float head[256];
+    const uint32_t h = blockIdx.x, i = threadIdx.x;
+    const uint32_t position = min(st->position, context - 1u);  // a full cache is refused on the host first
+    const size_t kv_row = (size_t)kv_heads * dim;
+    float *src = qkv + (size_t)h * dim;
+    if (h >= q_heads + kv_heads) {  // v: copy
+        values[position * kv_row + (size_t)(h - q_heads - kv_heads) * dim + i] = src[i];
+        return;
+    }
+    const float v = src[i];
+    float s = v * v;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((i & 31u) == 0) scratch[i >> 5] = s;
+    __syncthreads();
+    float sum = 0.0f;
+    for (uint32_t w = 0; w < dim / 32u; ++w) sum += scratch[w];
+    const float scale = 1.0f / sqrtf(sum / (float)dim + eps);
+    head[i] = v * scale * (h < q_heads ? q_norm : k_norm)[i];
+    __syncthreads();
+    const uint32_t half = dim / 2u, pair = i < half ? i : i - half;
+    const float angle = (float)position * powf(theta, -((float)(2u * pair)) / (float)dim);
+    float sn, cs;
+    sincosf(angle, &sn, &cs);
+    const float a = head[pair], b = head[pair + half];
+    const float out = i < half ? a * cs - b * sn : a * sn + b * cs;
+    if (h < q_heads)
+        src[i] = out;
+    else
+        keys[position * kv_row + (size_t)(h - q_heads) * dim + i] = out;
+}
+
+// Causal attention of one query head over one span of the cache (ripple.rs:716-735): scores q.k / sqrt(d),
+// softmax, probability-weighted values.  Each warp walks every 8th row of the span with its own running
+// (max, sum, accumulator); the warps' states are merged in shared memory and the span's state goes to
+// `part` for the merge kernel.  dim = 128: one float4 per lane.
+__global__ void __launch_bounds__(kAttnWarps * 32) moe_attention_kernel(const MoeState *st, const float *q,
+                                                                        const float *keys, const float *values,
+                                                                        float *part, uint32_t q_heads,
+                                                                        uint32_t kv_heads, float scale,
+                                                                        uint32_t context) {
+    constexpr uint32_t D = 128;
+    __shared__ float sm[kAttnWarps], sl[kAttnWarps];
+    __shared__ float4 sacc[kAttnWarps][32];
+    const uint32_t h = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t rows = min(st->position + 1u, context);
+    const uint32_t span = (rows + kAttnSplits - 1u) / kAttnSplits;
+    const uint32_t lo = min(rows, split * span), hi = min(rows, lo + span);
+    const size_t kv_row = (size_t)kv_heads * D;
+    const uint32_t begin = h / (q_heads / kv_heads) * D;
+    const float4 qv = reinterpret_cast<const float4 *>(q + (size_t)h * D)[lane];
+    float m = -INFINITY, l = 0.0f;
+    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (uint32_t t = lo + warp; t < hi; t += kAttnWarps) {
+        const float4 kv = reinterpret_cast<const float4 *>(keys + t * kv_row + begin)[lane];
+        float dot = qv.x * kv.x + qv.y * kv.y + qv.z * kv.z + qv.w * kv.w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float s = dot * scale;
+        const float4 vv = reinterpret_cast<const float4 *>(values + t * kv_row + begin)[lane];
+        const float nm = fmaxf(m, s);
+        const float c = expf(m - nm), p = expf(s - nm);  // expf(-inf) = 0 on the first row
+        l = l * c + p;
+        acc.x = acc.x * c + p * vv.x;
+        acc.y = acc.y * c + p * vv.y;
+        acc.z = acc.z * c + p * vv.z;
+        acc.w = acc.w * c + p * vv.w;
+        m = nm;
+    }
+    if (lane == 0) sm[warp] = m, sl[warp] = l;
+    sacc[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0) {
+        float gm = -INFINITY;
+        for (uint32_t w = 0; w < kAttnWarps; ++w) gm = fmaxf(gm, sm[w]);
+        float gl = 0.0f;
+        float4 g = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t w = 0; w < kAttnWarps; ++w) {
+            if (sm[w] == -INFINITY) continue;
+            const float c = expf(sm[w] - gm);
+            const float4 a = sacc[w][lane];
+            gl += sl[w] * c;
+            g.x += a.x * c, g.y += a.y * c, g.z += a.z * c, g.w += a.w * c;
+        }
+        float *dst = part + ((size_t)h * kAttnSplits + split) * (D + 2u);
+        if (lane == 0) dst[0] = gm, dst[1] = gl;
+        reinterpret_cast<float2 *>(dst + 2)[lane * 2u] = make_float2(g.x, g.y);
+        reinterpret_cast<float2 *>(dst + 2)[lane * 2u + 1u] = make_float2(g.z, g.w);
+    }
+}
+
+__global__ void __launch_bounds__(128) moe_attention_merge_kernel(const float *part, float *out) {
+    constexpr uint32_t D = 128;
+    const uint32_t h = blockIdx.x, i = threadIdx.x;
+    const float *src = part + (size_t)h * kAttnSplits * (D + 2u);
+    float gm = -INFINITY;
+    for (uint32_t s = 0; s < kAttnSplits; ++s) gm = fmaxf(gm, src[s * (D + 2u)]);
+    float l = 0.0f, a = 0.0f;
+    for (uint32_t s = 0; s < kAttnSplits; ++s) {
+        const float m = src[s * (D + 2u)];
+        if (m == -INFINITY) continue;
+        const float c = expf(m - gm);
+        l += src[s * (D + 2u) + 1u] * c;
+        a += src[s * (D + 2u) + 2u + i] * c;
+    }
+    out[(size_t)h * D + i] = a / l;
+}
+
+__global__ void moe_add_kernel(float *x, const float *update, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += update[i];
+}
+
+// x += sum_r probs[r] * rows[r], r ascending from zero (qwen.rs:894-899), then the residual add.
+__global__ void moe_mix_add_kernel(float *x, const float *rows, const float *probs, uint32_t active, uint32_t n) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float r = 0.0f;
+    for (uint32_t e = 0; e < active; ++e) r += probs[e] * rows[(size_t)e * n + i];
+    x[i] += r;
+}
+
+// End of a token: with logits, the first index of their maximum becomes `next` (non-finite logits raise
+// the error word, as Model::step refuses them, engine/hybrid/mod.rs:990); the cache grows by one row.
+__global__ void __launch_bounds__(1024) moe_finish_kernel(MoeState *st, const float *logits, uint32_t vocab) {
+    __shared__ float bv[32];
+    __shared__ uint32_t bi[32];
+    __shared__ int bad_any;
+    if (logits) {
+        float best = -INFINITY;
+        uint32_t idx = 0xffffffffu;
+        int bad = 0;
+        for (uint32_t i = threadIdx.x; i < vocab; i += 1024u) {
+            const float v = logits[i];
+            bad |= !isfinite(v);
+            if (idx == 0xffffffffu || v > best) best = v, idx = i;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (oi != 0xffffffffu && (idx == 0xffffffffu || ov > best || (ov == best && oi < idx))) best = ov, idx = oi;
+        }
+        bad = __syncthreads_or(bad);
+        if ((threadIdx.x & 31u) == 0) bv[threadIdx.x >> 5] = best, bi[threadIdx.x >> 5] = idx;
+        if (threadIdx.x == 0) bad_any = bad;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (uint32_t w = 1; w < 32u; ++w)
+                if (bi[w] != 0xffffffffu && (idx == 0xffffffffu || bv[w] > best || (bv[w] == best && bi[w] < idx)))
+                    best = bv[w], idx = bi[w];
+            st->next = idx;
+            if (bad_any) st->error |= 2u;
+        }
+    }
+    if (threadIdx.x == 0) st->position += 1u;
+}
+
+}  // namespace
+
+struct MoeModel {
+    stark_b200_moe_config cfg{};
+    int device = -1;
+    cudaStream_t stream = nullptr;
+    std::vector<const QMatrix *> qkv, o, gate, up, down;
+    const QMatrix *output = nullptr;
+    // owned device memory
+    uint8_t *token_table = nullptr;
+    float *norms = nullptr;   // [layers][2 * hidden + 2 * head_dim] then final [hidden]
+    float *router = nullptr;  // [layers][experts * hidden]
+    float *keys = nullptr, *values = nullptr;  // [layers][context][kv_heads * head_dim]
+    float *work = nullptr;    // activations, see carve()
+    uint32_t *ids = nullptr;  // [layers][active]
+    MoeState *state = nullptr;
+    std::vector<uint8_t> have;  // which tensors were set
+    // activations carved out of `work`
+    float *x, *n, *qkv_out, *att, *part, *update, *scores, *probs, *gate_out, *up_out, *expert_out, *logits;
+    cudaGraphExec_t graph[2] = {nullptr, nullptr};  // [0] cache only, [1] with logits
+    bool warmed[2] = {false, false};
+    uint32_t nodes = 0;
+    uint32_t position = 0;  // host mirror of the device position
+    bool poisoned = false;
+
+    size_t norm_stride() const { return 2u * (size_t)cfg.hidden + 2u * cfg.head_dim; }
+    float *norm(uint32_t kind, uint32_t layer) const {
+        if (kind == STARK_B200_MOE_TENSOR_FINAL_NORM) return norms + (size_t)cfg.layers * norm_stride();
+        float *base = norms + (size_t)layer * norm_stride();
+        if (kind == STARK_B200_MOE_TENSOR_ATTN_NORM) return base;
+        if (kind == STARK_B200_MOE_TENSOR_FFN_NORM) return base + cfg.hidden;
+        if (kind == STARK_B200_MOE_TENSOR_Q_NORM) return base + 2u * (size_t)cfg.hidden;
+        return base + 2u * (size_t)cfg.hidden + cfg.head_dim;
+    }
+    size_t kv_layer() const { return (size_t)cfg.context_tokens * cfg.kv_heads * cfg.head_dim; }
+    size_t have_index(uint32_t group, uint32_t kind, uint32_t layer) const {
+        return ((size_t)group * 8u + kind) * cfg.layers + layer;
+    }
+    bool complete() const {
+        for (uint32_t l = 0; l < cfg.layers; ++l) {
+            for (uint32_t k = 0; k <= STARK_B200_MOE_MAT_DOWN; ++k)
+                if (!have[have_index(0, k, l)]) return false;
+            for (uint32_t k : {STARK_B200_MOE_TENSOR_ATTN_NORM, STARK_B200_MOE_TENSOR_FFN_NORM,
+                               STARK_B200_MOE_TENSOR_Q_NORM, STARK_B200_MOE_TENSOR_K_NORM, STARK_B200_MOE_TENSOR_ROUTER})
+                if (!have[have_index(1, k, l)]) return false;
+        }
+        return have[have_index(0, STARK_B200_MOE_MAT_OUTPUT, 0)] && have[have_index(1, STARK_B200_MOE_TENSOR_FINAL_NORM, 0)] &&
+               have[have_index(1, STARK_B200_MOE_TENSOR_TOKEN_TABLE, 0)];
+    }
+};
+
+namespace {
+
+stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
+    const auto &c = m->cfg;
+    const uint32_t H = c.hidden, D = c.head_dim, QH = c.q_heads, KV = c.kv_heads, A = c.active_experts;
+    const uint32_t I = c.expert_intermediate;
+    const float scale = 1.0f / sqrtf((float)D);
+    moe_embed_kernel<<<1, 256, 0, s>>>(m->state, m->token_table, m->x, H, c.vocab, c.context_tokens);
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        float *keys = m->keys + (size_t)l * m->kv_layer(), *values = m->values + (size_t)l * m->kv_layer();
+        uint32_t *ids = m->ids + (size_t)l * A;
+        moe_rmsnorm_kernel<<<1, 1024, 0, s>>>(m->x, m->norm(STARK_B200_MOE_TENSOR_ATTN_NORM, l), m->n, H, c.rms_eps);
+        SB_TRY(qmv_rows_launch(m->qkv[l], m->n, 0, m->qkv_out, 1, nullptr, STARK_B200_F32, s));
+        moe_heads_kernel<<<QH + 2u * KV, D, 0, s>>>(m->state, m->qkv_out, m->norm(STARK_B200_MOE_TENSOR_Q_NORM, l),
+                                                   m->norm(STARK_B200_MOE_TENSOR_K_NORM, l), keys, values, QH, KV, D,
+                                                   c.rms_eps, c.rope_theta, c.context_tokens);
+        moe_attention_kernel<<<dim3(QH, kAttnSplits), kAttnWarps * 32, 0, s>>>(m->state, m->qkv_out, keys, values, m->part,
+                                                                             QH, KV, scale, c.context_tokens);
+        moe_attention_merge_kernel<<<QH, 128, 0, s>>>(m->part, m->att);
+        SB_TRY(qmv_rows_launch(m->o[l], m->att, 0, m->update, 1, nullptr, STARK_B200_F32, s));
+        moe_add_kernel<<<(H + 255u) / 256u, 256, 0, s>>>(m->x, m->update, H);
+        moe_rmsnorm_kernel<<<1, 1024, 0, s>>>(m->x, m->norm(STARK_B200_MOE_TENSOR_FFN_NORM, l), m->n, H, c.rms_eps);
+        SB_TRY(dense_matvec_f32_launch(m->router + (size_t)l * c.experts * H, m->n, m->scores, c.experts, H, s));
+        SB_TRY(moe_select_launch(m->scores, c.experts, A, ids, m->probs, s));
+        SB_TRY(qmv_rows_launch(m->gate[l], m->n, 0, m->gate_out, A, ids, STARK_B200_F32, s));
+        SB_TRY(qmv_rows_launch(m->up[l], m->n, 0, m->up_out, A, ids, STARK_B200_F32, s));
+        SB_TRY(silu_mul_f32_launch(m->gate_out, m->up_out, A * I, s));
+        SB_TRY(qmv_rows_launch(m->down[l], m->gate_out, I, m->expert_out, A, ids, STARK_B200_F32, s));
+        moe_mix_add_kernel<<<(H + 255u) / 256u, 256, 0, s>>>(m->x, m->expert_out, m->probs, A, H);
+    }
+    if (want_logits) {
+        moe_rmsnorm_kernel<<<1, 1024, 0, s>>>(m->x, m->norm(STARK_B200_MOE_TENSOR_FINAL_NORM, 0), m->n, H, c.rms_eps);
+        SB_TRY(qmv_rows_launch(m->output, m->n, 0, m->logits, 1, nullptr, STARK_B200_F32, s));
+    }
+    moe_finish_kernel<<<1, 1024, 0, s>>>(m->state, want_logits ? m->logits : nullptr, c.vocab);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+// One token through the graph of its kind; the first token of each kind runs eagerly (kernels opt into
+// their shared-memory sizes on first use, which a capture must not contain) and the graph is captured
+// from the second.
+stark_b200_status moe_token(MoeModel *m, bool want_logits) {
+    const int k = want_logits ? 1 : 0;
+    if (!m->warmed[k]) {
+        m->warmed[k] = true;
+        return moe_issue(m, want_logits, m->stream);
+    }
+    if (!m->graph[k]) {
+        cudaGraph_t g = nullptr;
+        SB_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+        const stark_b200_status st = moe_issue(m, want_logits, m->stream);
+        const cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+        if (st != STARK_B200_OK || e != cudaSuccess) {
+            if (g) cudaGraphDestroy(g);
+            return st != STARK_B200_OK ? st : cuda_status(e);
+        }
+        size_t count = 0;
+        cudaGraphGetNodes(g, nullptr, &count);
+        if (want_logits) m->nodes = (uint32_t)count;
+        const cudaError_t ie = cudaGraphInstantiate(&m->graph[k], g, 0);
+        cudaGraphDestroy(g);
+        SB_CUDA(ie);
+    }
+    SB_CUDA(cudaGraphLaunch(m->graph[k], m->stream));
+    return STARK_B200_OK;
+}
+
+stark_b200_status moe_set_input(MoeModel *m, uint32_t token, uint32_t chain) {
+    const uint32_t words[2] = {token, chain};
+    SB_CUDA(cudaMemcpyAsync(m->state, words, sizeof(words), cudaMemcpyHostToDevice, m->stream));
+    return STARK_B200_OK;
+}
+
+stark_b200_status moe_check(MoeModel *m) {  // after a synchronize: the device error word
+    MoeState st{};
+    SB_CUDA(cudaMemcpy(&st, m->state, sizeof(st), cudaMemcpyDeviceToHost));
+    if (st.error) {
+        m->poisoned = true;
+        return (st.error & 1u) ? STARK_B200_INVALID_ARGUMENT
+                               : ((st.error & 4u) ? STARK_B200_CONTEXT_LIMIT : STARK_B200_DEVICE_FAILURE);
+    }
+    return STARK_B200_OK;
+}
+
+stark_b200_status moe_reset(MoeModel *m) {
+    SB_CUDA(cudaMemsetAsync(m->state, 0, sizeof(MoeState), m->stream));
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    m->position = 0;
+    m->poisoned = false;
+    return STARK_B200_OK;
+}
+
+struct DeviceScope {
+    int previous = -1;
+    explicit DeviceScope(int device) {
+        cudaGetDevice(&previous);
+        if (previous != device) cudaSetDevice(device);
+    }
+    ~DeviceScope() { cudaSetDevice(previous); }
+};
+
+void moe_free(MoeModel *m) {
+    for (auto &g : m->graph)
+        if (g) cudaGraphExecDestroy(g);
+    cudaFree(m->token_table), cudaFree(m->norms), cudaFree(m->router), cudaFree(m->keys), cudaFree(m->values);
+    cudaFree(m->work), cudaFree(m->ids), cudaFree(m->state);
+    if (m->stream) cudaStreamDestroy(m->stream);
+    delete m;
+}
+
+}  // namespace
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+stark_b200_status stark_b200_moe_model_create(const stark_b200_moe_config *config, stark_b200_moe_model **out_model) {
+    if (!config || !out_model) return STARK_B200_INVALID_ARGUMENT;
+    if (config->struct_size != sizeof(stark_b200_moe_config)) return STARK_B200_ABI_MISMATCH;
+    const auto &c = *config;
+    if (c.vocab == 0 || c.layers == 0 || c.hidden == 0 || c.hidden % 256u || c.head_dim != 128u || c.q_heads == 0 ||
+        c.kv_heads == 0 || c.q_heads % c.kv_heads || c.experts == 0 || c.experts > 1024u || c.active_experts == 0 ||
+        c.active_experts > 32u || c.active_experts > c.experts || c.expert_intermediate == 0 ||
+        c.expert_intermediate % 256u || c.context_tokens == 0 || !(c.rms_eps > 0.0f) || !std::isfinite(c.rms_eps) ||
+        !(c.rope_theta > 0.0f) || !std::isfinite(c.rope_theta))
+        return STARK_B200_INVALID_ARGUMENT;
+    if (!device_context()) return STARK_B200_OUT_OF_MEMORY;
+    MoeModel *m = new MoeModel();
+    m->cfg = c;
+    cudaGetDevice(&m->device);
+    m->qkv.assign(c.layers, nullptr), m->o.assign(c.layers, nullptr), m->gate.assign(c.layers, nullptr);
+    m->up.assign(c.layers, nullptr), m->down.assign(c.layers, nullptr);
+    m->have.assign(2u * 8u * c.layers, 0);
+    const size_t QD = (size_t)c.q_heads * c.head_dim, KD = (size_t)c.kv_heads * c.head_dim;
+    const size_t AI = (size_t)c.active_experts * c.expert_intermediate;
+    const size_t sizes[] = {c.hidden, c.hidden, QD + 2u * KD, QD, (size_t)c.q_heads * kAttnSplits * (c.head_dim + 2u),
+                            c.hidden, c.experts, c.active_experts, AI, AI, (size_t)c.active_experts * c.hidden, c.vocab};
+    size_t total = 0;
+    for (size_t v : sizes) total += (v + 63u) / 64u * 64u;
+    bool ok = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->token_table, (size_t)c.vocab * (c.hidden / 32u) * 34u) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->norms, ((size_t)c.layers * m->norm_stride() + c.hidden) * 4u) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->router, (size_t)c.layers * c.experts * c.hidden * 4u) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->keys, (size_t)c.layers * m->kv_layer() * 4u) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->values, (size_t)c.layers * m->kv_layer() * 4u) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->work, total * 4u) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->ids, (size_t)c.layers * c.active_experts * 4u) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->state, sizeof(MoeState)) == cudaSuccess;
+    if (!ok) {
+        cudaGetLastError();
+        moe_free(m);
+        return STARK_B200_OUT_OF_MEMORY;
+    }
+    float **slots[] = {&m->x, &m->n, &m->qkv_out, &m->att, &m->part, &m->update, &m->scores, &m->probs,
+                       &m->gate_out, &m->up_out, &m->expert_out, &m->logits};
+    float *at = m->work;
+    for (size_t i = 0; i < sizeof(sizes) / sizeof(sizes[0]); ++i) {
+        *slots[i] = at;
+        at += (sizes[i] + 63u) / 64u * 64u;
+    }
+    cudaMemset(m->ids, 0, (size_t)c.layers * c.active_experts * 4u);
+    if (moe_reset(m) != STARK_B200_OK) {
+        moe_free(m);
+        return STARK_B200_DEVICE_FAILURE;
+    }
+    *out_model = reinterpret_cast<stark_b200_moe_model *>(m);
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_moe_model_set_matrix(stark_b200_moe_model *model, uint32_t kind, uint32_t layer,
+                                                  const stark_b200_qmatrix *matrix) {
+    MoeModel *m = reinterpret_cast<MoeModel *>(model);
+    const QMatrix *q = reinterpret_cast<const QMatrix *>(matrix);
+    if (!m || !q || kind > STARK_B200_MOE_MAT_OUTPUT) return STARK_B200_INVALID_ARGUMENT;
+    if (kind == STARK_B200_MOE_MAT_OUTPUT) layer = 0;
+    if (layer >= m->cfg.layers || q->device != m->device || !qmv_rows_supports(q)) return STARK_B200_INVALID_ARGUMENT;
+    const auto &c = m->cfg;
+    const uint32_t QD = c.q_heads * c.head_dim, KD = c.kv_heads * c.head_dim;
+    const bool q8 = q->format == kFmtQ8_0 || q->format == kFmtQ8_0T;
+    const bool q4 = q->format == kFmtQ4_K || q->format == kFmtQ4_KRaw;
+    const uint32_t banks = q->experts > 1u ? q->experts : 1u;
+    bool fits = false;
+    switch (kind) {
+        case STARK_B200_MOE_MAT_QKV: fits = q8 && banks == 1u && q->rows == QD + 2u * KD && q->columns == c.hidden; break;
+        case STARK_B200_MOE_MAT_O: fits = q8 && banks == 1u && q->rows == c.hidden && q->columns == QD; break;
+        case STARK_B200_MOE_MAT_GATE:
+        case STARK_B200_MOE_MAT_UP:
+            fits = q4 && banks == c.experts && q->rows == c.expert_intermediate && q->columns == c.hidden;
+            break;
+        case STARK_B200_MOE_MAT_DOWN:
+            fits = q4 && banks == c.experts && q->rows == c.hidden && q->columns == c.expert_intermediate;
+            break;
+        default: fits = q8 && banks == 1u && q->rows == c.vocab && q->columns == c.hidden; break;
+    }
+    if (!fits) return STARK_B200_INVALID_ARGUMENT;
+    switch (kind) {
+        case STARK_B200_MOE_MAT_QKV: m->qkv[layer] = q; break;
+        case STARK_B200_MOE_MAT_O: m->o[layer] = q; break;
+        case STARK_B200_MOE_MAT_GATE: m->gate[layer] = q; break;
+        case STARK_B200_MOE_MAT_UP: m->up[layer] = q; break;
+        case STARK_B200_MOE_MAT_DOWN: m->down[layer] = q; break;
+        default: m->output = q; break;
+    }
+    m->have[m->have_index(0, kind, layer)] = 1;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_moe_model_set_tensor(stark_b200_moe_model *model, uint32_t kind, uint32_t layer,
+                                                  const void *host_data, size_t bytes) {
+    MoeModel *m = reinterpret_cast<MoeModel *>(model);
+    if (!m || !host_data || kind > STARK_B200_MOE_TENSOR_TOKEN_TABLE) return STARK_B200_INVALID_ARGUMENT;
+    const auto &c = m->cfg;
+    if (kind == STARK_B200_MOE_TENSOR_FINAL_NORM || kind == STARK_B200_MOE_TENSOR_TOKEN_TABLE) layer = 0;
+    if (layer >= c.layers) return STARK_B200_INVALID_ARGUMENT;
+    DeviceScope scope(m->device);
+    void *dst;
+    size_t want;
+    if (kind == STARK_B200_MOE_TENSOR_TOKEN_TABLE) {
+        dst = m->token_table, want = (size_t)c.vocab * (c.hidden / 32u) * 34u;
+    } else if (kind == STARK_B200_MOE_TENSOR_ROUTER) {
+        dst = m->router + (size_t)layer * c.experts * c.hidden, want = (size_t)c.experts * c.hidden * 4u;
+    } else {
+        dst = m->norm(kind, layer);
+        want = (kind == STARK_B200_MOE_TENSOR_Q_NORM || kind == STARK_B200_MOE_TENSOR_K_NORM ? c.head_dim : c.hidden) * 4u;
+    }
+    if (bytes != want) return STARK_B200_INVALID_ARGUMENT;
+    if (kind != STARK_B200_MOE_TENSOR_TOKEN_TABLE) {  // rms_norm and the router refuse non-finite weights
+        const float *v = static_cast<const float *>(host_data);
+        for (size_t i = 0; i < bytes / 4u; ++i)
+            if (!std::isfinite(v[i])) return STARK_B200_INVALID_ARGUMENT;
+    }
+    SB_CUDA(cudaMemcpy(dst, host_data, bytes, cudaMemcpyHostToDevice));
+    m->have[m->have_index(1, kind, layer)] = 1;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_moe_model_reset(stark_b200_moe_model *model) {
+    MoeModel *m = reinterpret_cast<MoeModel *>(model);
+    if (!m) return STARK_B200_INVALID_ARGUMENT;
+    DeviceScope scope(m->device);
+    return moe_reset(m);
+}
+
+static stark_b200_status moe_ready(MoeModel *m, uint32_t tokens) {
+    if (!m) return STARK_B200_INVALID_ARGUMENT;
+    if (!m->complete()) return STARK_B200_INVALID_STATE;
+    if (m->poisoned) return STARK_B200_RELOAD_REQUIRED;
+    if ((uint64_t)m->position + tokens > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
+    return STARK_B200_OK;
+}
+
+// Any failure of a token resets the model, as hybrid::Model does (engine/hybrid/mod.rs:990).
+static stark_b200_status moe_fail(MoeModel *m, stark_b200_status st) {
+    cudaStreamSynchronize(m->stream);
+    moe_reset(m);
+    return st;
+}
+
+stark_b200_status stark_b200_moe_model_ingest(stark_b200_moe_model *model, const uint32_t *tokens, uint32_t count) {
+    MoeModel *m = reinterpret_cast<MoeModel *>(model);
+    SB_TRY(moe_ready(m, count));
+    if (count && !tokens) return STARK_B200_INVALID_ARGUMENT;
+    for (uint32_t i = 0; i < count; ++i)
+        if (tokens[i] >= m->cfg.vocab) return STARK_B200_INVALID_ARGUMENT;
+    DeviceScope scope(m->device);
+    for (uint32_t i = 0; i < count; ++i) {
+        stark_b200_status st = moe_set_input(m, tokens[i], 0);
+        if (st == STARK_B200_OK) st = moe_token(m, false);
+        if (st != STARK_B200_OK) return moe_fail(m, st);
+    }
+    if (cudaStreamSynchronize(m->stream) != cudaSuccess) return moe_fail(m, STARK_B200_DEVICE_FAILURE);
+    m->position += count;
+    const stark_b200_status st = moe_check(m);
+    return st == STARK_B200_OK ? st : moe_fail(m, st);
+}
+
+stark_b200_status stark_b200_moe_model_step(stark_b200_moe_model *model, uint32_t token, float *logits_host,
+                                            size_t count) {
+    MoeModel *m = reinterpret_cast<MoeModel *>(model);
+    SB_TRY(moe_ready(m, 1));
+    if (token >= m->cfg.vocab || (logits_host && count != m->cfg.vocab)) return STARK_B200_INVALID_ARGUMENT;
+    DeviceScope scope(m->device);
+    stark_b200_status st = moe_set_input(m, token, 0);
+    if (st == STARK_B200_OK) st = moe_token(m, true);
+    if (st != STARK_B200_OK) return moe_fail(m, st);
+    if (logits_host &&
+        cudaMemcpyAsync(logits_host, m->logits, (size_t)m->cfg.vocab * 4u, cudaMemcpyDeviceToHost, m->stream) != cudaSuccess)
+        return moe_fail(m, STARK_B200_DEVICE_FAILURE);
+    if (cudaStreamSynchronize(m->stream) != cudaSuccess) return moe_fail(m, STARK_B200_DEVICE_FAILURE);
+    m->position += 1;
+    st = moe_check(m);
+    return st == STARK_B200_OK ? st : moe_fail(m, st);
+}
+
+stark_b200_status stark_b200_moe_model_generate_greedy(stark_b200_moe_model *model, uint32_t first, uint32_t steps,
+                                                       uint32_t *out_tokens) {
+    MoeModel *m = reinterpret_cast<MoeModel *>(model);
+    SB_TRY(moe_ready(m, steps));
+    if (steps == 0 || !out_tokens || first >= m->cfg.vocab) return STARK_B200_INVALID_ARGUMENT;
+    DeviceScope scope(m->device);
+    uint32_t *picks = nullptr;  // the device-side record of every step's pick
+    SB_CUDA(cudaMalloc(&picks, (size_t)steps * 4u));
+    stark_b200_status st = STARK_B200_OK;
+    for (uint32_t i = 0; i < steps && st == STARK_B200_OK; ++i) {
+        st = moe_set_input(m, first, i == 0 ? 0u : 1u);
+        if (st == STARK_B200_OK) st = moe_token(m, true);
+        if (st == STARK_B200_OK &&
+            cudaMemcpyAsync(picks + i, &m->state->next, 4u, cudaMemcpyDeviceToDevice, m->stream) != cudaSuccess)
+            st = STARK_B200_DEVICE_FAILURE;
+    }
+    if (st == STARK_B200_OK && cudaMemcpyAsync(out_tokens, picks, (size_t)steps * 4u, cudaMemcpyDeviceToHost, m->stream) !=
+                                   cudaSuccess)
+        st = STARK_B200_DEVICE_FAILURE;
+    if (st == STARK_B200_OK && cudaStreamSynchronize(m->stream) != cudaSuccess) st = STARK_B200_DEVICE_FAILURE;
+    cudaFree(picks);
+    if (st != STARK_B200_OK) return moe_fail(m, st);
+    m->position += steps;
+    st = moe_check(m);
+    return st == STARK_B200_OK ? st : moe_fail(m, st);
+}
+
+stark_b200_status stark_b200_moe_model_last_experts(stark_b200_moe_model *model, uint32_t *ids_host, size_t count) {
+    MoeModel *m = reinterpret_cast<MoeModel *>(model);
+    if (!m || !ids_host || count != (size_t)m->cfg.layers * m->cfg.active_experts) return STARK_B200_INVALID_ARGUMENT;
+    DeviceScope scope(m->device);
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    SB_CUDA(cudaMemcpy(ids_host, m->ids, count * 4u, cudaMemcpyDeviceToHost));
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_moe_model_position(const stark_b200_moe_model *model, uint32_t *out_position) {
+    const MoeModel *m = reinterpret_cast<const MoeModel *>(model);
+    if (!m || !out_position) return STARK_B200_INVALID_ARGUMENT;
+    *out_position = m->position;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_moe_model_launches_per_token(const stark_b200_moe_model *model, uint32_t *out_launches) {
+    const MoeModel *m = reinterpret_cast<const MoeModel *>(model);
+    if (!m || !out_launches) return STARK_B200_INVALID_ARGUMENT;
+    *out_launches = m->nodes ? m->nodes : 3u + 15u * m->cfg.layers;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_moe_model_stream(const stark_b200_moe_model *model, void **out_stream) {
+    const MoeModel *m = reinterpret_cast<const MoeModel *>(model);
+    if (!m || !out_stream) return STARK_B200_INVALID_ARGUMENT;
+    *out_stream = m->stream;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_moe_model_destroy(stark_b200_moe_model **model) {
+    if (!model || !*model) return STARK_B200_INVALID_ARGUMENT;
+    MoeModel *m = reinterpret_cast<MoeModel *>(*model);
+    {
+        DeviceScope scope(m->device);
+        cudaStreamSynchronize(m->stream);
+        moe_free(m);
+    }
+    *model = nullptr;
+    return STARK_B200_OK;
+}
+
+}  // extern "C"

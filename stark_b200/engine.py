@@ -316,3 +316,129 @@ def reusable_prefix_rows(previous_prompt_len: int, common_prefix: int, new_promp
     retained = ((previous_prompt_len - 1) // chunk) * chunk
     limit = ((new_prompt_len - 1) // chunk) * chunk
     return (min(common_prefix, retained, limit) // chunk) * chunk
+
+
+class MoEModel:
+    """A routed-expert decoder on the conventions of the reference's hybrid host path (f32 activations and
+    logits, GGUF Q8_0 attention / token table / output, Q4_K expert banks), with the surface of
+    ``hybrid::Model`` (crates/stark-engine/src/engine/hybrid/mod.rs:347,863,897,990): ``load``, ``reset``,
+    ``ingest``, ``step -> logits``.  Any failing call leaves the model reset, as the reference does."""
+
+    def __init__(self, cfg: dict, context_tokens: int):
+        self.cfg = dict(cfg)
+        self.context_tokens = int(context_tokens)
+        self._h = C.c_void_p()
+        self._matrices = []  # the handle borrows them
+        c = _lib.MoeConfig(C.sizeof(_lib.MoeConfig), cfg["vocab"], cfg["hidden"], cfg["layers"], cfg["q_heads"],
+                           cfg["kv_heads"], cfg["head_dim"], cfg["experts"], cfg["active"], cfg["inter"],
+                           self.context_tokens, cfg["eps"], cfg["rope_theta"])
+        check(_lib.load().stark_b200_moe_model_create(C.byref(c), C.byref(self._h)), "moe_model_create")
+
+    def _matrix(self, kind: int, layer: int, blocks: np.ndarray, ggml_kind: int, rows: int, columns: int,
+                experts: int = 0):
+        from .ops import QMatrix
+        q = QMatrix.from_gguf(blocks, ggml_kind, rows, columns, experts)
+        self._matrices.append(q)
+        check(_lib.load().stark_b200_moe_model_set_matrix(self._h, kind, layer, q._h), "moe_model_set_matrix")
+
+    def _tensor(self, kind: int, layer: int, a: np.ndarray):
+        a = np.ascontiguousarray(a)
+        check(_lib.load().stark_b200_moe_model_set_tensor(self._h, kind, layer, a.ctypes.data, a.nbytes),
+              "moe_model_set_tensor")
+
+    def set_layer(self, layer: int, w: dict) -> None:
+        """One layer's tensors (``stark_b200.synthetic.moe_layer_weights`` layout); uploads as it goes, so a
+        large model can be streamed layer by layer."""
+        c, L = self.cfg, _lib
+        qd, kd = c["q_heads"] * c["head_dim"], c["kv_heads"] * c["head_dim"]
+        Q8_0, Q4_K = 8, 12
+        self._matrix(L.MOE_MAT_QKV, layer, w["qkv"], Q8_0, qd + 2 * kd, c["hidden"])
+        self._matrix(L.MOE_MAT_O, layer, w["o"], Q8_0, c["hidden"], qd)
+        self._matrix(L.MOE_MAT_GATE, layer, w["gate"], Q4_K, c["inter"], c["hidden"], c["experts"])
+        self._matrix(L.MOE_MAT_UP, layer, w["up"], Q4_K, c["inter"], c["hidden"], c["experts"])
+        self._matrix(L.MOE_MAT_DOWN, layer, w["down"], Q4_K, c["hidden"], c["inter"], c["experts"])
+        self._tensor(L.MOE_ROUTER, layer, np.asarray(w["router"], np.float32))
+        for kind, name in ((L.MOE_ATTN_NORM, "attn_norm"), (L.MOE_FFN_NORM, "ffn_norm"), (L.MOE_Q_NORM, "q_norm"),
+                           (L.MOE_K_NORM, "k_norm")):
+            self._tensor(kind, layer, np.asarray(w[name], np.float32))
+
+    def set_globals(self, token_table: np.ndarray, output: np.ndarray, final_norm: np.ndarray) -> None:
+        c, L = self.cfg, _lib
+        self._tensor(L.MOE_TOKEN_TABLE, 0, np.asarray(token_table, np.uint8))
+        self._matrix(L.MOE_MAT_OUTPUT, 0, output, 8, c["vocab"], c["hidden"])
+        self._tensor(L.MOE_FINAL_NORM, 0, np.asarray(final_norm, np.float32))
+
+    @classmethod
+    def load(cls, cfg: dict, weights: dict, context_tokens: int) -> "MoEModel":
+        m = cls(cfg, context_tokens)
+        m.set_globals(weights["token_table"], weights["output"], weights["final_norm"])
+        for layer, w in enumerate(weights["layers"]):
+            m.set_layer(layer, w)
+        return m
+
+    def reset(self) -> None:
+        check(_lib.load().stark_b200_moe_model_reset(self._h), "moe_model_reset")
+
+    def ingest(self, tokens) -> None:
+        t = np.ascontiguousarray(tokens, np.uint32).reshape(-1)
+        check(_lib.load().stark_b200_moe_model_ingest(self._h, t.ctypes.data, t.size), "moe_model_ingest")
+
+    def step(self, token: int, want_logits: bool = True):
+        out = np.empty(self.cfg["vocab"], np.float32) if want_logits else None
+        check(_lib.load().stark_b200_moe_model_step(self._h, int(token), out.ctypes.data if want_logits else None,
+                                                    self.cfg["vocab"] if want_logits else 0), "moe_model_step")
+        return out
+
+    def generate_greedy(self, first: int, steps: int) -> np.ndarray:
+        out = np.empty(steps, np.uint32)
+        check(_lib.load().stark_b200_moe_model_generate_greedy(self._h, int(first), steps, out.ctypes.data),
+              "moe_model_generate_greedy")
+        return out
+
+    def last_experts(self) -> np.ndarray:
+        out = np.empty((self.cfg["layers"], self.cfg["active"]), np.uint32)
+        check(_lib.load().stark_b200_moe_model_last_experts(self._h, out.ctypes.data, out.size), "moe_model_last_experts")
+        return out
+
+    @property
+    def position(self) -> int:
+        p = C.c_uint32(0)
+        check(_lib.load().stark_b200_moe_model_position(self._h, C.byref(p)), "moe_model_position")
+        return p.value
+
+    @property
+    def launches_per_token(self) -> int:
+        p = C.c_uint32(0)
+        check(_lib.load().stark_b200_moe_model_launches_per_token(self._h, C.byref(p)), "moe_model_launches_per_token")
+        return p.value
+
+    @property
+    def stream(self) -> int:
+        p = C.c_void_p()
+        check(_lib.load().stark_b200_moe_model_stream(self._h, C.byref(p)), "moe_model_stream")
+        return p.value or 0
+
+    def weight_bytes_per_token(self) -> int:
+        """Bytes of weights one decode token reads: attention and output matrices whole, the active experts
+        of each bank, the router, one row of the token table."""
+        c = self.cfg
+        qd, kd = c["q_heads"] * c["head_dim"], c["kv_heads"] * c["head_dim"]
+        q8 = lambda n: n // 32 * 34
+        q4 = lambda n: n // 256 * 144
+        per_layer = q8((qd + 2 * kd) * c["hidden"]) + q8(c["hidden"] * qd) + 4 * c["experts"] * c["hidden"] \
+            + 3 * c["active"] * q4(c["inter"] * c["hidden"])
+        return c["layers"] * per_layer + q8(c["vocab"] * c["hidden"]) + q8(c["hidden"])
+
+    def close(self) -> None:
+        if self._h:
+            _lib.load().stark_b200_moe_model_destroy(C.byref(self._h))
+            self._h = C.c_void_p()
+        for q in self._matrices:
+            q.destroy()
+        self._matrices = []
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -118,3 +118,40 @@ def affine8_matrix(rng: np.random.Generator, rows: int, columns: int, scale_lo: 
     scales = f32_to_bf16(rng.uniform(scale_lo, scale_hi, size=(rows, columns // group)).astype(np.float32))
     biases = f32_to_bf16(-128.0 * bf16_to_f32(scales))
     return dict(codes=codes, scales=scales, biases=biases, n=rows, k=columns, bits=8, group=group)
+
+
+# ----------------------------------------------------------------------------- routed-expert decoder
+
+MOE_CONFIGS = {
+    # the Qwen3-30B-A3B shape: 128 experts, 8 active, expert intermediate 768
+    "qwen3-30b-a3b": dict(layers=48, hidden=2048, q_heads=32, kv_heads=4, head_dim=128, experts=128, active=8,
+                          inter=768, vocab=151936, eps=1e-6, rope_theta=1e6),
+    "moe-tiny": dict(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=128, experts=8, active=2, inter=256,
+                     vocab=512, eps=1e-6, rope_theta=1e6),
+    "moe-small": dict(layers=3, hidden=512, q_heads=8, kv_heads=2, head_dim=128, experts=16, active=4, inter=256,
+                      vocab=2048, eps=1e-6, rope_theta=1e6),
+}
+
+
+def moe_layer_weights(cfg: dict, rng: np.random.Generator) -> dict:
+    """One layer: Q8_0 [q; k; v] and o, f32 router ~ N(0, 1/hidden) (unit-variance router logits on a
+    normalised input), Q4_K gate / up / down banks, f32 norm weights near 1."""
+    H, D, E, I = cfg["hidden"], cfg["head_dim"], cfg["experts"], cfg["inter"]
+    qd, kd = cfg["q_heads"] * D, cfg["kv_heads"] * D
+    near_one = lambda n: (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    return dict(
+        qkv=q8_0_rows(rng, qd + 2 * kd, H, scale=3e-4), o=q8_0_rows(rng, H, qd, scale=3e-4),
+        router=(rng.standard_normal((E, H)) / np.sqrt(H)).astype(np.float32),
+        gate=q4_k_rows(rng, E * I, H, scale=4e-3), up=q4_k_rows(rng, E * I, H, scale=4e-3),
+        down=q4_k_rows(rng, E * H, I, scale=4e-3),
+        attn_norm=near_one(H), ffn_norm=near_one(H), q_norm=near_one(D), k_norm=near_one(D))
+
+
+def moe_weights(cfg: dict, seed: int = 0) -> dict:
+    """Random-init weights of a routed-expert decoder in GGUF blocks (Q8_0 attention / token table / output,
+    Q4_K experts)."""
+    rng = np.random.default_rng(seed)
+    return dict(token_table=q8_0_rows(rng, cfg["vocab"], cfg["hidden"], scale=3e-4),
+                output=q8_0_rows(rng, cfg["vocab"], cfg["hidden"], scale=3e-4),
+                final_norm=(1.0 + 0.1 * rng.standard_normal(cfg["hidden"])).astype(np.float32),
+                layers=[moe_layer_weights(cfg, rng) for _ in range(cfg["layers"])])
