@@ -440,15 +440,15 @@ typedef struct stark_b200_moe_config {
     float rms_eps, rope_theta;
 } stark_b200_moe_config;
 /* Matrices are borrowed qmatrix handles (they must outlive the model): QKV = Q8_0 rows [q; k; v]
- * ((q_heads + 2 kv_heads) * head_dim x hidden), O = Q8_0 hidden x q_heads*head_dim, GATE / UP = Q4_K banks
- * [experts, expert_intermediate, hidden], DOWN = Q4_K bank [experts, hidden, expert_intermediate], OUTPUT =
+ * ((q_heads + 2 kv_heads) * head_dim x hidden), O = Q8_0 hidden x q_heads*head_dim, GATE_UP = one Q4_K bank
+ * [2 * experts, expert_intermediate, hidden] (every expert's gate matrix, then every expert's up matrix: one
+ * launch serves both), DOWN = Q4_K bank [experts, hidden, expert_intermediate], OUTPUT =
  * Q8_0 vocab x hidden (layer ignored). */
 #define STARK_B200_MOE_MAT_QKV 0u
 #define STARK_B200_MOE_MAT_O 1u
-#define STARK_B200_MOE_MAT_GATE 2u
-#define STARK_B200_MOE_MAT_UP 3u
-#define STARK_B200_MOE_MAT_DOWN 4u
-#define STARK_B200_MOE_MAT_OUTPUT 5u
+#define STARK_B200_MOE_MAT_GATE_UP 2u
+#define STARK_B200_MOE_MAT_DOWN 3u
+#define STARK_B200_MOE_MAT_OUTPUT 4u
 /* Host tensors, copied: f32 vectors ATTN_NORM / FFN_NORM [hidden], Q_NORM / K_NORM [head_dim], FINAL_NORM
  * [hidden] (layer ignored), ROUTER f32 [experts, hidden]; TOKEN_TABLE = the Q8_0 blocks of the token
  * embedding [vocab, hidden] in the file's byte layout (layer ignored).  `bytes` must match exactly. */

@@ -52,7 +52,7 @@ class MoeConfig(C.Structure):
         ("rms_eps", C.c_float), ("rope_theta", C.c_float)]
 
 
-MOE_MAT_QKV, MOE_MAT_O, MOE_MAT_GATE, MOE_MAT_UP, MOE_MAT_DOWN, MOE_MAT_OUTPUT = range(6)
+MOE_MAT_QKV, MOE_MAT_O, MOE_MAT_GATE_UP, MOE_MAT_DOWN, MOE_MAT_OUTPUT = range(5)
 (MOE_ATTN_NORM, MOE_FFN_NORM, MOE_Q_NORM, MOE_K_NORM, MOE_FINAL_NORM, MOE_ROUTER, MOE_TOKEN_TABLE) = range(7)
 
 

@@ -35,7 +35,7 @@ struct MoeState {
     uint32_t error;     // sticky: 1 token out of range, 2 non-finite logits, 4 context exhausted
 };
 
-constexpr uint32_t kAttnSplits = 8, kAttnWarps = 8;
+constexpr uint32_t kAttnSplits = 16, kAttnWarps = 8;
 
 template <int THREADS>
 __device__ inline float block_sum(float v, float *scratch /* [32] */) {
@@ -138,21 +138,36 @@ __global__ void __launch_bounds__(kAttnWarps * 32) moe_attention_kernel(const Mo
     const float4 qv = reinterpret_cast<const float4 *>(q + (size_t)h * D)[lane];
     float m = -INFINITY, l = 0.0f;
     float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-    for (uint32_t t = lo + warp; t < hi; t += kAttnWarps) {
-        const float4 kv = reinterpret_cast<const float4 *>(keys + t * kv_row + begin)[lane];
-        float dot = qv.x * kv.x + qv.y * kv.y + qv.z * kv.z + qv.w * kv.w;
+    // four rows per trip: their loads and reductions are independent, only the softmax update is serial
+    for (uint32_t t0 = lo + warp; t0 < hi; t0 += 4u * kAttnWarps) {
+        float4 kv[4], vv[4];
+        float dot[4];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        const float s = dot * scale;
-        const float4 vv = reinterpret_cast<const float4 *>(values + t * kv_row + begin)[lane];
-        const float nm = fmaxf(m, s);
-        const float c = expf(m - nm), p = expf(s - nm);  // expf(-inf) = 0 on the first row
-        l = l * c + p;
-        acc.x = acc.x * c + p * vv.x;
-        acc.y = acc.y * c + p * vv.y;
-        acc.z = acc.z * c + p * vv.z;
-        acc.w = acc.w * c + p * vv.w;
-        m = nm;
+        for (uint32_t j = 0; j < 4u; ++j) {
+            const uint32_t t = min(t0 + j * kAttnWarps, hi - 1u);  // rows past the end repeat the last one, unused
+            kv[j] = reinterpret_cast<const float4 *>(keys + t * kv_row + begin)[lane];
+            vv[j] = reinterpret_cast<const float4 *>(values + t * kv_row + begin)[lane];
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; ++j) dot[j] = qv.x * kv[j].x + qv.y * kv[j].y + qv.z * kv[j].z + qv.w * kv[j].w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (uint32_t j = 0; j < 4u; ++j) dot[j] += __shfl_xor_sync(0xffffffffu, dot[j], o);
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 4u; ++j) {
+            if (t0 + j * kAttnWarps >= hi) break;
+            const float s = dot[j] * scale;
+            const float nm = fmaxf(m, s);
+            const float c = expf(m - nm), p = expf(s - nm);  // expf(-inf) = 0 on the first row
+            l = l * c + p;
+            acc.x = acc.x * c + p * vv[j].x;
+            acc.y = acc.y * c + p * vv[j].y;
+            acc.z = acc.z * c + p * vv[j].z;
+            acc.w = acc.w * c + p * vv[j].w;
+            m = nm;
+        }
     }
     if (lane == 0) sm[warp] = m, sl[warp] = l;
     sacc[warp][lane] = acc;
@@ -193,18 +208,94 @@ __global__ void __launch_bounds__(128) moe_attention_merge_kernel(const float *p
     out[(size_t)h * D + i] = a / l;
 }
 
-__global__ void moe_add_kernel(float *x, const float *update, uint32_t n) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) x[i] += update[i];
+// Router scores (one CTA per expert: scores[e] = w[e] . x, f32) and, in the CTA that finishes last, the
+// selection: top-k of the scores (value descending, index ascending), softmax over the selected scores
+// (qwen.rs:872-874, math.rs:36-66).  ids[0, active) are the experts in selection order; ids[active, 2 active)
+// the same plus `experts`, which addresses the up half of a fused [gate; up] bank.
+__global__ void __launch_bounds__(256) moe_router_select_kernel(const float *w, const float *x, float *scores,
+                                                                uint32_t hidden, uint32_t experts, uint32_t active,
+                                                                uint32_t *ids, float *probs, uint32_t *arrivals) {
+    __shared__ float scratch[32];
+    __shared__ float sv[1024];
+    __shared__ bool last;
+    const uint32_t e = blockIdx.x;
+    const float4 *row = reinterpret_cast<const float4 *>(w + (size_t)e * hidden);
+    const float4 *xv = reinterpret_cast<const float4 *>(x);
+    float s = 0.0f;
+    for (uint32_t i = threadIdx.x; i < hidden / 4u; i += 256u) {
+        const float4 a = row[i], b = xv[i];
+        s += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+    }
+    s = block_sum<256>(s, scratch);
+    if (threadIdx.x == 0) {
+        scores[e] = s;
+        __threadfence();
+        last = atomicAdd(arrivals, 1u) == gridDim.x - 1u;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    for (uint32_t i = threadIdx.x; i < experts; i += 256u) sv[i] = __ldcg(scores + i);
+    if (threadIdx.x == 0) *arrivals = 0;  // ready for the next launch
+    __syncthreads();
+    if (threadIdx.x >= 32u) return;
+    const uint32_t lane = threadIdx.x;
+    uint32_t taken = 0;  // bit j: expert lane + 32 j is already selected
+    float chosen_v = 0.0f;  // lane r keeps the r-th selected score
+    uint32_t chosen = 0;
+    for (uint32_t r = 0; r < active; ++r) {
+        float best = -INFINITY;
+        uint32_t bi = 0xffffffffu;
+        for (uint32_t j = 0, i = lane; i < experts; ++j, i += 32u) {
+            const float v = sv[i];
+            if (!((taken >> j) & 1u) && (bi == 0xffffffffu || v > best)) best = v, bi = i;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0xffffffffu && (bi == 0xffffffffu || ov > best || (ov == best && oi < bi))) best = ov, bi = oi;
+        }
+        if ((bi & 31u) == lane) taken |= 1u << (bi >> 5);
+        if (lane == r) chosen_v = best, chosen = bi;
+    }
+    // softmax over the selected, sums in selection order
+    float mx = -INFINITY;
+    for (uint32_t r = 0; r < active; ++r) mx = fmaxf(mx, __shfl_sync(0xffffffffu, chosen_v, r));
+    const float p = lane < active ? expf(chosen_v - mx) : 0.0f;
+    float sum = 0.0f;
+    for (uint32_t r = 0; r < active; ++r) sum += __shfl_sync(0xffffffffu, p, r);
+    if (lane < active) {
+        probs[lane] = p / sum;
+        ids[lane] = chosen;
+        ids[active + lane] = chosen + experts;
+    }
 }
 
-// x += sum_r probs[r] * rows[r], r ascending from zero (qwen.rs:894-899), then the residual add.
-__global__ void moe_mix_add_kernel(float *x, const float *rows, const float *probs, uint32_t active, uint32_t n) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    float r = 0.0f;
-    for (uint32_t e = 0; e < active; ++e) r += probs[e] * rows[(size_t)e * n + i];
-    x[i] += r;
+// x += update, where update is one row (probs == nullptr) or the expert mixture sum_r probs[r] * rows[r]
+// with r ascending from zero (qwen.rs:894-899); then, if w is given, out = rms_norm(x, w): the residual add
+// and the norm that always follows it, in one CTA.
+__global__ void __launch_bounds__(1024) moe_add_norm_kernel(float *x, const float *rows, const float *probs,
+                                                            uint32_t active, const float *w, float *out, uint32_t n,
+                                                            float eps) {
+    __shared__ float scratch[32];
+    float s = 0.0f;
+    for (uint32_t i = threadIdx.x; i < n; i += 1024u) {
+        float r;
+        if (probs) {
+            r = 0.0f;
+            for (uint32_t e = 0; e < active; ++e) r += probs[e] * rows[(size_t)e * n + i];
+        } else {
+            r = rows[i];
+        }
+        const float v = x[i] + r;
+        x[i] = v;
+        s += v * v;
+    }
+    if (!w) return;
+    const float mean = block_sum<1024>(s, scratch) / (float)n;
+    const float scale = 1.0f / sqrtf(mean + eps);
+    for (uint32_t i = threadIdx.x; i < n; i += 1024u) out[i] = x[i] * scale * w[i];  // this thread's own writes
 }
 
 // End of a token: with logits, the first index of their maximum becomes `next` (non-finite logits raise
@@ -249,7 +340,7 @@ struct MoeModel {
     stark_b200_moe_config cfg{};
     int device = -1;
     cudaStream_t stream = nullptr;
-    std::vector<const QMatrix *> qkv, o, gate, up, down;
+    std::vector<const QMatrix *> qkv, o, gate_up, down;
     const QMatrix *output = nullptr;
     // owned device memory
     uint8_t *token_table = nullptr;
@@ -257,11 +348,12 @@ struct MoeModel {
     float *router = nullptr;  // [layers][experts * hidden]
     float *keys = nullptr, *values = nullptr;  // [layers][context][kv_heads * head_dim]
     float *work = nullptr;    // activations, see carve()
-    uint32_t *ids = nullptr;  // [layers][active]
+    uint32_t *ids = nullptr;  // [layers][2 * active]: the selected experts, then the same + experts
+    uint32_t *arrivals = nullptr;  // the router CTAs' arrival counter (returns to zero by itself)
     MoeState *state = nullptr;
     std::vector<uint8_t> have;  // which tensors were set
     // activations carved out of `work`
-    float *x, *n, *qkv_out, *att, *part, *update, *scores, *probs, *gate_out, *up_out, *expert_out, *logits;
+    float *x, *n, *qkv_out, *att, *part, *update, *scores, *probs, *gate_out, *expert_out, *logits;
     cudaGraphExec_t graph[2] = {nullptr, nullptr};  // [0] cache only, [1] with logits
     bool warmed[2] = {false, false};
     uint32_t nodes = 0;
@@ -302,10 +394,10 @@ stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
     const uint32_t I = c.expert_intermediate;
     const float scale = 1.0f / sqrtf((float)D);
     moe_embed_kernel<<<1, 256, 0, s>>>(m->state, m->token_table, m->x, H, c.vocab, c.context_tokens);
+    moe_rmsnorm_kernel<<<1, 1024, 0, s>>>(m->x, m->norm(STARK_B200_MOE_TENSOR_ATTN_NORM, 0), m->n, H, c.rms_eps);
     for (uint32_t l = 0; l < c.layers; ++l) {
         float *keys = m->keys + (size_t)l * m->kv_layer(), *values = m->values + (size_t)l * m->kv_layer();
-        uint32_t *ids = m->ids + (size_t)l * A;
-        moe_rmsnorm_kernel<<<1, 1024, 0, s>>>(m->x, m->norm(STARK_B200_MOE_TENSOR_ATTN_NORM, l), m->n, H, c.rms_eps);
+        uint32_t *ids = m->ids + (size_t)l * 2u * A;
         SB_TRY(qmv_rows_launch(m->qkv[l], m->n, 0, m->qkv_out, 1, nullptr, STARK_B200_F32, s));
         moe_heads_kernel<<<QH + 2u * KV, D, 0, s>>>(m->state, m->qkv_out, m->norm(STARK_B200_MOE_TENSOR_Q_NORM, l),
                                                    m->norm(STARK_B200_MOE_TENSOR_K_NORM, l), keys, values, QH, KV, D,
@@ -314,20 +406,19 @@ stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
                                                                              QH, KV, scale, c.context_tokens);
         moe_attention_merge_kernel<<<QH, 128, 0, s>>>(m->part, m->att);
         SB_TRY(qmv_rows_launch(m->o[l], m->att, 0, m->update, 1, nullptr, STARK_B200_F32, s));
-        moe_add_kernel<<<(H + 255u) / 256u, 256, 0, s>>>(m->x, m->update, H);
-        moe_rmsnorm_kernel<<<1, 1024, 0, s>>>(m->x, m->norm(STARK_B200_MOE_TENSOR_FFN_NORM, l), m->n, H, c.rms_eps);
-        SB_TRY(dense_matvec_f32_launch(m->router + (size_t)l * c.experts * H, m->n, m->scores, c.experts, H, s));
-        SB_TRY(moe_select_launch(m->scores, c.experts, A, ids, m->probs, s));
-        SB_TRY(qmv_rows_launch(m->gate[l], m->n, 0, m->gate_out, A, ids, STARK_B200_F32, s));
-        SB_TRY(qmv_rows_launch(m->up[l], m->n, 0, m->up_out, A, ids, STARK_B200_F32, s));
-        SB_TRY(silu_mul_f32_launch(m->gate_out, m->up_out, A * I, s));
+        moe_add_norm_kernel<<<1, 1024, 0, s>>>(m->x, m->update, nullptr, 1, m->norm(STARK_B200_MOE_TENSOR_FFN_NORM, l),
+                                               m->n, H, c.rms_eps);
+        moe_router_select_kernel<<<c.experts, 256, 0, s>>>(m->router + (size_t)l * c.experts * H, m->n, m->scores, H,
+                                                           c.experts, A, ids, m->probs, m->arrivals);
+        SB_TRY(qmv_rows_launch(m->gate_up[l], m->n, 0, m->gate_out, 2u * A, ids, STARK_B200_F32, s));
+        SB_TRY(silu_mul_f32_launch(m->gate_out, m->gate_out + (size_t)A * I, A * I, s));
         SB_TRY(qmv_rows_launch(m->down[l], m->gate_out, I, m->expert_out, A, ids, STARK_B200_F32, s));
-        moe_mix_add_kernel<<<(H + 255u) / 256u, 256, 0, s>>>(m->x, m->expert_out, m->probs, A, H);
+        // the mixture, the residual add and the next norm: the next layer's, or the final one before the logits
+        const float *next = l + 1u < c.layers ? m->norm(STARK_B200_MOE_TENSOR_ATTN_NORM, l + 1u)
+                                              : (want_logits ? m->norm(STARK_B200_MOE_TENSOR_FINAL_NORM, 0) : nullptr);
+        moe_add_norm_kernel<<<1, 1024, 0, s>>>(m->x, m->expert_out, m->probs, A, next, m->n, H, c.rms_eps);
     }
-    if (want_logits) {
-        moe_rmsnorm_kernel<<<1, 1024, 0, s>>>(m->x, m->norm(STARK_B200_MOE_TENSOR_FINAL_NORM, 0), m->n, H, c.rms_eps);
-        SB_TRY(qmv_rows_launch(m->output, m->n, 0, m->logits, 1, nullptr, STARK_B200_F32, s));
-    }
+    if (want_logits) SB_TRY(qmv_rows_launch(m->output, m->n, 0, m->logits, 1, nullptr, STARK_B200_F32, s));
     moe_finish_kernel<<<1, 1024, 0, s>>>(m->state, want_logits ? m->logits : nullptr, c.vocab);
     SB_CUDA(cudaGetLastError());
     return STARK_B200_OK;
@@ -400,7 +491,7 @@ void moe_free(MoeModel *m) {
     for (auto &g : m->graph)
         if (g) cudaGraphExecDestroy(g);
     cudaFree(m->token_table), cudaFree(m->norms), cudaFree(m->router), cudaFree(m->keys), cudaFree(m->values);
-    cudaFree(m->work), cudaFree(m->ids), cudaFree(m->state);
+    cudaFree(m->work), cudaFree(m->ids), cudaFree(m->arrivals), cudaFree(m->state);
     if (m->stream) cudaStreamDestroy(m->stream);
     delete m;
 }
@@ -427,13 +518,13 @@ stark_b200_status stark_b200_moe_model_create(const stark_b200_moe_config *confi
     MoeModel *m = new MoeModel();
     m->cfg = c;
     cudaGetDevice(&m->device);
-    m->qkv.assign(c.layers, nullptr), m->o.assign(c.layers, nullptr), m->gate.assign(c.layers, nullptr);
-    m->up.assign(c.layers, nullptr), m->down.assign(c.layers, nullptr);
+    m->qkv.assign(c.layers, nullptr), m->o.assign(c.layers, nullptr), m->gate_up.assign(c.layers, nullptr);
+    m->down.assign(c.layers, nullptr);
     m->have.assign(2u * 8u * c.layers, 0);
     const size_t QD = (size_t)c.q_heads * c.head_dim, KD = (size_t)c.kv_heads * c.head_dim;
     const size_t AI = (size_t)c.active_experts * c.expert_intermediate;
     const size_t sizes[] = {c.hidden, c.hidden, QD + 2u * KD, QD, (size_t)c.q_heads * kAttnSplits * (c.head_dim + 2u),
-                            c.hidden, c.experts, c.active_experts, AI, AI, (size_t)c.active_experts * c.hidden, c.vocab};
+                            c.hidden, c.experts, c.active_experts, 2u * AI, (size_t)c.active_experts * c.hidden, c.vocab};
     size_t total = 0;
     for (size_t v : sizes) total += (v + 63u) / 64u * 64u;
     bool ok = cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) == cudaSuccess;
@@ -443,7 +534,8 @@ stark_b200_status stark_b200_moe_model_create(const stark_b200_moe_config *confi
     ok = ok && cudaMalloc(&m->keys, (size_t)c.layers * m->kv_layer() * 4u) == cudaSuccess;
     ok = ok && cudaMalloc(&m->values, (size_t)c.layers * m->kv_layer() * 4u) == cudaSuccess;
     ok = ok && cudaMalloc(&m->work, total * 4u) == cudaSuccess;
-    ok = ok && cudaMalloc(&m->ids, (size_t)c.layers * c.active_experts * 4u) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->ids, (size_t)c.layers * c.active_experts * 8u) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->arrivals, 4u) == cudaSuccess;
     ok = ok && cudaMalloc(&m->state, sizeof(MoeState)) == cudaSuccess;
     if (!ok) {
         cudaGetLastError();
@@ -451,13 +543,14 @@ stark_b200_status stark_b200_moe_model_create(const stark_b200_moe_config *confi
         return STARK_B200_OUT_OF_MEMORY;
     }
     float **slots[] = {&m->x, &m->n, &m->qkv_out, &m->att, &m->part, &m->update, &m->scores, &m->probs,
-                       &m->gate_out, &m->up_out, &m->expert_out, &m->logits};
+                       &m->gate_out, &m->expert_out, &m->logits};
     float *at = m->work;
     for (size_t i = 0; i < sizeof(sizes) / sizeof(sizes[0]); ++i) {
         *slots[i] = at;
         at += (sizes[i] + 63u) / 64u * 64u;
     }
-    cudaMemset(m->ids, 0, (size_t)c.layers * c.active_experts * 4u);
+    cudaMemset(m->ids, 0, (size_t)c.layers * c.active_experts * 8u);
+    cudaMemset(m->arrivals, 0, 4u);
     if (moe_reset(m) != STARK_B200_OK) {
         moe_free(m);
         return STARK_B200_DEVICE_FAILURE;
@@ -482,9 +575,8 @@ stark_b200_status stark_b200_moe_model_set_matrix(stark_b200_moe_model *model, u
     switch (kind) {
         case STARK_B200_MOE_MAT_QKV: fits = q8 && banks == 1u && q->rows == QD + 2u * KD && q->columns == c.hidden; break;
         case STARK_B200_MOE_MAT_O: fits = q8 && banks == 1u && q->rows == c.hidden && q->columns == QD; break;
-        case STARK_B200_MOE_MAT_GATE:
-        case STARK_B200_MOE_MAT_UP:
-            fits = q4 && banks == c.experts && q->rows == c.expert_intermediate && q->columns == c.hidden;
+        case STARK_B200_MOE_MAT_GATE_UP:
+            fits = q4 && banks == 2u * c.experts && q->rows == c.expert_intermediate && q->columns == c.hidden;
             break;
         case STARK_B200_MOE_MAT_DOWN:
             fits = q4 && banks == c.experts && q->rows == c.hidden && q->columns == c.expert_intermediate;
@@ -495,8 +587,7 @@ stark_b200_status stark_b200_moe_model_set_matrix(stark_b200_moe_model *model, u
     switch (kind) {
         case STARK_B200_MOE_MAT_QKV: m->qkv[layer] = q; break;
         case STARK_B200_MOE_MAT_O: m->o[layer] = q; break;
-        case STARK_B200_MOE_MAT_GATE: m->gate[layer] = q; break;
-        case STARK_B200_MOE_MAT_UP: m->up[layer] = q; break;
+        case STARK_B200_MOE_MAT_GATE_UP: m->gate_up[layer] = q; break;
         case STARK_B200_MOE_MAT_DOWN: m->down[layer] = q; break;
         default: m->output = q; break;
     }
@@ -623,7 +714,8 @@ stark_b200_status stark_b200_moe_model_last_experts(stark_b200_moe_model *model,
     if (!m || !ids_host || count != (size_t)m->cfg.layers * m->cfg.active_experts) return STARK_B200_INVALID_ARGUMENT;
     DeviceScope scope(m->device);
     SB_CUDA(cudaStreamSynchronize(m->stream));
-    SB_CUDA(cudaMemcpy(ids_host, m->ids, count * 4u, cudaMemcpyDeviceToHost));
+    const size_t a = m->cfg.active_experts;
+    SB_CUDA(cudaMemcpy2D(ids_host, a * 4u, m->ids, 2u * a * 4u, a * 4u, m->cfg.layers, cudaMemcpyDeviceToHost));
     return STARK_B200_OK;
 }
 
@@ -637,7 +729,7 @@ stark_b200_status stark_b200_moe_model_position(const stark_b200_moe_model *mode
 stark_b200_status stark_b200_moe_model_launches_per_token(const stark_b200_moe_model *model, uint32_t *out_launches) {
     const MoeModel *m = reinterpret_cast<const MoeModel *>(model);
     if (!m || !out_launches) return STARK_B200_INVALID_ARGUMENT;
-    *out_launches = m->nodes ? m->nodes : 3u + 15u * m->cfg.layers;
+    *out_launches = m->nodes ? m->nodes : 4u + 11u * m->cfg.layers;
     return STARK_B200_OK;
 }
 

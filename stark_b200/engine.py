@@ -354,8 +354,8 @@ class MoEModel:
         Q8_0, Q4_K = 8, 12
         self._matrix(L.MOE_MAT_QKV, layer, w["qkv"], Q8_0, qd + 2 * kd, c["hidden"])
         self._matrix(L.MOE_MAT_O, layer, w["o"], Q8_0, c["hidden"], qd)
-        self._matrix(L.MOE_MAT_GATE, layer, w["gate"], Q4_K, c["inter"], c["hidden"], c["experts"])
-        self._matrix(L.MOE_MAT_UP, layer, w["up"], Q4_K, c["inter"], c["hidden"], c["experts"])
+        gate_up = np.concatenate([np.asarray(w["gate"], np.uint8).reshape(-1), np.asarray(w["up"], np.uint8).reshape(-1)])
+        self._matrix(L.MOE_MAT_GATE_UP, layer, gate_up, Q4_K, c["inter"], c["hidden"], 2 * c["experts"])
         self._matrix(L.MOE_MAT_DOWN, layer, w["down"], Q4_K, c["hidden"], c["inter"], c["experts"])
         self._tensor(L.MOE_ROUTER, layer, np.asarray(w["router"], np.float32))
         for kind, name in ((L.MOE_ATTN_NORM, "attn_norm"), (L.MOE_FFN_NORM, "ffn_norm"), (L.MOE_Q_NORM, "q_norm"),
