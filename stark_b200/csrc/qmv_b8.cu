@@ -68,6 +68,35 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_b8t_kernel(const B8Params p
     float *red = xsum + K / 32u;                       // [kQ4Warps] block maxima
     uint8_t *stage = reinterpret_cast<uint8_t *>(red + kQ4Warps) + (size_t)warp * kQ4Stages * kB8SuperBytes;
 
+    // The first copies of this warp's records go out before the input row is staged: they do not depend on it.
+    uint32_t expert = 0;
+    if (p.expert_ids) {
+        expert = p.expert_ids[b];
+        if (expert >= p.experts) expert = 0;  // moe_gather_rows: an invalid id falls back to expert 0 (moe.rs:84-101)
+    }
+    const uint8_t *base = p.data + (size_t)expert * p.expert_bytes;
+    const uint32_t team = warp / KS, member = warp % KS;
+    const uint32_t gw = blockIdx.x * kTeams + team, nw = gridDim.x * kTeams;  // teams, not warps
+    const uint32_t my_tiles = gw < p.row_tiles ? (p.row_tiles - gw + nw - 1u) / nw : 0u;
+    const uint32_t items = my_tiles * (p.supers / KS);  // the launcher makes KS divide the super-block count
+
+    uint32_t in_tile = gw, in_sb = member, in_item = 0;
+    auto issue = [&]() {
+        if (in_item < items) {
+            const uint8_t *src = base + ((size_t)in_tile * p.supers + in_sb) * kB8SuperBytes;
+            uint8_t *dst = stage + (in_item % kQ4Stages) * kB8SuperBytes;
+            for (uint32_t off = lane * 16u; off < kB8SuperBytes; off += 512u) cp_async16(dst + off, src + off);
+            ++in_item;
+            if ((in_sb += KS) >= p.supers) {
+                in_sb = member;
+                in_tile += nw;
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int i = 0; i < kQ4Stages - 1; ++i) issue();
+
     // ---- input row: exact power-of-two scale into f16 range, head + remainder, per-32 sums ----
     float vmax = 0.0f;
     for (uint32_t i = tid; i < K; i += kQ4Threads) {
@@ -100,33 +129,6 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_b8t_kernel(const B8Params p
     }
     __syncthreads();
 
-    uint32_t expert = 0;
-    if (p.expert_ids) {
-        expert = p.expert_ids[b];
-        if (expert >= p.experts) expert = 0;  // moe_gather_rows: an invalid id falls back to expert 0 (moe.rs:84-101)
-    }
-    const uint8_t *base = p.data + (size_t)expert * p.expert_bytes;
-    const uint32_t team = warp / KS, member = warp % KS;
-    const uint32_t gw = blockIdx.x * kTeams + team, nw = gridDim.x * kTeams;  // teams, not warps
-    const uint32_t my_tiles = gw < p.row_tiles ? (p.row_tiles - gw + nw - 1u) / nw : 0u;
-    const uint32_t items = my_tiles * (p.supers / KS);  // the launcher makes KS divide the super-block count
-
-    uint32_t in_tile = gw, in_sb = member, in_item = 0;
-    auto issue = [&]() {
-        if (in_item < items) {
-            const uint8_t *src = base + ((size_t)in_tile * p.supers + in_sb) * kB8SuperBytes;
-            uint8_t *dst = stage + (in_item % kQ4Stages) * kB8SuperBytes;
-            for (uint32_t off = lane * 16u; off < kB8SuperBytes; off += 512u) cp_async16(dst + off, src + off);
-            ++in_item;
-            if ((in_sb += KS) >= p.supers) {
-                in_sb = member;
-                in_tile += nw;
-            }
-        }
-        cp_async_commit();
-    };
-#pragma unroll
-    for (int i = 0; i < kQ4Stages - 1; ++i) issue();
 
     const __half *xsel = (g & 1u) ? xlo : xhi;  // B column n = g: even columns the head, odd the remainder
     float acc_s0 = 0.0f, acc_s1 = 0.0f, acc_m0 = 0.0f, acc_m1 = 0.0f;
