@@ -53,6 +53,8 @@ __device__ inline float block_sum(float v, float *scratch /* [32] */) {
 // (engine/hybrid/weights.rs:2936-2941).
 __global__ void __launch_bounds__(256) moe_embed_kernel(MoeState *st, const uint8_t *blocks, float *x, uint32_t hidden,
                                                         uint32_t vocab, uint32_t context) {
+    pdl_launch_dependents();
+    pdl_wait();
     uint32_t token = st->chain ? st->next : st->token;
     __syncthreads();
     if (token >= vocab || st->position >= context) {
@@ -71,6 +73,8 @@ __global__ void __launch_bounds__(256) moe_embed_kernel(MoeState *st, const uint
 // out = x * (1 / sqrt(mean(x^2) + eps)) * w   (math.rs:18-34)
 __global__ void __launch_bounds__(1024) moe_rmsnorm_kernel(const float *x, const float *w, float *out, uint32_t n,
                                                            float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     float s = 0.0f;
     for (uint32_t i = threadIdx.x; i < n; i += 1024u) s += x[i] * x[i];
@@ -84,6 +88,8 @@ __global__ void __launch_bounds__(1024) moe_rmsnorm_kernel(const float *x, const
 __global__ void moe_heads_kernel(const MoeState *st, float *qkv, const float *q_norm, const float *k_norm, float *keys,
                                  float *values, uint32_t q_heads, uint32_t kv_heads, uint32_t dim, float eps,
                                  float theta, uint32_t context) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     __shared__ float head[256];
     const uint32_t h = blockIdx.x, i = threadIdx.x;
@@ -126,6 +132,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) moe_attention_kernel(const Mo
                                                                         float *part, uint32_t q_heads,
                                                                         uint32_t kv_heads, float scale,
                                                                         uint32_t context) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr uint32_t D = 128;
     __shared__ float sm[kAttnWarps], sl[kAttnWarps];
     __shared__ float4 sacc[kAttnWarps][32];
@@ -192,6 +200,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) moe_attention_kernel(const Mo
 }
 
 __global__ void __launch_bounds__(128) moe_attention_merge_kernel(const float *part, float *out) {
+    pdl_launch_dependents();
+    pdl_wait();
     constexpr uint32_t D = 128;
     const uint32_t h = blockIdx.x, i = threadIdx.x;
     const float *src = part + (size_t)h * kAttnSplits * (D + 2u);
@@ -215,6 +225,8 @@ __global__ void __launch_bounds__(128) moe_attention_merge_kernel(const float *p
 __global__ void __launch_bounds__(256) moe_router_select_kernel(const float *w, const float *x, float *scores,
                                                                 uint32_t hidden, uint32_t experts, uint32_t active,
                                                                 uint32_t *ids, float *probs, uint32_t *arrivals) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     __shared__ float sv[1024];
     __shared__ bool last;
@@ -278,6 +290,8 @@ __global__ void __launch_bounds__(256) moe_router_select_kernel(const float *w, 
 __global__ void __launch_bounds__(1024) moe_add_norm_kernel(float *x, const float *rows, const float *probs,
                                                             uint32_t active, const float *w, float *out, uint32_t n,
                                                             float eps) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[32];
     float s = 0.0f;
     for (uint32_t i = threadIdx.x; i < n; i += 1024u) {
@@ -298,9 +312,28 @@ __global__ void __launch_bounds__(1024) moe_add_norm_kernel(float *x, const floa
     for (uint32_t i = threadIdx.x; i < n; i += 1024u) out[i] = x[i] * scale * w[i];  // this thread's own writes
 }
 
+// gate[i] = silu(gate[i]) * up[i]  (qwen.rs:889-891, math.rs:5-16)
+__global__ void moe_silu_mul_kernel(float *gate, const float *up, uint32_t n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float g = gate[i];
+    float sg;
+    if (g >= 0.0f) {
+        sg = 1.0f / (1.0f + expf(-g));
+    } else {
+        const float e = expf(g);
+        sg = e / (1.0f + e);
+    }
+    gate[i] = g * sg * up[i];
+}
+
 // End of a token: with logits, the first index of their maximum becomes `next` (non-finite logits raise
 // the error word, as Model::step refuses them, engine/hybrid/mod.rs:990); the cache grows by one row.
 __global__ void __launch_bounds__(1024) moe_finish_kernel(MoeState *st, const float *logits, uint32_t vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float bv[32];
     __shared__ uint32_t bi[32];
     __shared__ int bad_any;
@@ -388,39 +421,68 @@ struct MoeModel {
 
 namespace {
 
+template <typename... Params, typename... Args>
+stark_b200_status moe_launch(void (*kernel)(Params...), dim3 grid, dim3 block, bool pdl, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...));
+    return STARK_B200_OK;
+}
+
+// Every kernel of a token awaits its predecessor itself (programmatic dependent launch), so the next
+// kernel's CTAs are placed, and the matvecs' first weight records fetched, while the previous one drains.
+// STARK_B200_PDL=0 serializes the launches instead.
+bool moe_pdl() {
+    static const bool on = [] {
+        const char *e = getenv("STARK_B200_PDL");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
     const auto &c = m->cfg;
     const uint32_t H = c.hidden, D = c.head_dim, QH = c.q_heads, KV = c.kv_heads, A = c.active_experts;
     const uint32_t I = c.expert_intermediate;
     const float scale = 1.0f / sqrtf((float)D);
-    moe_embed_kernel<<<1, 256, 0, s>>>(m->state, m->token_table, m->x, H, c.vocab, c.context_tokens);
-    moe_rmsnorm_kernel<<<1, 1024, 0, s>>>(m->x, m->norm(STARK_B200_MOE_TENSOR_ATTN_NORM, 0), m->n, H, c.rms_eps);
+    const bool pdl = moe_pdl();
+    SB_TRY(moe_launch(moe_embed_kernel, 1, 256, false, s, m->state, m->token_table, m->x, H, c.vocab, c.context_tokens));
+    SB_TRY(moe_launch(moe_rmsnorm_kernel, 1, 1024, pdl, s, m->x, m->norm(STARK_B200_MOE_TENSOR_ATTN_NORM, 0), m->n, H,
+                      c.rms_eps));
     for (uint32_t l = 0; l < c.layers; ++l) {
         float *keys = m->keys + (size_t)l * m->kv_layer(), *values = m->values + (size_t)l * m->kv_layer();
         uint32_t *ids = m->ids + (size_t)l * 2u * A;
-        SB_TRY(qmv_rows_launch(m->qkv[l], m->n, 0, m->qkv_out, 1, nullptr, STARK_B200_F32, s));
-        moe_heads_kernel<<<QH + 2u * KV, D, 0, s>>>(m->state, m->qkv_out, m->norm(STARK_B200_MOE_TENSOR_Q_NORM, l),
-                                                   m->norm(STARK_B200_MOE_TENSOR_K_NORM, l), keys, values, QH, KV, D,
-                                                   c.rms_eps, c.rope_theta, c.context_tokens);
-        moe_attention_kernel<<<dim3(QH, kAttnSplits), kAttnWarps * 32, 0, s>>>(m->state, m->qkv_out, keys, values, m->part,
-                                                                             QH, KV, scale, c.context_tokens);
-        moe_attention_merge_kernel<<<QH, 128, 0, s>>>(m->part, m->att);
-        SB_TRY(qmv_rows_launch(m->o[l], m->att, 0, m->update, 1, nullptr, STARK_B200_F32, s));
-        moe_add_norm_kernel<<<1, 1024, 0, s>>>(m->x, m->update, nullptr, 1, m->norm(STARK_B200_MOE_TENSOR_FFN_NORM, l),
-                                               m->n, H, c.rms_eps);
-        moe_router_select_kernel<<<c.experts, 256, 0, s>>>(m->router + (size_t)l * c.experts * H, m->n, m->scores, H,
-                                                           c.experts, A, ids, m->probs, m->arrivals);
-        SB_TRY(qmv_rows_launch(m->gate_up[l], m->n, 0, m->gate_out, 2u * A, ids, STARK_B200_F32, s));
-        SB_TRY(silu_mul_f32_launch(m->gate_out, m->gate_out + (size_t)A * I, A * I, s));
-        SB_TRY(qmv_rows_launch(m->down[l], m->gate_out, I, m->expert_out, A, ids, STARK_B200_F32, s));
+        SB_TRY(qmv_rows_launch(m->qkv[l], m->n, 0, m->qkv_out, 1, nullptr, STARK_B200_F32, s, pdl));
+        SB_TRY(moe_launch(moe_heads_kernel, QH + 2u * KV, D, pdl, s, m->state, m->qkv_out,
+                          m->norm(STARK_B200_MOE_TENSOR_Q_NORM, l), m->norm(STARK_B200_MOE_TENSOR_K_NORM, l), keys, values,
+                          QH, KV, D, c.rms_eps, c.rope_theta, c.context_tokens));
+        SB_TRY(moe_launch(moe_attention_kernel, dim3(QH, kAttnSplits), kAttnWarps * 32, pdl, s, m->state, m->qkv_out,
+                          keys, values, m->part, QH, KV, scale, c.context_tokens));
+        SB_TRY(moe_launch(moe_attention_merge_kernel, QH, 128, pdl, s, m->part, m->att));
+        SB_TRY(qmv_rows_launch(m->o[l], m->att, 0, m->update, 1, nullptr, STARK_B200_F32, s, pdl));
+        SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->update, nullptr, 1u,
+                          m->norm(STARK_B200_MOE_TENSOR_FFN_NORM, l), m->n, H, c.rms_eps));
+        SB_TRY(moe_launch(moe_router_select_kernel, c.experts, 256, pdl, s, m->router + (size_t)l * c.experts * H, m->n,
+                          m->scores, H, c.experts, A, ids, m->probs, m->arrivals));
+        SB_TRY(qmv_rows_launch(m->gate_up[l], m->n, 0, m->gate_out, 2u * A, ids, STARK_B200_F32, s, pdl));
+        SB_TRY(moe_launch(moe_silu_mul_kernel, (A * I + 255u) / 256u, 256, pdl, s, m->gate_out,
+                          m->gate_out + (size_t)A * I, A * I));
+        SB_TRY(qmv_rows_launch(m->down[l], m->gate_out, I, m->expert_out, A, ids, STARK_B200_F32, s, pdl));
         // the mixture, the residual add and the next norm: the next layer's, or the final one before the logits
         const float *next = l + 1u < c.layers ? m->norm(STARK_B200_MOE_TENSOR_ATTN_NORM, l + 1u)
                                               : (want_logits ? m->norm(STARK_B200_MOE_TENSOR_FINAL_NORM, 0) : nullptr);
-        moe_add_norm_kernel<<<1, 1024, 0, s>>>(m->x, m->expert_out, m->probs, A, next, m->n, H, c.rms_eps);
+        SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->expert_out, m->probs, A, next, m->n, H, c.rms_eps));
     }
-    if (want_logits) SB_TRY(qmv_rows_launch(m->output, m->n, 0, m->logits, 1, nullptr, STARK_B200_F32, s));
-    moe_finish_kernel<<<1, 1024, 0, s>>>(m->state, want_logits ? m->logits : nullptr, c.vocab);
-    SB_CUDA(cudaGetLastError());
+    if (want_logits) SB_TRY(qmv_rows_launch(m->output, m->n, 0, m->logits, 1, nullptr, STARK_B200_F32, s, pdl));
+    SB_TRY(moe_launch(moe_finish_kernel, 1, 1024, pdl, s, m->state, want_logits ? m->logits : nullptr, c.vocab));
     return STARK_B200_OK;
 }
 

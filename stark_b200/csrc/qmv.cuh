@@ -118,8 +118,9 @@ void qmatrix_free(QMatrix *m);
 // Tensor-core Q4_K (qmv_q4k.cu): re-tile a device copy of the source blocks into m->data, multiply, decode.
 size_t q4kt_bytes(uint32_t experts, uint32_t rows, uint32_t columns);
 stark_b200_status q4kt_retile(const uint8_t *blocks_device, QMatrix *m, cudaStream_t stream);
+// pdl: launch with programmatic stream serialization (the kernel awaits its predecessor itself).
 stark_b200_status q4kt_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
-                              const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream);
+                              const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream, bool pdl = false);
 stark_b200_status q4kt_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,
                                   uint8_t *codes_device, cudaStream_t stream);
 
@@ -128,7 +129,7 @@ size_t b8t_bytes(uint32_t experts, uint32_t rows, uint32_t columns);
 stark_b200_status b8t_retile(const uint8_t *codes, const uint16_t *scales, const uint16_t *biases, QMatrix *m,
                              cudaStream_t stream);
 stark_b200_status b8t_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
-                             const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream);
+                             const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream, bool pdl = false);
 stark_b200_status b8t_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,
                                  uint8_t *codes_device, cudaStream_t stream);
 
@@ -136,8 +137,9 @@ stark_b200_status b8t_dequantize(const QMatrix *m, uint32_t expert, uint32_t row
 bool qmv_rows_supports(const QMatrix *m);
 // y[b, rows] = W[expert_ids[b]] x_b for b < batch (expert_ids == nullptr: the only matrix);
 // x_stride = elements between consecutive inputs, 0 if all launch rows share one input.
+// pdl only affects the re-tiled tensor-core formats; the streaming kernels launch fully serialized.
 stark_b200_status qmv_rows_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
-                                  const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream);
+                                  const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream, bool pdl = false);
 // One row dequantized to f32 (and / or its integer codes, one byte each), device outputs.
 stark_b200_status qmv_rows_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,
                                       uint8_t *codes_device, cudaStream_t stream);

@@ -68,7 +68,10 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_b8t_kernel(const B8Params p
     float *red = xsum + K / 32u;                       // [kQ4Warps] block maxima
     uint8_t *stage = reinterpret_cast<uint8_t *>(red + kQ4Warps) + (size_t)warp * kQ4Stages * kB8SuperBytes;
 
-    // The first copies of this warp's records go out before the input row is staged: they do not depend on it.
+    // The first copies of this warp's records go out before the input row is staged: they do not depend on it,
+    // nor (without expert ids) on the kernel before this one, whose completion is only awaited after them.
+    pdl_launch_dependents();
+    if (p.expert_ids) pdl_wait();
     uint32_t expert = 0;
     if (p.expert_ids) {
         expert = p.expert_ids[b];
@@ -97,6 +100,7 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_b8t_kernel(const B8Params p
 #pragma unroll
     for (int i = 0; i < kQ4Stages - 1; ++i) issue();
 
+    if (!p.expert_ids) pdl_wait();
     // ---- input row: exact power-of-two scale into f16 range, head + remainder, per-32 sums ----
     float vmax = 0.0f;
     for (uint32_t i = tid; i < K; i += kQ4Threads) {
@@ -303,7 +307,7 @@ __global__ void dequant_b8t_kernel(const uint8_t *__restrict__ data, uint32_t su
 }
 
 template <bool AFFINE>
-stark_b200_status launch_b8(const QMatrix *m, const B8Params &p, uint32_t batch, cudaStream_t stream) {
+stark_b200_status launch_b8(const QMatrix *m, const B8Params &p, uint32_t batch, cudaStream_t stream, bool pdl) {
     const uint32_t supers = m->columns / 256u;
     uint32_t ks = 1;
     double best = 0.0;
@@ -327,8 +331,17 @@ stark_b200_status launch_b8(const QMatrix *m, const B8Params &p, uint32_t batch,
     if (smem > 220u * 1024u) return STARK_B200_UNSUPPORTED;
     const uint32_t teams = warps / ks;
     const uint32_t blocks = std::max(1u, std::min((m->row_tiles + teams - 1u) / teams, (148u + batch - 1u) / batch));
-    kernel<<<dim3(blocks, batch), warps * 32u, smem, stream>>>(p);
-    SB_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks, batch);
+    cfg.blockDim = dim3(warps * 32u);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
     return STARK_B200_OK;
 }
 
@@ -353,7 +366,7 @@ stark_b200_status b8t_retile(const uint8_t *codes, const uint16_t *scales, const
 }
 
 stark_b200_status b8t_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
-                             const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream) {
+                             const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream, bool pdl) {
     if (m->columns % 256u != 0 || m->columns > 12288u) return STARK_B200_UNSUPPORTED;
     B8Params p{};
     p.data = m->data;
@@ -368,7 +381,7 @@ stark_b200_status b8t_launch(const QMatrix *m, const void *x, size_t x_stride, v
     p.x_stride = x_stride;
     p.y = y;
     p.io_type = io_type;
-    return m->format == kFmtAffine8T ? launch_b8<true>(m, p, batch, stream) : launch_b8<false>(m, p, batch, stream);
+    return m->format == kFmtAffine8T ? launch_b8<true>(m, p, batch, stream, pdl) : launch_b8<false>(m, p, batch, stream, pdl);
 }
 
 stark_b200_status b8t_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,

@@ -83,7 +83,10 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_q4kt_kernel(const Q4ktParam
     float *red = xsum + K / 32u;                       // [kQ4Warps] block maxima
     uint8_t *stage = reinterpret_cast<uint8_t *>(red + kQ4Warps) + (size_t)warp * kQ4Stages * kSuperBytes;
 
-    // The first copies of this warp's records go out before the input row is staged: they do not depend on it.
+    // The first copies of this warp's records go out before the input row is staged: they do not depend on it,
+    // nor (without expert ids) on the kernel before this one, whose completion is only awaited after them.
+    pdl_launch_dependents();
+    if (p.expert_ids) pdl_wait();
     uint32_t expert = 0;
     if (p.expert_ids) {
         expert = p.expert_ids[b];
@@ -112,6 +115,7 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_q4kt_kernel(const Q4ktParam
 #pragma unroll
     for (int i = 0; i < kQ4Stages - 1; ++i) issue();
 
+    if (!p.expert_ids) pdl_wait();
     // ---- input row: exact power-of-two scale into f16 range, head + remainder, per-32 sums ----
     float vmax = 0.0f;
     for (uint32_t i = tid; i < K; i += kQ4Threads) {
@@ -295,7 +299,7 @@ stark_b200_status q4kt_retile(const uint8_t *blocks, QMatrix *m, cudaStream_t st
 }
 
 stark_b200_status q4kt_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
-                              const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream) {
+                              const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream, bool pdl) {
     if (m->columns % 256u != 0 || m->columns > 12288u) return STARK_B200_UNSUPPORTED;
     Q4ktParams p{};
     p.data = m->data;
@@ -342,8 +346,17 @@ stark_b200_status q4kt_launch(const QMatrix *m, const void *x, size_t x_stride, 
     const uint32_t teams = warps / ks;
     const uint32_t blocks =
         std::max(1u, std::min((m->row_tiles + teams - 1u) / teams, (148u * per_sm + batch - 1u) / batch));
-    kernel<<<dim3(blocks, batch), warps * 32u, smem, stream>>>(p);
-    SB_CUDA(cudaGetLastError());
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks, batch);
+    cfg.blockDim = dim3(warps * 32u);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
     return STARK_B200_OK;
 }
 

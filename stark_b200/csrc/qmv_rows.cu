@@ -433,11 +433,11 @@ bool qmv_rows_supports(const QMatrix *m) {
 }
 
 stark_b200_status qmv_rows_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
-                                  const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream) {
+                                  const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream, bool pdl) {
     if (!qmv_rows_supports(m) || !x || !y || batch == 0) return STARK_B200_INVALID_ARGUMENT;
-    if (m->format == kFmtQ4_K) return q4kt_launch(m, x, x_stride, y, batch, expert_ids, io_type, stream);
+    if (m->format == kFmtQ4_K) return q4kt_launch(m, x, x_stride, y, batch, expert_ids, io_type, stream, pdl);
     if (m->format == kFmtQ8_0T || m->format == kFmtAffine8T)
-        return b8t_launch(m, x, x_stride, y, batch, expert_ids, io_type, stream);
+        return b8t_launch(m, x, x_stride, y, batch, expert_ids, io_type, stream, pdl);
     if (m->columns > 12288u) return STARK_B200_UNSUPPORTED;
     RowParams p = row_params(m);
     p.x = x;
