@@ -35,7 +35,7 @@ struct MoeState {
     uint32_t error;     // sticky: 1 token out of range, 2 non-finite logits, 4 context exhausted
 };
 
-constexpr uint32_t kAttnSplits = 16, kAttnWarps = 8;
+constexpr uint32_t kAttnSplits = 16, kAttnWarps = 8, kMoeMaxAttnSplits = 64;
 
 template <int THREADS>
 __device__ inline float block_sum(float v, float *scratch /* [32] */) {
@@ -199,16 +199,106 @@ __global__ void __launch_bounds__(kAttnWarps * 32) moe_attention_kernel(const Mo
     }
 }
 
-__global__ void __launch_bounds__(128) moe_attention_merge_kernel(const float *part, float *out) {
+// The same attention with the query heads of one KV head handled together (G = q_heads / kv_heads): a CTA
+// per (KV head, span) reads each K and V row once and scores it against all G queries, instead of G CTAs
+// reading the same rows.  Per warp: G running (max, sum, accumulator) states; warp g merges head g's states.
+template <int G>
+__global__ void __launch_bounds__(kAttnWarps * 32) moe_attention_grouped_kernel(const MoeState *st, const float *q,
+                                                                                const float *keys,
+                                                                                const float *values, float *part,
+                                                                                uint32_t splits, uint32_t kv_heads,
+                                                                                float scale, uint32_t context) {
+    constexpr uint32_t D = 128;
+    __shared__ float sm[kAttnWarps][G], sl[kAttnWarps][G];
+    __shared__ float4 sacc[kAttnWarps][G][32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t kvh = blockIdx.x, split = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t rows = min(st->position + 1u, context);
+    const uint32_t span = (rows + splits - 1u) / splits;
+    const uint32_t lo = min(rows, split * span), hi = min(rows, lo + span);
+    const size_t kv_row = (size_t)kv_heads * D;
+    const uint32_t begin = kvh * D;
+    float4 qv[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) qv[g] = reinterpret_cast<const float4 *>(q + ((size_t)kvh * G + g) * D)[lane];
+    float m[G], l[G];
+    float4 acc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) m[g] = -INFINITY, l[g] = 0.0f, acc[g] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    for (uint32_t t0 = lo + warp; t0 < hi; t0 += 2u * kAttnWarps) {
+        float4 kv[2], vv[2];
+        float dot[2][G];
+#pragma unroll
+        for (uint32_t j = 0; j < 2u; ++j) {
+            const uint32_t t = min(t0 + j * kAttnWarps, hi - 1u);  // a row past the end repeats the last one, unused
+            kv[j] = reinterpret_cast<const float4 *>(keys + t * kv_row + begin)[lane];
+            vv[j] = reinterpret_cast<const float4 *>(values + t * kv_row + begin)[lane];
+        }
+#pragma unroll
+        for (uint32_t j = 0; j < 2u; ++j)
+#pragma unroll
+            for (int g = 0; g < G; ++g)
+                dot[j][g] = qv[g].x * kv[j].x + qv[g].y * kv[j].y + qv[g].z * kv[j].z + qv[g].w * kv[j].w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (uint32_t j = 0; j < 2u; ++j)
+#pragma unroll
+                for (int g = 0; g < G; ++g) dot[j][g] += __shfl_xor_sync(0xffffffffu, dot[j][g], o);
+#pragma unroll
+        for (uint32_t j = 0; j < 2u; ++j) {
+            if (t0 + j * kAttnWarps >= hi) break;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float s = dot[j][g] * scale;
+                const float nm = fmaxf(m[g], s);
+                const float c = expf(m[g] - nm), p = expf(s - nm);
+                l[g] = l[g] * c + p;
+                acc[g].x = acc[g].x * c + p * vv[j].x;
+                acc[g].y = acc[g].y * c + p * vv[j].y;
+                acc[g].z = acc[g].z * c + p * vv[j].z;
+                acc[g].w = acc[g].w * c + p * vv[j].w;
+                m[g] = nm;
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        if (lane == 0) sm[warp][g] = m[g], sl[warp][g] = l[g];
+        sacc[warp][g][lane] = acc[g];
+    }
+    __syncthreads();
+    if (warp < (uint32_t)G) {
+        const uint32_t g = warp;
+        float gm = -INFINITY;
+        for (uint32_t w = 0; w < kAttnWarps; ++w) gm = fmaxf(gm, sm[w][g]);
+        float gl = 0.0f;
+        float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (uint32_t w = 0; w < kAttnWarps; ++w) {
+            if (sm[w][g] == -INFINITY) continue;
+            const float c = expf(sm[w][g] - gm);
+            const float4 v = sacc[w][g][lane];
+            gl += sl[w][g] * c;
+            a.x += v.x * c, a.y += v.y * c, a.z += v.z * c, a.w += v.w * c;
+        }
+        float *dst = part + (((size_t)kvh * G + g) * splits + split) * (D + 2u);
+        if (lane == 0) dst[0] = gm, dst[1] = gl;
+        reinterpret_cast<float2 *>(dst + 2)[lane * 2u] = make_float2(a.x, a.y);
+        reinterpret_cast<float2 *>(dst + 2)[lane * 2u + 1u] = make_float2(a.z, a.w);
+    }
+}
+
+__global__ void __launch_bounds__(128) moe_attention_merge_kernel(const float *part, float *out, uint32_t splits) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr uint32_t D = 128;
     const uint32_t h = blockIdx.x, i = threadIdx.x;
-    const float *src = part + (size_t)h * kAttnSplits * (D + 2u);
+    const float *src = part + (size_t)h * splits * (D + 2u);
     float gm = -INFINITY;
-    for (uint32_t s = 0; s < kAttnSplits; ++s) gm = fmaxf(gm, src[s * (D + 2u)]);
+    for (uint32_t s = 0; s < splits; ++s) gm = fmaxf(gm, src[s * (D + 2u)]);
     float l = 0.0f, a = 0.0f;
-    for (uint32_t s = 0; s < kAttnSplits; ++s) {
+    for (uint32_t s = 0; s < splits; ++s) {
         const float m = src[s * (D + 2u)];
         if (m == -INFINITY) continue;
         const float c = expf(m - gm);
@@ -464,9 +554,20 @@ stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
         SB_TRY(moe_launch(moe_heads_kernel, QH + 2u * KV, D, pdl, s, m->state, m->qkv_out,
                           m->norm(STARK_B200_MOE_TENSOR_Q_NORM, l), m->norm(STARK_B200_MOE_TENSOR_K_NORM, l), keys, values,
                           QH, KV, D, c.rms_eps, c.rope_theta, c.context_tokens));
-        SB_TRY(moe_launch(moe_attention_kernel, dim3(QH, kAttnSplits), kAttnWarps * 32, pdl, s, m->state, m->qkv_out,
-                          keys, values, m->part, QH, KV, scale, c.context_tokens));
-        SB_TRY(moe_launch(moe_attention_merge_kernel, QH, 128, pdl, s, m->part, m->att));
+        // query heads of one KV head together where the group size has an instantiation, else head by head
+        const uint32_t group = QH / KV, gsplits = std::max(kAttnSplits, std::min(kMoeMaxAttnSplits, 256u / KV));
+        uint32_t splits = kAttnSplits;
+        if (group == 8u || group == 4u || group == 2u) {
+            splits = gsplits;
+            auto grouped = group == 8u ? moe_attention_grouped_kernel<8>
+                                       : (group == 4u ? moe_attention_grouped_kernel<4> : moe_attention_grouped_kernel<2>);
+            SB_TRY(moe_launch(grouped, dim3(KV, splits), kAttnWarps * 32, pdl, s, m->state, m->qkv_out, keys, values,
+                              m->part, splits, KV, scale, c.context_tokens));
+        } else {
+            SB_TRY(moe_launch(moe_attention_kernel, dim3(QH, kAttnSplits), kAttnWarps * 32, pdl, s, m->state, m->qkv_out,
+                              keys, values, m->part, QH, KV, scale, c.context_tokens));
+        }
+        SB_TRY(moe_launch(moe_attention_merge_kernel, QH, 128, pdl, s, m->part, m->att, splits));
         SB_TRY(qmv_rows_launch(m->o[l], m->att, 0, m->update, 1, nullptr, STARK_B200_F32, s, pdl));
         SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->update, nullptr, 1u,
                           m->norm(STARK_B200_MOE_TENSOR_FFN_NORM, l), m->n, H, c.rms_eps));
@@ -585,7 +686,7 @@ stark_b200_status stark_b200_moe_model_create(const stark_b200_moe_config *confi
     m->have.assign(2u * 8u * c.layers, 0);
     const size_t QD = (size_t)c.q_heads * c.head_dim, KD = (size_t)c.kv_heads * c.head_dim;
     const size_t AI = (size_t)c.active_experts * c.expert_intermediate;
-    const size_t sizes[] = {c.hidden, c.hidden, QD + 2u * KD, QD, (size_t)c.q_heads * kAttnSplits * (c.head_dim + 2u),
+    const size_t sizes[] = {c.hidden, c.hidden, QD + 2u * KD, QD, (size_t)c.q_heads * kMoeMaxAttnSplits * (c.head_dim + 2u),
                             c.hidden, c.experts, c.active_experts, 2u * AI, (size_t)c.active_experts * c.hidden, c.vocab};
     size_t total = 0;
     for (size_t v : sizes) total += (v + 63u) / 64u * 64u;
