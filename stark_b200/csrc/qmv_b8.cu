@@ -321,13 +321,22 @@ stark_b200_status launch_b8(const QMatrix *m, const B8Params &p, uint32_t batch,
             ks = cand;
         }
     }
-    constexpr uint32_t warps = 12, stages = 3;
+    // 12 warps x 3 records in flight, or (STARK_B200_B8_WARPS=20) 20 warps x 2: more warps to hide the
+    // conversion and shared-memory latencies against fewer copies per warp.
+    static const bool wide = [] {
+        const char *e = getenv("STARK_B200_B8_WARPS");
+        return e && atoi(e) == 20;
+    }();
+    const uint32_t warps = wide ? 20u : 12u, stages = wide ? 2u : 3u;
     const size_t smem = (size_t)m->columns * 4u + 128u + (size_t)(m->columns / 32u) * 4u + 4u * warps +
                         (size_t)warps * stages * kB8SuperBytes;
-    auto kernel = ks == 4u ? qmv_b8t_kernel<AFFINE, 12, 3, 4>
-                           : (ks == 2u ? qmv_b8t_kernel<AFFINE, 12, 3, 2> : qmv_b8t_kernel<AFFINE, 12, 3, 1>);
-    static SmemOptIn once[3];
-    if (stark_b200_status s = ensure_dynamic_smem(kernel, 220 * 1024, once[ks == 4u ? 2 : (ks == 2u ? 1 : 0)])) return s;
+    const int slot = (wide ? 3 : 0) + (ks == 4u ? 2 : (ks == 2u ? 1 : 0));
+    void (*const kernels[6])(B8Params) = {qmv_b8t_kernel<AFFINE, 12, 3, 1>, qmv_b8t_kernel<AFFINE, 12, 3, 2>,
+                                          qmv_b8t_kernel<AFFINE, 12, 3, 4>, qmv_b8t_kernel<AFFINE, 20, 2, 1>,
+                                          qmv_b8t_kernel<AFFINE, 20, 2, 2>, qmv_b8t_kernel<AFFINE, 20, 2, 4>};
+    auto kernel = kernels[slot];
+    static SmemOptIn once[6];
+    if (stark_b200_status s = ensure_dynamic_smem(kernel, 220 * 1024, once[slot])) return s;
     if (smem > 220u * 1024u) return STARK_B200_UNSUPPORTED;
     const uint32_t teams = warps / ks;
     const uint32_t blocks = std::max(1u, std::min((m->row_tiles + teams - 1u) / teams, (148u + batch - 1u) / batch));

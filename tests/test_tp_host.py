@@ -33,6 +33,35 @@ def _mv(t, x):
     return O.affine_matvec_f32(t["codes"], t["scales"], t["biases"], 30, x, t["n"], t["k"])
 
 
+@pytest.mark.parametrize("ranks", [4, 8])
+def test_four_and_eight_rank_shards_cover_the_model(ranks):
+    """Every rank's shard of the `small` shape (8 KV heads): whole heads, whole quantization groups, and over
+    all ranks the column splits of o and down sum to the unsharded products."""
+    cfg = S.CONFIGS["small"]
+    w = S.dense_weights(cfg, seed=2)
+    rng = np.random.default_rng(9)
+    F = w["layers"][1]
+    a = rng.standard_normal(cfg["q_heads"] * cfg["head_dim"]).astype(np.float32)
+    g = rng.standard_normal(cfg["inter"]).astype(np.float32)
+    o_sum, d_sum, rows = 0.0, 0.0, 0
+    for rank in range(ranks):
+        local, lw, vocab_offset = shard_dense(cfg, w, rank, ranks)
+        L = lw["layers"][1]
+        assert local["q_heads"] * ranks == cfg["q_heads"] and local["kv_heads"] * ranks == cfg["kv_heads"]
+        assert local["inter"] * ranks == cfg["inter"] and local["inter"] % 64 == 0
+        assert L["qkv"]["n"] == (local["q_heads"] + 2 * local["kv_heads"]) * cfg["head_dim"]
+        ql, il = local["q_heads"] * cfg["head_dim"], local["inter"]
+        o_sum = o_sum + _mv(L["o"], a[rank * ql:(rank + 1) * ql]).astype(np.float64)
+        d_sum = d_sum + _mv(L["down"], g[rank * il:(rank + 1) * il]).astype(np.float64)
+        lo, hi = vocab_shard(cfg["vocab"], rank, ranks)
+        assert vocab_offset == lo and lw["lm_head"]["n"] == hi - lo
+        rows += hi - lo
+    assert rows == cfg["vocab"]
+    for got, t, x in ((o_sum, F["o"], a), (d_sum, F["down"], g)):
+        want = _mv(t, x).astype(np.float64)
+        assert np.abs(got - want).max() <= 1e-4 * max(1.0, np.abs(want).max())
+
+
 def _worker(rank: int, ranks: int, port: int, failures):
     import torch.distributed as dist
     try:
