@@ -574,9 +574,14 @@ stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
         SB_TRY(moe_launch(moe_router_select_kernel, c.experts, 256, pdl, s, m->router + (size_t)l * c.experts * H, m->n,
                           m->scores, H, c.experts, A, ids, m->probs, m->arrivals));
         SB_TRY(qmv_rows_launch(m->gate_up[l], m->n, 0, m->gate_out, 2u * A, ids, STARK_B200_F32, s, pdl));
-        SB_TRY(moe_launch(moe_silu_mul_kernel, (A * I + 255u) / 256u, 256, pdl, s, m->gate_out,
-                          m->gate_out + (size_t)A * I, A * I));
-        SB_TRY(qmv_rows_launch(m->down[l], m->gate_out, I, m->expert_out, A, ids, STARK_B200_F32, s, pdl));
+        if (m->down[l]->format == kFmtQ4_K) {  // the gated activation is formed while the down projection stages its input
+            SB_TRY(q4kt_launch(m->down[l], m->gate_out, I, m->expert_out, A, ids, STARK_B200_F32, s, pdl,
+                               m->gate_out + (size_t)A * I));
+        } else {
+            SB_TRY(moe_launch(moe_silu_mul_kernel, (A * I + 255u) / 256u, 256, pdl, s, m->gate_out,
+                              m->gate_out + (size_t)A * I, A * I));
+            SB_TRY(qmv_rows_launch(m->down[l], m->gate_out, I, m->expert_out, A, ids, STARK_B200_F32, s, pdl));
+        }
         // the mixture, the residual add and the next norm: the next layer's, or the final one before the logits
         const float *next = l + 1u < c.layers ? m->norm(STARK_B200_MOE_TENSOR_ATTN_NORM, l + 1u)
                                               : (want_logits ? m->norm(STARK_B200_MOE_TENSOR_FINAL_NORM, 0) : nullptr);
@@ -892,7 +897,7 @@ stark_b200_status stark_b200_moe_model_position(const stark_b200_moe_model *mode
 stark_b200_status stark_b200_moe_model_launches_per_token(const stark_b200_moe_model *model, uint32_t *out_launches) {
     const MoeModel *m = reinterpret_cast<const MoeModel *>(model);
     if (!m || !out_launches) return STARK_B200_INVALID_ARGUMENT;
-    *out_launches = m->nodes ? m->nodes : 4u + 11u * m->cfg.layers;
+    *out_launches = m->nodes ? m->nodes : 4u + 10u * m->cfg.layers;
     return STARK_B200_OK;
 }
 

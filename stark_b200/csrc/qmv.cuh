@@ -119,8 +119,10 @@ void qmatrix_free(QMatrix *m);
 size_t q4kt_bytes(uint32_t experts, uint32_t rows, uint32_t columns);
 stark_b200_status q4kt_retile(const uint8_t *blocks_device, QMatrix *m, cudaStream_t stream);
 // pdl: launch with programmatic stream serialization (the kernel awaits its predecessor itself).
+// x_mul (f32 input only): the input is silu(x) * x_mul, the gated activation of the expert feed-forward.
 stark_b200_status q4kt_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
-                              const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream, bool pdl = false);
+                              const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream, bool pdl = false,
+                              const float *x_mul = nullptr);
 stark_b200_status q4kt_dequantize(const QMatrix *m, uint32_t expert, uint32_t row, float *out_device,
                                   uint8_t *codes_device, cudaStream_t stream);
 

@@ -63,7 +63,26 @@ struct Q4ktParams {
     size_t x_stride;
     void *y;
     uint32_t io_type;
+    const float *x_mul;  // f32 input only: the input is silu(x[i]) * x_mul[i] (the gated activation), nullptr = x
 };
+
+// Element i of launch row b's input.  With x_mul the input is the gated activation of the routed-expert
+// feed-forward, silu(x) * x_mul with the reference's two-branch sigmoid (engine/hybrid/math.rs:5-16,
+// qwen.rs:889-891), formed here instead of in a kernel of its own.
+__device__ inline float load_input(const Q4ktParams &p, uint32_t b, uint32_t i) {
+    const size_t at = (size_t)b * p.x_stride + i;
+    if (p.io_type != STARK_B200_F32) return bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(p.x)[at]);
+    const float g = reinterpret_cast<const float *>(p.x)[at];
+    if (!p.x_mul) return g;
+    float sg;
+    if (g >= 0.0f) {
+        sg = 1.0f / (1.0f + expf(-g));
+    } else {
+        const float e = expf(g);
+        sg = e / (1.0f + e);
+    }
+    return g * sg * p.x_mul[at];
+}
 
 // WARPS x STAGES super-records of shared memory per CTA: how many warps hide the decode latency against how
 // many copies each keeps in flight.
@@ -119,9 +138,7 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_q4kt_kernel(const Q4ktParam
     // ---- input row: exact power-of-two scale into f16 range, head + remainder, per-32 sums ----
     float vmax = 0.0f;
     for (uint32_t i = tid; i < K; i += kQ4Threads) {
-        const float v = p.io_type == STARK_B200_F32
-                            ? reinterpret_cast<const float *>(p.x)[(size_t)b * p.x_stride + i]
-                            : bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(p.x)[(size_t)b * p.x_stride + i]);
+        const float v = load_input(p, b, i);
         vmax = fmaxf(vmax, fabsf(v));
     }
     vmax = warp_max(vmax);
@@ -136,9 +153,7 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_q4kt_kernel(const Q4ktParam
     const float xscale = __uint_as_float((uint32_t)(shift + 127) << 23);
     const float xunscale = __uint_as_float((uint32_t)(127 - shift) << 23);
     for (uint32_t i = tid; i < K; i += kQ4Threads) {  // K is a multiple of 256: every warp sums whole blocks
-        const float v = p.io_type == STARK_B200_F32
-                            ? reinterpret_cast<const float *>(p.x)[(size_t)b * p.x_stride + i]
-                            : bf16_bits_to_f32(reinterpret_cast<const uint16_t *>(p.x)[(size_t)b * p.x_stride + i]);
+        const float v = load_input(p, b, i);
         const float sv = v * xscale;
         const __half h = __float2half_rn(sv);
         xhi[i] = h;
@@ -299,8 +314,10 @@ stark_b200_status q4kt_retile(const uint8_t *blocks, QMatrix *m, cudaStream_t st
 }
 
 stark_b200_status q4kt_launch(const QMatrix *m, const void *x, size_t x_stride, void *y, uint32_t batch,
-                              const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream, bool pdl) {
+                              const uint32_t *expert_ids, uint32_t io_type, cudaStream_t stream, bool pdl,
+                              const float *x_mul) {
     if (m->columns % 256u != 0 || m->columns > 12288u) return STARK_B200_UNSUPPORTED;
+    if (x_mul && io_type != STARK_B200_F32) return STARK_B200_INVALID_ARGUMENT;
     Q4ktParams p{};
     p.data = m->data;
     p.rows = m->rows;
@@ -314,6 +331,7 @@ stark_b200_status q4kt_launch(const QMatrix *m, const void *x, size_t x_stride, 
     p.x_stride = x_stride;
     p.y = y;
     p.io_type = io_type;
+    p.x_mul = x_mul;
     // 12 warps x 3 copies in flight each; teams of 1, 2 or 4 warps per row tile so that a GPU's worth of warps
     // (~24 per SM) has work even when the matrix has few row tiles.  STARK_B200_Q4K_TEAM overrides.
     const uint32_t supers = m->columns / 256u;

@@ -157,7 +157,7 @@ def test_device_decoder_matches_oracle(name):
     model.reset()
     b = model.step(int(prompt[0]))
     assert model.position == 1 and a.tobytes() == b.tobytes()
-    assert model.launches_per_token >= 4 + 11 * cfg["layers"]
+    assert model.launches_per_token >= 4 + 10 * cfg["layers"]
     model.close()
 
 
