@@ -89,13 +89,24 @@ def prompt(cfg: dict, length: int, seed: int = 1) -> np.ndarray:
 
 # ----------------------------------------------------------------------------- GGUF blocks
 
+def _random_bytes(rng: np.random.Generator, count: int, pool: int = 1 << 23) -> np.ndarray:
+    """`count` uniform random bytes.  Beyond `pool` bytes the sequence is one drawn pool repeated, each repeat
+    XORed with its own drawn byte: hundreds of MB of expert banks then cost a copy instead of a draw."""
+    if count <= pool:
+        return rng.integers(0, 256, size=count, dtype=np.uint8)
+    base = rng.integers(0, 256, size=pool, dtype=np.uint8)
+    reps = -(-count // pool)
+    masks = rng.integers(0, 256, size=reps, dtype=np.uint8)
+    return (base[None, :] ^ masks[:, None]).reshape(-1)[:count].copy()
+
+
 def q8_0_rows(rng: np.random.Generator, rows: int, columns: int, scale: float = 0.01) -> np.ndarray:
     """Random Q8_0 rows: per 32 values an f16 scale d ~ U[0.5, 1.5] * scale and 32 int8 codes."""
     blocks = rows * columns // 32
     out = np.empty((blocks, 34), np.uint8)
     d = (rng.uniform(0.5, 1.5, blocks) * scale).astype(np.float16)
     out[:, 0:2] = d.view(np.uint8).reshape(blocks, 2)
-    out[:, 2:] = rng.integers(0, 256, size=(blocks, 32), dtype=np.uint8)
+    out[:, 2:] = _random_bytes(rng, blocks * 32).reshape(blocks, 32)
     return out.reshape(rows, -1)
 
 
@@ -103,7 +114,7 @@ def q4_k_rows(rng: np.random.Generator, rows: int, columns: int, scale: float = 
     """Random Q4_K rows: per 256 values f16 d and dmin, 12 bytes of packed 6-bit (scale, min) pairs, 128
     bytes of nibbles.  d is sized so that d * sc * q stays O(scale)."""
     blocks = rows * columns // 256
-    out = rng.integers(0, 256, size=(blocks, 144), dtype=np.uint8)
+    out = _random_bytes(rng, blocks * 144).reshape(blocks, 144)
     d = (rng.uniform(0.5, 1.5, blocks) * scale / 32.0).astype(np.float16)
     dmin = (rng.uniform(0.5, 1.5, blocks) * scale / 8.0).astype(np.float16)
     out[:, 0:2] = d.view(np.uint8).reshape(blocks, 2)
@@ -126,6 +137,9 @@ MOE_CONFIGS = {
     # the Qwen3-30B-A3B shape: 128 experts, 8 active, expert intermediate 768
     "qwen3-30b-a3b": dict(layers=48, hidden=2048, q_heads=32, kv_heads=4, head_dim=128, experts=128, active=8,
                           inter=768, vocab=151936, eps=1e-6, rope_theta=1e6),
+    # two layers of that shape over a small vocabulary: full-size layer dimensions at test cost
+    "moe-a3b-layers": dict(layers=2, hidden=2048, q_heads=32, kv_heads=4, head_dim=128, experts=128, active=8,
+                           inter=768, vocab=4096, eps=1e-6, rope_theta=1e6),
     "moe-tiny": dict(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=128, experts=8, active=2, inter=256,
                      vocab=512, eps=1e-6, rope_theta=1e6),
     "moe-small": dict(layers=3, hidden=512, q_heads=8, kv_heads=2, head_dim=128, experts=16, active=4, inter=256,

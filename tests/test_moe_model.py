@@ -117,7 +117,7 @@ def _close(got, want, bound=2e-4):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("name", ["moe-tiny", "moe-small"])
+@pytest.mark.parametrize("name", ["moe-tiny", "moe-small", "moe-a3b-layers"])
 def test_device_decoder_matches_oracle(name):
     from stark_b200.engine import MoEModel
     cfg = S.MOE_CONFIGS[name]
