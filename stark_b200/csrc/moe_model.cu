@@ -36,6 +36,7 @@ struct MoeState {
 };
 
 constexpr uint32_t kAttnSplits = 16, kAttnWarps = 8, kMoeMaxAttnSplits = 64;
+constexpr uint32_t kFinishCtas = 64;  // CTAs of the arg-max over the logits
 
 template <int THREADS>
 __device__ inline float block_sum(float v, float *scratch /* [32] */) {
@@ -419,42 +420,75 @@ __global__ void moe_silu_mul_kernel(float *gate, const float *up, uint32_t n) {
     gate[i] = g * sg * up[i];
 }
 
+// (value, first index) of the maximum over the CTA's threads, valid in thread 0.  idx = UINT32_MAX: no entry.
+__device__ inline void block_first_max(float &best, uint32_t &idx, float *bv /* [32] */, uint32_t *bi /* [32] */) {
+    const auto better = [](float ov, uint32_t oi, float v, uint32_t i) {
+        return oi != 0xffffffffu && (i == 0xffffffffu || ov > v || (ov == v && oi < i));
+    };
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (better(ov, oi, best, idx)) best = ov, idx = oi;
+    }
+    __syncthreads();
+    if ((threadIdx.x & 31u) == 0) bv[threadIdx.x >> 5] = best, bi[threadIdx.x >> 5] = idx;
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (uint32_t w = 1; w < blockDim.x / 32u; ++w)
+            if (better(bv[w], bi[w], best, idx)) best = bv[w], idx = bi[w];
+}
+
 // End of a token: with logits, the first index of their maximum becomes `next` (non-finite logits raise
 // the error word, as Model::step refuses them, engine/hybrid/mod.rs:990); the cache grows by one row.
-__global__ void __launch_bounds__(1024) moe_finish_kernel(MoeState *st, const float *logits, uint32_t vocab) {
+// Each CTA scans its share of the row and leaves (maximum, first index, non-finite seen) in `scratch`; the
+// CTA that arrives last reduces those.  Without logits: one CTA, position + 1 only.
+__global__ void __launch_bounds__(1024) moe_finish_kernel(MoeState *st, const float *logits, uint32_t vocab,
+                                                          float *scratch, uint32_t *arrivals) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float bv[32];
     __shared__ uint32_t bi[32];
-    __shared__ int bad_any;
-    if (logits) {
-        float best = -INFINITY;
-        uint32_t idx = 0xffffffffu;
-        int bad = 0;
-        for (uint32_t i = threadIdx.x; i < vocab; i += 1024u) {
-            const float v = logits[i];
-            bad |= !isfinite(v);
-            if (idx == 0xffffffffu || v > best) best = v, idx = i;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const uint32_t oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (oi != 0xffffffffu && (idx == 0xffffffffu || ov > best || (ov == best && oi < idx))) best = ov, idx = oi;
-        }
-        bad = __syncthreads_or(bad);
-        if ((threadIdx.x & 31u) == 0) bv[threadIdx.x >> 5] = best, bi[threadIdx.x >> 5] = idx;
-        if (threadIdx.x == 0) bad_any = bad;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            for (uint32_t w = 1; w < 32u; ++w)
-                if (bi[w] != 0xffffffffu && (idx == 0xffffffffu || bv[w] > best || (bv[w] == best && bi[w] < idx)))
-                    best = bv[w], idx = bi[w];
-            st->next = idx;
-            if (bad_any) st->error |= 2u;
-        }
+    __shared__ bool last;
+    if (!logits) {
+        if (blockIdx.x == 0 && threadIdx.x == 0) st->position += 1u;
+        return;
     }
-    if (threadIdx.x == 0) st->position += 1u;
+    const uint32_t ctas = gridDim.x;
+    float best = -INFINITY;
+    uint32_t idx = 0xffffffffu;
+    int bad = 0;
+    for (uint32_t i = blockIdx.x * 1024u + threadIdx.x; i < vocab; i += ctas * 1024u) {
+        const float v = logits[i];
+        bad |= !isfinite(v);
+        if (idx == 0xffffffffu || v > best) best = v, idx = i;
+    }
+    bad = __syncthreads_or(bad);
+    block_first_max(best, idx, bv, bi);
+    if (threadIdx.x == 0) {
+        scratch[blockIdx.x] = best;
+        scratch[ctas + blockIdx.x] = __uint_as_float(idx);
+        scratch[2u * ctas + blockIdx.x] = bad ? 1.0f : 0.0f;
+        __threadfence();
+        last = atomicAdd(arrivals, 1u) == ctas - 1u;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    best = -INFINITY, idx = 0xffffffffu, bad = 0;
+    if (threadIdx.x < ctas) {
+        best = __ldcg(scratch + threadIdx.x);
+        idx = __float_as_uint(__ldcg(scratch + ctas + threadIdx.x));
+        bad = __ldcg(scratch + 2u * ctas + threadIdx.x) != 0.0f;
+    }
+    bad = __syncthreads_or(bad);
+    block_first_max(best, idx, bv, bi);
+    if (threadIdx.x == 0) {
+        st->next = idx;
+        if (bad) st->error |= 2u;
+        st->position += 1u;
+        *arrivals = 0;  // ready for the next launch
+    }
 }
 
 }  // namespace
@@ -472,7 +506,7 @@ struct MoeModel {
     float *keys = nullptr, *values = nullptr;  // [layers][context][kv_heads * head_dim]
     float *work = nullptr;    // activations, see carve()
     uint32_t *ids = nullptr;  // [layers][2 * active]: the selected experts, then the same + experts
-    uint32_t *arrivals = nullptr;  // the router CTAs' arrival counter (returns to zero by itself)
+    uint32_t *arrivals = nullptr;  // arrival counters of [0] the router CTAs, [1] the arg-max CTAs (they return to zero by themselves)
     MoeState *state = nullptr;
     std::vector<uint8_t> have;  // which tensors were set
     // activations carved out of `work`
@@ -588,7 +622,9 @@ stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
         SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->expert_out, m->probs, A, next, m->n, H, c.rms_eps));
     }
     if (want_logits) SB_TRY(qmv_rows_launch(m->output, m->n, 0, m->logits, 1, nullptr, STARK_B200_F32, s, pdl));
-    SB_TRY(moe_launch(moe_finish_kernel, 1, 1024, pdl, s, m->state, want_logits ? m->logits : nullptr, c.vocab));
+    // the attention partials are free by now: scratch for the per-CTA maxima
+    SB_TRY(moe_launch(moe_finish_kernel, want_logits ? kFinishCtas : 1u, 1024, pdl, s, m->state,
+                      want_logits ? m->logits : nullptr, c.vocab, m->part, m->arrivals + 1));
     return STARK_B200_OK;
 }
 
@@ -703,7 +739,7 @@ stark_b200_status stark_b200_moe_model_create(const stark_b200_moe_config *confi
     ok = ok && cudaMalloc(&m->values, (size_t)c.layers * m->kv_layer() * 4u) == cudaSuccess;
     ok = ok && cudaMalloc(&m->work, total * 4u) == cudaSuccess;
     ok = ok && cudaMalloc(&m->ids, (size_t)c.layers * c.active_experts * 8u) == cudaSuccess;
-    ok = ok && cudaMalloc(&m->arrivals, 4u) == cudaSuccess;
+    ok = ok && cudaMalloc(&m->arrivals, 8u) == cudaSuccess;
     ok = ok && cudaMalloc(&m->state, sizeof(MoeState)) == cudaSuccess;
     if (!ok) {
         cudaGetLastError();
@@ -718,7 +754,7 @@ stark_b200_status stark_b200_moe_model_create(const stark_b200_moe_config *confi
         at += (sizes[i] + 63u) / 64u * 64u;
     }
     cudaMemset(m->ids, 0, (size_t)c.layers * c.active_experts * 8u);
-    cudaMemset(m->arrivals, 0, 4u);
+    cudaMemset(m->arrivals, 0, 8u);
     if (moe_reset(m) != STARK_B200_OK) {
         moe_free(m);
         return STARK_B200_DEVICE_FAILURE;
