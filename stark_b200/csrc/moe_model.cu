@@ -290,20 +290,29 @@ __global__ void __launch_bounds__(kAttnWarps * 32) moe_attention_grouped_kernel(
     }
 }
 
+// Merges the spans' (max, sum, accumulator) states of one head.  The per-span weights exp(m_s - max) are
+// formed once in shared memory, so that the loop over the spans is independent loads and multiply-adds.
 __global__ void __launch_bounds__(128) moe_attention_merge_kernel(const float *part, float *out, uint32_t splits) {
     pdl_launch_dependents();
     pdl_wait();
     constexpr uint32_t D = 128;
+    __shared__ float sm[kMoeMaxAttnSplits], sl[kMoeMaxAttnSplits], sc[kMoeMaxAttnSplits];
     const uint32_t h = blockIdx.x, i = threadIdx.x;
     const float *src = part + (size_t)h * splits * (D + 2u);
+    if (i < splits) {
+        sm[i] = src[i * (D + 2u)];
+        sl[i] = src[i * (D + 2u) + 1u];
+    }
+    __syncthreads();
     float gm = -INFINITY;
-    for (uint32_t s = 0; s < splits; ++s) gm = fmaxf(gm, src[s * (D + 2u)]);
+    for (uint32_t s = 0; s < splits; ++s) gm = fmaxf(gm, sm[s]);
+    if (i < splits) sc[i] = sm[i] == -INFINITY ? 0.0f : expf(sm[i] - gm);  // an empty span weighs nothing
+    __syncthreads();
     float l = 0.0f, a = 0.0f;
+#pragma unroll 8
     for (uint32_t s = 0; s < splits; ++s) {
-        const float m = src[s * (D + 2u)];
-        if (m == -INFINITY) continue;
-        const float c = expf(m - gm);
-        l += src[s * (D + 2u) + 1u] * c;
+        const float c = sc[s];
+        l += sl[s] * c;
         a += src[s * (D + 2u) + 2u + i] * c;
     }
     out[(size_t)h * D + i] = a / l;
