@@ -393,16 +393,21 @@ __global__ void __launch_bounds__(1024) moe_add_norm_kernel(float *x, const floa
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[32];
+    __shared__ float sp[32];  // the mixture weights, read once
+    if (probs && threadIdx.x < active) sp[threadIdx.x] = probs[threadIdx.x];
+    __syncthreads();
     float s = 0.0f;
     for (uint32_t i = threadIdx.x; i < n; i += 1024u) {
         float r;
+        const float xi = x[i];
         if (probs) {
             r = 0.0f;
-            for (uint32_t e = 0; e < active; ++e) r += probs[e] * rows[(size_t)e * n + i];
+#pragma unroll 8
+            for (uint32_t e = 0; e < active; ++e) r += sp[e] * __ldg(rows + (size_t)e * n + i);
         } else {
             r = rows[i];
         }
-        const float v = x[i] + r;
+        const float v = xi + r;
         x[i] = v;
         s += v * v;
     }
