@@ -247,7 +247,8 @@ def run_moe(args, wl) -> None:
             "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
     torch.cuda.set_device(0)
-    model = MoEModel.load(cfg, weights, wl["context"])
+    # rows of cache: the prompt, the warm-up and timed steps, and the end-to-end loop after them
+    model = MoEModel.load(cfg, weights, max(wl["context"], wl["prompt"] + warmup + steps + min(steps, 64) + 8))
     model.ingest(prompt[:-1])
     first = int(model.step(int(prompt[-1])).argmax())
     picks = model.generate_greedy(first, warmup)
