@@ -586,6 +586,16 @@ bool moe_pdl() {
     return on;
 }
 
+// CTAs of the grouped attention kernel over all KV heads (STARK_B200_MOE_ATTN_CTAS overrides).
+uint32_t moe_attention_ctas() {
+    static const uint32_t n = [] {
+        const char *e = getenv("STARK_B200_MOE_ATTN_CTAS");
+        const int v = e ? atoi(e) : 0;
+        return v >= 16 && v <= 1024 ? (uint32_t)v : 256u;
+    }();
+    return n;
+}
+
 stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
     const auto &c = m->cfg;
     const uint32_t H = c.hidden, D = c.head_dim, QH = c.q_heads, KV = c.kv_heads, A = c.active_experts;
@@ -603,7 +613,7 @@ stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
                           m->norm(STARK_B200_MOE_TENSOR_Q_NORM, l), m->norm(STARK_B200_MOE_TENSOR_K_NORM, l), keys, values,
                           QH, KV, D, c.rms_eps, c.rope_theta, c.context_tokens));
         // query heads of one KV head together where the group size has an instantiation, else head by head
-        const uint32_t group = QH / KV, gsplits = std::max(kAttnSplits, std::min(kMoeMaxAttnSplits, 256u / KV));
+        const uint32_t group = QH / KV, gsplits = std::max(kAttnSplits, std::min(kMoeMaxAttnSplits, moe_attention_ctas() / KV));
         uint32_t splits = kAttnSplits;
         if (group == 8u || group == 4u || group == 2u) {
             splits = gsplits;
