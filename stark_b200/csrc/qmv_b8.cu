@@ -48,6 +48,7 @@ struct B8Params {
     size_t x_stride;
     void *y;
     uint32_t io_type;
+    uint32_t team_major;
 };
 
 // WARPS x STAGES super-records of shared memory per CTA: how many warps hide the decode latency against how
@@ -79,7 +80,9 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_b8t_kernel(const B8Params p
     }
     const uint8_t *base = p.data + (size_t)expert * p.expert_bytes;
     const uint32_t team = warp / KS, member = warp % KS;
-    const uint32_t gw = blockIdx.x * kTeams + team, nw = gridDim.x * kTeams;  // teams, not warps
+    // teams, not warps; team-major numbering spreads few row tiles over many CTAs (one busy team in each)
+    const uint32_t nw = gridDim.x * kTeams;
+    const uint32_t gw = p.team_major ? team * gridDim.x + blockIdx.x : blockIdx.x * kTeams + team;
     const uint32_t my_tiles = gw < p.row_tiles ? (p.row_tiles - gw + nw - 1u) / nw : 0u;
     const uint32_t items = my_tiles * (p.supers / KS);  // the launcher makes KS divide the super-block count
 
@@ -339,7 +342,14 @@ stark_b200_status launch_b8(const QMatrix *m, const B8Params &p, uint32_t batch,
     if (stark_b200_status s = ensure_dynamic_smem(kernel, 220 * 1024, once[slot])) return s;
     if (smem > 220u * 1024u) return STARK_B200_UNSUPPORTED;
     const uint32_t teams = warps / ks;
-    const uint32_t blocks = std::max(1u, std::min((m->row_tiles + teams - 1u) / teams, (148u + batch - 1u) / batch));
+    uint32_t blocks = std::max(1u, std::min((m->row_tiles + teams - 1u) / teams, (148u + batch - 1u) / batch));
+    B8Params q = p;
+    // A matrix whose row tiles fill fewer than half the SMs (a 2048-row projection: 43 CTAs) is bound by what
+    // one SM can pull: one team per CTA on up to 148 CTAs instead.
+    if (batch == 1u && blocks * 2u <= 148u && m->row_tiles > blocks) {
+        q.team_major = 1u;
+        blocks = std::min(m->row_tiles, 148u);
+    }
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(blocks, batch);
     cfg.blockDim = dim3(warps * 32u);
@@ -350,7 +360,7 @@ stark_b200_status launch_b8(const QMatrix *m, const B8Params &p, uint32_t batch,
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+    SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, q));
     return STARK_B200_OK;
 }
 
