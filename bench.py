@@ -40,6 +40,15 @@ BYTES_PER_WEIGHT = 0.5625  # 4-bit codes + bf16 scale and bias per 64 columns
 DRAM_TRAFFIC_RATIO = 1.011  # measured dram bytes / algorithmic bytes of the 4-bit matvec (ncu, 151936x4096)
 
 
+def host_threads() -> int:
+    """Host cores this process may run on.  Passed to the CPU arm explicitly: launchers such as
+    torch.distributed.run export OMP_NUM_THREADS=1, which would otherwise pin it to one core."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
 def peaks() -> tuple[float, str]:
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -77,7 +86,7 @@ class ClockSampler:
              "clocks_event_reasons.sw_power_cap")
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
@@ -101,8 +110,11 @@ class ClockSampler:
         mx = [float(r[1]) for r in self.rows if len(r) >= 7 and r[1].replace(".", "").isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(len(r) >= 7 and r[3 + i] == "Active" for r in self.rows)]
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+        out = {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+               "reasons": reasons, "samples": len(sm)}
+        if not sm:
+            out["note"] = "unavailable: nvidia-smi returned no sample during the timed region"
+        return out
 
 
 def cpu_sample(cfg: dict, weights: dict, prompt: np.ndarray, prompt_rows: int, steps: int, threads: int) -> dict:
@@ -231,7 +243,7 @@ def run_moe(args, wl) -> None:
         return
     weights = moe_weights_cycled(cfg, args.seed)
     prompt = S.prompt(cfg, wl["prompt"], seed=args.seed + 1)
-    threads = os.cpu_count() or 1
+    threads = host_threads()
     if args.impl == "reference":
         sample_steps = max(1, min(args.steps, 4))
         rows = min(wl["prompt"], 16)
@@ -294,8 +306,8 @@ def run_reference(args, wl, cfg) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    threads = host_threads()
     from oracle import oracle as O
-    threads = O.max_threads()
     weights = S.dense_weights(cfg, seed=args.seed)
     prompt = S.prompt(cfg, wl["prompt"], seed=args.seed + 1)
     # bounded sample: a short prompt, then `warmup` untimed and `steps` timed decode steps
@@ -312,12 +324,13 @@ def run_reference(args, wl, cfg) -> None:
         tok = O.argmax_bf16(orc.step(tok))
     dt = time.perf_counter() - t0
     value = steps / dt
-    sample = f"{steps} greedy decode steps after an 8-token prompt (CPU oracle port, OpenMP over rows)"
+    sample = (f"{steps} greedy decode steps at 8 to {8 + warm + steps} rows of context (CPU oracle port, OpenMP over "
+              f"rows, {threads} threads)")
     print(json.dumps({
         "impl": "reference", "metric": "batch-1 decode tok/s", "value": value, "unit": "tok/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": warm, "ms_per_step": 1e3 * dt / steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": f"{wl['cfg']} 4-bit MLX-affine g64, batch 1, greedy decode"},
+        "config": {"workload": f"{wl['cfg']} 4-bit MLX-affine g64, batch 1, greedy decode; CPU arm: {sample}"},
         "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -331,6 +344,8 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="qwen3-8b", choices=sorted(WORKLOADS))
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--repeats", type=int, default=0,
+                    help="timed regions of --steps tokens each (0: at least 5, enough for 0.3 s of load)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--parallel", default="tp", choices=["tp", "replicas"],
                     help="N > 1: shard the one token stream over the GPUs (tensor parallel, strong scaling) or "
@@ -375,7 +390,12 @@ def main() -> None:
             tp = TensorParallel(rank, world, all_gather)
 
     steps, warmup = args.steps, max(args.warmup, 3)
-    context = max(wl["context"], wl["prompt"] + warmup + 2 * steps + 8)
+    # The timed region is `steps` tokens; it is taken `repeats` times back to back (the cache keeps growing)
+    # and the median region is the value, so that a 20-step region of 30 ms does not decide the line alone
+    # and the clock sampler sees at least 0.3 s of load.
+    repeats = args.repeats if args.repeats > 0 else max(5, min(64, -(-320 // max(steps, 1))))
+    e2e_steps = min(steps, 256)
+    context = max(wl["context"], wl["prompt"] + warmup + repeats * steps + 8, wl["prompt"] + warmup + repeats * e2e_steps + 8)
     weights = S.dense_weights(cfg, seed=args.seed)
     prompt = S.prompt(cfg, wl["prompt"], seed=args.seed + 1)
     model = DenseModel.load(cfg, weights, context_tokens=context, tp=tp)
@@ -388,35 +408,39 @@ def main() -> None:
         torch.cuda.synchronize()
 
     # ---- device-timed decode: tokens chained on the device, inputs resident in HBM ------------
+    t_prefill = time.perf_counter()
     model.prefill(prompt)
     model.drain()
+    prefill_s = time.perf_counter() - t_prefill
     model.generate_greedy(warmup)
     barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(repeats + 1)]
     with ClockSampler(local) as clocks:
-        e0.record(stream)
-        model.generate_greedy(steps)
-        e1.record(stream)
+        events[0].record(stream)
+        for r in range(repeats):
+            model.generate_greedy(steps)
+            events[r + 1].record(stream)
         barrier()
-    ms = e0.elapsed_time(e1)
-    assert take_device_error() == 0, "a kernel reported a timed-out wait"
-    mean_context = wl["prompt"] + warmup + steps / 2.0
+        regions = [events[r].elapsed_time(events[r + 1]) for r in range(repeats)]
+        assert take_device_error() == 0, "a kernel reported a timed-out wait"
+        mean_context = wl["prompt"] + warmup + repeats * steps / 2.0
 
-    # ---- end to end through the public API: host token in, host result out, every step --------
-    model.reset()
-    model.prefill(prompt)
-    tok = model.argmax()
-    for _ in range(warmup):
-        model.step_async(tok)
+        # ---- end to end through the public API: host token in, host result out, every step --------
+        model.reset()
+        model.prefill(prompt)
         tok = model.argmax()
-    barrier()
-    e2e_steps = min(steps, 256)
-    t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        model.step_async(tok)   # 4-byte host->device token copy
-        tok = model.argmax()    # 16-byte device->host read of the step result
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
+        for _ in range(warmup):
+            model.step_async(tok)
+            tok = model.argmax()
+        barrier()
+        e2e_regions = []
+        for r in range(repeats):
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                model.step_async(tok)   # 4-byte host->device token copy
+                tok = model.argmax()    # 16-byte device->host read of the step result
+            torch.cuda.synchronize()
+            e2e_regions.append(time.perf_counter() - t0)
 
     # ---- the second request of the workload: shares a prefix with the first, reuses its KV rows ----
     reuse = None
@@ -436,11 +460,13 @@ def main() -> None:
         reuse = {"shared_prefix_tokens": int(shared), "rows_reused": int(rows),
                  "rows_recomputed": int(len(second) - rows), "prefill_ms": 1e3 * (time.perf_counter() - t0)}
 
-    t = torch.tensor([ms, e2e_s], dtype=torch.float64, device="cuda")
+    # every region is the max over ranks (a token is done when the slowest rank is); then the median region
+    t = torch.tensor(regions + e2e_regions, dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, e2e_s = float(t[0]), float(t[1])
-    streams = 1 if tp is not None else world  # tensor parallel: all GPUs work on the one token stream
+    regions, e2e_regions = t[:repeats].tolist(), t[repeats:].tolist()
+    ms, e2e_s = float(np.median(regions)), float(np.median(e2e_regions))
+    streams = 1 if (tp is not None or world == 1) else world  # tensor parallel: all GPUs work on the one token stream
     value = streams * steps / (ms / 1e3)
     e2e_value = streams * e2e_steps / e2e_s
 
@@ -452,16 +478,23 @@ def main() -> None:
     line = {
         "metric": "batch-1 decode tok/s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": steps,
         "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,
-        "scaling": "strong" if tp is not None else "weak",
+        # one token stream however many GPUs work on it (tensor parallel): strong scaling at every N, N = 1
+        # included; independent replicas are the weak-scaling alternative
+        "scaling": "weak" if (world > 1 and tp is None) else "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{wl['cfg']} 4-bit MLX-affine g64, batch 1, {wl['prompt']}-token prompt, greedy decode",
                    "parallelism": "tp1" if world == 1 else (f"tp{world}" if tp is not None
                                                             else f"{world} independent replicas"),
                    "l2": "per-step inputs (weights %.2f GB + KV) exceed the 126 MB L2" % (info.weight_bytes / 1e9),
-                   "mean_context_rows": mean_context, "prefix_reuse": reuse},
+                   "mean_context_rows": mean_context, "prefix_reuse": reuse,
+                   "timed_regions": {"repeats": repeats, "steps_each": steps, "value_from": "median region",
+                                     "ms_per_step_min": min(regions) / steps, "ms_per_step_max": max(regions) / steps,
+                                     "e2e_tok_s_min": streams * e2e_steps / max(e2e_regions),
+                                     "e2e_tok_s_max": streams * e2e_steps / min(e2e_regions)},
+                   "prompt_ingest_ms": 1e3 * prefill_s},
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 16,
                 "steps": e2e_steps},
-        "gpu_launches": int(steps * info.launches_per_step),
+        "gpu_launches": int(repeats * steps * info.launches_per_step),
         "clocks": clocks.summary(),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "traffic": DRAM_TRAFFIC_RATIO * algo / (world if tp is not None else 1),
@@ -475,7 +508,7 @@ def main() -> None:
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import oracle as O
         n = 2 if cfg["layers"] >= 28 else 8
-        line["cpu_baseline"] = cpu_sample(cfg, weights, prompt, 8, n, O.max_threads())
+        line["cpu_baseline"] = cpu_sample(cfg, weights, prompt, 8, n, host_threads())
     if rank == 0:
         print(json.dumps(line))
     model.close()

@@ -399,12 +399,20 @@ stark_b200_status stark_b200_generate_greedy(stark_b200_model *model, uint32_t s
 stark_b200_status stark_b200_rewind(stark_b200_model *model, uint64_t position);
 stark_b200_status stark_b200_get_info(stark_b200_model *model, stark_b200_info *info);
 /* Per-launch timeline of the token sequences issued since the last call: for each of the
- * launches_per_step kernels, four device-clock values in ns {first CTA entered, wait on the previous
- * kernel returned, last prologue done, last CTA left}.  Only available when the library was started
+ * launches_per_step kernels, six device-clock values in ns {first CTA entered, first wait on the previous
+ * kernel returned, last prologue done, last CTA left, last CTA entered, last wait returned}.  Only available when the library was started
  * with STARK_B200_TRACE=1 (UNSUPPORTED otherwise); the analogue of the reference's aggregate
- * profiler (crates/stark-engine/src/engine/hybrid/profile.rs:1-89).  count = 4 * Info.trace_slots
+ * profiler (crates/stark-engine/src/engine/hybrid/profile.rs:1-89).  count = 6 * Info.trace_slots
  * (one slot per launch, or per operator of the persistent kernel). */
 stark_b200_status stark_b200_read_trace(stark_b200_model *model, uint64_t *dst, size_t count);
+/* Launch-shape settings of the decode kernels (no counterpart in the reference, whose Metal pipelines
+ * fix their threadgroup shapes at build time).  Names: "qmv_consumer_warps" (8 | 16), "qmv_smem_kb",
+ * "qmv_ctas_per_sm", "qmv_fold" (0 | 1 | 2), "attn_bufs" (2 | 3), "attn_splits", "pdl" (0 | 1); each
+ * starts from the environment variable STARK_B200_<NAME IN CAPITALS>-style switch read at first use.
+ * A model uses new values once stark_b200_model_recapture has recorded its launch sequences again
+ * (cache and position are kept; single-GPU models only). */
+stark_b200_status stark_b200_set_tunable(const char *name, uint32_t value);
+stark_b200_status stark_b200_model_recapture(stark_b200_model *model);
 /* The CUDA stream (cudaStream_t) the model's work is issued on, for callers that time it with
  * their own events. */
 stark_b200_status stark_b200_model_stream(stark_b200_model *model, void **out_stream);

@@ -153,6 +153,8 @@ def load() -> C.CDLL:
         "stark_b200_rewind": (u32, [vp, u64]),
         "stark_b200_get_info": (u32, [vp, C.POINTER(Info)]),
         "stark_b200_model_stream": (u32, [vp, C.POINTER(vp)]),
+        "stark_b200_set_tunable": (u32, [C.c_char_p, u32]),
+        "stark_b200_model_recapture": (u32, [vp]),
         "stark_b200_read_trace": (u32, [vp, vp, sz]),
         "stark_b200_moe_model_create": (u32, [C.POINTER(MoeConfig), C.POINTER(vp)]),
         "stark_b200_moe_model_set_matrix": (u32, [vp, u32, u32, vp]),

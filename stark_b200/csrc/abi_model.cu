@@ -5,6 +5,7 @@
 #include <vector>
 
 #include "model.cuh"
+#include "tunables.cuh"
 
 using namespace sb;
 
@@ -432,6 +433,16 @@ stark_b200_status stark_b200_generate_greedy(stark_b200_model *model, uint32_t s
 stark_b200_status stark_b200_rewind(stark_b200_model *model, uint64_t position) {
     if (!model) return STARK_B200_INVALID_ARGUMENT;
     return model_rewind(M(model), position);
+}
+
+stark_b200_status stark_b200_set_tunable(const char *name, uint32_t value) {
+    return set_tunable(name, value) ? STARK_B200_OK : STARK_B200_INVALID_ARGUMENT;
+}
+
+stark_b200_status stark_b200_model_recapture(stark_b200_model *model) {
+    if (!model) return STARK_B200_INVALID_ARGUMENT;
+    if (M(model)->tp.size > 1u) return STARK_B200_UNSUPPORTED;
+    return model_recapture(M(model));
 }
 
 stark_b200_status stark_b200_model_stream(stark_b200_model *model, void **out_stream) {

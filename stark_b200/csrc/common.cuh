@@ -137,11 +137,13 @@ __device__ inline uint4 ldg_nc_v4(const void *p) {
 }
 
 // ---- optional in-kernel timeline (off unless a trace buffer is passed) ---------------------------
-// One slot per launch of a recorded token sequence: when the first CTA entered, when its wait on
-// the previous kernel returned, when the last CTA finished its prologue, when the last CTA left.
+// One slot per launch of a recorded token sequence: when the first CTA entered, when the first wait on
+// the previous kernel returned, when the last CTA finished its prologue, when the last CTA left, and
+// when the last CTA entered / saw its wait return (how far the CTAs of a launch are spread).
 struct TraceSlot {
-    unsigned long long start, ready, compute, end;
+    unsigned long long start, ready, compute, end, start_last, ready_last;
 };
+constexpr unsigned kTraceFields = 6;
 __device__ inline unsigned long long global_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

@@ -31,14 +31,19 @@ struct AttnShared {
     uint16_t *knew, *vnew;            // [kHeadDim] the appended key / value row
     float (*ml_s)[kMaxGqa][2];        // [kAttnWarps] per-warp (max, sum)
 };
-constexpr uint32_t kAttnSharedBytes =
-    kAttnSmemBytes + kMaxGqa * kHeadDim * 2u + 2u * kHeadDim * 2u + kAttnWarps * kMaxGqa * 2u * 4u;
+// nbuf = K / V tile pairs in flight (2: double buffered; 3: a split of up to three pages is fetched whole
+// before the new row exists).
+__host__ __device__ constexpr uint32_t attn_shared_bytes(uint32_t nbuf) {
+    return nbuf * 2u * kTileBytes + kMaxGqa * kHeadDim * 2u + 2u * kHeadDim * 2u + kAttnWarps * kMaxGqa * 2u * 4u;
+}
+constexpr uint32_t kAttnSharedBytes = attn_shared_bytes(2);
 
-__device__ inline AttnShared carve_attn_shared(uint8_t *base /* 128-byte aligned */) {
+__device__ inline AttnShared carve_attn_shared(uint8_t *base /* 128-byte aligned */, uint32_t nbuf = 2) {
     AttnShared s;
+    const uint32_t tile_bytes = nbuf * 2u * kTileBytes;
     s.tiles = base;
-    s.q_s = reinterpret_cast<uint16_t(*)[kHeadDim]>(base + kAttnSmemBytes);
-    s.knew = reinterpret_cast<uint16_t *>(base + kAttnSmemBytes + kMaxGqa * kHeadDim * 2u);
+    s.q_s = reinterpret_cast<uint16_t(*)[kHeadDim]>(base + tile_bytes);
+    s.knew = reinterpret_cast<uint16_t *>(base + tile_bytes + kMaxGqa * kHeadDim * 2u);
     s.vnew = s.knew + kHeadDim;
     s.ml_s = reinterpret_cast<float(*)[kMaxGqa][2]>(s.vnew + kHeadDim);
     return s;
@@ -71,19 +76,21 @@ __device__ inline void attn_split_range(const AttnParams &p, uint32_t split, uin
     b1 = (uint32_t)(((uint64_t)(split + 1u) * nblocks) / p.splits);
 }
 
-// Starts the copies of the split's first two tiles (two cp.async groups, possibly empty) and loads the
+// Starts the copies of the split's first NBUF tiles (NBUF cp.async groups, possibly empty) and loads the
 // constants.  Touches nothing the kernel before this one writes, provided `pos` is already final; the
 // caller checks that after its wait and calls this again if it was not.
+template <int NBUF = 2>
 __device__ inline void attention_prefetch(const AttnParams &p, uint32_t split, uint32_t h, uint32_t pos,
                                           const AttnShared &sm, uint32_t tid, AttnPrefetch &pf) {
     pf.pos = pos;
     uint32_t b0, b1;
     attn_split_range(p, split, pos, b0, b1);
     if (tid < (uint32_t)kAttnThreads) {
-        if (b1 > b0) attn_issue_tile(p, h, b0, 0u, sm.tiles, tid);
-        cp_async_commit();
-        if (b1 > b0 + 1u) attn_issue_tile(p, h, b0 + 1u, 1u, sm.tiles, tid);
-        cp_async_commit();
+#pragma unroll
+        for (uint32_t i = 0; i < (uint32_t)NBUF; ++i) {
+            if (b1 > b0 + i) attn_issue_tile(p, h, b0 + i, i, sm.tiles, tid);
+            cp_async_commit();
+        }
         const float *cosr = p.rope_cos ? p.rope_cos + (size_t)pos * kHeadDim : nullptr;
         const float *sinr = p.rope_sin ? p.rope_sin + (size_t)pos * kHeadDim : nullptr;
         pf.cq = load_head_consts(p.q_norm, cosr, sinr, tid & 31u);
@@ -100,7 +107,7 @@ __device__ inline void attention_prefetch(const AttnParams &p, uint32_t split, u
 // are the M rows) and the same online softmax in f32, then O += P V for its own 32 of the 128 output
 // dims, with P carried as bf16 hi + lo so that the weights keep ~16 bits.  Warps only synchronise to
 // hand tile buffers over.  Inputs written by other CTAs of a running kernel are read with ld.cg.
-template <int BAR_ID, int BAR_THREADS>
+template <int BAR_ID, int BAR_THREADS, int NBUF = 2>
 __device__ inline void attention_partial(const AttnParams &p, uint32_t split, uint32_t h, uint32_t pos,
                                          const AttnShared &sm, uint32_t tid, const AttnPrefetch &pf) {
     const uint32_t lane = tid & 31u, warp = tid >> 5, G = p.gqa;
@@ -115,16 +122,33 @@ __device__ inline void attention_partial(const AttnParams &p, uint32_t split, ui
     uint8_t *tiles = sm.tiles;
 
     // Norm + RoPE: one warp per head (the G query heads, then the new key row on the owner split).
+    // All rows a warp needs are requested before the first is used: the owner split's extra row must not
+    // cost a second trip to memory, because the slowest CTA sets the kernel's duration.
     if (worker) {
-        for (uint32_t hh = warp; hh < G + 1u; hh += kAttnWarps) {
+        constexpr uint32_t kMaxHeadsPerWarp = (kMaxGqa + 1u + kAttnWarps - 1u) / kAttnWarps;
+        uint32_t raw_lo[kMaxHeadsPerWarp], raw_hi[kMaxHeadsPerWarp];
+        uint2 vv = make_uint2(0u, 0u);
+#pragma unroll
+        for (uint32_t i = 0; i < kMaxHeadsPerWarp; ++i) {
+            const uint32_t hh = warp + i * kAttnWarps;
+            const uint16_t *row = nullptr;
+            if (hh < G) row = p.qkv + (size_t)(h * G + hh) * kHeadDim;
+            else if (hh == G && owner) row = p.qkv + (size_t)(p.q_heads + h) * kHeadDim;
+            raw_lo[i] = raw_hi[i] = 0u;
+            if (row) load_head_row(row, lane, raw_lo[i], raw_hi[i]);
+            if (hh == G && owner)
+                vv = __ldcg(reinterpret_cast<const uint2 *>(p.qkv + (size_t)(p.q_heads + p.kv_heads + h) * kHeadDim +
+                                                            4u * lane));
+        }
+#pragma unroll
+        for (uint32_t i = 0; i < kMaxHeadsPerWarp; ++i) {
+            const uint32_t hh = warp + i * kAttnWarps;
             if (hh < G) {
-                warp_head_norm_rope(p.qkv + (size_t)(h * G + hh) * kHeadDim, pf.cq, p.q_norm != nullptr,
-                                    p.rope_cos != nullptr, p.eps, lane, sm.q_s[hh]);
-            } else if (owner) {
-                warp_head_norm_rope(p.qkv + (size_t)(p.q_heads + h) * kHeadDim, pf.ck, p.k_norm != nullptr,
-                                    p.rope_cos != nullptr, p.eps, lane, sm.knew);
-                const uint2 vv = __ldcg(reinterpret_cast<const uint2 *>(
-                    p.qkv + (size_t)(p.q_heads + p.kv_heads + h) * kHeadDim + 4u * lane));
+                head_norm_rope_regs(raw_lo[i], raw_hi[i], pf.cq, p.q_norm != nullptr, p.rope_cos != nullptr, p.eps, lane,
+                                    sm.q_s[hh]);
+            } else if (hh == G && owner) {
+                head_norm_rope_regs(raw_lo[i], raw_hi[i], pf.ck, p.k_norm != nullptr, p.rope_cos != nullptr, p.eps, lane,
+                                    sm.knew);
                 *reinterpret_cast<uint2 *>(sm.vnew + 4u * lane) = vv;
             }
         }
@@ -162,11 +186,11 @@ __device__ inline void attention_partial(const AttnParams &p, uint32_t split, ui
     const uint32_t k0 = warp * 16u;  // this warp's keys within a tile
 
     for (uint32_t tile = 0; tile < ntiles; ++tile) {
-        // groups in flight: this tile's and the next one's (one group is committed per iteration, empty
-        // past the end, so the count is uniform)
-        if (worker) cp_async_wait<1>();
+        // groups in flight: this tile's and the NBUF - 1 after it (one group is committed per iteration,
+        // empty past the end, so the count is uniform)
+        if (worker) cp_async_wait<NBUF - 1>();
         named_bar_sync(BAR_ID, BAR_THREADS);
-        const uint32_t buf = tile & 1u;
+        const uint32_t buf = tile % (uint32_t)NBUF;
         uint8_t *kt = tiles + (size_t)(buf * 2u) * kTileBytes, *vt = kt + kTileBytes;
         const uint32_t blk = b0 + tile;
         if (blk == new_block) {
@@ -243,9 +267,9 @@ __device__ inline void attention_partial(const AttnParams &p, uint32_t split, ui
                 mma_m16n8k16_bf16(o[mt], va4[0], va4[1], va4[2], va4[3], bl[0], bl[1]);
             }
         }
-        named_bar_sync(BAR_ID, BAR_THREADS);  // the buffer of this tile is free for tile + 2
+        named_bar_sync(BAR_ID, BAR_THREADS);  // the buffer of this tile is free for tile + NBUF
         if (worker) {
-            if (tile + 2u < ntiles) attn_issue_tile(p, h, b0 + tile + 2u, tile & 1u, tiles, tid);
+            if (tile + (uint32_t)NBUF < ntiles) attn_issue_tile(p, h, b0 + tile + (uint32_t)NBUF, buf, tiles, tid);
             cp_async_commit();
         }
     }
@@ -326,7 +350,7 @@ __device__ inline void attention_merge(const AttnParams &p, uint32_t h, float *w
         const float w = ms == -INFINITY ? 0.0f : expf(ms - mmax);
         const float inv = 1.0f / warp_sum(w * ls);
         float2 a0 = make_float2(0.0f, 0.0f), a1 = make_float2(0.0f, 0.0f);
-#pragma unroll 8
+#pragma unroll 16
         for (uint32_t sp = 0; sp < p.splits; ++sp) {
             const float ws = __shfl_sync(0xffffffffu, w, sp);
             const float *row = base + (size_t)(sp * G + gg) * stride;  // 520-byte rows: 8-byte aligned

@@ -15,22 +15,33 @@ constexpr uint32_t kAttnSmemBytes = 4u * kTileBytes;  // K and V, double buffere
 
 // 4-bit -> f16 conversion of one record word into an m16n8k16 A fragment.
 //   (w & 0x000f000f) | 0x64006400 is the f16 pair (1024 + q, 1024 + q');
-//   (w & 0x00f000f0) | 0x64006400 is (1024 + 16 q, ...).
-// FOLD == false: the offsets are removed here, exactly (x - 1024; x/16 - 64 in one FMA), so the
-//   tensor core sees the integers q.
-// FOLD == true: the patterns go to the tensor core as they are and the offsets are removed from
-//   the f32 group sums afterwards (row g: c - 1024 sum(x); row g+8: c/16 - 64 sum(x)).  That halves
-//   the instruction count of the extraction; the accumulation then carries 1024 x + q x, which
-//   costs about 7 bits of the f32 accumulator.
-template <bool FOLD>
+//   (w & 0x00f000f0) | 0x64006400 is (1024 + 16 q, ...);
+//   (w & 0x00f000f0) | 0x54005400 is (64 + q, ...): 0x5400 is 64.0 and bit 4 of an f16 in [64, 128) weighs 1.
+// FOLD == 0: the offsets are removed here, exactly (x - 1024; x/16 - 64 in one FMA), so the tensor core
+//   sees the integers q: 9 instructions per 8 codes.
+// FOLD == 1: the first two patterns go to the tensor core as they are and the offsets are removed from
+//   the f32 group sums afterwards (row g: c - 1024 sum(x); row g+8: c/16 - 64 sum(x)): 5 instructions.
+//   The accumulation then carries 1024 x + q x, which costs about 7 bits of the f32 accumulator.
+// FOLD == 2: every nibble is shifted to bits 4..7 of its half and becomes 64 + q; both row halves carry
+//   64 x + q x and the group sums lose 64 sum(x): 7 instructions, about 3 bits of the accumulator --
+//   less than what a sequential f32 sum over a row of a few thousand products loses anyway.
+template <int FOLD>
 __device__ inline void dequant_a4_word(uint32_t w, uint32_t (&a)[4]) {
+    if (FOLD == 2) {
+        const uint32_t magic64 = 0x54005400u, mask = 0x00f000f0u;
+        a[0] = lop3_and_or(w << 4, mask, magic64);
+        a[1] = lop3_and_or(w, mask, magic64);
+        a[2] = lop3_and_or(w >> 4, mask, magic64);
+        a[3] = lop3_and_or(w >> 8, mask, magic64);
+        return;
+    }
     const uint32_t magic = 0x64006400u;
     const uint32_t lo0 = lop3_and_or(w, 0x000f000fu, magic);
     const uint32_t hi0 = lop3_and_or(w, 0x00f000f0u, magic);
     const uint32_t w8 = w >> 8;
     const uint32_t lo1 = lop3_and_or(w8, 0x000f000fu, magic);
     const uint32_t hi1 = lop3_and_or(w8, 0x00f000f0u, magic);
-    if (FOLD) {
+    if (FOLD == 1) {
         a[0] = lo0;
         a[1] = hi0;
         a[2] = lo1;
@@ -110,11 +121,14 @@ __device__ inline HeadConsts load_head_consts(const float *norm_w, const float *
     }
     return c;
 }
-__device__ inline void warp_head_norm_rope(const uint16_t *head, const HeadConsts &c, bool has_norm, bool has_rope,
-                                           float eps, uint32_t lane, uint16_t *out /* smem [128] */) {
+// The lane's four values of a head row (two packed bf16 pairs).
+__device__ inline void load_head_row(const uint16_t *head, uint32_t lane, uint32_t &lo2, uint32_t &hi2) {
     // ld.cg: the row may have been written by another CTA of a kernel that is still running
-    const uint32_t lo2 = __ldcg(reinterpret_cast<const uint32_t *>(head + 2u * lane));
-    const uint32_t hi2 = __ldcg(reinterpret_cast<const uint32_t *>(head + 64u + 2u * lane));
+    lo2 = __ldcg(reinterpret_cast<const uint32_t *>(head + 2u * lane));
+    hi2 = __ldcg(reinterpret_cast<const uint32_t *>(head + 64u + 2u * lane));
+}
+__device__ inline void head_norm_rope_regs(uint32_t lo2, uint32_t hi2, const HeadConsts &c, bool has_norm, bool has_rope,
+                                           float eps, uint32_t lane, uint16_t *out /* smem [128] */) {
     float v[4] = {__uint_as_float(lo2 << 16), __uint_as_float(lo2 & 0xffff0000u), __uint_as_float(hi2 << 16),
                   __uint_as_float(hi2 & 0xffff0000u)};
     // The roundings go through the packed hardware conversion (round to nearest even, like the reference's
@@ -144,6 +158,12 @@ __device__ inline void warp_head_norm_rope(const uint16_t *head, const HeadConst
     }
     *reinterpret_cast<uint32_t *>(out + 2u * lane) = lo_pair;
     *reinterpret_cast<uint32_t *>(out + 64u + 2u * lane) = hi_pair;
+}
+__device__ inline void warp_head_norm_rope(const uint16_t *head, const HeadConsts &c, bool has_norm, bool has_rope,
+                                           float eps, uint32_t lane, uint16_t *out /* smem [128] */) {
+    uint32_t lo2, hi2;
+    load_head_row(head, lane, lo2, hi2);
+    head_norm_rope_regs(lo2, hi2, c, has_norm, has_rope, eps, lane, out);
 }
 __device__ inline void warp_head_norm_rope(const uint16_t *head, const float *norm_w, const float *cosr,
                                            const float *sinr, float eps, uint32_t lane, uint16_t *out) {

@@ -251,7 +251,7 @@ __device__ inline void consume_gemv(const Ctx &c, const MegaOp &op, float xunsca
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         uint32_t a[4];
-                        dequant_a4_word<false>(ww[j], a);
+                        dequant_a4_word<0>(ww[j], a);
                         mma_m16n8k16_f16(acc, a, xw[2 * j], xw[2 * j + 1]);
                     }
                     const float xs_g = c.xsum[kg0 + warp + (uint32_t)kCW * i];

@@ -14,6 +14,7 @@
 // then logits = W_head rmsnorm(h) with the greedy read-out fused into the matvec epilogue.
 #include "model.cuh"
 #include "mega.cuh"
+#include "tunables.cuh"
 
 #include <cmath>
 #include <cstring>
@@ -35,13 +36,7 @@ stark_b200_status dmalloc(T **p, size_t count) {
 // read-out shard of this rank).
 uint32_t input_vocab(const Model *m) { return m->tp.size > 1u ? m->tp_vocab_total : m->cfg.vocab; }
 
-bool pdl_on() {
-    static const bool on = [] {
-        const char *e = getenv("STARK_B200_PDL");
-        return !(e && e[0] == '0');
-    }();
-    return on;
-}
+bool pdl_on() { return tunables().pdl != 0u; }
 
 }  // namespace
 
@@ -158,10 +153,7 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     // resident CTAs of the matvec before it and fetches its cache tiles while that matvec runs; more
     // splits than that start cold.
     m->attn_splits = std::min<uint32_t>(kMaxAttnSplits, std::max<uint32_t>(1u, 192u / c.kv_heads));
-    if (const char *e = getenv("STARK_B200_ATTN_SPLITS")) {  // tuning: CTAs per KV head
-        const int v = atoi(e);
-        if (v >= 1 && v <= (int)kMaxAttnSplits) m->attn_splits = (uint32_t)v;
-    }
+    if (tunables().attn_splits) m->attn_splits = tunables().attn_splits;  // tuning: CTAs per KV head
     if ((st = dmalloc(&m->state, 1)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->pending, (size_t)c.context_tokens + 1u)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->generated, (size_t)c.context_tokens + 1u)) != STARK_B200_OK) return fail(st);
@@ -171,7 +163,7 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     if ((st = dmalloc(&m->attn, c.q_heads * kHeadDim)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->act, c.inter)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->logits, c.vocab)) != STARK_B200_OK) return fail(st);
-    if ((st = dmalloc(&m->attn_scratch, attention_scratch_floats(c.q_heads, c.kv_heads, m->attn_splits))) !=
+    if ((st = dmalloc(&m->attn_scratch, attention_scratch_floats(c.q_heads, c.kv_heads, kMaxAttnSplits))) !=
         STARK_B200_OK)
         return fail(st);
     if ((st = dmalloc(&m->attn_counters, c.kv_heads)) != STARK_B200_OK) return fail(st);
@@ -637,6 +629,38 @@ stark_b200_status model_finalize(Model *m) {
     return model_reset(m);
 }
 
+// Records both launch sequences again with the current launch-shape settings.  Cache and position are kept.
+stark_b200_status model_recapture(Model *m) {
+    if (!m->finalized || m->fenced) return STARK_B200_INVALID_STATE;
+    if (m->use_mega) return STARK_B200_UNSUPPORTED;
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    const uint32_t by_heads = std::min<uint32_t>(kMaxAttnSplits, std::max<uint32_t>(1u, 192u / m->cfg.kv_heads));
+    m->attn_splits = tunables().attn_splits ? tunables().attn_splits : by_heads;
+    // one eager pass on a scratch copy of the step state (first use of a kernel instance sets its attributes)
+    StepState saved;
+    SB_CUDA(cudaMemcpy(&saved, m->state, sizeof(StepState), cudaMemcpyDeviceToHost));
+    stark_b200_status st;
+    if ((st = issue_token(m, true, nullptr)) != STARK_B200_OK) return st;
+    if ((st = issue_token(m, false, nullptr)) != STARK_B200_OK) return st;
+    SB_CUDA(cudaStreamSynchronize(m->stream));
+    SB_CUDA(cudaMemcpy(m->state, &saved, sizeof(StepState), cudaMemcpyHostToDevice));
+    cudaGraphExec_t step = nullptr, ingest = nullptr;
+    uint32_t step_n = 0, ingest_n = 0;
+    if ((st = capture(m, true, &step, &step_n)) != STARK_B200_OK) return st;
+    if ((st = capture(m, false, &ingest, &ingest_n)) != STARK_B200_OK) {
+        cudaGraphExecDestroy(step);
+        return st;
+    }
+    cudaGraphExecDestroy(m->step_graph);
+    cudaGraphExecDestroy(m->ingest_graph);
+    m->step_graph = step;
+    m->ingest_graph = ingest;
+    m->step_launches = step_n;
+    m->ingest_launches = ingest_n;
+    m->has_logits = false;
+    return STARK_B200_OK;
+}
+
 stark_b200_status model_reset(Model *m) {
     SB_CUDA(cudaMemsetAsync(m->state, 0, sizeof(StepState), m->stream));
     SB_CUDA(cudaMemsetAsync(m->attn_counters, 0, m->cfg.kv_heads * 4, m->stream));
@@ -796,10 +820,10 @@ stark_b200_status model_generate_greedy(Model *m, uint32_t steps, uint32_t *out_
 // Copies out the timeline slots of the launches issued since the last call and re-arms them.
 stark_b200_status model_read_trace(Model *m, unsigned long long *dst, size_t count) {
     if (!m->trace) return STARK_B200_UNSUPPORTED;
-    if (count != (size_t)m->trace_slots * 4u) return STARK_B200_INVALID_ARGUMENT;
+    if (count != (size_t)m->trace_slots * kTraceFields) return STARK_B200_INVALID_ARGUMENT;
     SB_CUDA(cudaStreamSynchronize(m->stream));
     SB_CUDA(cudaMemcpy(dst, m->trace, count * 8u, cudaMemcpyDeviceToHost));
-    std::vector<TraceSlot> init(m->trace_slots, TraceSlot{~0ull, ~0ull, 0ull, 0ull});
+    std::vector<TraceSlot> init(m->trace_slots, TraceSlot{~0ull, ~0ull, 0ull, 0ull, 0ull, 0ull});
     SB_CUDA(cudaMemcpy(m->trace, init.data(), count * 8u, cudaMemcpyHostToDevice));
     return STARK_B200_OK;
 }

@@ -75,6 +75,7 @@ stark_b200_status model_tp_init(Model *m, uint32_t rank, uint32_t size, uint32_t
 stark_b200_status model_tp_connect(Model *m, const uint8_t *handles);
 stark_b200_status model_finalize(Model *m);
 stark_b200_status model_reset(Model *m);
+stark_b200_status model_recapture(Model *m);
 stark_b200_status model_rewind(Model *m, uint64_t position);
 stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count);
 stark_b200_status model_step(Model *m, uint32_t token, bool chained);

@@ -3,8 +3,10 @@
 // moves real bytes is the decode attention, which streams the KV pages of one head per CTA row.
 #include "ops.cuh"
 #include "device_attention.cuh"
+#include "tunables.cuh"
 
 #include <algorithm>
+#include <cstdlib>
 
 namespace sb {
 
@@ -12,31 +14,42 @@ namespace {
 
 // One CTA = (split, KV head), four warps: the split's partial, then the last split of the head to
 // arrive merges all of them (see device_attention.cuh).
-__global__ void __launch_bounds__(kAttnThreads, 5) attention_decode_kernel(const AttnParams p) {
+// NBUF K / V tile pairs in flight: with three, a split of up to three pages is on its way before the new
+// row exists (104 KB of shared memory instead of 70 KB).
+// MINB: CTAs per SM the register allocation is sized for (5: at most 96 registers, so that a CTA fits beside
+// two resident 320-thread matvec CTAs at 80; 4: up to 128).
+template <int NBUF, int MINB>
+__global__ void __launch_bounds__(kAttnThreads, MINB) attention_decode_kernel(const AttnParams p) {
     extern __shared__ __align__(128) uint8_t attn_smem[];
     __shared__ uint32_t is_last;
     pdl_launch_dependents();
     const uint32_t tid = threadIdx.x;
     const uint32_t split = blockIdx.x, h = blockIdx.y;
-    if (tid == 0 && p.trace) trace_min(&p.trace->start);
+    if (tid == 0 && p.trace) {
+        trace_min(&p.trace->start);
+        trace_max(&p.trace->start_last);
+    }
     // Before the wait: the cache rows of earlier tokens and the constants of this position do not
     // depend on the kernel before this one, so their fetch overlaps it.  Inside a recorded token the
     // position is final here (its writer ran in the previous token's graph).  In an unrecorded sequence
     // every kernel launches its dependents at once, so several later kernels can be resident and waiting
     // while the writer of `position` is still running: the position is read again after the wait and
     // the fetch repeated if it moved.
-    const AttnShared sm = carve_attn_shared(attn_smem);
+    const AttnShared sm = carve_attn_shared(attn_smem, NBUF);
     AttnPrefetch pf;
-    attention_prefetch(p, split, h, __ldcg(&p.state->position), sm, tid, pf);
+    attention_prefetch<NBUF>(p, split, h, __ldcg(&p.state->position), sm, tid, pf);
     pdl_wait();
-    if (tid == 0 && p.trace) trace_min(&p.trace->ready);
+    if (tid == 0 && p.trace) {
+        trace_min(&p.trace->ready);
+        trace_max(&p.trace->ready_last);
+    }
     const uint32_t pos = __ldcg(&p.state->position);
     if (pos != pf.pos) {  // uniform across the CTA
         cp_async_wait<0>();
         __syncthreads();
-        attention_prefetch(p, split, h, pos, sm, tid, pf);
+        attention_prefetch<NBUF>(p, split, h, pos, sm, tid, pf);
     }
-    attention_partial<0, kAttnThreads>(p, split, h, pos, sm, tid, pf);
+    attention_partial<0, kAttnThreads, NBUF>(p, split, h, pos, sm, tid, pf);
     if (tid == 0) {
         const uint32_t prev = atomicAdd(&p.counters[h], 1u);
         is_last = prev == p.splits - 1u;
@@ -427,10 +440,16 @@ stark_b200_status attention_decode_launch(const AttnArgs &a, cudaStream_t stream
     p.scratch = a.scratch;
     p.counters = a.counters;
     p.trace = a.trace;
-    static SmemOptIn once;
-    if (stark_b200_status s = ensure_dynamic_smem(attention_decode_kernel, (int)kAttnSharedBytes, once)) return s;
-    return launch_pdl_smem(attention_decode_kernel, dim3(a.splits, a.kv_heads), dim3(kAttnThreads), kAttnSharedBytes,
-                           a.pdl, stream, p);
+    const uint32_t bufs = tunables().attn_bufs;  // tile pairs in flight per CTA
+    const bool wide = tunables().attn_regs >= 128u;
+    using Kernel = void (*)(const AttnParams);
+    static const Kernel kernels[2][2] = {{attention_decode_kernel<2, 5>, attention_decode_kernel<2, 4>},
+                                         {attention_decode_kernel<3, 5>, attention_decode_kernel<3, 4>}};
+    static SmemOptIn once[2][2];
+    const uint32_t bi = bufs == 2u ? 0u : 1u, wi = wide ? 1u : 0u;
+    const uint32_t smem = attn_shared_bytes(bi ? 3u : 2u);
+    if (stark_b200_status s = ensure_dynamic_smem(kernels[bi][wi], (int)smem, once[bi][wi])) return s;
+    return launch_pdl_smem(kernels[bi][wi], dim3(a.splits, a.kv_heads), dim3(kAttnThreads), smem, a.pdl, stream, p);
 }
 
 stark_b200_status embedding_row_launch(const QMatrix *table, const StepState *state, uint16_t *out, bool pdl,

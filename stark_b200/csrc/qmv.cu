@@ -20,6 +20,7 @@
 //     the f16 range never clips it; bf16 inputs convert exactly.
 #include "qmv.cuh"
 #include "device_math.cuh"
+#include "tunables.cuh"
 
 #include <algorithm>
 #include <cstdlib>
@@ -29,12 +30,13 @@ namespace sb {
 
 namespace {
 
-constexpr int kConsumerWarps = 8;
-constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kProducerWarp = kConsumerWarps;
-constexpr int kEpilogueWarp = kConsumerWarps + 1;
-constexpr int kThreads = (kConsumerWarps + 2) * 32;
-constexpr int kMaxRounds = 6;  // input chunks (8 elements) a consumer thread keeps in registers: K <= 12288
+// Two CTA shapes, chosen per launch (CW = consumer warps; a producer warp and an epilogue warp come on top):
+//   CW = 8:  320 threads at 80 registers, two CTAs per SM.  Both fill the register file, so the CTAs of the
+//            next kernel of a programmatic launch chain become resident only when these exit.
+//   CW = 16: 576 threads at 56 registers and about half the shared memory, ONE CTA per SM.  The next
+//            kernel's CTA fits beside it, so everything a kernel does ahead of griddepcontrol.wait (barrier
+//            set-up, norm weights, filling its weight ring) overlaps the kernel before it.
+constexpr uint32_t kMaxColumns = 12288;  // a consumer thread keeps its chunks of the input row in registers
 constexpr int kRedSlots = 4;  // depth of the partial-sum hand-off ring between consumers and the epilogue warp
 
 struct QmvParams {
@@ -68,7 +70,7 @@ struct SmemLayout {
 };
 
 __host__ __device__ inline SmemLayout smem_layout(uint32_t num_stages, uint32_t stage_capacity, uint32_t columns,
-                                                  bool split, bool norm) {
+                                                  bool split, bool norm, uint32_t cw) {
     SmemLayout L;
     uint32_t off = 0;
     L.ring = off;
@@ -85,9 +87,9 @@ __host__ __device__ inline SmemLayout smem_layout(uint32_t num_stages, uint32_t 
     off += (columns / 64u) * 4u;
     off = (off + 15u) & ~15u;
     L.red = off;
-    off += kRedSlots * kConsumerWarps * 16u * 4u;
+    off += kRedSlots * cw * 16u * 4u;
     L.wred = off;
-    off += 2u * kConsumerWarps * 4u;
+    off += 2u * cw * 4u;
     L.bars = off;
     off += (8u + 8u + 2u * kRedSlots) * 8u;  // full[8], empty[8], red_full[4], red_empty[4]
     L.flags = off;
@@ -104,11 +106,12 @@ __device__ inline void wait_failed(volatile uint32_t *abort_flag, uint32_t *erro
 
 // The consumers' prologue: waits for the previous kernel, brings the input row into shared memory as
 // exactly scaled f16 (plus the per-group sums the bias term needs) and returns the factor that undoes
-// the scale.  ROUNDS = chunks of 8 elements a thread keeps in registers (K <= ROUNDS * 2048): the
+// the scale.  ROUNDS = chunks of 8 elements a thread keeps in registers (K <= ROUNDS * 256 * CW): the
 // code is straight-line per round, and a short instance matters because every launch runs it cold.
-template <int ROUNDS, bool NORM, bool SPLIT, bool TPX, bool FOLD>
+template <int CW, int ROUNDS, bool NORM, bool SPLIT, bool TPX, int FOLD>
 __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, uint32_t columns, __half *xs, __half *xlo,
                                             uint16_t *nws, float *xsum, float *xoff, float *wred, float &xunscale) {
+    constexpr int kConsumerWarps = CW, kConsumerThreads = CW * 32;
     const uint32_t warp = tid >> 5, lane = tid & 31u;
     // Before the wait: everything that does not depend on the previous kernel.  The norm weights
     // are constants, so their bf16-rounded values (normalization.rs:157-161 rounds them before the
@@ -128,7 +131,10 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
         }
     }
     pdl_wait();  // the input vector belongs to the previous kernel
-    if (tid == 0 && p.trace) trace_min(&p.trace->ready);
+    if (tid == 0 && p.trace) {
+        trace_min(&p.trace->ready);
+        trace_max(&p.trace->ready_last);
+    }
 
     // One trip to global memory: this thread's chunks of the input row stay in registers for the
     // whole prologue (up to ROUNDS chunks of 8 elements; the launcher checks the width).
@@ -304,7 +310,7 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
             s8 += b;
             const float sa = a * xscale, sb2 = b * xscale;
             asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(hh[i]) : "f"(sb2), "f"(sa));
-            if (SPLIT || FOLD) {
+            if (SPLIT || FOLD == 1) {
                 const float2 back = __half22float2(*reinterpret_cast<const __half2 *>(&hh[i]));
                 h8 += back.x;
                 if (SPLIT) {
@@ -326,11 +332,13 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
 #pragma unroll
         for (int o = 1; o < 8; o <<= 1) {
             s8 += __shfl_xor_sync(0xffffffffu, s8, o);
-            if (FOLD) h8 += __shfl_xor_sync(0xffffffffu, h8, o);
+            if (SPLIT || FOLD == 1) h8 += __shfl_xor_sync(0xffffffffu, h8, o);
         }
         if (c < chunks && (lane & 7u) == 0) {
             xsum[c >> 3] = s8;
-            if (FOLD) xoff[c >> 3] = -64.0f * h8;
+            // FOLD == 2 with a bf16 input: the scaled f16 values are the inputs times a power of two, so
+            // their sum is the sum already formed
+            if (FOLD) xoff[c >> 3] = (FOLD == 2 && !SPLIT) ? -64.0f * xscale * s8 : -64.0f * h8;
         }
     }
     named_bar_sync(1, kConsumerThreads);
@@ -344,11 +352,16 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
 // PRED:  the stage holds fewer than 8 * RPW records (group counts that are not a multiple of 8).
 // TPX:   the kernel takes part in a tensor-parallel exchange (QmvExchange); kept out of the single-GPU
 //        instances so that their code and register allocation stay as they are.
-template <bool SPLIT, int RPW, bool PRED, bool FOLD, bool TPX = false>
-__global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
+// FOLD:  0 = the tensor core sees the integer codes; 1, 2 = it sees codes plus an offset that is taken out of
+//        the group sums afterwards (dequant_a4_word).
+// CW:    consumer warps (8: two CTAs per SM, 16: one).
+template <bool SPLIT, int RPW, bool PRED, int FOLD, bool TPX = false, int CW = 8>
+__global__ void __maxnreg__(CW == 16 ? 56 : 80) qmv_a4_kernel(const QmvParams p) {
+    constexpr int kConsumerWarps = CW, kConsumerThreads = CW * 32;
+    constexpr int kProducerWarp = CW, kEpilogueWarp = CW + 1;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t columns = p.groups * 64u;
-    const SmemLayout L = smem_layout(p.num_stages, p.stage_capacity, columns, SPLIT, p.prologue == kProRmsNorm);
+    const SmemLayout L = smem_layout(p.num_stages, p.stage_capacity, columns, SPLIT, p.prologue == kProRmsNorm, CW);
     uint8_t *ring = smem + L.ring;
     __half *xs = reinterpret_cast<__half *>(smem + L.xs);
     __half *xlo = reinterpret_cast<__half *>(smem + L.xlo);
@@ -386,7 +399,10 @@ __global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
     }
     __syncthreads();
     pdl_launch_dependents();
-    if (tid == 0 && p.trace) trace_min(&p.trace->start);
+    if (tid == 0 && p.trace) {
+        trace_min(&p.trace->start);
+        trace_max(&p.trace->start_last);
+    }
 
     if (warp == kProducerWarp) {
         // ---------------- producer: stream this CTA's byte range through the ring ----------------
@@ -508,12 +524,14 @@ __global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
     // ---------------- consumers ----------------
     float xunscale;
     const bool norm = p.prologue == kProRmsNorm;
-    if (columns <= 2u * kConsumerThreads * 8u) {
-        if (norm) stage_input<2, true, SPLIT, TPX, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
-        else stage_input<2, false, SPLIT, false, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+    // Two instances of the prologue: rows of up to 4096 values, and up to kMaxColumns.
+    constexpr int kShortRounds = 4096 / (kConsumerThreads * 8), kLongRounds = (int)kMaxColumns / (kConsumerThreads * 8);
+    if (columns <= 4096u) {
+        if (norm) stage_input<CW, kShortRounds, true, SPLIT, TPX, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        else stage_input<CW, kShortRounds, false, SPLIT, false, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
     } else {
-        if (norm) stage_input<kMaxRounds, true, SPLIT, TPX, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
-        else stage_input<kMaxRounds, false, SPLIT, false, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        if (norm) stage_input<CW, kLongRounds, true, SPLIT, TPX, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
+        else stage_input<CW, kLongRounds, false, SPLIT, false, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
     }
 
     // Main loop: no block-wide barrier from here on.
@@ -536,16 +554,16 @@ __global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
             uint32_t sw[RPW], bw[RPW];
 #pragma unroll
             for (int i = 0; i < RPW; ++i) {
-                if (!PRED || warp + 8u * i < p.stage_records) {
-                    wq[i] = *reinterpret_cast<const uint4 *>(my_rec + soff + i * 8 * kA4RecordBytes);
-                    sw[i] = *reinterpret_cast<const uint32_t *>(my_planes + soff + i * 8 * kA4RecordBytes);
-                    bw[i] = *reinterpret_cast<const uint32_t *>(my_planes + soff + i * 8 * kA4RecordBytes + 32u);
+                if (!PRED || warp + (uint32_t)CW * i < p.stage_records) {
+                    wq[i] = *reinterpret_cast<const uint4 *>(my_rec + soff + i * CW * kA4RecordBytes);
+                    sw[i] = *reinterpret_cast<const uint32_t *>(my_planes + soff + i * CW * kA4RecordBytes);
+                    bw[i] = *reinterpret_cast<const uint32_t *>(my_planes + soff + i * CW * kA4RecordBytes + 32u);
                 }
             }
 #pragma unroll
             for (int i = 0; i < RPW; ++i) {
-                if (!PRED || warp + 8u * i < p.stage_records) {
-                    const uint32_t kofs = (kg0 + 8u * i) * 64u;  // my_x already includes warp * 64
+                if (!PRED || warp + (uint32_t)CW * i < p.stage_records) {
+                    const uint32_t kofs = (kg0 + (uint32_t)CW * i) * 64u;  // my_x already includes warp * 64
                     const uint4 *xp = reinterpret_cast<const uint4 *>(my_x + kofs);
                     const uint4 xa = xp[0], xb = xp[1];
                     const uint32_t ww[4] = {wq[i].x, wq[i].y, wq[i].z, wq[i].w};
@@ -561,13 +579,17 @@ __global__ void __maxnreg__(80) qmv_a4_kernel(const QmvParams p) {
                             mma_m16n8k16_f16(c, a, lw.x, lw.y);
                         }
                     }
-                    const uint32_t kg = kg0 + warp + 8u * i;
+                    const uint32_t kg = kg0 + warp + (uint32_t)CW * i;
                     const float xs_g = xsum[kg];
                     float d0 = c[0], d1 = c[2];
-                    if (FOLD) {
+                    if (FOLD == 1) {
                         const float xo = xoff[kg];      // -64 * sum of the f16 inputs of this group
                         d0 = fmaf(16.0f, xo, d0);       // c - 1024 sum
                         d1 = fmaf(d1, 0.0625f, xo);     // c / 16 - 64 sum
+                    } else if (FOLD == 2) {
+                        const float xo = xoff[kg];
+                        d0 += xo;                       // c - 64 sum, both row halves
+                        d1 += xo;
                     }
                     acc_s0 = fmaf(__uint_as_float(sw[i] << 16), d0, acc_s0);
                     acc_s1 = fmaf(__uint_as_float(sw[i] & 0xffff0000u), d1, acc_s1);
@@ -665,7 +687,7 @@ __global__ void unpack_a4_kernel(const uint8_t *__restrict__ data, uint8_t *__re
         const uint32_t row0 = tile_row0(tile, pair_halves, rows);
         const uint32_t word = *reinterpret_cast<const uint32_t *>(data + recno * kA4RecordBytes + lane * 16u + j * 4u);
         uint32_t a[4];
-        dequant_a4_word<false>(word, a);
+        dequant_a4_word<0>(word, a);
         // a[0]: row g, k-pair r=0; a[1]: row g+8, r=0; a[2]: row g, r=1; a[3]: row g+8, r=1
 #pragma unroll
         for (int reg = 0; reg < 4; ++reg) {
@@ -682,30 +704,13 @@ __global__ void unpack_a4_kernel(const uint8_t *__restrict__ data, uint8_t *__re
     }
 }
 
-// Launch-shape knobs; the defaults are the measured best, the environment overrides exist for sweeps.
-struct Tuning {
-    uint32_t smem_budget_kb = 64;
-    uint32_t ctas_per_sm = 2;
-    bool fold = false;
-};
-const Tuning &tuning() {
-    static Tuning t = [] {
-        Tuning v;
-        if (const char *e = getenv("STARK_B200_QMV_SMEM_KB")) v.smem_budget_kb = std::max(32, std::min(200, atoi(e)));
-        if (const char *e = getenv("STARK_B200_QMV_CTAS")) v.ctas_per_sm = std::max(1, std::min(2, atoi(e)));
-        if (const char *e = getenv("STARK_B200_QMV_FOLD")) v.fold = atoi(e) != 0;
-        return v;
-    }();
-    return t;
-}
-
-// Records per ring stage: 8 * RPW when the group count allows it (no per-record predicates),
-// otherwise the largest divisor of the group count that fits.
-void pick_stage(uint32_t groups, uint32_t *records, uint32_t *rpw, bool *pred) {
+// Records per ring stage: a multiple of the consumer warps when the group count allows it (no per-record
+// predicates), otherwise the largest divisor of the group count that fits.
+void pick_stage(uint32_t groups, uint32_t cw, uint32_t *records, uint32_t *rpw, bool *pred) {
     for (uint32_t r : {32u, 16u, 8u}) {
-        if (groups % r == 0) {
+        if (r >= cw && groups % r == 0) {
             *records = r;
-            *rpw = r / 8u;
+            *rpw = r / cw;
             *pred = false;
             return;
         }
@@ -717,7 +722,7 @@ void pick_stage(uint32_t groups, uint32_t *records, uint32_t *rpw, bool *pred) {
             break;
         }
     *records = best;
-    *rpw = (best + 7u) / 8u;
+    *rpw = (best + cw - 1u) / cw;
     if (*rpw == 3) *rpw = 4;
     *pred = true;
 }
@@ -735,10 +740,37 @@ int sm_count_cached() {
     return cached[dev];
 }
 
+using KernelFn = void (*)(const QmvParams);
+struct KernelChoice {
+    KernelFn fn;
+    SmemOptIn *opted;
+};
+
+// One table per CTA shape.  FOLD and the tensor-parallel hooks only exist for bf16 I/O (SPLIT == false).
+template <int CW>
+KernelChoice pick_kernel(bool split, int fold, bool pred, uint32_t rpw, bool tpx) {
+    const uint32_t ri = rpw == 1 ? 0u : (rpw == 2 ? 1u : 2u);
+    const uint32_t pi = pred ? 1u : 0u;
+#define SB_QMV_RPW(SP, PR, FO, TP) \
+    { qmv_a4_kernel<SP, 1, PR, FO, TP, CW>, qmv_a4_kernel<SP, 2, PR, FO, TP, CW>, qmv_a4_kernel<SP, (CW == 16 ? 2 : 4), PR, FO, TP, CW> }
+#define SB_QMV_PRED(SP, FO, TP) { SB_QMV_RPW(SP, false, FO, TP), SB_QMV_RPW(SP, true, FO, TP) }
+    static const KernelFn plain[3][2][3] = {SB_QMV_PRED(false, 0, false), SB_QMV_PRED(false, 1, false),
+                                            SB_QMV_PRED(false, 2, false)};
+    static const KernelFn splitk[2][3] = SB_QMV_PRED(true, 0, false);
+    static const KernelFn tpxk[3][2][3] = {SB_QMV_PRED(false, 0, true), SB_QMV_PRED(false, 1, true),
+                                           SB_QMV_PRED(false, 2, true)};
+#undef SB_QMV_PRED
+#undef SB_QMV_RPW
+    static SmemOptIn once_plain[3][2][3], once_split[2][3], once_tpx[3][2][3];
+    if (split) return {splitk[pi][ri], &once_split[pi][ri]};
+    if (tpx) return {tpxk[fold][pi][ri], &once_tpx[fold][pi][ri]};
+    return {plain[fold][pi][ri], &once_plain[fold][pi][ri]};
+}
+
 }  // namespace
 
 void qmv_pick_stage(uint32_t groups, uint32_t *records, uint32_t *rpw, bool *pred) {
-    pick_stage(groups, records, rpw, pred);
+    pick_stage(groups, 8u, records, rpw, pred);
 }
 
 stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
@@ -748,8 +780,11 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     if (a.epilogue == kEpiSwiGlu && !m->pair_halves) return STARK_B200_INVALID_ARGUMENT;
     if (a.io_type == STARK_B200_F32 && (a.prologue != kProPlain || a.epilogue != kEpiStore))
         return STARK_B200_UNSUPPORTED;
-    if (m->columns > (uint32_t)kMaxRounds * kConsumerThreads * 8u) return STARK_B200_UNSUPPORTED;
+    if (m->columns > kMaxColumns) return STARK_B200_UNSUPPORTED;
 
+    const bool split = a.io_type == STARK_B200_F32;
+    const Tunables &tune = tunables();
+    const uint32_t cw = tune.qmv_consumer_warps;
     QmvParams p{};
     p.w = m->data;
     p.rows = m->rows;
@@ -757,7 +792,7 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     p.groups = m->groups;
     uint32_t rpw = 1;
     bool pred = false;
-    pick_stage(m->groups, &p.stage_records, &rpw, &pred);
+    pick_stage(m->groups, cw, &p.stage_records, &rpw, &pred);
     p.stages_per_tile = m->groups / p.stage_records;
     p.stage_capacity = (p.stage_records * kA4RecordBytes + 127u) & ~127u;
     p.pair_halves = m->pair_halves;
@@ -778,47 +813,30 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     if ((a.epilogue == kEpiPush) != (p.ex.ranks != 0 && p.ex.push[0] != nullptr)) return STARK_B200_INVALID_ARGUMENT;
     if (p.ex.recv && a.prologue != kProRmsNorm) return STARK_B200_INVALID_ARGUMENT;
 
-    const bool split = a.io_type == STARK_B200_F32;
-    const bool fold = tuning().fold;
-    // Ring depth: what fits the per-CTA budget.  Two CTAs share an SM, and under programmatic
-    // dependent launch CTAs of the next kernel join them and prefetch while this one drains.
-    const uint32_t budget = tuning().smem_budget_kb * 1024u;
+    const int fold = split ? 0 : (int)tune.qmv_fold;
+    // Ring depth: what fits the per-CTA budget.  With two CTAs per SM the register file is full; with one,
+    // the CTA of the next kernel of a programmatic launch chain sits beside it and fills its own ring
+    // while this one drains.
+    const uint32_t ctas_per_sm = tune.qmv_ctas_per_sm ? tune.qmv_ctas_per_sm : (cw == 16u ? 1u : 2u);
+    const uint32_t budget = (tune.qmv_smem_kb ? tune.qmv_smem_kb : (cw == 16u ? 112u : 64u)) * 1024u;
     uint32_t stages = 8;
     const bool norm = a.prologue == kProRmsNorm;
-    while (stages > 2 && smem_layout(stages, p.stage_capacity, m->columns, split, norm).total > budget) --stages;
+    while (stages > 2 && smem_layout(stages, p.stage_capacity, m->columns, split, norm, cw).total > budget) --stages;
     p.num_stages = stages;
-    const uint32_t smem = smem_layout(stages, p.stage_capacity, m->columns, split, norm).total;
+    const uint32_t smem = smem_layout(stages, p.stage_capacity, m->columns, split, norm, cw).total;
     if (smem > 220u * 1024u) return STARK_B200_UNSUPPORTED;
 
     const uint32_t units = p.row_tiles / p.unit_tiles;
-    const uint32_t grid = std::max(1u, std::min(units, (uint32_t)sm_count_cached() * tuning().ctas_per_sm));
+    const uint32_t grid = std::max(1u, std::min(units, (uint32_t)sm_count_cached() * ctas_per_sm));
     if (a.out_grid) *a.out_grid = grid;
 
-    using KernelFn = void (*)(const QmvParams);
-#define SB_QMV_ROW(SP, FO)                                                                               \
-    {                                                                                                    \
-        {qmv_a4_kernel<SP, 1, false, FO>, qmv_a4_kernel<SP, 2, false, FO>, qmv_a4_kernel<SP, 4, false, FO>}, { \
-            qmv_a4_kernel<SP, 1, true, FO>, qmv_a4_kernel<SP, 2, true, FO>, qmv_a4_kernel<SP, 4, true, FO>     \
-        }                                                                                                \
-    }
-    static const KernelFn table[2][2][2][3] = {{SB_QMV_ROW(false, false), SB_QMV_ROW(false, true)},
-                                               {SB_QMV_ROW(true, false), SB_QMV_ROW(true, true)}};
-#undef SB_QMV_ROW
-    const uint32_t ri = rpw == 1 ? 0u : (rpw == 2 ? 1u : 2u);
-    static const KernelFn tpx_table[2][3] = {
-        {qmv_a4_kernel<false, 1, false, false, true>, qmv_a4_kernel<false, 2, false, false, true>,
-         qmv_a4_kernel<false, 4, false, false, true>},
-        {qmv_a4_kernel<false, 1, true, false, true>, qmv_a4_kernel<false, 2, true, false, true>,
-         qmv_a4_kernel<false, 4, true, false, true>}};
     const bool tpx = p.ex.ranks != 0;
     if (tpx && split) return STARK_B200_UNSUPPORTED;
-    KernelFn kernel = tpx ? tpx_table[pred ? 1 : 0][ri] : table[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
-    static SmemOptIn once[2][2][2][3], tpx_once[2][3];
-    SmemOptIn &opted = tpx ? tpx_once[pred ? 1 : 0][ri] : once[split ? 1 : 0][fold ? 1 : 0][pred ? 1 : 0][ri];
-    if (stark_b200_status s = ensure_dynamic_smem(kernel, 220 * 1024, opted)) return s;
+    const KernelChoice k = cw == 16u ? pick_kernel<16>(split, fold, pred, rpw, tpx) : pick_kernel<8>(split, fold, pred, rpw, tpx);
+    if (stark_b200_status s = ensure_dynamic_smem(k.fn, 220 * 1024, *k.opted)) return s;
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kThreads);
+    cfg.blockDim = dim3((cw + 2u) * 32u);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -826,7 +844,7 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = a.pdl ? 1 : 0;
-    SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+    SB_CUDA(cudaLaunchKernelEx(&cfg, k.fn, p));
     return STARK_B200_OK;
 }
 

@@ -186,9 +186,9 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_q4kt_kernel(const Q4ktParam
             const uint4 xv = *reinterpret_cast<const uint4 *>(xk + 32u * jb);
             float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t a[4];
-            dequant_a4_word<false>(w.x, a);
+            dequant_a4_word<0>(w.x, a);
             mma_m16n8k16_f16(c, a, xv.x, xv.y);
-            dequant_a4_word<false>(w.y, a);
+            dequant_a4_word<0>(w.y, a);
             mma_m16n8k16_f16(c, a, xv.z, xv.w);
             const bool mine = (jb & 3u) == t;
             s0[jb >> 2] = mine ? c[0] + c[1] : s0[jb >> 2];

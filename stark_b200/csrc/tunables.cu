@@ -1,0 +1,62 @@
+#include "tunables.cuh"
+
+#include <cstdlib>
+#include <cstring>
+
+namespace sb {
+
+namespace {
+
+struct Entry {
+    const char *name, *env;
+    uint32_t Tunables::*field;
+    uint32_t fallback, lo, hi;
+};
+
+const Entry kEntries[] = {
+    {"qmv_consumer_warps", "STARK_B200_QMV_CW", &Tunables::qmv_consumer_warps, 8u, 8u, 16u},
+    {"qmv_smem_kb", "STARK_B200_QMV_SMEM_KB", &Tunables::qmv_smem_kb, 0u, 0u, 200u},
+    {"qmv_ctas_per_sm", "STARK_B200_QMV_CTAS", &Tunables::qmv_ctas_per_sm, 0u, 0u, 2u},
+    {"qmv_fold", "STARK_B200_QMV_FOLD", &Tunables::qmv_fold, 0u, 0u, 2u},
+    {"attn_bufs", "STARK_B200_ATTN_BUFS", &Tunables::attn_bufs, 3u, 2u, 3u},
+    {"attn_splits", "STARK_B200_ATTN_SPLITS", &Tunables::attn_splits, 0u, 0u, 32u},
+    {"attn_regs", "STARK_B200_ATTN_REGS", &Tunables::attn_regs, 96u, 96u, 128u},
+    {"pdl", "STARK_B200_PDL", &Tunables::pdl, 1u, 0u, 1u},
+};
+
+bool valid(const Entry &e, uint32_t v) {
+    if (v < e.lo || v > e.hi) return false;
+    if (e.field == &Tunables::qmv_consumer_warps) return v == 8u || v == 16u;
+    if (e.field == &Tunables::qmv_smem_kb) return v == 0u || v >= 32u;
+    return true;
+}
+
+}  // namespace
+
+Tunables &tunables() {
+    static Tunables t = [] {
+        Tunables v{};
+        for (const Entry &e : kEntries) {
+            v.*(e.field) = e.fallback;
+            if (const char *s = getenv(e.env)) {
+                const long parsed = strtol(s, nullptr, 10);
+                if (parsed >= 0 && valid(e, (uint32_t)parsed)) v.*(e.field) = (uint32_t)parsed;
+            }
+        }
+        return v;
+    }();
+    return t;
+}
+
+bool set_tunable(const char *name, uint32_t value) {
+    if (!name) return false;
+    for (const Entry &e : kEntries)
+        if (strcmp(name, e.name) == 0) {
+            if (!valid(e, value)) return false;
+            tunables().*(e.field) = value;
+            return true;
+        }
+    return false;
+}
+
+}  // namespace sb

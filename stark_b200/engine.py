@@ -256,11 +256,18 @@ class DenseModel:
         return i
 
     def read_trace(self) -> np.ndarray:
-        """Timeline of the launches since the last call, ``uint64[launches_per_step, 4]`` (ns)."""
+        """Timeline of the launches since the last call, ``uint64[launches_per_step, 6]`` (ns): first CTA
+        entered, first wait returned, last prologue done, last CTA left, last CTA entered, last wait returned."""
         n = self.info().trace_slots
-        out = np.empty((n, 4), np.uint64)
+        out = np.empty((n, 6), np.uint64)
         check(_lib.load().stark_b200_read_trace(self._h, out.ctypes.data, out.size), "read_trace")
         return out
+
+    def recapture(self, **tunables: int) -> None:
+        """Sets launch-shape settings (``stark_b200_set_tunable`` names) and records the token sequences again."""
+        for name, value in tunables.items():
+            check(_lib.load().stark_b200_set_tunable(name.encode(), int(value)), f"set_tunable {name}")
+        check(_lib.load().stark_b200_model_recapture(self._h), "model_recapture")
 
     def stream(self) -> int:
         """The cudaStream_t the model issues its work on (an integer handle)."""

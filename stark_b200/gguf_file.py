@@ -3,8 +3,9 @@
 metadata counts, typed key/value metadata, then per tensor its name, rank (1..4), dimensions (fastest
 first in the file; reversed here, as the reference does, so that ``shape[0]`` is the slowest), ggml
 type and data offset; tensor data starts at the next multiple of ``general.alignment`` (default 32).
-The same checks as the reference: version, alignment a power of two <= 4096, unknown types, unaligned /
-truncated / overlapping / duplicate tensors.
+The same checks as the reference: version, alignment a power of two <= 4096, unknown types, empty
+dimensions, sizes that overflow 64 bits, unaligned / truncated / overlapping / duplicate tensors; every
+admitted block type is sized, whether or not this engine can multiply with it.
 
 Tensors of the types this engine multiplies with go straight to the device:
 ``tensor.qmatrix()`` -> ``stark_b200.ops.QMatrix`` for Q8_0 (8) and Q4_K (12), two-dimensional or
@@ -24,9 +25,15 @@ class GGUFError(ValueError):
 
 
 F32, F16, Q8_0, Q4_K, BF16 = 0, 1, 8, 12, 30
-# bytes per block, values per block (ggml): the types the reference admits and this engine can size
-_BLOCKS = {F32: (4, 1), F16: (2, 1), BF16: (2, 1), Q8_0: (34, 32), Q4_K: (144, 256)}
-_ADMITTED = {0, 1, 30, 8, 10, 11, 12, 13, 14, 16, 17, 18, 23}  # weights.rs:2811
+# bytes per block, values per block for every ggml type the reference admits from a GGUF header
+# (block_layout, weights.rs:2565-2584): a file may hold tensors this engine cannot multiply (Q6_K output
+# heads beside Q4_K layers, for example); they are sized and span-checked like the rest and only
+# qmatrix() / array() refuse them.
+_BLOCKS = {F32: (4, 1), F16: (2, 1), BF16: (2, 1), Q8_0: (34, 32), 10: (84, 256), 11: (110, 256),
+           Q4_K: (144, 256), 13: (176, 256), 14: (210, 256), 16: (66, 256), 17: (74, 256), 18: (98, 256),
+           23: (136, 256)}
+_ADMITTED = set(_BLOCKS)  # weights.rs:2811
+_U64 = 1 << 64
 _SCALARS = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
 
 
@@ -87,13 +94,28 @@ class _Reader:
         raise GGUFError("unknown GGUF metadata type")
 
 
+def element_count(dims) -> int:
+    """Product of the dimensions with the reference's refusals (`product`, weights.rs:2556-2563)."""
+    total = 1
+    for d in dims:
+        if d == 0:
+            raise GGUFError("empty tensor dimension")
+        total *= int(d)
+        if total >= _U64:
+            raise GGUFError("tensor size overflow")
+    return total
+
+
 def encoded_size(kind: int, count: int) -> int:
     if kind not in _BLOCKS:
-        raise GGUFError(f"ggml type {kind} is admitted by the reference but not sized by this engine")
+        raise GGUFError("unsupported weight block format")
     nbytes, values = _BLOCKS[kind]
     if count % values:
-        raise GGUFError("GGUF tensor is not a whole number of blocks")
-    return count // values * nbytes
+        raise GGUFError("weight dimension is not block aligned")
+    size = count // values * nbytes
+    if size >= _U64:
+        raise GGUFError("encoded weight size overflow")
+    return size
 
 
 def read_gguf(path) -> tuple[dict, dict]:
@@ -125,7 +147,7 @@ def read_gguf(path) -> tuple[dict, dict]:
         kind, offset = r.scalar("<I"), r.scalar("<Q")
         if kind not in _ADMITTED:
             raise GGUFError("unsupported GGUF tensor type")
-        size = encoded_size(kind, int(np.prod(dims, dtype=np.uint64)))
+        size = encoded_size(kind, element_count(dims))
         encoded_size(kind, dims[0])  # the fastest dimension holds whole blocks
         if offset % alignment:
             raise GGUFError("unaligned GGUF tensor")
@@ -138,6 +160,8 @@ def read_gguf(path) -> tuple[dict, dict]:
     spans = sorted((start + off, start + off + size) for _, _, off, size in infos.values())
     end = start
     for lo, hi in spans:
+        if lo >= _U64 or hi >= _U64:
+            raise GGUFError("GGUF offset overflow")
         if hi > buf.size:
             raise GGUFError("truncated GGUF tensor")
         if lo < end:

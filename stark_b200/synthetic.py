@@ -16,6 +16,12 @@ CONFIGS = {
                        tied=True, eps=1e-6, rope_theta=1e6),
     "qwen3-8b": dict(layers=36, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, inter=12288, vocab=151936,
                      tied=False, eps=1e-6, rope_theta=1e6),
+    # two layers with the layer and vocabulary dimensions of the named shapes: every matrix width, head count
+    # and the full-vocabulary read-out of those shapes at a cost the CPU oracle pays in seconds
+    "qwen3-0.6b-layers": dict(layers=2, hidden=1024, q_heads=16, kv_heads=8, head_dim=128, inter=3072, vocab=151936,
+                              tied=True, eps=1e-6, rope_theta=1e6),
+    "qwen3-8b-layers": dict(layers=2, hidden=4096, q_heads=32, kv_heads=8, head_dim=128, inter=12288, vocab=151936,
+                            tied=False, eps=1e-6, rope_theta=1e6),
     # small shapes for parity tests (same graph, minutes -> milliseconds on the CPU oracle)
     "tiny": dict(layers=2, hidden=256, q_heads=4, kv_heads=2, head_dim=128, inter=512, vocab=1024, tied=True,
                  eps=1e-6, rope_theta=1e6),

@@ -3,11 +3,19 @@ parity tests can also be checked against values that were produced once and neve
 
     python tests/golden/make_golden.py
 
+    python tests/golden/make_golden.py --full     # also the long continuations (minutes of CPU time)
+
 Inputs come from `stark_b200.synthetic` (seeded), outputs from `oracle/` only.  The arrays:
   matvec_y        bf16 bits, the 4-bit affine matvec of `matvec_case(seed=3, rows=512, columns=1024)`
   tiny_logits     bf16 bits, last-row logits of the `tiny` decoder (weights seed 0) after `prompt(tiny, 70, seed=5)`
   tiny_greedy     the oracle's own greedy continuation of that prompt, 8 tokens
   q8_0_row / q4_k_row   f32, row 1 of `q8_0_rows` / `q4_k_rows` (default_rng(11), 4 x 512) decoded
+  <shape>_logits        bf16 bits, last-row logits of the two-layer `qwen3-8b-layers` / `qwen3-0.6b-layers`
+                        decoders (weights seed 2) after `prompt(cfg, 24, seed=6)`
+  <shape>_teacher       (--full) LAYERS_STEPS seeded random tokens fed after that prompt (`prompt(cfg, 100, seed=7)`)
+  <shape>_top1          (--full) the oracle's pick (first index of the maximum) after each of those tokens
+  <shape>_top2          (--full) the oracle's two largest logits at each of those steps as bf16 bits, so that a
+                        test can tell a different pick at a tie from a different pick
 """
 import sys
 from pathlib import Path
@@ -21,8 +29,39 @@ from oracle import oracle as O  # noqa: E402
 from stark_b200 import synthetic as S  # noqa: E402
 
 
-def build() -> dict:
+LAYERS_STEPS = 100
+LAYERS_SHAPES = {"q8b": "qwen3-8b-layers", "q06b": "qwen3-0.6b-layers"}
+
+
+def layers_case(shape: str, steps: int) -> dict:
+    cfg = S.CONFIGS[LAYERS_SHAPES[shape]]
+    weights = S.dense_weights(cfg, seed=2)
+    prompt = S.prompt(cfg, 24, seed=6)
+    orc = O.DenseOracle(cfg, weights, capacity=24 + steps + 1)
+    for t in prompt[:-1]:
+        orc.ingest(int(t))
+    logits = np.asarray(orc.step(int(prompt[-1])), np.uint16)
+    out = {f"{shape}_logits": logits.copy()}
+    if steps:
+        # A random-init decoder decoded greedily falls into repeating one token, which would make agreement
+        # trivial; the continuation is therefore a seeded random token sequence fed to both sides.
+        teacher = S.prompt(cfg, steps, seed=7)
+        top1, top2 = [], []
+        for t in teacher:
+            logits = np.asarray(orc.step(int(t)), np.uint16)
+            order = np.sort(O.bf16_to_f32(logits))[-2:]
+            top2.append(S.f32_to_bf16(order[::-1].copy()))
+            top1.append(O.argmax_bf16(logits))
+        out[f"{shape}_teacher"] = np.asarray(teacher, np.uint32)
+        out[f"{shape}_top1"] = np.asarray(top1, np.uint32)
+        out[f"{shape}_top2"] = np.asarray(top2, np.uint16)
+    return out
+
+
+def build(full: bool = False) -> dict:
     out = {}
+    for shape in LAYERS_SHAPES:
+        out.update(layers_case(shape, LAYERS_STEPS if full else 0))
     w = S.matvec_case(seed=3, rows=512, columns=1024)
     out["matvec_y"] = O.affine_matvec_bf16(w["codes"], w["scales"], w["biases"], w["x"], 512, 1024)[0]
     cfg = S.CONFIGS["tiny"]
@@ -45,5 +84,5 @@ def build() -> dict:
 
 
 if __name__ == "__main__":
-    np.savez_compressed(Path(__file__).with_name("oracle_outputs.npz"), **build())
+    np.savez_compressed(Path(__file__).with_name("oracle_outputs.npz"), **build(full="--full" in sys.argv))
     print("wrote", Path(__file__).with_name("oracle_outputs.npz"))

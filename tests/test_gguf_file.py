@@ -104,6 +104,61 @@ def test_malformed_files_are_refused(sample, tmp_path):
             "<Q", struct.unpack("<Q", blob[at + 4:at + 12])[0] + 2))))
 
 
+def test_a_file_with_types_the_engine_cannot_multiply_still_opens(tmp_path):
+    """Q4_K checkpoints usually carry Q6_K tensors (output.weight, some ffn_down): the reference sizes
+    every admitted type (block_layout, weights.rs:2565-2584), so such a file opens and its Q4_K / Q8_0
+    tensors are usable; only the Q6_K tensor itself is refused, when asked for."""
+    rng = np.random.default_rng(5)
+    q4 = S.q4_k_rows(rng, 16, 256)
+    q6 = rng.integers(0, 256, size=(32, 210), dtype=np.uint8)       # 32 rows x 256 columns of Q6_K blocks
+    q5 = rng.integers(0, 256, size=(4, 2 * 176), dtype=np.uint8)    # Q5_K, 4 rows x 512 columns
+    path = tmp_path / "mixed.gguf"
+    _write(path, [("blk.0.ffn_up.weight", q4, gguf.GGMLQuantizationType.Q4_K),
+                  ("output.weight", q6, gguf.GGMLQuantizationType.Q6_K),
+                  ("blk.0.ffn_down.weight", q5, gguf.GGMLQuantizationType.Q5_K)])
+    tensors, _ = read_gguf(path)
+    assert tensors["output.weight"].kind == 14 and tensors["output.weight"].shape == (32, 256)
+    assert tensors["output.weight"].data.size == 32 * 210
+    assert tensors["blk.0.ffn_down.weight"].kind == 13 and tensors["blk.0.ffn_down.weight"].shape == (4, 512)
+    assert np.array_equal(tensors["blk.0.ffn_up.weight"].data.reshape(16, -1), q4)
+    with pytest.raises(GGUFError):
+        tensors["output.weight"].qmatrix()
+    with pytest.raises(GGUFError):
+        tensors["output.weight"].array()
+
+
+def _header(dims, kind=0, offset=0, payload=b""):
+    """A minimal GGUF v3 file with one tensor whose header fields are given."""
+    name = b"t"
+    out = b"GGUF" + struct.pack("<IQQ", 3, 1, 0)
+    out += struct.pack("<Q", len(name)) + name + struct.pack("<I", len(dims))
+    out += b"".join(struct.pack("<Q", d) for d in dims) + struct.pack("<IQ", kind, offset)
+    out += b"\0" * (-len(out) % 32)
+    return out + payload
+
+
+def test_crafted_headers_are_refused(tmp_path):
+    """`product` refuses an empty dimension and a size that overflows (weights.rs:2556-2563); a wrapped
+    64-bit product must not slip through the truncation check as a small tensor."""
+    def read(blob, name):
+        p = tmp_path / name
+        p.write_bytes(blob)
+        return read_gguf(p)
+
+    tensors, _ = read(_header([4], payload=struct.pack("<4f", 1, 2, 3, 4)), "ok")
+    assert tensors["t"].array().tolist() == [1.0, 2.0, 3.0, 4.0]
+    with pytest.raises(GGUFError, match="empty tensor dimension"):
+        read(_header([4, 0]), "zero")
+    with pytest.raises(GGUFError, match="tensor size overflow"):
+        read(_header([1 << 33, 1 << 33], payload=b"\0" * 64), "wrap")   # 2^66 elements, 0 modulo 2^64
+    with pytest.raises(GGUFError, match="overflow"):
+        read(_header([1 << 62, 2], payload=b"\0" * 64), "bytes")       # 2^63 f32 values: 2^65 bytes
+    with pytest.raises(GGUFError, match="block aligned"):
+        read(_header([48], kind=8, payload=b"\0" * 64), "blocks")      # Q8_0 row that is not whole blocks
+    with pytest.raises(GGUFError):
+        read(_header([4], offset=(1 << 64) - 32, payload=b"\0" * 64), "offset")
+
+
 @pytest.mark.gpu
 def test_tensors_from_a_file_multiply_like_the_source_bytes(sample):
     from stark_b200 import ops

@@ -165,3 +165,39 @@ def test_greedy_lowest_index_and_non_finite():
     assert O.argmax_bf16(v) == 0xFFFFFFFF
     lp = O.log_softmax_f64(np.array([0.0, 0.0], np.float32))
     np.testing.assert_allclose(lp, [-np.log(2.0)] * 2, rtol=1e-15)
+
+
+def rms_boundary_input(k):
+    """The input row of the reference's RMS boundary case as bf16 bits."""
+    x = np.ones(k["count"], np.float32)
+    for i in range(64):
+        x[(i * 37 + 102) % k["count"]] = 0.0
+    for i, power in enumerate(k["powers"]):
+        x[(i * 37 + 102) % k["count"]] = 2.0 ** power
+    x[k["probe_index"]] = k["probe_value"]
+    return O.f32_to_bf16(x)
+
+
+def test_rms_boundary_vector_pins_the_bf16_norm(kats):
+    """The probe sits on a bf16 rounding midpoint of the normalized value, so the output bit pattern tells
+    the order of the f32 sum of squares apart: the oracle must give the default policy's bits."""
+    k = kats["rms_boundary"]
+    x = rms_boundary_input(k)
+    out, _ = O.rmsnorm_bf16(x, np.ones(k["count"], np.float32), k["epsilon"])   # scale 1.0 = no scales
+    assert int(out[k["probe_index"]]) == k["expected_default_bits"]
+    # the two policies really differ on this input: a float64 sum lands on the other side
+    v = O.bf16_to_f32(x).astype(np.float64)
+    alt = np.float32(np.float32(k["probe_value"]) * np.float32(1.0 / np.sqrt(np.float32((v * v).sum() / k["count"] + 1e-6))))
+    assert int(O.f32_to_bf16(np.array([alt], np.float32))[0]) in (k["expected_default_bits"], k["expected_alternative_bits"])
+
+
+def test_prefix_reuse_arithmetic(kats):
+    """`reusable_prefill_rows` and `PrefixEntry::reusable` on the cases the reference's own tests hold."""
+    from stark_b200.engine import reusable_prefix_rows
+    k = kats["prefix_reuse"]
+    for prompt, rows in k["reusable_prefill_rows"]:
+        # the retained prefix of a prompt is what a longer prompt sharing all of it may reuse
+        assert reusable_prefix_rows(prompt, prompt, 10 ** 9, k["chunk"]) == rows, prompt
+    for case in k["reuse"]:
+        got = reusable_prefix_rows(k["previous_prompt"], case["common"], case["new_prompt"], k["chunk"])
+        assert got == case["expected"], case

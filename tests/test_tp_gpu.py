@@ -72,7 +72,7 @@ def _rank_main(config: str) -> None:
     assert logits.size == cfg["vocab"]
     first = model.argmax()
     assert first == O.argmax_bf16(logits)  # the cross-shard pick is the first index of the global maximum
-    steps = 24
+    steps = 100
     tokens = model.generate_greedy(steps)
     model.drain()
     assert take_device_error() == 0
@@ -89,7 +89,7 @@ def _rank_main(config: str) -> None:
         for i in range(steps):  # teacher-forced on the engine's tokens
             agree += int(O.argmax_bf16(oracle.step(tok)) == int(tokens[i + 1]))
             tok = int(tokens[i + 1])
-        assert agree / steps >= 0.95, agree
+        assert agree / steps >= 0.99, agree
         # the same model on one GPU: logits within the acceptance, and the same first token
         single = DenseModel.load(cfg, w, context)
         single.prefill(prompt)

@@ -88,6 +88,16 @@ def test_static_entry_point_matches_the_allocating_one_twice_in_a_row(q_heads, k
         w = O.bf16_to_f32(want[step]).astype(np.float64)
         assert np.all(np.abs(g - w) <= REL_TOL * np.maximum(np.abs(w), np.abs(w).mean())), f"call {step}"
         assert np.array_equal(got, want[step]), f"call {step}: same kernel, same split count, same bits"
+        # and against the CPU oracle directly: the rows of earlier positions plus the row this call appended
+        # (which the allocating entry point wrote back into the host cache, head norm and RoPE applied)
+        seq = position + step + 1
+        cosr, sinr = O.rope_coeffs(position + step, hd, theta)
+        q = O.head_norm_bf16(qkv, qn, 0, q_heads, hd, eps)
+        q = np.concatenate([O.rope_head_bf16(q[h * hd:(h + 1) * hd], cosr, sinr) for h in range(q_heads)])
+        ref = O.attention_decode_bf16(q, keys[:seq].reshape(seq, -1), values[:seq].reshape(seq, -1), q_heads,
+                                      kv_heads, hd, seq, 1.0 / np.sqrt(hd))
+        r = O.bf16_to_f32(ref).astype(np.float64)
+        assert np.all(np.abs(g - r) <= REL_TOL * np.maximum(np.abs(r), np.abs(r).mean())), f"call {step} vs oracle"
     # the rows both calls appended are the ones the allocating entry point wrote back to the host cache
     got_k = bufs["k"].download(np.uint16, blocks * kv_heads * PAGE * hd).reshape(blocks, kv_heads, PAGE, hd)
     for r in (position, position + 1):
@@ -103,8 +113,37 @@ def test_static_entry_point_rejects_what_does_not_fit():
     status = lib.stark_b200_op_attention_decode_static(dummy, dummy, dummy, dummy, dummy, None, None, None, None,
                                                        C.byref(d), None)
     assert status == _lib.STATUS_NAMES.index("context_limit")
-    d.splits = 31
-    d.kv_heads = 65  # more KV heads than the counter block holds
+    # more KV heads than the counter block holds, in a shape whose partials would fit (65 x 1 x 520 bytes): only
+    # the head bound can refuse it
+    d.splits = 1
+    d.kv_heads = 65
     d.q_heads = 65
     assert lib.stark_b200_op_attention_decode_static(dummy, dummy, dummy, dummy, dummy, None, None, None, None,
                                                      C.byref(d), None) == _lib.STATUS_NAMES.index("context_limit")
+
+
+def test_static_entry_point_accepts_the_largest_head_count():
+    """64 KV heads is the last count the arrival-counter block holds; the call must run and agree with the
+    allocating entry point."""
+    from stark_b200 import _lib, ops
+    from stark_b200._lib import check
+    lib = _lib.load()
+    rng = np.random.default_rng(7)
+    heads, hd, position, eps, theta = 64, 128, 5, 1e-6, 1e6
+    keys = np.zeros((position + 1, heads, hd), np.uint16)
+    values = np.zeros((position + 1, heads, hd), np.uint16)
+    keys[:position] = S.bf16_normal(rng, position * heads * hd).reshape(position, heads, hd)
+    values[:position] = S.bf16_normal(rng, position * heads * hd).reshape(position, heads, hd)
+    qkv = S.bf16_normal(rng, 3 * heads * hd, 2.0)
+    want = ops.attention_decode(qkv, keys.copy(), values.copy(), heads, heads, position, eps, theta, None, None,
+                                splits=2)
+    cos, sin = rope_tables(position + 1, theta)
+    k = ops.DeviceBuffer(heads * PAGE * hd * 2).upload(to_pages(keys[:position], 1))
+    v = ops.DeviceBuffer(heads * PAGE * hd * 2).upload(to_pages(values[:position], 1))
+    table = ops.DeviceBuffer(4).upload(np.zeros(1, np.int32))
+    dc, ds = ops.DeviceBuffer(cos.nbytes).upload(cos), ops.DeviceBuffer(sin.nbytes).upload(sin)
+    dq, out = ops.DeviceBuffer(qkv.nbytes).upload(qkv), ops.DeviceBuffer(heads * hd * 2)
+    d = _lib.AttentionDesc(C.sizeof(_lib.AttentionDesc), _lib.ABI_VERSION, heads, heads, hd, position, 0, 2, eps, 0.0)
+    check(lib.stark_b200_op_attention_decode_static(dq.ptr, k.ptr, v.ptr, table.ptr, out.ptr, None, None, dc.ptr,
+                                                    ds.ptr, C.byref(d), None), "op_attention_decode_static")
+    assert np.array_equal(out.download(np.uint16, heads * hd), want)
