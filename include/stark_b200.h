@@ -144,6 +144,16 @@ stark_b200_status stark_b200_qmatrix_device_bytes(const stark_b200_qmatrix *matr
 stark_b200_status stark_b200_qmatrix_unpack_codes(const stark_b200_qmatrix *matrix, uint8_t *dst_host,
                                                   size_t count);
 
+/* Y[m, rows] = X[m, columns] * W^T for many rows at once (a prompt chunk) on the tensor cores: bf16 rows in
+ * and out, f32 accumulation, a 4-bit affine matrix with a multiple of 32 rows (UNSUPPORTED otherwise); the
+ * dequantized operand is rounded to bf16, as in the reference's own tiled GEMM.
+ * Replaces MatmulKernel::encode with a quantized B and m > 8 rows
+ * (crates/stark-engine/src/backends/cpu/kernel/matmul/kernel.rs:168-285; on the reference's GPU path the tiled
+ * GEMM with a dequantizing prologue, backends/metal/kernel/matmul/gemm/gemm.metal:122-203).
+ * epilogue: 0 y = bf16(product); 1 y = bf16(bf16(product) + y), y holding the residual rows on entry;
+ * 2 SwiGLU over a pair-ordered [up; gate] matrix, y being [m, rows / 2]. */
+stark_b200_status stark_b200_op_qgemm(const stark_b200_qmatrix *matrix, const void *x, void *y, uint32_t m,
+                                      uint32_t epilogue, uint32_t location, void *stream);
 /* y[m, rows] = x[m, columns] * W^T.  Replaces MatmulKernel::encode for a quantized B with
  * m <= 8 input rows (crates/stark-engine/src/backends/cpu/kernel/matmul/kernel.rs:168-285) and
  * Weights::matvec (weights.rs:1311-1350, 2511-2553).  io_type selects bf16 or f32 vectors. */

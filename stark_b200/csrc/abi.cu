@@ -6,6 +6,7 @@
 
 #include "context.cuh"
 #include "qmv.cuh"
+#include "prefill.cuh"
 
 namespace sb {
 
@@ -287,6 +288,44 @@ stark_b200_status stark_b200_op_qmv(const stark_b200_qmatrix *matrix, const void
     }
     if (location == STARK_B200_HOST) {
         SB_CUDA(cudaMemcpyAsync(y, ctx->stage_out, yout * m, cudaMemcpyDeviceToHost, s));
+        SB_CUDA(cudaStreamSynchronize(s));
+    }
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_op_qgemm(const stark_b200_qmatrix *matrix, const void *x, void *y, uint32_t m,
+                                      uint32_t epilogue, uint32_t location, void *stream) {
+    QMatrix *w = const_cast<QMatrix *>(reinterpret_cast<const QMatrix *>(matrix));
+    if (!w || !x || !y || m == 0 || epilogue > 2u) return STARK_B200_INVALID_ARGUMENT;
+    if (w->format != kFmtAffine4) return STARK_B200_UNSUPPORTED;
+    DeviceContext *ctx = device_context();
+    if (!ctx) return STARK_B200_DEVICE_FAILURE;
+    cudaStream_t s = (cudaStream_t)stream;
+    stark_b200_status st;
+    const uint32_t out_cols = epilogue == 2u ? w->rows / 2u : w->rows;
+    const size_t xin = (size_t)m * w->columns * 2u, yout = (size_t)m * out_cols * 2u;
+    const uint16_t *dx = (const uint16_t *)x;
+    uint16_t *dy = (uint16_t *)y;
+    if (location == STARK_B200_HOST) {
+        if ((st = ensure_buffer(&ctx->stage_in, &ctx->stage_in_bytes, xin)) != STARK_B200_OK) return st;
+        if ((st = ensure_buffer(&ctx->stage_out, &ctx->stage_out_bytes, yout)) != STARK_B200_OK) return st;
+        SB_CUDA(cudaMemcpyAsync(ctx->stage_in, x, xin, cudaMemcpyHostToDevice, s));
+        if (epilogue == 1u) SB_CUDA(cudaMemcpyAsync(ctx->stage_out, y, yout, cudaMemcpyHostToDevice, s));
+        dx = (const uint16_t *)ctx->stage_in;
+        dy = (uint16_t *)ctx->stage_out;
+    }
+    GemmArgs a{};
+    a.w = w;
+    a.x = dx;
+    a.x_rows = m;
+    a.m = m;
+    a.out = dy;
+    a.ld_out = out_cols;
+    a.epilogue = epilogue == 0u ? kEpiStore : (epilogue == 1u ? kEpiResidual : kEpiSwiGlu);
+    a.error_word = ctx->error_word;
+    if ((st = prefill_gemm_launch(a, s)) != STARK_B200_OK) return st;
+    if (location == STARK_B200_HOST) {
+        SB_CUDA(cudaMemcpyAsync(y, ctx->stage_out, yout, cudaMemcpyDeviceToHost, s));
         SB_CUDA(cudaStreamSynchronize(s));
     }
     return STARK_B200_OK;

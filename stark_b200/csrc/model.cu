@@ -38,6 +38,13 @@ uint32_t input_vocab(const Model *m) { return m->tp.size > 1u ? m->tp_vocab_tota
 
 bool pdl_on() { return tunables().pdl != 0u; }
 
+// CTAs per KV head of the decode attention: about one CTA per SM in total, so that every CTA can be resident
+// beside the matvec before it and fetch its cache tiles while that matvec runs (measured on the 8-KV-head
+// shape: 18 per head beats 16, 20, 24 and 32).
+uint32_t default_attn_splits(uint32_t kv_heads) {
+    return std::min<uint32_t>(kMaxAttnSplits, std::max<uint32_t>(1u, 148u / kv_heads));
+}
+
 }  // namespace
 
 Model::~Model() {
@@ -50,6 +57,8 @@ Model::~Model() {
         qmatrix_free(L.down);
         cudaFree(L.attn_norm);
         cudaFree(L.mlp_norm);
+        cudaFree(L.attn_norm_b16);
+        cudaFree(L.mlp_norm_b16);
         cudaFree(L.q_norm);
         cudaFree(L.k_norm);
         cudaFree(L.kv.keys);
@@ -58,6 +67,7 @@ Model::~Model() {
     if (lm_head != embed) qmatrix_free(lm_head);
     qmatrix_free(embed);
     cudaFree(final_norm);
+    cudaFree(final_norm_b16);
     cudaFree(block_table);
     cudaFree(rope_cos);
     cudaFree(rope_sin);
@@ -82,6 +92,12 @@ Model::~Model() {
     if (tp_connected)
         for (uint32_t r = 0; r < tp.size; ++r)
             if (r != tp.rank && tp.base[r]) cudaIpcCloseMemHandle(tp.base[r]);
+    cudaFree(chunk_tokens);
+    cudaFree(chunk_h);
+    cudaFree(chunk_x);
+    cudaFree(chunk_qkv);
+    cudaFree(chunk_attn);
+    cudaFree(chunk_act);
     cudaFree(tp_local);
     cudaFree(sample_scratch);
     cudaFree(tp_seq);
@@ -152,7 +168,7 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     // CTAs per KV head: at most ~1.3 attention CTAs per SM in total.  One of them fits beside the two
     // resident CTAs of the matvec before it and fetches its cache tiles while that matvec runs; more
     // splits than that start cold.
-    m->attn_splits = std::min<uint32_t>(kMaxAttnSplits, std::max<uint32_t>(1u, 192u / c.kv_heads));
+    m->attn_splits = default_attn_splits(c.kv_heads);
     if (tunables().attn_splits) m->attn_splits = tunables().attn_splits;  // tuning: CTAs per KV head
     if ((st = dmalloc(&m->state, 1)) != STARK_B200_OK) return fail(st);
     if ((st = dmalloc(&m->pending, (size_t)c.context_tokens + 1u)) != STARK_B200_OK) return fail(st);
@@ -193,15 +209,29 @@ static stark_b200_status upload_f32(float **dst, const float *src, size_t n) {
     return STARK_B200_OK;
 }
 
+// The row norms multiply by bf16(weight) (normalization.rs:157-161): the rounded copy is made once, here.
+static stark_b200_status upload_norm(float **dst, uint16_t **dst_b16, const float *src, size_t n) {
+    stark_b200_status st = upload_f32(dst, src, n);
+    if (st != STARK_B200_OK) return st;
+    std::vector<uint16_t> rounded(n);
+    for (size_t i = 0; i < n; ++i) rounded[i] = f32_to_bf16_bits(src[i]);
+    if (*dst_b16) cudaFree(*dst_b16);
+    if ((st = dmalloc(dst_b16, n)) != STARK_B200_OK) return st;
+    SB_CUDA(cudaMemcpy(*dst_b16, rounded.data(), n * 2, cudaMemcpyHostToDevice));
+    return STARK_B200_OK;
+}
+
 stark_b200_status model_set_vector(Model *m, uint32_t layer, uint32_t which, const float *data, uint32_t count) {
     if (m->finalized) return STARK_B200_INVALID_STATE;
     const auto &c = m->cfg;
-    if (which == STARK_B200_VEC_FINAL_NORM) return count == c.hidden ? upload_f32(&m->final_norm, data, count) : STARK_B200_INVALID_ARGUMENT;
+    if (count != (which == STARK_B200_VEC_Q_NORM || which == STARK_B200_VEC_K_NORM ? kHeadDim : c.hidden) || count % 8u != 0)
+        return STARK_B200_INVALID_ARGUMENT;
+    if (which == STARK_B200_VEC_FINAL_NORM) return upload_norm(&m->final_norm, &m->final_norm_b16, data, count);
     if (layer >= c.layers) return STARK_B200_INVALID_ARGUMENT;
     auto &L = m->layers[layer];
     switch (which) {
-        case STARK_B200_VEC_ATTN_NORM: return count == c.hidden ? upload_f32(&L.attn_norm, data, count) : STARK_B200_INVALID_ARGUMENT;
-        case STARK_B200_VEC_MLP_NORM: return count == c.hidden ? upload_f32(&L.mlp_norm, data, count) : STARK_B200_INVALID_ARGUMENT;
+        case STARK_B200_VEC_ATTN_NORM: return upload_norm(&L.attn_norm, &L.attn_norm_b16, data, count);
+        case STARK_B200_VEC_MLP_NORM: return upload_norm(&L.mlp_norm, &L.mlp_norm_b16, data, count);
         case STARK_B200_VEC_Q_NORM: return count == kHeadDim ? upload_f32(&L.q_norm, data, count) : STARK_B200_INVALID_ARGUMENT;
         case STARK_B200_VEC_K_NORM: return count == kHeadDim ? upload_f32(&L.k_norm, data, count) : STARK_B200_INVALID_ARGUMENT;
         default: return STARK_B200_INVALID_ARGUMENT;
@@ -300,6 +330,7 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.y = m->qkv;
         a.prologue = kProRmsNorm;
         a.norm_weight = L.attn_norm;
+        a.norm_weight_bf16 = L.attn_norm_b16;
         a.epilogue = kEpiStore;
         a.trace = slot(n++);
         if (tp && l > 0) consume(a, 2u * l - 1u);
@@ -345,7 +376,9 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.y = m->act;
         a.prologue = kProRmsNorm;
         a.norm_weight = L.mlp_norm;
+        a.norm_weight_bf16 = L.mlp_norm_b16;
         a.epilogue = kEpiSwiGlu;
+        a.roomy = true;  // followed by the down projection, then the next layer's qkv: no attention CTA to host
         a.trace = slot(n++);
         if (tp) consume(a, 2u * l);
         if (consume_status != STARK_B200_OK) return consume_status;
@@ -374,7 +407,9 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
         a.y = m->logits;
         a.prologue = kProRmsNorm;
         a.norm_weight = m->final_norm;
+        a.norm_weight_bf16 = m->final_norm_b16;
         a.epilogue = kEpiLogits;
+        a.roomy = true;
         a.partial_max = m->partial_max;
         a.partial_index = m->partial_index;
         uint32_t grid = 0;
@@ -634,8 +669,7 @@ stark_b200_status model_recapture(Model *m) {
     if (!m->finalized || m->fenced) return STARK_B200_INVALID_STATE;
     if (m->use_mega) return STARK_B200_UNSUPPORTED;
     SB_CUDA(cudaStreamSynchronize(m->stream));
-    const uint32_t by_heads = std::min<uint32_t>(kMaxAttnSplits, std::max<uint32_t>(1u, 192u / m->cfg.kv_heads));
-    m->attn_splits = tunables().attn_splits ? tunables().attn_splits : by_heads;
+    m->attn_splits = tunables().attn_splits ? tunables().attn_splits : default_attn_splits(m->cfg.kv_heads);
     // one eager pass on a scratch copy of the step state (first use of a kernel instance sets its attributes)
     StepState saved;
     SB_CUDA(cudaMemcpy(&saved, m->state, sizeof(StepState), cudaMemcpyDeviceToHost));
@@ -691,6 +725,28 @@ stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count) {
     if (m->position + count > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
     for (size_t i = 0; i < count; ++i)
         if (ids[i] >= input_vocab(m)) return STARK_B200_INVALID_ARGUMENT;
+    // All rows but the last only fill the cache: enough of them go through the batched path (tensor-core
+    // contraction over whole chunks), after which the last row is an ordinary token at its position.
+    if (tunables().prefill_batch && count - 1 >= tunables().prefill_min_rows && model_batched_prefill_ready(m)) {
+        stark_b200_status bs = model_prefill_batched(m, ids, count - 1);
+        if (bs == STARK_B200_CANCELLED) {
+            m->cancel_requested = false;
+            cudaStreamSynchronize(m->stream);
+            model_reset(m);
+            return bs;
+        }
+        if (bs != STARK_B200_OK) return bs;
+        StepState last{};
+        last.position = (uint32_t)(m->position + count - 1);
+        last.token = ids[count - 1];
+        SB_CUDA(cudaMemcpyAsync(m->state, &last, sizeof(last), cudaMemcpyHostToDevice, m->stream));
+        stark_b200_status ls = launch_token(m, true);
+        if (ls != STARK_B200_OK) return ls;
+        m->position += count;
+        m->has_logits = true;
+        m->launches_issued += m->step_launches;
+        return STARK_B200_OK;
+    }
     // pending[0 .. count-2] = ids[1 ..]; the ingest-advance kernel pops one per row
     if (count > 1) SB_CUDA(cudaMemcpyAsync(m->pending, ids + 1, (count - 1) * 4, cudaMemcpyHostToDevice, m->stream));
     StepState hs{};

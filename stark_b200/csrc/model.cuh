@@ -13,6 +13,7 @@ namespace sb {
 struct ModelLayer {
     QMatrix *qkv = nullptr, *o = nullptr, *upgate = nullptr, *down = nullptr;
     float *attn_norm = nullptr, *mlp_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    uint16_t *attn_norm_b16 = nullptr, *mlp_norm_b16 = nullptr;  // the norm weights rounded to bf16, as the kernels use them
     KvLayer kv{nullptr, nullptr};
 };
 
@@ -23,6 +24,7 @@ struct Model {
     QMatrix *embed = nullptr, *lm_head = nullptr;
     std::vector<ModelLayer> layers;
     float *final_norm = nullptr;
+    uint16_t *final_norm_b16 = nullptr;
     uint32_t num_blocks = 0;
     int32_t *block_table = nullptr;
     float *rope_cos = nullptr, *rope_sin = nullptr;
@@ -54,6 +56,10 @@ struct Model {
     uint32_t *tp_seq = nullptr;    // [0] tokens finished: the base of the exchange tickets
     uint32_t tp_vocab_offset = 0, tp_vocab_total = 0;
     bool tp_connected = false;
+    // batched prompt ingest (prefill_model.cu): rows of one chunk, allocated at first use
+    uint32_t prefill_state = 0;  // 0 not examined, 1 the batched path serves this model, 2 it does not
+    uint32_t *chunk_tokens = nullptr;
+    uint16_t *chunk_h = nullptr, *chunk_x = nullptr, *chunk_qkv = nullptr, *chunk_attn = nullptr, *chunk_act = nullptr;
     void *sample_scratch = nullptr;     // device working memory of the sampler (allocated at first use)
     StepState *host_state = nullptr;    // pinned
     uint16_t *host_logits = nullptr;    // pinned
@@ -79,6 +85,8 @@ stark_b200_status model_recapture(Model *m);
 stark_b200_status model_rewind(Model *m, uint64_t position);
 stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count);
 stark_b200_status model_step(Model *m, uint32_t token, bool chained);
+bool model_batched_prefill_ready(Model *m);
+stark_b200_status model_prefill_batched(Model *m, const uint32_t *ids, size_t rows);
 stark_b200_status model_drain(Model *m);
 stark_b200_status model_next_token(Model *m, uint32_t *out);
 stark_b200_status model_readout_bf16(Model *m, uint16_t *dst, size_t count);

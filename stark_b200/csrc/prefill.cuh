@@ -1,0 +1,58 @@
+// Batched prompt rows: the dense contraction Y[M, N] = X[M, K] W[N, K]^T over a 4-bit affine matrix on the
+// tcgen05 tensor cores (prefill_gemm.cu), the row-wise operators around it and causal attention over the
+// paged cache (prefill_ops.cu), and the model-level chunk loop (prefill_model.cu).
+//
+// The reference prefills a prompt in chunks of 1024 rows through a tiled GEMM with a dequantizing prologue
+// (crates/stark-engine/src/engine/language_model/stream/stream.rs:441-686,
+// crates/stark-engine/src/backends/metal/kernel/matmul/gemm/gemm.metal:122-203); a prompt row here goes through
+// the same operators, with the same rounding points, as a row of the one-token path.
+#pragma once
+#include "ops.cuh"
+#include "qmv.cuh"
+
+namespace sb {
+
+constexpr uint32_t kPrefillChunkRows = 1024;  // crates/stark-engine/src/engine/language_model/stream/mod.rs:22
+
+struct GemmArgs {
+    const QMatrix *w;     // kFmtAffine4, rows a multiple of 32
+    const uint16_t *x;    // [x_rows, K] bf16, row stride K
+    uint32_t x_rows;      // rows the buffer holds (the extent the copy engine may touch)
+    uint32_t m;           // rows in use, <= x_rows
+    uint16_t *out;        // [m, ld_out] bf16; kEpiResidual reads and rewrites it
+    uint32_t ld_out;
+    QmvEpilogue epilogue;  // kEpiStore, kEpiResidual or kEpiSwiGlu
+    uint32_t *error_word;
+};
+// One launch; the kernel bounds every wait and reports through the error word.
+stark_b200_status prefill_gemm_launch(const GemmArgs &args, cudaStream_t stream);
+// ---- row-wise operators over a chunk of M rows (prefill_ops.cu) ---------------------------------------
+// h[i] = embedding row of tokens[i]
+stark_b200_status embed_rows_launch(const QMatrix *table, const uint32_t *tokens, uint32_t m, uint16_t *h,
+                                    cudaStream_t stream);
+// out[i] = bf16(bf16(h[i] * rms_inv_i) * bf16(w))        normalization.rs:13-191 (only-normalization mode)
+stark_b200_status rmsnorm_rows_launch(const uint16_t *h, const float *weight, uint16_t *out, uint32_t m, uint32_t d,
+                                      float eps, cudaStream_t stream);
+// Per row and head: q heads normalized and rotated in place, k heads normalized, rotated and appended to the
+// cache at position first_pos + i together with the v heads.
+struct RopeAppendArgs {
+    uint16_t *qkv;  // [m, (q_heads + 2 kv_heads) * 128]
+    KvLayer kv;
+    const int32_t *block_table;
+    const float *q_norm, *k_norm, *rope_cos, *rope_sin;
+    uint32_t m, first_pos, q_heads, kv_heads;
+    float eps;
+};
+stark_b200_status rope_append_rows_launch(const RopeAppendArgs &a, cudaStream_t stream);
+// Causal attention of the chunk's rows over the cache rows [0, first_pos + i]; out [m, q_heads * 128] bf16.
+struct PrefillAttnArgs {
+    const uint16_t *qkv;  // rotated q heads of the chunk
+    KvLayer kv;
+    const int32_t *block_table;
+    uint16_t *out;
+    uint32_t m, first_pos, q_heads, kv_heads;
+    float scale;
+};
+stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_t stream);
+
+}  // namespace sb

@@ -1,0 +1,450 @@
+// Y[M, N] = X[M, K] W[N, K]^T for a 4-bit affine group-64 matrix, many rows at a time: the prompt-chunk
+// contraction of the token loop on the sm_100a tensor cores (tcgen05.mma, accumulators in tensor memory).
+//
+// One CTA owns a tile of 256 rows x 128 output features and walks K in steps of one quantization group (64):
+//   warp 0      one thread: TMA loads of the two 128-row activation boxes of the step (bf16, 128-byte swizzle)
+//   warp 1      allocates tensor memory; one thread issues 2 x 4 tcgen05.mma (128 x 128 x 16) per step and
+//               commits them to the barrier that frees the stage
+//   warps 2-9   the dequantizing prologue: warp d turns record (16 features x 64 columns, 576 bytes, read
+//               straight from the re-tiled matrix the matvec kernels stream) into bf16 rows of the B operand --
+//               codes become exact bf16 integers (shift, lop3 and one bf16 subtract per pair), then
+//               bf16(scale * q + bias) in one bf16 FMA per pair -- written in the swizzled K-major layout the
+//               tensor core reads.  The same warps run the epilogue: tcgen05.ld of the accumulators, bf16 rounding,
+//               residual add or SwiGLU, 64-byte row segments to global memory.
+// Rounding points are those of the one-row path (f32 accumulation, one bf16 rounding of the product, then the
+// epilogue's own roundings); the operand W is rounded to bf16, the activations' type, as the reference's own
+// tiled GEMM does, where the one-row path keeps scale * q + bias in f32: inside the per-operator tolerance.
+// Every wait is bounded; a wait that runs out sets the error word, the CTA drains and frees its tensor memory.
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "device_math.cuh"
+#include "prefill.cuh"
+#include "tunables.cuh"
+
+namespace sb {
+
+namespace {
+
+constexpr uint32_t kBM = 256, kBN = 128, kBK = 64;
+constexpr uint32_t kStages = 4;
+constexpr uint32_t kABox = 128u * 128u;            // one 128-row x 64-column bf16 box: 16 KB
+constexpr uint32_t kAStage = 2u * kABox;           // 32 KB
+constexpr uint32_t kBStage = kBN * 128u;           // 16 KB
+constexpr uint32_t kStageBytes = kAStage + kBStage;
+constexpr uint32_t kDequantWarps = 8;
+constexpr uint32_t kGemmThreads = (2u + kDequantWarps) * 32u;
+constexpr uint32_t kTmemColumns = 256;             // two 128 x 128 f32 accumulators
+constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024u /* alignment */ + 256u /* barriers */;
+
+struct GemmParams {
+    const uint8_t *w;
+    uint32_t row_tiles, groups, rows;
+    uint32_t m;
+    uint16_t *out;
+    uint32_t ld_out;
+    uint32_t epilogue;
+    uint32_t *error_word;
+    uint32_t stop_after;  // 0: the whole kernel.  1: set-up and tensor-memory allocation only; 2: + operand staging
+                          // (no tensor-core work); 3: + tcgen05.mma (accumulators not read).  A bring-up aid: a
+                          // fault in one kind of instruction is located by the first stage that shows it.
+};
+
+__device__ inline void tma_load_2d(void *dst, const CUtensorMap *map, uint32_t x, uint32_t y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+__device__ inline void tmem_alloc(uint32_t *slot, uint32_t columns) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot)), "r"(columns)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ inline void tmem_dealloc(uint32_t taddr, uint32_t columns) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+__device__ inline void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ inline void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ inline void proxy_fence_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ inline void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ inline void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ inline void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ inline uint64_t smem_desc_sw128(uint32_t smem_addr) {
+    const uint64_t lo = (uint64_t)((smem_addr & 0x3ffffu) >> 4) | ((uint64_t)1u << 16);  // start, leading offset 16 B
+    const uint64_t hi = (uint64_t)(1024u >> 4)      // stride between 8-row groups
+                        | ((uint64_t)1u << 14)      // descriptor version of this architecture
+                        | ((uint64_t)2u << 29);     // 128-byte swizzle
+    return lo | (hi << 32);
+}
+// Instruction descriptor: D f32, A bf16 (activations), B bf16 (dequantized weights), both K-major, M 128, N 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((128u >> 4) << 24);
+
+struct RecordRegs {
+    uint4 q;
+    uint32_t scales, biases;  // bf16 pairs: rows g and g + 8
+};
+
+__device__ inline RecordRegs load_record(const uint8_t *w, uint32_t tile, uint32_t row_tiles, uint32_t groups,
+                                         uint32_t kg, uint32_t lane) {
+    RecordRegs r;
+    if (tile < row_tiles) {
+        const uint8_t *rec = w + ((size_t)tile * groups + kg) * kA4RecordBytes;
+        r.q = ldg_nc_v4(rec + lane * 16u);
+        r.scales = __ldg(reinterpret_cast<const uint32_t *>(rec + 512u + 4u * (lane >> 2)));
+        r.biases = __ldg(reinterpret_cast<const uint32_t *>(rec + 544u + 4u * (lane >> 2)));
+    } else {  // past the last row tile: zero rows
+        r.q = make_uint4(0u, 0u, 0u, 0u);
+        r.scales = 0u;
+        r.biases = 0u;
+    }
+    return r;
+}
+
+// One record word -> the eight codes as exact bf16 integers, in the fragment order of dequant_a4_word:
+// (w >> 4s) & 0x000f000f | 0x43004300 is the bf16 pair (128 + q, 128 + q') -- 0x4300 is 128.0 and the last
+// mantissa bit of a bf16 in [128, 256) weighs 1 -- and 128 is then subtracted exactly.
+__device__ inline void codes_to_bf16(uint32_t w, __nv_bfloat162 (&q)[4]) {
+    const uint32_t magic = 0x43004300u;
+    const __nv_bfloat162 k128 = __float2bfloat162_rn(128.0f);
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        const uint32_t v = lop3_and_or(w >> (4 * s), 0x000f000fu, magic);
+        q[s] = __hsub2(*reinterpret_cast<const __nv_bfloat162 *>(&v), k128);
+    }
+}
+__device__ inline __nv_bfloat162 bf16_pair(uint32_t bits16) {
+    const uint32_t v = bits16 | (bits16 << 16);
+    return *reinterpret_cast<const __nv_bfloat162 *>(&v);
+}
+
+// One record (16 features x 64 columns) into rows [16 d, 16 d + 16) of the B stage: lane (g, t) owns columns
+// 16 t .. 16 t + 15 of rows g and g + 8, i.e. two 16-byte chunks in each of the two rows.
+__device__ inline void dequant_record_to_smem(const RecordRegs &r, uint8_t *b_stage, uint32_t d, uint32_t lane) {
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const __nv_bfloat162 s0 = bf16_pair(r.scales & 0xffffu), s1 = bf16_pair(r.scales >> 16);
+    const __nv_bfloat162 b0 = bf16_pair(r.biases & 0xffffu), b1 = bf16_pair(r.biases >> 16);
+    const uint32_t ww[4] = {r.q.x, r.q.y, r.q.z, r.q.w};
+    uint32_t lo_row[8], hi_row[8];  // 16 bf16 values per row
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 a[4];
+        codes_to_bf16(ww[j], a);  // a[0], a[2]: row g, columns 4j + {0,1}, {2,3}; a[1], a[3]: row g + 8
+        // bf16(scale * q + bias): one fused multiply-add, one rounding -- the dequantized operand in the
+        // activations' type, as the reference's tiled GEMM stages it (gemm.metal:122-203, `threadgroup BT b_shared`)
+        const __nv_bfloat162 v0 = __hfma2(a[0], s0, b0);
+        const __nv_bfloat162 v2 = __hfma2(a[2], s0, b0);
+        const __nv_bfloat162 v1 = __hfma2(a[1], s1, b1);
+        const __nv_bfloat162 v3 = __hfma2(a[3], s1, b1);
+        lo_row[2 * j] = *reinterpret_cast<const uint32_t *>(&v0);
+        lo_row[2 * j + 1] = *reinterpret_cast<const uint32_t *>(&v2);
+        hi_row[2 * j] = *reinterpret_cast<const uint32_t *>(&v1);
+        hi_row[2 * j + 1] = *reinterpret_cast<const uint32_t *>(&v3);
+    }
+    // row R of the stage starts at R * 128; its 16-byte chunk c sits at chunk position c ^ (R & 7)
+    const uint32_t r_lo = 16u * d + g, r_hi = r_lo + 8u;  // both have (R & 7) == g
+    uint8_t *p_lo = b_stage + r_lo * 128u, *p_hi = b_stage + r_hi * 128u;
+    const uint32_t c0 = ((2u * t) ^ g) * 16u, c1 = ((2u * t + 1u) ^ g) * 16u;
+    *reinterpret_cast<uint4 *>(p_lo + c0) = make_uint4(lo_row[0], lo_row[1], lo_row[2], lo_row[3]);
+    *reinterpret_cast<uint4 *>(p_lo + c1) = make_uint4(lo_row[4], lo_row[5], lo_row[6], lo_row[7]);
+    *reinterpret_cast<uint4 *>(p_hi + c0) = make_uint4(hi_row[0], hi_row[1], hi_row[2], hi_row[3]);
+    *reinterpret_cast<uint4 *>(p_hi + c1) = make_uint4(hi_row[4], hi_row[5], hi_row[6], hi_row[7]);
+}
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) {
+    extern __shared__ uint8_t gemm_smem_raw[];
+    // operand stages need 1024-byte alignment (swizzle atom = 8 rows x 128 bytes)
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint8_t *stages = smem;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kStages * kStageBytes);
+    uint64_t *full_a = bars, *full_b = bars + kStages, *empty = bars + 2 * kStages, *acc_full = bars + 3 * kStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kStages + 1);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t n_tile0 = blockIdx.x * (kBN / 16u);  // first 16-row storage tile of this CTA
+    const uint32_t m0 = blockIdx.y * kBM;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < kStages; ++s) {
+            mbar_init(&full_a[s], 1);
+            mbar_init(&full_b[s], kDequantWarps);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, kTmemColumns);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t stop = p.stop_after;
+
+    if (stop == 1u) {
+        // nothing between allocation and release
+    } else if (warp == 0) {
+        // ------------------------------------------------ activation tiles by TMA
+        if (lane == 0) {
+            uint32_t slot = 0, phase = 1;  // a fresh barrier passes a wait on parity 1
+            for (uint32_t kg = 0; kg < p.groups; ++kg) {
+                if (!mbar_wait_bounded(&empty[slot], phase, abort_flag)) {
+                    *abort_flag = 1;
+                    atomicOr(p.error_word, kErrMbarTimeout);
+                    break;
+                }
+                uint8_t *a_stage = stages + slot * kStageBytes;
+                mbar_arrive_expect_tx(&full_a[slot], kAStage);
+                tma_load_2d(a_stage, &x_map, kg * kBK, m0, &full_a[slot]);
+                tma_load_2d(a_stage + kABox, &x_map, kg * kBK, m0 + 128u, &full_a[slot]);
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ tensor-core issue
+        if (lane == 0) {
+            uint32_t slot = 0, phase = 0;
+            bool ok = true;
+            for (uint32_t kg = 0; kg < p.groups && ok; ++kg) {
+                ok = mbar_wait_bounded(&full_a[slot], phase, abort_flag) && mbar_wait_bounded(&full_b[slot], phase, abort_flag);
+                if (!ok) {
+                    *abort_flag = 1;
+                    atomicOr(p.error_word, kErrMbarTimeout);
+                    break;
+                }
+                if (stop == 2u) {  // staging only: hand the stage back without touching the tensor core
+                    mbar_arrive(&empty[slot]);
+                    if (++slot == kStages) {
+                        slot = 0;
+                        phase ^= 1u;
+                    }
+                    continue;
+                }
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(stages + slot * kStageBytes);
+                const uint32_t b_addr = a_addr + kAStage;
+#pragma unroll
+                for (uint32_t half = 0; half < 2; ++half) {
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < kBK / 16u; ++k4) {
+                        const uint64_t adesc = smem_desc_sw128(a_addr + half * kABox + k4 * 32u);
+                        const uint64_t bdesc = smem_desc_sw128(b_addr + k4 * 32u);
+                        umma_f16(tmem_base + half * kBN, adesc, bdesc, kIdesc, (kg | k4) != 0u ? 1u : 0u);
+                    }
+                }
+                umma_commit(&empty[slot]);  // arrives when the MMAs reading this stage are done
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+            if (stop == 2u) mbar_arrive(acc_full);
+            else umma_commit(acc_full);  // also on the give-up path: the epilogue warps wait on it
+        }
+    } else {
+        // ------------------------------------------------ dequantizing prologue (one record per warp per step)
+        const uint32_t d = warp - 2u;
+        const uint32_t tile = n_tile0 + d;
+        uint32_t slot = 0, phase = 1;
+        constexpr uint32_t kAhead = 4;  // records requested ahead of use (global latency >> one step)
+        RecordRegs ring[kAhead];
+#pragma unroll
+        for (uint32_t i = 0; i < kAhead; ++i)
+            ring[i] = load_record(p.w, i < p.groups ? tile : 0xffffffffu, p.row_tiles, p.groups, i, lane);
+        bool ok = true;
+        for (uint32_t kb = 0; kb < p.groups && ok; kb += kAhead) {
+#pragma unroll
+            for (uint32_t i = 0; i < kAhead; ++i) {
+                const uint32_t kg = kb + i;
+                if (kg >= p.groups) break;
+                const RecordRegs cur = ring[i];
+                const uint32_t next = kg + kAhead;
+                ring[i] = load_record(p.w, next < p.groups ? tile : 0xffffffffu, p.row_tiles, p.groups,
+                                      next < p.groups ? next : 0u, lane);
+                if (!mbar_wait_bounded(&empty[slot], phase, abort_flag)) {
+                    if (lane == 0) {
+                        *abort_flag = 1;
+                        atomicOr(p.error_word, kErrMbarTimeout);
+                    }
+                    ok = false;
+                    break;
+                }
+                dequant_record_to_smem(cur, stages + slot * kStageBytes + kAStage, d, lane);
+                proxy_fence_async();  // the tensor core reads shared memory through the async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_b[slot]);
+                if (++slot == kStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+
+        // ------------------------------------------------ epilogue: warp -> (sub-partition, accumulator half)
+        const uint32_t sub = warp & 3u, half = d >> 2;
+        if (!mbar_wait_bounded(acc_full, 0, abort_flag) && lane == 0) atomicOr(p.error_word, kErrMbarTimeout);
+        tc_fence_after();
+        const uint32_t row = m0 + half * 128u + sub * 32u + lane;  // this thread's row of the output
+        const bool row_ok = row < p.m;
+#pragma unroll 1
+        for (uint32_t c = 0; c < (stop == 0u ? kBN / 32u : 0u); ++c) {
+            uint32_t acc[32];
+            tmem_ld_32x32(tmem_base + ((sub * 32u) << 16) + half * kBN + c * 32u, acc);
+            // columns of the accumulator are storage rows of the matrix: feature = 16 * tile + r
+            const uint32_t f0 = n_tile0 * 16u + c * 32u;
+            if (p.epilogue == kEpiSwiGlu) {
+                // storage tiles alternate up / gate (pair_halves): columns 0-15 up rows, 16-31 the gate rows
+                // of the same logical rows.  gated_act_mul.rs:80-95: silu in f32 -> bf16, product -> bf16
+                uint32_t packed[8];
+#pragma unroll
+                for (int i = 0; i < 16; i += 2) {
+                    float o2[2];
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float up = bf16_round(__uint_as_float(acc[i + e]));
+                        const float gate = bf16_round(__uint_as_float(acc[16 + i + e]));
+                        const float activated = bf16_round(gate / (1.0f + expf(-1.0f * gate)));
+                        o2[e] = up * activated;
+                    }
+                    packed[i >> 1] = f32x2_to_bf16x2(o2[0], o2[1]);
+                }
+                const uint32_t o0 = (f0 / 32u) * 16u;  // logical row of the pair
+                if (row_ok && o0 + 16u <= p.rows / 2u) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(p.out + (size_t)row * p.ld_out + o0);
+                    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+            } else {
+                const bool cols_ok = f0 + 32u <= p.rows;
+                uint16_t *dst16 = p.out + (size_t)row * p.ld_out + f0;
+                uint32_t packed[16];
+                if (p.epilogue == kEpiResidual && row_ok && cols_ok) {
+                    const uint4 *src = reinterpret_cast<const uint4 *>(dst16);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        const uint4 rv = src[q4];
+                        const uint32_t rr[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int i = q4 * 8 + e * 2;
+                            const uint32_t y2 = f32x2_to_bf16x2(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]));
+                            packed[q4 * 4 + e] = f32x2_to_bf16x2(__uint_as_float(y2 << 16) + __uint_as_float(rr[e] << 16),
+                                                                 __uint_as_float(y2 & 0xffff0000u) +
+                                                                     __uint_as_float(rr[e] & 0xffff0000u));
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2)
+                        packed[i >> 1] = f32x2_to_bf16x2(__uint_as_float(acc[i]), __uint_as_float(acc[i + 1]));
+                }
+                if (row_ok && cols_ok) {
+                    uint4 *dst = reinterpret_cast<uint4 *>(dst16);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        dst[q4] = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemColumns);
+    }
+}
+
+// ---------------------------------------------------------------------------------------- host side
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = [] {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(p);
+    }();
+    return fn;
+}
+
+}  // namespace
+
+stark_b200_status prefill_gemm_launch(const GemmArgs &a, cudaStream_t stream) {
+    const QMatrix *w = a.w;
+    if (!w || !a.x || !a.out || a.m == 0 || a.m > a.x_rows) return STARK_B200_INVALID_ARGUMENT;
+    if (w->format != kFmtAffine4) return STARK_B200_UNSUPPORTED;
+    if (a.epilogue != kEpiStore && a.epilogue != kEpiResidual && a.epilogue != kEpiSwiGlu) return STARK_B200_UNSUPPORTED;
+    if (a.epilogue == kEpiSwiGlu && !w->pair_halves) return STARK_B200_INVALID_ARGUMENT;
+    if (w->rows % 32u != 0) return STARK_B200_UNSUPPORTED;  // the epilogue writes whole 32-feature segments
+    if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.out) & 15u) || (a.ld_out % 8u) != 0)
+        return STARK_B200_INVALID_ARGUMENT;
+    EncodeTiledFn encode = encode_tiled();
+    if (!encode) return STARK_B200_UNSUPPORTED;
+
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {w->columns, a.x_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)w->columns * 2u};
+    const cuuint32_t box[2] = {kBK, 128u};
+    const cuuint32_t elem[2] = {1u, 1u};
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(a.x), dims, strides, box, elem,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return STARK_B200_DEVICE_FAILURE;
+
+    GemmParams p{};
+    p.w = w->data;
+    p.row_tiles = w->row_tiles;
+    p.groups = w->groups;
+    p.rows = w->rows;
+    p.m = a.m;
+    p.out = a.out;
+    p.ld_out = a.ld_out;
+    p.epilogue = a.epilogue;
+    p.error_word = a.error_word;
+    p.stop_after = tunables().gemm_stop_after;
+    static SmemOptIn once;
+    if (stark_b200_status s = ensure_dynamic_smem(prefill_gemm_a4_kernel, (int)kGemmSmem, once)) return s;
+    const dim3 grid((w->row_tiles * 16u + kBN - 1u) / kBN, (a.m + kBM - 1u) / kBM);
+    prefill_gemm_a4_kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(map, p);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+}  // namespace sb

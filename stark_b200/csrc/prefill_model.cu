@@ -1,0 +1,123 @@
+// Chunked prompt ingest of the dense decoder: up to 1024 rows at a time through the tensor-core contraction and
+// the row-wise operators, layer by layer, leaving the rows' keys and values in the paged cache exactly where the
+// one-token path would have put them.  Mirrors the reference's prefill loop
+// (crates/stark-engine/src/engine/language_model/stream/stream.rs:441-686: chunks of 1024 rows, each a batched
+// pass over the layers; the prompt's last row then goes through the sampling pass).
+#include <algorithm>
+#include <cmath>
+
+#include "model.cuh"
+#include "prefill.cuh"
+#include "tunables.cuh"
+
+namespace sb {
+
+namespace {
+
+template <typename T>
+stark_b200_status dmalloc_rows(T **p, size_t count) {
+    *p = nullptr;
+    SB_CUDA(cudaMalloc(p, count * sizeof(T)));
+    return STARK_B200_OK;
+}
+
+stark_b200_status ensure_chunk_buffers(Model *m) {
+    if (m->chunk_h) return STARK_B200_OK;
+    const auto &c = m->cfg;
+    const size_t rows = kPrefillChunkRows;
+    const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
+    stark_b200_status st;
+    if ((st = dmalloc_rows(&m->chunk_tokens, rows)) != STARK_B200_OK) return st;
+    if ((st = dmalloc_rows(&m->chunk_h, rows * c.hidden)) != STARK_B200_OK) return st;
+    if ((st = dmalloc_rows(&m->chunk_x, rows * c.hidden)) != STARK_B200_OK) return st;
+    if ((st = dmalloc_rows(&m->chunk_qkv, rows * qkv_n)) != STARK_B200_OK) return st;
+    if ((st = dmalloc_rows(&m->chunk_attn, rows * c.q_heads * kHeadDim)) != STARK_B200_OK) return st;
+    if ((st = dmalloc_rows(&m->chunk_act, rows * c.inter)) != STARK_B200_OK) return st;
+    return STARK_B200_OK;
+}
+
+}  // namespace
+
+// Whether the batched path can take this model's prompt rows: one GPU, the recorded-launch token path, layer
+// matrices whose rows fill whole 128-feature tiles (examined once, at first use).
+bool model_batched_prefill_ready(Model *m) {
+    if (m->prefill_state == 2u) return false;
+    if (m->prefill_state == 1u) return true;
+    m->prefill_state = 2u;
+    if (m->tp.size > 1u || m->use_mega) return false;
+    for (auto &L : m->layers)
+        for (QMatrix *q : {L.qkv, L.o, L.upgate, L.down}) {
+            if (q->rows % 128u != 0 || q->columns % 64u != 0) return false;
+        }
+    if (m->cfg.hidden > 12288u || ensure_chunk_buffers(m) != STARK_B200_OK) return false;
+    m->prefill_state = 1u;
+    return true;
+}
+
+// Ingests `rows` prompt rows starting at position m->position (cache only: no logits).  The caller has checked
+// ids and the context limit.
+stark_b200_status model_prefill_batched(Model *m, const uint32_t *ids, size_t rows) {
+    const auto &c = m->cfg;
+    DeviceContext *ctx = device_context();
+    if (!ctx) return STARK_B200_DEVICE_FAILURE;
+    cudaStream_t s = m->stream;
+    const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
+    const float scale = 1.0f / sqrtf((float)kHeadDim);
+    stark_b200_status st;
+    uint64_t launches = 0;
+    for (size_t done = 0; done < rows; done += kPrefillChunkRows) {
+        if (m->cancel_requested) return STARK_B200_CANCELLED;
+        const uint32_t mrows = (uint32_t)std::min<size_t>(kPrefillChunkRows, rows - done);
+        const uint32_t first_pos = (uint32_t)(m->position + done);
+        SB_CUDA(cudaMemcpyAsync(m->chunk_tokens, ids + done, (size_t)mrows * 4u, cudaMemcpyHostToDevice, s));
+        if ((st = embed_rows_launch(m->embed, m->chunk_tokens, mrows, m->chunk_h, s)) != STARK_B200_OK) return st;
+        ++launches;
+        for (auto &L : m->layers) {
+            GemmArgs g{};
+            g.x_rows = kPrefillChunkRows;
+            g.m = mrows;
+            g.error_word = ctx->error_word;
+            // qkv = W_qkv rmsnorm(h)
+            if ((st = rmsnorm_rows_launch(m->chunk_h, L.attn_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
+            g.w = L.qkv;
+            g.x = m->chunk_x;
+            g.out = m->chunk_qkv;
+            g.ld_out = qkv_n;
+            g.epilogue = kEpiStore;
+            if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+            // per-head norm, RoPE, cache append; causal attention over the cache
+            RopeAppendArgs ra{m->chunk_qkv, L.kv, m->block_table, L.q_norm, L.k_norm, m->rope_cos, m->rope_sin,
+                              mrows, first_pos, c.q_heads, c.kv_heads, c.eps};
+            if ((st = rope_append_rows_launch(ra, s)) != STARK_B200_OK) return st;
+            PrefillAttnArgs pa{m->chunk_qkv, L.kv, m->block_table, m->chunk_attn, mrows, first_pos, c.q_heads, c.kv_heads, scale};
+            if ((st = prefill_attention_launch(pa, s)) != STARK_B200_OK) return st;
+            // h = bf16(bf16(W_o attn) + h)
+            g.w = L.o;
+            g.x = m->chunk_attn;
+            g.out = m->chunk_h;
+            g.ld_out = c.hidden;
+            g.epilogue = kEpiResidual;
+            if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+            // act = silu(gate) * up
+            if ((st = rmsnorm_rows_launch(m->chunk_h, L.mlp_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
+            g.w = L.upgate;
+            g.x = m->chunk_x;
+            g.out = m->chunk_act;
+            g.ld_out = c.inter;
+            g.epilogue = kEpiSwiGlu;
+            if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+            // h = bf16(bf16(W_down act) + h)
+            g.w = L.down;
+            g.x = m->chunk_act;
+            g.out = m->chunk_h;
+            g.ld_out = c.hidden;
+            g.epilogue = kEpiResidual;
+            if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+            launches += 8;
+        }
+    }
+    m->launches_issued += launches;
+    return STARK_B200_OK;
+}
+
+}  // namespace sb

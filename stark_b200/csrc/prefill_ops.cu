@@ -1,0 +1,381 @@
+// Row-wise operators of the batched prompt path and causal attention over the paged cache (sm_100a).
+// Each reproduces, for every row of a chunk, what the one-token kernels do for their single row -- same
+// formulas, same rounding points -- so that a prompt row costs the same arithmetic whichever path takes it.
+#include <algorithm>
+
+#include "device_math.cuh"
+#include "prefill.cuh"
+
+namespace sb {
+
+namespace {
+
+// ------------------------------------------------------------------------------------------ embedding rows
+// input_embedding_lookup.rs:17-160: row `token` of the quantized table, scale * code + bias with two roundings,
+// then bf16.  Same record arithmetic as embedding_row_kernel (ops.cu), one row per blockIdx.y.
+__global__ void embed_rows_kernel(const uint8_t *__restrict__ data, uint32_t rows, uint32_t columns,
+                                  uint32_t pair_halves, const uint32_t *__restrict__ tokens, uint16_t *out) {
+    const uint32_t token = tokens[blockIdx.y];
+    uint16_t *dst = out + (size_t)blockIdx.y * columns;
+    const uint32_t groups = columns / 64u;
+    for (uint32_t col = blockIdx.x * blockDim.x + threadIdx.x; col < columns; col += gridDim.x * blockDim.x) {
+        if (token >= rows) {  // input_embedding_lookup.rs:64-68
+            dst[col] = 0;
+            continue;
+        }
+        uint32_t tile, r;
+        if (!pair_halves) {
+            tile = token / 16u;
+            r = token % 16u;
+        } else {
+            const uint32_t half = rows / 2u, inner = token % half;
+            tile = 2u * (inner / 16u) + (token >= half ? 1u : 0u);
+            r = inner % 16u;
+        }
+        const uint32_t g = r & 7u, hrow = r >> 3;
+        const uint32_t kg = col / 64u, c = col % 64u;
+        const uint32_t t = c / 16u, j = (c % 16u) / 4u, r2 = (c % 4u) / 2u, e = c & 1u;
+        const uint8_t *rec = data + ((size_t)tile * groups + kg) * kA4RecordBytes;
+        const uint32_t word = *reinterpret_cast<const uint32_t *>(rec + (g * 4u + t) * 16u + j * 4u);
+        const uint32_t q = (word >> (4u * (4u * e + 2u * r2 + hrow))) & 15u;
+        const uint16_t *planes = reinterpret_cast<const uint16_t *>(rec + 512u);
+        const float scale = bf16_bits_to_f32(planes[2u * g + hrow]);
+        const float bias = bf16_bits_to_f32(planes[16u + 2u * g + hrow]);
+        dst[col] = f32_to_bf16_bits(__fadd_rn(__fmul_rn(scale, (float)q), bias));
+    }
+}
+
+// ------------------------------------------------------------------------------------------ RMS norm rows
+// normalization.rs:13-191, only-normalization mode: f32 sum of squares, rms_inv = 1 / sqrt(mean + eps),
+// bf16(x * rms_inv) * bf16(weight) rounded to bf16.  One CTA per row, the row held in registers.
+constexpr int kNormThreads = 256;
+constexpr int kNormMaxChunks = 6;  // 8 elements each: rows of up to 12288
+__global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const uint16_t *__restrict__ h,
+                                                                    const float *__restrict__ weight,
+                                                                    uint16_t *__restrict__ out, uint32_t d, float eps) {
+    __shared__ float red[kNormThreads / 32];
+    const uint32_t tid = threadIdx.x, chunks = d / 8u;
+    const uint4 *src = reinterpret_cast<const uint4 *>(h + (size_t)blockIdx.x * d);
+    uint4 v[kNormMaxChunks];
+    float sumsq = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kNormMaxChunks; ++r) {
+        const uint32_t c = tid + r * kNormThreads;
+        v[r] = c < chunks ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+        const uint32_t w4[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float a = __uint_as_float(w4[i] << 16), b = __uint_as_float(w4[i] & 0xffff0000u);
+            sumsq = fmaf(a, a, sumsq);
+            sumsq = fmaf(b, b, sumsq);
+        }
+    }
+    sumsq = warp_sum(sumsq);
+    if ((tid & 31u) == 0) red[tid >> 5] = sumsq;
+    __syncthreads();
+    float total = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kNormThreads / 32; ++i) total += red[i];
+    const float rms_inv = 1.0f / sqrtf(total / (float)d + eps);
+    uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t)blockIdx.x * d);
+#pragma unroll
+    for (int r = 0; r < kNormMaxChunks; ++r) {
+        const uint32_t c = tid + r * kNormThreads;
+        if (c >= chunks) continue;
+        const float4 w0 = reinterpret_cast<const float4 *>(weight)[2 * c], w1 = reinterpret_cast<const float4 *>(weight)[2 * c + 1];
+        const float wf[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const uint32_t w4[4] = {v[r].x, v[r].y, v[r].z, v[r].w};
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t n2 = f32x2_to_bf16x2(__uint_as_float(w4[i] << 16) * rms_inv,
+                                                __uint_as_float(w4[i] & 0xffff0000u) * rms_inv);
+            o[i] = f32x2_to_bf16x2(__uint_as_float(n2 << 16) * bf16_round(wf[2 * i]),
+                                   __uint_as_float(n2 & 0xffff0000u) * bf16_round(wf[2 * i + 1]));
+        }
+        dst[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ head norm + RoPE + append
+// One warp per (row, head): q heads in place, k heads into the cache row of the token's position, v heads copied
+// (qkv_norm.rs:8-111, attention_prepare.rs:7-43,187-316; the helper is the one the decode attention uses).
+struct RopeParams {
+    uint16_t *qkv;
+    uint16_t *keys, *values;
+    const int32_t *block_table;
+    const float *q_norm, *k_norm, *rope_cos, *rope_sin;
+    uint32_t first_pos, q_heads, kv_heads;
+    float eps;
+};
+__global__ void __launch_bounds__(128) rope_append_rows_kernel(const RopeParams p) {
+    __shared__ __align__(16) uint16_t head_s[4][kHeadDim];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t head = blockIdx.x * 4u + warp, row = blockIdx.y;
+    const uint32_t heads = p.q_heads + 2u * p.kv_heads;
+    if (head >= heads) return;
+    const uint32_t pos = p.first_pos + row;
+    uint16_t *src = p.qkv + ((size_t)row * heads + head) * kHeadDim;
+    if (head < p.q_heads) {
+        warp_head_norm_rope(src, p.q_norm, p.rope_cos ? p.rope_cos + (size_t)pos * kHeadDim : nullptr,
+                            p.rope_sin ? p.rope_sin + (size_t)pos * kHeadDim : nullptr, p.eps, lane, head_s[warp]);
+        __syncwarp();
+        reinterpret_cast<uint2 *>(src)[lane] = reinterpret_cast<const uint2 *>(head_s[warp])[lane];
+        return;
+    }
+    const bool is_key = head < p.q_heads + p.kv_heads;
+    const uint32_t kvh = is_key ? head - p.q_heads : head - p.q_heads - p.kv_heads;
+    const size_t cache_row = ((size_t)p.block_table[pos / kPageTokens] * p.kv_heads + kvh) * kPageTokens + pos % kPageTokens;
+    if (is_key) {
+        warp_head_norm_rope(src, p.k_norm, p.rope_cos ? p.rope_cos + (size_t)pos * kHeadDim : nullptr,
+                            p.rope_sin ? p.rope_sin + (size_t)pos * kHeadDim : nullptr, p.eps, lane, head_s[warp]);
+        __syncwarp();
+        reinterpret_cast<uint2 *>(p.keys + cache_row * kHeadDim)[lane] = reinterpret_cast<const uint2 *>(head_s[warp])[lane];
+    } else {
+        reinterpret_cast<uint2 *>(p.values + cache_row * kHeadDim)[lane] = reinterpret_cast<const uint2 *>(src)[lane];
+    }
+}
+
+// ------------------------------------------------------------------------------------------ causal attention
+// attention_single_pass.rs:11-133 for every row of the chunk: scores q.k in f32 scaled by 1/sqrt(d), online
+// softmax in f32, output rounded to bf16.  A CTA takes one KV head and a block of rows; warp w works on query
+// head (w mod G) of the group and row block (w div G), 16 rows each, so every K / V page (one 64-key tile,
+// 16 KB each, contiguous in the paged cache) is fetched once for the whole group.  Tensor cores through
+// mma.sync.m16n8k16 (bf16): S = Q K^T with the rows as M, then O += P V with P carried as bf16 hi + lo so that
+// the weights keep ~16 bits, as in the decode kernel.
+struct PrefillAttnParams {
+    const uint16_t *qkv;
+    const uint16_t *keys, *values;
+    const int32_t *block_table;
+    uint16_t *out;
+    uint32_t m, first_pos, q_heads, kv_heads, gqa, row_blocks;  // row_blocks = 16-row blocks per CTA
+    float scale;
+};
+
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const PrefillAttnParams p) {
+    extern __shared__ __align__(128) uint8_t pa_smem[];  // [2][K, V][64 rows][272 B]
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t kvh = blockIdx.y;
+    const uint32_t rows_per_cta = 16u * p.row_blocks;
+    const uint32_t row0_cta = blockIdx.x * rows_per_cta;
+    const uint32_t head = kvh * p.gqa + warp % p.gqa;
+    const uint32_t row0 = row0_cta + 16u * (warp / p.gqa);  // this warp's 16 rows
+    const uint32_t heads = p.q_heads + 2u * p.kv_heads;
+    const uint32_t last_row = min(p.m, row0_cta + rows_per_cta) - 1u;
+    const uint32_t ntiles = (p.first_pos + last_row) / kPageTokens + 1u;
+
+    auto issue_tile = [&](uint32_t tile, uint32_t buf) {
+        const size_t page = ((size_t)p.block_table[tile] * p.kv_heads + kvh) * kPageTokens * kHeadDim;
+        const uint8_t *ksrc = reinterpret_cast<const uint8_t *>(p.keys + page);
+        const uint8_t *vsrc = reinterpret_cast<const uint8_t *>(p.values + page);
+        uint8_t *kd = pa_smem + (size_t)(buf * 2u) * kTileBytes, *vd = kd + kTileBytes;
+        for (uint32_t idx = tid; idx < kPageTokens * 16u; idx += WARPS * 32u) {
+            const uint32_t r = idx >> 4, ch = idx & 15u;
+            cp_async16(kd + r * kTileRowBytes + ch * 16u, ksrc + r * 256u + ch * 16u);
+            cp_async16(vd + r * kTileRowBytes + ch * 16u, vsrc + r * 256u + ch * 16u);
+        }
+    };
+    issue_tile(0, 0);
+    cp_async_commit();
+    if (ntiles > 1) issue_tile(1, 1);
+    cp_async_commit();
+
+    // Q as the A operand: rows row0 + g and row0 + g + 8, dims 16 kk + {2t, 2t+1} and + 8
+    uint32_t qa[8][4];
+    const uint32_t ra = row0 + g, rb = row0 + g + 8u;
+    const uint16_t *qa_row = p.qkv + ((size_t)min(ra, p.m - 1u) * heads + head) * kHeadDim;
+    const uint16_t *qb_row = p.qkv + ((size_t)min(rb, p.m - 1u) * heads + head) * kHeadDim;
+#pragma unroll
+    for (int kk = 0; kk < 8; ++kk) {
+        qa[kk][0] = *reinterpret_cast<const uint32_t *>(qa_row + kk * 16 + 2 * t);
+        qa[kk][1] = *reinterpret_cast<const uint32_t *>(qb_row + kk * 16 + 2 * t);
+        qa[kk][2] = *reinterpret_cast<const uint32_t *>(qa_row + kk * 16 + 8 + 2 * t);
+        qa[kk][3] = *reinterpret_cast<const uint32_t *>(qb_row + kk * 16 + 8 + 2 * t);
+    }
+    const uint32_t pos_a = p.first_pos + ra, pos_b = p.first_pos + rb;  // last key each row may see
+
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+    float o[16][4];
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
+    const uint32_t lrow = lane & 7u, lmat = lane >> 3;
+
+    for (uint32_t tile = 0; tile < ntiles; ++tile) {
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t buf = tile & 1u;
+        const uint8_t *kt = pa_smem + (size_t)(buf * 2u) * kTileBytes, *vt = kt + kTileBytes;
+        const uint32_t key0 = tile * kPageTokens;
+        if (key0 <= p.first_pos + min(row0 + 15u, p.m - 1u) && row0 < p.m) {  // some row of the warp sees this tile
+            // ---- S = Q K^T: 8 key blocks of 8 keys; K as the B operand (n = key, k = dim) straight from [key][dim]
+            float s[8][4];
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb) s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+#pragma unroll
+                for (int nb2 = 0; nb2 < 4; ++nb2) {
+                    // matrices: (keys 16 nb2 + 0-7, dims 16 kk + 0-7), (same keys, dims + 8), (keys + 8, dims 0-7), (keys + 8, dims + 8)
+                    uint32_t kb[4];
+                    ldmatrix_x4(kb, kt + (16u * nb2 + (lmat >> 1) * 8u + lrow) * kTileRowBytes + (kk * 16u + (lmat & 1u) * 8u) * 2u);
+                    mma_m16n8k16_bf16(s[2 * nb2], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], kb[0], kb[1]);
+                    mma_m16n8k16_bf16(s[2 * nb2 + 1], qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], kb[2], kb[3]);
+                }
+            }
+            // s[nb][0..1]: row a, keys key0 + 8 nb + 2t, +1;  s[nb][2..3]: row b
+            float tmax[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t key = key0 + 8u * nb + 2u * t + e;
+                    s[nb][e] = key <= pos_a ? s[nb][e] * p.scale : -INFINITY;
+                    s[nb][2 + e] = key <= pos_b ? s[nb][2 + e] * p.scale : -INFINITY;
+                    tmax[0] = fmaxf(tmax[0], s[nb][e]);
+                    tmax[1] = fmaxf(tmax[1], s[nb][2 + e]);
+                }
+            }
+            float factor[2], m_new[2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 1));
+                tmax[j] = fmaxf(tmax[j], __shfl_xor_sync(0xffffffffu, tmax[j], 2));
+                m_new[j] = fmaxf(m_run[j], tmax[j]);
+                // a row past the end of the chunk, or one that sees no key of this tile, keeps -inf
+                factor[j] = (m_run[j] == -INFINITY) ? 0.0f : expf(m_run[j] - m_new[j]);
+            }
+            float tsum[2] = {0.0f, 0.0f};
+            uint32_t ph[8][2], pl[8][2];
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb) {
+                float e4[4];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    e4[e] = m_new[0] == -INFINITY ? 0.0f : expf(s[nb][e] - m_new[0]);
+                    e4[2 + e] = m_new[1] == -INFINITY ? 0.0f : expf(s[nb][2 + e] - m_new[1]);
+                }
+                tsum[0] += e4[0] + e4[1];
+                tsum[1] += e4[2] + e4[3];
+                split_bf16x2(e4[0], e4[1], ph[nb][0], pl[nb][0]);  // row a, keys 8 nb + 2t, +1
+                split_bf16x2(e4[2], e4[3], ph[nb][1], pl[nb][1]);  // row b
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                tsum[j] += __shfl_xor_sync(0xffffffffu, tsum[j], 1);
+                tsum[j] += __shfl_xor_sync(0xffffffffu, tsum[j], 2);
+                l_run[j] = l_run[j] * factor[j] + tsum[j];
+                m_run[j] = m_new[j];
+            }
+#pragma unroll
+            for (int nt = 0; nt < 16; ++nt) {
+                o[nt][0] *= factor[0];
+                o[nt][1] *= factor[0];
+                o[nt][2] *= factor[1];
+                o[nt][3] *= factor[1];
+            }
+            // ---- O += P V: P (the C layout of two adjacent key blocks) is the A operand of a 16-key step;
+            // V as the B operand (n = dim, k = key) is the transpose of the [key][dim] tile: ldmatrix.trans
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {  // 16 keys per step
+                const uint32_t a_h[4] = {ph[2 * ks][0], ph[2 * ks][1], ph[2 * ks + 1][0], ph[2 * ks + 1][1]};
+                const uint32_t a_l[4] = {pl[2 * ks][0], pl[2 * ks][1], pl[2 * ks + 1][0], pl[2 * ks + 1][1]};
+#pragma unroll
+                for (int nt2 = 0; nt2 < 8; ++nt2) {
+                    // matrices: (keys 16 ks + 0-7, dims 16 nt2 + 0-7), (keys + 8, same dims), (keys 0-7, dims + 8), (keys + 8, dims + 8)
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, vt + (16u * ks + (lmat & 1u) * 8u + lrow) * kTileRowBytes + (nt2 * 16u + (lmat >> 1) * 8u) * 2u);
+                    mma_m16n8k16_bf16(o[2 * nt2], a_h[0], a_h[1], a_h[2], a_h[3], vb[0], vb[1]);
+                    mma_m16n8k16_bf16(o[2 * nt2], a_l[0], a_l[1], a_l[2], a_l[3], vb[0], vb[1]);
+                    mma_m16n8k16_bf16(o[2 * nt2 + 1], a_h[0], a_h[1], a_h[2], a_h[3], vb[2], vb[3]);
+                    mma_m16n8k16_bf16(o[2 * nt2 + 1], a_l[0], a_l[1], a_l[2], a_l[3], vb[2], vb[3]);
+                }
+            }
+        }
+        __syncthreads();  // the buffer of this tile is free for tile + 2
+        if (tile + 2u < ntiles) issue_tile(tile + 2u, buf);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
+
+    // o[nt][0..1]: row a, dims 8 nt + 2t, +1;  o[nt][2..3]: row b
+    const float inv_a = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, inv_b = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
+    if (ra < p.m) {
+        uint16_t *dst = p.out + ((size_t)ra * p.q_heads + head) * kHeadDim;
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt)
+            *reinterpret_cast<uint32_t *>(dst + 8 * nt + 2 * t) = f32x2_to_bf16x2(o[nt][0] * inv_a, o[nt][1] * inv_a);
+    }
+    if (rb < p.m) {
+        uint16_t *dst = p.out + ((size_t)rb * p.q_heads + head) * kHeadDim;
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt)
+            *reinterpret_cast<uint32_t *>(dst + 8 * nt + 2 * t) = f32x2_to_bf16x2(o[nt][2] * inv_b, o[nt][3] * inv_b);
+    }
+}
+
+}  // namespace
+
+stark_b200_status embed_rows_launch(const QMatrix *table, const uint32_t *tokens, uint32_t m, uint16_t *h,
+                                    cudaStream_t stream) {
+    if (!table || table->format != kFmtAffine4 || !tokens || !h || m == 0) return STARK_B200_INVALID_ARGUMENT;
+    const dim3 grid(std::max(1u, std::min(16u, table->columns / 256u)), m);
+    embed_rows_kernel<<<grid, 256, 0, stream>>>(table->data, table->rows, table->columns, table->pair_halves, tokens, h);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+stark_b200_status rmsnorm_rows_launch(const uint16_t *h, const float *weight, uint16_t *out, uint32_t m, uint32_t d,
+                                      float eps, cudaStream_t stream) {
+    if (!h || !weight || !out || m == 0 || d % 8u != 0 || d > (uint32_t)kNormThreads * kNormMaxChunks * 8u)
+        return STARK_B200_INVALID_ARGUMENT;
+    rmsnorm_rows_kernel<<<m, kNormThreads, 0, stream>>>(h, weight, out, d, eps);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+stark_b200_status rope_append_rows_launch(const RopeAppendArgs &a, cudaStream_t stream) {
+    if (!a.qkv || !a.kv.keys || !a.kv.values || !a.block_table || a.m == 0) return STARK_B200_INVALID_ARGUMENT;
+    RopeParams p{a.qkv, a.kv.keys, a.kv.values, a.block_table, a.q_norm, a.k_norm, a.rope_cos, a.rope_sin,
+                 a.first_pos, a.q_heads, a.kv_heads, a.eps};
+    const uint32_t heads = a.q_heads + 2u * a.kv_heads;
+    rope_append_rows_kernel<<<dim3((heads + 3u) / 4u, a.m), 128, 0, stream>>>(p);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_t stream) {
+    if (!a.qkv || !a.kv.keys || !a.kv.values || !a.block_table || !a.out || a.m == 0) return STARK_B200_INVALID_ARGUMENT;
+    if (a.kv_heads == 0 || a.q_heads % a.kv_heads != 0) return STARK_B200_UNSUPPORTED;
+    const uint32_t gqa = a.q_heads / a.kv_heads;
+    if (gqa != 1u && gqa != 2u && gqa != 4u && gqa != 8u) return STARK_B200_UNSUPPORTED;
+    PrefillAttnParams p{};
+    p.qkv = a.qkv;
+    p.keys = a.kv.keys;
+    p.values = a.kv.values;
+    p.block_table = a.block_table;
+    p.out = a.out;
+    p.m = a.m;
+    p.first_pos = a.first_pos;
+    p.q_heads = a.q_heads;
+    p.kv_heads = a.kv_heads;
+    p.gqa = gqa;
+    p.scale = a.scale;
+    const uint32_t smem = 4u * kTileBytes;
+    static SmemOptIn once4, once8;
+    if (gqa == 8u) {
+        p.row_blocks = 1;
+        if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<8>, (int)smem, once8)) return s;
+        prefill_attention_kernel<8><<<dim3((a.m + 15u) / 16u, a.kv_heads), 256, smem, stream>>>(p);
+    } else {
+        p.row_blocks = 4u / gqa;
+        const uint32_t rows_per_cta = 16u * p.row_blocks;
+        if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<4>, (int)smem, once4)) return s;
+        prefill_attention_kernel<4><<<dim3((a.m + rows_per_cta - 1u) / rows_per_cta, a.kv_heads), 128, smem, stream>>>(p);
+    }
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+}  // namespace sb

@@ -56,6 +56,7 @@ struct QmvParams {
     const void *x;
     void *y;
     const float *norm_weight;
+    const uint16_t *norm_weight_bf16;
     float eps;
     const void *resid;
     float *partial_max;
@@ -118,7 +119,13 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
     // product) are staged in shared memory while the previous kernel is still running.
     const uint32_t chunks = columns / 8u;
     const bool f32_in = !NORM && p.io_type == STARK_B200_F32;
-    if (NORM) {
+    if (NORM && p.norm_weight_bf16) {
+        // Already rounded at load time: asynchronous copies, so that a CTA which starts late reaches its wait at
+        // once and the weights arrive while the input row is on its way.
+        for (uint32_t c = tid; c < chunks; c += kConsumerThreads)
+            cp_async16(reinterpret_cast<uint4 *>(nws) + c, reinterpret_cast<const uint4 *>(p.norm_weight_bf16) + c);
+        cp_async_commit();
+    } else if (NORM) {
         const float4 *nw = reinterpret_cast<const float4 *>(p.norm_weight);
         for (uint32_t c = tid; c < chunks; c += kConsumerThreads) {
             const float4 n0 = nw[2 * c], n1 = nw[2 * c + 1];
@@ -229,6 +236,7 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
     // thread reads back only the norm weights it staged itself, so no barrier is needed before this.
     float sumsq = 0.0f, vmax = 0.0f;
     if (NORM) {
+        cp_async_wait<0>();  // this thread's own copies of the norm weights (if any)
 #pragma unroll
         for (int r = 0; r < ROUNDS; ++r) {
             const uint32_t c = tid + r * kConsumerThreads;
@@ -803,6 +811,7 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     p.x = a.x;
     p.y = a.y;
     p.norm_weight = a.norm_weight;
+    p.norm_weight_bf16 = a.norm_weight_bf16;
     p.eps = a.eps;
     p.resid = a.resid;
     p.partial_max = a.partial_max;
@@ -818,7 +827,11 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     // the CTA of the next kernel of a programmatic launch chain sits beside it and fills its own ring
     // while this one drains.
     const uint32_t ctas_per_sm = tune.qmv_ctas_per_sm ? tune.qmv_ctas_per_sm : (cw == 16u ? 1u : 2u);
-    const uint32_t budget = (tune.qmv_smem_kb ? tune.qmv_smem_kb : (cw == 16u ? 112u : 64u)) * 1024u;
+    // 56 KB: two CTAs leave room for a three-buffer attention CTA that fetches its cache tiles meanwhile (the qkv
+    // projection before attention, the o projection that starts beside it); 104 KB where nothing of the kind
+    // follows, which buys a deeper ring (measured on the read-out: 61 -> 57 us).
+    const uint32_t own_budget = cw == 16u ? 112u : (a.roomy ? tune.qmv_roomy_kb : 56u);
+    const uint32_t budget = (tune.qmv_smem_kb ? tune.qmv_smem_kb : own_budget) * 1024u;
     uint32_t stages = 8;
     const bool norm = a.prologue == kProRmsNorm;
     while (stages > 2 && smem_layout(stages, p.stage_capacity, m->columns, split, norm, cw).total > budget) --stages;

@@ -92,6 +92,7 @@ struct QmvArgs {
     QmvPrologue prologue;
     QmvEpilogue epilogue;
     const float *norm_weight;  // kProRmsNorm
+    const uint16_t *norm_weight_bf16;  // optional: the same weights already rounded to bf16 (copied, not converted)
     float eps;
     const void *resid;        // kEpiResidual
     float *partial_max;       // kEpiLogits: [grid] per-CTA maxima
@@ -101,6 +102,7 @@ struct QmvArgs {
     bool pdl;                 // launch with programmatic stream serialization
     uint32_t *out_grid;       // optional: number of CTAs launched
     const QmvExchange *exchange;  // optional tensor-parallel hooks
+    bool roomy;                   // no small kernel needs shared memory beside this launch: take a deeper ring
 };
 
 stark_b200_status qmv_launch(const QmvArgs &args, cudaStream_t stream);

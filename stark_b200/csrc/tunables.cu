@@ -16,12 +16,16 @@ struct Entry {
 const Entry kEntries[] = {
     {"qmv_consumer_warps", "STARK_B200_QMV_CW", &Tunables::qmv_consumer_warps, 8u, 8u, 16u},
     {"qmv_smem_kb", "STARK_B200_QMV_SMEM_KB", &Tunables::qmv_smem_kb, 0u, 0u, 200u},
+    {"qmv_roomy_kb", "STARK_B200_QMV_ROOMY_KB", &Tunables::qmv_roomy_kb, 104u, 32u, 110u},
     {"qmv_ctas_per_sm", "STARK_B200_QMV_CTAS", &Tunables::qmv_ctas_per_sm, 0u, 0u, 2u},
     {"qmv_fold", "STARK_B200_QMV_FOLD", &Tunables::qmv_fold, 0u, 0u, 2u},
     {"attn_bufs", "STARK_B200_ATTN_BUFS", &Tunables::attn_bufs, 3u, 2u, 3u},
     {"attn_splits", "STARK_B200_ATTN_SPLITS", &Tunables::attn_splits, 0u, 0u, 32u},
     {"attn_regs", "STARK_B200_ATTN_REGS", &Tunables::attn_regs, 96u, 96u, 128u},
     {"pdl", "STARK_B200_PDL", &Tunables::pdl, 1u, 0u, 1u},
+    {"prefill_batch", "STARK_B200_PREFILL_BATCH", &Tunables::prefill_batch, 1u, 0u, 1u},
+    {"gemm_stop_after", "STARK_B200_GEMM_STOP_AFTER", &Tunables::gemm_stop_after, 0u, 0u, 3u},
+    {"prefill_min_rows", "STARK_B200_PREFILL_MIN_ROWS", &Tunables::prefill_min_rows, 16u, 1u, 1u << 20},
 };
 
 bool valid(const Entry &e, uint32_t v) {

@@ -8,13 +8,17 @@ namespace sb {
 
 struct Tunables {
     uint32_t qmv_consumer_warps;  // STARK_B200_QMV_CW      8 | 16
-    uint32_t qmv_smem_kb;         // STARK_B200_QMV_SMEM_KB 0 = the shape's own budget
+    uint32_t qmv_smem_kb;         // STARK_B200_QMV_SMEM_KB 0 = the shape's own budget (56: two CTAs and a three-buffer attention CTA per SM)
+    uint32_t qmv_roomy_kb;        // STARK_B200_QMV_ROOMY_KB per-CTA budget of launches flagged `roomy`
     uint32_t qmv_ctas_per_sm;     // STARK_B200_QMV_CTAS    0 = the shape's own count
     uint32_t qmv_fold;            // STARK_B200_QMV_FOLD    0 | 1 | 2
     uint32_t attn_bufs;           // STARK_B200_ATTN_BUFS   2 | 3
     uint32_t attn_splits;         // STARK_B200_ATTN_SPLITS 0 = chosen from the head count
     uint32_t attn_regs;           // STARK_B200_ATTN_REGS   96 | 128 registers per attention thread
     uint32_t pdl;                 // STARK_B200_PDL         programmatic dependent launch on / off
+    uint32_t prefill_batch;       // STARK_B200_PREFILL_BATCH    0: prompt rows one at a time, 1: in chunks on the tensor cores
+    uint32_t gemm_stop_after;     // STARK_B200_GEMM_STOP_AFTER  bring-up aid of the tensor-core contraction (0: whole kernel)
+    uint32_t prefill_min_rows;    // STARK_B200_PREFILL_MIN_ROWS fewest cache-only rows worth a batched pass
 };
 
 Tunables &tunables();

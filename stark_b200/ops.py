@@ -117,6 +117,20 @@ class QMatrix:
         check(_lib.load().stark_b200_op_qmv(self._h, _ptr(x), _ptr(y), m, io_type, HOST, None), "op_qmv")
         return y[0] if x.ndim == 1 else y
 
+    def gemm(self, x: np.ndarray, epilogue: int = 0, residual: np.ndarray | None = None) -> np.ndarray:
+        """Y = X W^T for many bf16 rows at once on the tensor cores (``stark_b200_op_qgemm``).
+        epilogue 0: store; 1: ``bf16(bf16(product) + residual)``; 2: SwiGLU over a pair-ordered matrix."""
+        x = np.ascontiguousarray(x, np.uint16)
+        m = x.shape[0]
+        if x.ndim != 2 or x.shape[1] != self.columns:
+            raise ValueError("invalid gemm input shape")
+        cols = self.rows // 2 if epilogue == 2 else self.rows
+        y = np.ascontiguousarray(residual, np.uint16).copy() if epilogue == 1 else np.empty((m, cols), np.uint16)
+        if y.shape != (m, cols):
+            raise ValueError("invalid residual shape")
+        check(_lib.load().stark_b200_op_qgemm(self._h, _ptr(x), _ptr(y), m, epilogue, HOST, None), "op_qgemm")
+        return y
+
     def matvec_device(self, x_ptr: int, y_ptr: int, m: int = 1, io_type: int = BF16, stream: int = 0) -> None:
         check(_lib.load().stark_b200_op_qmv(self._h, x_ptr, y_ptr, m, io_type, DEVICE, stream), "op_qmv")
 

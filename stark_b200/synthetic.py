@@ -40,13 +40,15 @@ def bf16_to_f32(h: np.ndarray) -> np.ndarray:
 
 
 def affine4_matrix(rng: np.random.Generator, rows: int, columns: int, scale_lo: float = 0.005,
-                   scale_hi: float = 0.02, group: int = 64) -> dict:
-    """One 4-bit MLX-affine matrix: nibbles uniform 0..15, scale U[lo, hi] (bf16), bias = -8*scale."""
+                   scale_hi: float = 0.02, group: int = 64, zero_point: float = 8.0) -> dict:
+    """One 4-bit MLX-affine matrix: nibbles uniform 0..15, scale U[lo, hi] (bf16), bias = -zero_point*scale.
+    The default zero point of 8 is the benchmarked distribution; its weights have mean -scale/2, so every
+    output carries a common-mode term.  7.5 gives zero-mean weights (input-dependent arg-max)."""
     words = rows * columns // 8
     codes = rng.integers(0, 1 << 32, size=words, dtype=np.uint32).reshape(rows, columns // 8)
     scales_f = rng.uniform(scale_lo, scale_hi, size=(rows, columns // group)).astype(np.float32)
     scales = f32_to_bf16(scales_f)
-    biases = f32_to_bf16(-8.0 * bf16_to_f32(scales))
+    biases = f32_to_bf16(-zero_point * bf16_to_f32(scales))
     return dict(codes=codes, scales=scales, biases=biases, n=rows, k=columns, bits=4, group=group)
 
 
@@ -62,7 +64,7 @@ def matvec_case(seed: int = 0, rows: int = 4096, columns: int = 4096) -> dict:
     return w
 
 
-def dense_weights(cfg: dict, seed: int = 0) -> dict:
+def dense_weights(cfg: dict, seed: int = 0, zero_point: float = 8.0) -> dict:
     """Random-init weights for a Qwen3-shaped dense decoder.
 
     Scale ranges are the single-matvec range times 17.3/sqrt(K), which keeps every linear layer's
@@ -74,7 +76,7 @@ def dense_weights(cfg: dict, seed: int = 0) -> dict:
 
     def mat(n, k, gain=1.0):
         c = gain * 17.3 / np.sqrt(k)
-        return affine4_matrix(rng, n, k, 0.005 * c, 0.02 * c)
+        return affine4_matrix(rng, n, k, 0.005 * c, 0.02 * c, zero_point=zero_point)
 
     def norm(n):
         return (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)

@@ -11,11 +11,12 @@ Inputs come from `stark_b200.synthetic` (seeded), outputs from `oracle/` only.  
   tiny_greedy     the oracle's own greedy continuation of that prompt, 8 tokens
   q8_0_row / q4_k_row   f32, row 1 of `q8_0_rows` / `q4_k_rows` (default_rng(11), 4 x 512) decoded
   <shape>_logits        bf16 bits, last-row logits of the two-layer `qwen3-8b-layers` / `qwen3-0.6b-layers`
-                        decoders (weights seed 2) after `prompt(cfg, 24, seed=6)`
+                        decoders (weights seed 2, zero point 7.5: zero-mean weights, so that the arg-max depends on the
+                        input) after `prompt(cfg, 24, seed=6)`
   <shape>_teacher       (--full) LAYERS_STEPS seeded random tokens fed after that prompt (`prompt(cfg, 100, seed=7)`)
   <shape>_top1          (--full) the oracle's pick (first index of the maximum) after each of those tokens
-  <shape>_top2          (--full) the oracle's two largest logits at each of those steps as bf16 bits, so that a
-                        test can tell a different pick at a tie from a different pick
+  <shape>_lead_ids / _lead_bits   (--full) the oracle's eight largest logits at each of those steps (token ids and
+                        bf16 bits), so that a test can tell a different pick at a near-tie from a different pick
 """
 import sys
 from pathlib import Path
@@ -30,12 +31,13 @@ from stark_b200 import synthetic as S  # noqa: E402
 
 
 LAYERS_STEPS = 100
+LEADERS = 8  # largest logits kept per step
 LAYERS_SHAPES = {"q8b": "qwen3-8b-layers", "q06b": "qwen3-0.6b-layers"}
 
 
 def layers_case(shape: str, steps: int) -> dict:
     cfg = S.CONFIGS[LAYERS_SHAPES[shape]]
-    weights = S.dense_weights(cfg, seed=2)
+    weights = S.dense_weights(cfg, seed=2, zero_point=7.5)
     prompt = S.prompt(cfg, 24, seed=6)
     orc = O.DenseOracle(cfg, weights, capacity=24 + steps + 1)
     for t in prompt[:-1]:
@@ -46,15 +48,18 @@ def layers_case(shape: str, steps: int) -> dict:
         # A random-init decoder decoded greedily falls into repeating one token, which would make agreement
         # trivial; the continuation is therefore a seeded random token sequence fed to both sides.
         teacher = S.prompt(cfg, steps, seed=7)
-        top1, top2 = [], []
+        top1, lead_ids, lead_bits = [], [], []
         for t in teacher:
             logits = np.asarray(orc.step(int(t)), np.uint16)
-            order = np.sort(O.bf16_to_f32(logits))[-2:]
-            top2.append(S.f32_to_bf16(order[::-1].copy()))
+            values = O.bf16_to_f32(logits)
+            lead = np.argsort(-values, kind="stable")[:LEADERS]      # equal values: lower index first
+            lead_ids.append(lead.astype(np.uint32))
+            lead_bits.append(logits[lead])
             top1.append(O.argmax_bf16(logits))
         out[f"{shape}_teacher"] = np.asarray(teacher, np.uint32)
         out[f"{shape}_top1"] = np.asarray(top1, np.uint32)
-        out[f"{shape}_top2"] = np.asarray(top2, np.uint16)
+        out[f"{shape}_lead_ids"] = np.asarray(lead_ids, np.uint32)
+        out[f"{shape}_lead_bits"] = np.asarray(lead_bits, np.uint16)
     return out
 
 

@@ -165,21 +165,30 @@ def test_named_shape_layers_against_stored_oracle_outputs(shape, name):
     from stark_b200.ops import take_device_error
     stored = dict(np.load(Path(__file__).parent / "golden" / "oracle_outputs.npz"))
     cfg = S.CONFIGS[name]
-    model = DenseModel.load(cfg, S.dense_weights(cfg, seed=2), context_tokens=256)
+    model = DenseModel.load(cfg, S.dense_weights(cfg, seed=2, zero_point=7.5), context_tokens=256)
     model.prefill(S.prompt(cfg, 24, seed=6))
     assert_logits_accepted(stored[f"{shape}_logits"], model.logits_bf16())
     teacher, want = stored[f"{shape}_teacher"], stored[f"{shape}_top1"]
-    top2 = O.bf16_to_f32(stored[f"{shape}_top2"])
+    lead_ids, lead = stored[f"{shape}_lead_ids"], O.bf16_to_f32(stored[f"{shape}_lead_bits"])
     assert len(teacher) >= 100
     picks = []
     for t in teacher:
         model.step_async(int(t))
         picks.append(model.argmax())
     assert take_device_error() == 0
-    agree = np.asarray(picks, np.uint32) == want
-    # a step whose two largest oracle logits are equal as bf16 has no unique top-1 to agree with
-    tied = top2[:, 0] == top2[:, 1]
-    print(f"{name}: top-1 agreement {agree.mean():.4f} over {len(teacher)} steps, {int(tied.sum())} exact ties, "
-          f"{int((~agree & ~tied).sum())} disagreements away from a tie")
-    assert (agree | tied).mean() >= 0.99, (agree.mean(), np.nonzero(~agree)[0])
+    picks = np.asarray(picks, np.uint32)
+    agree = picks == want
+    # A pick that differs from the oracle's is still a tie at the resolution of the logits when the oracle's own
+    # value for it is within one bf16 step of the oracle's maximum: both kernels round f32 sums that differ in
+    # the last bits, and either neighbour is a correct bf16 result.
+    ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(lead[:, 0]), 1e-30))) - 7)
+    near = np.zeros(len(picks), bool)
+    for i, p in enumerate(picks):
+        hit = np.nonzero(lead_ids[i] == p)[0]
+        near[i] = hit.size > 0 and lead[i, 0] - lead[i, hit[0]] <= ulp[i]
+    print(f"{name}: strict top-1 agreement {agree.mean():.4f} over {len(teacher)} steps; "
+          f"{int((~agree & near).sum())} picks within one bf16 step of the oracle's maximum; "
+          f"{int((~agree & ~near).sum())} real disagreements")
+    assert (agree | near).mean() >= 0.99, (agree.mean(), np.nonzero(~(agree | near))[0])
+    assert agree.mean() >= 0.90
     model.close()

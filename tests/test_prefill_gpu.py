@@ -1,0 +1,144 @@
+"""GPU parity of the batched prompt path: the tensor-core contraction over a 4-bit matrix against the CPU
+oracle's matmul (crates/stark-engine/src/backends/cpu/kernel/matmul/kernel.rs:168-285, many input rows), then
+the whole chunked prefill against row-by-row steps."""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from stark_b200 import synthetic as S
+
+pytestmark = pytest.mark.gpu
+REL_TOL = 1e-2  # per-operator bar: bf16 outputs, f32 accumulation
+
+
+def _rel(got_bits, want_bits):
+    g, w = O.bf16_to_f32(got_bits).astype(np.float64), O.bf16_to_f32(want_bits).astype(np.float64)
+    return np.abs(g - w) / np.maximum(np.abs(w), np.abs(w).mean() + 1e-30)
+
+
+def _oracle_rows(w, x, rows, columns):
+    return np.stack([O.affine_matvec_bf16(w["codes"], w["scales"], w["biases"], xr, rows, columns)[0] for xr in x])
+
+
+@pytest.mark.parametrize("m,rows,columns", [(1, 128, 64), (5, 256, 256), (128, 128, 1024), (300, 384, 512),
+                                            (257, 6144, 4096), (64, 4096, 12288)])
+def test_gemm_matches_oracle_rows(m, rows, columns):
+    """Row counts on and off the 128 / 256 row tiles, K from one quantization group to the widest layer."""
+    from stark_b200 import ops
+    rng = np.random.default_rng(m + rows)
+    w = S.affine4_matrix(rng, rows, columns, 0.005 * 17.3 / np.sqrt(columns), 0.02 * 17.3 / np.sqrt(columns))
+    x = S.bf16_normal(rng, m * columns).reshape(m, columns)
+    q = ops.QMatrix.from_affine(w["codes"], w["scales"], w["biases"], rows, columns)
+    got = q.gemm(x)
+    assert ops.take_device_error() == 0
+    check = np.unique(np.concatenate([[0, m - 1], rng.integers(0, m, size=min(m, 6))]))
+    want = _oracle_rows(w, x[check], rows, columns)
+    assert _rel(got[check], want).max() < REL_TOL
+    # the same rows through the one-row kernel: both round the same f32 sums, up to the bf16 rounding of the
+    # dequantized operand that the tiled contraction (like the reference's own) makes
+    one = np.stack([q.matvec(x[i]) for i in check[:3]])
+    assert _rel(got[check[:3]], one).max() < REL_TOL
+
+
+def test_gemm_residual_and_swiglu_epilogues():
+    from stark_b200 import ops
+    rng = np.random.default_rng(17)
+    m, hidden, inter = 70, 512, 768
+    wd = S.affine4_matrix(rng, hidden, inter, 0.005 * 0.6, 0.02 * 0.6)
+    x = S.bf16_normal(rng, m * inter).reshape(m, inter)
+    resid = S.bf16_normal(rng, m * hidden, 2.0).reshape(m, hidden)
+    q = ops.QMatrix.from_affine(wd["codes"], wd["scales"], wd["biases"], hidden, inter)
+    got = q.gemm(x, epilogue=1, residual=resid)
+    prod = _oracle_rows(wd, x, hidden, inter)
+    want = O.f32_to_bf16(O.bf16_to_f32(prod) + O.bf16_to_f32(resid))
+    assert _rel(got, want).max() < REL_TOL
+    # [up; gate] with the SwiGLU folded into the epilogue
+    wu = S.affine4_matrix(rng, 2 * inter, hidden, 0.005 * 0.7, 0.02 * 0.7)
+    xh = S.bf16_normal(rng, m * hidden).reshape(m, hidden)
+    qu = ops.QMatrix.from_affine(wu["codes"], wu["scales"], wu["biases"], 2 * inter, hidden, pair_halves=True)
+    got = qu.gemm(xh, epilogue=2)
+    fused = _oracle_rows(wu, xh, 2 * inter, hidden)
+    want = np.stack([O.swiglu_bf16(f, inter) for f in fused])
+    assert got.shape == (m, inter)
+    assert _rel(got, want).max() < 2 * REL_TOL
+
+
+def test_gemm_properties_at_full_size():
+    """Size-independent checks at the widest layer shape: zero input, exact power-of-two scaling of the input,
+    and bitwise repeatability."""
+    from stark_b200 import ops
+    rng = np.random.default_rng(23)
+    rows, columns, m = 4096, 12288, 512
+    w = S.affine4_matrix(rng, rows, columns, 0.005 * 0.15, 0.02 * 0.15)
+    q = ops.QMatrix.from_affine(w["codes"], w["scales"], w["biases"], rows, columns)
+    x = S.bf16_normal(rng, m * columns).reshape(m, columns)
+    y = q.gemm(x)
+    assert np.array_equal(y, q.gemm(x))
+    assert not q.gemm(np.zeros_like(x)).any()
+    x4 = O.f32_to_bf16(O.bf16_to_f32(x) * 4.0)
+    y4 = q.gemm(x4)
+    assert np.array_equal(O.bf16_to_f32(y4), O.bf16_to_f32(y) * 4.0)
+    assert ops.take_device_error() == 0
+
+
+def _set(name, value):
+    from stark_b200 import _lib
+    _lib.check(_lib.load().stark_b200_set_tunable(name.encode(), int(value)), f"set_tunable {name}")
+
+
+@pytest.mark.parametrize("name,prompt_len", [("tiny", 200), ("small", 96), ("small", 1500), ("qwen3-0.6b-layers", 300),
+                                             ("qwen3-8b-layers", 1100)])
+def test_chunked_prefill_equals_row_by_row(name, prompt_len):
+    """A prompt ingested in chunks on the tensor cores must leave the model where row-by-row steps leave it: the
+    last row's logits inside the logits acceptance, the same greedy continuation while no near-tie separates the
+    two, and a cache that later tokens can extend (positions past one chunk of 1024 rows included)."""
+    from stark_b200.engine import DenseModel
+    from stark_b200.ops import take_device_error
+    from tests.test_model_gpu import assert_logits_accepted
+    cfg = S.CONFIGS[name]
+    w = S.dense_weights(cfg, seed=4, zero_point=7.5)
+    model = DenseModel.load(cfg, w, context_tokens=prompt_len + 64)
+    prompt = S.prompt(cfg, prompt_len, seed=11)
+    try:
+        _set("prefill_batch", 0)
+        model.prefill(prompt)
+        rows_logits = model.logits_bf16().copy()
+        rows_next = model.generate_greedy(12)
+        model.reset()
+        _set("prefill_batch", 1)
+        launches = model.info().launches_issued
+        model.prefill(prompt)
+        issued = model.info().launches_issued - launches
+        chunks = -(-(prompt_len - 1) // 1024)
+        assert issued == chunks * (1 + 8 * cfg["layers"]) + model.info().launches_per_step   # the batched path ran
+        assert take_device_error() == 0
+        assert_logits_accepted(rows_logits, model.logits_bf16())
+        got_next = model.generate_greedy(12)
+        assert int(got_next[0]) == int(rows_next[0])
+        assert (got_next[:6] == rows_next[:6]).sum() >= 5, (got_next, rows_next)
+        assert model.position == prompt_len + 12
+    finally:
+        _set("prefill_batch", 1)
+        model.close()
+
+
+def test_chunked_prefill_against_the_oracle():
+    """The chunked path against the CPU oracle directly (not only against the one-row kernels)."""
+    from stark_b200.engine import DenseModel
+    from tests.test_model_gpu import assert_logits_accepted
+    cfg = S.CONFIGS["small"]
+    w = S.dense_weights(cfg, seed=1, zero_point=7.5)
+    model = DenseModel.load(cfg, w, context_tokens=256)
+    oracle = O.DenseOracle(cfg, w, capacity=256)
+    prompt = S.prompt(cfg, 150, seed=4)
+    model.prefill(prompt)
+    for t in prompt[:-1]:
+        oracle.ingest(int(t))
+    assert_logits_accepted(oracle.step(int(prompt[-1])), model.logits_bf16())
+    agree, steps = 0, 60
+    teacher = S.prompt(cfg, steps, seed=12)
+    for t in teacher:
+        model.step_async(int(t))
+        agree += int(model.argmax() == O.argmax_bf16(oracle.step(int(t))))
+    assert agree / steps >= 0.99, agree
+    model.close()
