@@ -35,6 +35,8 @@ WORKLOADS = {
     "moe-small": dict(cfg="moe-small", prompt=64, context=256, moe=True),
     # a single quantized matvec (BASELINE config 1 by default): micro-benchmark / profiling target
     "matvec": dict(cfg=None, prompt=0, context=0),
+    # the prompt-chunk contraction alone (tensor-core GEMM over a 4-bit matrix): profiling target
+    "gemm": dict(cfg=None, prompt=0, context=0),
 }
 BYTES_PER_WEIGHT = 0.5625  # 4-bit codes + bf16 scale and bias per 64 columns
 DRAM_TRAFFIC_RATIO = 1.011  # measured dram bytes / algorithmic bytes of the 4-bit matvec (ncu, 151936x4096)
@@ -61,6 +63,23 @@ def weight_count(cfg: dict) -> tuple[int, int]:
     D, hd, I, V = cfg["hidden"], cfg["head_dim"], cfg["inter"], cfg["vocab"]
     per_layer = (cfg["q_heads"] + 2 * cfg["kv_heads"]) * hd * D + D * cfg["q_heads"] * hd + 2 * I * D + D * I
     return cfg["layers"] * per_layer + V * D, V * D
+
+
+def prefill_flops(cfg: dict, prompt_rows: int) -> float:
+    """Multiply-add work of ingesting a prompt: 2 M N K per layer matrix over the cache-only rows, plus attention
+    4 * rows * context * q_heads * head_dim with the causal mean context (the last row is a decode step)."""
+    rows = prompt_rows - 1
+    per_layer_weights = (weight_count(cfg)[0] - weight_count(cfg)[1]) / cfg["layers"]
+    gemm = 2.0 * rows * per_layer_weights * cfg["layers"]
+    attention = 4.0 * rows * (rows / 2.0) * cfg["q_heads"] * cfg["head_dim"] * cfg["layers"]
+    return gemm + attention
+
+
+def tensor_peak() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        return float(json.loads(p.read_text())["bf16_tflops_sustained"]), "measured sustained"
+    return 1400.0, "fallback"
 
 
 def step_bytes(cfg: dict, context_rows: float) -> float:
@@ -197,6 +216,66 @@ def run_matvec(args) -> None:
         "roofline": {"bound": "hbm", "achieved": per / us / 1e3, "peak": peak, "unit": "GB/s",
                      "frac": per / us / 1e3 / peak,
                      "traffic": DRAM_TRAFFIC_RATIO * per if args.format == "affine4" else None, "peak_kind": kind},
+    }))
+
+
+def run_gemm(args) -> None:
+    """One Y[M, N] = X[M, K] W^T per step (the prompt-chunk contraction) over a pool of matrices larger than L2."""
+    import torch
+
+    from stark_b200 import _lib
+    from stark_b200.ops import QMatrix, take_device_error
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    rows, cols, m = args.rows, args.columns, args.m
+    rng = np.random.default_rng(args.seed)
+    c = 17.3 / np.sqrt(cols)
+    per = rows * cols * BYTES_PER_WEIGHT
+    pool_n = min(24, max(2, int(300e6 // per) + 1))
+    pool = []
+    for _ in range(pool_n):
+        w = S.affine4_matrix(rng, rows, cols, 0.005 * c, 0.02 * c)
+        pool.append(QMatrix.from_affine(w["codes"], w["scales"], w["biases"], rows, cols))
+    x = torch.from_numpy(S.bf16_normal(rng, m * cols).view(np.int16)).cuda()
+    y = torch.empty(m * rows, dtype=torch.int16, device="cuda")
+    lib = _lib.load()
+    stream = torch.cuda.Stream()
+    st = stream.cuda_stream
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def one(q):
+        _lib.check(lib.stark_b200_op_qgemm(q._h, x.data_ptr(), y.data_ptr(), m, 0, _lib.DEVICE, st), "op_qgemm")
+    with torch.cuda.stream(stream):
+        for i in range(warmup):
+            one(pool[i % pool_n])
+        stream.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            one(pool[i % pool_n])
+        e1.record(stream)
+        stream.synchronize()
+    assert take_device_error() == 0
+    us = e0.elapsed_time(e1) * 1e3 / steps
+    flops = 2.0 * m * rows * cols
+    tpeak, tkind = tensor_peak()
+    tf = flops / us / 1e6
+    # end to end: host rows in and out through the operator call
+    xh = S.bf16_normal(rng, m * cols).reshape(m, cols)
+    t0 = time.perf_counter()
+    for i in range(min(steps, 8)):
+        pool[i % pool_n].gemm(xh)
+    e2e = (time.perf_counter() - t0) / min(steps, 8)
+    print(json.dumps({
+        "metric": "4-bit affine GEMM TFLOP/s", "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": us / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"gemm {m} rows x [{rows} x {cols}] 4-bit affine g64, bf16 in/out",
+                   "l2": f"pool of {pool_n} matrices ({pool_n * per / 1e6:.0f} MB) cycled, larger than L2"},
+        "e2e": {"value": flops / e2e / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * m * cols,
+                "d2h_bytes_per_step": 2 * m * rows},
+        "gpu_launches": steps,
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": tpeak, "unit": "TFLOP/s", "frac": tf / tpeak,
+                     "traffic": None, "peak_kind": tkind},
     }))
 
 
@@ -352,6 +431,7 @@ def main() -> None:
                          "run N independent streams (weak scaling)")
     ap.add_argument("--rows", type=int, default=4096, help="matvec workload only")
     ap.add_argument("--columns", type=int, default=4096, help="matvec workload only")
+    ap.add_argument("--m", type=int, default=1024, help="gemm workload only: rows of activations")
     ap.add_argument("--format", default="affine4", choices=["affine4", "affine8", "q8_0", "q4_k"],
                     help="matvec workload only")
     args = ap.parse_args()
@@ -361,6 +441,9 @@ def main() -> None:
         return
     if args.workload == "matvec":
         run_matvec(args)
+        return
+    if args.workload == "gemm":
+        run_gemm(args)
         return
     cfg = S.CONFIGS[wl["cfg"]]
     if args.impl == "reference":
@@ -408,10 +491,16 @@ def main() -> None:
         torch.cuda.synchronize()
 
     # ---- device-timed decode: tokens chained on the device, inputs resident in HBM ------------
-    t_prefill = time.perf_counter()
-    model.prefill(prompt)
+    model.prefill(prompt)   # untimed first pass: allocates the chunk buffers, touches every weight
     model.drain()
-    prefill_s = time.perf_counter() - t_prefill
+    model.reset()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    p0.record(stream)
+    model.prefill(prompt)
+    p1.record(stream)
+    model.drain()
+    prefill_ms = p0.elapsed_time(p1)
     model.generate_greedy(warmup)
     barrier()
     events = [torch.cuda.Event(enable_timing=True) for _ in range(repeats + 1)]
@@ -491,7 +580,7 @@ def main() -> None:
                                      "ms_per_step_min": min(regions) / steps, "ms_per_step_max": max(regions) / steps,
                                      "e2e_tok_s_min": streams * e2e_steps / max(e2e_regions),
                                      "e2e_tok_s_max": streams * e2e_steps / min(e2e_regions)},
-                   "prompt_ingest_ms": 1e3 * prefill_s},
+                   "prompt_ingest_ms": prefill_ms},
         "e2e": {"value": e2e_value, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": 16,
                 "steps": e2e_steps},
         "gpu_launches": int(repeats * steps * info.launches_per_step),
@@ -505,6 +594,15 @@ def main() -> None:
                      "note": "whole decode step (all kernels of the token) over the step's algorithmic bytes"
                              + (", per GPU" if world > 1 else "")},
     }
+    if tp is None:
+        # Prompt ingest (chunks of 1024 rows through the tcgen05 contraction): a dense contraction, so it is set
+        # against the tensor-pipe peak, not the HBM one.
+        tpeak, tkind = tensor_peak()
+        tflops = prefill_flops(cfg, wl["prompt"]) / (prefill_ms * 1e-3) / 1e12
+        line["prefill"] = {"prefill_tok_s": wl["prompt"] / (prefill_ms * 1e-3), "ms": prefill_ms,
+                           "prompt_tokens": wl["prompt"], "achieved_tflops": tflops, "peak_tflops": tpeak,
+                           "frac": tflops / tpeak, "peak_kind": tkind, "bound": "tensor",
+                           "note": "device time (CUDA events) of ingesting the prompt, last row included"}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import oracle as O
         n = 2 if cfg["layers"] >= 28 else 8

@@ -341,11 +341,18 @@ stark_b200_status stark_b200_model_set_vector(stark_b200_model *model, uint32_t 
  * over NVLink peer memory fused with the bf16 rounding and the residual add; the greedy token is chosen
  * across vocabulary shards on the device.  readout_f32 / readout_bf16 return this rank's slice
  * (config.vocab entries, starting at vocab_offset); readout_logprobs_f32 is UNSUPPORTED.  A peer that
- * does not arrive within 4 s sets the device error word: the next drain returns DEVICE_FAILURE and
- * fences the handle.  cancel is not collective and must not be used between ranks' calls. */
+ * does not arrive within the wait limit (4 s unless tp_set_wait changed it, between tp_init and finalize)
+ * sets the device error word: the rank's position and exchange tickets stay at the failed exchange, the
+ * next drain returns DEVICE_FAILURE and fences the handle (reset then answers RELOAD_REQUIRED; destroy
+ * works).  cancel is not collective and must not be used between ranks' calls.
+ *   tp_connect_unanswered  instead of tp_connect: every peer is a zeroed local buffer nobody writes, so the
+ *               rank's waits run out.  It exists to exercise the bounded wait on one GPU (the reference
+ *               fences a backend after a device fault the same way, glm_exl3.rs:243-256). */
 stark_b200_status stark_b200_model_tp_init(stark_b200_model *model, uint32_t rank, uint32_t ranks,
                                            uint32_t vocab_offset, uint32_t vocab_total, uint8_t handle_out[64]);
 stark_b200_status stark_b200_model_tp_connect(stark_b200_model *model, const uint8_t *handles, size_t handle_bytes);
+stark_b200_status stark_b200_model_tp_set_wait(stark_b200_model *model, uint64_t nanoseconds);
+stark_b200_status stark_b200_model_tp_connect_unanswered(stark_b200_model *model);
 stark_b200_status stark_b200_model_finalize(stark_b200_model *model);
 stark_b200_status stark_b200_destroy(stark_b200_model **model);
 stark_b200_status stark_b200_reset(stark_b200_model *model);

@@ -137,6 +137,8 @@ def load() -> C.CDLL:
         "stark_b200_model_set_vector": (u32, [vp, u32, u32, vp, u32]),
         "stark_b200_model_tp_init": (u32, [vp, u32, u32, u32, u32, vp]),
         "stark_b200_model_tp_connect": (u32, [vp, vp, sz]),
+        "stark_b200_model_tp_set_wait": (u32, [vp, u64]),
+        "stark_b200_model_tp_connect_unanswered": (u32, [vp]),
         "stark_b200_model_finalize": (u32, [vp]),
         "stark_b200_destroy": (u32, [C.POINTER(vp)]),
         "stark_b200_reset": (u32, [vp]),

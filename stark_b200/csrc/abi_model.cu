@@ -308,6 +308,16 @@ stark_b200_status stark_b200_model_tp_connect(stark_b200_model *model, const uin
     return model_tp_connect(M(model), handles);
 }
 
+stark_b200_status stark_b200_model_tp_set_wait(stark_b200_model *model, uint64_t nanoseconds) {
+    if (!model) return STARK_B200_INVALID_ARGUMENT;
+    return model_tp_set_wait(M(model), nanoseconds);
+}
+
+stark_b200_status stark_b200_model_tp_connect_unanswered(stark_b200_model *model) {
+    if (!model) return STARK_B200_INVALID_ARGUMENT;
+    return model_tp_connect_unanswered(M(model));
+}
+
 stark_b200_status stark_b200_model_finalize(stark_b200_model *model) {
     if (!model) return STARK_B200_INVALID_ARGUMENT;
     return model_finalize(M(model));

@@ -91,7 +91,10 @@ Model::~Model() {
     cudaFree(partial_index);
     if (tp_connected)
         for (uint32_t r = 0; r < tp.size; ++r)
-            if (r != tp.rank && tp.base[r]) cudaIpcCloseMemHandle(tp.base[r]);
+            if (r != tp.rank && tp.base[r]) {
+                if (tp_stand_ins) cudaFree(tp.base[r]);
+                else cudaIpcCloseMemHandle(tp.base[r]);
+            }
     cudaFree(chunk_tokens);
     cudaFree(chunk_h);
     cudaFree(chunk_x);
@@ -612,6 +615,7 @@ stark_b200_status model_tp_init(Model *m, uint32_t rank, uint32_t size, uint32_t
     m->tp.rank = rank;
     m->tp.size = size;
     m->tp.hidden = m->cfg.hidden;
+    m->tp.wait_ns = kDefaultPeerWaitNs;
     m->tp.base[rank] = m->tp_local;
     m->tp_vocab_offset = vocab_offset;
     m->tp_vocab_total = vocab_total;
@@ -629,6 +633,34 @@ stark_b200_status model_tp_connect(Model *m, const uint8_t *handles) {
         m->tp.base[r] = static_cast<uint8_t *>(p);
     }
     m->tp_connected = true;
+    return STARK_B200_OK;
+}
+
+// Between init and finalize: how long this rank's kernels wait for a peer (the value is part of the recorded
+// launch sequences).
+stark_b200_status model_tp_set_wait(Model *m, uint64_t nanoseconds) {
+    if (m->finalized || !m->tp_local) return STARK_B200_INVALID_STATE;
+    if (nanoseconds < 1000ull || nanoseconds > 600000000000ull) return STARK_B200_INVALID_ARGUMENT;
+    m->tp.wait_ns = nanoseconds;
+    return STARK_B200_OK;
+}
+
+// Connects the rank to peers that never answer: every other rank's region is a zeroed local allocation that
+// nobody writes.  The rank's own pushes land there harmlessly; its waits for the peers' packets run out after
+// the wait limit and surface as a device failure.  This is how the bounded wait is exercised on one GPU without
+// hanging or faulting anything.
+stark_b200_status model_tp_connect_unanswered(Model *m) {
+    if (m->finalized || !m->tp_local || m->tp_connected) return STARK_B200_INVALID_STATE;
+    const size_t bytes = tp_region_bytes(m->cfg.hidden);
+    for (uint32_t r = 0; r < m->tp.size; ++r) {
+        if (r == m->tp.rank) continue;
+        uint8_t *p = nullptr;
+        SB_CUDA(cudaMalloc(&p, bytes));
+        SB_CUDA(cudaMemset(p, 0, bytes));
+        m->tp.base[r] = p;
+    }
+    m->tp_connected = true;
+    m->tp_stand_ins = true;
     return STARK_B200_OK;
 }
 

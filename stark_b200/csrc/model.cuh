@@ -55,7 +55,7 @@ struct Model {
     uint8_t *tp_local = nullptr;   // this rank's exchange region
     uint32_t *tp_seq = nullptr;    // [0] tokens finished: the base of the exchange tickets
     uint32_t tp_vocab_offset = 0, tp_vocab_total = 0;
-    bool tp_connected = false;
+    bool tp_connected = false, tp_stand_ins = false;
     // batched prompt ingest (prefill_model.cu): rows of one chunk, allocated at first use
     uint32_t prefill_state = 0;  // 0 not examined, 1 the batched path serves this model, 2 it does not
     uint32_t *chunk_tokens = nullptr;
@@ -79,6 +79,8 @@ stark_b200_status model_set_vector(Model *m, uint32_t layer, uint32_t which, con
 stark_b200_status model_tp_init(Model *m, uint32_t rank, uint32_t size, uint32_t vocab_offset, uint32_t vocab_total,
                                 uint8_t *handle_out);
 stark_b200_status model_tp_connect(Model *m, const uint8_t *handles);
+stark_b200_status model_tp_set_wait(Model *m, uint64_t nanoseconds);
+stark_b200_status model_tp_connect_unanswered(Model *m);
 stark_b200_status model_finalize(Model *m);
 stark_b200_status model_reset(Model *m);
 stark_b200_status model_recapture(Model *m);

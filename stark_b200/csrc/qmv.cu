@@ -205,7 +205,7 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
                         if (all) break;
                         if (++spins > 8u) {
                             __nanosleep(64);
-                            if (global_ns() - t0 > 4000000000ull) {  // a rank is missing: give up after 4 s
+                            if (global_ns() - t0 > p.ex.wait_ns) {  // a rank is missing: give up
                                 atomicOr(p.error_word, kErrPeerTimeout);
                                 break;
                             }

@@ -81,6 +81,7 @@ struct QmvExchange {
     uint16_t *h_out;                              // consumer: [columns] bf16, written by block 0
     const uint32_t *tokens;
     uint32_t ticket_mul, ticket_add;
+    unsigned long long wait_ns;  // consumer: how long to poll for a rank's packets
 };
 
 struct QmvArgs {

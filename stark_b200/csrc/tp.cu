@@ -7,8 +7,6 @@ namespace sb {
 
 namespace {
 
-constexpr unsigned long long kPeerWaitNs = 4000000000ull;  // give up on a peer after 4 s
-
 __device__ inline void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -37,7 +35,7 @@ __device__ inline bool wait_flags(const TpRegion &g, uint32_t set, uint32_t tick
         while (ld_acquire_sys(mine) != ticket) {
             if (++spins > 32u) {
                 __nanosleep(100);
-                if (global_ns() - t0 > kPeerWaitNs) {
+                if (global_ns() - t0 > g.wait_ns) {
                     atomicOr(error_word, kErrPeerTimeout);
                     ok = false;
                     break;
@@ -67,7 +65,7 @@ __global__ void __launch_bounds__(256) tp_ingest_advance_kernel(TpRegion g, uint
                 if ((uint32_t)(q >> 32) == ticket) break;
                 if (++spins > 8u) {
                     __nanosleep(100);
-                    if (global_ns() - t0 > kPeerWaitNs) {
+                    if (global_ns() - t0 > g.wait_ns) {
                         atomicOr(error_word, kErrPeerTimeout);
                         ok = false;
                         break;
@@ -76,8 +74,9 @@ __global__ void __launch_bounds__(256) tp_ingest_advance_kernel(TpRegion g, uint
             }
         }
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
+    // A rank whose wait ran out stays where it is: position, cursor and ticket base do not move on rows that
+    // were never complete, so the failed exchange remains the one every rank is at.
+    if (__syncthreads_and(ok ? 1 : 0) && threadIdx.x == 0) {
         state->position += 1u;
         state->token = pending[state->cursor];
         state->cursor += 1u;
@@ -114,7 +113,7 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_residual_kernel(TpRe
                 if ((uint32_t)(q0 >> 32) == ticket && (uint32_t)(q1 >> 32) == ticket) break;
                 if (++spins > 8u) {
                     __nanosleep(64);
-                    if (global_ns() - t0 > kPeerWaitNs) {
+                    if (global_ns() - t0 > g.wait_ns) {
                         atomicOr(error_word, kErrPeerTimeout);
                         ok = false;
                         break;
@@ -185,10 +184,11 @@ __global__ void __launch_bounds__(256) tp_argmax_finalize_kernel(TpRegion g, uin
         st_release_sys(tp_flags(g.base[threadIdx.x], set) + g.rank, ticket);
     }
     const bool ok = wait_flags(g, set, ticket, error_word);
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0 && !ok) state->next_token = 0xffffffffu;  // no token; position and ticket base stay
+    if (threadIdx.x == 0 && ok) {
         float top = -INFINITY;
         uint32_t ti = 0xffffffffu;
-        if (ok) {
+        {
             for (uint32_t r = 0; r < g.size; ++r) {
                 const uint2 c = ld_sys_u32x2(tp_gather(g.base[g.rank]) + 2u * r);
                 const float v = __uint_as_float(c.x);
@@ -241,6 +241,7 @@ QmvExchange tp_consumer_hooks(const TpRegion &g, uint32_t index, uint32_t per_to
     x.ranks = g.size;
     x.recv = tp_recv(g.base[g.rank], index & 1u, 0u, g.hidden);
     x.h_out = h_out;
+    x.wait_ns = g.wait_ns;
     x.tokens = tokens;
     x.ticket_mul = per_token;
     x.ticket_add = index + 1u;

@@ -25,7 +25,9 @@ constexpr uint32_t kTpFlagSets = 1;  // the greedy-token gather
 struct TpRegion {
     uint8_t *base[kMaxTpRanks];  // this rank's view of every rank's region (base[rank] is local)
     uint32_t rank, size, hidden;
+    unsigned long long wait_ns;  // how long a kernel waits for a peer before it gives up (kDefaultPeerWaitNs)
 };
+constexpr unsigned long long kDefaultPeerWaitNs = 4000000000ull;  // 4 s
 __host__ __device__ inline size_t tp_region_bytes(uint32_t hidden) {
     return 8192u + 2u * (size_t)kMaxTpRanks * hidden * 8u;
 }

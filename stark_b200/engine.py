@@ -82,8 +82,11 @@ class TensorParallel:
     """Rank layout of a tensor-parallel group plus the one host-side collective the engine needs:
     ``all_gather(bytes) -> [bytes per rank]`` (for example ``torch.distributed.all_gather_object``)."""
 
-    def __init__(self, rank: int, ranks: int, all_gather):
+    def __init__(self, rank: int, ranks: int, all_gather, wait_ns: int | None = None, unanswered: bool = False):
         self.rank, self.ranks, self.all_gather = int(rank), int(ranks), all_gather
+        # wait_ns: how long a kernel of this rank waits for a peer's data before it reports a device failure
+        # (library default 4 s).  unanswered: connect to stand-in peers nobody writes (exercises that limit).
+        self.wait_ns, self.unanswered = wait_ns, bool(unanswered)
 
 
 class DenseModel:
@@ -134,8 +137,13 @@ class DenseModel:
             handle = (C.c_uint8 * 64)()
             check(_lib.load().stark_b200_model_tp_init(m._h, tp.rank, tp.ranks, vocab_offset, cfg["vocab_total"],
                                                        handle), "model_tp_init")
-            handles = b"".join(tp.all_gather(bytes(handle)))
-            check(_lib.load().stark_b200_model_tp_connect(m._h, handles, len(handles)), "model_tp_connect")
+            if tp.wait_ns is not None:
+                check(_lib.load().stark_b200_model_tp_set_wait(m._h, int(tp.wait_ns)), "model_tp_set_wait")
+            if tp.unanswered:
+                check(_lib.load().stark_b200_model_tp_connect_unanswered(m._h), "model_tp_connect_unanswered")
+            else:
+                handles = b"".join(tp.all_gather(bytes(handle)))
+                check(_lib.load().stark_b200_model_tp_connect(m._h, handles, len(handles)), "model_tp_connect")
         m._set_matrix(0, _lib.MAT_EMBED, weights["embed"])
         if not cfg["tied"]:
             m._set_matrix(0, _lib.MAT_LM_HEAD, weights["lm_head"])

@@ -192,3 +192,36 @@ def test_named_shape_layers_against_stored_oracle_outputs(shape, name):
     assert (agree | near).mean() >= 0.99, (agree.mean(), np.nonzero(~(agree | near))[0])
     assert agree.mean() >= 0.90
     model.close()
+
+
+def test_a_peer_that_never_answers_fences_the_handle_and_nothing_else():
+    """The bounded wait of the tensor-parallel exchange, on one GPU: rank 0 of 2 is connected to a stand-in peer
+    nobody writes, with a 2 ms limit.  Its small reduction kernels give up, the next drain reports a device
+    failure and fences the handle, reset then asks for a reload, destroy works, and a fresh model on the same
+    device runs normally: nothing hung and the context stayed usable."""
+    import time
+    from stark_b200 import _lib
+    from stark_b200._lib import StarkB200Error
+    from stark_b200.engine import DenseModel, TensorParallel
+    from stark_b200.ops import take_device_error
+    cfg = S.CONFIGS["tiny"]
+    w = S.dense_weights(cfg, seed=0)
+    tp = TensorParallel(0, 2, lambda blob: [blob, blob], wait_ns=2_000_000, unanswered=True)
+    started = time.perf_counter()
+    model = DenseModel.load(cfg, w, context_tokens=128, tp=tp)     # its recording passes already wait in vain
+    assert take_device_error() & 4                                  # bit 2: a wait on a peer ran out
+    model.prefill(S.prompt(cfg, 3, seed=1))
+    with pytest.raises(StarkB200Error) as failure:
+        model.drain()
+    assert failure.value.status == _lib.STATUS_NAMES.index("device_failure")
+    assert time.perf_counter() - started < 30.0                     # every wait was a few milliseconds
+    assert model.info().fenced == 1
+    with pytest.raises(StarkB200Error) as again:
+        model.reset()
+    assert again.value.status == _lib.STATUS_NAMES.index("reload_required")
+    model.close(collective=False)
+    take_device_error()
+    fresh = DenseModel.load(cfg, w, context_tokens=128)
+    fresh.prefill(S.prompt(cfg, 5, seed=1))
+    assert np.isfinite(fresh.logits()).all() and take_device_error() == 0
+    fresh.close()

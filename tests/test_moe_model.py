@@ -159,7 +159,7 @@ def test_device_decoder_matches_oracle(name):
     token, agree, steps = int(prompt[-1]), 0, 100
     for i in range(steps):
         got, want = model.step(token), oracle.step(token)
-        assert _close(got, want)
+        assert _close(got, want, 1e-3)   # absolute tolerance on the f32 logits: 1e-3 of the largest magnitude
         agree += int(got.argmax() == want.argmax())
         token = int(want.argmax())
     assert agree >= 99, agree

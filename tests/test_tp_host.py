@@ -143,3 +143,52 @@ def test_two_gloo_ranks_reassemble_the_unsharded_results():
             p.kill()
             msgs.append("a rank did not finish")
     assert not msgs and all(p.exitcode == 0 for p in procs), msgs
+
+
+def _leaver(rank: int, port: int, results):
+    """Rank 1 leaves between two requests; rank 0 must learn of it on the host, at the rendezvous that opens its
+    next request (`DenseModel.prefill` starts with one), before it would launch anything."""
+    import datetime
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=2, timeout=datetime.timedelta(seconds=6))
+
+    def all_gather(blob: bytes):
+        out = [None, None]
+        dist.all_gather_object(out, blob)
+        return out
+
+    tp = TensorParallel(rank, 2, all_gather)
+    assert tp.all_gather(b"request 1") == [b"request 1", b"request 1"]   # both ranks open the first request
+    if rank == 1:
+        results.put("rank 1 left between requests")
+        os._exit(0)                                                     # no kernel in flight: a host-side leave
+    try:
+        tp.all_gather(b"request 2")
+        results.put("rank 0 was not told")
+    except Exception as e:  # noqa: BLE001 - gloo reports a closed connection or a timeout
+        results.put(f"rank 0 learned of it on the host: {type(e).__name__}")
+    os._exit(0)
+
+
+def test_a_rank_that_leaves_between_requests_is_noticed_on_the_host():
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    results = ctx.Queue()
+    procs = [ctx.Process(target=_leaver, args=(r, port, results)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(60)
+    msgs = []
+    while not results.empty():
+        msgs.append(results.get())
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+            msgs.append("a rank hung")
+    assert any(m.startswith("rank 0 learned of it on the host") for m in msgs), msgs
+    assert not any("hung" in m or "not told" in m for m in msgs), msgs
