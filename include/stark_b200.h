@@ -281,7 +281,7 @@ typedef struct stark_b200_dense_config {
     uint32_t context_tokens;
     float eps;
     float rope_theta;
-    uint32_t reserved;
+    uint32_t reserved; /* draft-head layers of the multi-token-prediction path: 0 (none) or 1 */
 } stark_b200_dense_config;
 
 /* Which tensor a set call addresses.  Matrices: rows [q; k; v] for QKV and [up; gate] for UPGATE
@@ -292,11 +292,15 @@ typedef struct stark_b200_dense_config {
 #define STARK_B200_MAT_O 3u
 #define STARK_B200_MAT_UPGATE 4u
 #define STARK_B200_MAT_DOWN 5u
+#define STARK_B200_MAT_MTP_FUSION 6u /* draft head: [hidden, 2 * hidden] over [norm_e(embedding) ; norm_h(hidden)] */
 #define STARK_B200_VEC_FINAL_NORM 0u
 #define STARK_B200_VEC_ATTN_NORM 1u
 #define STARK_B200_VEC_MLP_NORM 2u
 #define STARK_B200_VEC_Q_NORM 3u
 #define STARK_B200_VEC_K_NORM 4u
+#define STARK_B200_VEC_MTP_EMBED_NORM 5u  /* draft head: norm of the token embedding */
+#define STARK_B200_VEC_MTP_HIDDEN_NORM 6u /* draft head: norm of the incoming hidden row */
+#define STARK_B200_VEC_MTP_OUT_NORM 7u    /* draft head: output norm, before the shared read-out */
 
 typedef struct stark_b200_info {
     uint32_t struct_size;
@@ -422,6 +426,46 @@ stark_b200_status stark_b200_get_info(stark_b200_model *model, stark_b200_info *
  * profiler (crates/stark-engine/src/engine/hybrid/profile.rs:1-89).  count = 6 * Info.trace_slots
  * (one slot per launch, or per operator of the persistent kernel). */
 stark_b200_status stark_b200_read_trace(stark_b200_model *model, uint64_t *dst, size_t count);
+/* ------------------------------------------------------------------------------------------
+ * Dense multi-token prediction (speculative decoding with a one-layer draft head that shares the embedding and
+ * read-out of the target): LanguageModel::dense_mtp_round,
+ * crates/stark-engine/src/engine/language_model/dense_mtp.rs:661-686, 786-886; head
+ * crates/stark-engine/src/encodable_block/qwen_mtp.rs:262-330.  The call shape follows the reference's own native
+ * round of its foreign-engine bridge (stark_glm_native_initial / stark_glm_native_round,
+ * vendor/glm-exl3-bridge/include/stark_glm.h:103-110): a pending token goes in, the committed tokens and the next
+ * pending token come out.
+ *
+ * A model created with config.reserved = 1 has a draft head: set its matrices and norms with layer = config.layers
+ * (QKV, O, UPGATE, DOWN, ATTN_NORM, MLP_NORM, Q_NORM, K_NORM), STARK_B200_MAT_MTP_FUSION and the three
+ * STARK_B200_VEC_MTP_* norms before finalize.  prefill then also primes the head's cache; rewind to a position
+ * other than 0 is UNSUPPORTED (the head would need the hidden row before the cut).
+ *   mtp_initial  after prefill: the greedy token of the prompt's last row, not yet committed.
+ *   mtp_round    drafts (<= 7; the reference allows 3) proposals by the head, one (drafts + 1)-row pass of the
+ *                target, acceptance, commit.  policy GREEDY: a proposal is accepted while it equals the arg-max of
+ *                the target row before it, which reproduces plain greedy decoding token for token.  policy FORCED:
+ *                proposal i is accepted iff bit i of accept_mask is set (a timing aid with a fixed work mix; the
+ *                reference's acceptance is data dependent, crates/stark-generate/src/hybrid/mtp.rs:226-263).
+ *                tokens[0 .. count) are the committed tokens (tokens[0] is the pending token passed in).
+ *   mtp_readout_row_f32  full-vocabulary logits of row `row` of the last round's target pass, for a host-side
+ *                sampler (valid until the next round).
+ */
+#define STARK_B200_MTP_GREEDY 0u
+#define STARK_B200_MTP_FORCED 1u
+typedef struct stark_b200_mtp_round_result {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    uint32_t count;        /* rows committed to the target: 1 + accepted */
+    uint32_t accepted;     /* accepted proposals */
+    uint32_t proposed;     /* proposals made */
+    uint32_t next_pending; /* sampled after the last committed row: the input of the next round */
+    uint32_t tokens[8];    /* committed tokens */
+    uint64_t position;     /* rows in the target's cache afterwards */
+} stark_b200_mtp_round_result;
+stark_b200_status stark_b200_mtp_initial(stark_b200_model *model, uint32_t *out_pending);
+stark_b200_status stark_b200_mtp_round(stark_b200_model *model, uint32_t pending, uint32_t drafts, uint32_t policy,
+                                       uint32_t accept_mask, stark_b200_mtp_round_result *out);
+stark_b200_status stark_b200_mtp_readout_row_f32(stark_b200_model *model, uint32_t row, float *dst, size_t count);
+
 /* Launch-shape settings of the decode kernels (no counterpart in the reference, whose Metal pipelines
  * fix their threadgroup shapes at build time).  Names: "qmv_consumer_warps" (8 | 16), "qmv_smem_kb",
  * "qmv_ctas_per_sm", "qmv_fold" (0 | 1 | 2), "attn_bufs" (2 | 3), "attn_splits", "pdl" (0 | 1); each

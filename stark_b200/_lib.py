@@ -64,8 +64,17 @@ class Info(C.Structure):
                 ("trace_slots", C.c_uint32), ("persistent", C.c_uint32)]
 
 
-MAT_EMBED, MAT_LM_HEAD, MAT_QKV, MAT_O, MAT_UPGATE, MAT_DOWN = range(6)
-VEC_FINAL_NORM, VEC_ATTN_NORM, VEC_MLP_NORM, VEC_Q_NORM, VEC_K_NORM = range(5)
+MAT_EMBED, MAT_LM_HEAD, MAT_QKV, MAT_O, MAT_UPGATE, MAT_DOWN, MAT_MTP_FUSION = range(7)
+(VEC_FINAL_NORM, VEC_ATTN_NORM, VEC_MLP_NORM, VEC_Q_NORM, VEC_K_NORM, VEC_MTP_EMBED_NORM, VEC_MTP_HIDDEN_NORM,
+ VEC_MTP_OUT_NORM) = range(8)
+MTP_GREEDY, MTP_FORCED = 0, 1
+
+
+class MtpRoundResult(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("abi_version", C.c_uint32), ("count", C.c_uint32),
+                ("accepted", C.c_uint32), ("proposed", C.c_uint32), ("next_pending", C.c_uint32),
+                ("tokens", C.c_uint32 * 8), ("position", C.c_uint64)]
+
 
 class Sampling(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("flags", C.c_uint32), ("seed", C.c_uint64),
@@ -156,6 +165,9 @@ def load() -> C.CDLL:
         "stark_b200_rewind": (u32, [vp, u64]),
         "stark_b200_get_info": (u32, [vp, C.POINTER(Info)]),
         "stark_b200_model_stream": (u32, [vp, C.POINTER(vp)]),
+        "stark_b200_mtp_initial": (u32, [vp, C.POINTER(u32)]),
+        "stark_b200_mtp_round": (u32, [vp, u32, u32, u32, u32, C.POINTER(MtpRoundResult)]),
+        "stark_b200_mtp_readout_row_f32": (u32, [vp, u32, vp, sz]),
         "stark_b200_set_tunable": (u32, [C.c_char_p, u32]),
         "stark_b200_model_recapture": (u32, [vp]),
         "stark_b200_read_trace": (u32, [vp, vp, sz]),

@@ -455,6 +455,27 @@ stark_b200_status stark_b200_model_recapture(stark_b200_model *model) {
     return model_recapture(M(model));
 }
 
+stark_b200_status stark_b200_mtp_initial(stark_b200_model *model, uint32_t *out_pending) {
+    if (!model || !out_pending) return STARK_B200_INVALID_ARGUMENT;
+    Model *m = M(model);
+    if (!m->mtp.enabled) return STARK_B200_UNSUPPORTED;
+    if (!m->mtp.has_pending || !m->has_logits) return STARK_B200_INVALID_STATE;
+    return model_next_token(m, out_pending);
+}
+
+stark_b200_status stark_b200_mtp_round(stark_b200_model *model, uint32_t pending, uint32_t drafts, uint32_t policy,
+                                       uint32_t accept_mask, stark_b200_mtp_round_result *out) {
+    if (!model || !out) return STARK_B200_INVALID_ARGUMENT;
+    if (out->struct_size != sizeof(stark_b200_mtp_round_result) || out->abi_version != STARK_B200_ABI_VERSION)
+        return STARK_B200_ABI_MISMATCH;
+    return mtp_round(M(model), pending, drafts, policy, accept_mask, out);
+}
+
+stark_b200_status stark_b200_mtp_readout_row_f32(stark_b200_model *model, uint32_t row, float *dst, size_t count) {
+    if (!model || !dst) return STARK_B200_INVALID_ARGUMENT;
+    return mtp_readout_row_f32(M(model), row, dst, count);
+}
+
 stark_b200_status stark_b200_model_stream(stark_b200_model *model, void **out_stream) {
     if (!model || !out_stream) return STARK_B200_INVALID_ARGUMENT;
     *out_stream = (void *)M(model)->stream;

@@ -64,6 +64,7 @@ Model::~Model() {
         cudaFree(L.kv.keys);
         cudaFree(L.kv.values);
     }
+    mtp_destroy(this);
     if (lm_head != embed) qmatrix_free(lm_head);
     qmatrix_free(embed);
     cudaFree(final_norm);
@@ -118,8 +119,12 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     Model *m = new (std::nothrow) Model();
     if (!m) return STARK_B200_OUT_OF_MEMORY;
     m->cfg = c;
+    if (c.reserved > 1u) {  // the field counts draft-head layers: 0 or 1
+        delete m;
+        return STARK_B200_INVALID_ARGUMENT;
+    }
     cudaGetDevice(&m->device);
-    m->layers.resize(c.layers);
+    m->layers.resize(c.layers + c.reserved);  // the draft head's layer (with its own cache) comes last
     stark_b200_status st = STARK_B200_OK;
     auto fail = [&](stark_b200_status s) {
         delete m;
@@ -200,6 +205,7 @@ stark_b200_status model_create(const stark_b200_dense_config &c, Model **out) {
     if (cudaMallocHost(&m->host_state, sizeof(StepState)) != cudaSuccess ||
         cudaMallocHost(&m->host_logits, (size_t)c.vocab * 2u) != cudaSuccess)
         return fail(STARK_B200_OUT_OF_MEMORY);
+    if (c.reserved == 1u && (st = mtp_create(m)) != STARK_B200_OK) return fail(st);
     *out = m;
     return STARK_B200_OK;
 }
@@ -230,7 +236,13 @@ stark_b200_status model_set_vector(Model *m, uint32_t layer, uint32_t which, con
     if (count != (which == STARK_B200_VEC_Q_NORM || which == STARK_B200_VEC_K_NORM ? kHeadDim : c.hidden) || count % 8u != 0)
         return STARK_B200_INVALID_ARGUMENT;
     if (which == STARK_B200_VEC_FINAL_NORM) return upload_norm(&m->final_norm, &m->final_norm_b16, data, count);
-    if (layer >= c.layers) return STARK_B200_INVALID_ARGUMENT;
+    if (which >= STARK_B200_VEC_MTP_EMBED_NORM && which <= STARK_B200_VEC_MTP_OUT_NORM) {
+        if (!m->mtp.enabled) return STARK_B200_INVALID_STATE;
+        float **slot = which == STARK_B200_VEC_MTP_EMBED_NORM ? &m->mtp.embed_norm
+                       : (which == STARK_B200_VEC_MTP_HIDDEN_NORM ? &m->mtp.hidden_norm : &m->mtp.out_norm);
+        return upload_f32(slot, data, count);
+    }
+    if (layer >= m->layers.size()) return STARK_B200_INVALID_ARGUMENT;  // layers, then the draft head's layer
     auto &L = m->layers[layer];
     switch (which) {
         case STARK_B200_VEC_ATTN_NORM: return upload_norm(&L.attn_norm, &L.attn_norm_b16, data, count);
@@ -260,7 +272,11 @@ stark_b200_status model_set_matrix(Model *m, uint32_t layer, uint32_t which, QMa
         if (c.tied) return STARK_B200_INVALID_ARGUMENT;
         return put(&m->lm_head, c.vocab, c.hidden, false);
     }
-    if (layer >= c.layers) return STARK_B200_INVALID_ARGUMENT;
+    if (which == STARK_B200_MAT_MTP_FUSION) {
+        if (!m->mtp.enabled) return STARK_B200_INVALID_STATE;
+        return put(&m->mtp.fusion, c.hidden, 2u * c.hidden, false);
+    }
+    if (layer >= m->layers.size()) return STARK_B200_INVALID_ARGUMENT;  // layers, then the draft head's layer
     auto &L = m->layers[layer];
     switch (which) {
         case STARK_B200_MAT_QKV: return put(&L.qkv, qkv_n, c.hidden, false);
@@ -692,6 +708,7 @@ stark_b200_status model_finalize(Model *m) {
         m->step_launches = 1;
         m->ingest_launches = 1;
     }
+    if ((st = mtp_finalize(m)) != STARK_B200_OK) return st;
     m->finalized = true;
     return model_reset(m);
 }
@@ -735,11 +752,14 @@ stark_b200_status model_reset(Model *m) {
     SB_CUDA(cudaStreamSynchronize(m->stream));
     m->position = 0;
     m->has_logits = false;
-    return STARK_B200_OK;
+    return mtp_reset(m);
 }
 
 stark_b200_status model_rewind(Model *m, uint64_t position) {
     if (position > m->position) return STARK_B200_INVALID_ARGUMENT;
+    // the draft head's cache would need the hidden row before the cut, which is not kept
+    if (m->mtp.enabled && position != 0) return STARK_B200_UNSUPPORTED;
+    if (m->mtp.enabled) mtp_reset(m);
     const uint32_t pos = (uint32_t)position;
     SB_CUDA(cudaMemcpyAsync(&m->state->position, &pos, 4, cudaMemcpyHostToDevice, m->stream));
     SB_CUDA(cudaStreamSynchronize(m->stream));
@@ -759,8 +779,16 @@ stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count) {
         if (ids[i] >= input_vocab(m)) return STARK_B200_INVALID_ARGUMENT;
     // All rows but the last only fill the cache: enough of them go through the batched path (tensor-core
     // contraction over whole chunks), after which the last row is an ordinary token at its position.
-    if (tunables().prefill_batch && count - 1 >= tunables().prefill_min_rows && model_batched_prefill_ready(m)) {
-        stark_b200_status bs = model_prefill_batched(m, ids, count - 1);
+    const bool batched = tunables().prefill_batch && model_batched_prefill_ready(m);
+    if (m->mtp.enabled && (!batched || (m->position > 0 && !m->mtp.has_pending))) return STARK_B200_UNSUPPORTED;
+    if (batched && (m->mtp.enabled || count - 1 >= tunables().prefill_min_rows)) {
+        if (m->mtp.enabled && m->position > 0) {
+            // a continued prompt: the pair (first new token, hidden of the last row so far) enters the head's cache
+            SB_CUDA(cudaMemcpyAsync(m->chunk_tokens, ids, 4, cudaMemcpyHostToDevice, m->stream));
+            stark_b200_status ps = mtp_prime_continue(m);
+            if (ps != STARK_B200_OK) return ps;
+        }
+        stark_b200_status bs = model_prefill_batched(m, ids, count - 1, count);
         if (bs == STARK_B200_CANCELLED) {
             m->cancel_requested = false;
             cudaStreamSynchronize(m->stream);
@@ -777,7 +805,7 @@ stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count) {
         m->position += count;
         m->has_logits = true;
         m->launches_issued += m->step_launches;
-        return STARK_B200_OK;
+        return mtp_after_prompt(m);
     }
     // pending[0 .. count-2] = ids[1 ..]; the ingest-advance kernel pops one per row
     if (count > 1) SB_CUDA(cudaMemcpyAsync(m->pending, ids + 1, (count - 1) * 4, cudaMemcpyHostToDevice, m->stream));

@@ -17,6 +17,31 @@ struct ModelLayer {
     KvLayer kv{nullptr, nullptr};
 };
 
+// Draft head of the dense multi-token-prediction path (crates/stark-engine/src/encodable_block/qwen_mtp.rs:36-330):
+// rows [norm_e(embedding(token)) ; norm_h(hidden)] -> fusion [D, 2D] -> one decoder layer with a cache of its own
+// -> output norm -> the target's read-out matrix.  Its layer is stored as layers[cfg.layers].
+struct MtpHead {
+    bool enabled = false;
+    QMatrix *fusion = nullptr;
+    float *embed_norm = nullptr, *hidden_norm = nullptr, *out_norm = nullptr;
+    StepState *state = nullptr;        // device: position = rows in the head's cache, token = next input
+    uint64_t position = 0;             // host mirror
+    uint16_t *last_hidden = nullptr;   // [D] normalized hidden of the target's last committed row
+    uint16_t *draft_in = nullptr;      // [D] hidden input of the next draft step (then that step's own output)
+    uint16_t *joined = nullptr;        // [2D]
+    uint16_t *embedded = nullptr;      // [D]
+    uint16_t *stream_h = nullptr;      // [D] residual stream of the head
+    uint16_t *rows_e = nullptr;        // [chunk, D] embedding rows of a priming / repair pass
+    uint16_t *rows_j = nullptr;        // [chunk, 2D] joined rows
+    uint16_t *rows_hidden = nullptr;   // [16, D] normalized hidden rows of a verify pass
+    uint16_t *rows_logits = nullptr;   // [16, vocab] logits rows of a verify pass
+    uint32_t *rows_pick = nullptr;     // [16] greedy pick of each verify row
+    uint32_t *host_words = nullptr;    // pinned scratch for the round's small read-backs
+    cudaGraphExec_t draft_graph = nullptr;
+    uint32_t verified_rows = 0;        // rows of the last verify pass (read-out window)
+    bool has_pending = false;
+};
+
 struct Model {
     stark_b200_dense_config cfg{};
     int device = 0;
@@ -60,6 +85,7 @@ struct Model {
     uint32_t prefill_state = 0;  // 0 not examined, 1 the batched path serves this model, 2 it does not
     uint32_t *chunk_tokens = nullptr;
     uint16_t *chunk_h = nullptr, *chunk_x = nullptr, *chunk_qkv = nullptr, *chunk_attn = nullptr, *chunk_act = nullptr;
+    MtpHead mtp;
     void *sample_scratch = nullptr;     // device working memory of the sampler (allocated at first use)
     StepState *host_state = nullptr;    // pinned
     uint16_t *host_logits = nullptr;    // pinned
@@ -88,12 +114,31 @@ stark_b200_status model_rewind(Model *m, uint64_t position);
 stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count);
 stark_b200_status model_step(Model *m, uint32_t token, bool chained);
 bool model_batched_prefill_ready(Model *m);
-stark_b200_status model_prefill_batched(Model *m, const uint32_t *ids, size_t rows);
+stark_b200_status model_prefill_batched(Model *m, const uint32_t *ids, size_t rows, size_t ids_total);
+stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint32_t mrows, uint32_t first_pos);
+stark_b200_status ensure_chunk_buffers(Model *m);
 stark_b200_status model_drain(Model *m);
 stark_b200_status model_next_token(Model *m, uint32_t *out);
 stark_b200_status model_readout_bf16(Model *m, uint16_t *dst, size_t count);
 stark_b200_status model_readout_f32(Model *m, float *dst, size_t count);
 stark_b200_status model_generate_greedy(Model *m, uint32_t steps, uint32_t *out_tokens);
 stark_b200_status model_read_trace(Model *m, unsigned long long *dst, size_t count);
+
+// ---- dense multi-token prediction (mtp.cu)
+constexpr uint32_t kMaxMtpDrafts = 7;   // rows of a verify pass <= 8 (the reference allows 3; dense_mtp.rs:671)
+stark_b200_status mtp_create(Model *m);
+void mtp_destroy(Model *m);
+stark_b200_status mtp_finalize(Model *m);
+stark_b200_status mtp_reset(Model *m);
+// after a chunk of the target's prompt rows: the head's cache rows for the pairs (next token, row's hidden);
+// `pairs` <= mrows is how many rows have a next token
+stark_b200_status mtp_prime_rows(Model *m, uint32_t mrows, uint32_t pairs, uint32_t first_pos);
+// after the prompt's last row went through the token path: its normalized hidden becomes the head's input
+stark_b200_status mtp_after_prompt(Model *m);
+// a prompt continued at a position > 0: the pair (chunk_tokens[0], last hidden) becomes the head's next cache row
+stark_b200_status mtp_prime_continue(Model *m);
+stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_t policy, uint32_t accept_mask,
+                            stark_b200_mtp_round_result *out);
+stark_b200_status mtp_readout_row_f32(Model *m, uint32_t row, float *dst, size_t count);
 
 }  // namespace sb

@@ -31,8 +31,13 @@ stark_b200_status prefill_gemm_launch(const GemmArgs &args, cudaStream_t stream)
 stark_b200_status embed_rows_launch(const QMatrix *table, const uint32_t *tokens, uint32_t m, uint16_t *h,
                                     cudaStream_t stream);
 // out[i] = bf16(bf16(h[i] * rms_inv_i) * bf16(w))        normalization.rs:13-191 (only-normalization mode)
+// in_stride / out_stride: elements between consecutive rows (0 = d), so that rows can be read from or written
+// into a wider buffer (the [e ; h] rows of the draft head's fusion input)
 stark_b200_status rmsnorm_rows_launch(const uint16_t *h, const float *weight, uint16_t *out, uint32_t m, uint32_t d,
-                                      float eps, cudaStream_t stream);
+                                      float eps, cudaStream_t stream, uint32_t in_stride = 0, uint32_t out_stride = 0);
+// first[i] = first index of the maximum of row i of a [m, n] bf16 matrix (UINT32_MAX if a value is not finite):
+// the greedy read-out of several rows at once (unified_sampling.rs:42-45, 108-113)
+stark_b200_status argmax_rows_launch(const uint16_t *rows, uint32_t m, uint32_t n, uint32_t *first, cudaStream_t stream);
 // Per row and head: q heads normalized and rotated in place, k heads normalized, rotated and appended to the
 // cache at position first_pos + i together with the v heads.
 struct RopeAppendArgs {

@@ -95,6 +95,17 @@ __device__ inline void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ inline void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ inline uint64_t smem_desc_sw128(uint32_t smem_addr) {
     const uint64_t lo = (uint64_t)((smem_addr & 0x3ffffu) >> 4) | ((uint64_t)1u << 16);  // start, leading offset 16 B
@@ -386,6 +397,166 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
     }
 }
 
+// ---------------------------------------------------------------------------------------- few rows
+// The same contraction for a handful of rows (the k + 1 rows a speculative round verifies): the operand roles are
+// swapped so that the 128 output features of a CTA are the M rows of the tensor-core tile and at most 16
+// activation rows its N columns.  The tensor-core work then shrinks with the row count (128 x 16 x 16 per
+// instruction instead of 128 x 128 x 16) and the kernel runs at the pace of its dequantizing prologue, i.e. of
+// the weight stream.  Accumulators: lane = feature, column = row.
+constexpr uint32_t kSmallRows = 16;
+constexpr uint32_t kSmallXStage = kSmallRows * 128u;            // 2 KB: 16 rows x 64 columns bf16
+constexpr uint32_t kSmallStageBytes = kBStage + kSmallXStage;   // 18 KB, a multiple of 1024
+constexpr uint32_t kSmallStages = 6;
+constexpr uint32_t kSmallSmem = kSmallStages * kSmallStageBytes + 1024u + 256u;
+constexpr uint32_t kSmallTmemColumns = 32;
+constexpr uint32_t kIdescSmall = (1u << 4) | (1u << 7) | (1u << 10) | ((kSmallRows >> 3) << 17) | ((128u >> 4) << 24);
+
+__global__ void __launch_bounds__(kGemmThreads, 1)
+prefill_gemm_a4_small_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) {
+    extern __shared__ uint8_t gemm_smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023u) & ~(uintptr_t)1023u);
+    uint8_t *stages = smem;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + kSmallStages * kSmallStageBytes);
+    uint64_t *full_x = bars, *full_w = bars + kSmallStages, *empty = bars + 2 * kSmallStages, *acc_full = bars + 3 * kSmallStages;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 3 * kSmallStages + 1);
+    volatile uint32_t *abort_flag = tmem_slot + 1;
+
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t n_tile0 = blockIdx.x * (kBN / 16u);
+    const uint32_t t0 = blockIdx.y * kSmallRows;  // first activation row of this CTA
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < kSmallStages; ++s) {
+            mbar_init(&full_x[s], 1);
+            mbar_init(&full_w[s], kDequantWarps);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, kSmallTmemColumns);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t slot = 0, phase = 1;
+            for (uint32_t kg = 0; kg < p.groups; ++kg) {
+                if (!mbar_wait_bounded(&empty[slot], phase, abort_flag)) {
+                    *abort_flag = 1;
+                    atomicOr(p.error_word, kErrMbarTimeout);
+                    break;
+                }
+                mbar_arrive_expect_tx(&full_x[slot], kSmallXStage);
+                tma_load_2d(stages + slot * kSmallStageBytes + kBStage, &x_map, kg * kBK, t0, &full_x[slot]);
+                if (++slot == kSmallStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t slot = 0, phase = 0;
+            for (uint32_t kg = 0; kg < p.groups; ++kg) {
+                if (!(mbar_wait_bounded(&full_x[slot], phase, abort_flag) && mbar_wait_bounded(&full_w[slot], phase, abort_flag))) {
+                    *abort_flag = 1;
+                    atomicOr(p.error_word, kErrMbarTimeout);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t w_addr = smem_u32(stages + slot * kSmallStageBytes);
+                const uint32_t x_addr = w_addr + kBStage;
+#pragma unroll
+                for (uint32_t k4 = 0; k4 < kBK / 16u; ++k4)
+                    umma_f16(tmem_base, smem_desc_sw128(w_addr + k4 * 32u), smem_desc_sw128(x_addr + k4 * 32u), kIdescSmall,
+                             (kg | k4) != 0u ? 1u : 0u);
+                umma_commit(&empty[slot]);
+                if (++slot == kSmallStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+            umma_commit(acc_full);
+        }
+    } else {
+        const uint32_t d = warp - 2u;
+        const uint32_t tile = n_tile0 + d;
+        uint32_t slot = 0, phase = 1;
+        constexpr uint32_t kAhead = 4;
+        RecordRegs ring[kAhead];
+#pragma unroll
+        for (uint32_t i = 0; i < kAhead; ++i)
+            ring[i] = load_record(p.w, i < p.groups ? tile : 0xffffffffu, p.row_tiles, p.groups, i, lane);
+        bool ok = true;
+        for (uint32_t kb = 0; kb < p.groups && ok; kb += kAhead) {
+#pragma unroll
+            for (uint32_t i = 0; i < kAhead; ++i) {
+                const uint32_t kg = kb + i;
+                if (kg >= p.groups) break;
+                const RecordRegs cur = ring[i];
+                const uint32_t next = kg + kAhead;
+                ring[i] = load_record(p.w, next < p.groups ? tile : 0xffffffffu, p.row_tiles, p.groups,
+                                      next < p.groups ? next : 0u, lane);
+                if (!mbar_wait_bounded(&empty[slot], phase, abort_flag)) {
+                    if (lane == 0) {
+                        *abort_flag = 1;
+                        atomicOr(p.error_word, kErrMbarTimeout);
+                    }
+                    ok = false;
+                    break;
+                }
+                dequant_record_to_smem(cur, stages + slot * kSmallStageBytes, d, lane);
+                proxy_fence_async();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full_w[slot]);
+                if (++slot == kSmallStages) {
+                    slot = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
+        if (d < 4u) {
+            // ---- epilogue: four warps cover the 128 lanes of the accumulator; lane = feature, column = row
+            const uint32_t sub = warp & 3u;
+            if (!mbar_wait_bounded(acc_full, 0, abort_flag) && lane == 0) atomicOr(p.error_word, kErrMbarTimeout);
+            tc_fence_after();
+            uint32_t acc[16];
+            tmem_ld_32x16(tmem_base + ((sub * 32u) << 16), acc);
+            const uint32_t feature = n_tile0 * 16u + sub * 32u + lane;  // storage row of the matrix
+#pragma unroll
+            for (uint32_t j = 0; j < kSmallRows; ++j) {
+                const uint32_t row = t0 + j;
+                const float v = __uint_as_float(acc[j]);
+                if (p.epilogue == kEpiSwiGlu) {
+                    // lanes 0-15 hold an `up` tile, lanes 16-31 the `gate` tile of the same logical rows
+                    const float gate_raw = __shfl_down_sync(0xffffffffu, v, 16);
+                    if (lane < 16u && row < p.m) {
+                        const float up = bf16_round(v), gate = bf16_round(gate_raw);
+                        const float activated = bf16_round(gate / (1.0f + expf(-1.0f * gate)));
+                        const uint32_t logical = (feature / 32u) * 16u + lane;
+                        if (logical < p.rows / 2u)
+                            p.out[(size_t)row * p.ld_out + logical] = f32_to_bf16_bits(up * activated);
+                    }
+                } else if (row < p.m && feature < p.rows) {
+                    uint16_t *dst = p.out + (size_t)row * p.ld_out + feature;
+                    const float y = bf16_round(v);
+                    *dst = p.epilogue == kEpiResidual ? f32_to_bf16_bits(y + bf16_bits_to_f32(*dst)) : f32_to_bf16_bits(y);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kSmallTmemColumns);
+    }
+}
+
 // ---------------------------------------------------------------------------------------- host side
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -418,10 +589,12 @@ stark_b200_status prefill_gemm_launch(const GemmArgs &a, cudaStream_t stream) {
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return STARK_B200_UNSUPPORTED;
 
+    // Up to 16 rows take the few-rows kernel (rows as the N side of the tile); more take 256-row tiles.
+    const bool small = a.m <= kSmallRows;
     CUtensorMap map;
     const cuuint64_t dims[2] = {w->columns, a.x_rows};
     const cuuint64_t strides[1] = {(cuuint64_t)w->columns * 2u};
-    const cuuint32_t box[2] = {kBK, 128u};
+    const cuuint32_t box[2] = {kBK, small ? kSmallRows : 128u};
     const cuuint32_t elem[2] = {1u, 1u};
     if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<uint16_t *>(a.x), dims, strides, box, elem,
                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -439,10 +612,16 @@ stark_b200_status prefill_gemm_launch(const GemmArgs &a, cudaStream_t stream) {
     p.epilogue = a.epilogue;
     p.error_word = a.error_word;
     p.stop_after = tunables().gemm_stop_after;
-    static SmemOptIn once;
-    if (stark_b200_status s = ensure_dynamic_smem(prefill_gemm_a4_kernel, (int)kGemmSmem, once)) return s;
-    const dim3 grid((w->row_tiles * 16u + kBN - 1u) / kBN, (a.m + kBM - 1u) / kBM);
-    prefill_gemm_a4_kernel<<<grid, kGemmThreads, kGemmSmem, stream>>>(map, p);
+    static SmemOptIn once, once_small;
+    const uint32_t feature_tiles = (w->row_tiles * 16u + kBN - 1u) / kBN;
+    if (small) {
+        if (stark_b200_status s = ensure_dynamic_smem(prefill_gemm_a4_small_kernel, (int)kSmallSmem, once_small)) return s;
+        prefill_gemm_a4_small_kernel<<<dim3(feature_tiles, (a.m + kSmallRows - 1u) / kSmallRows), kGemmThreads, kSmallSmem,
+                                       stream>>>(map, p);
+    } else {
+        if (stark_b200_status s = ensure_dynamic_smem(prefill_gemm_a4_kernel, (int)kGemmSmem, once)) return s;
+        prefill_gemm_a4_kernel<<<dim3(feature_tiles, (a.m + kBM - 1u) / kBM), kGemmThreads, kGemmSmem, stream>>>(map, p);
+    }
     SB_CUDA(cudaGetLastError());
     return STARK_B200_OK;
 }

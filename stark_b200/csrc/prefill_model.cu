@@ -21,13 +21,15 @@ stark_b200_status dmalloc_rows(T **p, size_t count) {
     return STARK_B200_OK;
 }
 
+}  // namespace
+
 stark_b200_status ensure_chunk_buffers(Model *m) {
     if (m->chunk_h) return STARK_B200_OK;
     const auto &c = m->cfg;
     const size_t rows = kPrefillChunkRows;
     const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
     stark_b200_status st;
-    if ((st = dmalloc_rows(&m->chunk_tokens, rows)) != STARK_B200_OK) return st;
+    if ((st = dmalloc_rows(&m->chunk_tokens, rows + 8u)) != STARK_B200_OK) return st;
     if ((st = dmalloc_rows(&m->chunk_h, rows * c.hidden)) != STARK_B200_OK) return st;
     if ((st = dmalloc_rows(&m->chunk_x, rows * c.hidden)) != STARK_B200_OK) return st;
     if ((st = dmalloc_rows(&m->chunk_qkv, rows * qkv_n)) != STARK_B200_OK) return st;
@@ -36,8 +38,6 @@ stark_b200_status ensure_chunk_buffers(Model *m) {
     return STARK_B200_OK;
 }
 
-}  // namespace
-
 // Whether the batched path can take this model's prompt rows: one GPU, the recorded-launch token path, layer
 // matrices whose rows fill whole 128-feature tiles (examined once, at first use).
 bool model_batched_prefill_ready(Model *m) {
@@ -45,7 +45,7 @@ bool model_batched_prefill_ready(Model *m) {
     if (m->prefill_state == 1u) return true;
     m->prefill_state = 2u;
     if (m->tp.size > 1u || m->use_mega) return false;
-    for (auto &L : m->layers)
+    for (auto &L : m->layers)  // the draft head's layer, if any, included
         for (QMatrix *q : {L.qkv, L.o, L.upgate, L.down}) {
             if (q->rows % 128u != 0 || q->columns % 64u != 0) return false;
         }
@@ -54,69 +54,80 @@ bool model_batched_prefill_ready(Model *m) {
     return true;
 }
 
-// Ingests `rows` prompt rows starting at position m->position (cache only: no logits).  The caller has checked
-// ids and the context limit.
-stark_b200_status model_prefill_batched(Model *m, const uint32_t *ids, size_t rows) {
+// One chunk of rows whose token ids are already on the device, at cache positions first_pos .. first_pos + mrows:
+// embedding, then every layer of the target.  Leaves the rows' final residual stream in m->chunk_h.
+stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint32_t mrows, uint32_t first_pos) {
     const auto &c = m->cfg;
     DeviceContext *ctx = device_context();
     if (!ctx) return STARK_B200_DEVICE_FAILURE;
+    if (mrows == 0 || mrows > kPrefillChunkRows) return STARK_B200_INVALID_ARGUMENT;
     cudaStream_t s = m->stream;
     const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
     const float scale = 1.0f / sqrtf((float)kHeadDim);
     stark_b200_status st;
-    uint64_t launches = 0;
+    if ((st = embed_rows_launch(m->embed, tokens_device, mrows, m->chunk_h, s)) != STARK_B200_OK) return st;
+    for (uint32_t l = 0; l < c.layers; ++l) {
+        auto &L = m->layers[l];
+        GemmArgs g{};
+        g.x_rows = kPrefillChunkRows;
+        g.m = mrows;
+        g.error_word = ctx->error_word;
+        // qkv = W_qkv rmsnorm(h)
+        if ((st = rmsnorm_rows_launch(m->chunk_h, L.attn_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
+        g.w = L.qkv;
+        g.x = m->chunk_x;
+        g.out = m->chunk_qkv;
+        g.ld_out = qkv_n;
+        g.epilogue = kEpiStore;
+        if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        // per-head norm, RoPE, cache append; causal attention over the cache
+        RopeAppendArgs ra{m->chunk_qkv, L.kv, m->block_table, L.q_norm, L.k_norm, m->rope_cos, m->rope_sin,
+                          mrows, first_pos, c.q_heads, c.kv_heads, c.eps};
+        if ((st = rope_append_rows_launch(ra, s)) != STARK_B200_OK) return st;
+        PrefillAttnArgs pa{m->chunk_qkv, L.kv, m->block_table, m->chunk_attn, mrows, first_pos, c.q_heads, c.kv_heads, scale};
+        if ((st = prefill_attention_launch(pa, s)) != STARK_B200_OK) return st;
+        // h = bf16(bf16(W_o attn) + h)
+        g.w = L.o;
+        g.x = m->chunk_attn;
+        g.out = m->chunk_h;
+        g.ld_out = c.hidden;
+        g.epilogue = kEpiResidual;
+        if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        // act = silu(gate) * up
+        if ((st = rmsnorm_rows_launch(m->chunk_h, L.mlp_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
+        g.w = L.upgate;
+        g.x = m->chunk_x;
+        g.out = m->chunk_act;
+        g.ld_out = c.inter;
+        g.epilogue = kEpiSwiGlu;
+        if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        // h = bf16(bf16(W_down act) + h)
+        g.w = L.down;
+        g.x = m->chunk_act;
+        g.out = m->chunk_h;
+        g.ld_out = c.hidden;
+        g.epilogue = kEpiResidual;
+        if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+    }
+    m->launches_issued += 1u + 8u * c.layers;
+    return STARK_B200_OK;
+}
+
+// Ingests `rows` prompt rows starting at position m->position (cache only: no logits).  The caller has checked
+// ids and the context limit.  With a draft head loaded, every chunk also primes the head's cache with the pairs
+// (next prompt token, this row's normalized hidden): dense_mtp.rs:462-584.
+stark_b200_status model_prefill_batched(Model *m, const uint32_t *ids, size_t rows, size_t ids_total) {
+    stark_b200_status st;
     for (size_t done = 0; done < rows; done += kPrefillChunkRows) {
         if (m->cancel_requested) return STARK_B200_CANCELLED;
         const uint32_t mrows = (uint32_t)std::min<size_t>(kPrefillChunkRows, rows - done);
         const uint32_t first_pos = (uint32_t)(m->position + done);
-        SB_CUDA(cudaMemcpyAsync(m->chunk_tokens, ids + done, (size_t)mrows * 4u, cudaMemcpyHostToDevice, s));
-        if ((st = embed_rows_launch(m->embed, m->chunk_tokens, mrows, m->chunk_h, s)) != STARK_B200_OK) return st;
-        ++launches;
-        for (auto &L : m->layers) {
-            GemmArgs g{};
-            g.x_rows = kPrefillChunkRows;
-            g.m = mrows;
-            g.error_word = ctx->error_word;
-            // qkv = W_qkv rmsnorm(h)
-            if ((st = rmsnorm_rows_launch(m->chunk_h, L.attn_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
-            g.w = L.qkv;
-            g.x = m->chunk_x;
-            g.out = m->chunk_qkv;
-            g.ld_out = qkv_n;
-            g.epilogue = kEpiStore;
-            if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
-            // per-head norm, RoPE, cache append; causal attention over the cache
-            RopeAppendArgs ra{m->chunk_qkv, L.kv, m->block_table, L.q_norm, L.k_norm, m->rope_cos, m->rope_sin,
-                              mrows, first_pos, c.q_heads, c.kv_heads, c.eps};
-            if ((st = rope_append_rows_launch(ra, s)) != STARK_B200_OK) return st;
-            PrefillAttnArgs pa{m->chunk_qkv, L.kv, m->block_table, m->chunk_attn, mrows, first_pos, c.q_heads, c.kv_heads, scale};
-            if ((st = prefill_attention_launch(pa, s)) != STARK_B200_OK) return st;
-            // h = bf16(bf16(W_o attn) + h)
-            g.w = L.o;
-            g.x = m->chunk_attn;
-            g.out = m->chunk_h;
-            g.ld_out = c.hidden;
-            g.epilogue = kEpiResidual;
-            if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
-            // act = silu(gate) * up
-            if ((st = rmsnorm_rows_launch(m->chunk_h, L.mlp_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
-            g.w = L.upgate;
-            g.x = m->chunk_x;
-            g.out = m->chunk_act;
-            g.ld_out = c.inter;
-            g.epilogue = kEpiSwiGlu;
-            if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
-            // h = bf16(bf16(W_down act) + h)
-            g.w = L.down;
-            g.x = m->chunk_act;
-            g.out = m->chunk_h;
-            g.ld_out = c.hidden;
-            g.epilogue = kEpiResidual;
-            if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
-            launches += 8;
-        }
+        // one extra id when there is one: the head's pairs need the token after each row
+        const size_t upload = std::min<size_t>((size_t)mrows + 1u, ids_total - done);
+        SB_CUDA(cudaMemcpyAsync(m->chunk_tokens, ids + done, upload * 4u, cudaMemcpyHostToDevice, m->stream));
+        if ((st = model_rows_pass(m, m->chunk_tokens, mrows, first_pos)) != STARK_B200_OK) return st;
+        if (m->mtp.enabled && (st = mtp_prime_rows(m, mrows, (uint32_t)(upload - 1u), first_pos)) != STARK_B200_OK) return st;
     }
-    m->launches_issued += launches;
     return STARK_B200_OK;
 }
 

@@ -52,10 +52,11 @@ constexpr int kNormThreads = 256;
 constexpr int kNormMaxChunks = 6;  // 8 elements each: rows of up to 12288
 __global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const uint16_t *__restrict__ h,
                                                                     const float *__restrict__ weight,
-                                                                    uint16_t *__restrict__ out, uint32_t d, float eps) {
+                                                                    uint16_t *__restrict__ out, uint32_t d, float eps,
+                                                                    uint32_t in_stride, uint32_t out_stride) {
     __shared__ float red[kNormThreads / 32];
     const uint32_t tid = threadIdx.x, chunks = d / 8u;
-    const uint4 *src = reinterpret_cast<const uint4 *>(h + (size_t)blockIdx.x * d);
+    const uint4 *src = reinterpret_cast<const uint4 *>(h + (size_t)blockIdx.x * in_stride);
     uint4 v[kNormMaxChunks];
     float sumsq = 0.0f;
 #pragma unroll
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const uint16
 #pragma unroll
     for (int i = 0; i < kNormThreads / 32; ++i) total += red[i];
     const float rms_inv = 1.0f / sqrtf(total / (float)d + eps);
-    uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t)blockIdx.x * d);
+    uint4 *dst = reinterpret_cast<uint4 *>(out + (size_t)blockIdx.x * out_stride);
 #pragma unroll
     for (int r = 0; r < kNormMaxChunks; ++r) {
         const uint32_t c = tid + r * kNormThreads;
@@ -94,6 +95,45 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_rows_kernel(const uint16
                                    __uint_as_float(n2 & 0xffff0000u) * bf16_round(wf[2 * i + 1]));
         }
         dst[c] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ row arg-max
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const uint16_t *__restrict__ rows, uint32_t n, uint32_t *first) {
+    __shared__ float vs[32];
+    __shared__ uint32_t is[32];
+    const uint16_t *row = rows + (size_t)blockIdx.x * n;
+    float best = -INFINITY;
+    uint32_t bi = 0xffffffffu;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = bf16_bits_to_f32(row[i]);
+        const float key = isfinite(v) ? v : INFINITY;  // a non-finite logit must surface
+        if (key > best || (key == best && i < bi)) {
+            best = key;
+            bi = i;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) {
+            best = ov;
+            bi = oi;
+        }
+    }
+    if ((threadIdx.x & 31u) == 0) {
+        vs[threadIdx.x >> 5] = best;
+        is[threadIdx.x >> 5] = bi;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (uint32_t w = 1; w < blockDim.x / 32u; ++w)
+            if (vs[w] > best || (vs[w] == best && is[w] < bi)) {
+                best = vs[w];
+                bi = is[w];
+            }
+        first[blockIdx.x] = isfinite(best) ? bi : 0xffffffffu;
     }
 }
 
@@ -327,10 +367,19 @@ stark_b200_status embed_rows_launch(const QMatrix *table, const uint32_t *tokens
 }
 
 stark_b200_status rmsnorm_rows_launch(const uint16_t *h, const float *weight, uint16_t *out, uint32_t m, uint32_t d,
-                                      float eps, cudaStream_t stream) {
-    if (!h || !weight || !out || m == 0 || d % 8u != 0 || d > (uint32_t)kNormThreads * kNormMaxChunks * 8u)
+                                      float eps, cudaStream_t stream, uint32_t in_stride, uint32_t out_stride) {
+    if (!h || !weight || !out || m == 0 || d % 8u != 0 || d > (uint32_t)kNormThreads * kNormMaxChunks * 8u ||
+        in_stride % 8u != 0 || out_stride % 8u != 0)
         return STARK_B200_INVALID_ARGUMENT;
-    rmsnorm_rows_kernel<<<m, kNormThreads, 0, stream>>>(h, weight, out, d, eps);
+    rmsnorm_rows_kernel<<<m, kNormThreads, 0, stream>>>(h, weight, out, d, eps, in_stride ? in_stride : d,
+                                                        out_stride ? out_stride : d);
+    SB_CUDA(cudaGetLastError());
+    return STARK_B200_OK;
+}
+
+stark_b200_status argmax_rows_launch(const uint16_t *rows, uint32_t m, uint32_t n, uint32_t *first, cudaStream_t stream) {
+    if (!rows || !first || m == 0 || n == 0) return STARK_B200_INVALID_ARGUMENT;
+    argmax_rows_kernel<<<m, 1024, 0, stream>>>(rows, n, first);
     SB_CUDA(cudaGetLastError());
     return STARK_B200_OK;
 }

@@ -99,7 +99,8 @@ class DenseModel:
         self._h = C.c_void_p()
         c = _lib.DenseConfig(C.sizeof(_lib.DenseConfig), _lib.ABI_VERSION, cfg["layers"], cfg["hidden"],
                              cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["inter"], cfg["vocab"],
-                             int(cfg["tied"]), self.context_tokens, cfg["eps"], cfg["rope_theta"], 0)
+                             int(cfg["tied"]), self.context_tokens, cfg["eps"], cfg["rope_theta"],
+                             1 if cfg.get("mtp") else 0)
         check(_lib.load().stark_b200_model_create(C.byref(c), C.byref(self._h)), "model_create")
 
     # ------------------------------------------------------------------ loading
@@ -157,6 +158,18 @@ class DenseModel:
             m._set_vector(i, _lib.VEC_MLP_NORM, lw["mlp_norm"])
             m._set_vector(i, _lib.VEC_Q_NORM, lw["q_norm"])
             m._set_vector(i, _lib.VEC_K_NORM, lw["k_norm"])
+        if cfg.get("mtp"):
+            # the draft head (qwen_mtp.rs:36-330): its decoder layer is stored after the target's layers
+            head, at = weights["mtp"], cfg["layers"]
+            m._set_matrix(at, _lib.MAT_MTP_FUSION, head["fusion"])
+            for which, key in ((_lib.MAT_QKV, "qkv"), (_lib.MAT_O, "o"), (_lib.MAT_UPGATE, "upgate"), (_lib.MAT_DOWN, "down")):
+                m._set_matrix(at, which, head["layer"][key])
+            for which, key in ((_lib.VEC_ATTN_NORM, "attn_norm"), (_lib.VEC_MLP_NORM, "mlp_norm"),
+                               (_lib.VEC_Q_NORM, "q_norm"), (_lib.VEC_K_NORM, "k_norm")):
+                m._set_vector(at, which, head["layer"][key])
+            m._set_vector(at, _lib.VEC_MTP_EMBED_NORM, head["embed_norm"])
+            m._set_vector(at, _lib.VEC_MTP_HIDDEN_NORM, head["hidden_norm"])
+            m._set_vector(at, _lib.VEC_MTP_OUT_NORM, head["out_norm"])
         if tp is not None:
             tp.all_gather(b"")  # every rank has uploaded its shard: the recording pass below is collective
         check(_lib.load().stark_b200_model_finalize(m._h), "model_finalize")
@@ -269,6 +282,33 @@ class DenseModel:
         n = self.info().trace_slots
         out = np.empty((n, 6), np.uint64)
         check(_lib.load().stark_b200_read_trace(self._h, out.ctypes.data, out.size), "read_trace")
+        return out
+
+    # ------------------------------------------------------------------ multi-token prediction
+    def mtp_initial(self) -> int:
+        """After ``prefill``: the pending token (greedy pick of the prompt's last row), not yet committed."""
+        t = C.c_uint32(0)
+        self._guard(_lib.load().stark_b200_mtp_initial(self._h, C.byref(t)), "mtp_initial")
+        return t.value
+
+    def mtp_round(self, pending: int, drafts: int, accept_mask: int | None = None) -> dict:
+        """One speculative round (``LanguageModel::dense_mtp_round``, dense_mtp.rs:661-886): ``drafts`` proposals of
+        the head, one target pass over ``drafts + 1`` rows, acceptance, commit.  Greedy acceptance unless
+        ``accept_mask`` gives the pattern (bit i accepts proposal i).  Returns the committed tokens (the first is
+        ``pending``), the accepted count and the next pending token."""
+        r = _lib.MtpRoundResult()
+        r.struct_size, r.abi_version = C.sizeof(_lib.MtpRoundResult), _lib.ABI_VERSION
+        policy = _lib.MTP_GREEDY if accept_mask is None else _lib.MTP_FORCED
+        self._guard(_lib.load().stark_b200_mtp_round(self._h, int(pending), int(drafts), policy, int(accept_mask or 0),
+                                                     C.byref(r)), "mtp_round")
+        return dict(tokens=[int(t) for t in r.tokens[:r.count]], accepted=int(r.accepted), proposed=int(r.proposed),
+                    next_pending=int(r.next_pending), position=int(r.position))
+
+    def mtp_row_logits(self, row: int) -> np.ndarray:
+        """Full-vocabulary logits (f32) of one row of the last round's target pass."""
+        out = np.empty(self.cfg["vocab"], np.float32)
+        self._guard(_lib.load().stark_b200_mtp_readout_row_f32(self._h, int(row), out.ctypes.data, out.size),
+                    "mtp_readout_row_f32")
         return out
 
     def recapture(self, **tunables: int) -> None:

@@ -91,6 +91,25 @@ def dense_weights(cfg: dict, seed: int = 0, zero_point: float = 8.0) -> dict:
     return dict(layers=layers, embed=embed, lm_head=lm_head, final_norm=norm(D))
 
 
+def mtp_weights(cfg: dict, seed: int = 0, zero_point: float = 8.0) -> dict:
+    """Random-init draft head of the dense multi-token-prediction path: fusion [D, 2D], one decoder layer of the
+    target's dimensions, and the three norms (embedding, incoming hidden, output)."""
+    rng = np.random.default_rng(seed + 7919)
+    D, hd, I = cfg["hidden"], cfg["head_dim"], cfg["inter"]
+    qkv_n = (cfg["q_heads"] + 2 * cfg["kv_heads"]) * hd
+
+    def mat(n, k, gain=1.0):
+        c = gain * 17.3 / np.sqrt(k)
+        return affine4_matrix(rng, n, k, 0.005 * c, 0.02 * c, zero_point=zero_point)
+
+    def norm(n):
+        return (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+
+    layer = dict(attn_norm=norm(D), mlp_norm=norm(D), q_norm=norm(hd), k_norm=norm(hd), qkv=mat(qkv_n, D),
+                 o=mat(D, cfg["q_heads"] * hd, 0.5), upgate=mat(2 * I, D), down=mat(D, I, 0.5))
+    return dict(fusion=mat(D, 2 * D), layer=layer, embed_norm=norm(D), hidden_norm=norm(D), out_norm=norm(D))
+
+
 def prompt(cfg: dict, length: int, seed: int = 1) -> np.ndarray:
     return np.random.default_rng(seed).integers(0, cfg["vocab"], size=length, dtype=np.uint32)
 
