@@ -325,6 +325,22 @@ typedef struct stark_b200_info {
 #define STARK_B200_CAP_DEVICE_GREEDY UINT64_C(8)
 
 stark_b200_status stark_b200_model_create(const stark_b200_dense_config *config, stark_b200_model **out_model);
+/* A converted-model directory (config.json + model.safetensors in the reference's own layout) loaded, re-tiled
+ * and finalized in one call, for hosts that are not Python: the image of
+ * stark_glm_load(path_utf8, path_len, options, &model) (vendor/glm-exl3-bridge/include/stark_glm.h:85-87) over the
+ * reference's artifact loader (crates/stark-engine/src/engine/language_model/mod.rs:72-127,
+ * parameters/loader.rs:80-128, 373-408).  context_tokens 0 = the model's own maximum.  IO_FAILURE: a file is
+ * missing or unreadable; INVALID_ARGUMENT: malformed JSON, a tensor with the wrong type, shape or offsets, or a
+ * tensor the decoder does not consume; UNSUPPORTED: a well-formed model outside the dense decode path (other layer
+ * types, scaled RoPE, biases, bit widths other than 4, ...); CONTEXT_LIMIT: more context than the model allows. */
+typedef struct stark_b200_load_options {
+    uint32_t struct_size;
+    uint32_t abi_version;
+    uint64_t context_tokens;
+    uint64_t flags; /* 0 */
+} stark_b200_load_options;
+stark_b200_status stark_b200_load(const uint8_t *path_utf8, size_t path_len, const stark_b200_load_options *options,
+                                  stark_b200_model **out_model);
 /* desc->pair_halves is set by the library for UPGATE; pass the matrix in the reference's layout. */
 stark_b200_status stark_b200_model_set_affine(stark_b200_model *model, uint32_t layer, uint32_t which,
                                               const void *codes, const void *scales, const void *biases,

@@ -70,6 +70,11 @@ MAT_EMBED, MAT_LM_HEAD, MAT_QKV, MAT_O, MAT_UPGATE, MAT_DOWN, MAT_MTP_FUSION = r
 MTP_GREEDY, MTP_FORCED = 0, 1
 
 
+class LoadOptions(C.Structure):
+    _fields_ = [("struct_size", C.c_uint32), ("abi_version", C.c_uint32), ("context_tokens", C.c_uint64),
+                ("flags", C.c_uint64)]
+
+
 class MtpRoundResult(C.Structure):
     _fields_ = [("struct_size", C.c_uint32), ("abi_version", C.c_uint32), ("count", C.c_uint32),
                 ("accepted", C.c_uint32), ("proposed", C.c_uint32), ("next_pending", C.c_uint32),
@@ -142,6 +147,7 @@ def load() -> C.CDLL:
         "stark_b200_op_attention_decode_static": (u32, [vp, vp, vp, vp, vp, vp, vp, vp, vp,
                                                         C.POINTER(AttentionDesc), vp]),
         "stark_b200_model_create": (u32, [C.POINTER(DenseConfig), C.POINTER(vp)]),
+        "stark_b200_load": (u32, [C.c_char_p, sz, C.POINTER(LoadOptions), C.POINTER(vp)]),
         "stark_b200_model_set_affine": (u32, [vp, u32, u32, vp, vp, vp, C.POINTER(AffineDesc)]),
         "stark_b200_model_set_vector": (u32, [vp, u32, u32, vp, u32]),
         "stark_b200_model_tp_init": (u32, [vp, u32, u32, u32, u32, vp]),

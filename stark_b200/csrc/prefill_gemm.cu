@@ -582,7 +582,8 @@ stark_b200_status prefill_gemm_launch(const GemmArgs &a, cudaStream_t stream) {
     if (!w || !a.x || !a.out || a.m == 0 || a.m > a.x_rows) return STARK_B200_INVALID_ARGUMENT;
     if (w->format != kFmtAffine4) return STARK_B200_UNSUPPORTED;
     if (a.epilogue != kEpiStore && a.epilogue != kEpiResidual && a.epilogue != kEpiSwiGlu) return STARK_B200_UNSUPPORTED;
-    if (a.epilogue == kEpiSwiGlu && !w->pair_halves) return STARK_B200_INVALID_ARGUMENT;
+    // a pair-ordered [up; gate] matrix stores its rows interleaved: only the SwiGLU epilogue puts them back
+    if ((a.epilogue == kEpiSwiGlu) != (w->pair_halves != 0)) return STARK_B200_INVALID_ARGUMENT;
     if (w->rows % 32u != 0) return STARK_B200_UNSUPPORTED;  // the epilogue writes whole 32-feature segments
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.out) & 15u) || (a.ld_out % 8u) != 0)
         return STARK_B200_INVALID_ARGUMENT;

@@ -184,6 +184,22 @@ class DenseModel:
         cfg, weights = read_artifact(directory)
         return cls.load(cfg, weights, context_tokens, tp=tp)
 
+    @classmethod
+    def load_path(cls, directory, context_tokens: int = 0) -> "DenseModel":
+        """The same artifact through the library's own loader (``stark_b200_load``): what a host that is not
+        Python calls.  The Python object only wraps the handle it gets back."""
+        from .artifact import read_artifact
+        path = str(directory).encode("utf-8")
+        opts = _lib.LoadOptions(C.sizeof(_lib.LoadOptions), _lib.ABI_VERSION, int(context_tokens), 0)
+        handle = C.c_void_p()
+        check(_lib.load().stark_b200_load(path, len(path), C.byref(opts), C.byref(handle)), "load")
+        m = cls.__new__(cls)
+        m._h, m.tp = handle, None
+        info = m.info()
+        m.context_tokens = int(info.context_tokens)
+        m.cfg = dict(vocab=int(info.vocab_size))
+        return m
+
     def _gather_vocab(self, local: np.ndarray) -> np.ndarray:
         """Whole-vocabulary vector from the ranks' read-out shards (identity on one GPU)."""
         if self.tp is None:

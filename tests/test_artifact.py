@@ -116,3 +116,90 @@ def test_engine_loaded_from_artifact_equals_engine_loaded_from_tensors(tiny_arti
     loaded.prefill(prompt)
     assert np.array_equal(loaded.logits_bf16(), want_logits)
     assert np.array_equal(loaded.generate_greedy(6), want_tokens)
+
+
+def _load_status(directory, context_tokens=0):
+    """Status of the library's own loader (`stark_b200_load`) on a directory; a model that loads is destroyed."""
+    import ctypes as C
+    from stark_b200 import _lib
+    lib = _lib.load()
+    path = str(directory).encode()
+    opts = _lib.LoadOptions(C.sizeof(_lib.LoadOptions), _lib.ABI_VERSION, context_tokens, 0)
+    handle = C.c_void_p()
+    status = lib.stark_b200_load(path, len(path), C.byref(opts), C.byref(handle))
+    if status == 0:
+        lib.stark_b200_destroy(C.byref(handle))
+    return _lib.STATUS_NAMES[status]
+
+
+def test_library_loader_refuses_what_the_python_reader_refuses(tiny_artifact, tmp_path):
+    """The C loader walks the whole artifact (config, header, every tensor it will read, the all-consumed rule)
+    before it touches the device, so its refusals can be checked without a GPU."""
+    cfg, w, path = tiny_artifact
+    root = json.loads((path / "config.json").read_text())
+    blob = (path / "model.safetensors").read_bytes()
+    (n,) = struct.unpack("<Q", blob[:8])
+
+    def variant(name, mutate_config=None, mutate_header=None):
+        d = tmp_path / name
+        d.mkdir()
+        r = json.loads(json.dumps(root))
+        if mutate_config:
+            mutate_config(r)
+        (d / "config.json").write_text(json.dumps(r))
+        header = json.loads(blob[8:8 + n])
+        if mutate_header:
+            mutate_header(header)
+        enc = json.dumps(header).encode()
+        enc += b" " * (-len(enc) % 8)
+        (d / "model.safetensors").write_bytes(struct.pack("<Q", len(enc)) + enc + blob[8 + n:])
+        return d
+
+    def window(r):
+        for lc in r["decoder_config"]["transformer_config"]["layer_configs"]:
+            lc["mixer_config"]["sliding_window_size"] = 4096
+
+    def five_bit(h):
+        h["__metadata__"]["decoder.embedding.embedding.spec"] = json.dumps(
+            {"type": "MLXSpec", "bits": 5, "group_size": 64, "layout": "input_output"})
+
+    def wrong_shape(h):
+        h["decoder.transformer.output_norm.scales"]["shape"] = [cfg["hidden"] // 2, 2]
+
+    assert _load_status(tmp_path / "nowhere") == "io_failure"
+    assert _load_status(variant("window", mutate_config=window)) == "unsupported"
+    assert _load_status(variant("type", mutate_config=lambda r: r.update(type="Qwen38LanguageModelConfig"))) == "unsupported"
+    assert _load_status(variant("bits", mutate_header=five_bit)) == "unsupported"
+    assert _load_status(variant("extra", mutate_header=lambda h: h.update(
+        {"decoder.extra.scales": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]}}))) == "invalid_argument"
+    assert _load_status(variant("missing", mutate_header=lambda h: h.pop("decoder.transformer.output_norm.scales"))) == "invalid_argument"
+    assert _load_status(variant("shape", mutate_header=wrong_shape)) == "invalid_argument"
+    assert _load_status(variant("good"), context_tokens=1 << 20) == "context_limit"
+    d = tmp_path / "short"
+    d.mkdir()
+    (d / "config.json").write_text(json.dumps(root))
+    (d / "model.safetensors").write_bytes(struct.pack("<Q", 1 << 40))
+    assert _load_status(d) == "invalid_argument"
+    (d / "config.json").write_text("{not json")
+    assert _load_status(d) == "invalid_argument"
+    # a well-formed artifact gets as far as the device: without one here, that is where it stops
+    import torch
+    if not torch.cuda.is_available():
+        assert _load_status(variant("good2"), context_tokens=128) in ("device_failure", "out_of_memory")
+
+
+@pytest.mark.gpu
+def test_library_loader_equals_the_python_loader(tiny_artifact):
+    from stark_b200.engine import DenseModel
+    cfg, w, path = tiny_artifact
+    prompt = S.prompt(cfg, 40, seed=4)
+    a = DenseModel.from_artifact(path, context_tokens=128)
+    a.prefill(prompt)
+    want_logits, want_tokens = a.logits_bf16().copy(), a.generate_greedy(6)
+    a.close()
+    b = DenseModel.load_path(path, context_tokens=128)
+    assert b.info().context_tokens == 128 and b.info().vocab_size == cfg["vocab"]
+    b.prefill(prompt)
+    assert np.array_equal(b.logits_bf16(), want_logits)
+    assert np.array_equal(b.generate_greedy(6), want_tokens)
+    b.close()
