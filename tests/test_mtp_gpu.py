@@ -1,6 +1,9 @@
-"""Dense multi-token prediction on the GPU: greedy speculative rounds must reproduce plain greedy decoding token
-for token (the acceptance rule guarantees it: a proposal is kept only when it is the target's own pick), and the
-caches must be consistent after rounds that accept and reject, whatever the draft depth."""
+"""Dense multi-token prediction on the GPU: greedy speculative rounds must reproduce plain greedy decoding (the
+acceptance rule guarantees it: a proposal is kept only when it is the target's own pick), and the caches must be
+consistent after rounds that accept and reject, whatever the draft depth.  The verify pass multiplies its rows on
+the tensor cores with the dequantized operand rounded to bf16 while the one-row path keeps f32 products, so two
+near-tied logits may swap; the checks therefore replay the speculative text through the plain model and require
+each token to be that model's pick given the same prefix, up to a bf16 near-tie."""
 import numpy as np
 import pytest
 
@@ -38,19 +41,14 @@ def _decode_with_rounds(spec, prompt, budget, drafts):
 @pytest.mark.parametrize("drafts", [0, 1, 3, 4])
 def test_greedy_rounds_reproduce_plain_greedy_decoding(name, prompt_len, drafts):
     from stark_b200.ops import take_device_error
+    from tests.test_model_gpu import assert_sequence_is_greedy
     cfg, plain, spec = _models(name, 512)
     prompt = S.prompt(cfg, prompt_len, seed=21)
-    plain.prefill(prompt)
-    want = plain.generate_greedy(47).tolist()            # 48 tokens: the prompt's pick and 47 steps
-    got, accepted, rounds = _decode_with_rounds(spec, prompt, 48, drafts)
+    got, accepted, rounds = _decode_with_rounds(spec, prompt, 48, drafts)   # 48 tokens: the prompt's pick and 47 more
     assert take_device_error() == 0
-    print(f"{name} k={drafts}: {accepted} proposals accepted over {rounds} rounds")
-    agree = sum(int(a == b) for a, b in zip(got, want))
-    # the verify pass multiplies rows on the tensor cores with the dequantized operand rounded to bf16, the plain
-    # path keeps f32 products: a near-tie may part the two sequences, after which they are not comparable
-    first_diff = next((i for i, (a, b) in enumerate(zip(got, want)) if a != b), len(want))
-    assert first_diff >= 40 or agree == len(want), (first_diff, got, want)
-    assert spec.position == prompt_len + len(got) or spec.position >= prompt_len + 48
+    strict = assert_sequence_is_greedy(plain, prompt, got)
+    print(f"{name} k={drafts}: {accepted} proposals accepted over {rounds} rounds; {strict}/48 strict picks")
+    assert spec.position >= prompt_len + 47
     plain.close()
     spec.close()
 
@@ -75,19 +73,14 @@ def test_forced_acceptance_leaves_consistent_caches():
         pending = r["next_pending"]
     assert spec.position == 200 + len(committed)
     # the same rows through the plain path of a fresh model
-    plain.prefill(np.concatenate([prompt, np.asarray(committed, np.uint32)]))
-    assert plain.argmax() == pending or True           # a near-tie may differ; the continuation below is the check
-    # greedy rounds from here on both: speculative (k = 2) against plain steps
+    # greedy rounds from here (k = 2), replayed through the plain path of a fresh model over the same tokens
+    from tests.test_model_gpu import assert_sequence_is_greedy
     out = []
     while len(out) < 24:
         r = spec.mtp_round(pending, 2)
         out += r["tokens"]
         pending = r["next_pending"]
-    plain_next = [plain.argmax()]
-    want = plain.generate_greedy(23).tolist()
-    first_diff = next((i for i, (a, b) in enumerate(zip(out, want)) if a != b), 24)
-    assert first_diff >= 20, (first_diff, out[:24], want)
-    assert plain_next[0] == want[0]
+    assert_sequence_is_greedy(plain, np.concatenate([prompt, np.asarray(committed, np.uint32)]), out)
     plain.close()
     spec.close()
 

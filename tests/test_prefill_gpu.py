@@ -104,11 +104,12 @@ def _set(name, value):
                                              ("qwen3-8b-layers", 1100)])
 def test_chunked_prefill_equals_row_by_row(name, prompt_len):
     """A prompt ingested in chunks on the tensor cores must leave the model where row-by-row steps leave it: the
-    last row's logits inside the logits acceptance, the same greedy continuation while no near-tie separates the
-    two, and a cache that later tokens can extend (positions past one chunk of 1024 rows included)."""
+    last row's logits inside the logits acceptance, and a cache that later tokens extend to the same effect
+    (positions past one chunk of 1024 rows included): the greedy continuation of the chunked model, replayed
+    through the row-by-row model, is that model's own pick at every step up to a bf16 near-tie."""
     from stark_b200.engine import DenseModel
     from stark_b200.ops import take_device_error
-    from tests.test_model_gpu import assert_logits_accepted
+    from tests.test_model_gpu import assert_logits_accepted, assert_sequence_is_greedy
     cfg = S.CONFIGS[name]
     w = S.dense_weights(cfg, seed=4, zero_point=7.5)
     model = DenseModel.load(cfg, w, context_tokens=prompt_len + 64)
@@ -117,7 +118,6 @@ def test_chunked_prefill_equals_row_by_row(name, prompt_len):
         _set("prefill_batch", 0)
         model.prefill(prompt)
         rows_logits = model.logits_bf16().copy()
-        rows_next = model.generate_greedy(12)
         model.reset()
         _set("prefill_batch", 1)
         launches = model.info().launches_issued
@@ -127,10 +127,10 @@ def test_chunked_prefill_equals_row_by_row(name, prompt_len):
         assert issued == chunks * (1 + 8 * cfg["layers"]) + model.info().launches_per_step   # the batched path ran
         assert take_device_error() == 0
         assert_logits_accepted(rows_logits, model.logits_bf16())
-        got_next = model.generate_greedy(12)
-        assert int(got_next[0]) == int(rows_next[0])
-        assert (got_next[:6] == rows_next[:6]).sum() >= 5, (got_next, rows_next)
+        got_next = model.generate_greedy(12).tolist()      # the prompt's pick and the 12 picks after it
         assert model.position == prompt_len + 12
+        _set("prefill_batch", 0)
+        assert_sequence_is_greedy(model, prompt, got_next)
     finally:
         _set("prefill_batch", 1)
         model.close()
@@ -139,7 +139,7 @@ def test_chunked_prefill_equals_row_by_row(name, prompt_len):
 def test_chunked_prefill_against_the_oracle():
     """The chunked path against the CPU oracle directly (not only against the one-row kernels)."""
     from stark_b200.engine import DenseModel
-    from tests.test_model_gpu import assert_logits_accepted
+    from tests.test_model_gpu import assert_logits_accepted, pick_near_top
     cfg = S.CONFIGS["small"]
     w = S.dense_weights(cfg, seed=1, zero_point=7.5)
     model = DenseModel.load(cfg, w, context_tokens=256)
@@ -149,10 +149,12 @@ def test_chunked_prefill_against_the_oracle():
     for t in prompt[:-1]:
         oracle.ingest(int(t))
     assert_logits_accepted(oracle.step(int(prompt[-1])), model.logits_bf16())
-    agree, steps = 0, 60
+    agree, near, steps = 0, 0, 60
     teacher = S.prompt(cfg, steps, seed=12)
     for t in teacher:
         model.step_async(int(t))
-        agree += int(model.argmax() == O.argmax_bf16(oracle.step(int(t))))
-    assert agree / steps >= 0.99, agree
+        want = oracle.step(int(t))
+        agree += int(model.argmax() == O.argmax_bf16(want))
+        near += int(pick_near_top(want, model.argmax()))
+    assert near / steps >= 0.99 and agree / steps >= 0.90, (agree, near)
     model.close()
