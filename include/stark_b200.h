@@ -154,6 +154,16 @@ stark_b200_status stark_b200_qmatrix_unpack_codes(const stark_b200_qmatrix *matr
  * 2 SwiGLU over a pair-ordered [up; gate] matrix, y being [m, rows / 2]. */
 stark_b200_status stark_b200_op_qgemm(const stark_b200_qmatrix *matrix, const void *x, void *y, uint32_t m,
                                       uint32_t epilogue, uint32_t location, void *stream);
+/* y[m, rows] = x[m, columns] * W^T for m <= 8 bf16 rows with ONE pass over a 4-bit affine matrix: the verify pass
+ * of a speculative round (k + 1 rows through the target; the reference's GEMV with an input-row tile,
+ * crates/stark-engine/src/backends/metal/kernel/matmul/gemv/gemv.metal:59-63, driven from
+ * engine/language_model/dense_mtp.rs:786-886).  norm_weight (f32[columns], nullable; columns <= 4096): every row
+ * first goes through the RMS norm with the reference's rounding points (normalization.rs:13-191).  Epilogues as
+ * stark_b200_op_qgemm.  With location DEVICE all three pointers are device pointers.  UNSUPPORTED when the rows do
+ * not fit the kernel's shared memory beside its weight ring (m * columns * 2 bytes). */
+stark_b200_status stark_b200_op_qmv_rows(const stark_b200_qmatrix *matrix, const void *x, void *y, uint32_t m,
+                                         uint32_t epilogue, const float *norm_weight, float eps, uint32_t location,
+                                         void *stream);
 /* y[m, rows] = x[m, columns] * W^T.  Replaces MatmulKernel::encode for a quantized B with
  * m <= 8 input rows (crates/stark-engine/src/backends/cpu/kernel/matmul/kernel.rs:168-285) and
  * Weights::matvec (weights.rs:1311-1350, 2511-2553).  io_type selects bf16 or f32 vectors. */

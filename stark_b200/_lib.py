@@ -137,6 +137,7 @@ def load() -> C.CDLL:
         "stark_b200_qmatrix_unpack_codes": (u32, [vp, vp, sz]),
         "stark_b200_op_qmv": (u32, [vp, vp, vp, u32, u32, u32, vp]),
         "stark_b200_op_qgemm": (u32, [vp, vp, vp, u32, u32, u32, vp]),
+        "stark_b200_op_qmv_rows": (u32, [vp, vp, vp, u32, u32, vp, C.c_float, u32, vp]),
         "stark_b200_op_rmsnorm": (u32, [vp, vp, vp, vp, u32, C.c_float, u32, u32, vp]),
         "stark_b200_op_swiglu": (u32, [vp, vp, u32, u32, vp]),
         "stark_b200_op_qmv_swiglu": (u32, [vp, vp, vp, u32, vp]),

@@ -331,6 +331,57 @@ stark_b200_status stark_b200_op_qgemm(const stark_b200_qmatrix *matrix, const vo
     return STARK_B200_OK;
 }
 
+stark_b200_status stark_b200_op_qmv_rows(const stark_b200_qmatrix *matrix, const void *x, void *y, uint32_t m,
+                                         uint32_t epilogue, const float *norm_weight_host, float eps, uint32_t location,
+                                         void *stream) {
+    QMatrix *w = const_cast<QMatrix *>(reinterpret_cast<const QMatrix *>(matrix));
+    if (!w || !x || !y || m == 0 || m > kQmvMultiMaxRows || epilogue > 2u) return STARK_B200_INVALID_ARGUMENT;
+    if (!qmv_multi_supports(w, m, norm_weight_host != nullptr)) return STARK_B200_UNSUPPORTED;
+    DeviceContext *ctx = device_context();
+    if (!ctx) return STARK_B200_DEVICE_FAILURE;
+    cudaStream_t s = (cudaStream_t)stream;
+    stark_b200_status st;
+    const uint32_t out_cols = epilogue == 2u ? w->rows / 2u : w->rows;
+    const size_t xin = (size_t)m * w->columns * 2u, yout = (size_t)m * out_cols * 2u;
+    const size_t norm_bytes = norm_weight_host ? (size_t)w->columns * 4u : 0u;
+    const uint16_t *dx = (const uint16_t *)x;
+    uint16_t *dy = (uint16_t *)y;
+    const float *dnorm = nullptr;
+    if (location == STARK_B200_HOST) {
+        // input rows, then the norm weights, in the one staging buffer (16-byte aligned parts)
+        const size_t xin_padded = (xin + 15u) & ~(size_t)15u;
+        if ((st = ensure_buffer(&ctx->stage_in, &ctx->stage_in_bytes, xin_padded + norm_bytes)) != STARK_B200_OK) return st;
+        if ((st = ensure_buffer(&ctx->stage_out, &ctx->stage_out_bytes, yout)) != STARK_B200_OK) return st;
+        SB_CUDA(cudaMemcpyAsync(ctx->stage_in, x, xin, cudaMemcpyHostToDevice, s));
+        if (norm_bytes) {
+            SB_CUDA(cudaMemcpyAsync((uint8_t *)ctx->stage_in + xin_padded, norm_weight_host, norm_bytes, cudaMemcpyHostToDevice, s));
+            dnorm = (const float *)((uint8_t *)ctx->stage_in + xin_padded);
+        }
+        if (epilogue == 1u) SB_CUDA(cudaMemcpyAsync(ctx->stage_out, y, yout, cudaMemcpyHostToDevice, s));
+        dx = (const uint16_t *)ctx->stage_in;
+        dy = (uint16_t *)ctx->stage_out;
+    } else {
+        dnorm = norm_weight_host;  // with device buffers the weights are a device pointer too
+    }
+    QmvMultiArgs a{};
+    a.matrix = w;
+    a.x = dx;
+    a.x_stride = w->columns;
+    a.m = m;
+    a.y = dy;
+    a.y_stride = out_cols;
+    a.norm_weight = dnorm;
+    a.eps = eps;
+    a.epilogue = epilogue == 0u ? kEpiStore : (epilogue == 1u ? kEpiResidual : kEpiSwiGlu);
+    a.error_word = ctx->error_word;
+    if ((st = qmv_multi_launch(a, s)) != STARK_B200_OK) return st;
+    if (location == STARK_B200_HOST) {
+        SB_CUDA(cudaMemcpyAsync(y, ctx->stage_out, yout, cudaMemcpyDeviceToHost, s));
+        SB_CUDA(cudaStreamSynchronize(s));
+    }
+    return STARK_B200_OK;
+}
+
 struct stark_b200_graph {
     cudaGraph_t graph;
     cudaGraphExec_t exec;

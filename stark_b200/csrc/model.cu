@@ -102,6 +102,7 @@ Model::~Model() {
     cudaFree(chunk_qkv);
     cudaFree(chunk_attn);
     cudaFree(chunk_act);
+    cudaFree(rows_attn_partials);
     cudaFree(tp_local);
     cudaFree(sample_scratch);
     cudaFree(tp_seq);

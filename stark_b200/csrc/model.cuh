@@ -85,6 +85,7 @@ struct Model {
     uint32_t prefill_state = 0;  // 0 not examined, 1 the batched path serves this model, 2 it does not
     uint32_t *chunk_tokens = nullptr;
     uint16_t *chunk_h = nullptr, *chunk_x = nullptr, *chunk_qkv = nullptr, *chunk_attn = nullptr, *chunk_act = nullptr;
+    float *rows_attn_partials = nullptr;  // working memory of the few-rows attention (split key tiles)
     MtpHead mtp;
     void *sample_scratch = nullptr;     // device working memory of the sampler (allocated at first use)
     StepState *host_state = nullptr;    // pinned

@@ -57,7 +57,16 @@ struct PrefillAttnArgs {
     uint16_t *out;
     uint32_t m, first_pos, q_heads, kv_heads;
     float scale;
+    // Optional working memory for the few-rows form (m <= 16): prefill_attention_partial_floats(q_heads, max_splits)
+    // floats.  With it, the key tiles of a long cache are divided among up to max_splits CTAs per KV head and
+    // merged by a second launch; without it every (row block, KV head) is one CTA.
+    float *partials = nullptr;
+    uint32_t max_splits = 0;
 };
+constexpr uint32_t kPrefillAttnMaxSplits = 64;
+inline size_t prefill_attention_partial_floats(uint32_t q_heads, uint32_t max_splits) {
+    return (size_t)16u * q_heads * max_splits * (4u + 128u);
+}
 stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_t stream);
 
 }  // namespace sb

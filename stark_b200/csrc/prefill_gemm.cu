@@ -587,6 +587,21 @@ stark_b200_status prefill_gemm_launch(const GemmArgs &a, cudaStream_t stream) {
     if (w->rows % 32u != 0) return STARK_B200_UNSUPPORTED;  // the epilogue writes whole 32-feature segments
     if ((reinterpret_cast<uintptr_t>(a.x) & 15u) || (reinterpret_cast<uintptr_t>(a.out) & 15u) || (a.ld_out % 8u) != 0)
         return STARK_B200_INVALID_ARGUMENT;
+    // A handful of rows is a weight stream, not a contraction: the several-rows matvec reads the matrix once at the
+    // pace of the one-token path.
+    if (tunables().rows_matvec && qmv_multi_supports(w, a.m, false)) {
+        QmvMultiArgs q{};
+        q.matrix = w;
+        q.x = a.x;
+        q.x_stride = w->columns;
+        q.m = a.m;
+        q.y = a.out;
+        q.y_stride = a.ld_out;
+        q.epilogue = a.epilogue;
+        q.error_word = a.error_word;
+        q.pdl = true;  // the kernel awaits its predecessor itself, after its weight ring has begun to fill
+        return qmv_multi_launch(q, stream);
+    }
     EncodeTiledFn encode = encode_tiled();
     if (!encode) return STARK_B200_UNSUPPORTED;
 

@@ -35,6 +35,8 @@ stark_b200_status ensure_chunk_buffers(Model *m) {
     if ((st = dmalloc_rows(&m->chunk_qkv, rows * qkv_n)) != STARK_B200_OK) return st;
     if ((st = dmalloc_rows(&m->chunk_attn, rows * c.q_heads * kHeadDim)) != STARK_B200_OK) return st;
     if ((st = dmalloc_rows(&m->chunk_act, rows * c.inter)) != STARK_B200_OK) return st;
+    if ((st = dmalloc_rows(&m->rows_attn_partials, prefill_attention_partial_floats(c.q_heads, kPrefillAttnMaxSplits))) != STARK_B200_OK)
+        return st;
     return STARK_B200_OK;
 }
 
@@ -65,6 +67,12 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
     const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
     const float scale = 1.0f / sqrtf((float)kHeadDim);
     stark_b200_status st;
+    // the few-rows form of the attention adds a merge launch per layer (same rule as prefill_attention_launch)
+    const bool split_rows = mrows <= 16u && std::min((first_pos + mrows - 1u) / kPageTokens + 1u,
+                                                      std::min(kPrefillAttnMaxSplits, std::max(1u, 296u / c.kv_heads))) >= 2u;
+    // a handful of rows: the several-rows matvec normalizes the rows in its own prologue
+    const bool fused_norm = tunables().rows_matvec && qmv_multi_supports(m->layers[0].qkv, mrows, true) &&
+                            qmv_multi_supports(m->layers[0].upgate, mrows, true);
     if ((st = embed_rows_launch(m->embed, tokens_device, mrows, m->chunk_h, s)) != STARK_B200_OK) return st;
     for (uint32_t l = 0; l < c.layers; ++l) {
         auto &L = m->layers[l];
@@ -73,18 +81,26 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
         g.m = mrows;
         g.error_word = ctx->error_word;
         // qkv = W_qkv rmsnorm(h)
-        if ((st = rmsnorm_rows_launch(m->chunk_h, L.attn_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
-        g.w = L.qkv;
-        g.x = m->chunk_x;
-        g.out = m->chunk_qkv;
-        g.ld_out = qkv_n;
-        g.epilogue = kEpiStore;
-        if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        if (fused_norm) {
+            QmvMultiArgs q{L.qkv, m->chunk_h, c.hidden, mrows, m->chunk_qkv, qkv_n, L.attn_norm, c.eps, kEpiStore,
+                           ctx->error_word, true};
+            if ((st = qmv_multi_launch(q, s)) != STARK_B200_OK) return st;
+        } else {
+            if ((st = rmsnorm_rows_launch(m->chunk_h, L.attn_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
+            g.w = L.qkv;
+            g.x = m->chunk_x;
+            g.out = m->chunk_qkv;
+            g.ld_out = qkv_n;
+            g.epilogue = kEpiStore;
+            if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        }
         // per-head norm, RoPE, cache append; causal attention over the cache
         RopeAppendArgs ra{m->chunk_qkv, L.kv, m->block_table, L.q_norm, L.k_norm, m->rope_cos, m->rope_sin,
                           mrows, first_pos, c.q_heads, c.kv_heads, c.eps};
         if ((st = rope_append_rows_launch(ra, s)) != STARK_B200_OK) return st;
         PrefillAttnArgs pa{m->chunk_qkv, L.kv, m->block_table, m->chunk_attn, mrows, first_pos, c.q_heads, c.kv_heads, scale};
+        pa.partials = m->rows_attn_partials;
+        pa.max_splits = kPrefillAttnMaxSplits;
         if ((st = prefill_attention_launch(pa, s)) != STARK_B200_OK) return st;
         // h = bf16(bf16(W_o attn) + h)
         g.w = L.o;
@@ -94,13 +110,19 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
         g.epilogue = kEpiResidual;
         if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
         // act = silu(gate) * up
-        if ((st = rmsnorm_rows_launch(m->chunk_h, L.mlp_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
-        g.w = L.upgate;
-        g.x = m->chunk_x;
-        g.out = m->chunk_act;
-        g.ld_out = c.inter;
-        g.epilogue = kEpiSwiGlu;
-        if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        if (fused_norm) {
+            QmvMultiArgs q{L.upgate, m->chunk_h, c.hidden, mrows, m->chunk_act, c.inter, L.mlp_norm, c.eps, kEpiSwiGlu,
+                           ctx->error_word, true};
+            if ((st = qmv_multi_launch(q, s)) != STARK_B200_OK) return st;
+        } else {
+            if ((st = rmsnorm_rows_launch(m->chunk_h, L.mlp_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
+            g.w = L.upgate;
+            g.x = m->chunk_x;
+            g.out = m->chunk_act;
+            g.ld_out = c.inter;
+            g.epilogue = kEpiSwiGlu;
+            if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        }
         // h = bf16(bf16(W_down act) + h)
         g.w = L.down;
         g.x = m->chunk_act;
@@ -109,7 +131,7 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
         g.epilogue = kEpiResidual;
         if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
     }
-    m->launches_issued += 1u + 8u * c.layers;
+    m->launches_issued += 1u + (fused_norm ? 6u : 8u) * c.layers + (split_rows ? c.layers : 0u);
     return STARK_B200_OK;
 }
 

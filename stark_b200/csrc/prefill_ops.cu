@@ -190,9 +190,15 @@ struct PrefillAttnParams {
     uint16_t *out;
     uint32_t m, first_pos, q_heads, kv_heads, gqa, row_blocks;  // row_blocks = 16-row blocks per CTA
     float scale;
+    float *partials;  // SPLIT: [m][q_heads][splits][kPartialFloats] = running maximum, denominator, unnormalized output
+    uint32_t splits;
 };
+constexpr uint32_t kPartialFloats = 4u + kHeadDim;
 
-template <int WARPS>
+// SPLIT: a handful of rows over a long cache (the rows a speculative round verifies).  The key tiles are divided
+// among gridDim.z CTAs per (row block, KV head); each leaves its running maximum, denominator and unnormalized
+// output, which prefill_attention_merge_kernel combines -- the same scheme as the one-row decode kernel.
+template <int WARPS, bool SPLIT>
 __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const PrefillAttnParams p) {
     extern __shared__ __align__(128) uint8_t pa_smem[];  // [2][K, V][64 rows][272 B]
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
@@ -204,7 +210,9 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
     const uint32_t row0 = row0_cta + 16u * (warp / p.gqa);  // this warp's 16 rows
     const uint32_t heads = p.q_heads + 2u * p.kv_heads;
     const uint32_t last_row = min(p.m, row0_cta + rows_per_cta) - 1u;
-    const uint32_t ntiles = (p.first_pos + last_row) / kPageTokens + 1u;
+    const uint32_t all_tiles = (p.first_pos + last_row) / kPageTokens + 1u;
+    const uint32_t tile_begin = SPLIT ? (uint32_t)((uint64_t)all_tiles * blockIdx.z / p.splits) : 0u;
+    const uint32_t ntiles = SPLIT ? (uint32_t)((uint64_t)all_tiles * (blockIdx.z + 1u) / p.splits) : all_tiles;
 
     auto issue_tile = [&](uint32_t tile, uint32_t buf) {
         const size_t page = ((size_t)p.block_table[tile] * p.kv_heads + kvh) * kPageTokens * kHeadDim;
@@ -217,9 +225,9 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
             cp_async16(vd + r * kTileRowBytes + ch * 16u, vsrc + r * 256u + ch * 16u);
         }
     };
-    issue_tile(0, 0);
+    if (tile_begin < ntiles) issue_tile(tile_begin, 0);
     cp_async_commit();
-    if (ntiles > 1) issue_tile(1, 1);
+    if (tile_begin + 1u < ntiles) issue_tile(tile_begin + 1u, 1);
     cp_async_commit();
 
     // Q as the A operand: rows row0 + g and row0 + g + 8, dims 16 kk + {2t, 2t+1} and + 8
@@ -242,10 +250,10 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
     for (int nt = 0; nt < 16; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.0f;
     const uint32_t lrow = lane & 7u, lmat = lane >> 3;
 
-    for (uint32_t tile = 0; tile < ntiles; ++tile) {
+    for (uint32_t tile = tile_begin; tile < ntiles; ++tile) {
         cp_async_wait<1>();
         __syncthreads();
-        const uint32_t buf = tile & 1u;
+        const uint32_t buf = (tile - tile_begin) & 1u;
         const uint8_t *kt = pa_smem + (size_t)(buf * 2u) * kTileBytes, *vt = kt + kTileBytes;
         const uint32_t key0 = tile * kPageTokens;
         if (key0 <= p.first_pos + min(row0 + 15u, p.m - 1u) && row0 < p.m) {  // some row of the warp sees this tile
@@ -340,6 +348,22 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
     cp_async_wait<0>();
 
     // o[nt][0..1]: row a, dims 8 nt + 2t, +1;  o[nt][2..3]: row b
+    if (SPLIT) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            const uint32_t r = j ? rb : ra;
+            if (r >= p.m) continue;
+            float *dst = p.partials + (((size_t)r * p.q_heads + head) * p.splits + blockIdx.z) * kPartialFloats;
+            if (t == 0) {
+                dst[0] = m_run[j];
+                dst[1] = l_run[j];
+            }
+#pragma unroll
+            for (int nt = 0; nt < 16; ++nt)
+                *reinterpret_cast<float2 *>(dst + 4 + 8 * nt + 2 * t) = make_float2(o[nt][2 * j], o[nt][2 * j + 1]);
+        }
+        return;
+    }
     const float inv_a = l_run[0] > 0.0f ? 1.0f / l_run[0] : 0.0f, inv_b = l_run[1] > 0.0f ? 1.0f / l_run[1] : 0.0f;
     if (ra < p.m) {
         uint16_t *dst = p.out + ((size_t)ra * p.q_heads + head) * kHeadDim;
@@ -353,6 +377,25 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
         for (int nt = 0; nt < 16; ++nt)
             *reinterpret_cast<uint32_t *>(dst + 8 * nt + 2 * t) = f32x2_to_bf16x2(o[nt][2] * inv_b, o[nt][3] * inv_b);
     }
+}
+
+// out[row][head][d] = sum_s w_s o_s[d] / sum_s w_s l_s with w_s = exp(m_s - max m): one CTA per (row, head)
+__global__ void __launch_bounds__(kHeadDim) prefill_attention_merge_kernel(const float *partials, uint16_t *out,
+                                                                           uint32_t q_heads, uint32_t splits) {
+    const uint32_t row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
+    pdl_launch_dependents();  // a matvec that follows may start filling its weight ring; it awaits this grid itself
+    const float *src = partials + ((size_t)row * q_heads + head) * splits * kPartialFloats;
+    float top = -INFINITY;
+    for (uint32_t s = 0; s < splits; ++s) top = fmaxf(top, src[(size_t)s * kPartialFloats]);
+    float denom = 0.0f, acc = 0.0f;
+    for (uint32_t s = 0; s < splits; ++s) {
+        const float *ps = src + (size_t)s * kPartialFloats;
+        const float w = ps[0] == -INFINITY ? 0.0f : expf(ps[0] - top);
+        denom += w * ps[1];
+        acc += w * ps[4 + d];
+    }
+    const float v = denom > 0.0f ? acc / denom : 0.0f;
+    out[((size_t)row * q_heads + head) * kHeadDim + d] = f32_to_bf16_bits(v);
 }
 
 }  // namespace
@@ -412,18 +455,42 @@ stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_
     p.gqa = gqa;
     p.scale = a.scale;
     const uint32_t smem = 4u * kTileBytes;
-    static SmemOptIn once4, once8;
+    static SmemOptIn once4, once8, once4s, once8s;
+    // few rows over a long cache: divide the key tiles among CTAs so that the whole GPU reads the cache
+    uint32_t splits = 0;
+    if (a.partials && a.max_splits > 1u && a.m <= 16u) {
+        const uint32_t tiles = (a.first_pos + a.m - 1u) / kPageTokens + 1u;
+        // two CTAs per SM (70 KB of shared memory each): about 300 CTAs share the cache's key tiles
+        splits = std::min(std::min(tiles, a.max_splits), std::max(1u, 296u / a.kv_heads));
+        if (splits < 2u) splits = 0;
+    }
+    p.partials = a.partials;
+    p.splits = splits;
     if (gqa == 8u) {
         p.row_blocks = 1;
-        if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<8>, (int)smem, once8)) return s;
-        prefill_attention_kernel<8><<<dim3((a.m + 15u) / 16u, a.kv_heads), 256, smem, stream>>>(p);
+        if (splits) {
+            if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<8, true>, (int)smem, once8s)) return s;
+            prefill_attention_kernel<8, true><<<dim3(1, a.kv_heads, splits), 256, smem, stream>>>(p);
+        } else {
+            if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<8, false>, (int)smem, once8)) return s;
+            prefill_attention_kernel<8, false><<<dim3((a.m + 15u) / 16u, a.kv_heads), 256, smem, stream>>>(p);
+        }
     } else {
         p.row_blocks = 4u / gqa;
         const uint32_t rows_per_cta = 16u * p.row_blocks;
-        if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<4>, (int)smem, once4)) return s;
-        prefill_attention_kernel<4><<<dim3((a.m + rows_per_cta - 1u) / rows_per_cta, a.kv_heads), 128, smem, stream>>>(p);
+        if (splits) {
+            if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<4, true>, (int)smem, once4s)) return s;
+            prefill_attention_kernel<4, true><<<dim3(1, a.kv_heads, splits), 128, smem, stream>>>(p);
+        } else {
+            if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<4, false>, (int)smem, once4)) return s;
+            prefill_attention_kernel<4, false><<<dim3((a.m + rows_per_cta - 1u) / rows_per_cta, a.kv_heads), 128, smem, stream>>>(p);
+        }
     }
     SB_CUDA(cudaGetLastError());
+    if (splits) {
+        prefill_attention_merge_kernel<<<dim3(a.m, a.q_heads), kHeadDim, 0, stream>>>(a.partials, a.out, a.q_heads, splits);
+        SB_CUDA(cudaGetLastError());
+    }
     return STARK_B200_OK;
 }
 

@@ -111,6 +111,25 @@ stark_b200_status qmv_launch(const QmvArgs &args, cudaStream_t stream);
 // consumer warp, and whether the stage is ragged (needs per-record predicates).
 void qmv_pick_stage(uint32_t groups, uint32_t *records, uint32_t *rpw, bool *pred);
 
+// A handful of input rows against one pass over the matrix (qmv_multi.cu): y[r] = W x[r] for r < m <= 8, bf16 in
+// and out.  norm_weight != nullptr: every row goes through the RMS norm first (columns <= 4096).
+constexpr uint32_t kQmvMultiMaxRows = 8;
+struct QmvMultiArgs {
+    const QMatrix *matrix;
+    const uint16_t *x;   // [m, K] bf16
+    uint32_t x_stride;   // elements between rows (0 = K)
+    uint32_t m;
+    uint16_t *y;         // [m, y_stride]; kEpiResidual reads and rewrites it
+    uint32_t y_stride;
+    const float *norm_weight;
+    float eps;
+    QmvEpilogue epilogue;  // kEpiStore, kEpiResidual or kEpiSwiGlu
+    uint32_t *error_word;
+    bool pdl;
+};
+bool qmv_multi_supports(const QMatrix *w, uint32_t m, bool norm);
+stark_b200_status qmv_multi_launch(const QmvMultiArgs &args, cudaStream_t stream);
+
 // Re-tiling (device kernels; inputs already in device memory).
 stark_b200_status qmatrix_from_affine_device(const uint8_t *codes, const void *scales, const void *biases,
                                              const stark_b200_affine_desc &desc, cudaStream_t stream,

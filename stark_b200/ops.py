@@ -131,6 +131,25 @@ class QMatrix:
         check(_lib.load().stark_b200_op_qgemm(self._h, _ptr(x), _ptr(y), m, epilogue, HOST, None), "op_qgemm")
         return y
 
+    def matvec_rows(self, x: np.ndarray, epilogue: int = 0, residual: np.ndarray | None = None,
+                    norm_weight: np.ndarray | None = None, eps: float = 1e-6) -> np.ndarray:
+        """Up to 8 bf16 rows against one pass over the matrix (``stark_b200_op_qmv_rows``): the verify pass of a
+        speculative round.  ``norm_weight``: RMS norm of every row in the kernel's prologue.  Epilogues as ``gemm``."""
+        x = np.ascontiguousarray(x, np.uint16)
+        m = x.shape[0]
+        if x.ndim != 2 or x.shape[1] != self.columns:
+            raise ValueError("invalid input shape")
+        cols = self.rows // 2 if epilogue == 2 else self.rows
+        y = np.ascontiguousarray(residual, np.uint16).copy() if epilogue == 1 else np.empty((m, cols), np.uint16)
+        if y.shape != (m, cols):
+            raise ValueError("invalid residual shape")
+        nw = None if norm_weight is None else np.ascontiguousarray(norm_weight, np.float32)
+        if nw is not None and nw.shape != (self.columns,):
+            raise ValueError("invalid norm weight shape")
+        check(_lib.load().stark_b200_op_qmv_rows(self._h, _ptr(x), _ptr(y), m, epilogue, None if nw is None else _ptr(nw),
+                                                 float(eps), HOST, None), "op_qmv_rows")
+        return y
+
     def matvec_device(self, x_ptr: int, y_ptr: int, m: int = 1, io_type: int = BF16, stream: int = 0) -> None:
         check(_lib.load().stark_b200_op_qmv(self._h, x_ptr, y_ptr, m, io_type, DEVICE, stream), "op_qmv")
 

@@ -52,7 +52,7 @@ def assert_sequence_is_greedy(model, prompt, tokens, steps=2.0, strict_share=0.8
         strict += int(model.argmax() == int(t))
         if i + 1 < len(tokens):
             model.step_async(int(t))
-    assert strict >= strict_share * len(tokens), (strict, len(tokens))
+    assert len(tokens) - strict <= max(3, (1.0 - strict_share) * len(tokens)), (strict, len(tokens))
     return strict
 
 
