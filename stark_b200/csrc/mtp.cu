@@ -146,7 +146,7 @@ stark_b200_status head_cache_rows(Model *m, const uint32_t *tokens_device, const
     if ((st = rmsnorm_rows_launch(h.rows_e, h.embed_norm, h.rows_j, rows, c.hidden, c.eps, s, 0, 2u * c.hidden)) != STARK_B200_OK) return st;
     if ((st = rmsnorm_rows_launch(hidden_rows, h.hidden_norm, h.rows_j + c.hidden, rows, c.hidden, c.eps, s, 0, 2u * c.hidden)) != STARK_B200_OK) return st;
     GemmArgs g{};
-    g.x_rows = kPrefillChunkRows;
+    g.x_rows = kPrefillBatchRows;
     g.m = rows;
     g.error_word = ctx->error_word;
     g.w = h.fusion;
@@ -182,8 +182,8 @@ stark_b200_status mtp_create(Model *m) {
     if ((st = dalloc(&h.joined, 2u * (size_t)c.hidden)) != STARK_B200_OK) return st;
     if ((st = dalloc(&h.embedded, c.hidden)) != STARK_B200_OK) return st;
     if ((st = dalloc(&h.stream_h, c.hidden)) != STARK_B200_OK) return st;
-    if ((st = dalloc(&h.rows_e, (size_t)kPrefillChunkRows * c.hidden)) != STARK_B200_OK) return st;
-    if ((st = dalloc(&h.rows_j, (size_t)kPrefillChunkRows * 2u * c.hidden)) != STARK_B200_OK) return st;
+    if ((st = dalloc(&h.rows_e, (size_t)kPrefillBatchRows * c.hidden)) != STARK_B200_OK) return st;
+    if ((st = dalloc(&h.rows_j, (size_t)kPrefillBatchRows * 2u * c.hidden)) != STARK_B200_OK) return st;
     if ((st = dalloc(&h.rows_hidden, (size_t)16u * c.hidden)) != STARK_B200_OK) return st;
     if ((st = dalloc(&h.rows_logits, (size_t)16u * c.vocab)) != STARK_B200_OK) return st;
     if ((st = dalloc(&h.rows_pick, 16)) != STARK_B200_OK) return st;

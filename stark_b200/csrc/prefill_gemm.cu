@@ -1,12 +1,12 @@
 // Y[M, N] = X[M, K] W[N, K]^T for a 4-bit affine group-64 matrix, many rows at a time: the prompt-chunk
 // contraction of the token loop on the sm_100a tensor cores (tcgen05.mma, accumulators in tensor memory).
 //
-// One CTA owns a tile of 256 rows x 128 output features and walks K in steps of one quantization group (64):
+// One CTA owns a tile of 256 rows x 256 output features and walks K in steps of one quantization group (64):
 //   warp 0      one thread: TMA loads of the two 128-row activation boxes of the step (bf16, 128-byte swizzle)
-//   warp 1      allocates tensor memory; one thread issues 2 x 4 tcgen05.mma (128 x 128 x 16) per step and
-//               commits them to the barrier that frees the stage
-//   warps 2-9   the dequantizing prologue: warp d turns record (16 features x 64 columns, 576 bytes, read
-//               straight from the re-tiled matrix the matvec kernels stream) into bf16 rows of the B operand --
+//   warp 1      allocates tensor memory (all 512 columns: two 128 x 256 f32 accumulators); one thread issues
+//               2 x 4 tcgen05.mma (128 x 256 x 16) per step and commits them to the barrier that frees the stage
+//   warps 2-9   the dequantizing prologue: warp d turns two records (16 features x 64 columns, 576 bytes each,
+//               read straight from the re-tiled matrix the matvec kernels stream) into bf16 rows of the B operand --
 //               codes become exact bf16 integers (shift, lop3 and one bf16 subtract per pair), then
 //               bf16(scale * q + bias) in one bf16 FMA per pair -- written in the swizzled K-major layout the
 //               tensor core reads.  The same warps run the epilogue: tcgen05.ld of the accumulators, bf16 rounding,
@@ -14,6 +14,10 @@
 // Rounding points are those of the one-row path (f32 accumulation, one bf16 rounding of the product, then the
 // epilogue's own roundings); the operand W is rounded to bf16, the activations' type, as the reference's own
 // tiled GEMM does, where the one-row path keeps scale * q + bias in f32: inside the per-operator tolerance.
+// The tile is as wide as tensor memory allows because the activation tile is what the step re-reads from L2 (once
+// per feature tile) and what the tensor core re-reads from shared memory: at 256 features a step moves 41 KB from
+// L2 and 160 KB through shared memory for 1024 tensor-core cycles (156 B/cycle of the 128 B/cycle an SM has, the
+// binding limit), at 128 features 37 KB and 112 KB for 512 cycles.
 // Every wait is bounded; a wait that runs out sets the error word, the CTA drains and frees its tensor memory.
 #include <cuda.h>
 
@@ -27,15 +31,15 @@ namespace sb {
 
 namespace {
 
-constexpr uint32_t kBM = 256, kBN = 128, kBK = 64;
-constexpr uint32_t kStages = 4;
+constexpr uint32_t kBM = 256, kBN = 256, kBK = 64;
+constexpr uint32_t kStages = 3;
 constexpr uint32_t kABox = 128u * 128u;            // one 128-row x 64-column bf16 box: 16 KB
 constexpr uint32_t kAStage = 2u * kABox;           // 32 KB
-constexpr uint32_t kBStage = kBN * 128u;           // 16 KB
+constexpr uint32_t kBStage = kBN * 128u;           // 32 KB
 constexpr uint32_t kStageBytes = kAStage + kBStage;
 constexpr uint32_t kDequantWarps = 8;
 constexpr uint32_t kGemmThreads = (2u + kDequantWarps) * 32u;
-constexpr uint32_t kTmemColumns = 256;             // two 128 x 128 f32 accumulators
+constexpr uint32_t kTmemColumns = 512;             // two 128 x 256 f32 accumulators: all of tensor memory
 constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024u /* alignment */ + 256u /* barriers */;
 
 struct GemmParams {
@@ -114,7 +118,7 @@ __device__ inline uint64_t smem_desc_sw128(uint32_t smem_addr) {
                         | ((uint64_t)2u << 29);     // 128-byte swizzle
     return lo | (hi << 32);
 }
-// Instruction descriptor: D f32, A bf16 (activations), B bf16 (dequantized weights), both K-major, M 128, N 128.
+// Instruction descriptor: D f32, A bf16 (activations), B bf16 (dequantized weights), both K-major, M 128, N 256.
 constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kBN >> 3) << 17) | ((128u >> 4) << 24);
 
 struct RecordRegs {
@@ -286,23 +290,27 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
     } else {
         // ------------------------------------------------ dequantizing prologue (one record per warp per step)
         const uint32_t d = warp - 2u;
-        const uint32_t tile = n_tile0 + d;
+        const uint32_t tile = n_tile0 + d;  // and tile + 8: rows 16 d .. and 128 + 16 d .. of the B stage
         uint32_t slot = 0, phase = 1;
-        constexpr uint32_t kAhead = 4;  // records requested ahead of use (global latency >> one step)
-        RecordRegs ring[kAhead];
+        constexpr uint32_t kAhead = 4;  // steps requested ahead of use (global latency >> one step)
+        RecordRegs ring[kAhead][2];
 #pragma unroll
-        for (uint32_t i = 0; i < kAhead; ++i)
-            ring[i] = load_record(p.w, i < p.groups ? tile : 0xffffffffu, p.row_tiles, p.groups, i, lane);
+        for (uint32_t i = 0; i < kAhead; ++i) {
+            ring[i][0] = load_record(p.w, i < p.groups ? tile : 0xffffffffu, p.row_tiles, p.groups, i, lane);
+            ring[i][1] = load_record(p.w, i < p.groups ? tile + 8u : 0xffffffffu, p.row_tiles, p.groups, i, lane);
+        }
         bool ok = true;
         for (uint32_t kb = 0; kb < p.groups && ok; kb += kAhead) {
 #pragma unroll
             for (uint32_t i = 0; i < kAhead; ++i) {
                 const uint32_t kg = kb + i;
                 if (kg >= p.groups) break;
-                const RecordRegs cur = ring[i];
+                const RecordRegs cur0 = ring[i][0], cur1 = ring[i][1];
                 const uint32_t next = kg + kAhead;
-                ring[i] = load_record(p.w, next < p.groups ? tile : 0xffffffffu, p.row_tiles, p.groups,
-                                      next < p.groups ? next : 0u, lane);
+                ring[i][0] = load_record(p.w, next < p.groups ? tile : 0xffffffffu, p.row_tiles, p.groups,
+                                         next < p.groups ? next : 0u, lane);
+                ring[i][1] = load_record(p.w, next < p.groups ? tile + 8u : 0xffffffffu, p.row_tiles, p.groups,
+                                         next < p.groups ? next : 0u, lane);
                 if (!mbar_wait_bounded(&empty[slot], phase, abort_flag)) {
                     if (lane == 0) {
                         *abort_flag = 1;
@@ -311,7 +319,8 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
                     ok = false;
                     break;
                 }
-                dequant_record_to_smem(cur, stages + slot * kStageBytes + kAStage, d, lane);
+                dequant_record_to_smem(cur0, stages + slot * kStageBytes + kAStage, d, lane);
+                dequant_record_to_smem(cur1, stages + slot * kStageBytes + kAStage, d + 8u, lane);
                 proxy_fence_async();  // the tensor core reads shared memory through the async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&full_b[slot]);
@@ -405,7 +414,8 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
 // the weight stream.  Accumulators: lane = feature, column = row.
 constexpr uint32_t kSmallRows = 16;
 constexpr uint32_t kSmallXStage = kSmallRows * 128u;            // 2 KB: 16 rows x 64 columns bf16
-constexpr uint32_t kSmallStageBytes = kBStage + kSmallXStage;   // 18 KB, a multiple of 1024
+constexpr uint32_t kSmallWStage = 128u * 128u;                  // 16 KB: 128 features x 64 columns bf16
+constexpr uint32_t kSmallStageBytes = kSmallWStage + kSmallXStage;   // 18 KB, a multiple of 1024
 constexpr uint32_t kSmallStages = 6;
 constexpr uint32_t kSmallSmem = kSmallStages * kSmallStageBytes + 1024u + 256u;
 constexpr uint32_t kSmallTmemColumns = 32;
@@ -422,7 +432,7 @@ prefill_gemm_a4_small_kernel(const __grid_constant__ CUtensorMap x_map, const Ge
     volatile uint32_t *abort_flag = tmem_slot + 1;
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const uint32_t n_tile0 = blockIdx.x * (kBN / 16u);
+    const uint32_t n_tile0 = blockIdx.x * 8u;  // 128 features = 8 storage tiles per CTA
     const uint32_t t0 = blockIdx.y * kSmallRows;  // first activation row of this CTA
 
     if (tid == 0) {
@@ -451,7 +461,7 @@ prefill_gemm_a4_small_kernel(const __grid_constant__ CUtensorMap x_map, const Ge
                     break;
                 }
                 mbar_arrive_expect_tx(&full_x[slot], kSmallXStage);
-                tma_load_2d(stages + slot * kSmallStageBytes + kBStage, &x_map, kg * kBK, t0, &full_x[slot]);
+                tma_load_2d(stages + slot * kSmallStageBytes + kSmallWStage, &x_map, kg * kBK, t0, &full_x[slot]);
                 if (++slot == kSmallStages) {
                     slot = 0;
                     phase ^= 1u;
@@ -469,7 +479,7 @@ prefill_gemm_a4_small_kernel(const __grid_constant__ CUtensorMap x_map, const Ge
                 }
                 tc_fence_after();
                 const uint32_t w_addr = smem_u32(stages + slot * kSmallStageBytes);
-                const uint32_t x_addr = w_addr + kBStage;
+                const uint32_t x_addr = w_addr + kSmallWStage;
 #pragma unroll
                 for (uint32_t k4 = 0; k4 < kBK / 16u; ++k4)
                     umma_f16(tmem_base, smem_desc_sw128(w_addr + k4 * 32u), smem_desc_sw128(x_addr + k4 * 32u), kIdescSmall,
@@ -629,7 +639,8 @@ stark_b200_status prefill_gemm_launch(const GemmArgs &a, cudaStream_t stream) {
     p.error_word = a.error_word;
     p.stop_after = tunables().gemm_stop_after;
     static SmemOptIn once, once_small;
-    const uint32_t feature_tiles = (w->row_tiles * 16u + kBN - 1u) / kBN;
+    const uint32_t width = small ? 128u : kBN;
+    const uint32_t feature_tiles = (w->row_tiles * 16u + width - 1u) / width;
     if (small) {
         if (stark_b200_status s = ensure_dynamic_smem(prefill_gemm_a4_small_kernel, (int)kSmallSmem, once_small)) return s;
         prefill_gemm_a4_small_kernel<<<dim3(feature_tiles, (a.m + kSmallRows - 1u) / kSmallRows), kGemmThreads, kSmallSmem,

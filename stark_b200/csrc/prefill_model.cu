@@ -1,8 +1,9 @@
-// Chunked prompt ingest of the dense decoder: up to 1024 rows at a time through the tensor-core contraction and
+// Batched prompt ingest of the dense decoder: up to 4096 rows at a time through the tensor-core contraction and
 // the row-wise operators, layer by layer, leaving the rows' keys and values in the paged cache exactly where the
 // one-token path would have put them.  Mirrors the reference's prefill loop
 // (crates/stark-engine/src/engine/language_model/stream/stream.rs:441-686: chunks of 1024 rows, each a batched
-// pass over the layers; the prompt's last row then goes through the sampling pass).
+// pass over the layers; the prompt's last row then goes through the sampling pass).  The rows of a pass are
+// independent, so the larger pass here changes no value.
 #include <algorithm>
 #include <cmath>
 
@@ -26,7 +27,7 @@ stark_b200_status dmalloc_rows(T **p, size_t count) {
 stark_b200_status ensure_chunk_buffers(Model *m) {
     if (m->chunk_h) return STARK_B200_OK;
     const auto &c = m->cfg;
-    const size_t rows = kPrefillChunkRows;
+    const size_t rows = kPrefillBatchRows;
     const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
     stark_b200_status st;
     if ((st = dmalloc_rows(&m->chunk_tokens, rows + 8u)) != STARK_B200_OK) return st;
@@ -62,7 +63,7 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
     const auto &c = m->cfg;
     DeviceContext *ctx = device_context();
     if (!ctx) return STARK_B200_DEVICE_FAILURE;
-    if (mrows == 0 || mrows > kPrefillChunkRows) return STARK_B200_INVALID_ARGUMENT;
+    if (mrows == 0 || mrows > kPrefillBatchRows) return STARK_B200_INVALID_ARGUMENT;
     cudaStream_t s = m->stream;
     const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
     const float scale = 1.0f / sqrtf((float)kHeadDim);
@@ -77,7 +78,7 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
     for (uint32_t l = 0; l < c.layers; ++l) {
         auto &L = m->layers[l];
         GemmArgs g{};
-        g.x_rows = kPrefillChunkRows;
+        g.x_rows = kPrefillBatchRows;
         g.m = mrows;
         g.error_word = ctx->error_word;
         // qkv = W_qkv rmsnorm(h)
@@ -140,9 +141,9 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
 // (next prompt token, this row's normalized hidden): dense_mtp.rs:462-584.
 stark_b200_status model_prefill_batched(Model *m, const uint32_t *ids, size_t rows, size_t ids_total) {
     stark_b200_status st;
-    for (size_t done = 0; done < rows; done += kPrefillChunkRows) {
+    for (size_t done = 0; done < rows; done += kPrefillBatchRows) {
         if (m->cancel_requested) return STARK_B200_CANCELLED;
-        const uint32_t mrows = (uint32_t)std::min<size_t>(kPrefillChunkRows, rows - done);
+        const uint32_t mrows = (uint32_t)std::min<size_t>(kPrefillBatchRows, rows - done);
         const uint32_t first_pos = (uint32_t)(m->position + done);
         // one extra id when there is one: the head's pairs need the token after each row
         const size_t upload = std::min<size_t>((size_t)mrows + 1u, ids_total - done);

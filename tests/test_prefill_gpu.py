@@ -100,12 +100,12 @@ def _set(name, value):
     _lib.check(_lib.load().stark_b200_set_tunable(name.encode(), int(value)), f"set_tunable {name}")
 
 
-@pytest.mark.parametrize("name,prompt_len", [("tiny", 200), ("small", 96), ("small", 1500), ("qwen3-0.6b-layers", 300),
+@pytest.mark.parametrize("name,prompt_len", [("tiny", 200), ("small", 96), ("small", 4300), ("qwen3-0.6b-layers", 300),
                                              ("qwen3-8b-layers", 1100)])
 def test_chunked_prefill_equals_row_by_row(name, prompt_len):
     """A prompt ingested in chunks on the tensor cores must leave the model where row-by-row steps leave it: the
     last row's logits inside the logits acceptance, and a cache that later tokens extend to the same effect
-    (positions past one chunk of 1024 rows included): the greedy continuation of the chunked model, replayed
+    (positions past one pass of 4096 rows included): the greedy continuation of the chunked model, replayed
     through the row-by-row model, is that model's own pick at every step up to a bf16 near-tie."""
     from stark_b200.engine import DenseModel
     from stark_b200.ops import take_device_error
@@ -123,7 +123,7 @@ def test_chunked_prefill_equals_row_by_row(name, prompt_len):
         launches = model.info().launches_issued
         model.prefill(prompt)
         issued = model.info().launches_issued - launches
-        chunks = -(-(prompt_len - 1) // 1024)
+        chunks = -(-(prompt_len - 1) // 4096)
         assert issued == chunks * (1 + 8 * cfg["layers"]) + model.info().launches_per_step   # the batched path ran
         assert take_device_error() == 0
         assert_logits_accepted(rows_logits, model.logits_bf16())
