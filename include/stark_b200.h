@@ -559,6 +559,20 @@ stark_b200_status stark_b200_moe_model_set_matrix(stark_b200_moe_model *model, u
                                                   const stark_b200_qmatrix *matrix);
 stark_b200_status stark_b200_moe_model_set_tensor(stark_b200_moe_model *model, uint32_t kind, uint32_t layer,
                                                   const void *host_data, size_t bytes);
+/* Expert parallelism over the GPUs of one node, one process per GPU (no counterpart in the reference, which runs
+ * on one device).  Every rank runs the whole token except the expert feed-forward: rank r holds experts
+ * [r * experts / ranks, (r + 1) * experts / ranks) -- its GATE_UP and DOWN banks are set AFTER ep_init and contain
+ * only those -- and computes the selected experts it owns; the owners push their output rows to every rank over
+ * NVLink peer mappings and every rank forms the mixture in selection order, so logits and tokens are the same
+ * bits on every rank and for every rank count.  ep_init (before the first token) allocates this rank's exchange
+ * region and returns its 64-byte CUDA IPC handle; ep_connect takes the handles of all ranks in rank order
+ * (handle_bytes = 64 * ranks).  Calls that run tokens are collective: every rank makes the same calls with the
+ * same tokens.  A rank whose peers do not answer within the wait (default 4 s, ep_set_wait before the first
+ * token) reports DEVICE_FAILURE and resets. */
+stark_b200_status stark_b200_moe_model_ep_init(stark_b200_moe_model *model, uint32_t rank, uint32_t ranks,
+                                               uint8_t *handle_out);
+stark_b200_status stark_b200_moe_model_ep_connect(stark_b200_moe_model *model, const uint8_t *handles, size_t handle_bytes);
+stark_b200_status stark_b200_moe_model_ep_set_wait(stark_b200_moe_model *model, uint64_t nanoseconds);
 stark_b200_status stark_b200_moe_model_reset(stark_b200_moe_model *model);
 /* Appends `count` prompt tokens to the cache without computing logits (Model::ingest). */
 stark_b200_status stark_b200_moe_model_ingest(stark_b200_moe_model *model, const uint32_t *tokens, uint32_t count);

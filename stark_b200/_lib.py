@@ -181,6 +181,9 @@ def load() -> C.CDLL:
         "stark_b200_moe_model_create": (u32, [C.POINTER(MoeConfig), C.POINTER(vp)]),
         "stark_b200_moe_model_set_matrix": (u32, [vp, u32, u32, vp]),
         "stark_b200_moe_model_set_tensor": (u32, [vp, u32, u32, vp, sz]),
+        "stark_b200_moe_model_ep_init": (u32, [vp, u32, u32, vp]),
+        "stark_b200_moe_model_ep_connect": (u32, [vp, vp, sz]),
+        "stark_b200_moe_model_ep_set_wait": (u32, [vp, u64]),
         "stark_b200_moe_model_reset": (u32, [vp]),
         "stark_b200_moe_model_ingest": (u32, [vp, vp, u32]),
         "stark_b200_moe_model_step": (u32, [vp, u32, vp, sz]),

@@ -11,6 +11,7 @@
 // the kernels here are the f32 glue between them.  One token = one CUDA graph; token and position live on
 // the device, so greedy decode chains without the host.
 #include <cmath>
+#include <cstring>
 #include <vector>
 
 #include "context.cuh"
@@ -32,8 +33,33 @@ struct MoeState {
     uint32_t chain;     // 1: consume `next` (the greedy pick of the previous step)
     uint32_t next;      // first index of the maximum of the last logits
     uint32_t position;  // rows in the cache
-    uint32_t error;     // sticky: 1 token out of range, 2 non-finite logits, 4 context exhausted
+    uint32_t error;     // sticky: 1 token out of range, 2 non-finite logits, 4 context exhausted, 8 a peer did not answer
 };
+
+// ---- expert parallelism -------------------------------------------------------------------------------------
+// One process per GPU.  Every rank runs the whole token (attention, router, read-out: replicated, so all ranks
+// hold identical activations bit for bit) except the expert feed-forward: rank r keeps experts
+// [r * E/G, (r + 1) * E/G) and computes only the selected experts it owns.  The exchange step of a layer is the
+// combine: the owner of selection slot i pushes that expert's output row into EVERY rank's receive buffer
+// (plain 64-bit stores over NVLink peer mappings, {value, ticket} packets that are valid exactly when the ticket
+// is this layer's), and the kernel that forms the mixture polls the `active` rows and adds them in selection
+// order -- the same order and the same operands as on one GPU, so the result does not depend on the rank count.
+// Receive buffers are per layer; a flag round at the end of every token keeps a fast rank from overwriting a
+// layer's packets before a slow rank has read them.  Every wait is bounded (error bit 8).
+// Region of one rank: [0, 4 KB) flags[kMaxEpRanks] written by the peers; then packets[layers][active][hidden].
+constexpr uint32_t kMaxEpRanks = 8;
+constexpr uint32_t kEpSkip = 0xffffffffu;  // expert id of a selection slot another rank owns
+struct EpRegion {
+    uint8_t *base[kMaxEpRanks];
+    uint32_t rank, ranks, local_experts;
+    unsigned long long wait_ns;
+};
+__host__ __device__ inline size_t ep_region_bytes(uint32_t layers, uint32_t active, uint32_t hidden) {
+    return 4096u + (size_t)layers * active * hidden * 8u;
+}
+__host__ __device__ inline unsigned long long *ep_packets(uint8_t *base, uint32_t layer, uint32_t active, uint32_t hidden) {
+    return reinterpret_cast<unsigned long long *>(base + 4096u) + (size_t)layer * active * hidden;
+}
 
 constexpr uint32_t kAttnSplits = 16, kAttnWarps = 8, kMoeMaxAttnSplits = 64;
 constexpr uint32_t kFinishCtas = 64;  // CTAs of the arg-max over the logits
@@ -324,7 +350,9 @@ __global__ void __launch_bounds__(128) moe_attention_merge_kernel(const float *p
 // the same plus `experts`, which addresses the up half of a fused [gate; up] bank.
 __global__ void __launch_bounds__(256) moe_router_select_kernel(const float *w, const float *x, float *scores,
                                                                 uint32_t hidden, uint32_t experts, uint32_t active,
-                                                                uint32_t *ids, float *probs, uint32_t *arrivals) {
+                                                                uint32_t *ids, float *probs, uint32_t *arrivals,
+                                                                uint32_t *ids_global, uint32_t ep_first,
+                                                                uint32_t ep_local) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[32];
@@ -379,8 +407,16 @@ __global__ void __launch_bounds__(256) moe_router_select_kernel(const float *w, 
     for (uint32_t r = 0; r < active; ++r) sum += __shfl_sync(0xffffffffu, p, r);
     if (lane < active) {
         probs[lane] = p / sum;
-        ids[lane] = chosen;
-        ids[active + lane] = chosen + experts;
+        if (ep_local) {
+            // expert parallel: the bank holds this rank's experts only; slots of other ranks are skipped
+            const bool mine = chosen >= ep_first && chosen < ep_first + ep_local;
+            ids[lane] = mine ? chosen - ep_first : kEpSkip;
+            ids[active + lane] = mine ? chosen - ep_first + ep_local : kEpSkip;
+            ids_global[lane] = chosen;
+        } else {
+            ids[lane] = chosen;
+            ids[active + lane] = chosen + experts;
+        }
     }
 }
 
@@ -415,6 +451,107 @@ __global__ void __launch_bounds__(1024) moe_add_norm_kernel(float *x, const floa
     const float mean = block_sum<1024>(s, scratch) / (float)n;
     const float scale = 1.0f / sqrtf(mean + eps);
     for (uint32_t i = threadIdx.x; i < n; i += 1024u) out[i] = x[i] * scale * w[i];  // this thread's own writes
+}
+
+// Expert parallel: the rows of the selection slots this rank owns go to every rank (itself included).
+__global__ void __launch_bounds__(256) moe_ep_push_kernel(EpRegion g, const float *rows, const uint32_t *ids, uint32_t layer,
+                                                          uint32_t layers, uint32_t active, uint32_t n,
+                                                          const uint32_t *ep_tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t slot = blockIdx.x;
+    if (ids[slot] == kEpSkip) return;
+    const uint32_t ticket = __ldcg(ep_tokens) * layers + layer + 1u;
+    const float *row = rows + (size_t)slot * n;
+    for (uint32_t i = threadIdx.x; i < n; i += 256u) {
+        const unsigned long long packet = ((unsigned long long)ticket << 32) | __float_as_uint(row[i]);
+        for (uint32_t r = 0; r < g.ranks; ++r)
+            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(ep_packets(g.base[r], layer, active, n) + (size_t)slot * n + i),
+                         "l"(packet)
+                         : "memory");
+    }
+}
+
+// moe_add_norm_kernel with the expert rows taken from this rank's receive buffer: x += sum_r probs[r] * row_r in
+// selection order, then the norm.  A row is there when its packets carry this layer's ticket.
+__global__ void __launch_bounds__(1024) moe_ep_mix_norm_kernel(float *x, const unsigned long long *packets, const float *probs,
+                                                               uint32_t active, const float *w, float *out, uint32_t n,
+                                                               float eps, const uint32_t *ep_tokens, uint32_t layer,
+                                                               uint32_t layers, unsigned long long wait_ns, MoeState *st) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float scratch[32];
+    __shared__ float sp[32];
+    if (threadIdx.x < active) sp[threadIdx.x] = probs[threadIdx.x];
+    __syncthreads();
+    const uint32_t ticket = __ldcg(ep_tokens) * layers + layer + 1u;
+    const unsigned long long t0 = global_ns();
+    float s = 0.0f;
+    for (uint32_t i = threadIdx.x; i < n; i += 1024u) {
+        float r = 0.0f;
+        for (uint32_t e0 = 0; e0 < active; e0 += 8u) {  // eight rows per trip to memory
+            unsigned long long q[8];
+            uint32_t spins = 0;
+            for (;;) {
+                bool all = true;
+#pragma unroll
+                for (uint32_t j = 0; j < 8u; ++j) {
+                    if (e0 + j < active) {
+                        asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(q[j]) : "l"(packets + (size_t)(e0 + j) * n + i) : "memory");
+                    } else {
+                        q[j] = (unsigned long long)ticket << 32;
+                    }
+                }
+#pragma unroll
+                for (uint32_t j = 0; j < 8u; ++j) all = all && (uint32_t)(q[j] >> 32) == ticket;
+                if (all) break;
+                if (++spins > 8u) {
+                    __nanosleep(64);
+                    if (global_ns() - t0 > wait_ns) {  // a rank is missing: report and go on with what is there
+                        atomicOr(&st->error, 8u);
+                        break;
+                    }
+                }
+            }
+#pragma unroll
+            for (uint32_t j = 0; j < 8u; ++j)
+                if (e0 + j < active) r += sp[e0 + j] * __uint_as_float((uint32_t)q[j]);
+        }
+        const float v = x[i] + r;
+        x[i] = v;
+        s += v * v;
+    }
+    if (!w) return;
+    const float mean = block_sum<1024>(s, scratch) / (float)n;
+    const float scale = 1.0f / sqrtf(mean + eps);
+    for (uint32_t i = threadIdx.x; i < n; i += 1024u) out[i] = x[i] * scale * w[i];
+}
+
+// End of a token under expert parallelism: every rank tells every rank that it is through with the token's
+// receive buffers, waits for all of them, and only then advances the counter the tickets are made of.
+__global__ void __launch_bounds__(32) moe_ep_token_barrier_kernel(EpRegion g, uint32_t *ep_tokens, MoeState *st) {
+    const uint32_t lane = threadIdx.x;
+    const uint32_t done = *ep_tokens + 1u;
+    if (lane < g.ranks) {
+        uint32_t *peer_flag = reinterpret_cast<uint32_t *>(g.base[lane]) + g.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_flag), "r"(done) : "memory");
+        const uint32_t *mine = reinterpret_cast<const uint32_t *>(g.base[g.rank]) + lane;
+        const unsigned long long t0 = global_ns();
+        for (uint32_t spins = 0;; ++spins) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if ((int32_t)(seen - done) >= 0) break;
+            if (spins > 8u) {
+                __nanosleep(128);
+                if (global_ns() - t0 > g.wait_ns) {
+                    atomicOr(&st->error, 8u);
+                    break;
+                }
+            }
+        }
+    }
+    __syncwarp();
+    if (lane == 0) *ep_tokens = done;
 }
 
 // gate[i] = silu(gate[i]) * up[i]  (qwen.rs:889-891, math.rs:5-16)
@@ -530,6 +667,14 @@ struct MoeModel {
     uint32_t nodes = 0;
     uint32_t position = 0;  // host mirror of the device position
     bool poisoned = false;
+    // expert parallelism (ep.ranks == 0: one GPU)
+    EpRegion ep{};
+    uint8_t *ep_local = nullptr;      // this rank's exchange region
+    uint32_t *ep_tokens = nullptr;    // tokens finished, never reset: what the tickets are made of
+    uint32_t *ids_global = nullptr;   // [layers][active] the selected experts in the model's numbering
+    bool ep_connected = false;
+    std::vector<void *> ep_opened;    // peers' regions opened through IPC
+    uint32_t local_experts() const { return ep.ranks ? ep.local_experts : cfg.experts; }
 
     size_t norm_stride() const { return 2u * (size_t)cfg.hidden + 2u * cfg.head_dim; }
     float *norm(uint32_t kind, uint32_t layer) const {
@@ -629,8 +774,11 @@ stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
         SB_TRY(qmv_rows_launch(m->o[l], m->att, 0, m->update, 1, nullptr, STARK_B200_F32, s, pdl));
         SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->update, nullptr, 1u,
                           m->norm(STARK_B200_MOE_TENSOR_FFN_NORM, l), m->n, H, c.rms_eps));
+        const bool ep = m->ep.ranks > 1u;
         SB_TRY(moe_launch(moe_router_select_kernel, c.experts, 256, pdl, s, m->router + (size_t)l * c.experts * H, m->n,
-                          m->scores, H, c.experts, A, ids, m->probs, m->arrivals));
+                          m->scores, H, c.experts, A, ids, m->probs, m->arrivals,
+                          ep ? m->ids_global + (size_t)l * A : nullptr, ep ? m->ep.rank * m->ep.local_experts : 0u,
+                          ep ? m->ep.local_experts : 0u));
         SB_TRY(qmv_rows_launch(m->gate_up[l], m->n, 0, m->gate_out, 2u * A, ids, STARK_B200_F32, s, pdl));
         if (m->down[l]->format == kFmtQ4_K) {  // the gated activation is formed while the down projection stages its input
             SB_TRY(q4kt_launch(m->down[l], m->gate_out, I, m->expert_out, A, ids, STARK_B200_F32, s, pdl,
@@ -643,12 +791,19 @@ stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
         // the mixture, the residual add and the next norm: the next layer's, or the final one before the logits
         const float *next = l + 1u < c.layers ? m->norm(STARK_B200_MOE_TENSOR_ATTN_NORM, l + 1u)
                                               : (want_logits ? m->norm(STARK_B200_MOE_TENSOR_FINAL_NORM, 0) : nullptr);
-        SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->expert_out, m->probs, A, next, m->n, H, c.rms_eps));
+        if (ep) {
+            SB_TRY(moe_launch(moe_ep_push_kernel, A, 256, pdl, s, m->ep, m->expert_out, ids, l, c.layers, A, H, m->ep_tokens));
+            SB_TRY(moe_launch(moe_ep_mix_norm_kernel, 1, 1024, pdl, s, m->x, ep_packets(m->ep_local, l, A, H), m->probs, A,
+                              next, m->n, H, c.rms_eps, m->ep_tokens, l, c.layers, m->ep.wait_ns, m->state));
+        } else {
+            SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->expert_out, m->probs, A, next, m->n, H, c.rms_eps));
+        }
     }
     if (want_logits) SB_TRY(qmv_rows_launch(m->output, m->n, 0, m->logits, 1, nullptr, STARK_B200_F32, s, pdl));
     // the attention partials are free by now: scratch for the per-CTA maxima
     SB_TRY(moe_launch(moe_finish_kernel, want_logits ? kFinishCtas : 1u, 1024, pdl, s, m->state,
                       want_logits ? m->logits : nullptr, c.vocab, m->part, m->arrivals + 1));
+    if (m->ep.ranks > 1u) SB_TRY(moe_launch(moe_ep_token_barrier_kernel, 1, 32, false, s, m->ep, m->ep_tokens, m->state));
     return STARK_B200_OK;
 }
 
@@ -720,6 +875,8 @@ void moe_free(MoeModel *m) {
         if (g) cudaGraphExecDestroy(g);
     cudaFree(m->token_table), cudaFree(m->norms), cudaFree(m->router), cudaFree(m->keys), cudaFree(m->values);
     cudaFree(m->work), cudaFree(m->ids), cudaFree(m->arrivals), cudaFree(m->state);
+    for (void *p : m->ep_opened) cudaIpcCloseMemHandle(p);
+    cudaFree(m->ep_local), cudaFree(m->ep_tokens), cudaFree(m->ids_global);
     if (m->stream) cudaStreamDestroy(m->stream);
     delete m;
 }
@@ -804,10 +961,10 @@ stark_b200_status stark_b200_moe_model_set_matrix(stark_b200_moe_model *model, u
         case STARK_B200_MOE_MAT_QKV: fits = q8 && banks == 1u && q->rows == QD + 2u * KD && q->columns == c.hidden; break;
         case STARK_B200_MOE_MAT_O: fits = q8 && banks == 1u && q->rows == c.hidden && q->columns == QD; break;
         case STARK_B200_MOE_MAT_GATE_UP:
-            fits = q4 && banks == 2u * c.experts && q->rows == c.expert_intermediate && q->columns == c.hidden;
+            fits = q4 && banks == 2u * m->local_experts() && q->rows == c.expert_intermediate && q->columns == c.hidden;
             break;
         case STARK_B200_MOE_MAT_DOWN:
-            fits = q4 && banks == c.experts && q->rows == c.hidden && q->columns == c.expert_intermediate;
+            fits = q4 && banks == m->local_experts() && q->rows == c.hidden && q->columns == c.expert_intermediate;
             break;
         default: fits = q8 && banks == 1u && q->rows == c.vocab && q->columns == c.hidden; break;
     }
@@ -852,6 +1009,64 @@ stark_b200_status stark_b200_moe_model_set_tensor(stark_b200_moe_model *model, u
     return STARK_B200_OK;
 }
 
+stark_b200_status stark_b200_moe_model_ep_init(stark_b200_moe_model *model, uint32_t rank, uint32_t ranks,
+                                               uint8_t *handle_out) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size is part of the interface");
+    MoeModel *m = reinterpret_cast<MoeModel *>(model);
+    if (!m || !handle_out) return STARK_B200_INVALID_ARGUMENT;
+    if (m->ep_local || m->warmed[0] || m->warmed[1]) return STARK_B200_INVALID_STATE;
+    for (uint32_t l = 0; l < m->cfg.layers; ++l)  // the banks are checked against the rank's share: set them afterwards
+        if (m->gate_up[l] || m->down[l]) return STARK_B200_INVALID_STATE;
+    const auto &c = m->cfg;
+    if (ranks < 2u || ranks > kMaxEpRanks || rank >= ranks || c.experts % ranks != 0) return STARK_B200_INVALID_ARGUMENT;
+    DeviceScope scope(m->device);
+    const size_t bytes = ep_region_bytes(c.layers, c.active_experts, c.hidden);
+    SB_CUDA(cudaMalloc(&m->ep_local, bytes));
+    SB_CUDA(cudaMemset(m->ep_local, 0, bytes));
+    SB_CUDA(cudaMalloc(&m->ep_tokens, 16u));
+    SB_CUDA(cudaMemset(m->ep_tokens, 0, 16u));
+    SB_CUDA(cudaMalloc(&m->ids_global, (size_t)c.layers * c.active_experts * 4u));
+    SB_CUDA(cudaMemset(m->ids_global, 0, (size_t)c.layers * c.active_experts * 4u));
+    SB_CUDA(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t handle;
+    SB_CUDA(cudaIpcGetMemHandle(&handle, m->ep_local));
+    memcpy(handle_out, &handle, 64);
+    m->ep.rank = rank;
+    m->ep.ranks = ranks;
+    m->ep.local_experts = c.experts / ranks;
+    m->ep.wait_ns = 4000000000ull;
+    m->ep.base[rank] = m->ep_local;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_moe_model_ep_connect(stark_b200_moe_model *model, const uint8_t *handles, size_t handle_bytes) {
+    MoeModel *m = reinterpret_cast<MoeModel *>(model);
+    if (!m || !handles) return STARK_B200_INVALID_ARGUMENT;
+    if (!m->ep_local || m->ep_connected) return STARK_B200_INVALID_STATE;
+    if (handle_bytes != (size_t)m->ep.ranks * 64u) return STARK_B200_INVALID_ARGUMENT;
+    DeviceScope scope(m->device);
+    for (uint32_t r = 0; r < m->ep.ranks; ++r) {
+        if (r == m->ep.rank) continue;
+        cudaIpcMemHandle_t handle;
+        memcpy(&handle, handles + (size_t)r * 64u, 64);
+        void *p = nullptr;
+        SB_CUDA(cudaIpcOpenMemHandle(&p, handle, cudaIpcMemLazyEnablePeerAccess));
+        m->ep_opened.push_back(p);
+        m->ep.base[r] = static_cast<uint8_t *>(p);
+    }
+    m->ep_connected = true;
+    return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_moe_model_ep_set_wait(stark_b200_moe_model *model, uint64_t nanoseconds) {
+    MoeModel *m = reinterpret_cast<MoeModel *>(model);
+    if (!m) return STARK_B200_INVALID_ARGUMENT;
+    if (!m->ep_local || m->warmed[0] || m->warmed[1]) return STARK_B200_INVALID_STATE;
+    if (nanoseconds < 1000ull || nanoseconds > 600000000000ull) return STARK_B200_INVALID_ARGUMENT;
+    m->ep.wait_ns = nanoseconds;
+    return STARK_B200_OK;
+}
+
 stark_b200_status stark_b200_moe_model_reset(stark_b200_moe_model *model) {
     MoeModel *m = reinterpret_cast<MoeModel *>(model);
     if (!m) return STARK_B200_INVALID_ARGUMENT;
@@ -861,7 +1076,7 @@ stark_b200_status stark_b200_moe_model_reset(stark_b200_moe_model *model) {
 
 static stark_b200_status moe_ready(MoeModel *m, uint32_t tokens) {
     if (!m) return STARK_B200_INVALID_ARGUMENT;
-    if (!m->complete()) return STARK_B200_INVALID_STATE;
+    if (!m->complete() || (m->ep_local && !m->ep_connected)) return STARK_B200_INVALID_STATE;
     if (m->poisoned) return STARK_B200_RELOAD_REQUIRED;
     if ((uint64_t)m->position + tokens > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
     return STARK_B200_OK;
@@ -943,7 +1158,11 @@ stark_b200_status stark_b200_moe_model_last_experts(stark_b200_moe_model *model,
     DeviceScope scope(m->device);
     SB_CUDA(cudaStreamSynchronize(m->stream));
     const size_t a = m->cfg.active_experts;
-    SB_CUDA(cudaMemcpy2D(ids_host, a * 4u, m->ids, 2u * a * 4u, a * 4u, m->cfg.layers, cudaMemcpyDeviceToHost));
+    if (m->ep.ranks > 1u) {
+        SB_CUDA(cudaMemcpy(ids_host, m->ids_global, count * 4u, cudaMemcpyDeviceToHost));
+    } else {
+        SB_CUDA(cudaMemcpy2D(ids_host, a * 4u, m->ids, 2u * a * 4u, a * 4u, m->cfg.layers, cudaMemcpyDeviceToHost));
+    }
     return STARK_B200_OK;
 }
 
@@ -957,7 +1176,7 @@ stark_b200_status stark_b200_moe_model_position(const stark_b200_moe_model *mode
 stark_b200_status stark_b200_moe_model_launches_per_token(const stark_b200_moe_model *model, uint32_t *out_launches) {
     const MoeModel *m = reinterpret_cast<const MoeModel *>(model);
     if (!m || !out_launches) return STARK_B200_INVALID_ARGUMENT;
-    *out_launches = m->nodes ? m->nodes : 4u + 10u * m->cfg.layers;
+    *out_launches = m->nodes ? m->nodes : 4u + 10u * m->cfg.layers + (m->ep.ranks > 1u ? m->cfg.layers + 1u : 0u);
     return STARK_B200_OK;
 }
 

@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(kQ4Warps * 32) qmv_b8t_kernel(const B8Params p
     uint32_t expert = 0;
     if (p.expert_ids) {
         expert = p.expert_ids[b];
+        if (expert == 0xffffffffu) return;  // expert parallel: another rank owns this selection slot (whole CTA, before any barrier)
         if (expert >= p.experts) expert = 0;  // moe_gather_rows: an invalid id falls back to expert 0 (moe.rs:84-101)
     }
     const uint8_t *base = p.data + (size_t)expert * p.expert_bytes;

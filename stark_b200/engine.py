@@ -389,21 +389,56 @@ def reusable_prefix_rows(previous_prompt_len: int, common_prefix: int, new_promp
     return (min(common_prefix, retained, limit) // chunk) * chunk
 
 
+class ExpertParallel:
+    """Rank layout of an expert-parallel group plus the one host-side collective the engine needs:
+    ``all_gather(bytes) -> [bytes per rank]`` (for example ``torch.distributed.all_gather_object``)."""
+
+    def __init__(self, rank: int, ranks: int, all_gather, wait_ns: int | None = None):
+        self.rank, self.ranks, self.all_gather, self.wait_ns = int(rank), int(ranks), all_gather, wait_ns
+
+
+def expert_shard(bank: np.ndarray, rank: int, ranks: int) -> np.ndarray:
+    """Rank ``rank``'s experts of a bank whose first axis counts experts: the contiguous block
+    ``[rank * E / ranks, (rank + 1) * E / ranks)``."""
+    experts = bank.shape[0]
+    if experts % ranks:
+        raise ValueError("the expert count must be a multiple of the rank count")
+    per = experts // ranks
+    return bank[rank * per:(rank + 1) * per]
+
+
+def expert_owner(expert: int, experts: int, ranks: int) -> int:
+    return int(expert) // (experts // ranks)
+
+
 class MoEModel:
     """A routed-expert decoder on the conventions of the reference's hybrid host path (f32 activations and
     logits, GGUF Q8_0 attention / token table / output, Q4_K expert banks), with the surface of
     ``hybrid::Model`` (crates/stark-engine/src/engine/hybrid/mod.rs:347,863,897,990): ``load``, ``reset``,
     ``ingest``, ``step -> logits``.  Any failing call leaves the model reset, as the reference does."""
 
-    def __init__(self, cfg: dict, context_tokens: int):
+    def __init__(self, cfg: dict, context_tokens: int, ep: "ExpertParallel | None" = None):
         self.cfg = dict(cfg)
         self.context_tokens = int(context_tokens)
+        self.ep = ep if ep is not None and ep.ranks > 1 else None
         self._h = C.c_void_p()
         self._matrices = []  # the handle borrows them
         c = _lib.MoeConfig(C.sizeof(_lib.MoeConfig), cfg["vocab"], cfg["hidden"], cfg["layers"], cfg["q_heads"],
                            cfg["kv_heads"], cfg["head_dim"], cfg["experts"], cfg["active"], cfg["inter"],
                            self.context_tokens, cfg["eps"], cfg["rope_theta"])
         check(_lib.load().stark_b200_moe_model_create(C.byref(c), C.byref(self._h)), "moe_model_create")
+        if self.ep is not None:
+            # collective: every rank allocates its exchange region, the 64-byte handles travel over the host-side
+            # collective, every rank maps every other rank's region
+            if cfg["experts"] % self.ep.ranks:
+                raise ValueError("the expert count must be a multiple of the rank count")
+            handle = (C.c_uint8 * 64)()
+            check(_lib.load().stark_b200_moe_model_ep_init(self._h, self.ep.rank, self.ep.ranks, handle), "moe_model_ep_init")
+            if self.ep.wait_ns is not None:
+                check(_lib.load().stark_b200_moe_model_ep_set_wait(self._h, int(self.ep.wait_ns)), "moe_model_ep_set_wait")
+            handles = b"".join(self.ep.all_gather(bytes(handle)))
+            buf = (C.c_uint8 * len(handles)).from_buffer_copy(handles)
+            check(_lib.load().stark_b200_moe_model_ep_connect(self._h, buf, len(handles)), "moe_model_ep_connect")
 
     def _matrix(self, kind: int, layer: int, blocks: np.ndarray, ggml_kind: int, rows: int, columns: int,
                 experts: int = 0):
@@ -425,9 +460,14 @@ class MoEModel:
         Q8_0, Q4_K = 8, 12
         self._matrix(L.MOE_MAT_QKV, layer, w["qkv"], Q8_0, qd + 2 * kd, c["hidden"])
         self._matrix(L.MOE_MAT_O, layer, w["o"], Q8_0, c["hidden"], qd)
-        gate_up = np.concatenate([np.asarray(w["gate"], np.uint8).reshape(-1), np.asarray(w["up"], np.uint8).reshape(-1)])
-        self._matrix(L.MOE_MAT_GATE_UP, layer, gate_up, Q4_K, c["inter"], c["hidden"], 2 * c["experts"])
-        self._matrix(L.MOE_MAT_DOWN, layer, w["down"], Q4_K, c["hidden"], c["inter"], c["experts"])
+        gate, up, down = (np.asarray(w[k], np.uint8).reshape(c["experts"], -1) for k in ("gate", "up", "down"))
+        local = c["experts"]
+        if self.ep is not None:  # this rank's contiguous share of the expert banks
+            gate, up, down = (expert_shard(a, self.ep.rank, self.ep.ranks) for a in (gate, up, down))
+            local = c["experts"] // self.ep.ranks
+        gate_up = np.concatenate([gate.reshape(-1), up.reshape(-1)])
+        self._matrix(L.MOE_MAT_GATE_UP, layer, gate_up, Q4_K, c["inter"], c["hidden"], 2 * local)
+        self._matrix(L.MOE_MAT_DOWN, layer, down.reshape(-1), Q4_K, c["hidden"], c["inter"], local)
         self._tensor(L.MOE_ROUTER, layer, np.asarray(w["router"], np.float32))
         for kind, name in ((L.MOE_ATTN_NORM, "attn_norm"), (L.MOE_FFN_NORM, "ffn_norm"), (L.MOE_Q_NORM, "q_norm"),
                            (L.MOE_K_NORM, "k_norm")):
@@ -440,17 +480,29 @@ class MoEModel:
         self._tensor(L.MOE_FINAL_NORM, 0, np.asarray(final_norm, np.float32))
 
     @classmethod
-    def load(cls, cfg: dict, weights: dict, context_tokens: int) -> "MoEModel":
-        m = cls(cfg, context_tokens)
+    def load(cls, cfg: dict, weights: dict, context_tokens: int, ep: "ExpertParallel | None" = None) -> "MoEModel":
+        """With ``ep`` the call is collective: every rank passes the whole model's weights and keeps the experts
+        it owns (``expert_shard``); attention, router, token table and read-out are replicated."""
+        m = cls(cfg, context_tokens, ep)
         m.set_globals(weights["token_table"], weights["output"], weights["final_norm"])
         for layer, w in enumerate(weights["layers"]):
             m.set_layer(layer, w)
         return m
 
+    def _line_up(self) -> None:
+        """Expert parallel: the calls that start a request are collective.  Ranks meet on the host first, so that
+        no rank's kernels sit waiting for a peer that is still busy with something else (the device-side wait is
+        bounded and would report a failure).  Single steps do not meet: ranks that step together drift by host
+        jitter only."""
+        if self.ep is not None:
+            self.ep.all_gather(b"")
+
     def reset(self) -> None:
+        self._line_up()
         check(_lib.load().stark_b200_moe_model_reset(self._h), "moe_model_reset")
 
     def ingest(self, tokens) -> None:
+        self._line_up()
         t = np.ascontiguousarray(tokens, np.uint32).reshape(-1)
         check(_lib.load().stark_b200_moe_model_ingest(self._h, t.ctypes.data, t.size), "moe_model_ingest")
 
@@ -461,6 +513,7 @@ class MoEModel:
         return out
 
     def generate_greedy(self, first: int, steps: int) -> np.ndarray:
+        self._line_up()
         out = np.empty(steps, np.uint32)
         check(_lib.load().stark_b200_moe_model_generate_greedy(self._h, int(first), steps, out.ctypes.data),
               "moe_model_generate_greedy")
