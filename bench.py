@@ -316,13 +316,16 @@ def moe_cpu_sample(cfg: dict, weights: dict, prompt: np.ndarray, prompt_rows: in
 
 
 def run_moe(args, wl) -> None:
-    """Greedy decode of a routed-expert decoder on one GPU (the path has no multi-GPU form yet)."""
+    """Greedy decode of a routed-expert decoder: one GPU, or expert parallel over the ranks of the launch (one
+    token stream; every rank runs attention, router and read-out, the experts are divided: strong scaling)."""
     import torch
 
-    from stark_b200.engine import MoEModel
+    from stark_b200.engine import ExpertParallel, MoEModel
     cfg = S.MOE_CONFIGS[wl["cfg"]]
     steps, warmup = args.steps, max(args.warmup, 3)
-    if int(os.environ.get("RANK", "0")) != 0:
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference" and rank != 0:
         return
     weights = moe_weights_cycled(cfg, args.seed)
     prompt = S.prompt(cfg, wl["prompt"], seed=args.seed + 1)
@@ -341,16 +344,29 @@ def run_moe(args, wl) -> None:
             "cpu_baseline": base,
             "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
         return
-    torch.cuda.set_device(0)
+    torch.cuda.set_device(local)
+    ep = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        host_group = dist.new_group(backend="gloo")  # moves the 64-byte buffer handles and lines requests up
+
+        def all_gather(blob: bytes):
+            out = [None] * world
+            dist.all_gather_object(out, blob, group=host_group)
+            return out
+        ep = ExpertParallel(rank, world, all_gather)
     # rows of cache: the prompt, the warm-up and timed steps, and the end-to-end loop after them
-    model = MoEModel.load(cfg, weights, max(wl["context"], wl["prompt"] + warmup + steps + min(steps, 64) + 8))
+    model = MoEModel.load(cfg, weights, max(wl["context"], wl["prompt"] + warmup + steps + min(steps, 64) + 8), ep=ep)
     model.ingest(prompt[:-1])
     first = int(model.step(int(prompt[-1])).argmax())
     picks = model.generate_greedy(first, warmup)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     stream = torch.cuda.ExternalStream(model.stream)  # events go on the stream the decoder launches on
-    with ClockSampler(0) as clocks:
+    with ClockSampler(local) as clocks:
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         e0.record(stream)
         out = model.generate_greedy(int(picks[-1]), steps)
         e1.record(stream)
@@ -363,15 +379,21 @@ def run_moe(args, wl) -> None:
             tok = int(model.step(tok).argmax())
         e2e = (time.perf_counter() - t0) / e2e_steps
     ms = e0.elapsed_time(e1) / steps
+    if world > 1:  # a token is done when the slowest rank is
+        t = torch.tensor([ms, e2e], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e = t.tolist()
     rows = wl["prompt"] + warmup + steps / 2
     per = moe_step_bytes(model, cfg, rows)
     peak, kind = peaks()
     line = {
-        "metric": "decode tokens/s", "value": 1e3 / ms, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "metric": "decode tokens/s", "value": 1e3 / ms, "unit": "tok/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
         "config": {"workload": f"{wl['cfg']} routed-expert decoder, GGUF Q8_0 attention + Q4_K experts, batch 1, "
                                f"{wl['prompt']}-token prompt, greedy decode",
+                   "parallelism": "one GPU" if world == 1 else f"ep{world}: experts divided over the ranks, attention, "
+                                                               "router and read-out on every rank, rows exchanged over peer memory",
                    "l2": f"{per / 1e6:.0f} MB read per step, larger than L2" if per > 126e6 else
                          f"{per / 1e6:.0f} MB read per step (fits in L2: a test shape, not a bench line)"},
         "e2e": {"value": 1.0 / e2e, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4 * cfg["vocab"]},
@@ -379,10 +401,16 @@ def run_moe(args, wl) -> None:
         "roofline": {"bound": "hbm", "achieved": per / ms / 1e6, "peak": peak, "unit": "GB/s",
                      "frac": per / ms / 1e6 / peak, "traffic": None, "peak_kind": kind},
     }
-    if not args.no_cpu_baseline:
+    if world > 1:
+        line["roofline"]["note"] = "per GPU: replicated matrices and cache plus the rank's mean share of the selected experts"
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = moe_cpu_sample(cfg, weights, prompt, min(wl["prompt"], 16), 2, threads)
     model.close()
-    print(json.dumps(line))
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
 
 
 def mtp_round_bytes(cfg: dict, drafts: int, context_rows: float) -> float:

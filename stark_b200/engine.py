@@ -549,8 +549,9 @@ class MoEModel:
         qd, kd = c["q_heads"] * c["head_dim"], c["kv_heads"] * c["head_dim"]
         q8 = lambda n: n // 32 * 34
         q4 = lambda n: n // 256 * 144
+        ranks = self.ep.ranks if self.ep is not None else 1   # a rank reads the selected experts it owns: active / ranks on average
         per_layer = q8((qd + 2 * kd) * c["hidden"]) + q8(c["hidden"] * qd) + 4 * c["experts"] * c["hidden"] \
-            + 3 * c["active"] * q4(c["inter"] * c["hidden"])
+            + 3 * c["active"] * q4(c["inter"] * c["hidden"]) // ranks
         return c["layers"] * per_layer + q8(c["vocab"] * c["hidden"]) + q8(c["hidden"])
 
     def close(self) -> None:
