@@ -433,7 +433,8 @@ def run_mtp(args, wl) -> None:
     from stark_b200.ops import take_device_error
     assert int(os.environ.get("WORLD_SIZE", "1")) == 1, "the speculative workload runs on one GPU"
     cfg = S.CONFIGS[wl["cfg"]]
-    drafts, p_accept = wl["drafts"], wl["accept"]
+    drafts = wl["drafts"] if args.drafts < 0 else min(args.drafts, 7)
+    p_accept = wl["accept"] if args.accept < 0 else min(args.accept, 1.0)
     rounds, warmup = args.steps, max(args.warmup, 3)
     repeats = args.repeats if args.repeats > 0 else max(5, min(64, -(-160 // max(rounds, 1))))
     weights = S.dense_weights(cfg, seed=args.seed)
@@ -577,6 +578,8 @@ def main() -> None:
     ap.add_argument("--rows", type=int, default=4096, help="matvec workload only")
     ap.add_argument("--columns", type=int, default=4096, help="matvec workload only")
     ap.add_argument("--m", type=int, default=1024, help="gemm workload only: rows of activations")
+    ap.add_argument("--drafts", type=int, default=-1, help="speculative workloads only: proposals per round (0..7)")
+    ap.add_argument("--accept", type=float, default=-1.0, help="speculative workloads only: acceptance probability")
     ap.add_argument("--format", default="affine4", choices=["affine4", "affine8", "q8_0", "q4_k"],
                     help="matvec workload only")
     args = ap.parse_args()

@@ -472,6 +472,10 @@ stark_b200_status stark_b200_read_trace(stark_b200_model *model, uint64_t *dst, 
  *                proposal i is accepted iff bit i of accept_mask is set (a timing aid with a fixed work mix; the
  *                reference's acceptance is data dependent, crates/stark-generate/src/hybrid/mtp.rs:226-263).
  *                tokens[0 .. count) are the committed tokens (tokens[0] is the pending token passed in).
+ *   mtp_round_lookup  the same round with `count` proposals supplied by the caller instead of the head: tokens
+ *                copied from the request's own context (prompt lookup, crates/stark-engine/src/engine/hybrid/
+ *                mtp_lookup.rs:96-121; `RoundPlan::Lookup` in mtp_policy.rs:286-301).  No head step runs; the head's
+ *                cache gets the pending row written instead.
  *   mtp_readout_row_f32  full-vocabulary logits of row `row` of the last round's target pass, for a host-side
  *                sampler (valid until the next round).
  */
@@ -490,6 +494,9 @@ typedef struct stark_b200_mtp_round_result {
 stark_b200_status stark_b200_mtp_initial(stark_b200_model *model, uint32_t *out_pending);
 stark_b200_status stark_b200_mtp_round(stark_b200_model *model, uint32_t pending, uint32_t drafts, uint32_t policy,
                                        uint32_t accept_mask, stark_b200_mtp_round_result *out);
+stark_b200_status stark_b200_mtp_round_lookup(stark_b200_model *model, uint32_t pending, const uint32_t *proposals,
+                                              uint32_t count, uint32_t policy, uint32_t accept_mask,
+                                              stark_b200_mtp_round_result *out);
 stark_b200_status stark_b200_mtp_readout_row_f32(stark_b200_model *model, uint32_t row, float *dst, size_t count);
 
 /* Launch-shape settings of the decode kernels (no counterpart in the reference, whose Metal pipelines

@@ -174,6 +174,7 @@ def load() -> C.CDLL:
         "stark_b200_model_stream": (u32, [vp, C.POINTER(vp)]),
         "stark_b200_mtp_initial": (u32, [vp, C.POINTER(u32)]),
         "stark_b200_mtp_round": (u32, [vp, u32, u32, u32, u32, C.POINTER(MtpRoundResult)]),
+        "stark_b200_mtp_round_lookup": (u32, [vp, u32, vp, u32, u32, u32, C.POINTER(MtpRoundResult)]),
         "stark_b200_mtp_readout_row_f32": (u32, [vp, u32, vp, sz]),
         "stark_b200_set_tunable": (u32, [C.c_char_p, u32]),
         "stark_b200_model_recapture": (u32, [vp]),

@@ -471,6 +471,16 @@ stark_b200_status stark_b200_mtp_round(stark_b200_model *model, uint32_t pending
     return mtp_round(M(model), pending, drafts, policy, accept_mask, out);
 }
 
+stark_b200_status stark_b200_mtp_round_lookup(stark_b200_model *model, uint32_t pending, const uint32_t *proposals,
+                                              uint32_t count, uint32_t policy, uint32_t accept_mask,
+                                              stark_b200_mtp_round_result *out) {
+    if (!model || !out || (count && !proposals)) return STARK_B200_INVALID_ARGUMENT;
+    if (out->struct_size != sizeof(stark_b200_mtp_round_result) || out->abi_version != STARK_B200_ABI_VERSION)
+        return STARK_B200_ABI_MISMATCH;
+    static const uint32_t none = 0;
+    return mtp_round(M(model), pending, count, policy, accept_mask, out, count ? proposals : &none);
+}
+
 stark_b200_status stark_b200_mtp_readout_row_f32(stark_b200_model *model, uint32_t row, float *dst, size_t count) {
     if (!model || !dst) return STARK_B200_INVALID_ARGUMENT;
     return mtp_readout_row_f32(M(model), row, dst, count);

@@ -139,7 +139,7 @@ stark_b200_status mtp_after_prompt(Model *m);
 // a prompt continued at a position > 0: the pair (chunk_tokens[0], last hidden) becomes the head's next cache row
 stark_b200_status mtp_prime_continue(Model *m);
 stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_t policy, uint32_t accept_mask,
-                            stark_b200_mtp_round_result *out);
+                            stark_b200_mtp_round_result *out, const uint32_t *proposals = nullptr);
 stark_b200_status mtp_readout_row_f32(Model *m, uint32_t row, float *dst, size_t count);
 
 }  // namespace sb

@@ -287,8 +287,11 @@ stark_b200_status mtp_after_prompt(Model *m) {
     return STARK_B200_OK;
 }
 
+// proposals == nullptr: the head drafts `drafts` tokens.  Otherwise the caller proposes them (tokens it copied from
+// the request's own context: a prompt-lookup round, engine/hybrid/mtp_policy.rs `RoundPlan::Lookup`), no head
+// step runs, and the head's cache gets the pending row written instead ("head advance").
 stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_t policy, uint32_t accept_mask,
-                            stark_b200_mtp_round_result *out) {
+                            stark_b200_mtp_round_result *out, const uint32_t *proposals) {
     const auto &c = m->cfg;
     MtpHead &h = m->mtp;
     if (!h.enabled) return STARK_B200_UNSUPPORTED;
@@ -311,9 +314,16 @@ stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_
     hs.gen_capacity = drafts;
     SB_CUDA(cudaMemcpyAsync(h.state, &hs, sizeof(hs), cudaMemcpyHostToDevice, s));
     SB_CUDA(cudaMemcpyAsync(m->chunk_tokens, &pending, 4, cudaMemcpyHostToDevice, s));
-    SB_CUDA(cudaMemcpyAsync(h.draft_in, h.last_hidden, (size_t)c.hidden * 2u, cudaMemcpyDeviceToDevice, s));
-    for (uint32_t d = 0; d < drafts; ++d) SB_CUDA(cudaGraphLaunch(h.draft_graph, s));
-    m->launches_issued += 12ull * drafts;
+    if (proposals) {
+        for (uint32_t d = 0; d < drafts; ++d)
+            if (proposals[d] >= c.vocab) return STARK_B200_INVALID_ARGUMENT;
+        // pageable host memory: the copy is staged before the call returns, the caller's array may go away
+        if (drafts) SB_CUDA(cudaMemcpyAsync(m->chunk_tokens + 1, proposals, (size_t)drafts * 4u, cudaMemcpyHostToDevice, s));
+    } else {
+        SB_CUDA(cudaMemcpyAsync(h.draft_in, h.last_hidden, (size_t)c.hidden * 2u, cudaMemcpyDeviceToDevice, s));
+        for (uint32_t d = 0; d < drafts; ++d) SB_CUDA(cudaGraphLaunch(h.draft_graph, s));
+        m->launches_issued += 12ull * drafts;
+    }
 
     // ---- verify: the target over [pending, d1 .. dk] at its own positions; logits and hidden of every row
     if ((st = model_rows_pass(m, m->chunk_tokens, rows, (uint32_t)m->position)) != STARK_B200_OK) return st;
@@ -367,7 +377,7 @@ stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_
     const uint32_t pos32 = (uint32_t)m->position;
     SB_CUDA(cudaMemcpyAsync(&m->state->position, &pos32, 4, cudaMemcpyHostToDevice, s));
     h.position = prefix;
-    if (drafts == 0) {
+    if (drafts == 0 || proposals) {
         // no draft step ran: the pair (pending, previous hidden) still has to enter the head's cache
         if ((st = head_cache_rows(m, m->chunk_tokens, h.last_hidden, 1, prefix)) != STARK_B200_OK) return st;
     }

@@ -320,6 +320,19 @@ class DenseModel:
         return dict(tokens=[int(t) for t in r.tokens[:r.count]], accepted=int(r.accepted), proposed=int(r.proposed),
                     next_pending=int(r.next_pending), position=int(r.position))
 
+    def mtp_round_lookup(self, pending: int, proposals, accept_mask: int | None = None) -> dict:
+        """A round whose proposals the caller supplies (prompt lookup: tokens copied from the request's own
+        context, engine/hybrid/mtp_lookup.rs) instead of the head; otherwise as ``mtp_round``."""
+        r = _lib.MtpRoundResult()
+        r.struct_size, r.abi_version = C.sizeof(_lib.MtpRoundResult), _lib.ABI_VERSION
+        p = np.ascontiguousarray(proposals, np.uint32).reshape(-1)
+        policy = _lib.MTP_GREEDY if accept_mask is None else _lib.MTP_FORCED
+        self._guard(_lib.load().stark_b200_mtp_round_lookup(self._h, int(pending), p.ctypes.data if p.size else None,
+                                                            p.size, policy, int(accept_mask or 0), C.byref(r)),
+                    "mtp_round_lookup")
+        return dict(tokens=[int(t) for t in r.tokens[:r.count]], accepted=int(r.accepted), proposed=int(r.proposed),
+                    next_pending=int(r.next_pending), position=int(r.position))
+
     def mtp_row_logits(self, row: int) -> np.ndarray:
         """Full-vocabulary logits (f32) of one row of the last round's target pass."""
         out = np.empty(self.cfg["vocab"], np.float32)

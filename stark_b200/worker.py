@@ -388,6 +388,9 @@ class B200Backend:
             self.model = DenseModel.load(cfg, weights, context_tokens=self.capacity)
         except Exception:  # noqa: BLE001
             raise Refusal("model_load_failed") from None
+        self.has_head = bool(cfg.get("mtp"))
+        self.rounds = None   # speculative state of the request in flight
+        self._newline = None
         self.key = hashlib.sha256((path / "model.safetensors").stat().st_size.to_bytes(8, "little")
                                   + config.read_bytes()).hexdigest()
         self.position_tokens: list[int] = []   # tokens whose rows the cache currently holds
@@ -401,6 +404,33 @@ class B200Backend:
 
     def eos_token_ids(self) -> list[int]:
         return self.eos
+
+    # -- speculative decoding (GenerationBackend::mtp_capabilities and friends, generation.rs:585-615)
+    def mtp_capabilities(self):
+        if not self.has_head:
+            return None
+        return {"max_drafts": 4, "recommended_drafts": 2, "sampling": "greedy-exact-v1",
+                "verification": "dense-target-verify-rows-v1"}
+
+    def supports_mtp_scheduling(self) -> bool:
+        return self.has_head
+
+    def prefix_cache_supported(self) -> bool:
+        return not self.has_head    # the head's cache cannot be cut inside a prompt
+
+    def effective_mtp_drafts(self, drafts: int, sampling: dict) -> int:
+        """Acceptance on the device is the greedy rule; a stochastic request runs without proposals (the reference's
+        backends fall back the same way and the reply says so)."""
+        return drafts if sampling["mode"] == "greedy" else 0
+
+    def newline_tokens(self):
+        from .mtp_schedule import NewlineTokens
+        if self._newline is None:
+            tk = self.tokenizer
+            self._newline = NewlineTokens(self.cfg["vocab"] if tk is not None else 0,
+                                          (lambda i: "\n" in tk.decode([i], skip_special_tokens=False)) if tk is not None
+                                          else (lambda i: False))
+        return self._newline
 
     # -- text
     def tokenize(self, text: str, add_special_tokens: bool) -> list[int]:
@@ -420,11 +450,14 @@ class B200Backend:
             raise Refusal("decoding_failed") from None
 
     # -- generation
-    def begin(self, input_ids: list[int], reuse_rows: int, sampling: dict, seed: int) -> None:
+    def begin(self, input_ids: list[int], reuse_rows: int, sampling: dict, seed: int, mtp: dict | None = None,
+              budget_tokens: int = 0) -> None:
         """Brings the cache to the end of the prompt (reusing `reuse_rows` rows it already holds) with the
-        prompt's last row read out; `next_token` then samples."""
+        prompt's last row read out; `next_token` then samples.  mtp = {"drafts", "adaptive", "lookup"}: tokens
+        come from speculative rounds planned by a RoundScheduler (greedy acceptance)."""
         from ._lib import StarkB200Error
         import numpy as np
+        self.rounds = None
         try:
             if reuse_rows and self.position_tokens[:reuse_rows] == input_ids[:reuse_rows]:
                 self.model.rewind(reuse_rows)
@@ -438,11 +471,66 @@ class B200Backend:
             self.position_tokens = []
             raise Refusal("native_generation_failed") from None
         self.sampling, self.seed, self.sampled = sampling, seed, 0
+        if mtp and mtp["drafts"] > 0:
+            from .mtp_schedule import B200_QWEN3_8B_V1, PromptLookup, RoundScheduler
+            lookup = PromptLookup(input_ids, self.newline_tokens()) if mtp["lookup"] else None
+            try:
+                first = self.model.mtp_initial()
+            except StarkB200Error:
+                self.position_tokens = []
+                raise Refusal("native_generation_failed") from None
+            self.rounds = dict(scheduler=RoundScheduler(mtp["adaptive"], B200_QWEN3_8B_V1.greedy, mtp["drafts"], lookup,
+                                                        B200_QWEN3_8B_V1.id),
+                               queue=[first], pending=first, budget=budget_tokens, handed=0, count=0, proposed=0,
+                               accepted=0, by_accepted=[0] * (mtp["drafts"] + 1), verified_rows=0, seconds=0.0)
+
+    def _round(self) -> None:
+        """One speculative round: the pending token and the accepted proposals enter the cache, the accepted
+        proposals and the next pending token join the queue."""
+        import time as _time
+        r = self.rounds
+        cap = max(0, min(r["scheduler"].planner.limit, r["budget"] - r["handed"] - 1))
+        plan = r["scheduler"].plan(cap)
+        t0 = _time.perf_counter()
+        if plan[0] == "lookup":
+            out = self.model.mtp_round_lookup(r["pending"], plan[1])
+        else:
+            out = self.model.mtp_round(r["pending"], plan[1])
+        seconds = _time.perf_counter() - t0
+        r["scheduler"].observe(plan, out["accepted"], out["tokens"], seconds)
+        if plan[0] == "lookup" or plan[1] == 0:
+            r["scheduler"].record_head_advance(0.0)
+        r["count"] += 1
+        r["proposed"] += out["proposed"]
+        r["accepted"] += out["accepted"]
+        r["by_accepted"][out["accepted"]] += 1
+        r["verified_rows"] += out["proposed"] + 1
+        r["seconds"] += seconds
+        self.position_tokens.extend(out["tokens"])
+        r["queue"] = out["tokens"][1:] + [out["next_pending"]]
+        r["pending"] = out["next_pending"]
+
+    def mtp_metadata(self):
+        r = self.rounds
+        if r is None:
+            return None
+        return {"rounds": r["count"], "proposed": r["proposed"], "accepted": r["accepted"],
+                "rounds_by_accepted_drafts": r["by_accepted"], "verified_rows": r["verified_rows"],
+                "round_seconds": r["seconds"], "schedule": r["scheduler"].stats.as_json()}
 
     def next_token(self) -> int:
         """Samples from the logits of the last row and feeds the sample back (one decode step)."""
         from ._lib import StarkB200Error
         from .engine import position_seed
+        if self.rounds is not None:
+            try:
+                if not self.rounds["queue"]:
+                    self._round()
+                self.rounds["handed"] += 1
+                return self.rounds["queue"].pop(0)
+            except StarkB200Error:
+                self.position_tokens = []
+                raise Refusal("native_generation_failed") from None
         try:
             if self.sampling["mode"] == "greedy":
                 token = self.model.argmax()
@@ -460,6 +548,8 @@ class B200Backend:
     def advance(self, token: int) -> None:
         """Feeds an accepted sample so that the next `next_token` sees its row (skipped after the last sample)."""
         from ._lib import StarkB200Error
+        if self.rounds is not None:
+            return   # a round feeds its own tokens
         try:
             self.model.step_async(int(token))
             self.position_tokens.append(int(token))
@@ -532,9 +622,56 @@ class GenerationWorker:
         if self.prefix_cache:
             ready["state_policy"] = PREFIX_POLICY
             ready["operations"] = ["tokenize", "decode", "generate", "reset_cache"]
-        ready["mtp"] = {"supported": False, "max_drafts": 0, "recommended_drafts": 0, "default_drafts": 0,
-                        "operations": []}
+        caps = self.mtp_capabilities()
+        if caps is None:
+            ready["mtp"] = {"supported": False, "max_drafts": 0, "recommended_drafts": 0, "default_drafts": 0,
+                            "operations": []}
+        else:   # generation.rs:1562-1575
+            ready["mtp"] = {"supported": True, "max_drafts": caps["max_drafts"],
+                            "recommended_drafts": caps["recommended_drafts"], "default_drafts": 0,
+                            "sampling": caps["sampling"], "verification": caps["verification"], "operations": ["generate"]}
+            if self.backend.supports_mtp_scheduling():
+                ready["mtp"].update(policies=["fixed", "adaptive"], default_policy="fixed", default_lookup=False, lookup=True)
         return ready
+
+    def mtp_capabilities(self):
+        fn = getattr(self.backend, "mtp_capabilities", None)
+        return fn() if fn is not None else None
+
+    def resolve_mtp(self, enabled, drafts) -> int:
+        """generation.rs:788-821: `mtp` and `mtp_drafts` exclude each other; `mtp: true` takes the recommended count."""
+        if enabled is not None and drafts is not None:
+            raise Refusal("invalid_generation_request")
+        caps = self.mtp_capabilities()
+        if enabled is True:
+            if caps is None:
+                raise Refusal("mtp_not_supported")
+            drafts = caps["recommended_drafts"]
+        elif enabled is False or drafts is None:
+            drafts = 0
+        if drafts > 0:
+            if caps is None:
+                raise Refusal("mtp_not_supported")
+            if drafts > caps["max_drafts"]:
+                raise Refusal("invalid_generation_request")
+        return drafts
+
+    def resolve_mtp_scheduling(self, policy, lookup, explicit_drafts: bool, drafts: int):
+        """generation.rs:823-860.  Returns (adaptive, lookup, drafts)."""
+        if policy is not None and policy not in ("fixed", "adaptive"):
+            raise Refusal("invalid_generation_request")
+        adaptive = policy == "adaptive"
+        lookup = bool(lookup) if lookup is not None else False
+        if not adaptive and not lookup:
+            return False, False, drafts
+        if drafts == 0:
+            raise Refusal("invalid_generation_request")
+        supports = getattr(self.backend, "supports_mtp_scheduling", None)
+        if supports is None or not supports():
+            raise Refusal("mtp_not_supported")
+        if adaptive and not explicit_drafts:
+            drafts = self.mtp_capabilities()["max_drafts"]
+        return adaptive, lookup, drafts
 
     # -- prefix policy
     def clear_prefix(self) -> None:
@@ -632,14 +769,8 @@ class GenerationWorker:
             scope = parse_scope(scope_text) if self.prefix_cache else None
             if scope is None:
                 raise Refusal("invalid_generation_request")
-        if mtp is not None and mtp_drafts is not None:
-            raise Refusal("invalid_generation_request")
-        if mtp or (mtp_drafts or 0) > 0:
-            raise Refusal("mtp_not_supported")
-        if mtp_policy is not None and mtp_policy not in ("fixed", "adaptive"):
-            raise Refusal("invalid_generation_request")
-        if mtp_policy == "adaptive" or mtp_lookup:
-            raise Refusal("invalid_generation_request")   # a non-default schedule needs drafts > 0
+        drafts = self.resolve_mtp(mtp, mtp_drafts)
+        adaptive, lookup, drafts = self.resolve_mtp_scheduling(mtp_policy, mtp_lookup, mtp_drafts is not None, drafts)
         vocab = b.vocab_size()
         if (context_tokens == 0 or max_new == 0 or len(stop_ids) > MAX_EXTRA_STOPS or len(stop) > 4
                 or any(not s or len(s) > 1024 for s in stop) or any(t >= vocab for t in stop_ids)
@@ -666,7 +797,8 @@ class GenerationWorker:
             raise Refusal("context_overflow")
         return self.complete(ids, dict(context_tokens=context_tokens, max_new_tokens=max_new, seed=seed,
                                        sampling=sampling, stop_ids=stop_ids, stop=stop, request_id=request_id,
-                                       scope=scope), stream, out)
+                                       scope=scope, mtp_drafts=drafts, mtp_adaptive=adaptive, mtp_lookup=lookup),
+                             stream, out)
 
     def cancelled(self, request_id: int) -> bool:
         return self.cancel.check(request_id) if self.cancel is not None else False
@@ -692,7 +824,18 @@ class GenerationWorker:
         if self.cancelled(o["request_id"]):
             raise Refusal("generation_cancelled")
         self.pending_entry = None
-        b.begin(ids, reused, o["sampling"], o["seed"])
+        requested_drafts = o.get("mtp_drafts", 0)
+        effective_drafts = requested_drafts
+        if requested_drafts:
+            effective_drafts = b.effective_mtp_drafts(requested_drafts, o["sampling"])
+            if effective_drafts > requested_drafts or (effective_drafts != 0 and effective_drafts != requested_drafts):
+                raise Refusal("invalid_generation_output")
+        if effective_drafts:
+            b.begin(ids, reused, o["sampling"], o["seed"],
+                    mtp={"drafts": effective_drafts, "adaptive": o["mtp_adaptive"], "lookup": o["mtp_lookup"]},
+                    budget_tokens=budget_tokens)
+        else:
+            b.begin(ids, reused, o["sampling"], o["seed"])
         generated, sampled, emitted = [], 0, ""
         finish = "context" if o["context_tokens"] - input_tokens < o["max_new_tokens"] else "length"
         stop_token, first_sample, last_sample, text_so_far = None, None, None, ""
@@ -760,6 +903,17 @@ class GenerationWorker:
                  "input_tokens_per_second": rate(input_tokens - reused, prefill_seconds),
                  "output_tokens_per_second": rate(max(sampled - 1, 0), decode_seconds),
                  "timing_method": "first-token-wall-clock-v1"}
+        caps = self.mtp_capabilities()
+        if caps is not None:   # generation.rs:1029-1063
+            meta_fn = getattr(b, "mtp_metadata", None)
+            metadata = (meta_fn() if meta_fn is not None else None) or {}
+            metadata.update(enabled=effective_drafts > 0, drafts=effective_drafts, sampling=caps["sampling"],
+                            verification=caps["verification"])
+            if o.get("mtp_adaptive") or o.get("mtp_lookup"):
+                metadata.update(policy="adaptive" if o["mtp_adaptive"] else "fixed", lookup=bool(o["mtp_lookup"]))
+            if effective_drafts != requested_drafts:
+                metadata.update(requested_drafts=requested_drafts, fallback_reason="unsupported_sampling")
+            reply["mtp"] = metadata
         if self.prefix_cache:
             reply["reused_input_tokens"] = reused
             if o["scope"] is not None:
@@ -1011,6 +1165,9 @@ def main(argv=None, backend_factory=None) -> int:
         backend = factory(path)
         if scoring:
             return serve_scoring(ScoreWorker(backend, budget, flag), time.perf_counter() - started, sys.stdin.buffer, out)
+        supported = getattr(backend, "prefix_cache_supported", None)
+        if flag and supported is not None and not supported():
+            flag = False   # a model with a draft head: its cache cannot be cut inside a prompt
         return serve_generation(GenerationWorker(backend, budget, flag, cancel), sys.stdin.buffer, out)
     except Refusal as e:
         try:

@@ -381,3 +381,110 @@ def test_worker_process_round_trip_on_a_small_artifact(tmp_path):
     np.testing.assert_allclose(lines[1]["log_probabilities"], want, rtol=0, atol=1e-9)
     assert lines[1]["logits"] == [float(logits[c]) for c in (1, 2, 3)]
     model.close()
+
+
+# ----------------------------------------------------------------------------------------------- speculative rounds
+
+class SpeculativeBackend(ScriptedBackend):
+    """A scripted backend that declares a draft head (generation.rs:1706-1830 does the same with its FakeBackend)."""
+    CAPS = {"max_drafts": 3, "recommended_drafts": 2, "sampling": "greedy-exact-v1", "verification": "v"}
+
+    def __init__(self, tokens, scheduling=True, **kw):
+        super().__init__(tokens, **kw)
+        self.scheduling, self.begun = scheduling, []
+
+    def mtp_capabilities(self):
+        return dict(self.CAPS)
+
+    def supports_mtp_scheduling(self):
+        return self.scheduling
+
+    def effective_mtp_drafts(self, drafts, sampling):
+        return drafts if sampling["mode"] == "greedy" else 0
+
+    def begin(self, ids, reuse, sampling, seed, mtp=None, budget_tokens=0):
+        self.begun.append((mtp, budget_tokens))
+        super().begin(ids, reuse, sampling, seed)
+
+    def mtp_metadata(self):
+        return {"rounds": 1}
+
+
+def _spec(tokens, **kw):
+    return W.GenerationWorker(SpeculativeBackend(tokens, **kw), W.Budget(16), False)
+
+
+def test_speculative_selectors_resolve_as_the_reference_does():
+    # without a draft head every way of asking for proposals is refused, and a schedule without proposals is malformed
+    plain = _worker([1, 2, 3, 4])
+    assert plain.readiness()["mtp"] == {"supported": False, "max_drafts": 0, "recommended_drafts": 0, "default_drafts": 0,
+                                        "operations": []}
+    assert _ask(plain, dict(GEN, mtp=True)) == [{"error": "mtp_not_supported"}]
+    assert _ask(plain, dict(GEN, mtp_drafts=1)) == [{"error": "mtp_not_supported"}]
+    assert "error" not in _ask(plain, dict(GEN, mtp=False))[0] and "mtp" not in _ask(plain, dict(GEN, mtp_drafts=0))[0]
+    assert _ask(plain, dict(GEN, mtp_policy="adaptive")) == [{"error": "invalid_generation_request"}]
+    # with one
+    w = _spec([1, 2, 3, 4])
+    ready = w.readiness()["mtp"]
+    assert ready["supported"] and ready["max_drafts"] == 3 and ready["recommended_drafts"] == 2 and ready["operations"] == ["generate"]
+    assert ready["policies"] == ["fixed", "adaptive"] and ready["default_policy"] == "fixed" and ready["lookup"] is True
+    assert _ask(w, dict(GEN, mtp=True, mtp_drafts=2)) == [{"error": "invalid_generation_request"}]   # both selectors
+    assert _ask(w, dict(GEN, mtp_drafts=4)) == [{"error": "invalid_generation_request"}]              # past the limit
+    assert _ask(w, dict(GEN, mtp=None)) == [{"error": "invalid_request"}]                              # an explicit null
+    assert _ask(w, dict(GEN, mtp_policy="eager", mtp_drafts=1)) == [{"error": "invalid_generation_request"}]
+    assert _ask(w, dict(GEN, mtp_lookup=True)) == [{"error": "invalid_generation_request"}]            # a schedule, no proposals
+    reply = _ask(w, dict(GEN, mtp=True))[0]
+    assert reply["mtp"] == {"rounds": 1, "enabled": True, "drafts": 2, "sampling": "greedy-exact-v1", "verification": "v"}
+    assert w.backend.begun[-1] == ({"drafts": 2, "adaptive": False, "lookup": False}, 4)
+    reply = _ask(w, dict(GEN, mtp=True, mtp_policy="adaptive", mtp_lookup=True))[0]
+    assert reply["mtp"]["drafts"] == 3 and reply["mtp"]["policy"] == "adaptive" and reply["mtp"]["lookup"] is True
+    assert w.backend.begun[-1][0] == {"drafts": 3, "adaptive": True, "lookup": True}                 # adaptive plans up to the limit
+    reply = _ask(w, dict(GEN, mtp_drafts=1, mtp_policy="adaptive"))[0]
+    assert reply["mtp"]["drafts"] == 1                                                                # an explicit count wins
+    reply = _ask(w, dict(GEN, mtp_drafts=0))[0]
+    assert reply["mtp"]["enabled"] is False and reply["mtp"]["drafts"] == 0 and w.backend.begun[-1][0] is None
+    # a stochastic request runs without proposals and says so
+    reply = _ask(w, dict(GEN, mtp=True, sampling=dict(mode="stochastic", temperature=1.0)))[0]
+    assert reply["mtp"]["enabled"] is False and reply["mtp"]["requested_drafts"] == 2
+    assert reply["mtp"]["fallback_reason"] == "unsupported_sampling" and w.backend.begun[-1][0] is None
+    # a backend without scheduling support
+    w = _spec([1, 2, 3, 4], scheduling=False)
+    assert "policies" not in w.readiness()["mtp"]
+    assert _ask(w, dict(GEN, mtp=True, mtp_policy="adaptive")) == [{"error": "mtp_not_supported"}]
+
+
+@pytest.mark.gpu
+def test_speculative_generation_equals_plain_greedy_through_the_worker():
+    """The engine behind the worker with a draft head: fixed, adaptive and prompt-lookup schedules must all emit the
+    target's own greedy text (replayed through the one-row path, up to bf16 near-ties), whatever the rounds accept."""
+    from stark_b200 import synthetic as S
+    from stark_b200.engine import DenseModel
+    from tests.test_model_gpu import assert_sequence_is_greedy
+    cfg = S.CONFIGS["small"]
+    w = S.dense_weights(cfg, seed=3, zero_point=7.5)
+    backend = object.__new__(W.B200Backend)      # the engine without an artifact directory
+    backend.cfg, backend.capacity, backend.eos, backend.tokenizer, backend.key = dict(cfg, mtp=True), 1024, [], None, "k"
+    backend.model = DenseModel.load(dict(cfg, mtp=True), dict(w, mtp=S.mtp_weights(cfg, seed=3, zero_point=7.5)), 1024)
+    backend.has_head, backend.rounds, backend._newline, backend.position_tokens = True, None, None, []
+    worker = W.GenerationWorker(backend, W.Budget(16), False)
+    block = [int(t) for t in S.prompt(cfg, 48, seed=8)]
+    prompt = [int(t) for t in S.prompt(cfg, 90, seed=9)] + block + block[:40]       # the tail repeats: lookup proposes
+    plain = DenseModel.load(cfg, w, context_tokens=1024)
+    base = dict(operation="generate", input_token_ids=prompt, context_tokens=512, max_new_tokens=40)
+    seen = {}
+    for name, extra in (("fixed", dict(mtp_drafts=3)), ("adaptive", dict(mtp=True, mtp_policy="adaptive")),
+                        ("lookup", dict(mtp_drafts=3, mtp_lookup=True)), ("off", dict(mtp_drafts=0))):
+        reply = _ask(worker, dict(base, **extra))[0]
+        assert "error" not in reply, (name, reply)
+        assert reply["sampled_tokens"] == 40 and reply["finish_reason"] == "length"
+        assert_sequence_is_greedy(plain, prompt, reply["generated_token_ids"])
+        seen[name] = reply
+        if name != "off":
+            m = reply["mtp"]
+            assert m["enabled"] and m["verified_rows"] >= m["rounds"] >= 1 and m["accepted"] <= m["proposed"]
+            assert sum(m["rounds_by_accepted_drafts"]) == m["rounds"]
+    assert seen["adaptive"]["mtp"]["drafts"] == 4 and seen["adaptive"]["mtp"]["schedule"]["cost_table"]
+    assert seen["lookup"]["mtp"]["schedule"]["lookup_rounds"] >= 1                  # the repeated tail was tried
+    assert seen["off"]["mtp"]["enabled"] is False
+    plain.close()
+    backend.model.close()
