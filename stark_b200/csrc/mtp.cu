@@ -306,6 +306,35 @@ stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_
     const uint32_t prefix = (uint32_t)h.position;
     stark_b200_status st;
 
+    if (drafts == 0) {
+        // A round without proposals is one ordinary token: the recorded one-token sequence (every launch a
+        // programmatic dependent of the one before) instead of a one-row pass of the several-rows kernels.  The
+        // head's cache gets the pair (pending, previous hidden) first, while that hidden row is still there.
+        SB_CUDA(cudaMemcpyAsync(m->chunk_tokens, &pending, 4, cudaMemcpyHostToDevice, s));
+        if ((st = head_cache_rows(m, m->chunk_tokens, h.last_hidden, 1, prefix)) != STARK_B200_OK) return st;
+        if ((st = model_step(m, pending, false)) != STARK_B200_OK) return st;
+        if ((st = rmsnorm_rows_launch(m->h, m->final_norm, h.last_hidden, 1, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
+        SB_CUDA(cudaMemcpyAsync(h.rows_logits, m->logits, (size_t)c.vocab * 2u, cudaMemcpyDeviceToDevice, s));
+        SB_CUDA(cudaMemcpyAsync(h.host_words, &m->state->next_token, 4, cudaMemcpyDeviceToHost, s));
+        SB_CUDA(cudaMemcpyAsync(h.host_words + 32, ctx->error_word, 4, cudaMemcpyDeviceToHost, s));
+        const cudaError_t se = cudaStreamSynchronize(s);
+        if (se != cudaSuccess || h.host_words[32]) {
+            m->fenced = true;
+            return se != cudaSuccess ? cuda_status(se) : STARK_B200_DEVICE_FAILURE;
+        }
+        if (h.host_words[0] >= c.vocab) return STARK_B200_DEVICE_FAILURE;  // a non-finite row
+        h.position = prefix + 1u;
+        h.verified_rows = 1;
+        memset(out->tokens, 0, sizeof(out->tokens));
+        out->count = 1;
+        out->accepted = 0;
+        out->proposed = 0;
+        out->next_pending = h.host_words[0];
+        out->tokens[0] = pending;
+        out->position = m->position;
+        return STARK_B200_OK;
+    }
+
     // ---- drafts, chained on the device: state.token = pending, proposals appended at chunk_tokens[1 ..]
     StepState hs{};
     hs.position = prefix;
