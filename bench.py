@@ -34,6 +34,9 @@ WORKLOADS = {
     # against 8192 cache rows, acceptance forced to a seeded Bernoulli(0.6) per proposal
     "qwen3-8b-mtp": dict(cfg="qwen3-8b", prompt=8192, context=8192, mtp=True, drafts=4, accept=0.6),
     "small-mtp": dict(cfg="small", prompt=96, context=96, mtp=True, drafts=4, accept=0.6),
+    # two layers at the 8B shape's dimensions: the same kernels on a gigabyte of weights (what the ncu captures run)
+    "qwen3-8b-layers-mtp": dict(cfg="qwen3-8b-layers", prompt=8192, context=8192, mtp=True, drafts=4, accept=0.6),
+    "qwen3-8b-layers": dict(cfg="qwen3-8b-layers", prompt=4096, context=4096 + 1024),
     # routed-expert decoders (f32 host-path conventions, GGUF Q8_0 attention + Q4_K experts)
     "qwen3-30b-a3b": dict(cfg="qwen3-30b-a3b", prompt=2048, context=2048 + 512, moe=True),
     "moe-small": dict(cfg="moe-small", prompt=64, context=256, moe=True),
