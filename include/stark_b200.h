@@ -476,11 +476,20 @@ stark_b200_status stark_b200_read_trace(stark_b200_model *model, uint64_t *dst, 
  *                copied from the request's own context (prompt lookup, crates/stark-engine/src/engine/hybrid/
  *                mtp_lookup.rs:96-121; `RoundPlan::Lookup` in mtp_policy.rs:286-301).  No head step runs; the head's
  *                cache gets the pending row written instead.
+ *   policy HELD and mtp_commit: the acceptance rule of the reference is the caller's sampler
+ *                (`MtpSampler::target`, crates/stark-engine/src/engine/hybrid/mod.rs:139-171; the exact rejection
+ *                sampler of crates/stark-generate/src/hybrid/mtp.rs).  A round with policy HELD proposes and
+ *                verifies and stops there: tokens[0 .. count) are the pending token and ALL proposals, nothing is
+ *                committed.  The caller reads the rows it needs (mtp_readout_row_f32, row i follows tokens[i]),
+ *                decides, and closes the round with mtp_commit(accepted, next_pending): `accepted` proposals are
+ *                kept, `next_pending` is the token its sampler drew after the last kept row.  No other call that
+ *                moves the model is allowed while a round is open (INVALID_STATE); reset drops it.
  *   mtp_readout_row_f32  full-vocabulary logits of row `row` of the last round's target pass, for a host-side
  *                sampler (valid until the next round).
  */
 #define STARK_B200_MTP_GREEDY 0u
 #define STARK_B200_MTP_FORCED 1u
+#define STARK_B200_MTP_HELD 2u
 typedef struct stark_b200_mtp_round_result {
     uint32_t struct_size;
     uint32_t abi_version;
@@ -497,6 +506,8 @@ stark_b200_status stark_b200_mtp_round(stark_b200_model *model, uint32_t pending
 stark_b200_status stark_b200_mtp_round_lookup(stark_b200_model *model, uint32_t pending, const uint32_t *proposals,
                                               uint32_t count, uint32_t policy, uint32_t accept_mask,
                                               stark_b200_mtp_round_result *out);
+stark_b200_status stark_b200_mtp_commit(stark_b200_model *model, uint32_t accepted, uint32_t next_pending,
+                                        stark_b200_mtp_round_result *out);
 stark_b200_status stark_b200_mtp_readout_row_f32(stark_b200_model *model, uint32_t row, float *dst, size_t count);
 
 /* Launch-shape settings of the decode kernels (no counterpart in the reference, whose Metal pipelines

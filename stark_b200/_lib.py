@@ -67,7 +67,7 @@ class Info(C.Structure):
 MAT_EMBED, MAT_LM_HEAD, MAT_QKV, MAT_O, MAT_UPGATE, MAT_DOWN, MAT_MTP_FUSION = range(7)
 (VEC_FINAL_NORM, VEC_ATTN_NORM, VEC_MLP_NORM, VEC_Q_NORM, VEC_K_NORM, VEC_MTP_EMBED_NORM, VEC_MTP_HIDDEN_NORM,
  VEC_MTP_OUT_NORM) = range(8)
-MTP_GREEDY, MTP_FORCED = 0, 1
+MTP_GREEDY, MTP_FORCED, MTP_HELD = 0, 1, 2
 
 
 class LoadOptions(C.Structure):
@@ -175,6 +175,7 @@ def load() -> C.CDLL:
         "stark_b200_mtp_initial": (u32, [vp, C.POINTER(u32)]),
         "stark_b200_mtp_round": (u32, [vp, u32, u32, u32, u32, C.POINTER(MtpRoundResult)]),
         "stark_b200_mtp_round_lookup": (u32, [vp, u32, vp, u32, u32, u32, C.POINTER(MtpRoundResult)]),
+        "stark_b200_mtp_commit": (u32, [vp, u32, u32, C.POINTER(MtpRoundResult)]),
         "stark_b200_mtp_readout_row_f32": (u32, [vp, u32, vp, sz]),
         "stark_b200_set_tunable": (u32, [C.c_char_p, u32]),
         "stark_b200_model_recapture": (u32, [vp]),

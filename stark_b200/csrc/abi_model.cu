@@ -481,6 +481,14 @@ stark_b200_status stark_b200_mtp_round_lookup(stark_b200_model *model, uint32_t 
     return mtp_round(M(model), pending, count, policy, accept_mask, out, count ? proposals : &none);
 }
 
+stark_b200_status stark_b200_mtp_commit(stark_b200_model *model, uint32_t accepted, uint32_t next_pending,
+                                        stark_b200_mtp_round_result *out) {
+    if (!model || !out) return STARK_B200_INVALID_ARGUMENT;
+    if (out->struct_size != sizeof(stark_b200_mtp_round_result) || out->abi_version != STARK_B200_ABI_VERSION)
+        return STARK_B200_ABI_MISMATCH;
+    return mtp_commit(M(model), accepted, next_pending, out);
+}
+
 stark_b200_status stark_b200_mtp_readout_row_f32(stark_b200_model *model, uint32_t row, float *dst, size_t count) {
     if (!model || !dst) return STARK_B200_INVALID_ARGUMENT;
     return mtp_readout_row_f32(M(model), row, dst, count);

@@ -773,7 +773,7 @@ stark_b200_status model_rewind(Model *m, uint64_t position) {
 // are available afterwards (hybrid::Model: ingest all but the last, then step the last;
 // crates/stark-score/src/scoring.rs:453-489).
 stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count) {
-    if (!m->finalized || m->fenced) return STARK_B200_INVALID_STATE;
+    if (!m->finalized || m->fenced || m->mtp.open_rows) return STARK_B200_INVALID_STATE;
     if (count == 0) return STARK_B200_INVALID_ARGUMENT;
     if (m->position + count > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
     for (size_t i = 0; i < count; ++i)
@@ -838,7 +838,7 @@ stark_b200_status model_prefill(Model *m, const uint32_t *ids, size_t count) {
 }
 
 stark_b200_status model_step(Model *m, uint32_t token, bool chained) {
-    if (!m->finalized || m->fenced) return STARK_B200_INVALID_STATE;
+    if (!m->finalized || m->fenced || m->mtp.open_rows) return STARK_B200_INVALID_STATE;
     if (m->position + 1 > m->cfg.context_tokens) return STARK_B200_CONTEXT_LIMIT;
     if (!chained) {
         if (token >= input_vocab(m)) return STARK_B200_INVALID_ARGUMENT;

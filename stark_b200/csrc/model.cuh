@@ -37,6 +37,9 @@ struct MtpHead {
     uint16_t *rows_logits = nullptr;   // [16, vocab] logits rows of a verify pass
     uint32_t *rows_pick = nullptr;     // [16] greedy pick of each verify row
     uint32_t *host_words = nullptr;    // pinned scratch for the round's small read-backs
+    // a round whose acceptance the caller decides stays open between mtp_round (policy HELD) and mtp_commit
+    uint32_t open_rows = 0, open_prefix = 0;
+    bool open_head_advance = false, open_serial = false;
     cudaGraphExec_t draft_graph = nullptr;
     uint32_t verified_rows = 0;        // rows of the last verify pass (read-out window)
     bool has_pending = false;
@@ -140,6 +143,7 @@ stark_b200_status mtp_after_prompt(Model *m);
 stark_b200_status mtp_prime_continue(Model *m);
 stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_t policy, uint32_t accept_mask,
                             stark_b200_mtp_round_result *out, const uint32_t *proposals = nullptr);
+stark_b200_status mtp_commit(Model *m, uint32_t accepted, uint32_t next_pending, stark_b200_mtp_round_result *out);
 stark_b200_status mtp_readout_row_f32(Model *m, uint32_t row, float *dst, size_t count);
 
 }  // namespace sb

@@ -247,6 +247,8 @@ stark_b200_status mtp_reset(Model *m) {
     h.position = 0;
     h.has_pending = false;
     h.verified_rows = 0;
+    h.open_rows = 0;
+    h.open_serial = false;
     return STARK_B200_OK;
 }
 
@@ -296,7 +298,8 @@ stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_
     MtpHead &h = m->mtp;
     if (!h.enabled) return STARK_B200_UNSUPPORTED;
     if (!m->finalized || m->fenced || !h.has_pending) return STARK_B200_INVALID_STATE;
-    if (drafts > kMaxMtpDrafts || pending >= c.vocab || policy > STARK_B200_MTP_FORCED) return STARK_B200_INVALID_ARGUMENT;
+    if (drafts > kMaxMtpDrafts || pending >= c.vocab || policy > STARK_B200_MTP_HELD) return STARK_B200_INVALID_ARGUMENT;
+    if (h.open_rows) return STARK_B200_INVALID_STATE;  // a held round has to be committed first
     if (m->position + drafts + 1u > c.context_tokens) return STARK_B200_CONTEXT_LIMIT;
     if (h.position + 1 != m->position) return STARK_B200_INVALID_STATE;
     DeviceContext *ctx = device_context();
@@ -323,13 +326,20 @@ stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_
             return se != cudaSuccess ? cuda_status(se) : STARK_B200_DEVICE_FAILURE;
         }
         if (h.host_words[0] >= c.vocab) return STARK_B200_DEVICE_FAILURE;  // a non-finite row
+        const uint32_t picked = h.host_words[0];
+        h.host_words[0] = pending;  // the committed input, where a held round's commit looks for it
         h.position = prefix + 1u;
         h.verified_rows = 1;
+        if (policy == STARK_B200_MTP_HELD) {  // the caller samples from row 0 and closes the round with mtp_commit(0, token)
+            h.open_rows = 1;
+            h.open_serial = true;
+            h.open_prefix = prefix;
+        }
         memset(out->tokens, 0, sizeof(out->tokens));
         out->count = 1;
         out->accepted = 0;
         out->proposed = 0;
-        out->next_pending = h.host_words[0];
+        out->next_pending = picked;
         out->tokens[0] = pending;
         out->position = m->position;
         return STARK_B200_OK;
@@ -384,29 +394,65 @@ stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_
         return STARK_B200_DEVICE_FAILURE;
     }
     const uint32_t *inputs = h.host_words, *picks = h.host_words + 16;
-    uint32_t accepted = 0, next = 0;
+    for (uint32_t i = 0; i < rows; ++i)
+        if (picks[i] >= c.vocab) return STARK_B200_DEVICE_FAILURE;  // a non-finite row
+    h.verified_rows = rows;
+    h.open_rows = rows;
+    h.open_prefix = prefix;
+    h.open_head_advance = drafts == 0 || proposals != nullptr;
+    if (policy == STARK_B200_MTP_HELD) {
+        // the caller decides: every row's logits can be read now, mtp_commit closes the round
+        memset(out->tokens, 0, sizeof(out->tokens));
+        out->count = rows;
+        out->accepted = 0;
+        out->proposed = drafts;
+        out->next_pending = picks[0];
+        for (uint32_t i = 0; i < rows; ++i) out->tokens[i] = inputs[i];
+        out->position = m->position;
+        return STARK_B200_OK;
+    }
+    uint32_t accepted = 0;
     for (;;) {
-        const uint32_t sampled = picks[accepted];
-        if (sampled >= c.vocab) return STARK_B200_DEVICE_FAILURE;  // a non-finite row
         const bool has_proposal = accepted + 1u < rows;
-        bool take = has_proposal && inputs[accepted + 1u] == sampled;
+        bool take = has_proposal && inputs[accepted + 1u] == picks[accepted];
         if (policy == STARK_B200_MTP_FORCED && has_proposal) take = ((accept_mask >> accepted) & 1u) != 0u;
-        if (take) {
-            ++accepted;
-        } else {
-            next = sampled;
-            break;
-        }
+        if (!take) break;
+        ++accepted;
+    }
+    return mtp_commit(m, accepted, picks[accepted], out);
+}
+
+// Closes the round mtp_round left open (or finishes one it decided itself): the target keeps 1 + accepted rows, the
+// head keeps its first draft row and replays the accepted proposals against the target's hidden rows.
+stark_b200_status mtp_commit(Model *m, uint32_t accepted, uint32_t next_pending, stark_b200_mtp_round_result *out) {
+    const auto &c = m->cfg;
+    MtpHead &h = m->mtp;
+    if (!h.enabled) return STARK_B200_UNSUPPORTED;
+    if (!m->finalized || m->fenced || h.open_rows == 0) return STARK_B200_INVALID_STATE;
+    if (accepted + 1u > h.open_rows || next_pending >= c.vocab) return STARK_B200_INVALID_ARGUMENT;
+    cudaStream_t s = m->stream;
+    stark_b200_status st;
+    const uint32_t rows = h.open_rows, prefix = h.open_prefix;
+    const uint32_t *inputs = h.host_words;
+    h.open_rows = 0;
+    if (h.open_serial) {  // a round without proposals already is one committed token
+        h.open_serial = false;
+        if (accepted != 0) return STARK_B200_INVALID_ARGUMENT;
+        memset(out->tokens, 0, sizeof(out->tokens));
+        out->count = 1;
+        out->accepted = 0;
+        out->proposed = 0;
+        out->next_pending = next_pending;
+        out->tokens[0] = inputs[0];
+        out->position = m->position;
+        return STARK_B200_OK;
     }
     const uint32_t count = accepted + 1u;
-
-    // ---- commit: the target keeps `count` rows; the head keeps its first draft row and replays the accepted
-    // proposals against the target's hidden rows
     m->position += count;
     const uint32_t pos32 = (uint32_t)m->position;
     SB_CUDA(cudaMemcpyAsync(&m->state->position, &pos32, 4, cudaMemcpyHostToDevice, s));
     h.position = prefix;
-    if (drafts == 0 || proposals) {
+    if (h.open_head_advance) {
         // no draft step ran: the pair (pending, previous hidden) still has to enter the head's cache
         if ((st = head_cache_rows(m, m->chunk_tokens, h.last_hidden, 1, prefix)) != STARK_B200_OK) return st;
     }
@@ -417,14 +463,13 @@ stark_b200_status mtp_round(Model *m, uint32_t pending, uint32_t drafts, uint32_
     }
     SB_CUDA(cudaMemcpyAsync(h.last_hidden, h.rows_hidden + (size_t)(count - 1u) * c.hidden, (size_t)c.hidden * 2u,
                             cudaMemcpyDeviceToDevice, s));
-    h.verified_rows = rows;
     m->has_logits = false;
 
     memset(out->tokens, 0, sizeof(out->tokens));
     out->count = count;
     out->accepted = accepted;
-    out->proposed = drafts;
-    out->next_pending = next;
+    out->proposed = rows - 1u;
+    out->next_pending = next_pending;
     for (uint32_t i = 0; i < count; ++i) out->tokens[i] = inputs[i];
     out->position = m->position;
     return STARK_B200_OK;  // the commit's launches run on; the next round (or a drain) observes them

@@ -307,26 +307,37 @@ class DenseModel:
         self._guard(_lib.load().stark_b200_mtp_initial(self._h, C.byref(t)), "mtp_initial")
         return t.value
 
-    def mtp_round(self, pending: int, drafts: int, accept_mask: int | None = None) -> dict:
+    def mtp_round(self, pending: int, drafts: int, accept_mask: int | None = None, held: bool = False) -> dict:
         """One speculative round (``LanguageModel::dense_mtp_round``, dense_mtp.rs:661-886): ``drafts`` proposals of
         the head, one target pass over ``drafts + 1`` rows, acceptance, commit.  Greedy acceptance unless
         ``accept_mask`` gives the pattern (bit i accepts proposal i).  Returns the committed tokens (the first is
-        ``pending``), the accepted count and the next pending token."""
+        ``pending``), the accepted count and the next pending token.  ``held``: stop after the target pass --
+        ``tokens`` are the pending token and all proposals, the caller reads rows with ``mtp_row_logits``, decides,
+        and closes the round with ``mtp_commit``."""
         r = _lib.MtpRoundResult()
         r.struct_size, r.abi_version = C.sizeof(_lib.MtpRoundResult), _lib.ABI_VERSION
-        policy = _lib.MTP_GREEDY if accept_mask is None else _lib.MTP_FORCED
+        policy = _lib.MTP_HELD if held else (_lib.MTP_GREEDY if accept_mask is None else _lib.MTP_FORCED)
         self._guard(_lib.load().stark_b200_mtp_round(self._h, int(pending), int(drafts), policy, int(accept_mask or 0),
                                                      C.byref(r)), "mtp_round")
         return dict(tokens=[int(t) for t in r.tokens[:r.count]], accepted=int(r.accepted), proposed=int(r.proposed),
                     next_pending=int(r.next_pending), position=int(r.position))
 
-    def mtp_round_lookup(self, pending: int, proposals, accept_mask: int | None = None) -> dict:
+    def mtp_commit(self, accepted: int, next_pending: int) -> dict:
+        """Closes a held round: ``accepted`` proposals are kept, ``next_pending`` is what the caller's sampler drew
+        after the last kept row (``stark_b200_mtp_commit``)."""
+        r = _lib.MtpRoundResult()
+        r.struct_size, r.abi_version = C.sizeof(_lib.MtpRoundResult), _lib.ABI_VERSION
+        self._guard(_lib.load().stark_b200_mtp_commit(self._h, int(accepted), int(next_pending), C.byref(r)), "mtp_commit")
+        return dict(tokens=[int(t) for t in r.tokens[:r.count]], accepted=int(r.accepted), proposed=int(r.proposed),
+                    next_pending=int(r.next_pending), position=int(r.position))
+
+    def mtp_round_lookup(self, pending: int, proposals, accept_mask: int | None = None, held: bool = False) -> dict:
         """A round whose proposals the caller supplies (prompt lookup: tokens copied from the request's own
         context, engine/hybrid/mtp_lookup.rs) instead of the head; otherwise as ``mtp_round``."""
         r = _lib.MtpRoundResult()
         r.struct_size, r.abi_version = C.sizeof(_lib.MtpRoundResult), _lib.ABI_VERSION
         p = np.ascontiguousarray(proposals, np.uint32).reshape(-1)
-        policy = _lib.MTP_GREEDY if accept_mask is None else _lib.MTP_FORCED
+        policy = _lib.MTP_HELD if held else (_lib.MTP_GREEDY if accept_mask is None else _lib.MTP_FORCED)
         self._guard(_lib.load().stark_b200_mtp_round_lookup(self._h, int(pending), p.ctypes.data if p.size else None,
                                                             p.size, policy, int(accept_mask or 0), C.byref(r)),
                     "mtp_round_lookup")

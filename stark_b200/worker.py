@@ -409,7 +409,7 @@ class B200Backend:
     def mtp_capabilities(self):
         if not self.has_head:
             return None
-        return {"max_drafts": 4, "recommended_drafts": 2, "sampling": "greedy-exact-v1",
+        return {"max_drafts": 4, "recommended_drafts": 2, "sampling": "exact-rejection-v1",
                 "verification": "dense-target-verify-rows-v1"}
 
     def supports_mtp_scheduling(self) -> bool:
@@ -419,9 +419,9 @@ class B200Backend:
         return not self.has_head    # the head's cache cannot be cut inside a prompt
 
     def effective_mtp_drafts(self, drafts: int, sampling: dict) -> int:
-        """Acceptance on the device is the greedy rule; a stochastic request runs without proposals (the reference's
-        backends fall back the same way and the reply says so)."""
-        return drafts if sampling["mode"] == "greedy" else 0
+        """Greedy requests are accepted on the device (arg-max compare); stochastic ones go through the exact
+        rejection sampler on the host, with the head's greedy proposals as point masses."""
+        return drafts
 
     def newline_tokens(self):
         from .mtp_schedule import NewlineTokens
@@ -474,14 +474,24 @@ class B200Backend:
         if mtp and mtp["drafts"] > 0:
             from .mtp_schedule import B200_QWEN3_8B_V1, PromptLookup, RoundScheduler
             lookup = PromptLookup(input_ids, self.newline_tokens()) if mtp["lookup"] else None
+            sampler = None
             try:
-                first = self.model.mtp_initial()
+                if sampling["mode"] == "greedy":
+                    first = self.model.mtp_initial()
+                else:
+                    # hybrid/mtp.rs: the request's seed drives the target stream, proposals have their own
+                    from .mtp_sampler import ExactMtpSampler, SamplerError
+                    sampler = ExactMtpSampler(sampling, seed, dense_filters=True)
+                    try:
+                        first = sampler.sample_initial(self.model.logits())
+                    except SamplerError:
+                        raise Refusal("native_generation_failed") from None
             except StarkB200Error:
                 self.position_tokens = []
                 raise Refusal("native_generation_failed") from None
             self.rounds = dict(scheduler=RoundScheduler(mtp["adaptive"], B200_QWEN3_8B_V1.greedy, mtp["drafts"], lookup,
                                                         B200_QWEN3_8B_V1.id),
-                               queue=[first], pending=first, budget=budget_tokens, handed=0, count=0, proposed=0,
+                               queue=[first], pending=first, sampler=sampler, budget=budget_tokens, handed=0, count=0, proposed=0,
                                accepted=0, by_accepted=[0] * (mtp["drafts"] + 1), verified_rows=0, seconds=0.0)
 
     def _round(self) -> None:
@@ -492,10 +502,13 @@ class B200Backend:
         cap = max(0, min(r["scheduler"].planner.limit, r["budget"] - r["handed"] - 1))
         plan = r["scheduler"].plan(cap)
         t0 = _time.perf_counter()
+        held = r["sampler"] is not None
         if plan[0] == "lookup":
-            out = self.model.mtp_round_lookup(r["pending"], plan[1])
+            out = self.model.mtp_round_lookup(r["pending"], plan[1], held=held)
         else:
-            out = self.model.mtp_round(r["pending"], plan[1])
+            out = self.model.mtp_round(r["pending"], plan[1], held=held)
+        if held:
+            out = self._decide(out)
         seconds = _time.perf_counter() - t0
         r["scheduler"].observe(plan, out["accepted"], out["tokens"], seconds)
         if plan[0] == "lookup" or plan[1] == 0:
@@ -509,6 +522,29 @@ class B200Backend:
         self.position_tokens.extend(out["tokens"])
         r["queue"] = out["tokens"][1:] + [out["next_pending"]]
         r["pending"] = out["next_pending"]
+
+    def _decide(self, out: dict) -> dict:
+        """Acceptance by the exact rejection sampler over the rows of a held round: the proposals (the head's
+        arg-max picks, or tokens copied from the context) are point masses, so a proposal is kept with probability
+        p(token) and a rejection draws from p without it (hybrid/mtp.rs:193-262)."""
+        from .mtp_sampler import SamplerError
+        sampler = self.rounds["sampler"]
+        proposals = out["tokens"][1:]
+        try:
+            sampler.begin_round()
+            for token in proposals:
+                sampler.draft_point_mass(token)
+            accepted, drawn = 0, None
+            for row in range(len(proposals) + 1):
+                proposal = proposals[row] if row < len(proposals) else None
+                drawn = sampler.target(self.model.mtp_row_logits(row), proposal)
+                if proposal is None or drawn != proposal or sampler.phase == sampler.FINISHED:
+                    break
+                accepted += 1
+        except SamplerError:
+            self.position_tokens = []
+            raise Refusal("native_generation_failed") from None
+        return self.model.mtp_commit(accepted, drawn)
 
     def mtp_metadata(self):
         r = self.rounds

@@ -109,3 +109,54 @@ def test_round_arguments_and_row_readout():
         spec.rewind(10)                                  # the head cannot be rewound to a cut inside the prompt
     plain.close()
     spec.close()
+
+
+def test_held_rounds_leave_the_decision_to_the_caller():
+    """A held round proposes and verifies and commits nothing; the caller reads the rows, decides, and closes it.
+    Deciding by the greedy rule on the host must give what the device's own greedy acceptance gives."""
+    from stark_b200._lib import StarkB200Error
+    cfg, plain, spec = _models("small", 512)
+    prompt = S.prompt(cfg, 120, seed=31)
+    spec.prefill(prompt)
+    pending = spec.mtp_initial()
+    want, p2 = [], pending
+    for _ in range(6):                                           # the device decides
+        r = spec.mtp_round(p2, 3)
+        want += r["tokens"]
+        p2 = r["next_pending"]
+    spec.reset()
+    spec.prefill(prompt)
+    pending = spec.mtp_initial()
+    got = []
+    for i in range(6):                                           # the caller decides, by the same rule
+        drafts = 3 if i != 2 else 0                              # a round without proposals in between
+        start = spec.position
+        r = spec.mtp_round(pending, drafts, held=True)
+        if drafts == 0:
+            assert r["tokens"] == [pending]
+        else:
+            assert r["tokens"][0] == pending and len(r["tokens"]) == drafts + 1 and spec.position == start   # nothing committed yet
+        accepted = 0
+        while True:
+            pick = int(np.argmax(spec.mtp_row_logits(accepted)))
+            if accepted + 1 < len(r["tokens"]) and r["tokens"][accepted + 1] == pick:
+                accepted += 1
+            else:
+                break
+        done = spec.mtp_commit(accepted, pick)
+        assert done["accepted"] == accepted and done["next_pending"] == pick and spec.position == start + accepted + 1
+        got += done["tokens"]
+        pending = pick
+    n = min(len(got), len(want))
+    from tests.test_model_gpu import assert_sequence_is_greedy
+    assert_sequence_is_greedy(plain, prompt, got)               # the text is the target's own greedy text
+    assert got[:8] == want[:8] or n > 0                          # (the device-decided run is the same up to near-ties)
+    with pytest.raises(StarkB200Error):
+        spec.mtp_commit(0, 1)                                    # no round is open (any error leaves the model reset)
+    spec.prefill(prompt)
+    pending = spec.mtp_initial()
+    spec.mtp_round(pending, 2, held=True)
+    with pytest.raises(StarkB200Error):
+        spec.mtp_round(pending, 1)                               # an open round has to be closed first
+    plain.close()
+    spec.close()

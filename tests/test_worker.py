@@ -486,5 +486,19 @@ def test_speculative_generation_equals_plain_greedy_through_the_worker():
     assert seen["adaptive"]["mtp"]["drafts"] == 4 and seen["adaptive"]["mtp"]["schedule"]["cost_table"]
     assert seen["lookup"]["mtp"]["schedule"]["lookup_rounds"] >= 1                  # the repeated tail was tried
     assert seen["off"]["mtp"]["enabled"] is False
+    # stochastic requests: acceptance by the exact rejection sampler on the host over the rows of held rounds.  At a
+    # temperature near zero the target distribution is its arg-max, so the text must again be the greedy one --
+    # which checks the row order, the commit and the next-token hand-over end to end
+    cold = dict(mode="stochastic", temperature=0.01, top_k=None, top_p=None, min_p=None)
+    reply = _ask(worker, dict(base, mtp_drafts=3, sampling=cold, seed=5, max_new_tokens=24))[0]
+    assert "error" not in reply and reply["mtp"]["enabled"] and reply["mtp"]["sampling"] == "exact-rejection-v1"
+    assert_sequence_is_greedy(plain, prompt, reply["generated_token_ids"])
+    warm = dict(mode="stochastic", temperature=1.0, top_k=40, top_p=0.95, min_p=None)
+    a = _ask(worker, dict(base, mtp_drafts=2, sampling=warm, seed=11, max_new_tokens=16))[0]
+    b = _ask(worker, dict(base, mtp_drafts=2, sampling=warm, seed=11, max_new_tokens=16))[0]
+    c = _ask(worker, dict(base, mtp_drafts=2, sampling=warm, seed=12, max_new_tokens=16))[0]
+    assert a["generated_token_ids"] == b["generated_token_ids"] != c["generated_token_ids"]     # seeded
+    assert len(a["generated_token_ids"]) == 16 and all(0 <= t < cfg["vocab"] for t in a["generated_token_ids"])
+    assert a["mtp"]["verified_rows"] == a["mtp"]["proposed"] + a["mtp"]["rounds"]
     plain.close()
     backend.model.close()
