@@ -79,6 +79,10 @@ const char *stark_b200_last_cuda_error(void);
 
 /* Device plumbing for callers that do not bring their own allocator. */
 stark_b200_status stark_b200_device_count(int32_t *out_count);
+/* Free and total memory of the current device: what the memory-admission planner of a worker measures its headroom
+ * against (the reference asks its host for available memory, crates/stark-generate/src/generation.rs:1161-1164,
+ * because its device memory is the host's; here the cache and the working buffers live in HBM). */
+stark_b200_status stark_b200_device_memory(uint64_t *out_free_bytes, uint64_t *out_total_bytes);
 stark_b200_status stark_b200_set_device(int32_t device);
 stark_b200_status stark_b200_device_malloc(void **out_ptr, size_t bytes);
 stark_b200_status stark_b200_device_free(void *ptr);

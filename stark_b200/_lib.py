@@ -118,6 +118,7 @@ def load() -> C.CDLL:
         "stark_b200_status_name": (C.c_char_p, [u32]),
         "stark_b200_last_cuda_error": (C.c_char_p, []),
         "stark_b200_device_count": (u32, [C.POINTER(C.c_int32)]),
+        "stark_b200_device_memory": (u32, [C.POINTER(u64), C.POINTER(u64)]),
         "stark_b200_set_device": (u32, [C.c_int32]),
         "stark_b200_device_malloc": (u32, [C.POINTER(vp), sz]),
         "stark_b200_device_free": (u32, [vp]),

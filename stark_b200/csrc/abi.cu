@@ -90,6 +90,15 @@ stark_b200_status stark_b200_device_count(int32_t *out_count) {
     return STARK_B200_OK;
 }
 
+stark_b200_status stark_b200_device_memory(uint64_t *out_free_bytes, uint64_t *out_total_bytes) {
+    if (!out_free_bytes || !out_total_bytes) return STARK_B200_INVALID_ARGUMENT;
+    size_t free_bytes = 0, total_bytes = 0;
+    SB_CUDA(cudaMemGetInfo(&free_bytes, &total_bytes));
+    *out_free_bytes = free_bytes;
+    *out_total_bytes = total_bytes;
+    return STARK_B200_OK;
+}
+
 stark_b200_status stark_b200_set_device(int32_t device) {
     SB_CUDA(cudaSetDevice(device));
     return STARK_B200_OK;

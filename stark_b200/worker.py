@@ -415,6 +415,31 @@ class B200Backend:
     def supports_mtp_scheduling(self) -> bool:
         return self.has_head
 
+    def plan_context_length(self, input_tokens: int, maximum: int, drafts: int):
+        """The largest context up to `maximum` this engine can serve now.  The paged cache is allocated when the model
+        loads (`capacity` rows: 147 KB each for the 8B shape), so a context costs nothing further; what a request may
+        still allocate are the working buffers of a prompt pass (4 096 rows of every intermediate) and, with
+        proposals, the rows of the verify pass.  They have to fit the device memory that is free, with a reserve."""
+        import ctypes as C
+        from . import _lib
+        c = self.cfg
+        rows = 4096
+        qkv = (c["q_heads"] + 2 * c["kv_heads"]) * c["head_dim"]
+        scratch = rows * 2 * (2 * c["hidden"] + qkv + c["q_heads"] * c["head_dim"] + c["inter"])
+        if drafts:
+            scratch += 16 * 2 * (c["vocab"] + 4 * c["hidden"])
+        free, total = C.c_uint64(0), C.c_uint64(0)
+        try:
+            _lib.check(_lib.load().stark_b200_device_memory(C.byref(free), C.byref(total)), "device_memory")
+        except Exception:  # noqa: BLE001
+            return None
+        reserve = 512 << 20
+        if getattr(self, "_scratch_ready", False):
+            scratch = 0
+        if free.value < scratch + reserve:
+            return None
+        return min(maximum, self.capacity)
+
     def prefix_cache_supported(self) -> bool:
         return not self.has_head    # the head's cache cannot be cut inside a prompt
 
@@ -466,6 +491,7 @@ class B200Backend:
                 self.model.reset()
             self.position_tokens = list(input_ids[:reuse_rows])
             self.model.prefill(np.asarray(input_ids[reuse_rows:], np.uint32))
+            self._scratch_ready = True    # the prompt pass has its working buffers now
             self.position_tokens = list(input_ids)
         except StarkB200Error:
             self.position_tokens = []
@@ -768,18 +794,48 @@ class GenerationWorker:
         if op == "generate":
             return self.generate(f, out)
         if op == "plan_generation":
-            for name in ("input_tokens", "context_tokens"):
-                f.required(name, lambda x: _uint(x, U32_MAX))
-            f.present("input_token_ids", _ids)
-            f.present("cache_scope", _string)
-            f.present("mtp", _boolean)
-            f.present("mtp_drafts", lambda x: _uint(x, U32_MAX))
-            f.defaulted("sampling", parse_sampling, {"mode": "greedy"})
+            plan = {name: f.required(name, lambda x: _uint(x, U32_MAX)) for name in ("input_tokens", "context_tokens")}
+            plan["input_token_ids"] = f.present("input_token_ids", _ids)
+            plan["cache_scope"] = f.present("cache_scope", _string)
+            plan["mtp"] = f.present("mtp", _boolean)
+            plan["mtp_drafts"] = f.present("mtp_drafts", lambda x: _uint(x, U32_MAX))
+            sampling = f.defaulted("sampling", parse_sampling, {"mode": "greedy"})
             f.done()
-            raise Refusal("context_planning_unavailable")
+            return self.plan_generation(plan, sampling)
         if op in ("prepare_image", "generate_image", "discard_image"):
             raise Refusal("images_not_supported" if op != "discard_image" else "invalid_request")
         raise Refusal("invalid_request")
+
+    def plan_generation(self, obj: dict, sampling: dict):
+        """generation.rs:1114-1182: the largest context the loaded model can serve for this input within the
+        memory that is left.  The fields were type-checked by the caller."""
+        b = self.backend
+        planner = getattr(b, "plan_context_length", None)
+        if planner is None:
+            raise Refusal("context_planning_unavailable")
+        input_tokens, context_tokens = obj["input_tokens"], obj["context_tokens"]
+        token_limit = min(self.budget.input_bytes // 4, U32_MAX)
+        maximum = min(input_tokens + token_limit, context_tokens, b.max_context_length())
+        if input_tokens == 0 or input_tokens > token_limit or maximum <= input_tokens:
+            raise Refusal("invalid_generation_request")
+        ids = obj.get("input_token_ids")
+        if ids is not None and (len(ids) != input_tokens or any(t >= b.vocab_size() for t in ids)):
+            raise Refusal("invalid_generation_request")
+        drafts = self.resolve_mtp(obj.get("mtp"), obj.get("mtp_drafts"))
+        scope_text = obj.get("cache_scope")
+        if scope_text is not None and (not self.prefix_cache or parse_scope(scope_text) is None):
+            raise Refusal("invalid_generation_request")
+        validate_sampling(sampling, b.vocab_size())
+        if drafts:
+            effective = b.effective_mtp_drafts(drafts, sampling)
+            if effective > drafts or (effective != 0 and effective != drafts):
+                raise Refusal("invalid_generation_output")
+            drafts = effective
+        capacity = planner(input_tokens, maximum, drafts)
+        if capacity is None or capacity <= input_tokens or capacity > maximum:
+            raise Refusal("resource_budget_exceeded")
+        return {"context_tokens": capacity, "max_new_tokens": capacity - input_tokens,
+                "context_capacity_known": True, "budget_kind": "memory"}
 
     def generate(self, f: Fields, out):
         b = self.backend

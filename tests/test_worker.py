@@ -349,12 +349,14 @@ def test_worker_process_round_trip_on_a_small_artifact(tmp_path):
                 dict(operation="generate", input_token_ids=longer, context_tokens=2048, max_new_tokens=3, cache_scope=scope),
                 dict(operation="generate", input_token_ids=prompt[:9], context_tokens=64, max_new_tokens=5, seed=4,
                      sampling=dict(mode="stochastic", temperature=0.8, top_k=50)),
-                dict(operation="bogus")]
+                dict(operation="bogus"),
+                dict(operation="plan_generation", input_tokens=40, context_tokens=100000)]
     r = _run(["--model-path", str(tmp_path / "model"), "--prefix-cache"],
              stdin="".join(json.dumps(q) + "\n" for q in requests).encode(), env={"STARK_B200_WORKER_CONTEXT": "2048"})
     assert r.returncode == 0 and not r.stderr, r
     lines = [json.loads(x) for x in r.stdout.splitlines()]
-    assert len(lines) == 5 and lines[0]["ready"] is True and lines[0]["vocab_size"] == cfg["vocab"]
+    assert len(lines) == 6 and lines[0]["ready"] is True and lines[0]["vocab_size"] == cfg["vocab"]
+    assert lines[5] == {"context_tokens": 2048, "max_new_tokens": 2008, "context_capacity_known": True, "budget_kind": "memory"}
     assert lines[0]["max_context_tokens"] == 2048 and lines[0]["state_policy"] == "consecutive-prefix-v1"
     model = DenseModel.load(cfg, w, context_tokens=2048)
     model.prefill(np.asarray(prompt, np.uint32))
@@ -502,3 +504,37 @@ def test_speculative_generation_equals_plain_greedy_through_the_worker():
     assert a["mtp"]["verified_rows"] == a["mtp"]["proposed"] + a["mtp"]["rounds"]
     plain.close()
     backend.model.close()
+
+
+def test_plan_generation_answers_the_largest_context_that_fits():
+    """generation.rs:1114-1182 with a scripted planner: limits, validation order and the reply's fields."""
+    class Planning(ScriptedBackend):
+        def __init__(self, *a, fits=None, **kw):
+            super().__init__(*a, **kw)
+            self.fits, self.asked = fits, []
+
+        def plan_context_length(self, input_tokens, maximum, drafts):
+            self.asked.append((input_tokens, maximum, drafts))
+            return self.fits if self.fits is not None else maximum
+
+    plan = {"operation": "plan_generation", "input_tokens": 100, "context_tokens": 4000}
+    w = W.GenerationWorker(Planning([1], max_context=3000), W.Budget(16), False)
+    assert _ask(w, plan) == [{"context_tokens": 3000, "max_new_tokens": 2900, "context_capacity_known": True, "budget_kind": "memory"}]
+    assert w.backend.asked == [(100, 3000, 0)]                                   # capped by the model's limit
+    assert _ask(w, dict(plan, context_tokens=500))[0]["context_tokens"] == 500   # and by the request's
+    for bad in (dict(plan, input_tokens=0), dict(plan, context_tokens=100), dict(plan, input_token_ids=[1, 2]),
+                dict(plan, input_tokens=2, input_token_ids=[1, 100]), dict(plan, cache_scope="ab" * 16),
+                dict(plan, mtp=True, mtp_drafts=1)):
+        assert _ask(w, bad) == [{"error": "invalid_generation_request"}], bad
+    assert _ask(w, dict(plan, mtp=True)) == [{"error": "mtp_not_supported"}]
+    assert _ask(w, dict(plan, extra=1)) == [{"error": "invalid_request"}]
+    assert _ask(w, dict(plan, input_tokens=2, input_token_ids=[1, 2]))[0]["max_new_tokens"] == 2998
+    # the planner's answer is checked: nothing fits, or an answer outside (input, maximum]
+    for fits in (0, 100, 3001):
+        w = W.GenerationWorker(Planning([1], max_context=3000, fits=fits), W.Budget(16), False)
+        assert _ask(w, plan) == [{"error": "resource_budget_exceeded"}]
+    w = W.GenerationWorker(Planning([1], max_context=3000, fits=1200), W.Budget(16), False)
+    assert _ask(w, plan)[0] == {"context_tokens": 1200, "max_new_tokens": 1100, "context_capacity_known": True,
+                                "budget_kind": "memory"}
+    # a planning request does not disturb a retained prefix, anything unknown does
+    assert _ask(_worker([1]), plan) == [{"error": "context_planning_unavailable"}]
