@@ -433,6 +433,52 @@ class DenseOracle:
         return (logits, hidden) if want_hidden else logits
 
 
+class MtpHeadOracle:
+    """The dense multi-token-prediction head on the CPU (``so_mtp_head_step``): fusion of the token's embedding
+    with the target's normalized hidden row, one decoder layer with its own cache, output norm, the target's
+    read-out.  ``target`` is the ``DenseOracle`` whose tables and dimensions it shares; ``head`` is the dict of
+    ``stark_b200.synthetic.mtp_weights``."""
+
+    def __init__(self, target: "DenseOracle", head: dict, capacity: int):
+        self.target, self.head, cfg = target, head, target.cfg
+        lw = head["layer"]
+        self._layer = _Layer(lw["attn_norm"].ctypes.data, lw["mlp_norm"].ctypes.data, lw["q_norm"].ctypes.data,
+                             lw["k_norm"].ctypes.data, _qmat(lw["qkv"]), _qmat(lw["o"]), _qmat(lw["upgate"]),
+                             _qmat(lw["down"]))
+        self._fusion = _qmat(head["fusion"])
+        kv_row = cfg["kv_heads"] * cfg["head_dim"]
+        self.keys = np.zeros((capacity, kv_row), np.uint16)
+        self.values = np.zeros((capacity, kv_row), np.uint16)
+        self._state = _State(self.keys.ctypes.data, self.values.ctypes.data, capacity, 0)
+
+    @property
+    def position(self) -> int:
+        return int(self._state.position)
+
+    def rewind(self, position: int) -> None:
+        self._state.position = position
+
+    def _run(self, token: int, hidden, logits, out_hidden):
+        hidden = _c(hidden, np.uint16)
+        h = self.head
+        if lib().so_mtp_head_step(C.byref(self.target._model), C.byref(self._layer), C.byref(self._fusion),
+                                  _p(_c(h["embed_norm"], np.float32)), _p(_c(h["hidden_norm"], np.float32)),
+                                  _p(_c(h["out_norm"], np.float32)), C.byref(self._state), int(token), _p(hidden),
+                                  _p(logits), _p(out_hidden), self.target.threads):
+            raise ValueError("invalid token, geometry or context overflow")
+
+    def cache_row(self, token: int, hidden) -> None:
+        """A cache-only row: the pair (token, normalized hidden of the row before it)."""
+        self._run(token, hidden, None, None)
+
+    def step(self, token: int, hidden):
+        """(logits, normalized output): bf16 bit patterns; the output is the hidden of the next draft step."""
+        logits = np.empty(self.target.cfg["vocab"], np.uint16)
+        out = np.empty(self.target.cfg["hidden"], np.uint16)
+        self._run(token, hidden, logits, out)
+        return logits, out
+
+
 # ----------------------------------------------------------------------------- routed experts (f32 host path)
 
 def silu_f32(x: float) -> float:

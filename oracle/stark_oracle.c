@@ -696,6 +696,82 @@ int so_dense_step(const so_dense_model *m, so_dense_state *s, uint32_t token, ui
     return SO_OK;
 }
 
+/* One row through the dense multi-token-prediction head:
+ *   fuse     crates/stark-engine/src/encodable_block/qwen_mtp.rs:322-352 -- joined = [embedding_norm(e) ; hidden_norm(h)]
+ *            with e the embedding row of `token` and h the target's normalized hidden of the row before; fusion
+ *            linear [hidden, 2 hidden]
+ *   layer    the head's transformer: ONE decoder layer with its own cache, then its output norm (qwen_mtp.rs:277-300;
+ *            the layer is the graph of so_dense_step)
+ *   readout  the target's read-out over the normalized output; that output is also the hidden of the next
+ *            draft step (crates/stark-engine/src/engine/language_model/dense_mtp.rs:291-372)
+ * `m` supplies the dimensions, the embedding table and the read-out; `s` is the head's own one-layer cache.
+ * logits_out and hidden_out both NULL: cache-only row (qwen_mtp.rs:302-320, keys and values only). */
+int so_mtp_head_step(const so_dense_model *m, const so_dense_layer *L, const so_qmat *fusion, const float *embed_norm,
+                     const float *hidden_norm, const float *out_norm, so_dense_state *s, uint32_t token,
+                     const uint16_t *hidden_in, uint16_t *logits_out, uint16_t *hidden_out, int threads) {
+    if (s->position >= s->capacity || token >= m->vocab) return SO_INVALID;
+    const uint32_t D = m->hidden, hd = m->head_dim, QH = m->q_heads, KH = m->kv_heads, I = m->inter;
+    if (fusion->n != D || fusion->k != 2 * D) return SO_INVALID;
+    const uint32_t qkv_n = (QH + 2 * KH) * hd;
+    const size_t kv_row = (size_t)KH * hd;
+    uint16_t *joined = (uint16_t *)malloc(2 * (size_t)2 * D);
+    uint16_t *hidden = (uint16_t *)malloc(2 * (size_t)D);
+    uint16_t *shortcut = (uint16_t *)malloc(2 * (size_t)D);
+    uint16_t *normed = (uint16_t *)malloc(2 * (size_t)D);
+    uint16_t *qkv = (uint16_t *)malloc(2 * (size_t)qkv_n);
+    uint16_t *attn = (uint16_t *)malloc(2 * (size_t)QH * hd);
+    uint16_t *fused = (uint16_t *)malloc(2 * (size_t)2 * I);
+    uint16_t *act = (uint16_t *)malloc(2 * (size_t)I);
+    uint16_t *tmp = (uint16_t *)malloc(2 * (size_t)hd);
+    float *cosines = (float *)malloc(4 * (size_t)hd), *sines = (float *)malloc(4 * (size_t)hd);
+    const uint32_t pos = s->position;
+    so_rope_coeffs(pos, hd, m->rope_theta, cosines, sines);
+    const float scale = 1.0f / sqrtf((float)hd);
+
+    so_embedding_row_bf16(m->embed.codes, m->embed.scales, m->embed.biases, token, m->vocab, D, m->embed.bits,
+                          m->embed.group, hidden);
+    so_rmsnorm_bf16(hidden, embed_norm, joined, shortcut, 1, D, m->eps, 0);
+    so_rmsnorm_bf16(hidden_in, hidden_norm, joined + D, shortcut, 1, D, m->eps, 0);
+    qmv(fusion, joined, hidden, threads);
+
+    so_rmsnorm_bf16(hidden, L->attn_norm, normed, shortcut, 1, D, m->eps, 0);
+    qmv(&L->qkv, normed, qkv, threads);
+    so_head_norm_bf16(qkv, L->q_norm, 0, QH, hd, m->eps);
+    so_head_norm_bf16(qkv, L->k_norm, QH, KH, hd, m->eps);
+    uint16_t *kc = s->keys + (size_t)pos * kv_row, *vc = s->values + (size_t)pos * kv_row;
+    for (uint32_t h = 0; h < QH; h++) {
+        so_rope_head_bf16(qkv + (size_t)h * hd, tmp, cosines, sines, hd);
+        memcpy(qkv + (size_t)h * hd, tmp, 2 * (size_t)hd);
+    }
+    for (uint32_t h = 0; h < KH; h++)
+        so_rope_head_bf16(qkv + (size_t)(QH + h) * hd, kc + (size_t)h * hd, cosines, sines, hd);
+    memcpy(vc, qkv + (size_t)(QH + KH) * hd, 2 * kv_row);
+    s->position = pos + 1;
+    if (logits_out || hidden_out) {
+        so_attention_decode_bf16(qkv, s->keys, s->values, attn, QH, KH, hd, pos + 1, scale, threads);
+        qmv(&L->o, attn, hidden, threads);
+        so_rmsnorm_bf16(hidden, L->mlp_norm, normed, shortcut, 1, D, m->eps, 1);
+        qmv(&L->upgate, normed, fused, threads);
+        so_swiglu_bf16(fused, act, I);
+        qmv(&L->down, act, hidden, threads);
+        so_rmsnorm_bf16(hidden, out_norm, normed, shortcut, 1, D, m->eps, 1);
+        if (hidden_out) memcpy(hidden_out, normed, 2 * (size_t)D);
+        if (logits_out) qmv(&m->lm_head, normed, logits_out, threads);
+    }
+    free(joined);
+    free(hidden);
+    free(shortcut);
+    free(normed);
+    free(qkv);
+    free(attn);
+    free(fused);
+    free(act);
+    free(tmp);
+    free(cosines);
+    free(sines);
+    return SO_OK;
+}
+
 int so_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

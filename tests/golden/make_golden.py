@@ -82,6 +82,20 @@ def build(full: bool = False) -> dict:
         toks.append(tok)
         tok = O.argmax_bf16(orc.step(tok))
     out["tiny_greedy"] = np.asarray(toks, np.uint32)
+    # the draft head of the dense multi-token-prediction path after a 24-token prompt: two chained draft steps
+    weights = S.dense_weights(cfg, seed=3, zero_point=7.5)
+    head_w = S.mtp_weights(cfg, seed=3, zero_point=7.5)
+    target = O.DenseOracle(cfg, weights, capacity=64)
+    head = O.MtpHeadOracle(target, head_w, 64)
+    prompt = S.prompt(cfg, 24, seed=17)
+    for i, t in enumerate(prompt):
+        logits, hidden = target.step(int(t), want_hidden=True)
+        if i + 1 < len(prompt):
+            head.cache_row(int(prompt[i + 1]), hidden)
+    first, out_hidden = head.step(O.argmax_bf16(logits), hidden)
+    second, _ = head.step(O.argmax_bf16(first), out_hidden)
+    out["tiny_mtp_draft_logits"] = np.stack([first, second]).astype(np.uint16)
+    out["tiny_mtp_draft_hidden"] = np.asarray(out_hidden, np.uint16)
     rng = np.random.default_rng(11)
     out["q8_0_row"] = O.gguf_decode_row(O.Q8_0, S.q8_0_rows(rng, 4, 512)[1], 512)
     out["q4_k_row"] = O.gguf_decode_row(O.Q4_K, S.q4_k_rows(rng, 4, 512)[1], 512)

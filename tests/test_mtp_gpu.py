@@ -160,3 +160,57 @@ def test_held_rounds_leave_the_decision_to_the_caller():
         spec.mtp_round(pending, 1)                               # an open round has to be closed first
     plain.close()
     spec.close()
+
+
+@pytest.mark.parametrize("name,prompt_len", [("tiny", 24), ("small", 70)])
+def test_rounds_against_the_cpu_restatement_of_the_head(name, prompt_len):
+    """Draft head and verify pass against the oracle (`so_mtp_head_step`, `so_dense_step`): the head's proposals are
+    the oracle head's picks up to bf16 near-ties (the oracle is fed the engine's proposals, so the two chains stay on
+    the same prefix), every verified row's logits are inside the logits acceptance, and after commits that keep 0, 1
+    or 2 proposals the next round still agrees -- which it cannot unless both caches were repaired the same way."""
+    from oracle import oracle as O
+    from tests.test_model_gpu import assert_logits_accepted, pick_near_top
+    cfg, plain, spec = _models(name, 512)
+    plain.close()
+    w = S.dense_weights(cfg, seed=3, zero_point=7.5)
+    hw = S.mtp_weights(cfg, seed=3, zero_point=7.5)
+    target = O.DenseOracle(cfg, w, capacity=512)
+    head = O.MtpHeadOracle(target, hw, 512)
+    prompt = S.prompt(cfg, prompt_len, seed=17)
+    spec.prefill(prompt)
+    for i, tok in enumerate(prompt):                             # the oracle's prompt: target rows, head pairs
+        logits, hidden = target.step(int(tok), want_hidden=True)
+        if i + 1 < len(prompt):
+            head.cache_row(int(prompt[i + 1]), hidden)
+    assert_logits_accepted(logits, spec.logits_bf16())
+    pending = spec.mtp_initial()
+    assert pick_near_top(logits, pending)
+    near, strict, rows_checked = 0, 0, 0
+    for keep in (0, 1, 2, 0, 2, 1):
+        r = spec.mtp_round(pending, 3, held=True)
+        proposals = r["tokens"][1:]
+        prefix = head.position
+        tok, hid = pending, hidden
+        for d in proposals:                                      # the head's chain, teacher-forced on the engine's picks
+            lg, hid = head.step(tok, hid)
+            near += int(pick_near_top(lg, d, 2.0))
+            strict += int(O.argmax_bf16(lg) == d)
+            tok = d
+        kept = proposals[:keep]
+        hiddens = []
+        for i, x in enumerate([pending] + kept):                 # the verify rows that stay
+            lg, hidden = target.step(int(x), want_hidden=True)
+            assert_logits_accepted(lg, O.f32_to_bf16(spec.mtp_row_logits(i)))
+            hiddens.append(hidden)
+            rows_checked += 1
+        pick = int(np.argmax(spec.mtp_row_logits(keep)))
+        assert pick_near_top(lg, pick)
+        done = spec.mtp_commit(keep, pick)
+        assert done["tokens"] == [pending] + kept
+        head.rewind(prefix + 1)                                  # the first draft row stays, the rest is replayed
+        for i, d in enumerate(kept):
+            head.cache_row(int(d), hiddens[i])
+        hidden, pending = hiddens[keep], pick
+    assert near == 18 and strict >= 15, (near, strict)
+    assert rows_checked == 12 and spec.position == target.position == head.position + 1
+    spec.close()
