@@ -10,6 +10,25 @@ namespace sb {
 
 namespace {
 
+// A launch that may begin while the kernel before it is still running (programmatic stream serialization): the
+// kernels launched through this call griddepcontrol.wait before they touch anything that kernel writes.
+template <typename... Params, typename... Args>
+cudaError_t launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
+
 // ------------------------------------------------------------------------------------------ embedding rows
 // input_embedding_lookup.rs:17-160: row `token` of the quantized table, scale * code + bias with two roundings,
 // then bf16.  Same record arithmetic as embedding_row_kernel (ops.cu), one row per blockIdx.y.
@@ -105,14 +124,29 @@ __global__ void __launch_bounds__(1024) argmax_rows_kernel(const uint16_t *__res
     const uint16_t *row = rows + (size_t)blockIdx.x * n;
     float best = -INFINITY;
     uint32_t bi = 0xffffffffu;
-    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
-        const float v = bf16_bits_to_f32(row[i]);
+    auto consider = [&](uint32_t bits, uint32_t i) {
+        const float v = bf16_bits_to_f32((uint16_t)bits);
         const float key = isfinite(v) ? v : INFINITY;  // a non-finite logit must surface
         if (key > best || (key == best && i < bi)) {
             best = key;
             bi = i;
         }
+    };
+    // eight values per 16-byte load where the row allows it (the loads of several iterations are in flight at
+    // once: they do not depend on the comparisons), the rest one by one
+    const bool wide = ((reinterpret_cast<uintptr_t>(row) | ((size_t)n * 2u)) & 15u) == 0;
+    const uint32_t chunks = wide ? n / 8u : 0u;
+#pragma unroll 4
+    for (uint32_t c = threadIdx.x; c < chunks; c += blockDim.x) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(row) + c);
+        const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (uint32_t e = 0; e < 4; ++e) {
+            consider(w4[e] & 0xffffu, c * 8u + 2u * e);
+            consider(w4[e] >> 16, c * 8u + 2u * e + 1u);
+        }
     }
+    for (uint32_t i = chunks * 8u + threadIdx.x; i < n; i += blockDim.x) consider(row[i], i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
@@ -153,6 +187,8 @@ __global__ void __launch_bounds__(128) rope_append_rows_kernel(const RopeParams 
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t head = blockIdx.x * 4u + warp, row = blockIdx.y;
     const uint32_t heads = p.q_heads + 2u * p.kv_heads;
+    pdl_launch_dependents();
+    pdl_wait();  // the rows come from the projection before this launch
     if (head >= heads) return;
     const uint32_t pos = p.first_pos + row;
     uint16_t *src = p.qkv + ((size_t)row * heads + head) * kHeadDim;
@@ -208,6 +244,8 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t kvh = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait();  // query rows and the appended cache rows come from the launch before this one
     const uint32_t rows_per_cta = 16u * p.row_blocks;
     // causal: a block of late rows reads the most keys, so the late blocks are issued first and the short ones fill
     // the tail of the launch
@@ -395,6 +433,7 @@ __global__ void __launch_bounds__(kHeadDim) prefill_attention_merge_kernel(const
                                                                            uint32_t q_heads, uint32_t splits) {
     const uint32_t row = blockIdx.x, head = blockIdx.y, d = threadIdx.x;
     pdl_launch_dependents();  // a matvec that follows may start filling its weight ring; it awaits this grid itself
+    pdl_wait();               // the partials come from the launch before this one
     const float *src = partials + ((size_t)row * q_heads + head) * splits * kPartialFloats;
     float top = -INFINITY;
     for (uint32_t s = 0; s < splits; ++s) top = fmaxf(top, src[(size_t)s * kPartialFloats]);
@@ -443,8 +482,7 @@ stark_b200_status rope_append_rows_launch(const RopeAppendArgs &a, cudaStream_t 
     RopeParams p{a.qkv, a.kv.keys, a.kv.values, a.block_table, a.q_norm, a.k_norm, a.rope_cos, a.rope_sin,
                  a.first_pos, a.q_heads, a.kv_heads, a.eps};
     const uint32_t heads = a.q_heads + 2u * a.kv_heads;
-    rope_append_rows_kernel<<<dim3((heads + 3u) / 4u, a.m), 128, 0, stream>>>(p);
-    SB_CUDA(cudaGetLastError());
+    SB_CUDA(launch_dependent(rope_append_rows_kernel, dim3((heads + 3u) / 4u, a.m), dim3(128), 0, stream, p));
     return STARK_B200_OK;
 }
 
@@ -481,7 +519,7 @@ stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_
         p.row_blocks = 1;
         if (splits) {
             if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<8, true>, (int)smem, once8s)) return s;
-            prefill_attention_kernel<8, true><<<dim3(1, a.kv_heads, splits), 256, smem, stream>>>(p);
+            SB_CUDA(launch_dependent(prefill_attention_kernel<8, true>, dim3(1, a.kv_heads, splits), dim3(256), smem, stream, p));
         } else {
             if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<8, false>, (int)smem, once8)) return s;
             prefill_attention_kernel<8, false><<<dim3((a.m + 15u) / 16u, a.kv_heads), 256, smem, stream>>>(p);
@@ -491,7 +529,7 @@ stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_
         const uint32_t rows_per_cta = 16u * p.row_blocks;
         if (splits) {
             if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<4, true>, (int)smem, once4s)) return s;
-            prefill_attention_kernel<4, true><<<dim3(1, a.kv_heads, splits), 128, smem, stream>>>(p);
+            SB_CUDA(launch_dependent(prefill_attention_kernel<4, true>, dim3(1, a.kv_heads, splits), dim3(128), smem, stream, p));
         } else {
             if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<4, false>, (int)smem, once4)) return s;
             prefill_attention_kernel<4, false><<<dim3((a.m + rows_per_cta - 1u) / rows_per_cta, a.kv_heads), 128, smem, stream>>>(p);
@@ -499,8 +537,8 @@ stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_
     }
     SB_CUDA(cudaGetLastError());
     if (splits) {
-        prefill_attention_merge_kernel<<<dim3(a.m, a.q_heads), kHeadDim, 0, stream>>>(a.partials, a.out, a.q_heads, splits);
-        SB_CUDA(cudaGetLastError());
+        SB_CUDA(launch_dependent(prefill_attention_merge_kernel, dim3(a.m, a.q_heads), dim3(kHeadDim), 0, stream, a.partials,
+                                 a.out, a.q_heads, splits));
     }
     return STARK_B200_OK;
 }

@@ -64,7 +64,7 @@ __host__ __device__ inline MultiSmem multi_layout(uint32_t num_stages, uint32_t 
     off += m * L.x_row_bytes;
     off = (off + 15u) & ~15u;
     L.xsum = off;
-    off += m * (columns / 64u) * 4u;
+    off += 8u * (columns / 64u) * 4u;  // [group][8 rows]: the two rows a lane needs are one 8-byte load
     off = (off + 15u) & ~15u;
     L.red = off;
     off += kRed * kCW * 128u * 4u;
@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_multi_a4_kernel(const MultiPa
             if (mine) *reinterpret_cast<uint4 *>(xs + (size_t)r * L.x_row_bytes + tid * 16u) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) s8 += __shfl_xor_sync(0xffffffffu, s8, o);
-            if (mine && (lane & 7u) == 0) xsum[r * p.groups + (tid >> 3)] = s8;
+            if (mine && (lane & 7u) == 0) xsum[(tid >> 3) * 8u + r] = s8;
         }
     } else {
         pdl_wait();
@@ -286,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_multi_a4_kernel(const MultiPa
                 if (idx < total) {
                     const uint32_t r = idx / chunks, c = idx - r * chunks;
                     *reinterpret_cast<uint4 *>(xs + (size_t)r * L.x_row_bytes + c * 16u) = v[u];
-                    if ((lane & 7u) == 0) xsum[r * p.groups + (c >> 3)] = s8;
+                    if ((lane & 7u) == 0) xsum[(c >> 3) * 8u + r] = s8;
                 }
             }
         }
@@ -297,8 +297,8 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_multi_a4_kernel(const MultiPa
     const uint32_t g = lane >> 2, t = lane & 3u;
     const uint32_t xrow = g < p.m ? g : 0u;  // columns of the tensor-core tile beyond the last row repeat row 0
     const uint8_t *my_x = xs + (size_t)xrow * L.x_row_bytes + t * 32u;
-    const float *xsum_a = xsum + (2u * t < p.m ? 2u * t : 0u) * p.groups;
-    const float *xsum_b = xsum + (2u * t + 1u < p.m ? 2u * t + 1u : 0u) * p.groups;
+    const float *my_xsum = xsum + 2u * t;  // rows 2t and 2t + 1 of a group (rows past the last one hold stale values
+                                           // whose results nobody reads)
     uint32_t slot = 0, phase = 0, rb = 0, rphase = 1;
     for (uint32_t tile = t0; tile < t1; ++tile) {
         float acc[2][2] = {{0.0f, 0.0f}, {0.0f, 0.0f}};  // [matrix row g, g + 8][input row 2t, 2t + 1]
@@ -319,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_multi_a4_kernel(const MultiPa
                     const uint4 xa = xp[0], xb = xp[1];
                     const uint32_t ww[4] = {wq.x, wq.y, wq.z, wq.w};
                     const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-                    float c[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    float c[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const uint32_t magic = 0x43004300u, mask = 0x000f000fu;  // bf16 pair (128 + q, 128 + q')
@@ -327,12 +327,21 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_multi_a4_kernel(const MultiPa
                         const uint32_t a1 = lop3_and_or(ww[j] >> 4, mask, magic);
                         const uint32_t a2 = lop3_and_or(ww[j] >> 8, mask, magic);
                         const uint32_t a3 = lop3_and_or(ww[j] >> 12, mask, magic);
-                        mma_m16n8k16_bf16(c, a0, a1, a2, a3, xw[2 * j], xw[2 * j + 1]);
+                        if (j == 0) {  // the record's first product starts from zero: no accumulator to clear
+                            asm volatile(
+                                "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+                                "{%10,%10,%10,%10};"
+                                : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+                                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(xw[0]), "r"(xw[1]), "f"(0.0f));
+                        } else {
+                            mma_m16n8k16_bf16(c, a0, a1, a2, a3, xw[2 * j], xw[2 * j + 1]);
+                        }
                     }
                     const float s0 = __uint_as_float(sw << 16), s1 = __uint_as_float(sw & 0xffff0000u);
                     const float b0 = fmaf(-128.0f, s0, __uint_as_float(bw << 16));
                     const float b1 = fmaf(-128.0f, s1, __uint_as_float(bw & 0xffff0000u));
-                    const float xa_sum = xsum_a[kg], xb_sum = xsum_b[kg];
+                    const float2 xs2 = *reinterpret_cast<const float2 *>(my_xsum + kg * 8u);
+                    const float xa_sum = xs2.x, xb_sum = xs2.y;
                     acc[0][0] = fmaf(b0, xa_sum, fmaf(s0, c[0], acc[0][0]));
                     acc[0][1] = fmaf(b0, xb_sum, fmaf(s0, c[1], acc[0][1]));
                     acc[1][0] = fmaf(b1, xa_sum, fmaf(s1, c[2], acc[1][0]));
