@@ -257,38 +257,34 @@ __global__ void __launch_bounds__(kThreads, 1) qmv_multi_a4_kernel(const MultiPa
         }
     } else {
         pdl_wait();
-        // chunk c of row r: copied to shared memory, summed per group of 8 chunks (8 consecutive lanes)
+        // Every 16-byte chunk of every row goes global -> shared memory as an asynchronous copy, all of them in
+        // flight at once (one trip to L2 instead of one per batch of registers); the per-group sums are then formed
+        // from shared memory: chunk c of row r by the lane that copied it, 8 consecutive lanes per group.
         const uint32_t total = p.m * chunks;
-        for (uint32_t base = 0; base < total; base += kConsumerThreads * 4u) {
-            uint4 v[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t idx = base + u * kConsumerThreads + tid;
-                if (idx < total) {
-                    const uint32_t r = idx / chunks, c = idx - r * chunks;
-                    v[u] = reinterpret_cast<const uint4 *>(p.x + (size_t)r * p.x_stride)[c];
-                } else {
-                    v[u] = make_uint4(0u, 0u, 0u, 0u);
-                }
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const uint32_t idx = base + u * kConsumerThreads + tid;
-                const uint32_t wv[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-                float s8 = 0.0f;
+        for (uint32_t idx = tid; idx < total; idx += kConsumerThreads) {
+            const uint32_t r = idx / chunks, c = idx - r * chunks;
+            cp_async16(xs + (size_t)r * L.x_row_bytes + c * 16u, reinterpret_cast<const uint4 *>(p.x + (size_t)r * p.x_stride) + c);
+        }
+        cp_async_commit();
+        cp_async_wait<0>();
+        for (uint32_t base = 0; base < total; base += kConsumerThreads) {
+            const uint32_t idx = base + tid;
+            float s8 = 0.0f;
+            uint32_t r = 0, c = 0;
+            if (idx < total) {
+                r = idx / chunks;
+                c = idx - r * chunks;
+                const uint4 v = *reinterpret_cast<const uint4 *>(xs + (size_t)r * L.x_row_bytes + c * 16u);  // this thread's own copy
+                const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     s8 += __uint_as_float(wv[i] << 16);
                     s8 += __uint_as_float(wv[i] & 0xffff0000u);
                 }
-#pragma unroll
-                for (int o = 1; o < 8; o <<= 1) s8 += __shfl_xor_sync(0xffffffffu, s8, o);
-                if (idx < total) {
-                    const uint32_t r = idx / chunks, c = idx - r * chunks;
-                    *reinterpret_cast<uint4 *>(xs + (size_t)r * L.x_row_bytes + c * 16u) = v[u];
-                    if ((lane & 7u) == 0) xsum[(c >> 3) * 8u + r] = s8;
-                }
             }
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) s8 += __shfl_xor_sync(0xffffffffu, s8, o);
+            if (idx < total && (lane & 7u) == 0) xsum[(c >> 3) * 8u + r] = s8;
         }
     }
     named_bar_sync(1, kConsumerThreads);
