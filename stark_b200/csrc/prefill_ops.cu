@@ -5,6 +5,7 @@
 
 #include "device_math.cuh"
 #include "prefill.cuh"
+#include "tunables.cuh"
 
 namespace sb {
 
@@ -428,6 +429,205 @@ __global__ void __launch_bounds__(WARPS * 32) prefill_attention_kernel(const Pre
     }
 }
 
+// A handful of rows (the verify pass of a speculative round) in the one-row kernel's form: the KEYS are the M rows of
+// both tensor-core products and the columns are (row, head of the group) pairs, 8 per column tile, so that no
+// tensor-core work is spent on padding rows (the 16-row tile kernel above runs 5 rows as 16):
+//   S^T[key, col] = K[key, :] Q_col^T          8 NT mma per 16 keys, the K fragments shared by the column tiles
+//   O^T[dim, col] += V^T[dim, key] P^T         16 NT mma per 16 keys (P as bf16 hi + lo), the V fragments shared
+// One CTA per (KV head, split of the key tiles); each of its four warps owns 16 keys of a 64-key tile with its own
+// online softmax per column, merged once at the end; the causal limit is per column (row r sees keys up to
+// first_pos + r).  Query rows are already normalized and rotated, the new keys and values already in the cache
+// (rope_append_rows_kernel).  Partials go where prefill_attention_merge_kernel expects them.
+template <int NT>
+__global__ void __launch_bounds__(128) rows_attention_kernel(const PrefillAttnParams p) {
+    extern __shared__ __align__(128) uint8_t ra_smem[];  // [2][K, V][64 rows][272 B], reused for the warps' outputs
+    __shared__ float ml_s[4][NT * 8][2];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t g = lane >> 2, t = lane & 3u;
+    const uint32_t kvh = blockIdx.y, G = p.gqa, ncols = p.m * G;
+    pdl_launch_dependents();
+    pdl_wait();  // query rows and the appended cache rows come from the launch before this one
+    const uint32_t heads = p.q_heads + 2u * p.kv_heads;
+    const uint32_t all_tiles = (p.first_pos + p.m - 1u) / kPageTokens + 1u;
+    const uint32_t tile_begin = (uint32_t)((uint64_t)all_tiles * blockIdx.z / p.splits);
+    const uint32_t tile_end = (uint32_t)((uint64_t)all_tiles * (blockIdx.z + 1u) / p.splits);
+
+    auto issue_tile = [&](uint32_t tile, uint32_t buf) {
+        const size_t page = ((size_t)p.block_table[tile] * p.kv_heads + kvh) * kPageTokens * kHeadDim;
+        const uint8_t *ksrc = reinterpret_cast<const uint8_t *>(p.keys + page);
+        const uint8_t *vsrc = reinterpret_cast<const uint8_t *>(p.values + page);
+        uint8_t *kd = ra_smem + (size_t)(buf * 2u) * kTileBytes, *vd = kd + kTileBytes;
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) {  // 64 rows x 16 chunks of 16 B per tile
+            const uint32_t idx = tid + i * 128u, r = idx >> 4, ch = idx & 15u;
+            cp_async16(kd + r * kTileRowBytes + ch * 16u, ksrc + r * 256u + ch * 16u);
+            cp_async16(vd + r * kTileRowBytes + ch * 16u, vsrc + r * 256u + ch * 16u);
+        }
+    };
+    if (tile_begin < tile_end) issue_tile(tile_begin, 0);
+    cp_async_commit();
+    if (tile_begin + 1u < tile_end) issue_tile(tile_begin + 1u, 1);
+    cp_async_commit();
+
+    // Q^T as the B operand: lane (g, t) holds column 8 j + g, dims 16 kk + {2t, 2t+1} and + 8
+    uint32_t qb[NT][8][2];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const uint32_t col = 8u * j + g;
+        const uint16_t *q = col < ncols ? p.qkv + ((size_t)(col / G) * heads + kvh * G + col % G) * kHeadDim : nullptr;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+            qb[j][kk][0] = q ? *reinterpret_cast<const uint32_t *>(q + kk * 16 + 2 * t) : 0u;
+            qb[j][kk][1] = q ? *reinterpret_cast<const uint32_t *>(q + kk * 16 + 8 + 2 * t) : 0u;
+        }
+    }
+    // last key each of this lane's columns (8 j + 2t, + 1 in the accumulator layout) may see; -1: no such column
+    int32_t limit[NT][2];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const uint32_t col = 8u * j + 2u * t + e;
+            limit[j][e] = col < ncols ? (int32_t)(p.first_pos + col / G) : -1;
+        }
+    float m_run[NT][2], l_run[NT][2], o[NT][8][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        m_run[j][0] = m_run[j][1] = -INFINITY;
+        l_run[j][0] = l_run[j][1] = 0.0f;
+#pragma unroll
+        for (int mt = 0; mt < 8; ++mt) o[j][mt][0] = o[j][mt][1] = o[j][mt][2] = o[j][mt][3] = 0.0f;
+    }
+    const uint32_t lrow = lane & 7u, lmat = lane >> 3;
+    const uint32_t k0 = warp * 16u;
+    const int32_t last_key = (int32_t)(p.first_pos + p.m - 1u);
+
+    for (uint32_t tile = tile_begin; tile < tile_end; ++tile) {
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t buf = (tile - tile_begin) & 1u;
+        const uint8_t *kt = ra_smem + (size_t)(buf * 2u) * kTileBytes, *vt = kt + kTileBytes;
+        const int32_t key_a = (int32_t)(tile * kPageTokens + k0 + g), key_b = key_a + 8;
+        if ((int32_t)(tile * kPageTokens + k0) <= last_key) {  // some column sees a key of this warp's slab
+            float sc[NT][4];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.0f;
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk) {
+                uint32_t ka[4];
+                ldmatrix_x4(ka, kt + (k0 + (lmat & 1u) * 8u + lrow) * kTileRowBytes + (kk * 16u + (lmat >> 1) * 8u) * 2u);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) mma_m16n8k16_bf16(sc[j], ka[0], ka[1], ka[2], ka[3], qb[j][kk][0], qb[j][kk][1]);
+            }
+            uint32_t bh[NT][2], bl[NT][2];
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                float e4[4], factor[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float sa = key_a <= limit[j][e] ? sc[j][e] * p.scale : -INFINITY;
+                    const float sb = key_b <= limit[j][e] ? sc[j][2 + e] * p.scale : -INFINITY;
+                    float tm = fmaxf(sa, sb);
+                    tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 4));
+                    tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 8));
+                    tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 16));
+                    const float m_new = fmaxf(m_run[j][e], tm);
+                    const bool none = m_new == -INFINITY;  // the column sees no key so far
+                    factor[e] = m_run[j][e] == -INFINITY ? 0.0f : expf(m_run[j][e] - m_new);
+                    e4[e] = none ? 0.0f : expf(sa - m_new);
+                    e4[2 + e] = none ? 0.0f : expf(sb - m_new);
+                    float ts = e4[e] + e4[2 + e];
+                    ts += __shfl_xor_sync(0xffffffffu, ts, 4);
+                    ts += __shfl_xor_sync(0xffffffffu, ts, 8);
+                    ts += __shfl_xor_sync(0xffffffffu, ts, 16);
+                    l_run[j][e] = l_run[j][e] * factor[e] + ts;
+                    m_run[j][e] = m_new;
+                }
+#pragma unroll
+                for (int mt = 0; mt < 8; ++mt) {
+                    o[j][mt][0] *= factor[0];
+                    o[j][mt][1] *= factor[1];
+                    o[j][mt][2] *= factor[0];
+                    o[j][mt][3] *= factor[1];
+                }
+                uint32_t ph[2], pl[2];
+                split_bf16x2(e4[0], e4[1], ph[0], pl[0]);
+                split_bf16x2(e4[2], e4[3], ph[1], pl[1]);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    bh[j][i] = movmatrix_trans(ph[i]);
+                    bl[j][i] = movmatrix_trans(pl[i]);
+                }
+            }
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                uint32_t va4[4];
+                ldmatrix_x4_trans(va4, vt + (k0 + (lmat >> 1) * 8u + lrow) * kTileRowBytes + (mt * 16u + (lmat & 1u) * 8u) * 2u);
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    mma_m16n8k16_bf16(o[j][mt], va4[0], va4[1], va4[2], va4[3], bh[j][0], bh[j][1]);
+                    mma_m16n8k16_bf16(o[j][mt], va4[0], va4[1], va4[2], va4[3], bl[j][0], bl[j][1]);
+                }
+            }
+        }
+        __syncthreads();  // the buffer of this tile is free for tile + 2
+        if (tile + 2u < tile_end) issue_tile(tile + 2u, buf);
+        cp_async_commit();
+    }
+    cp_async_wait<0>();
+
+    // ---- merge the four warps' states, publish this split's partial (max, sum, unnormalized output) per column
+    if (g == 0) {
+#pragma unroll
+        for (int j = 0; j < NT; ++j)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                ml_s[warp][8 * j + 2 * t + e][0] = m_run[j][e];
+                ml_s[warp][8 * j + 2 * t + e][1] = l_run[j][e];
+            }
+    }
+    __syncthreads();  // also: nobody reads the tiles any more
+    float *o_s = reinterpret_cast<float *>(ra_smem);  // [4 warps][NT * 8 columns][128] f32
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const uint32_t col = 8u * j + 2u * t + e;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mx = fmaxf(mx, ml_s[w][col][0]);
+            const float f = m_run[j][e] == -INFINITY ? 0.0f : expf(m_run[j][e] - mx);
+            float *dst = o_s + ((size_t)warp * (NT * 8) + col) * kHeadDim;
+#pragma unroll
+            for (int mt = 0; mt < 8; ++mt) {
+                dst[mt * 16 + g] = o[j][mt][e] * f;
+                dst[mt * 16 + g + 8] = o[j][mt][2 + e] * f;
+            }
+        }
+    __syncthreads();
+    for (uint32_t i = tid; i < ncols * kHeadDim; i += 128u) {
+        const uint32_t col = i >> 7, d = i & 127u;
+        float acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) acc += o_s[((size_t)w * (NT * 8) + col) * kHeadDim + d];
+        float *dst = p.partials + (((size_t)(col / G) * p.q_heads + kvh * G + col % G) * p.splits + blockIdx.z) * kPartialFloats;
+        dst[4 + d] = acc;
+    }
+    if (tid < ncols) {
+        float mx = -INFINITY, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, ml_s[w][tid][0]);
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = ml_s[w][tid][0];
+            l += mw == -INFINITY ? 0.0f : ml_s[w][tid][1] * expf(mw - mx);
+        }
+        float *dst = p.partials + (((size_t)(tid / G) * p.q_heads + kvh * G + tid % G) * p.splits + blockIdx.z) * kPartialFloats;
+        dst[0] = mx;
+        dst[1] = l;
+    }
+}
+
 // out[row][head][d] = sum_s w_s o_s[d] / sum_s w_s l_s with w_s = exp(m_s - max m): one CTA per (row, head)
 __global__ void __launch_bounds__(kHeadDim) prefill_attention_merge_kernel(const float *partials, uint16_t *out,
                                                                            uint32_t q_heads, uint32_t splits) {
@@ -515,7 +715,16 @@ stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_
     }
     p.partials = a.partials;
     p.splits = splits;
-    if (gqa == 8u) {
+    const uint32_t column_tiles = (a.m * gqa + 7u) / 8u;
+    if (splits && column_tiles <= 4u && tunables().rows_attention) {
+        // a handful of (row, head) columns: the keys-as-rows form
+        static SmemOptIn once_rows[4];
+        void (*fn)(PrefillAttnParams) = column_tiles == 1u ? rows_attention_kernel<1>
+                                        : column_tiles == 2u ? rows_attention_kernel<2>
+                                        : column_tiles == 3u ? rows_attention_kernel<3> : rows_attention_kernel<4>;
+        if (stark_b200_status s = ensure_dynamic_smem(fn, (int)smem, once_rows[column_tiles - 1u])) return s;
+        SB_CUDA(launch_dependent(fn, dim3(1, a.kv_heads, splits), dim3(128), smem, stream, p));
+    } else if (gqa == 8u) {
         p.row_blocks = 1;
         if (splits) {
             if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<8, true>, (int)smem, once8s)) return s;
