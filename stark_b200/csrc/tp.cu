@@ -102,27 +102,42 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_residual_kernel(TpRe
     const unsigned long long t0 = global_ns();
     for (uint32_t i = (blockIdx.x * kReduceThreads + threadIdx.x) * 2u; i < g.hidden;
          i += kReduceCtas * kReduceThreads * 2u) {
-        float a0 = 0.0f, a1 = 0.0f;
+        // The packets of ALL ranks are requested in one trip to memory and checked together (a poll per rank in turn
+        // costs a round trip per rank even when every packet is already there: 8 of them at 8 ranks); a trip is
+        // repeated until every ticket is this exchange's.  The sum is formed in rank order afterwards, so every
+        // rank computes the same bits.
+        unsigned long long q0[kMaxTpRanks], q1[kMaxTpRanks];
         bool ok = true;
-        for (uint32_t r = 0; r < g.size && ok; ++r) {  // rank order: every rank computes the same bits
-            const unsigned long long *src = tp_recv(g.base[g.rank], buf, r, g.hidden) + i;
-            unsigned long long q0, q1;
-            uint32_t spins = 0;
-            for (;;) {
-                asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(q0), "=l"(q1) : "l"(src) : "memory");
-                if ((uint32_t)(q0 >> 32) == ticket && (uint32_t)(q1 >> 32) == ticket) break;
-                if (++spins > 8u) {
-                    __nanosleep(64);
-                    if (global_ns() - t0 > g.wait_ns) {
-                        atomicOr(error_word, kErrPeerTimeout);
-                        ok = false;
-                        break;
-                    }
+        uint32_t spins = 0;
+        for (;;) {
+            bool all = true;
+#pragma unroll
+            for (uint32_t r = 0; r < kMaxTpRanks; ++r) {
+                if (r < g.size) {
+                    const unsigned long long *src = tp_recv(g.base[g.rank], buf, r, g.hidden) + i;
+                    asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(q0[r]), "=l"(q1[r]) : "l"(src) : "memory");
                 }
             }
-            a0 += __uint_as_float((uint32_t)q0);
-            a1 += __uint_as_float((uint32_t)q1);
+#pragma unroll
+            for (uint32_t r = 0; r < kMaxTpRanks; ++r)
+                if (r < g.size) all = all && (uint32_t)(q0[r] >> 32) == ticket && (uint32_t)(q1[r] >> 32) == ticket;
+            if (all) break;
+            if (++spins > 8u) {
+                __nanosleep(64);
+                if (global_ns() - t0 > g.wait_ns) {
+                    atomicOr(error_word, kErrPeerTimeout);
+                    ok = false;
+                    break;
+                }
+            }
         }
+        float a0 = 0.0f, a1 = 0.0f;
+#pragma unroll
+        for (uint32_t r = 0; r < kMaxTpRanks; ++r)
+            if (r < g.size) {
+                a0 += __uint_as_float((uint32_t)q0[r]);
+                a1 += __uint_as_float((uint32_t)q1[r]);
+            }
         if (ok) {
             const uint32_t old = *reinterpret_cast<const uint32_t *>(h + i);
             const uint32_t s2 = f32x2_to_bf16x2(a0, a1);  // the projection's bf16 output
