@@ -76,6 +76,7 @@ Model::~Model() {
     cudaFree(pending);
     cudaFree(generated);
     cudaFree(trace);
+    cudaFree(tp_staged);
     cudaFree(mega_ops);
     cudaFree(mega_ingest_ops);
     cudaFree(mega_done);
@@ -326,7 +327,15 @@ static stark_b200_status issue_token(Model *m, bool full, uint32_t *launches) {
             std::swap(hcur, hnext);  // after this matvec the residual stream lives in the other buffer
         } else {
             TraceSlot *own = a.trace;  // the reduction takes the slot, the matvec the next one
-            consume_status = tp_reduce_residual_launch(m->tp, index, per_token, tokens, hcur, ctx->error_word, own, pdl, s);
+            if (tunables().tp_stage && m->tp_staged && a.prologue == kProRmsNorm) {
+                // the reduction holds the whole new row: it also normalizes and scales it for this matvec
+                consume_status = tp_reduce_stage_launch(m->tp, index, per_token, tokens, hcur, a.norm_weight, c.eps,
+                                                        m->tp_staged, ctx->error_word, own, pdl, s);
+                a.prologue = kProStaged;
+                a.staged = m->tp_staged;
+            } else {
+                consume_status = tp_reduce_residual_launch(m->tp, index, per_token, tokens, hcur, ctx->error_word, own, pdl, s);
+            }
             a.trace = slot(n++);
         }
     };
@@ -624,6 +633,8 @@ stark_b200_status model_tp_init(Model *m, uint32_t rank, uint32_t size, uint32_t
     SB_CUDA(cudaMemset(m->tp_local, 0, bytes));
     stark_b200_status st = dmalloc(&m->tp_seq, 4);
     if (st != STARK_B200_OK) return st;
+    SB_CUDA(cudaMalloc(&m->tp_staged, qmv_staged_bytes(m->cfg.hidden)));
+    SB_CUDA(cudaMemset(m->tp_staged, 0, qmv_staged_bytes(m->cfg.hidden)));
     SB_CUDA(cudaMemset(m->tp_seq, 0, 16u));
     SB_CUDA(cudaDeviceSynchronize());
     cudaIpcMemHandle_t handle;

@@ -82,6 +82,7 @@ struct Model {
     TpRegion tp{};
     uint8_t *tp_local = nullptr;   // this rank's exchange region
     uint32_t *tp_seq = nullptr;    // [0] tokens finished: the base of the exchange tickets
+    void *tp_staged = nullptr;     // the input row a reduction leaves ready for the matvec after it (qmv_staged_bytes)
     uint32_t tp_vocab_offset = 0, tp_vocab_total = 0;
     bool tp_connected = false, tp_stand_ins = false;
     // batched prompt ingest (prefill_model.cu): rows of one chunk, allocated at first use

@@ -57,6 +57,7 @@ struct QmvParams {
     void *y;
     const float *norm_weight;
     const uint16_t *norm_weight_bf16;
+    const void *staged;
     float eps;
     const void *resid;
     float *partial_max;
@@ -354,6 +355,31 @@ __device__ __forceinline__ void stage_input(const QmvParams &p, uint32_t tid, ui
 
 }
 
+// The prologue of a launch whose input row was staged by the kernel before it: scaled f16 values and per-group sums
+// are copied as they are (16-byte asynchronous copies), the factor that undoes the scale is one load.
+template <int CW>
+__device__ __forceinline__ void stage_input_staged(const QmvParams &p, uint32_t tid, uint32_t columns, __half *xs,
+                                                   float *xsum, float &xunscale) {
+    constexpr int kConsumerThreads = CW * 32;
+    pdl_wait();  // the staged row belongs to the previous kernel
+    if (tid == 0 && p.trace) {
+        trace_min(&p.trace->ready);
+        trace_max(&p.trace->ready_last);
+    }
+    const uint8_t *src = static_cast<const uint8_t *>(p.staged);
+    const uint32_t groups = columns / 64u;
+    for (uint32_t c = tid; c < columns / 8u; c += kConsumerThreads) cp_async16(reinterpret_cast<uint4 *>(xs) + c, src + 16u * c);
+    const uint8_t *sums = src + (size_t)columns * 2u;
+    for (uint32_t c = tid; c < groups / 4u; c += kConsumerThreads) cp_async16(reinterpret_cast<uint4 *>(xsum) + c, sums + 16u * c);
+    for (uint32_t g = (groups / 4u) * 4u + tid; g < groups; g += kConsumerThreads)
+        xsum[g] = __ldcg(reinterpret_cast<const float *>(sums) + g);
+    cp_async_commit();
+    xunscale = __ldcg(reinterpret_cast<const float *>(sums + (size_t)groups * 4u));
+    cp_async_wait<0>();
+    named_bar_sync(1, kConsumerThreads);
+    if (tid == 0 && p.trace) trace_max(&p.trace->compute);
+}
+
 // SPLIT: the input is f32 and is carried as two f16 terms (hi + lo) so that ~22 mantissa bits
 //        survive; bf16 inputs need one term.
 // RPW:   records per consumer warp per ring stage (stage = 8 * RPW records unless PRED).
@@ -534,7 +560,9 @@ __global__ void __maxnreg__(CW == 16 ? 56 : 80) qmv_a4_kernel(const QmvParams p)
     const bool norm = p.prologue == kProRmsNorm;
     // Two instances of the prologue: rows of up to 4096 values, and up to kMaxColumns.
     constexpr int kShortRounds = 4096 / (kConsumerThreads * 8), kLongRounds = (int)kMaxColumns / (kConsumerThreads * 8);
-    if (columns <= 4096u) {
+    if (p.prologue == kProStaged) {
+        stage_input_staged<CW>(p, tid, columns, xs, xsum, xunscale);
+    } else if (columns <= 4096u) {
         if (norm) stage_input<CW, kShortRounds, true, SPLIT, TPX, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
         else stage_input<CW, kShortRounds, false, SPLIT, false, FOLD>(p, tid, columns, xs, xlo, nws, xsum, xoff, wred, xunscale);
     } else {
@@ -812,6 +840,7 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     p.y = a.y;
     p.norm_weight = a.norm_weight;
     p.norm_weight_bf16 = a.norm_weight_bf16;
+    p.staged = a.staged;
     p.eps = a.eps;
     p.resid = a.resid;
     p.partial_max = a.partial_max;
@@ -822,7 +851,10 @@ stark_b200_status qmv_launch(const QmvArgs &a, cudaStream_t stream) {
     if ((a.epilogue == kEpiPush) != (p.ex.ranks != 0 && p.ex.push[0] != nullptr)) return STARK_B200_INVALID_ARGUMENT;
     if (p.ex.recv && a.prologue != kProRmsNorm) return STARK_B200_INVALID_ARGUMENT;
 
-    const int fold = split ? 0 : (int)tune.qmv_fold;
+    if (a.prologue == kProStaged && (!a.staged || split || (reinterpret_cast<uintptr_t>(a.staged) & 15u)))
+        return STARK_B200_INVALID_ARGUMENT;
+    // a staged row carries no offset sums: the plain extraction only
+    const int fold = (split || a.prologue == kProStaged) ? 0 : (int)tune.qmv_fold;
     // Ring depth: what fits the per-CTA budget.  With two CTAs per SM the register file is full; with one,
     // the CTA of the next kernel of a programmatic launch chain sits beside it and fills its own ring
     // while this one drains.

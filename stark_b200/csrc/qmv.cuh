@@ -52,7 +52,16 @@ __host__ __device__ inline uint32_t tile_row0(uint32_t tile, uint32_t pair_halve
 enum QmvPrologue : uint32_t {
     kProPlain = 0,    // x is the input vector (bf16 or f32)
     kProRmsNorm = 1,  // x = bf16(bf16(h * rms_inv) * bf16(norm_w)), h bf16
+    kProStaged = 2,   // the kernel before this one left the row ready to use (QmvStagedRow): a plain copy
 };
+// A matvec input as the kernel keeps it in shared memory, written once by the kernel that produces the row (the
+// tensor-parallel reduction, which holds the whole new residual row anyway) instead of once per consuming CTA:
+//   [columns] f16      the normalized row times an exact power of two (largest element in [2^14, 2^15))
+//   [columns / 64] f32 per-group sums of the normalized (unscaled) row
+//   f32                the factor that undoes the scale
+__host__ __device__ inline size_t qmv_staged_bytes(uint32_t columns) {
+    return ((size_t)columns * 2u + (size_t)(columns / 64u) * 4u + 16u + 15u) & ~(size_t)15u;
+}
 enum QmvEpilogue : uint32_t {
     kEpiStore = 0,     // y[row] = value (bf16 or f32)
     kEpiResidual = 1,  // y[row] = bf16(bf16(value) + resid[row])   (resid may alias y)
@@ -94,6 +103,7 @@ struct QmvArgs {
     QmvEpilogue epilogue;
     const float *norm_weight;  // kProRmsNorm
     const uint16_t *norm_weight_bf16;  // optional: the same weights already rounded to bf16 (copied, not converted)
+    const void *staged;        // kProStaged: the row as qmv_staged_bytes describes it (device memory)
     float eps;
     const void *resid;        // kEpiResidual
     float *partial_max;       // kEpiLogits: [grid] per-CTA maxima

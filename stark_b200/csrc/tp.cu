@@ -149,6 +149,141 @@ __global__ void __launch_bounds__(kReduceThreads) tp_reduce_residual_kernel(TpRe
     if (threadIdx.x == 0 && trace) trace_max(&trace->end);
 }
 
+// The same reduction by ONE CTA that then also prepares the input of the matvec that follows: it holds the whole new
+// residual row, so the RMS norm (normalization.rs:13-191: bf16(bf16(h * rms_inv) * bf16(w))), the power-of-two scale
+// into f16 range and the per-group sums are formed here once (QmvStagedRow) and the 2 x 148 CTAs of the matvec copy
+// 8 KB instead of each normalizing the row again behind this kernel.  Four elements per thread and round.
+constexpr int kStageThreads = 1024, kStageRounds = 3;  // hidden <= 12288
+__global__ void __launch_bounds__(kStageThreads) tp_reduce_stage_kernel(TpRegion g, uint32_t buf, uint32_t ticket_mul,
+                                                                        uint32_t ticket_add, const uint32_t *tokens,
+                                                                        uint16_t *h, const float *norm_weight, float eps,
+                                                                        uint8_t *staged, uint32_t *error_word,
+                                                                        TraceSlot *trace) {
+    __shared__ float red_s[32], red_m[32];
+    pdl_launch_dependents();
+    if (threadIdx.x == 0 && trace) trace_min(&trace->start);
+    pdl_wait();
+    if (threadIdx.x == 0 && trace) trace_min(&trace->ready);
+    const uint32_t ticket = __ldcg(tokens) * ticket_mul + ticket_add;
+    const unsigned long long t0 = global_ns();
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    float f[kStageRounds][4];
+    float sumsq = 0.0f, vmax = 0.0f;
+#pragma unroll
+    for (int round = 0; round < kStageRounds; ++round) {
+        const uint32_t i = (round * kStageThreads + tid) * 4u;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) f[round][e] = 0.0f;
+        if (i >= g.hidden) continue;
+        float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        // the packets of four ranks per trip to memory, repeated until their tickets are this exchange's; the
+        // shares are added in rank order, so every rank computes the same bits
+        for (uint32_t r0 = 0; r0 < g.size; r0 += 4u) {
+            unsigned long long q[4][4];
+            uint32_t spins = 0;
+            for (;;) {
+                bool all = true;
+#pragma unroll
+                for (uint32_t r = 0; r < 4u; ++r) {
+                    if (r0 + r < g.size) {
+                        const unsigned long long *src = tp_recv(g.base[g.rank], buf, r0 + r, g.hidden) + i;
+                        asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(q[r][0]), "=l"(q[r][1]) : "l"(src) : "memory");
+                        asm volatile("ld.relaxed.sys.global.v2.u64 {%0,%1}, [%2];" : "=l"(q[r][2]), "=l"(q[r][3]) : "l"(src + 2) : "memory");
+                    }
+                }
+#pragma unroll
+                for (uint32_t r = 0; r < 4u; ++r)
+                    if (r0 + r < g.size)
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) all = all && (uint32_t)(q[r][e] >> 32) == ticket;
+                if (all) break;
+                if (++spins > 8u) {
+                    __nanosleep(64);
+                    if (global_ns() - t0 > g.wait_ns) {  // a rank is missing: report, go on with what is there
+                        atomicOr(error_word, kErrPeerTimeout);
+                        break;
+                    }
+                }
+            }
+#pragma unroll
+            for (uint32_t r = 0; r < 4u; ++r)
+                if (r0 + r < g.size)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) a[e] += __uint_as_float((uint32_t)q[r][e]);
+        }
+        const uint2 old = *reinterpret_cast<const uint2 *>(h + i);
+        const uint32_t s01 = f32x2_to_bf16x2(a[0], a[1]), s23 = f32x2_to_bf16x2(a[2], a[3]);  // the projection's bf16 output
+        const uint32_t h01 = f32x2_to_bf16x2(__uint_as_float(s01 << 16) + __uint_as_float(old.x << 16),
+                                             __uint_as_float(s01 & 0xffff0000u) + __uint_as_float(old.x & 0xffff0000u));
+        const uint32_t h23 = f32x2_to_bf16x2(__uint_as_float(s23 << 16) + __uint_as_float(old.y << 16),
+                                             __uint_as_float(s23 & 0xffff0000u) + __uint_as_float(old.y & 0xffff0000u));
+        *reinterpret_cast<uint2 *>(h + i) = make_uint2(h01, h23);
+        f[round][0] = __uint_as_float(h01 << 16);
+        f[round][1] = __uint_as_float(h01 & 0xffff0000u);
+        f[round][2] = __uint_as_float(h23 << 16);
+        f[round][3] = __uint_as_float(h23 & 0xffff0000u);
+        const float4 w4 = *reinterpret_cast<const float4 *>(norm_weight + i);
+        const float nw[4] = {bf16_round(w4.x), bf16_round(w4.y), bf16_round(w4.z), bf16_round(w4.w)};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            sumsq = fmaf(f[round][e], f[round][e], sumsq);
+            vmax = fmaxf(vmax, fabsf(f[round][e] * nw[e]));
+        }
+    }
+    // one block-wide reduction for the sum of squares and for the bound the f16 scale is chosen from
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
+        vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, o));
+    }
+    if (lane == 0) red_s[warp] = sumsq, red_m[warp] = vmax;
+    __syncthreads();
+    sumsq = 0.0f, vmax = 0.0f;
+#pragma unroll
+    for (int w = 0; w < kStageThreads / 32; ++w) {
+        sumsq += red_s[w];
+        vmax = fmaxf(vmax, red_m[w]);
+    }
+    const float rms_inv = 1.0f / sqrtf(sumsq / (float)g.hidden + eps);
+    vmax *= rms_inv * 1.015625f;  // bounds the normalized values up to their two bf16 roundings
+    int shift = 14 - ((int)((__float_as_uint(vmax) >> 23) & 0xffu) - 127);
+    shift = max(-100, min(100, shift));
+    if (!(vmax > 0.0f) || !isfinite(vmax)) shift = 0;
+    const float xscale = __uint_as_float((uint32_t)(shift + 127) << 23);
+    float *sums = reinterpret_cast<float *>(staged + (size_t)g.hidden * 2u);
+#pragma unroll
+    for (int round = 0; round < kStageRounds; ++round) {
+        const uint32_t i = (round * kStageThreads + tid) * 4u;
+        float s4 = 0.0f;
+        uint32_t hh[2] = {0u, 0u};
+        float nw[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (i < g.hidden) {  // the weights again (cached), rather than held in registers across the reduction
+            const float4 w4 = *reinterpret_cast<const float4 *>(norm_weight + i);
+            nw[0] = bf16_round(w4.x), nw[1] = bf16_round(w4.y), nw[2] = bf16_round(w4.z), nw[3] = bf16_round(w4.w);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; e += 2) {
+            const uint32_t n2 = f32x2_to_bf16x2(f[round][e] * rms_inv, f[round][e + 1] * rms_inv);
+            const uint32_t p2 = f32x2_to_bf16x2(__uint_as_float(n2 << 16) * nw[e], __uint_as_float(n2 & 0xffff0000u) * nw[e + 1]);
+            const float a = __uint_as_float(p2 << 16), b = __uint_as_float(p2 & 0xffff0000u);
+            s4 += a;
+            s4 += b;
+            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(hh[e >> 1]) : "f"(b * xscale), "f"(a * xscale));
+        }
+        // a group of 64 columns is 16 consecutive threads
+#pragma unroll
+        for (int o = 1; o < 16; o <<= 1) s4 += __shfl_xor_sync(0xffffffffu, s4, o);
+        if (i < g.hidden) {
+            *reinterpret_cast<uint2 *>(staged + (size_t)i * 2u) = make_uint2(hh[0], hh[1]);
+            if ((lane & 15u) == 0) sums[i >> 6] = s4;
+        }
+    }
+    if (tid == 0) {
+        sums[g.hidden / 64u] = __uint_as_float((uint32_t)(127 - shift) << 23);  // undoes the scale
+        if (trace) trace_max(&trace->end);
+    }
+}
+
 __global__ void __launch_bounds__(256) tp_argmax_finalize_kernel(TpRegion g, uint32_t *tokens, const float *partial_max,
                                                                  const uint32_t *partial_index, uint32_t count,
                                                                  uint32_t vocab_offset, StepState *state,
@@ -278,6 +413,26 @@ stark_b200_status tp_reduce_residual_launch(const TpRegion &g, uint32_t index, u
     cfg.numAttrs = pdl ? 1 : 0;
     SB_CUDA(cudaLaunchKernelEx(&cfg, tp_reduce_residual_kernel, g, index & 1u, per_token, index + 1u, tokens, h,
                                error_word, trace));
+    return STARK_B200_OK;
+}
+
+stark_b200_status tp_reduce_stage_launch(const TpRegion &g, uint32_t index, uint32_t per_token, const uint32_t *tokens,
+                                         uint16_t *h, const float *norm_weight, float eps, void *staged,
+                                         uint32_t *error_word, TraceSlot *trace, bool pdl, cudaStream_t stream) {
+    if (g.size < 2 || g.size > kMaxTpRanks || g.rank >= g.size || g.hidden % 64u != 0 ||
+        g.hidden > (uint32_t)kStageThreads * kStageRounds * 4u || !norm_weight || !staged)
+        return STARK_B200_INVALID_ARGUMENT;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(kStageThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    SB_CUDA(cudaLaunchKernelEx(&cfg, tp_reduce_stage_kernel, g, index & 1u, per_token, index + 1u, tokens, h, norm_weight, eps,
+                               static_cast<uint8_t *>(staged), error_word, trace));
     return STARK_B200_OK;
 }
 

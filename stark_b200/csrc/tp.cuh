@@ -52,6 +52,12 @@ stark_b200_status tp_reduce_residual_launch(const TpRegion &g, uint32_t index, u
                                             const uint32_t *tokens, uint16_t *h, uint32_t *error_word, TraceSlot *trace,
                                             bool pdl, cudaStream_t stream);
 
+// The same step by one CTA that also leaves the following matvec's input ready (qmv.cuh `kProStaged`): the RMS norm
+// with `norm_weight`, the f16 scale and the per-group sums are formed once here instead of once per consuming CTA.
+stark_b200_status tp_reduce_stage_launch(const TpRegion &g, uint32_t index, uint32_t per_token, const uint32_t *tokens,
+                                         uint16_t *h, const float *norm_weight, float eps, void *staged,
+                                         uint32_t *error_word, TraceSlot *trace, bool pdl, cudaStream_t stream);
+
 // End of a cache-only prompt row: waits until every rank's packets of the row's last exchange are in
 // (nobody may start the next row's pushes into a buffer a slower rank still reads), then position += 1,
 // token = pending[cursor++], tokens += 1.

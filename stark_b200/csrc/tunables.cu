@@ -28,6 +28,7 @@ const Entry kEntries[] = {
     {"prefill_min_rows", "STARK_B200_PREFILL_MIN_ROWS", &Tunables::prefill_min_rows, 16u, 1u, 1u << 20},
     {"rows_matvec", "STARK_B200_ROWS_MATVEC", &Tunables::rows_matvec, 1u, 0u, 1u},
     {"rows_attention", "STARK_B200_ROWS_ATTENTION", &Tunables::rows_attention, 1u, 0u, 1u},
+    {"tp_stage", "STARK_B200_TP_STAGE", &Tunables::tp_stage, 0u, 0u, 1u},
 };
 
 bool valid(const Entry &e, uint32_t v) {

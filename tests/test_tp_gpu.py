@@ -24,8 +24,10 @@ def _gpu_count() -> int:
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("config,ranks", [("tiny", 2), ("small", 2), ("small", 4), ("small", 8)])
-def test_ranks_match_oracle_and_single_gpu(config, ranks):
+@pytest.mark.parametrize("config,ranks,staged", [("tiny", 2, 0), ("small", 2, 0), ("small", 2, 1), ("small", 4, 0),
+                                                 ("small", 8, 0)])
+def test_ranks_match_oracle_and_single_gpu(config, ranks, staged):
+    """`staged`: the reduction kernel also normalizes and scales the row for the matvec behind it (off by default)."""
     if _gpu_count() < ranks:
         pytest.skip(f"needs {ranks} GPUs")
     with socket.socket() as s:
@@ -33,7 +35,8 @@ def test_ranks_match_oracle_and_single_gpu(config, ranks):
         port = s.getsockname()[1]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
            "127.0.0.1", "--master-port", str(port), str(Path(__file__).resolve()), config]
-    res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=900)
+    env = dict(os.environ, STARK_B200_TP_STAGE=str(staged))
+    res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=900, env=env)
     failed = [line for line in res.stdout.splitlines() if "RANK-FAILED" in line]
     assert res.returncode == 0, "\n".join(failed) + res.stdout[-3000:] + res.stderr[-1500:]
     assert "TP-OK" in res.stdout
