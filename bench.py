@@ -704,10 +704,10 @@ def main() -> None:
                  "rows_recomputed": int(len(second) - rows), "prefill_ms": 1e3 * (time.perf_counter() - t0)}
 
     # every region is the max over ranks (a token is done when the slowest rank is); then the median region
-    t = torch.tensor(regions + e2e_regions, dtype=torch.float64, device="cuda")
+    t = torch.tensor(regions + e2e_regions + [prefill_ms], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    regions, e2e_regions = t[:repeats].tolist(), t[repeats:].tolist()
+    regions, e2e_regions, prefill_ms = t[:repeats].tolist(), t[repeats:2 * repeats].tolist(), float(t[-1])
     ms, e2e_s = float(np.median(regions)), float(np.median(e2e_regions))
     streams = 1 if (tp is not None or world == 1) else world  # tensor parallel: all GPUs work on the one token stream
     value = streams * steps / (ms / 1e3)
@@ -748,15 +748,18 @@ def main() -> None:
                      "note": "whole decode step (all kernels of the token) over the step's algorithmic bytes"
                              + (", per GPU" if world > 1 else "")},
     }
-    if tp is None:
-        # Prompt ingest (chunks of 1024 rows through the tcgen05 contraction): a dense contraction, so it is set
-        # against the tensor-pipe peak, not the HBM one.
+    if tp is None or world == 1 or tp.rows:
+        # Prompt ingest (passes of up to 4096 rows through the tcgen05 contraction): a dense contraction, so it is
+        # set against the tensor-pipe peak, not the HBM one.  Tensor parallel: a rank contracts 1/N of every matrix
+        # and the ranks gather column slices over NVLink; FLOP/s are per GPU.
         tpeak, tkind = tensor_peak()
-        tflops = prefill_flops(cfg, wl["prompt"]) / (prefill_ms * 1e-3) / 1e12
+        share = world if tp is not None else 1
+        tflops = prefill_flops(cfg, wl["prompt"]) / share / (prefill_ms * 1e-3) / 1e12
         line["prefill"] = {"prefill_tok_s": wl["prompt"] / (prefill_ms * 1e-3), "ms": prefill_ms,
                            "prompt_tokens": wl["prompt"], "achieved_tflops": tflops, "peak_tflops": tpeak,
                            "frac": tflops / tpeak, "peak_kind": tkind, "bound": "tensor",
-                           "note": "device time (CUDA events) of ingesting the prompt, last row included"}
+                           "note": "device time (CUDA events, max over ranks) of ingesting the prompt, last row included"
+                                   + (", FLOP/s per GPU" if share > 1 else "")}
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         from oracle import oracle as O
         n = 2 if cfg["layers"] >= 28 else 8

@@ -307,6 +307,10 @@ typedef struct stark_b200_dense_config {
 #define STARK_B200_MAT_UPGATE 4u
 #define STARK_B200_MAT_DOWN 5u
 #define STARK_B200_MAT_MTP_FUSION 6u /* draft head: [hidden, 2 * hidden] over [norm_e(embedding) ; norm_h(hidden)] */
+/* Tensor parallel only, optional: this rank's OUTPUT ROWS [rank * hidden / ranks, (rank + 1) * hidden / ranks) of the
+ * whole o- and down-projection (all input columns), used by batched prompt passes (see tp_rows_init). */
+#define STARK_B200_MAT_O_ROWS 7u
+#define STARK_B200_MAT_DOWN_ROWS 8u
 #define STARK_B200_VEC_FINAL_NORM 0u
 #define STARK_B200_VEC_ATTN_NORM 1u
 #define STARK_B200_VEC_MLP_NORM 2u
@@ -387,6 +391,17 @@ stark_b200_status stark_b200_model_tp_init(stark_b200_model *model, uint32_t ran
 stark_b200_status stark_b200_model_tp_connect(stark_b200_model *model, const uint8_t *handles, size_t handle_bytes);
 stark_b200_status stark_b200_model_tp_set_wait(stark_b200_model *model, uint64_t nanoseconds);
 stark_b200_status stark_b200_model_tp_connect_unanswered(stark_b200_model *model);
+/* Batched prompt passes under tensor parallelism (optional; without these calls, or without the two *_ROWS matrices
+ * of every layer, a rank group ingests prompt rows one token at a time).  A prompt pass is a chain of dense
+ * contractions over thousands of rows, so its exchange is an all-gather bound by bandwidth: each rank computes its
+ * column slice of the attention output, of the residual stream (o and down cut by output rows, contracted over
+ * their full width) and of the gated activation, and the ranks store the slices into one another's row buffers
+ * over NVLink; every element is the same bits as on one GPU.
+ *   tp_rows_init     after tp_connect, before finalize: allocates the row buffers (4 096 rows of hidden +
+ *                    attention width + intermediate width, bf16) and returns their 64-byte handle;
+ *   tp_rows_connect  takes all ranks' handles in rank order, as tp_connect does. */
+stark_b200_status stark_b200_model_tp_rows_init(stark_b200_model *model, uint8_t handle_out[64]);
+stark_b200_status stark_b200_model_tp_rows_connect(stark_b200_model *model, const uint8_t *handles, size_t handle_bytes);
 stark_b200_status stark_b200_model_finalize(stark_b200_model *model);
 stark_b200_status stark_b200_destroy(stark_b200_model **model);
 stark_b200_status stark_b200_reset(stark_b200_model *model);

@@ -64,7 +64,8 @@ class Info(C.Structure):
                 ("trace_slots", C.c_uint32), ("persistent", C.c_uint32)]
 
 
-MAT_EMBED, MAT_LM_HEAD, MAT_QKV, MAT_O, MAT_UPGATE, MAT_DOWN, MAT_MTP_FUSION = range(7)
+(MAT_EMBED, MAT_LM_HEAD, MAT_QKV, MAT_O, MAT_UPGATE, MAT_DOWN, MAT_MTP_FUSION, MAT_O_ROWS,
+ MAT_DOWN_ROWS) = range(9)
 (VEC_FINAL_NORM, VEC_ATTN_NORM, VEC_MLP_NORM, VEC_Q_NORM, VEC_K_NORM, VEC_MTP_EMBED_NORM, VEC_MTP_HIDDEN_NORM,
  VEC_MTP_OUT_NORM) = range(8)
 MTP_GREEDY, MTP_FORCED, MTP_HELD = 0, 1, 2
@@ -156,6 +157,8 @@ def load() -> C.CDLL:
         "stark_b200_model_tp_connect": (u32, [vp, vp, sz]),
         "stark_b200_model_tp_set_wait": (u32, [vp, u64]),
         "stark_b200_model_tp_connect_unanswered": (u32, [vp]),
+        "stark_b200_model_tp_rows_init": (u32, [vp, vp]),
+        "stark_b200_model_tp_rows_connect": (u32, [vp, vp, sz]),
         "stark_b200_model_finalize": (u32, [vp]),
         "stark_b200_destroy": (u32, [C.POINTER(vp)]),
         "stark_b200_reset": (u32, [vp]),

@@ -318,6 +318,17 @@ stark_b200_status stark_b200_model_tp_connect_unanswered(stark_b200_model *model
     return model_tp_connect_unanswered(M(model));
 }
 
+stark_b200_status stark_b200_model_tp_rows_init(stark_b200_model *model, uint8_t handle_out[64]) {
+    if (!model || !handle_out) return STARK_B200_INVALID_ARGUMENT;
+    return model_tp_rows_init(M(model), handle_out);
+}
+
+stark_b200_status stark_b200_model_tp_rows_connect(stark_b200_model *model, const uint8_t *handles, size_t handle_bytes) {
+    if (!model || !handles) return STARK_B200_INVALID_ARGUMENT;
+    if (handle_bytes != (size_t)M(model)->tp.size * 64u) return STARK_B200_INVALID_ARGUMENT;
+    return model_tp_rows_connect(M(model), handles);
+}
+
 stark_b200_status stark_b200_model_finalize(stark_b200_model *model) {
     if (!model) return STARK_B200_INVALID_ARGUMENT;
     return model_finalize(M(model));

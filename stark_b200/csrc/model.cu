@@ -14,6 +14,7 @@
 // then logits = W_head rmsnorm(h) with the greedy read-out fused into the matvec epilogue.
 #include "model.cuh"
 #include "mega.cuh"
+#include "prefill.cuh"
 #include "tunables.cuh"
 
 #include <cmath>
@@ -55,6 +56,8 @@ Model::~Model() {
         qmatrix_free(L.o);
         qmatrix_free(L.upgate);
         qmatrix_free(L.down);
+        qmatrix_free(L.o_rows);
+        qmatrix_free(L.down_rows);
         cudaFree(L.attn_norm);
         cudaFree(L.mlp_norm);
         cudaFree(L.attn_norm_b16);
@@ -97,12 +100,19 @@ Model::~Model() {
                 if (tp_stand_ins) cudaFree(tp.base[r]);
                 else cudaIpcCloseMemHandle(tp.base[r]);
             }
+    if (tp_rows_connected)
+        for (uint32_t r = 0; r < tp_rows.size; ++r)
+            if (r != tp_rows.rank && tp_rows.base[r]) cudaIpcCloseMemHandle(tp_rows.base[r]);
     cudaFree(chunk_tokens);
-    cudaFree(chunk_h);
+    if (!tp_rows_local) {  // under tensor parallelism these two live inside the rows region
+        cudaFree(chunk_h);
+        cudaFree(chunk_act);
+    }
     cudaFree(chunk_x);
     cudaFree(chunk_qkv);
     cudaFree(chunk_attn);
-    cudaFree(chunk_act);
+    cudaFree(tp_rows_local);
+    cudaFree(tp_rows_arrive);
     cudaFree(rows_attn_partials);
     cudaFree(tp_local);
     cudaFree(sample_scratch);
@@ -285,6 +295,12 @@ stark_b200_status model_set_matrix(Model *m, uint32_t layer, uint32_t which, QMa
         case STARK_B200_MAT_O: return put(&L.o, c.hidden, c.q_heads * kHeadDim, false);
         case STARK_B200_MAT_UPGATE: return put(&L.upgate, 2u * c.inter, c.hidden, true);
         case STARK_B200_MAT_DOWN: return put(&L.down, c.hidden, c.inter, false);
+        case STARK_B200_MAT_O_ROWS:
+            if (m->tp.size < 2u || c.hidden % m->tp.size) return STARK_B200_INVALID_STATE;
+            return put(&L.o_rows, c.hidden / m->tp.size, c.q_heads * m->tp.size * kHeadDim, false);
+        case STARK_B200_MAT_DOWN_ROWS:
+            if (m->tp.size < 2u || c.hidden % m->tp.size) return STARK_B200_INVALID_STATE;
+            return put(&L.down_rows, c.hidden / m->tp.size, c.inter * m->tp.size, false);
         default: return STARK_B200_INVALID_ARGUMENT;
     }
 }
@@ -661,6 +677,40 @@ stark_b200_status model_tp_connect(Model *m, const uint8_t *handles) {
         m->tp.base[r] = static_cast<uint8_t *>(p);
     }
     m->tp_connected = true;
+    return STARK_B200_OK;
+}
+
+stark_b200_status model_tp_rows_init(Model *m, uint8_t *handle_out) {
+    if (m->finalized || !m->tp_local || m->tp_rows_local || m->tp_stand_ins || m->chunk_h) return STARK_B200_INVALID_STATE;
+    const auto &c = m->cfg;
+    const size_t bytes = tp_rows_region_bytes(kPrefillBatchRows, c.hidden, (size_t)c.q_heads * m->tp.size * kHeadDim,
+                                              (size_t)c.inter * m->tp.size);
+    SB_CUDA(cudaMalloc(&m->tp_rows_local, bytes));
+    SB_CUDA(cudaMemset(m->tp_rows_local, 0, kTpRowsHeaderBytes));
+    stark_b200_status st = dmalloc(&m->tp_rows_arrive, 1);
+    if (st != STARK_B200_OK) return st;
+    SB_CUDA(cudaMemset(m->tp_rows_arrive, 0, 4u));
+    SB_CUDA(cudaDeviceSynchronize());
+    cudaIpcMemHandle_t handle;
+    SB_CUDA(cudaIpcGetMemHandle(&handle, m->tp_rows_local));
+    memcpy(handle_out, &handle, 64);
+    m->tp_rows.rank = m->tp.rank;
+    m->tp_rows.size = m->tp.size;
+    m->tp_rows.base[m->tp.rank] = m->tp_rows_local;
+    return STARK_B200_OK;
+}
+
+stark_b200_status model_tp_rows_connect(Model *m, const uint8_t *handles) {
+    if (m->finalized || !m->tp_rows_local || m->tp_rows_connected) return STARK_B200_INVALID_STATE;
+    for (uint32_t r = 0; r < m->tp_rows.size; ++r) {
+        if (r == m->tp_rows.rank) continue;
+        cudaIpcMemHandle_t handle;
+        memcpy(&handle, handles + (size_t)r * 64u, 64);
+        void *p = nullptr;
+        SB_CUDA(cudaIpcOpenMemHandle(&p, handle, cudaIpcMemLazyEnablePeerAccess));
+        m->tp_rows.base[r] = static_cast<uint8_t *>(p);
+    }
+    m->tp_rows_connected = true;
     return STARK_B200_OK;
 }
 

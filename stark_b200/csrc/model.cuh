@@ -12,6 +12,9 @@ namespace sb {
 
 struct ModelLayer {
     QMatrix *qkv = nullptr, *o = nullptr, *upgate = nullptr, *down = nullptr;
+    // tensor parallel, optional: this rank's OUTPUT ROWS of the o- and down-projection over all input columns, for
+    // prompt passes (the token path uses the column cuts above)
+    QMatrix *o_rows = nullptr, *down_rows = nullptr;
     float *attn_norm = nullptr, *mlp_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
     uint16_t *attn_norm_b16 = nullptr, *mlp_norm_b16 = nullptr;  // the norm weights rounded to bf16, as the kernels use them
     KvLayer kv{nullptr, nullptr};
@@ -85,6 +88,13 @@ struct Model {
     void *tp_staged = nullptr;     // the input row a reduction leaves ready for the matvec after it (qmv_staged_bytes)
     uint32_t tp_vocab_offset = 0, tp_vocab_total = 0;
     bool tp_connected = false, tp_stand_ins = false;
+    // prompt passes under tensor parallelism (optional second exchange region: whole rows of h, attention output
+    // and gated activation, gathered from the ranks' column slices)
+    TpRowsRegion tp_rows{};
+    uint8_t *tp_rows_local = nullptr;
+    uint32_t *tp_rows_arrive = nullptr;
+    uint32_t tp_rows_ticket = 0;       // gathers launched so far (the same number on every rank)
+    bool tp_rows_connected = false;
     // batched prompt ingest (prefill_model.cu): rows of one chunk, allocated at first use
     uint32_t prefill_state = 0;  // 0 not examined, 1 the batched path serves this model, 2 it does not
     uint32_t *chunk_tokens = nullptr;
@@ -112,6 +122,10 @@ stark_b200_status model_tp_init(Model *m, uint32_t rank, uint32_t size, uint32_t
 stark_b200_status model_tp_connect(Model *m, const uint8_t *handles);
 stark_b200_status model_tp_set_wait(Model *m, uint64_t nanoseconds);
 stark_b200_status model_tp_connect_unanswered(Model *m);
+// Optional, after tp_connect and before finalize: the exchange region of batched prompt passes (same handle
+// protocol).  Without it, or without the row cuts of o and down, prompt rows go through the token path.
+stark_b200_status model_tp_rows_init(Model *m, uint8_t *handle_out);
+stark_b200_status model_tp_rows_connect(Model *m, const uint8_t *handles);
 stark_b200_status model_finalize(Model *m);
 stark_b200_status model_reset(Model *m);
 stark_b200_status model_recapture(Model *m);

@@ -22,6 +22,13 @@ stark_b200_status dmalloc_rows(T **p, size_t count) {
     return STARK_B200_OK;
 }
 
+// byte offsets of the three row buffers inside the rows region (tp.cuh)
+size_t rows_region_h(const Model *) { return kTpRowsHeaderBytes; }
+size_t rows_region_attn(const Model *m) { return rows_region_h(m) + (size_t)kPrefillBatchRows * m->cfg.hidden * 2u; }
+size_t rows_region_act(const Model *m) {
+    return rows_region_attn(m) + (size_t)kPrefillBatchRows * m->cfg.q_heads * m->tp.size * kHeadDim * 2u;
+}
+
 }  // namespace
 
 stark_b200_status ensure_chunk_buffers(Model *m) {
@@ -31,11 +38,17 @@ stark_b200_status ensure_chunk_buffers(Model *m) {
     const uint32_t qkv_n = (c.q_heads + 2u * c.kv_heads) * kHeadDim;
     stark_b200_status st;
     if ((st = dmalloc_rows(&m->chunk_tokens, rows + 8u)) != STARK_B200_OK) return st;
-    if ((st = dmalloc_rows(&m->chunk_h, rows * c.hidden)) != STARK_B200_OK) return st;
+    if (m->tp_rows_local) {
+        // whole rows of all ranks, inside the exported region: the peers store their column slices there
+        m->chunk_h = reinterpret_cast<uint16_t *>(m->tp_rows_local + rows_region_h(m));
+        m->chunk_act = reinterpret_cast<uint16_t *>(m->tp_rows_local + rows_region_act(m));
+    } else {
+        if ((st = dmalloc_rows(&m->chunk_h, rows * c.hidden)) != STARK_B200_OK) return st;
+        if ((st = dmalloc_rows(&m->chunk_act, rows * c.inter)) != STARK_B200_OK) return st;
+    }
     if ((st = dmalloc_rows(&m->chunk_x, rows * c.hidden)) != STARK_B200_OK) return st;
     if ((st = dmalloc_rows(&m->chunk_qkv, rows * qkv_n)) != STARK_B200_OK) return st;
     if ((st = dmalloc_rows(&m->chunk_attn, rows * c.q_heads * kHeadDim)) != STARK_B200_OK) return st;
-    if ((st = dmalloc_rows(&m->chunk_act, rows * c.inter)) != STARK_B200_OK) return st;
     if ((st = dmalloc_rows(&m->rows_attn_partials, prefill_attention_partial_floats(c.q_heads, kPrefillAttnMaxSplits))) != STARK_B200_OK)
         return st;
     return STARK_B200_OK;
@@ -47,10 +60,13 @@ bool model_batched_prefill_ready(Model *m) {
     if (m->prefill_state == 2u) return false;
     if (m->prefill_state == 1u) return true;
     m->prefill_state = 2u;
-    if (m->tp.size > 1u || m->use_mega) return false;
+    if (m->use_mega) return false;
+    const bool tp = m->tp.size > 1u;
+    // tensor parallel: needs the rows region and the row cuts of o and down; otherwise rows take the token path
+    if (tp && !m->tp_rows_connected) return false;
     for (auto &L : m->layers)  // the draft head's layer, if any, included
-        for (QMatrix *q : {L.qkv, L.o, L.upgate, L.down}) {
-            if (q->rows % 128u != 0 || q->columns % 64u != 0) return false;
+        for (QMatrix *q : {L.qkv, tp ? L.o_rows : L.o, L.upgate, tp ? L.down_rows : L.down}) {
+            if (!q || q->rows % 128u != 0 || q->columns % 64u != 0) return false;
         }
     if (m->cfg.hidden > 12288u || ensure_chunk_buffers(m) != STARK_B200_OK) return false;
     m->prefill_state = 1u;
@@ -74,6 +90,22 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
     // a handful of rows: the several-rows matvec normalizes the rows in its own prologue
     const bool fused_norm = tunables().rows_matvec && qmv_multi_supports(m->layers[0].qkv, mrows, true) &&
                             qmv_multi_supports(m->layers[0].upgate, mrows, true);
+    // Tensor parallel (tp.cuh): every rank holds whole rows of h; its contractions produce column slices -- of the
+    // attention output, of the new h (o and down cut by output rows), of the gated activation -- which the ranks
+    // then copy into one another's buffers.  Four gathers per layer.
+    const bool tp = m->tp.size > 1u;
+    const uint32_t ranks = tp ? m->tp.size : 1u, rank = tp ? m->tp.rank : 0u;
+    const uint32_t attn_local = c.q_heads * kHeadDim, attn_width = attn_local * ranks, inter_total = c.inter * ranks;
+    const uint32_t h_slice = c.hidden / ranks;
+    uint16_t *attn_rows = tp ? reinterpret_cast<uint16_t *>(m->tp_rows_local + rows_region_attn(m)) : m->chunk_attn;
+    uint32_t gathers = 0;
+    auto gather = [&](const uint16_t *src, uint32_t src_ld, size_t dst_offset, uint32_t dst_ld, uint32_t column,
+                      uint32_t width, bool own) -> stark_b200_status {
+        m->tp_rows.wait_ns = m->tp.wait_ns;
+        TpGatherArgs ga{src, src_ld, dst_offset, dst_ld, column, width, mrows, own, ++m->tp_rows_ticket};
+        ++gathers;
+        return tp_rows_gather_launch(m->tp_rows, ga, m->tp_rows_arrive, ctx->error_word, s);
+    };
     if ((st = embed_rows_launch(m->embed, tokens_device, mrows, m->chunk_h, s)) != STARK_B200_OK) return st;
     for (uint32_t l = 0; l < c.layers; ++l) {
         auto &L = m->layers[l];
@@ -103,36 +135,49 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
         pa.partials = m->rows_attn_partials;
         pa.max_splits = kPrefillAttnMaxSplits;
         if ((st = prefill_attention_launch(pa, s)) != STARK_B200_OK) return st;
-        // h = bf16(bf16(W_o attn) + h)
-        g.w = L.o;
-        g.x = m->chunk_attn;
-        g.out = m->chunk_h;
+        if (tp && (st = gather(m->chunk_attn, attn_local, rows_region_attn(m), attn_width, rank * attn_local, attn_local,
+                               true)) != STARK_B200_OK)
+            return st;
+        // h = bf16(bf16(W_o attn) + h); tensor parallel: this rank's columns of h, in place, then gathered
+        g.w = tp ? L.o_rows : L.o;
+        g.x = attn_rows;
+        g.out = m->chunk_h + (size_t)rank * h_slice;
         g.ld_out = c.hidden;
         g.epilogue = kEpiResidual;
         if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        if (tp && (st = gather(m->chunk_h + (size_t)rank * h_slice, c.hidden, rows_region_h(m), c.hidden, rank * h_slice,
+                               h_slice, false)) != STARK_B200_OK)
+            return st;
         // act = silu(gate) * up
+        uint16_t *act_slice = m->chunk_act + (size_t)rank * c.inter;  // this rank's columns of the whole rows
         if (fused_norm) {
-            QmvMultiArgs q{L.upgate, m->chunk_h, c.hidden, mrows, m->chunk_act, c.inter, L.mlp_norm, c.eps, kEpiSwiGlu,
+            QmvMultiArgs q{L.upgate, m->chunk_h, c.hidden, mrows, act_slice, inter_total, L.mlp_norm, c.eps, kEpiSwiGlu,
                            ctx->error_word, true};
             if ((st = qmv_multi_launch(q, s)) != STARK_B200_OK) return st;
         } else {
             if ((st = rmsnorm_rows_launch(m->chunk_h, L.mlp_norm, m->chunk_x, mrows, c.hidden, c.eps, s)) != STARK_B200_OK) return st;
             g.w = L.upgate;
             g.x = m->chunk_x;
-            g.out = m->chunk_act;
-            g.ld_out = c.inter;
+            g.out = act_slice;
+            g.ld_out = inter_total;
             g.epilogue = kEpiSwiGlu;
             if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
         }
+        if (tp && (st = gather(act_slice, inter_total, rows_region_act(m), inter_total, rank * c.inter, c.inter, false)) !=
+                      STARK_B200_OK)
+            return st;
         // h = bf16(bf16(W_down act) + h)
-        g.w = L.down;
+        g.w = tp ? L.down_rows : L.down;
         g.x = m->chunk_act;
-        g.out = m->chunk_h;
+        g.out = m->chunk_h + (size_t)rank * h_slice;
         g.ld_out = c.hidden;
         g.epilogue = kEpiResidual;
         if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        if (tp && (st = gather(m->chunk_h + (size_t)rank * h_slice, c.hidden, rows_region_h(m), c.hidden, rank * h_slice,
+                               h_slice, false)) != STARK_B200_OK)
+            return st;
     }
-    m->launches_issued += 1u + (fused_norm ? 6u : 8u) * c.layers + (split_rows ? c.layers : 0u);
+    m->launches_issued += 1u + (fused_norm ? 6u : 8u) * c.layers + (split_rows ? c.layers : 0u) + gathers;
     return STARK_B200_OK;
 }
 

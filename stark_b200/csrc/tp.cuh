@@ -72,4 +72,38 @@ stark_b200_status tp_argmax_finalize_launch(const TpRegion &g, uint32_t *tokens,
                                             StepState *state, uint32_t *generated, uint32_t *error_word, bool pdl,
                                             cudaStream_t stream);
 
+// ---- prompt passes (several rows at a time) ----------------------------------------------------------------
+// A prompt pass is a chain of dense contractions over up to kPrefillBatchRows rows, so its exchange is bound by
+// bandwidth, not latency, and it is an all-gather, not an all-reduce: for these passes a rank also holds the o- and
+// down-projection cut by OUTPUT ROWS (a second copy of 1/size of each), computes whole output elements with the
+// full contraction length, and the ranks copy their column slices of the attention output, the residual stream
+// and the gated activation into one another's buffers.  Every element of every row is then the same bits as on
+// one GPU.  The buffers live in a second exported allocation:
+//   [0, 4 KB)   flags: [kMaxTpRanks] u32, flag r written by rank r (the number of the last gather it completed)
+//   then        h [rows, hidden], attn [rows, attn_width], act [rows, inter]   bf16, whole rows of all ranks
+struct TpRowsRegion {
+    uint8_t *base[kMaxTpRanks];
+    uint32_t rank, size;
+    unsigned long long wait_ns;
+};
+constexpr size_t kTpRowsHeaderBytes = 4096;
+inline size_t tp_rows_region_bytes(size_t rows, size_t hidden, size_t attn_width, size_t inter) {
+    return kTpRowsHeaderBytes + rows * (hidden + attn_width + inter) * 2u;
+}
+// Copies columns [column, column + width) of `rows` rows from `src` (row stride src_ld elements) to byte offset
+// `dst_offset` + the same columns (row stride dst_ld) of every OTHER rank's region -- and of this rank's own when
+// `own` is set -- then publishes gather number `ticket` to the peers and waits (bounded) until every peer has
+// published it too.  When the launch has finished, the buffer holds the whole rows.  `arrive` is a zeroed device
+// word the launches share.  width and both strides are multiples of 8 elements.
+struct TpGatherArgs {
+    const uint16_t *src;
+    uint32_t src_ld;
+    size_t dst_offset;
+    uint32_t dst_ld, column, width, rows;
+    bool own;
+    uint32_t ticket;
+};
+stark_b200_status tp_rows_gather_launch(const TpRowsRegion &g, const TpGatherArgs &a, uint32_t *arrive,
+                                        uint32_t *error_word, cudaStream_t stream);
+
 }  // namespace sb

@@ -48,7 +48,8 @@ def shard_dense(cfg: dict, weights: dict, rank: int, ranks: int) -> tuple[dict, 
 
     qkv and up||gate are cut by output rows (whole heads, the KV cache follows the KV heads), the o- and
     down-projections by input columns (whole quantization groups), the read-out by vocabulary rows; the
-    embedding table and all norm vectors stay whole.  Returns (local config, local weights, first
+    embedding table and all norm vectors stay whole.  For batched prompt passes a rank also gets its output rows
+    of the whole o- and down-projection (`o_rows`, `down_rows`: 1/ranks of each again).  Returns (local config, local weights, first
     vocabulary row of the read-out shard).  The reference runs on one device; this is how the same
     graph (crates/stark-engine/src/encodable_block/transformer_layer.rs:549-659) is spread over several.
     """
@@ -56,7 +57,7 @@ def shard_dense(cfg: dict, weights: dict, rank: int, ranks: int) -> tuple[dict, 
     weights = dict(weights, embed=row_major_planes(weights["embed"]), lm_head=row_major_planes(weights["lm_head"]),
                    layers=[dict(lw, **{k: row_major_planes(lw[k]) for k in ("qkv", "o", "upgate", "down")})
                            for lw in weights["layers"]])
-    hq, hkv, hd, inter = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["inter"]
+    hq, hkv, hd, inter, hidden = cfg["q_heads"], cfg["kv_heads"], cfg["head_dim"], cfg["inter"], cfg["hidden"]
     if hq % ranks or hkv % ranks or inter % (16 * ranks) or (inter // ranks) % 64:
         raise ValueError(f"{ranks} ranks do not divide heads {hq}/{hkv} or width {inter} into whole shards")
     ql, kl, il = hq // ranks, hkv // ranks, inter // ranks
@@ -72,8 +73,15 @@ def shard_dense(cfg: dict, weights: dict, rank: int, ranks: int) -> tuple[dict, 
                       _rows(lw["qkv"], v0 + rank * kl * hd, v0 + (rank + 1) * kl * hd)])
         upgate = _stack([_rows(lw["upgate"], rank * il, (rank + 1) * il),
                          _rows(lw["upgate"], inter + rank * il, inter + (rank + 1) * il)])
-        layers.append(dict(lw, qkv=qkv, upgate=upgate, o=_columns(lw["o"], rank * ql * hd, (rank + 1) * ql * hd),
-                           down=_columns(lw["down"], rank * il, (rank + 1) * il)))
+        layer = dict(lw, qkv=qkv, upgate=upgate, o=_columns(lw["o"], rank * ql * hd, (rank + 1) * ql * hd),
+                     down=_columns(lw["down"], rank * il, (rank + 1) * il))
+        if hidden % (128 * ranks) == 0:
+            # prompt passes: the same two projections cut by output rows over all columns (whole output elements,
+            # gathered between ranks instead of reduced)
+            hs = hidden // ranks
+            layer.update(o_rows=_rows(lw["o"], rank * hs, (rank + 1) * hs),
+                         down_rows=_rows(lw["down"], rank * hs, (rank + 1) * hs))
+        layers.append(layer)
     out = dict(weights, layers=layers, lm_head=_rows(weights["lm_head"], lo, hi))
     return local, out, lo
 
@@ -82,8 +90,11 @@ class TensorParallel:
     """Rank layout of a tensor-parallel group plus the one host-side collective the engine needs:
     ``all_gather(bytes) -> [bytes per rank]`` (for example ``torch.distributed.all_gather_object``)."""
 
-    def __init__(self, rank: int, ranks: int, all_gather, wait_ns: int | None = None, unanswered: bool = False):
+    def __init__(self, rank: int, ranks: int, all_gather, wait_ns: int | None = None, unanswered: bool = False,
+                 rows: bool = True):
         self.rank, self.ranks, self.all_gather = int(rank), int(ranks), all_gather
+        # rows: batched prompt passes across the ranks (False: prompt rows take the token path)
+        self.rows = bool(rows) and not unanswered
         # wait_ns: how long a kernel of this rank waits for a peer's data before it reports a device failure
         # (library default 4 s).  unanswered: connect to stand-in peers nobody writes (exercises that limit).
         self.wait_ns, self.unanswered = wait_ns, bool(unanswered)
@@ -145,6 +156,12 @@ class DenseModel:
             else:
                 handles = b"".join(tp.all_gather(bytes(handle)))
                 check(_lib.load().stark_b200_model_tp_connect(m._h, handles, len(handles)), "model_tp_connect")
+                if tp.rows and all("o_rows" in lw for lw in weights["layers"]):
+                    # batched prompt passes: a second exported region holds whole rows gathered from the ranks
+                    check(_lib.load().stark_b200_model_tp_rows_init(m._h, handle), "model_tp_rows_init")
+                    handles = b"".join(tp.all_gather(bytes(handle)))
+                    check(_lib.load().stark_b200_model_tp_rows_connect(m._h, handles, len(handles)),
+                          "model_tp_rows_connect")
         m._set_matrix(0, _lib.MAT_EMBED, weights["embed"])
         if not cfg["tied"]:
             m._set_matrix(0, _lib.MAT_LM_HEAD, weights["lm_head"])
@@ -154,6 +171,9 @@ class DenseModel:
             m._set_matrix(i, _lib.MAT_O, lw["o"])
             m._set_matrix(i, _lib.MAT_UPGATE, lw["upgate"])
             m._set_matrix(i, _lib.MAT_DOWN, lw["down"])
+            if tp is not None and tp.rows and "o_rows" in lw:
+                m._set_matrix(i, _lib.MAT_O_ROWS, lw["o_rows"])
+                m._set_matrix(i, _lib.MAT_DOWN_ROWS, lw["down_rows"])
             m._set_vector(i, _lib.VEC_ATTN_NORM, lw["attn_norm"])
             m._set_vector(i, _lib.VEC_MLP_NORM, lw["mlp_norm"])
             m._set_vector(i, _lib.VEC_Q_NORM, lw["q_norm"])

@@ -24,10 +24,11 @@ def _gpu_count() -> int:
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("config,ranks,staged", [("tiny", 2, 0), ("small", 2, 0), ("small", 2, 1), ("small", 4, 0),
-                                                 ("small", 8, 0)])
-def test_ranks_match_oracle_and_single_gpu(config, ranks, staged):
-    """`staged`: the reduction kernel also normalizes and scales the row for the matvec behind it (off by default)."""
+@pytest.mark.parametrize("config,ranks,mode", [("tiny", 2, ""), ("small", 2, ""), ("small", 2, "staged"),
+                                               ("small", 2, "token-rows"), ("small", 4, ""), ("small", 8, "")])
+def test_ranks_match_oracle_and_single_gpu(config, ranks, mode):
+    """Modes: "staged", the reduction kernel also normalizes and scales the row for the matvec behind it (off by
+    default); "token-rows", prompt rows take the token path instead of batched passes across the ranks."""
     if _gpu_count() < ranks:
         pytest.skip(f"needs {ranks} GPUs")
     with socket.socket() as s:
@@ -35,7 +36,7 @@ def test_ranks_match_oracle_and_single_gpu(config, ranks, staged):
         port = s.getsockname()[1]
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
            "127.0.0.1", "--master-port", str(port), str(Path(__file__).resolve()), config]
-    env = dict(os.environ, STARK_B200_TP_STAGE=str(staged))
+    env = dict(os.environ, STARK_B200_TP_STAGE=str(int(mode == "staged")), STARK_B200_TEST_TP_MODE=mode)
     res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=900, env=env)
     failed = [line for line in res.stdout.splitlines() if "RANK-FAILED" in line]
     assert res.returncode == 0, "\n".join(failed) + res.stdout[-3000:] + res.stderr[-1500:]
@@ -64,13 +65,20 @@ def _rank_main(config: str) -> None:
     cfg = S.CONFIGS[config]
     w = S.dense_weights(cfg, seed=0)
     context = 256
-    model = DenseModel.load(cfg, w, context, tp=TensorParallel(rank, ranks, all_gather))
+    batched = os.environ.get("STARK_B200_TEST_TP_MODE", "") != "token-rows"
+    model = DenseModel.load(cfg, w, context, tp=TensorParallel(rank, ranks, all_gather, rows=batched))
     info = model.info()
     # 5 launches per layer, plus one small reduction kernel per exchange unless the exchanges are fused
     assert info.launches_per_step in (1 + 5 * cfg["layers"] + 2, 1 + 7 * cfg["layers"] + 2)
 
     prompt = S.prompt(cfg, 70, seed=5)  # crosses a KV page boundary
+    before = model.info().launches_issued
     model.prefill(prompt)
+    issued = model.info().launches_issued - before
+    if batched:  # one pass over 69 rows (8 kernels and 4 gathers a layer) and one token, not 70 tokens
+        assert issued == 1 + 12 * cfg["layers"] + info.launches_per_step, issued
+    else:
+        assert issued >= 69 * 5 * cfg["layers"]
     logits = model.logits_bf16()        # gathered from the ranks' vocabulary shards
     assert logits.size == cfg["vocab"]
     first = model.argmax()
@@ -108,6 +116,21 @@ def _rank_main(config: str) -> None:
         model.step_async(tok)
         tok = model.argmax()
     assert fed == tokens[:4].tolist()
+    # a longer prompt in two calls (several row tiles; the second call continues at a position that is not a page
+    # boundary), against the same calls on one GPU: the batched rows are the same bits there, the last row differs
+    # by the token path's summation order
+    model.reset()
+    longer = S.prompt(cfg, 230, seed=8)
+    model.prefill(longer[:150])
+    model.prefill(longer[150:])
+    logits = model.logits_bf16()
+    assert take_device_error() == 0
+    if rank == 0:
+        single = DenseModel.load(cfg, w, context)
+        single.prefill(longer[:150])
+        single.prefill(longer[150:])
+        assert_logits_accepted(single.logits_bf16(), logits)
+        single.close()
     model.close()
     dist.barrier()
     dist.destroy_process_group()

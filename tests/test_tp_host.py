@@ -33,6 +33,31 @@ def _mv(t, x):
     return O.affine_matvec_f32(t["codes"], t["scales"], t["biases"], 30, x, t["n"], t["k"])
 
 
+@pytest.mark.parametrize("ranks", [2, 8])
+def test_row_cuts_for_prompt_passes_gather_to_the_unsharded_products(ranks):
+    """The second cut of o and down (output rows over ALL columns, for batched prompt passes): each rank's product
+    is a slice of the unsharded one, bit for bit, so gathering the slices needs no arithmetic."""
+    cfg = S.CONFIGS["small"]
+    w = S.dense_weights(cfg, seed=2)
+    rng = np.random.default_rng(11)
+    a = rng.standard_normal(cfg["q_heads"] * cfg["head_dim"]).astype(np.float32)
+    g = rng.standard_normal(cfg["inter"]).astype(np.float32)
+    F = w["layers"][2]
+    parts_o, parts_d = [], []
+    for rank in range(ranks):
+        _, lw, _ = shard_dense(cfg, w, rank, ranks)
+        L = lw["layers"][2]
+        assert L["o_rows"]["n"] == L["down_rows"]["n"] == cfg["hidden"] // ranks
+        assert L["o_rows"]["k"] == cfg["q_heads"] * cfg["head_dim"] and L["down_rows"]["k"] == cfg["inter"]
+        parts_o.append(_mv(L["o_rows"], a))
+        parts_d.append(_mv(L["down_rows"], g))
+    assert np.array_equal(np.concatenate(parts_o), _mv(F["o"], a))
+    assert np.array_equal(np.concatenate(parts_d), _mv(F["down"], g))
+    # the smallest width that still fills a whole 128-row tile per rank
+    _, lw, _ = shard_dense(S.CONFIGS["tiny"], S.dense_weights(S.CONFIGS["tiny"], seed=0), 0, 2)
+    assert "o_rows" in lw["layers"][0]           # 256 / 2 = 128 rows
+
+
 @pytest.mark.parametrize("ranks", [4, 8])
 def test_four_and_eight_rank_shards_cover_the_model(ranks):
     """Every rank's shard of the `small` shape (8 KV heads): whole heads, whole quantization groups, and over
