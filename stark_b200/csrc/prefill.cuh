@@ -27,7 +27,13 @@ struct GemmArgs {
     uint32_t ld_out;
     QmvEpilogue epilogue;  // kEpiStore, kEpiResidual or kEpiSwiGlu
     uint32_t *error_word;
+    // Tensor parallel (more than kPrefillSmallRows rows): `peers` further destinations, each the place of `out` in
+    // another rank's row buffer.  The epilogue stores every output segment there too, so that the column slice is
+    // in every rank's buffer when the launch has finished (a flag round then closes the gather).
+    uint16_t *peer_out[kMaxExchangeRanks] = {};
+    uint32_t peers = 0;
 };
+constexpr uint32_t kPrefillSmallRows = 16;  // up to this many rows take the few-rows kernels
 // One launch; the kernel bounds every wait and reports through the error word.
 stark_b200_status prefill_gemm_launch(const GemmArgs &args, cudaStream_t stream);
 // ---- row-wise operators over a chunk of M rows (prefill_ops.cu) ---------------------------------------

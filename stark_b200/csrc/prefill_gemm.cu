@@ -50,6 +50,10 @@ struct GemmParams {
     uint32_t ld_out;
     uint32_t epilogue;
     uint32_t *error_word;
+    // tensor parallel: the same place in the other ranks' row buffers (peer mappings); the epilogue stores every
+    // output segment there as well, tile by tile, so the all-gather of the column slices rides under the contraction
+    uint16_t *peer_out[kMaxExchangeRanks];
+    uint32_t peers;
     uint32_t stop_after;  // 0: the whole kernel.  1: set-up and tensor-memory allocation only; 2: + operand staging
                           // (no tensor-core work); 3: + tcgen05.mma (accumulators not read).  A bring-up aid: a
                           // fault in one kind of instruction is located by the first stage that shows it.
@@ -333,8 +337,11 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
 
         // ------------------------------------------------ epilogue: warp -> (sub-partition, accumulator half)
         const uint32_t sub = warp & 3u, half = d >> 2;
-        if (!mbar_wait_bounded(acc_full, 0, abort_flag) && lane == 0) atomicOr(p.error_word, kErrMbarTimeout);
+        const bool acc_ok = mbar_wait_bounded(acc_full, 0, abort_flag);
+        if (!acc_ok && lane == 0) atomicOr(p.error_word, kErrMbarTimeout);
         tc_fence_after();
+        // every tensor-core read of the operand stages has completed: their first bytes serve as 4 KB of scratch per warp
+        uint8_t *scratch = stages + d * 4096u;
         const uint32_t row = m0 + half * 128u + sub * 32u + lane;  // this thread's row of the output
         const bool row_ok = row < p.m;
 #pragma unroll 1
@@ -364,6 +371,31 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
                     uint4 *dst = reinterpret_cast<uint4 *>(p.out + (size_t)row * p.ld_out + o0);
                     dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                     dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                }
+                if (p.peers && acc_ok) {
+                    // The same 32 x 16 block to the other ranks.  A lane holds 32 bytes of ITS row: stored from here, one
+                    // instruction would touch 32 rows with 16 bytes each, and over NVLink every such fragment is a packet
+                    // of its own.  Through the warp's scratch rows (48-byte pitch: conflict-free) the lanes regroup
+                    // so that two neighbours write one row's 32 contiguous bytes.
+                    uint4 *mine = reinterpret_cast<uint4 *>(scratch + lane * 48u);
+                    mine[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    mine[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                    __syncwarp();
+#pragma unroll
+                    for (uint32_t j = 0; j < 2u; ++j) {
+                        const uint32_t r = 16u * j + (lane >> 1), q = lane & 1u;
+                        const uint4 v = *reinterpret_cast<const uint4 *>(scratch + r * 48u + q * 16u);
+                        const uint32_t prow = row - lane + r;
+                        if (prow < p.m && o0 + 16u <= p.rows / 2u) {
+                            const size_t at = (size_t)prow * p.ld_out + o0 + q * 8u;
+#pragma unroll
+                            for (uint32_t k = 0; k + 1u < kMaxExchangeRanks; ++k) {
+                                if (k >= p.peers) break;
+                                *reinterpret_cast<uint4 *>(p.peer_out[k] + at) = v;
+                            }
+                        }
+                    }
+                    __syncwarp();
                 }
             } else {
                 const bool cols_ok = f0 + 32u <= p.rows;
@@ -395,6 +427,30 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
                     for (int q4 = 0; q4 < 4; ++q4)
                         dst[q4] = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
                 }
+                if (p.peers && acc_ok) {
+                    // to the other ranks, regrouped through the warp's scratch rows (80-byte pitch) so that four
+                    // neighbouring lanes write one row's 64 contiguous bytes (see the gated branch)
+                    uint4 *mine = reinterpret_cast<uint4 *>(scratch + lane * 80u);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        mine[q4] = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+                    __syncwarp();
+#pragma unroll
+                    for (uint32_t j = 0; j < 4u; ++j) {
+                        const uint32_t r = 8u * j + (lane >> 2), q = lane & 3u;
+                        const uint4 v = *reinterpret_cast<const uint4 *>(scratch + r * 80u + q * 16u);
+                        const uint32_t prow = row - lane + r;
+                        if (prow < p.m && cols_ok) {
+                            const size_t at = (size_t)prow * p.ld_out + f0 + q * 8u;
+#pragma unroll
+                            for (uint32_t k = 0; k + 1u < kMaxExchangeRanks; ++k) {
+                                if (k >= p.peers) break;
+                                *reinterpret_cast<uint4 *>(p.peer_out[k] + at) = v;
+                            }
+                        }
+                    }
+                    __syncwarp();
+                }
             }
         }
     }
@@ -413,6 +469,7 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
 // instruction instead of 128 x 128 x 16) and the kernel runs at the pace of its dequantizing prologue, i.e. of
 // the weight stream.  Accumulators: lane = feature, column = row.
 constexpr uint32_t kSmallRows = 16;
+static_assert(kSmallRows == kPrefillSmallRows, "the model-level pass decides by this bound who stores to the peers");
 constexpr uint32_t kSmallXStage = kSmallRows * 128u;            // 2 KB: 16 rows x 64 columns bf16
 constexpr uint32_t kSmallWStage = 128u * 128u;                  // 16 KB: 128 features x 64 columns bf16
 constexpr uint32_t kSmallStageBytes = kSmallWStage + kSmallXStage;   // 18 KB, a multiple of 1024
@@ -599,6 +656,10 @@ stark_b200_status prefill_gemm_launch(const GemmArgs &a, cudaStream_t stream) {
         return STARK_B200_INVALID_ARGUMENT;
     // A handful of rows is a weight stream, not a contraction: the several-rows matvec reads the matrix once at the
     // pace of the one-token path.
+    if (a.peers > kMaxExchangeRanks) return STARK_B200_INVALID_ARGUMENT;
+    for (uint32_t r = 0; r < a.peers; ++r)
+        if (!a.peer_out[r] || (reinterpret_cast<uintptr_t>(a.peer_out[r]) & 15u)) return STARK_B200_INVALID_ARGUMENT;
+    if (a.peers && a.m <= kSmallRows) return STARK_B200_UNSUPPORTED;  // only the 256-row tile kernel stores to peers
     if (tunables().rows_matvec && qmv_multi_supports(w, a.m, false)) {
         QmvMultiArgs q{};
         q.matrix = w;
@@ -637,6 +698,8 @@ stark_b200_status prefill_gemm_launch(const GemmArgs &a, cudaStream_t stream) {
     p.ld_out = a.ld_out;
     p.epilogue = a.epilogue;
     p.error_word = a.error_word;
+    p.peers = a.peers;
+    for (uint32_t r = 0; r < a.peers; ++r) p.peer_out[r] = a.peer_out[r];
     p.stop_after = tunables().gemm_stop_after;
     static SmemOptIn once, once_small;
     const uint32_t width = small ? 128u : kBN;

@@ -98,6 +98,14 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
     const uint32_t attn_local = c.q_heads * kHeadDim, attn_width = attn_local * ranks, inter_total = c.inter * ranks;
     const uint32_t h_slice = c.hidden / ranks;
     uint16_t *attn_rows = tp ? reinterpret_cast<uint16_t *>(m->tp_rows_local + rows_region_attn(m)) : m->chunk_attn;
+    // more than a handful of rows: the contraction's epilogue stores its tiles to the peers itself
+    const bool push = tp && mrows > kPrefillSmallRows && tunables().tp_rows_push;
+    auto peers_of = [&](GemmArgs &g, size_t region_offset) {  // the place of g.out in the other ranks' buffers
+        g.peers = 0;
+        if (!push) return;
+        for (uint32_t r = 0; r < ranks; ++r)
+            if (r != rank) g.peer_out[g.peers++] = reinterpret_cast<uint16_t *>(m->tp_rows.base[r] + region_offset);
+    };
     uint32_t gathers = 0;
     auto gather = [&](const uint16_t *src, uint32_t src_ld, size_t dst_offset, uint32_t dst_ld, uint32_t column,
                       uint32_t width, bool own) -> stark_b200_status {
@@ -144,9 +152,11 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
         g.out = m->chunk_h + (size_t)rank * h_slice;
         g.ld_out = c.hidden;
         g.epilogue = kEpiResidual;
+        peers_of(g, rows_region_h(m) + (size_t)rank * h_slice * 2u);
         if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        g.peers = 0;
         if (tp && (st = gather(m->chunk_h + (size_t)rank * h_slice, c.hidden, rows_region_h(m), c.hidden, rank * h_slice,
-                               h_slice, false)) != STARK_B200_OK)
+                               push ? 0u : h_slice, false)) != STARK_B200_OK)
             return st;
         // act = silu(gate) * up
         uint16_t *act_slice = m->chunk_act + (size_t)rank * c.inter;  // this rank's columns of the whole rows
@@ -161,10 +171,12 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
             g.out = act_slice;
             g.ld_out = inter_total;
             g.epilogue = kEpiSwiGlu;
+            peers_of(g, rows_region_act(m) + (size_t)rank * c.inter * 2u);
             if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+            g.peers = 0;
         }
-        if (tp && (st = gather(act_slice, inter_total, rows_region_act(m), inter_total, rank * c.inter, c.inter, false)) !=
-                      STARK_B200_OK)
+        if (tp && (st = gather(act_slice, inter_total, rows_region_act(m), inter_total, rank * c.inter,
+                               push ? 0u : c.inter, false)) != STARK_B200_OK)
             return st;
         // h = bf16(bf16(W_down act) + h)
         g.w = tp ? L.down_rows : L.down;
@@ -172,9 +184,11 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
         g.out = m->chunk_h + (size_t)rank * h_slice;
         g.ld_out = c.hidden;
         g.epilogue = kEpiResidual;
+        peers_of(g, rows_region_h(m) + (size_t)rank * h_slice * 2u);
         if ((st = prefill_gemm_launch(g, s)) != STARK_B200_OK) return st;
+        g.peers = 0;
         if (tp && (st = gather(m->chunk_h + (size_t)rank * h_slice, c.hidden, rows_region_h(m), c.hidden, rank * h_slice,
-                               h_slice, false)) != STARK_B200_OK)
+                               push ? 0u : h_slice, false)) != STARK_B200_OK)
             return st;
     }
     m->launches_issued += 1u + (fused_norm ? 6u : 8u) * c.layers + (split_rows ? c.layers : 0u) + gathers;

@@ -94,7 +94,8 @@ inline size_t tp_rows_region_bytes(size_t rows, size_t hidden, size_t attn_width
 // `dst_offset` + the same columns (row stride dst_ld) of every OTHER rank's region -- and of this rank's own when
 // `own` is set -- then publishes gather number `ticket` to the peers and waits (bounded) until every peer has
 // published it too.  When the launch has finished, the buffer holds the whole rows.  `arrive` is a zeroed device
-// word the launches share.  width and both strides are multiples of 8 elements.
+// word the launches share.  width and both strides are multiples of 8 elements.  width 0: no copy, the flag round
+// alone (the kernel before it stored its output to the peers as it went: GemmArgs::peer_out).
 struct TpGatherArgs {
     const uint16_t *src;
     uint32_t src_ld;

@@ -18,7 +18,7 @@ __global__ void __launch_bounds__(kGatherThreads) tp_rows_gather_kernel(TpRowsRe
     pdl_wait();  // the slice is the previous kernel's output
     __shared__ uint32_t last_s;
     const uint32_t per_row = a.width / 8u;
-    const size_t total = (size_t)a.rows * per_row;
+    const size_t total = per_row ? (size_t)a.rows * per_row : 0u;
     for (size_t i = (size_t)blockIdx.x * kGatherThreads + threadIdx.x; i < total; i += (size_t)gridDim.x * kGatherThreads) {
         const uint32_t row = (uint32_t)(i / per_row), c = (uint32_t)(i % per_row) * 8u;
         const uint4 v = *reinterpret_cast<const uint4 *>(a.src + (size_t)row * a.src_ld + c);
@@ -61,12 +61,14 @@ __global__ void __launch_bounds__(kGatherThreads) tp_rows_gather_kernel(TpRowsRe
 
 stark_b200_status tp_rows_gather_launch(const TpRowsRegion &g, const TpGatherArgs &a, uint32_t *arrive,
                                         uint32_t *error_word, cudaStream_t stream) {
-    if (g.size < 2 || g.size > kMaxTpRanks || g.rank >= g.size || !a.src || !arrive || a.rows == 0 || a.width == 0 ||
-        a.width % 8u || a.src_ld % 8u || a.dst_ld % 8u || a.column % 8u || (a.dst_offset & 15u) ||
-        (reinterpret_cast<uintptr_t>(a.src) & 15u) || a.column + a.width > a.dst_ld)
+    if (g.size < 2 || g.size > kMaxTpRanks || g.rank >= g.size || !arrive) return STARK_B200_INVALID_ARGUMENT;
+    // width 0: the producing kernel has stored the slice to the peers itself; only the flag round is left
+    if (a.width != 0 &&
+        (!a.src || a.rows == 0 || a.width % 8u || a.src_ld % 8u || a.dst_ld % 8u || a.column % 8u || (a.dst_offset & 15u) ||
+         (reinterpret_cast<uintptr_t>(a.src) & 15u) || a.column + a.width > a.dst_ld))
         return STARK_B200_INVALID_ARGUMENT;
     const size_t chunks = (size_t)a.rows * (a.width / 8u);
-    const uint32_t ctas = (uint32_t)std::min<size_t>(148u * 4u, (chunks + kGatherThreads - 1u) / kGatherThreads);
+    const uint32_t ctas = (uint32_t)std::max<size_t>(1u, std::min<size_t>(148u * 4u, (chunks + kGatherThreads - 1u) / kGatherThreads));
     tp_rows_gather_kernel<<<ctas, kGatherThreads, 0, stream>>>(g, a, arrive, error_word);
     SB_CUDA(cudaGetLastError());
     return STARK_B200_OK;
