@@ -229,12 +229,53 @@ __global__ void __launch_bounds__(kAttnWarps * 32) moe_attention_kernel(const Mo
 // The same attention with the query heads of one KV head handled together (G = q_heads / kv_heads): a CTA
 // per (KV head, span) reads each K and V row once and scores it against all G queries, instead of G CTAs
 // reading the same rows.  Per warp: G running (max, sum, accumulator) states; warp g merges head g's states.
+// One 128-wide head by one warp, as moe_heads_kernel does it with one thread per element: per-head norm, then rope
+// on the pairs (i, i + 64).  Lane L holds elements L, 32 + L, 64 + L, 96 + L -- the four 32-element runs whose sums
+// that kernel's four warps form, added in the same order -- so the values are the same bits; both halves of a
+// rotation pair sit in one lane.
+__device__ inline void moe_head_prepare(const float *src, const float *norm_w, float eps, float theta, uint32_t position,
+                                        uint32_t lane, float out[4]) {
+    constexpr uint32_t D = 128;
+    float v[4], part[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        v[k] = src[32 * k + lane];
+        float s = v[k] * v[k];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+        part[k] = s;
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) sum += part[k];
+    const float scale = 1.0f / sqrtf(sum / (float)D + eps);
+    float head[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) head[k] = v[k] * scale * norm_w[32 * k + lane];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const uint32_t pair = 32u * k + lane;
+        const float angle = (float)position * powf(theta, -((float)(2u * pair)) / (float)D);
+        float sn, cs;
+        sincosf(angle, &sn, &cs);
+        const float a = head[k], b = head[k + 2];
+        out[k] = a * cs - b * sn;
+        out[k + 2] = a * sn + b * cs;
+    }
+}
+
+// `raw` (fused form): the [q; k; v] projection as the matvec left it.  Every CTA then prepares the group's query
+// heads itself (norm, rope; one warp per head) and the CTA whose span holds the new position also prepares the
+// key head and writes it and the value head into the cache before anybody reads that row -- the work of
+// moe_heads_kernel without its launch.  raw == nullptr: `q` holds prepared heads and the cache row is there.
 template <int G>
 __global__ void __launch_bounds__(kAttnWarps * 32) moe_attention_grouped_kernel(const MoeState *st, const float *q,
-                                                                                const float *keys,
-                                                                                const float *values, float *part,
+                                                                                float *keys, float *values, float *part,
                                                                                 uint32_t splits, uint32_t kv_heads,
-                                                                                float scale, uint32_t context) {
+                                                                                float scale, uint32_t context,
+                                                                                const float *raw, const float *q_norm,
+                                                                                const float *k_norm, float eps,
+                                                                                float theta) {
     constexpr uint32_t D = 128;
     __shared__ float sm[kAttnWarps][G], sl[kAttnWarps][G];
     __shared__ float4 sacc[kAttnWarps][G][32];
@@ -246,9 +287,34 @@ __global__ void __launch_bounds__(kAttnWarps * 32) moe_attention_grouped_kernel(
     const uint32_t lo = min(rows, split * span), hi = min(rows, lo + span);
     const size_t kv_row = (size_t)kv_heads * D;
     const uint32_t begin = kvh * D;
+    if (raw) {
+        float *qs = reinterpret_cast<float *>(&sacc[0][0][0]);  // [G][128], before the accumulators need the space
+        const uint32_t position = rows - 1u, q_heads = kv_heads * G;
+        float o[4];
+        for (uint32_t g = warp; g < (uint32_t)G; g += kAttnWarps) {
+            moe_head_prepare(raw + ((size_t)kvh * G + g) * D, q_norm, eps, theta, position, lane, o);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) qs[g * D + 32 * k + lane] = o[k];
+        }
+        if (hi == rows && lo < hi) {  // this span ends with the new row
+            if (warp == kAttnWarps - 1u) {
+                moe_head_prepare(raw + ((size_t)q_heads + kvh) * D, k_norm, eps, theta, position, lane, o);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) keys[position * kv_row + begin + 32 * k + lane] = o[k];
+            } else if (warp == kAttnWarps - 2u) {
+                const float *src = raw + ((size_t)q_heads + kv_heads + kvh) * D;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) values[position * kv_row + begin + 32 * k + lane] = src[32 * k + lane];
+            }
+        }
+        __syncthreads();  // the heads are in shared memory, the new cache row is visible to this CTA
+        q = qs;
+    }
     float4 qv[G];
 #pragma unroll
-    for (int g = 0; g < G; ++g) qv[g] = reinterpret_cast<const float4 *>(q + ((size_t)kvh * G + g) * D)[lane];
+    for (int g = 0; g < G; ++g)
+        qv[g] = reinterpret_cast<const float4 *>(q + (raw ? (size_t)g : (size_t)kvh * G + g) * D)[lane];
+    if (raw) __syncthreads();  // every warp has its copy: the accumulators may take the space
     float m[G], l[G];
     float4 acc[G];
 #pragma unroll
@@ -348,19 +414,60 @@ __global__ void __launch_bounds__(128) moe_attention_merge_kernel(const float *p
 // selection: top-k of the scores (value descending, index ascending), softmax over the selected scores
 // (qwen.rs:872-874, math.rs:36-66).  ids[0, active) are the experts in selection order; ids[active, 2 active)
 // the same plus `experts`, which addresses the up half of a fused [gate; up] bank.
-__global__ void __launch_bounds__(256) moe_router_select_kernel(const float *w, const float *x, float *scores,
+//
+// With `update` the kernel also does what moe_add_norm_kernel would have done in a launch of its own before it:
+// every CTA forms n = rms_norm(residual + update, norm_w) in shared memory for its own dot product (8 KB of
+// redundant reads per CTA against a launch and its hand-off), and CTA 0 leaves n in `x` for the expert matvecs.
+// The residual itself is NOT rewritten here (other CTAs are still reading it): the mixture kernel after the
+// experts adds `update` first and the mixture second, the order of two separate adds.  The sums are formed in the
+// order of moe_add_norm_kernel's 1024 threads (thread t stands for t, t + 256, t + 512 and t + 768 of them), so
+// the values are the same bits.
+constexpr uint32_t kRouterNormMaxHidden = 4096;
+__global__ void __launch_bounds__(256) moe_router_select_kernel(const float *w, float *x, float *scores,
                                                                 uint32_t hidden, uint32_t experts, uint32_t active,
                                                                 uint32_t *ids, float *probs, uint32_t *arrivals,
                                                                 uint32_t *ids_global, uint32_t ep_first,
-                                                                uint32_t ep_local) {
+                                                                uint32_t ep_local, const float *residual,
+                                                                const float *update, const float *norm_w, float eps) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[32];
     __shared__ float sv[1024];
     __shared__ bool last;
+    __shared__ __align__(16) float xs[kRouterNormMaxHidden];
     const uint32_t e = blockIdx.x;
     const float4 *row = reinterpret_cast<const float4 *>(w + (size_t)e * hidden);
     const float4 *xv = reinterpret_cast<const float4 *>(x);
+    if (update) {
+        float part[4];
+#pragma unroll
+        for (uint32_t k = 0; k < 4u; ++k) {
+            float s = 0.0f;
+            for (uint32_t i = threadIdx.x + 256u * k; i < hidden; i += 1024u) {
+                const float v = residual[i] + update[i];
+                xs[i] = v;
+                s += v * v;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            part[k] = s;
+        }
+        if ((threadIdx.x & 31u) == 0) {
+#pragma unroll
+            for (uint32_t k = 0; k < 4u; ++k) scratch[(threadIdx.x >> 5) + 8u * k] = part[k];
+        }
+        __syncthreads();
+        float total = 0.0f;
+        for (int wi = 0; wi < 32; ++wi) total += scratch[wi];
+        const float scale = 1.0f / sqrtf(total / (float)hidden + eps);
+        for (uint32_t i = threadIdx.x; i < hidden; i += 256u) {  // each thread its own elements again
+            const float nv = xs[i] * scale * norm_w[i];
+            xs[i] = nv;
+            if (e == 0) x[i] = nv;
+        }
+        __syncthreads();  // also frees `scratch` for the block sum below
+        xv = reinterpret_cast<const float4 *>(xs);
+    }
     float s = 0.0f;
     for (uint32_t i = threadIdx.x; i < hidden / 4u; i += 256u) {
         const float4 a = row[i], b = xv[i];
@@ -423,9 +530,10 @@ __global__ void __launch_bounds__(256) moe_router_select_kernel(const float *w, 
 // x += update, where update is one row (probs == nullptr) or the expert mixture sum_r probs[r] * rows[r]
 // with r ascending from zero (qwen.rs:894-899); then, if w is given, out = rms_norm(x, w): the residual add
 // and the norm that always follows it, in one CTA.
+// `first`, if given, is a row added before that (the attention update the router kernel left to this one).
 __global__ void __launch_bounds__(1024) moe_add_norm_kernel(float *x, const float *rows, const float *probs,
                                                             uint32_t active, const float *w, float *out, uint32_t n,
-                                                            float eps) {
+                                                            float eps, const float *first) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[32];
@@ -435,7 +543,7 @@ __global__ void __launch_bounds__(1024) moe_add_norm_kernel(float *x, const floa
     float s = 0.0f;
     for (uint32_t i = threadIdx.x; i < n; i += 1024u) {
         float r;
-        const float xi = x[i];
+        const float xi = first ? x[i] + first[i] : x[i];
         if (probs) {
             r = 0.0f;
 #pragma unroll 8
@@ -477,7 +585,8 @@ __global__ void __launch_bounds__(256) moe_ep_push_kernel(EpRegion g, const floa
 __global__ void __launch_bounds__(1024) moe_ep_mix_norm_kernel(float *x, const unsigned long long *packets, const float *probs,
                                                                uint32_t active, const float *w, float *out, uint32_t n,
                                                                float eps, const uint32_t *ep_tokens, uint32_t layer,
-                                                               uint32_t layers, unsigned long long wait_ns, MoeState *st) {
+                                                               uint32_t layers, unsigned long long wait_ns, MoeState *st,
+                                                               const float *first) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ float scratch[32];
@@ -517,7 +626,7 @@ __global__ void __launch_bounds__(1024) moe_ep_mix_norm_kernel(float *x, const u
             for (uint32_t j = 0; j < 8u; ++j)
                 if (e0 + j < active) r += sp[e0 + j] * __uint_as_float((uint32_t)q[j]);
         }
-        const float v = x[i] + r;
+        const float v = (first ? x[i] + first[i] : x[i]) + r;
         x[i] = v;
         s += v * v;
     }
@@ -667,6 +776,10 @@ struct MoeModel {
     uint32_t nodes = 0;
     uint32_t position = 0;  // host mirror of the device position
     bool poisoned = false;
+    // STARK_B200_MOE_FUSE=1: the launches that hold only a hand-off (residual add + norm, per-head norm + rope) run
+    // inside the kernel that consumes them: 8 launches a layer instead of 10, the same bits, and no faster (the
+    // consumers' CTAs repeat the work behind the same wait), so it is off by default
+    bool fuse = false;
     // expert parallelism (ep.ranks == 0: one GPU)
     EpRegion ep{};
     uint8_t *ep_local = nullptr;      // this rank's exchange region
@@ -754,31 +867,42 @@ stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
         float *keys = m->keys + (size_t)l * m->kv_layer(), *values = m->values + (size_t)l * m->kv_layer();
         uint32_t *ids = m->ids + (size_t)l * 2u * A;
         SB_TRY(qmv_rows_launch(m->qkv[l], m->n, 0, m->qkv_out, 1, nullptr, STARK_B200_F32, s, pdl));
-        SB_TRY(moe_launch(moe_heads_kernel, QH + 2u * KV, D, pdl, s, m->state, m->qkv_out,
-                          m->norm(STARK_B200_MOE_TENSOR_Q_NORM, l), m->norm(STARK_B200_MOE_TENSOR_K_NORM, l), keys, values,
-                          QH, KV, D, c.rms_eps, c.rope_theta, c.context_tokens));
         // query heads of one KV head together where the group size has an instantiation, else head by head
         const uint32_t group = QH / KV, gsplits = std::max(kAttnSplits, std::min(kMoeMaxAttnSplits, moe_attention_ctas() / KV));
+        const bool grouped_form = group == 8u || group == 4u || group == 2u;
+        // per-head norm, rope and the cache row: inside the grouped attention kernel (fused), or a launch of their own
+        const bool fused_heads = m->fuse && grouped_form && D == 128u;
+        if (!fused_heads)
+            SB_TRY(moe_launch(moe_heads_kernel, QH + 2u * KV, D, pdl, s, m->state, m->qkv_out,
+                              m->norm(STARK_B200_MOE_TENSOR_Q_NORM, l), m->norm(STARK_B200_MOE_TENSOR_K_NORM, l), keys, values,
+                              QH, KV, D, c.rms_eps, c.rope_theta, c.context_tokens));
         uint32_t splits = kAttnSplits;
-        if (group == 8u || group == 4u || group == 2u) {
+        if (grouped_form) {
             splits = gsplits;
             auto grouped = group == 8u ? moe_attention_grouped_kernel<8>
                                        : (group == 4u ? moe_attention_grouped_kernel<4> : moe_attention_grouped_kernel<2>);
             SB_TRY(moe_launch(grouped, dim3(KV, splits), kAttnWarps * 32, pdl, s, m->state, m->qkv_out, keys, values,
-                              m->part, splits, KV, scale, c.context_tokens));
+                              m->part, splits, KV, scale, c.context_tokens, fused_heads ? m->qkv_out : nullptr,
+                              m->norm(STARK_B200_MOE_TENSOR_Q_NORM, l), m->norm(STARK_B200_MOE_TENSOR_K_NORM, l), c.rms_eps,
+                              c.rope_theta));
         } else {
             SB_TRY(moe_launch(moe_attention_kernel, dim3(QH, kAttnSplits), kAttnWarps * 32, pdl, s, m->state, m->qkv_out,
                               keys, values, m->part, QH, KV, scale, c.context_tokens));
         }
         SB_TRY(moe_launch(moe_attention_merge_kernel, QH, 128, pdl, s, m->part, m->att, splits));
         SB_TRY(qmv_rows_launch(m->o[l], m->att, 0, m->update, 1, nullptr, STARK_B200_F32, s, pdl));
-        SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->update, nullptr, 1u,
-                          m->norm(STARK_B200_MOE_TENSOR_FFN_NORM, l), m->n, H, c.rms_eps));
+        // the residual add and the norm before the router: in the router's CTAs (fused), or a launch of their own
+        const bool fused_norm = m->fuse && H <= kRouterNormMaxHidden;
+        if (!fused_norm)
+            SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->update, nullptr, 1u,
+                              m->norm(STARK_B200_MOE_TENSOR_FFN_NORM, l), m->n, H, c.rms_eps, nullptr));
+        const float *pending_update = fused_norm ? m->update : nullptr;  // added to the residual by the mixture kernel
         const bool ep = m->ep.ranks > 1u;
         SB_TRY(moe_launch(moe_router_select_kernel, c.experts, 256, pdl, s, m->router + (size_t)l * c.experts * H, m->n,
                           m->scores, H, c.experts, A, ids, m->probs, m->arrivals,
                           ep ? m->ids_global + (size_t)l * A : nullptr, ep ? m->ep.rank * m->ep.local_experts : 0u,
-                          ep ? m->ep.local_experts : 0u));
+                          ep ? m->ep.local_experts : 0u, m->x, pending_update,
+                          m->norm(STARK_B200_MOE_TENSOR_FFN_NORM, l), c.rms_eps));
         SB_TRY(qmv_rows_launch(m->gate_up[l], m->n, 0, m->gate_out, 2u * A, ids, STARK_B200_F32, s, pdl));
         if (m->down[l]->format == kFmtQ4_K) {  // the gated activation is formed while the down projection stages its input
             SB_TRY(q4kt_launch(m->down[l], m->gate_out, I, m->expert_out, A, ids, STARK_B200_F32, s, pdl,
@@ -794,9 +918,10 @@ stark_b200_status moe_issue(MoeModel *m, bool want_logits, cudaStream_t s) {
         if (ep) {
             SB_TRY(moe_launch(moe_ep_push_kernel, A, 256, pdl, s, m->ep, m->expert_out, ids, l, c.layers, A, H, m->ep_tokens));
             SB_TRY(moe_launch(moe_ep_mix_norm_kernel, 1, 1024, pdl, s, m->x, ep_packets(m->ep_local, l, A, H), m->probs, A,
-                              next, m->n, H, c.rms_eps, m->ep_tokens, l, c.layers, m->ep.wait_ns, m->state));
+                              next, m->n, H, c.rms_eps, m->ep_tokens, l, c.layers, m->ep.wait_ns, m->state, pending_update));
         } else {
-            SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->expert_out, m->probs, A, next, m->n, H, c.rms_eps));
+            SB_TRY(moe_launch(moe_add_norm_kernel, 1, 1024, pdl, s, m->x, m->expert_out, m->probs, A, next, m->n, H, c.rms_eps,
+                              pending_update));
         }
     }
     if (want_logits) SB_TRY(qmv_rows_launch(m->output, m->n, 0, m->logits, 1, nullptr, STARK_B200_F32, s, pdl));
@@ -901,6 +1026,7 @@ stark_b200_status stark_b200_moe_model_create(const stark_b200_moe_config *confi
         return STARK_B200_INVALID_ARGUMENT;
     if (!device_context()) return STARK_B200_OUT_OF_MEMORY;
     MoeModel *m = new MoeModel();
+    if (const char *e = getenv("STARK_B200_MOE_FUSE")) m->fuse = e[0] == '1';
     m->cfg = c;
     cudaGetDevice(&m->device);
     m->qkv.assign(c.layers, nullptr), m->o.assign(c.layers, nullptr), m->gate_up.assign(c.layers, nullptr);
@@ -1176,7 +1302,7 @@ stark_b200_status stark_b200_moe_model_position(const stark_b200_moe_model *mode
 stark_b200_status stark_b200_moe_model_launches_per_token(const stark_b200_moe_model *model, uint32_t *out_launches) {
     const MoeModel *m = reinterpret_cast<const MoeModel *>(model);
     if (!m || !out_launches) return STARK_B200_INVALID_ARGUMENT;
-    *out_launches = m->nodes ? m->nodes : 4u + 10u * m->cfg.layers + (m->ep.ranks > 1u ? m->cfg.layers + 1u : 0u);
+    *out_launches = m->nodes ? m->nodes : 4u + (m->fuse ? 8u : 10u) * m->cfg.layers + (m->ep.ranks > 1u ? m->cfg.layers + 1u : 0u);
     return STARK_B200_OK;
 }
 

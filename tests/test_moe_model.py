@@ -170,8 +170,31 @@ def test_device_decoder_matches_oracle(name):
     model.reset()
     b = model.step(int(prompt[0]))
     assert model.position == 1 and a.tobytes() == b.tobytes()
-    assert model.launches_per_token >= 4 + 10 * cfg["layers"]
+    assert model.launches_per_token >= 4 + 8 * cfg["layers"]
     model.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["moe-small", "moe-a3b-layers"])
+def test_fused_hand_offs_change_no_bit(name, monkeypatch):
+    """The residual add + norm inside the router kernel and the per-head norm + rope inside the attention kernel
+    form their sums in the order of the separate kernels: logits, experts and tokens are the same bits."""
+    from stark_b200.engine import MoEModel
+    cfg = S.MOE_CONFIGS[name]
+    w = S.moe_weights(cfg, seed=4)
+    prompt = S.prompt(cfg, 70, seed=6)
+    seen = []
+    for fuse in ("1", "0"):
+        monkeypatch.setenv("STARK_B200_MOE_FUSE", fuse)
+        model = MoEModel.load(cfg, w, 128)
+        assert model.launches_per_token == 4 + (8 if fuse == "1" else 10) * cfg["layers"]
+        model.ingest(prompt[:-1])
+        logits = model.step(int(prompt[-1]))
+        experts = model.last_experts().tolist()
+        picks = model.generate_greedy(int(logits.argmax()), 12)
+        seen.append((logits.tobytes(), experts, picks.tolist(), model.step(3).tobytes()))
+        model.close()
+    assert seen[0] == seen[1]
 
 
 @pytest.mark.gpu
