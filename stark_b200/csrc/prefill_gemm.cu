@@ -196,6 +196,10 @@ __device__ inline void dequant_record_to_smem(const RecordRegs &r, uint8_t *b_st
     *reinterpret_cast<uint4 *>(p_hi + c1) = make_uint4(hi_row[4], hi_row[5], hi_row[6], hi_row[7]);
 }
 
+// HALVES = 2: a CTA owns 256 rows (two 128-row accumulators over one dequantized weight tile).  HALVES = 1: 128
+// rows -- twice the CTAs, each amortizing its dequantization over half the rows -- for contractions too narrow to
+// fill the SMs with 256-row tiles (a 1 024-feature slice of o or down under tensor parallelism, a 1 024-row pass).
+template <uint32_t HALVES>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmParams p) {
     extern __shared__ uint8_t gemm_smem_raw[];
@@ -209,7 +213,7 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
 
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t n_tile0 = blockIdx.x * (kBN / 16u);  // first 16-row storage tile of this CTA
-    const uint32_t m0 = blockIdx.y * kBM;
+    const uint32_t m0 = blockIdx.y * (128u * HALVES);
 
     if (tid == 0) {
         for (uint32_t s = 0; s < kStages; ++s) {
@@ -241,9 +245,9 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
                     break;
                 }
                 uint8_t *a_stage = stages + slot * kStageBytes;
-                mbar_arrive_expect_tx(&full_a[slot], kAStage);
+                mbar_arrive_expect_tx(&full_a[slot], HALVES * kABox);
                 tma_load_2d(a_stage, &x_map, kg * kBK, m0, &full_a[slot]);
-                tma_load_2d(a_stage + kABox, &x_map, kg * kBK, m0 + 128u, &full_a[slot]);
+                if (HALVES == 2u) tma_load_2d(a_stage + kABox, &x_map, kg * kBK, m0 + 128u, &full_a[slot]);
                 if (++slot == kStages) {
                     slot = 0;
                     phase ^= 1u;
@@ -274,7 +278,7 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
                 const uint32_t a_addr = smem_u32(stages + slot * kStageBytes);
                 const uint32_t b_addr = a_addr + kAStage;
 #pragma unroll
-                for (uint32_t half = 0; half < 2; ++half) {
+                for (uint32_t half = 0; half < HALVES; ++half) {
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < kBK / 16u; ++k4) {
                         const uint64_t adesc = smem_desc_sw128(a_addr + half * kABox + k4 * 32u);
@@ -336,7 +340,9 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
         }
 
         // ------------------------------------------------ epilogue: warp -> (sub-partition, accumulator half)
-        const uint32_t sub = warp & 3u, half = d >> 2;
+        // (with one accumulator the two warps of a sub-partition share its columns instead)
+        const uint32_t sub = warp & 3u, half = HALVES == 2u ? d >> 2 : 0u;
+        const uint32_t c_first = HALVES == 2u ? 0u : (d >> 2) * (kBN / 64u), c_count = kBN / 32u / (3u - HALVES);
         const bool acc_ok = mbar_wait_bounded(acc_full, 0, abort_flag);
         if (!acc_ok && lane == 0) atomicOr(p.error_word, kErrMbarTimeout);
         tc_fence_after();
@@ -345,7 +351,7 @@ prefill_gemm_a4_kernel(const __grid_constant__ CUtensorMap x_map, const GemmPara
         const uint32_t row = m0 + half * 128u + sub * 32u + lane;  // this thread's row of the output
         const bool row_ok = row < p.m;
 #pragma unroll 1
-        for (uint32_t c = 0; c < (stop == 0u ? kBN / 32u : 0u); ++c) {
+        for (uint32_t c = c_first; c < (stop == 0u ? c_first + c_count : 0u); ++c) {
             uint32_t acc[32];
             tmem_ld_32x32(tmem_base + ((sub * 32u) << 16) + half * kBN + c * 32u, acc);
             // columns of the accumulator are storage rows of the matrix: feature = 16 * tile + r
@@ -709,8 +715,20 @@ stark_b200_status prefill_gemm_launch(const GemmArgs &a, cudaStream_t stream) {
         prefill_gemm_a4_small_kernel<<<dim3(feature_tiles, (a.m + kSmallRows - 1u) / kSmallRows), kGemmThreads, kSmallSmem,
                                        stream>>>(map, p);
     } else {
-        if (stark_b200_status s = ensure_dynamic_smem(prefill_gemm_a4_kernel, (int)kGemmSmem, once)) return s;
-        prefill_gemm_a4_kernel<<<dim3(feature_tiles, (a.m + kBM - 1u) / kBM), kGemmThreads, kGemmSmem, stream>>>(map, p);
+        // Tile height by waves over the SMs: a 128-row tile takes 0.87 of a 256-row tile's time (measured: it
+        // dequantizes the same weight tile for half the rows), so it pays only where 256-row tiles leave more than
+        // half of the SMs idle.
+        const uint32_t sms = 148u, full = feature_tiles * ((a.m + kBM - 1u) / kBM), halved = feature_tiles * ((a.m + 127u) / 128u);
+        const float cost_full = (float)((full + sms - 1u) / sms), cost_half = 0.87f * (float)((halved + sms - 1u) / sms);
+        const uint32_t mode = tunables().gemm_half_tiles;  // 0 never, 1 by the rule above, 2 always
+        if (mode == 2u || (mode == 1u && cost_half < cost_full)) {
+            static SmemOptIn once_half;
+            if (stark_b200_status s = ensure_dynamic_smem(prefill_gemm_a4_kernel<1>, (int)kGemmSmem, once_half)) return s;
+            prefill_gemm_a4_kernel<1><<<dim3(feature_tiles, (a.m + 127u) / 128u), kGemmThreads, kGemmSmem, stream>>>(map, p);
+        } else {
+            if (stark_b200_status s = ensure_dynamic_smem(prefill_gemm_a4_kernel<2>, (int)kGemmSmem, once)) return s;
+            prefill_gemm_a4_kernel<2><<<dim3(feature_tiles, (a.m + kBM - 1u) / kBM), kGemmThreads, kGemmSmem, stream>>>(map, p);
+        }
     }
     SB_CUDA(cudaGetLastError());
     return STARK_B200_OK;

@@ -98,8 +98,13 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
     const uint32_t attn_local = c.q_heads * kHeadDim, attn_width = attn_local * ranks, inter_total = c.inter * ranks;
     const uint32_t h_slice = c.hidden / ranks;
     uint16_t *attn_rows = tp ? reinterpret_cast<uint16_t *>(m->tp_rows_local + rows_region_attn(m)) : m->chunk_attn;
-    // more than a handful of rows: the contraction's epilogue stores its tiles to the peers itself
-    const bool push = tp && mrows > kPrefillSmallRows && tunables().tp_rows_push;
+    // More than a handful of rows: the contraction's epilogue can store its tiles to the peers itself
+    // (tp_rows_push 1: always, 0: never, 2: between two ranks only).  Measured on the 8B shape, 4 096 rows: with one
+    // peer the stores ride under the contraction (55.8 ms a pass against 57.1 with the copy kernel); with three
+    // peers they hold the CTA, and with it the SM, three times as long, and the copy kernel -- 592 CTAs that do
+    // nothing else -- wins (41.2 ms against 43.7; pushing only from the one contraction of several waves: 43.1).
+    const uint32_t push_mode = tp && mrows > kPrefillSmallRows ? tunables().tp_rows_push : 0u;
+    const bool push = push_mode == 1u || (push_mode == 2u && ranks == 2u);
     auto peers_of = [&](GemmArgs &g, size_t region_offset) {  // the place of g.out in the other ranks' buffers
         g.peers = 0;
         if (!push) return;

@@ -25,12 +25,14 @@ def _gpu_count() -> int:
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("config,ranks,mode", [("tiny", 2, ""), ("small", 2, ""), ("small", 2, "staged"),
-                                               ("small", 2, "token-rows"), ("small", 2, "copy-rows"), ("small", 4, ""),
+                                               ("small", 2, "token-rows"), ("small", 2, "copy-rows"), ("small", 2, "push-rows"),
+                                               ("small", 4, "push-rows"), ("small", 4, ""),
                                                ("small", 8, "")])
 def test_ranks_match_oracle_and_single_gpu(config, ranks, mode):
     """Modes: "staged", the reduction kernel also normalizes and scales the row for the matvec behind it (off by
     default); "token-rows", prompt rows take the token path instead of batched passes across the ranks; "copy-rows",
-    a copy kernel moves the column slices of a batched pass instead of the contractions' own epilogues."""
+    a copy kernel moves every column slice of a batched pass; "push-rows", every contraction's own epilogue does (the
+    default between two ranks; more ranks use the copy kernel unless told otherwise)."""
     if _gpu_count() < ranks:
         pytest.skip(f"needs {ranks} GPUs")
     with socket.socket() as s:
@@ -39,7 +41,7 @@ def test_ranks_match_oracle_and_single_gpu(config, ranks, mode):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
            "127.0.0.1", "--master-port", str(port), str(Path(__file__).resolve()), config]
     env = dict(os.environ, STARK_B200_TP_STAGE=str(int(mode == "staged")), STARK_B200_TEST_TP_MODE=mode,
-               STARK_B200_TP_ROWS_PUSH=str(int(mode != "copy-rows")))
+               STARK_B200_TP_ROWS_PUSH={"copy-rows": "0", "push-rows": "1"}.get(mode, "2"))
     res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=900, env=env)
     failed = [line for line in res.stdout.splitlines() if "RANK-FAILED" in line]
     assert res.returncode == 0, "\n".join(failed) + res.stdout[-3000:] + res.stderr[-1500:]
