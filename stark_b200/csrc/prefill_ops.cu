@@ -724,14 +724,15 @@ stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_
                                         : column_tiles == 3u ? rows_attention_kernel<3> : rows_attention_kernel<4>;
         if (stark_b200_status s = ensure_dynamic_smem(fn, (int)smem, once_rows[column_tiles - 1u])) return s;
         SB_CUDA(launch_dependent(fn, dim3(1, a.kv_heads, splits), dim3(128), smem, stream, p));
-    } else if (gqa == 8u) {
-        p.row_blocks = 1;
+    } else if (gqa == 8u || (!splits && a.m > 16u && tunables().prefill_attn_warps == 8u)) {
+        p.row_blocks = 8u / gqa;  // 8 warps a CTA: a key / value tile serves 8 / gqa blocks of 16 rows
         if (splits) {
             if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<8, true>, (int)smem, once8s)) return s;
             SB_CUDA(launch_dependent(prefill_attention_kernel<8, true>, dim3(1, a.kv_heads, splits), dim3(256), smem, stream, p));
         } else {
             if (stark_b200_status s = ensure_dynamic_smem(prefill_attention_kernel<8, false>, (int)smem, once8)) return s;
-            prefill_attention_kernel<8, false><<<dim3((a.m + 15u) / 16u, a.kv_heads), 256, smem, stream>>>(p);
+            const uint32_t rows_per_cta = 16u * p.row_blocks;
+            prefill_attention_kernel<8, false><<<dim3((a.m + rows_per_cta - 1u) / rows_per_cta, a.kv_heads), 256, smem, stream>>>(p);
         }
     } else {
         p.row_blocks = 4u / gqa;
