@@ -148,6 +148,15 @@ stark_b200_status stark_b200_qmatrix_device_bytes(const stark_b200_qmatrix *matr
 stark_b200_status stark_b200_qmatrix_unpack_codes(const stark_b200_qmatrix *matrix, uint8_t *dst_host,
                                                   size_t count);
 
+/* Test-only: causal attention of `m` rows of a prompt pass over a paged cache (pages of 64 tokens; cache arrays
+ * [num_blocks][kv_heads][64][128] bf16, already holding the pass's own keys and values), all HOST arrays.  qkv is
+ * [m][(q_heads + 2 kv_heads) * 128] bf16 with the query heads normalized and rotated; out [m][q_heads * 128] bf16.
+ * variant 0: the mma.sync kernel, 1: the tcgen05 kernel (more than 16 rows).  Replaces nothing in the reference; it
+ * exposes attention_single_pass.rs:11-133 over many rows for the parity tests. */
+stark_b200_status stark_b200_op_prefill_attention(const void *qkv, const void *keys, const void *values,
+                                                  const int32_t *block_table, uint32_t num_blocks, void *out, uint32_t m,
+                                                  uint32_t first_pos, uint32_t q_heads, uint32_t kv_heads,
+                                                  uint32_t variant);
 /* Y[m, rows] = X[m, columns] * W^T for many rows at once (a prompt chunk) on the tensor cores: bf16 rows in
  * and out, f32 accumulation, a 4-bit affine matrix with a multiple of 32 rows (UNSUPPORTED otherwise); the
  * dequantized operand is rounded to bf16, as in the reference's own tiled GEMM.

@@ -157,6 +157,7 @@ def load() -> C.CDLL:
         "stark_b200_model_tp_connect": (u32, [vp, vp, sz]),
         "stark_b200_model_tp_set_wait": (u32, [vp, u64]),
         "stark_b200_model_tp_connect_unanswered": (u32, [vp]),
+        "stark_b200_op_prefill_attention": (u32, [vp, vp, vp, vp, u32, vp, u32, u32, u32, u32, u32]),
         "stark_b200_model_tp_rows_init": (u32, [vp, vp]),
         "stark_b200_model_tp_rows_connect": (u32, [vp, vp, sz]),
         "stark_b200_model_finalize": (u32, [vp]),

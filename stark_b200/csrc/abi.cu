@@ -1,5 +1,6 @@
 // extern "C" surface of libstark_b200.so (declared in include/stark_b200.h).
 // No exception crosses the boundary and nothing is printed.
+#include <cmath>
 #include <cstdlib>
 #include <mutex>
 #include <new>
@@ -438,6 +439,48 @@ stark_b200_status stark_b200_graph_destroy(stark_b200_graph **graph) {
         *graph = nullptr;
     }
     return STARK_B200_OK;
+}
+
+stark_b200_status stark_b200_op_prefill_attention(const void *qkv, const void *keys, const void *values,
+                                                  const int32_t *block_table, uint32_t num_blocks, void *out, uint32_t m,
+                                                  uint32_t first_pos, uint32_t q_heads, uint32_t kv_heads,
+                                                  uint32_t variant) {
+    if (!qkv || !keys || !values || !block_table || !out || m == 0 || num_blocks == 0 || kv_heads == 0 || q_heads == 0 ||
+        q_heads % kv_heads != 0 || variant > 1u)
+        return STARK_B200_INVALID_ARGUMENT;
+    if ((uint64_t)first_pos + m > (uint64_t)num_blocks * kPageTokens) return STARK_B200_CONTEXT_LIMIT;
+    for (uint32_t i = 0; i < num_blocks; ++i)
+        if (block_table[i] < 0 || (uint32_t)block_table[i] >= num_blocks) return STARK_B200_INVALID_ARGUMENT;
+    if (!device_context()) return STARK_B200_DEVICE_FAILURE;
+    const size_t heads = q_heads + 2u * (size_t)kv_heads;
+    const size_t qkv_bytes = (size_t)m * heads * kHeadDim * 2u, out_bytes = (size_t)m * q_heads * kHeadDim * 2u;
+    const size_t cache_bytes = (size_t)num_blocks * kv_heads * kPageTokens * kHeadDim * 2u;
+    uint16_t *dq = nullptr, *dk = nullptr, *dv = nullptr, *dout = nullptr;
+    int32_t *dtable = nullptr;
+    stark_b200_status st = STARK_B200_OK;
+    auto ok = [&](cudaError_t e) {
+        if (e != cudaSuccess && st == STARK_B200_OK) st = cuda_status(e);
+        return e == cudaSuccess;
+    };
+    if (ok(cudaMalloc(&dq, qkv_bytes)) && ok(cudaMalloc(&dk, cache_bytes)) && ok(cudaMalloc(&dv, cache_bytes)) &&
+        ok(cudaMalloc(&dout, out_bytes)) && ok(cudaMalloc(&dtable, (size_t)num_blocks * 4u)) &&
+        ok(cudaMemcpy(dq, qkv, qkv_bytes, cudaMemcpyHostToDevice)) && ok(cudaMemcpy(dk, keys, cache_bytes, cudaMemcpyHostToDevice)) &&
+        ok(cudaMemcpy(dv, values, cache_bytes, cudaMemcpyHostToDevice)) && ok(cudaMemset(dout, 0, out_bytes)) &&
+        ok(cudaMemcpy(dtable, block_table, (size_t)num_blocks * 4u, cudaMemcpyHostToDevice))) {
+        PrefillAttnArgs a{dq, KvLayer{dk, dv}, dtable, dout, m, first_pos, q_heads, kv_heads, 1.0f / sqrtf((float)kHeadDim)};
+        a.num_blocks = num_blocks;
+        st = variant == 1u ? prefill_attention_tc_launch(a, nullptr) : [&] {
+            a.num_blocks = 0;  // the mma.sync kernel
+            return prefill_attention_launch(a, nullptr);
+        }();
+        if (st == STARK_B200_OK && ok(cudaDeviceSynchronize())) ok(cudaMemcpy(out, dout, out_bytes, cudaMemcpyDeviceToHost));
+    }
+    cudaFree(dq);
+    cudaFree(dk);
+    cudaFree(dv);
+    cudaFree(dout);
+    cudaFree(dtable);
+    return st;
 }
 
 }  // extern "C"

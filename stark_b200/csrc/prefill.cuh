@@ -72,11 +72,18 @@ struct PrefillAttnArgs {
     // merged by a second launch; without it every (row block, KV head) is one CTA.
     float *partials = nullptr;
     uint32_t max_splits = 0;
+    // Pages the cache arrays hold (the extent of the tensor maps): with it, passes of more than 16 rows run on the
+    // tcgen05 tensor cores (prefill_attention_tc.cu); 0 keeps them on the mma.sync kernel.
+    uint32_t num_blocks = 0;
 };
 constexpr uint32_t kPrefillAttnMaxSplits = 64;
 inline size_t prefill_attention_partial_floats(uint32_t q_heads, uint32_t max_splits) {
     return (size_t)16u * q_heads * max_splits * (4u + 128u);
 }
 stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_t stream);
+// The same attention for more than 16 rows on the tcgen05 tensor cores (what prefill_attention_launch calls when the
+// arguments allow it and the tunable `prefill_attn_tc` is on).
+bool prefill_attention_tc_supports(const PrefillAttnArgs &a);
+stark_b200_status prefill_attention_tc_launch(const PrefillAttnArgs &a, cudaStream_t stream);
 
 }  // namespace sb

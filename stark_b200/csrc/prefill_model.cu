@@ -147,6 +147,7 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
         PrefillAttnArgs pa{m->chunk_qkv, L.kv, m->block_table, m->chunk_attn, mrows, first_pos, c.q_heads, c.kv_heads, scale};
         pa.partials = m->rows_attn_partials;
         pa.max_splits = kPrefillAttnMaxSplits;
+        pa.num_blocks = m->num_blocks;
         if ((st = prefill_attention_launch(pa, s)) != STARK_B200_OK) return st;
         if (tp && (st = gather(m->chunk_attn, attn_local, rows_region_attn(m), attn_width, rank * attn_local, attn_local,
                                true)) != STARK_B200_OK)

@@ -690,6 +690,7 @@ stark_b200_status prefill_attention_launch(const PrefillAttnArgs &a, cudaStream_
     if (!a.qkv || !a.kv.keys || !a.kv.values || !a.block_table || !a.out || a.m == 0) return STARK_B200_INVALID_ARGUMENT;
     if (a.kv_heads == 0 || a.q_heads % a.kv_heads != 0) return STARK_B200_UNSUPPORTED;
     const uint32_t gqa = a.q_heads / a.kv_heads;
+    if (a.m > 16u && tunables().prefill_attn_tc && prefill_attention_tc_supports(a)) return prefill_attention_tc_launch(a, stream);
     if (gqa != 1u && gqa != 2u && gqa != 4u && gqa != 8u) return STARK_B200_UNSUPPORTED;
     PrefillAttnParams p{};
     p.qkv = a.qkv;

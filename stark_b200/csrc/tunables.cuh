@@ -20,6 +20,8 @@ struct Tunables {
     uint32_t gemm_stop_after;     // STARK_B200_GEMM_STOP_AFTER  bring-up aid of the tensor-core contraction (0: whole kernel)
     uint32_t prefill_min_rows;    // STARK_B200_PREFILL_MIN_ROWS fewest cache-only rows worth a batched pass
     uint32_t tp_stage;            // STARK_B200_TP_STAGE         1: the tensor-parallel reduction also prepares the next matvec's input (one CTA; measured slower)
+    uint32_t prefill_attn_tc;     // STARK_B200_PREFILL_ATTN_TC  1: attention of a prompt pass (more than 16 rows) on the tcgen05 tensor cores, 0: mma.sync
+    uint32_t attn_tc_stop_after;  // STARK_B200_ATTN_TC_STOP_AFTER bring-up aid of that kernel (0: whole kernel)
     uint32_t prefill_attn_warps;  // STARK_B200_PREFILL_ATTN_WARPS warps of a prompt pass's attention CTA (4 or 8): rows that share a key / value tile
     uint32_t gemm_half_tiles;     // STARK_B200_GEMM_HALF_TILES  128-row tiles in the prompt contraction: 0 never, 1 where 256-row tiles leave SMs idle, 2 always
     uint32_t tp_rows_push;        // STARK_B200_TP_ROWS_PUSH     a prompt pass's contractions store their tiles to the other ranks themselves: 1 always, 2 between two ranks only, 0 never (a copy kernel after each)
