@@ -29,7 +29,7 @@ const Entry kEntries[] = {
     {"rows_matvec", "STARK_B200_ROWS_MATVEC", &Tunables::rows_matvec, 1u, 0u, 1u},
     {"rows_attention", "STARK_B200_ROWS_ATTENTION", &Tunables::rows_attention, 1u, 0u, 1u},
     {"tp_stage", "STARK_B200_TP_STAGE", &Tunables::tp_stage, 0u, 0u, 1u},
-    {"prefill_attn_tc", "STARK_B200_PREFILL_ATTN_TC", &Tunables::prefill_attn_tc, 0u, 0u, 1u},
+    {"prefill_attn_tc", "STARK_B200_PREFILL_ATTN_TC", &Tunables::prefill_attn_tc, 1u, 0u, 1u},
     {"attn_tc_stop_after", "STARK_B200_ATTN_TC_STOP_AFTER", &Tunables::attn_tc_stop_after, 0u, 0u, 2u},
     {"prefill_attn_warps", "STARK_B200_PREFILL_ATTN_WARPS", &Tunables::prefill_attn_warps, 4u, 4u, 8u},
     {"gemm_half_tiles", "STARK_B200_GEMM_HALF_TILES", &Tunables::gemm_half_tiles, 1u, 0u, 2u},

@@ -157,7 +157,9 @@ def test_chunked_prefill_against_the_oracle():
         model.step_async(int(t))
         want = oracle.step(int(t))
         agree += int(model.argmax() == O.argmax_bf16(want))
-        near += int(pick_near_top(want, model.argmax()))
+        # the engine's logits sit about one bf16 step (rmse) from the oracle's, so two near-tied tokens can trade
+        # places when they are up to two steps apart
+        near += int(pick_near_top(want, model.argmax(), steps=2.0))
     assert near / steps >= 0.99 and agree / steps >= 0.90, (agree, near)
     model.close()
 
