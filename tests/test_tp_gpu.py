@@ -35,14 +35,19 @@ def test_ranks_match_oracle_and_single_gpu(config, ranks, mode):
     default between two ranks; more ranks use the copy kernel unless told otherwise)."""
     if _gpu_count() < ranks:
         pytest.skip(f"needs {ranks} GPUs")
-    with socket.socket() as s:
-        s.bind(("127.0.0.1", 0))
-        port = s.getsockname()[1]
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
-           "127.0.0.1", "--master-port", str(port), str(Path(__file__).resolve()), config]
     env = dict(os.environ, STARK_B200_TP_STAGE=str(int(mode == "staged")), STARK_B200_TEST_TP_MODE=mode,
                STARK_B200_TP_ROWS_PUSH={"copy-rows": "0", "push-rows": "1"}.get(mode, "2"))
-    res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=900, env=env)
+    for attempt in range(2):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", str(ranks), "--master-addr",
+               "127.0.0.1", "--master-port", str(port), str(Path(__file__).resolve()), config]
+        res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=900, env=env)
+        # A rank that fails says so itself (RANK-FAILED).  A launch that dies without any rank's word -- the port
+        # found above taken by someone else before the launcher bound it -- is tried once more on another port.
+        if res.returncode == 0 or "RANK-FAILED" in res.stdout:
+            break
     failed = [line for line in res.stdout.splitlines() if "RANK-FAILED" in line]
     assert res.returncode == 0, "\n".join(failed) + res.stdout[-3000:] + res.stderr[-1500:]
     assert "TP-OK" in res.stdout
