@@ -753,8 +753,15 @@ stark_b200_status model_finalize(Model *m) {
     // a recording), on a scratch position; then record both sequences.
     stark_b200_status st = model_reset(m);
     if (st != STARK_B200_OK) return st;
-    if ((st = issue_token(m, true, nullptr)) != STARK_B200_OK) return st;
-    if ((st = issue_token(m, false, nullptr)) != STARK_B200_OK) return st;
+    // Tensor parallel: this first pass is where every rank's kernels are loaded, and on a machine that has not run
+    // the library yet one rank can take seconds longer over that than another.  That is start-up skew, not a peer
+    // that left: the first pass waits a minute for its peers; the recorded sequences keep the configured limit.
+    const unsigned long long configured_wait = m->tp.wait_ns;
+    if (m->tp.size > 1u && !m->tp_stand_ins) m->tp.wait_ns = std::max<unsigned long long>(configured_wait, 60000000000ull);
+    st = issue_token(m, true, nullptr);
+    if (st == STARK_B200_OK) st = issue_token(m, false, nullptr);
+    m->tp.wait_ns = configured_wait;
+    if (st != STARK_B200_OK) return st;
     SB_CUDA(cudaStreamSynchronize(m->stream));
     if ((st = capture(m, true, &m->step_graph, &m->step_launches)) != STARK_B200_OK) return st;
     if ((st = capture(m, false, &m->ingest_graph, &m->ingest_launches)) != STARK_B200_OK) return st;

@@ -112,9 +112,13 @@ stark_b200_status model_rows_pass(Model *m, const uint32_t *tokens_device, uint3
             if (r != rank) g.peer_out[g.peers++] = reinterpret_cast<uint16_t *>(m->tp_rows.base[r] + region_offset);
     };
     uint32_t gathers = 0;
+    // a rank group's first pass loads these kernels and allocates the row buffers: start-up skew between ranks is
+    // given a minute, later passes the configured limit
+    const unsigned long long rows_wait =
+        m->tp_rows_ticket == 0 ? std::max<unsigned long long>(m->tp.wait_ns, 60000000000ull) : m->tp.wait_ns;
     auto gather = [&](const uint16_t *src, uint32_t src_ld, size_t dst_offset, uint32_t dst_ld, uint32_t column,
                       uint32_t width, bool own) -> stark_b200_status {
-        m->tp_rows.wait_ns = m->tp.wait_ns;
+        m->tp_rows.wait_ns = rows_wait;
         TpGatherArgs ga{src, src_ld, dst_offset, dst_ld, column, width, mrows, own, ++m->tp_rows_ticket};
         ++gathers;
         return tp_rows_gather_launch(m->tp_rows, ga, m->tp_rows_arrive, ctx->error_word, s);
