@@ -939,7 +939,13 @@ stark_b200_status moe_token(MoeModel *m, bool want_logits) {
     const int k = want_logits ? 1 : 0;
     if (!m->warmed[k]) {
         m->warmed[k] = true;
-        return moe_issue(m, want_logits, m->stream);
+        // The first token of a kind runs eagerly and loads its kernels: between ranks that is start-up skew, not a
+        // rank that left, so its waits get a minute; the recorded graphs keep the configured limit.
+        const unsigned long long configured_wait = m->ep.wait_ns;
+        if (m->ep.ranks > 1u) m->ep.wait_ns = std::max<unsigned long long>(configured_wait, 60000000000ull);
+        const stark_b200_status st = moe_issue(m, want_logits, m->stream);
+        m->ep.wait_ns = configured_wait;
+        return st;
     }
     if (!m->graph[k]) {
         cudaGraph_t g = nullptr;
