@@ -284,6 +284,27 @@ def attention_decode(qkv: np.ndarray, keys: np.ndarray, values: np.ndarray, q_he
     return out
 
 
+def prompt_attention(qkv: np.ndarray, keys: np.ndarray, values: np.ndarray, block_table: np.ndarray, first_pos: int,
+                     q_heads: int, kv_heads: int, tensor_memory: bool = True) -> np.ndarray:
+    """Causal attention of the rows of one prompt pass over a paged cache (attention_single_pass.rs:11-133, many rows).
+
+    qkv: ``uint16[m, q_heads + 2 kv_heads, 128]`` with the query heads already normalized and rotated; keys / values:
+    ``uint16[pages, kv_heads, 64, 128]`` holding positions ``0 .. first_pos + m - 1`` (the pass's own rows included)
+    through ``block_table`` (``int32[pages]``: logical page -> physical page).  ``tensor_memory`` selects the tcgen05
+    kernel (more than 16 rows) over the mma.sync one.  Returns ``uint16[m, q_heads, 128]``.
+    """
+    qkv = np.ascontiguousarray(qkv, np.uint16)
+    keys, values = np.ascontiguousarray(keys, np.uint16), np.ascontiguousarray(values, np.uint16)
+    table = np.ascontiguousarray(block_table, np.int32)
+    m = qkv.shape[0]
+    assert qkv.shape[1:] == (q_heads + 2 * kv_heads, 128) and keys.shape == values.shape == (len(table), kv_heads, 64, 128)
+    out = np.zeros((m, q_heads, 128), np.uint16)
+    check(_lib.load().stark_b200_op_prefill_attention(_ptr(qkv), _ptr(keys), _ptr(values), _ptr(table), len(table),
+                                                      _ptr(out), m, int(first_pos), q_heads, kv_heads,
+                                                      1 if tensor_memory else 0), "op_prefill_attention")
+    return out
+
+
 # ----------------------------------------------------------------------------- GGUF / 8-bit matrices, expert banks
 
 def _qmatrix_from_gguf(blocks: np.ndarray, kind: int, rows: int, columns: int, experts: int = 0) -> QMatrix:

@@ -1,13 +1,11 @@
 """Causal attention of a prompt pass over the paged cache, operator by operator: the mma.sync kernel and the tcgen05
 kernel against an f64 restatement of attention_single_pass.rs:11-133 (scores q.k / sqrt(d) over the keys a row may
 see, softmax, probability-weighted values) and against each other."""
-import ctypes as C
-
 import numpy as np
 import pytest
 
 from oracle import oracle as O
-from stark_b200 import _lib, synthetic as S
+from stark_b200 import synthetic as S
 
 PAGE, DIM = 64, 128
 
@@ -44,12 +42,9 @@ def _reference(qkv, k, v, m, first_pos, q_heads, kv_heads):
 
 
 def _run(qkv, keys, values, table, m, first_pos, q_heads, kv_heads, variant):
-    out = np.zeros((m, q_heads, DIM), np.uint16)
-    _lib.check(_lib.load().stark_b200_op_prefill_attention(
-        qkv.ctypes.data, keys.ctypes.data, values.ctypes.data, table.ctypes.data, len(table), out.ctypes.data, m,
-        first_pos, q_heads, kv_heads, variant), "op_prefill_attention")
-    from stark_b200.ops import take_device_error
-    assert take_device_error() == 0
+    from stark_b200.ops import prompt_attention, take_device_error
+    out = prompt_attention(qkv, keys, values, table, first_pos, q_heads, kv_heads, tensor_memory=bool(variant))
+    assert out.shape == (m, q_heads, DIM) and take_device_error() == 0
     return O.bf16_to_f32(out).astype(np.float64)
 
 

@@ -183,17 +183,21 @@ def _leaver(rank: int, port: int, results):
         dist.all_gather_object(out, blob)
         return out
 
+    def report_and_leave(message: str):
+        results.put(message)
+        results.close()
+        results.join_thread()  # the queue's feeder thread has written the message: an abrupt exit cannot lose it
+        os._exit(0)
+
     tp = TensorParallel(rank, 2, all_gather)
     assert tp.all_gather(b"request 1") == [b"request 1", b"request 1"]   # both ranks open the first request
     if rank == 1:
-        results.put("rank 1 left between requests")
-        os._exit(0)                                                     # no kernel in flight: a host-side leave
+        report_and_leave("rank 1 left between requests")                # no kernel in flight: a host-side leave
     try:
         tp.all_gather(b"request 2")
-        results.put("rank 0 was not told")
+        report_and_leave("rank 0 was not told")
     except Exception as e:  # noqa: BLE001 - gloo reports a closed connection or a timeout
-        results.put(f"rank 0 learned of it on the host: {type(e).__name__}")
-    os._exit(0)
+        report_and_leave(f"rank 0 learned of it on the host: {type(e).__name__}")
 
 
 def test_a_rank_that_leaves_between_requests_is_noticed_on_the_host():
