@@ -468,11 +468,8 @@ stark_b200_status stark_b200_op_prefill_attention(const void *qkv, const void *k
         ok(cudaMemcpy(dv, values, cache_bytes, cudaMemcpyHostToDevice)) && ok(cudaMemset(dout, 0, out_bytes)) &&
         ok(cudaMemcpy(dtable, block_table, (size_t)num_blocks * 4u, cudaMemcpyHostToDevice))) {
         PrefillAttnArgs a{dq, KvLayer{dk, dv}, dtable, dout, m, first_pos, q_heads, kv_heads, 1.0f / sqrtf((float)kHeadDim)};
-        a.num_blocks = num_blocks;
-        st = variant == 1u ? prefill_attention_tc_launch(a, nullptr) : [&] {
-            a.num_blocks = 0;  // the mma.sync kernel
-            return prefill_attention_launch(a, nullptr);
-        }();
+        a.num_blocks = variant == 1u ? num_blocks : 0u;  // without the cache's extent: the mma.sync kernel
+        st = variant == 1u ? prefill_attention_tc_launch(a, nullptr) : prefill_attention_launch(a, nullptr);
         if (st == STARK_B200_OK && ok(cudaDeviceSynchronize())) ok(cudaMemcpy(out, dout, out_bytes, cudaMemcpyDeviceToHost));
     }
     cudaFree(dq);
