@@ -19,9 +19,10 @@ object; every request gets exactly one terminal reply, in order; a fencing error
 
 The request layer talks to a backend object (``vocab_size``, ``max_context_length``, ``eos_token_ids``,
 ``tokenize``, ``decode``, ``begin`` / ``next_token``, ``score``), the image of the reference's crate-private
-``GenerationBackend`` / ``ScoringBackend`` traits; ``B200Backend`` implements it over ``DenseModel``.  Images,
-MTP scheduling selectors and chat templates belong to the reference's product shell and are answered with the
-reference's own refusals (``images_not_supported``, ``mtp_not_supported``).
+``GenerationBackend`` / ``ScoringBackend`` traits; ``B200Backend`` implements it over ``DenseModel``.  The
+``mtp`` / ``mtp_drafts`` / ``mtp_policy`` / ``mtp_lookup`` selectors are resolved as the reference resolves them and
+served when the model carries a draft head (``mtp_not_supported`` otherwise); images and chat templates belong to
+the reference's product shell and are answered with its own refusals (``images_not_supported``).
 """
 from __future__ import annotations
 
