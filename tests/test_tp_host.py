@@ -129,6 +129,16 @@ def _worker(rank: int, ranks: int, port: int, failures):
             full = _mv(F[name], a)
             np.testing.assert_allclose(total, full, rtol=0, atol=2e-5 * np.abs(full).max() + 1e-6)
 
+        # prompt passes: the row cuts of o and down produce whole output elements over the full width, so the
+        # ranks' slices of several rows only have to be gathered -- no sum, the same bits as unsharded
+        rows = rng.standard_normal((3, hq * hd)).astype(np.float32)
+        for name, inputs in (("o", rows), ("down", rng.standard_normal((3, inter)).astype(np.float32))):
+            mine = np.stack([_mv(L[name + "_rows"], a) for a in inputs])          # [3, hidden / ranks]
+            slices = [np.frombuffer(b, np.float32).reshape(3, -1) for b in tp.all_gather(mine.tobytes())]
+            gathered = np.concatenate(slices, axis=1)
+            full = np.stack([_mv(F[name], a) for a in inputs])
+            assert np.array_equal(gathered.view(np.uint32), full.view(np.uint32))
+
         # vocabulary split: (max, first index) per shard reduces to the unsharded greedy token
         h = rng.standard_normal(cfg["hidden"]).astype(np.float32)
         full = O.f32_to_bf16(_mv(w["lm_head"], h))
