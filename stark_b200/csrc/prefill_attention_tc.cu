@@ -50,9 +50,9 @@ __device__ inline float ex2_approx(float x) {
 }
 
 // x = hi + lo with both parts bf16 by TRUNCATION: hi is the upper half of x's bits, lo the upper half of the exact
-// remainder x - hi.  What is dropped is below 2^-16 of x, the same order as two round-to-nearest conversions keep, and
-// the split costs logic and adds only: conversions share the special-function unit's issue rate with the exponential,
-// which is what bounds this kernel's second pass.
+// remainder x - hi.  What is dropped is below 2^-14 of x (two round-to-nearest conversions would keep 2^-16), always
+// downwards: 2^-15 of the output on average, against the 2^-9 of its own bf16 rounding.  The split costs logic and
+// adds only, no conversion instructions.
 __device__ inline void split_trunc_bf16x2(float x, float y, uint32_t &hi, uint32_t &lo) {
     const uint32_t xb = __float_as_uint(x), yb = __float_as_uint(y);
     const float xr = x - __uint_as_float(xb & 0xffff0000u), yr = y - __uint_as_float(yb & 0xffff0000u);
