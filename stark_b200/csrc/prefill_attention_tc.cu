@@ -49,17 +49,6 @@ __device__ inline float ex2_approx(float x) {
     return y;
 }
 
-// x = hi + lo with both parts bf16 by TRUNCATION: hi is the upper half of x's bits, lo the upper half of the exact
-// remainder x - hi.  What is dropped is below 2^-14 of x (two round-to-nearest conversions would keep 2^-16), always
-// downwards: 2^-15 of the output on average, against the 2^-9 of its own bf16 rounding.  The split costs logic and
-// adds only, no conversion instructions.
-__device__ inline void split_trunc_bf16x2(float x, float y, uint32_t &hi, uint32_t &lo) {
-    const uint32_t xb = __float_as_uint(x), yb = __float_as_uint(y);
-    const float xr = x - __uint_as_float(xb & 0xffff0000u), yr = y - __uint_as_float(yb & 0xffff0000u);
-    hi = __byte_perm(xb, yb, 0x7632);  // (y's upper half) << 16 | x's upper half
-    lo = __byte_perm(__float_as_uint(xr), __float_as_uint(yr), 0x7632);
-}
-
 struct TcAttnParams {
     uint16_t *out;
     const int32_t *block_table;
@@ -293,7 +282,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                         }
                         l += e0;
                         l += e1;
-                        split_trunc_bf16x2(e0, e1, hi[i >> 1], lo[i >> 1]);
+                        split_bf16x2(e0, e1, hi[i >> 1], lo[i >> 1]);
                     }
                     // the previous step's second product must have read P before it is overwritten
                     if (c == 0u && !(ok = mbar_wait_bounded(p_free, (j & 1u) ^ 1u, abort_flag))) break;
